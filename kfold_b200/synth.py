@@ -1,0 +1,153 @@
+"""Seeded synthetic inputs and random-init weights for the hot-path operators.
+
+K-Fold ships no public test vectors and its released weights are not available
+offline, so every test and benchmark here runs on synthetic data: activations
+``~ N(0,1)``, every 2-D weight ``~ N(0, 1/fan_in)`` (including the ones the
+reference zero-initialises, which would make every output identically zero),
+LayerNorm scales near one.  All values come from ``numpy.random.RandomState``,
+whose stream is frozen across numpy versions, so the same seed gives the same
+bits on every machine.  Tensors are created on the CPU in float32; callers move
+them to the device.
+
+Weight dictionaries are keyed exactly like the ``state_dict()`` of the
+reference module of the same name.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+class _Rng:
+    def __init__(self, seed: int):
+        self.rs = np.random.RandomState(seed)
+
+    def normal(self, *shape, std: float = 1.0) -> torch.Tensor:
+        return torch.from_numpy((self.rs.standard_normal(shape) * std).astype(np.float32))
+
+    def linear(self, out_f: int, in_f: int) -> torch.Tensor:
+        return self.normal(out_f, in_f, std=in_f ** -0.5)
+
+    def ln_w(self, n: int) -> torch.Tensor:
+        return 1.0 + self.normal(n, std=0.1)
+
+    def ln_b(self, n: int) -> torch.Tensor:
+        return self.normal(n, std=0.1)
+
+
+def _prefixed(prefix: str, d: dict) -> dict:
+    return {f"{prefix}.{k}": v for k, v in d.items()}
+
+
+def trimul_weights(rng: _Rng, c: int) -> dict:
+    """TriangleMultiplication{Outgoing,Incoming} (model/primitives/triangle_multiplication.py:171-177)."""
+    return {
+        "layernorm_in.weight": rng.ln_w(c), "layernorm_in.bias": rng.ln_b(c),
+        "linear_p_in.weight": rng.linear(2 * c, c), "linear_g_in.weight": rng.linear(2 * c, c),
+        "layernorm_out.weight": rng.ln_w(c), "layernorm_out.bias": rng.ln_b(c),
+        "linear_p_out.weight": rng.linear(c, c), "linear_g_out.weight": rng.linear(c, c),
+    }
+
+
+def triatt_weights(rng: _Rng, c: int, heads: int) -> dict:
+    """TriangleAttention (model/primitives/triangle_attention.py:338-373)."""
+    hd = c  # c_hidden * heads == c_in
+    return {
+        "layer_norm.weight": rng.ln_w(c), "layer_norm.bias": rng.ln_b(c),
+        "linear.weight": rng.linear(heads, c),
+        "mha.linear_q.weight": rng.linear(hd, c), "mha.linear_k.weight": rng.linear(hd, c),
+        "mha.linear_v.weight": rng.linear(hd, c), "mha.linear_o.weight": rng.linear(c, hd),
+        "mha.linear_g.weight": rng.linear(hd, c),
+    }
+
+
+def transition_weights(rng: _Rng, c: int, factor: int) -> dict:
+    """Transition (model/layers/folding/transition.py:27-46)."""
+    return {
+        "layernorm.weight": rng.ln_w(c), "layernorm.bias": rng.ln_b(c),
+        "swiglu.linear.weight": rng.linear(2 * c * factor, c),
+        "linear_out.weight": rng.linear(c, c * factor),
+    }
+
+
+def adaln_weights(rng: _Rng, c_a: int, c_s: int) -> dict:
+    """AdaLN (model/primitives/normalization.py:99-115)."""
+    return {
+        "layernorm_s.weight": rng.ln_w(c_s),
+        "linear_g.weight": rng.linear(c_a, c_s), "linear_g.bias": rng.normal(c_a, std=0.1),
+        "linear_bias.weight": rng.linear(c_a, c_s),
+    }
+
+
+def apb_weights(rng: _Rng, c_a: int, c_s: int | None) -> dict:
+    """SelfAttentionPairBias (model/layers/folding/attention_pair_bias.py:57-112)."""
+    w = {
+        "linear_q.weight": rng.linear(c_a, c_a), "linear_q.bias": rng.normal(c_a, std=0.1),
+        "linear_k.weight": rng.linear(c_a, c_a), "linear_v.weight": rng.linear(c_a, c_a),
+        "linear_g.weight": rng.linear(c_a, c_a), "linear_out.weight": rng.linear(c_a, c_a),
+    }
+    if c_s is None:
+        w["layernorm_a.weight"] = rng.ln_w(c_a)
+        w["layernorm_a.bias"] = rng.ln_b(c_a)
+    else:
+        w.update(_prefixed("adaln_a", adaln_weights(rng, c_a, c_s)))
+        w["linear_ada_out.weight"] = rng.linear(c_a, c_s)
+        w["linear_ada_out.bias"] = rng.normal(c_a, std=0.1) - 2.0
+    return w
+
+
+def conditioned_transition_weights(rng: _Rng, c_a: int, c_s: int, factor: int = 2) -> dict:
+    """ConditionedTransitionBlock (model/layers/folding/diffusion_transformer.py:50-71)."""
+    w = _prefixed("adaln", adaln_weights(rng, c_a, c_s))
+    w["swiglu.linear.weight"] = rng.linear(2 * c_a * factor, c_a)
+    w["linear_g.weight"] = rng.linear(c_a, c_s)
+    w["linear_g.bias"] = rng.normal(c_a, std=0.1) - 2.0
+    w["linear_out.weight"] = rng.linear(c_a, c_a * factor)
+    return w
+
+
+def pairformer_block_weights(seed: int, c_z: int = 128, c_s: int = 384, tri_heads: int = 4,
+                             single_heads: int = 16) -> dict:
+    """All weights of the composite Pairformer block (pair track + single track)."""
+    rng = _Rng(seed)
+    w = {}
+    w.update(_prefixed("tri_mul_out", trimul_weights(rng, c_z)))
+    w.update(_prefixed("tri_mul_in", trimul_weights(rng, c_z)))
+    w.update(_prefixed("tri_att_start", triatt_weights(rng, c_z, tri_heads)))
+    w.update(_prefixed("tri_att_end", triatt_weights(rng, c_z, tri_heads)))
+    w.update(_prefixed("transition_z", transition_weights(rng, c_z, 4)))
+    w["layernorm_z.weight"] = rng.ln_w(c_z)
+    w["layernorm_z.bias"] = rng.ln_b(c_z)
+    w["linear_pair_bias.weight"] = rng.linear(single_heads, c_z)
+    w.update(_prefixed("attention", apb_weights(rng, c_s, None)))
+    w.update(_prefixed("transition", transition_weights(rng, c_s, 4)))
+    return w
+
+
+def token_mask(n: int, valid: int | None = None, pad_frac: float | None = None) -> torch.Tensor:
+    """Boolean token mask with a trailing padding tail (how K-Fold pads, inference/data_pipeline.py:129-134)."""
+    if valid is None:
+        valid = n if pad_frac is None else n - int(pad_frac * n)
+    m = torch.zeros(n, dtype=torch.bool)
+    m[:valid] = True
+    return m
+
+
+def pair_inputs(seed: int, n: int, c_z: int = 128, batch: int = 1, valid: int | None = None,
+                pad_frac: float | None = None):
+    """z ~ N(0,1) of shape (B,N,N,C) and the outer-product pair mask (B,N,N) bool."""
+    rng = _Rng(seed + 7919)
+    z = rng.normal(batch, n, n, c_z)
+    m = token_mask(n, valid, pad_frac)
+    pm = (m[:, None] & m[None, :]).unsqueeze(0).expand(batch, n, n).contiguous()
+    return z, pm, m.unsqueeze(0).expand(batch, n).contiguous()
+
+
+def single_inputs(seed: int, n: int, c_s: int = 384, batch: int = 1) -> torch.Tensor:
+    return _Rng(seed + 104729).normal(batch, n, c_s)
+
+
+def block_mask(seed: int, batch: int, n: int) -> torch.Tensor:
+    """A general, non-separable (B,N,N) mask like the Apo stack's (model/modules/apo_module.py:322-330)."""
+    rs = np.random.RandomState(seed + 31)
+    return torch.from_numpy(rs.rand(batch, n, n) > 0.2)

@@ -1,0 +1,260 @@
+"""CPU oracle for the Pairformer / diffusion hot path.  TEST INFRASTRUCTURE ONLY.
+
+This file restates, in plain PyTorch on the CPU, the arithmetic that K-Fold's
+``kernel_backend="torch"`` path performs for the operators this repository
+accelerates.  Nothing under ``kfold_b200/`` may import it: it exists so that
+tests, the smoke check and the CPU-baseline leg of the benchmark have an
+independent result to compare the CUDA kernels against.
+
+Parity is pinned: ``tests/golden/make_golden.py`` runs the real reference
+modules (imported from the K-Fold source tree) on seeded inputs, stores their
+outputs under ``tests/golden/``, and ``tests/test_oracle_golden.py`` checks every
+function here against those vectors.
+
+Every function takes a flat ``dict`` of weights keyed exactly like the
+``state_dict()`` of the reference module it follows, so a reference module's
+weights drop straight in.
+
+``mode`` selects the arithmetic:
+  * ``"fp32"``  -- everything in float32 (ground truth).
+  * ``"bf16"``  -- rounds to bfloat16 at the points where the reference rounds
+    when it runs under ``torch.autocast("cuda", dtype=torch.bfloat16)``:
+    linear / matmul / einsum outputs are bf16 (fp32 accumulate), LayerNorm and
+    softmax are computed in fp32 and LayerNorm is rounded back to the input
+    dtype.  Used to report the reference's own bf16 noise floor.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+__all__ = [
+    "layer_norm",
+    "triangle_multiplication",
+    "triangle_attention",
+    "attention_pair_bias",
+    "self_attention_pair_bias",
+    "adaln",
+    "transition",
+    "conditioned_transition",
+    "pairformer_block",
+    "triangular_block",
+    "sub",
+]
+
+
+def sub(weights: dict, prefix: str) -> dict:
+    """Select ``prefix.*`` from a flat state dict and strip the prefix."""
+    p = prefix + "."
+    return {k[len(p):]: v for k, v in weights.items() if k.startswith(p)}
+
+
+class _Mode:
+    def __init__(self, mode: str):
+        if mode not in ("fp32", "bf16"):
+            raise ValueError(f"unknown oracle mode {mode!r}")
+        self.bf16 = mode == "bf16"
+
+    def r(self, t: torch.Tensor) -> torch.Tensor:
+        """Round to the compute dtype (identity in fp32 mode), stay float32."""
+        return t.to(torch.bfloat16).float() if self.bf16 else t
+
+    def linear(self, x, w, b=None):
+        # autocast casts inputs and weights to bf16, accumulates fp32, rounds the result
+        out = F.linear(self.r(x), self.r(w), None if b is None else self.r(b))
+        return self.r(out)
+
+
+def layer_norm(x, weight, bias, eps: float = 1e-5, mode: str = "fp32"):
+    """``LayerNorm.forward`` -- model/primitives/normalization.py:61-91.
+
+    Statistics and affine in fp32 whatever the input dtype; the result is cast
+    back to the input dtype (which is bf16 inside a bf16 pipeline).
+    """
+    m = _Mode(mode)
+    out = F.layer_norm(x.float(), (x.shape[-1],), weight, bias, eps)
+    return m.r(out)
+
+
+def triangle_multiplication(x, mask, w: dict, direction: str, mode: str = "fp32", eps: float = 1e-5):
+    """``TriangleMultiplication{Outgoing,Incoming}.forward`` --
+    model/primitives/triangle_multiplication.py:179-229 and :263-313.
+
+    x (B,N,N,C); mask (B,N,N); returns the update (the caller adds it to x).
+    """
+    m = _Mode(mode)
+    x = m.r(x.float())
+    xn = layer_norm(x, w["layernorm_in.weight"], w["layernorm_in.bias"], eps, mode)
+    ab = m.r(m.linear(xn, w["linear_p_in.weight"]) * torch.sigmoid(m.linear(xn, w["linear_g_in.weight"])))
+    ab = m.r(ab * mask.unsqueeze(-1).to(ab.dtype))
+    a, b = torch.chunk(ab, 2, dim=-1)
+    if direction == "outgoing":
+        t = torch.einsum("bikd,bjkd->bijd", a, b)      # :224
+    elif direction == "incoming":
+        t = torch.einsum("bkid,bkjd->bijd", a, b)      # :308
+    else:
+        raise ValueError(f"unknown direction {direction!r}")
+    t = m.r(t)  # einsum is autocast to bf16 although its inputs were .float()
+    tn = layer_norm(t, w["layernorm_out.weight"], w["layernorm_out.bias"], eps, mode)
+    out = m.linear(tn, w["linear_p_out.weight"]) * torch.sigmoid(m.linear(xn, w["linear_g_out.weight"]))
+    return m.r(out)
+
+
+def triangle_attention(x, mask, w: dict, num_heads: int, starting: bool, mode: str = "fp32",
+                       inf: float = 1e9, eps: float = 1e-5):
+    """``TriangleAttention.forward`` + ``MultiHeadAttention.forward`` --
+    model/primitives/triangle_attention.py:375-434 and :285-335.
+
+    x (*,I,J,C); mask (*,I,J) or None.  Ending node = starting node on the
+    transposed pair representation (:400-402), transposed back (:431-432).
+    """
+    m = _Mode(mode)
+    x = m.r(x.float())
+    if mask is None:
+        mask = x.new_ones(x.shape[:-1])
+    if not starting:
+        x = x.transpose(-2, -3)
+        mask = mask.transpose(-1, -2)
+    H = num_heads
+    C = x.shape[-1]
+    D = C // H
+    xn = layer_norm(x, w["layer_norm.weight"], w["layer_norm.bias"], eps, mode)
+    # bias[..., h, j, k] = linear(xn)[..., j, k, h]                (:416-422)
+    tri_bias = m.linear(xn, w["linear.weight"]).movedim(-1, -3).unsqueeze(-4)
+    q = m.linear(xn, w["mha.linear_q.weight"])
+    k = m.linear(xn, w["mha.linear_k.weight"])
+    v = m.linear(xn, w["mha.linear_v.weight"])
+    q, k, v = (t.unflatten(-1, (H, D)).transpose(-2, -3) for t in (q, k, v))   # (*,I,H,J,D)
+    q = m.r(q / math.sqrt(D))                                                    # :264-265
+    mask_bias = -inf * (~mask.bool()).to(q.dtype)[..., :, None, None, :]        # (*,I,1,1,J)  :328
+    a = m.r(torch.matmul(q, k.transpose(-1, -2)))                               # (*,I,H,J,J)  :139
+    a = m.r(a + mask_bias)
+    a = m.r(a + tri_bias)
+    a = a.softmax(dim=-1)       # CUDA autocast runs softmax in fp32 and keeps it fp32
+    o = m.r(torch.matmul(m.r(a), v))                                            # :149
+    o = o.transpose(-2, -3)                                                      # (*,I,J,H,D)
+    g = torch.sigmoid(m.linear(xn, w["mha.linear_g.weight"])).unflatten(-1, (H, D))
+    o = m.r(o * g).flatten(-2)                                                   # :269-278
+    out = m.linear(o, w["mha.linear_o.weight"])                                  # :281
+    if not starting:
+        out = out.transpose(-2, -3)
+    return out
+
+
+def attention_pair_bias(x_q, x_k, pair_bias, mask, w: dict, num_heads: int, mode: str = "fp32",
+                        inf: float = 1e9):
+    """``attention_pair_bias`` with the torch kernel --
+    model/primitives/attention.py:28-94 and ``torch_attention_pair_bias`` :239-271,
+    ``_attention`` :122-168.  Inputs are already normalised.
+
+    x_q (*,Lq,c); x_k (*,Lk,c); pair_bias broadcastable to (*,H,Lq,Lk);
+    mask broadcastable to (*,Lk).  The logits and softmax are fp32 in every mode.
+    """
+    m = _Mode(mode)
+    H = num_heads
+    c = x_q.shape[-1]
+    D = c // H
+    x_q = m.r(x_q.float())
+    x_k = m.r(x_k.float())
+    q = m.linear(x_q, w["linear_q.weight"], w.get("linear_q.bias"))
+    k = m.linear(x_k, w["linear_k.weight"])
+    v = m.linear(x_k, w["linear_v.weight"])
+    q, k, v = (t.unflatten(-1, (H, D)).transpose(-2, -3) for t in (q, k, v))    # (*,H,L,D)
+    bias = pair_bias.float() - inf * (~mask.bool()).float()[..., None, None, :]  # :254-257
+    scale = 1.0 / math.sqrt(D)
+    attn = torch.einsum("...qc,...kc->...qk", q * scale, k) + bias              # fp32 :155-160
+    attn = m.r(attn.softmax(dim=-1))                                            # .to(value.dtype) :163
+    av = m.r(torch.einsum("...qk,...kc->...qc", attn, v))
+    av = av.transpose(-2, -3).reshape(x_q.shape)                                # :267
+    g = torch.sigmoid(m.linear(x_q, w["linear_g.weight"], w.get("linear_g.bias")))
+    return m.linear(m.r(g * av), w["linear_out.weight"], w.get("linear_out.bias"))
+
+
+def adaln(a, s, w: dict, mode: str = "fp32", eps: float = 1e-5):
+    """``AdaLN.forward`` -- model/primitives/normalization.py:117-125."""
+    m = _Mode(mode)
+    a = layer_norm(a, None, None, eps, mode)
+    s = layer_norm(s, w["layernorm_s.weight"], None, eps, mode)
+    g = torch.sigmoid(m.linear(s, w["linear_g.weight"], w["linear_g.bias"]))
+    return m.r(g * a + m.linear(s, w["linear_bias.weight"]))
+
+
+def self_attention_pair_bias(a, s, pair_bias, mask, w: dict, num_heads: int, mode: str = "fp32",
+                             inf: float = 1e9):
+    """``SelfAttentionPairBias.forward`` -- model/layers/folding/attention_pair_bias.py:114-158.
+
+    With ``s is None`` the prologue is a plain LayerNorm (the confidence / single
+    track form); otherwise AdaLN prologue and the sigmoid(Linear(s)) output gate.
+    """
+    m = _Mode(mode)
+    if s is None:
+        an = layer_norm(a, w["layernorm_a.weight"], w["layernorm_a.bias"], 1e-5, mode)
+    else:
+        an = adaln(a, s, sub(w, "adaln_a"), mode)
+    out = attention_pair_bias(an, an, pair_bias, mask, w, num_heads, mode, inf)
+    if s is not None:
+        gate = torch.sigmoid(m.linear(m.r(s.float()), w["linear_ada_out.weight"], w["linear_ada_out.bias"]))
+        out = m.r(gate * out)
+    return out
+
+
+def transition(x, w: dict, mode: str = "fp32", eps: float = 1e-5):
+    """``Transition.forward`` -- model/layers/folding/transition.py:48-68 with
+    ``SwiGLU.forward`` -- model/primitives/activation.py:27-29."""
+    m = _Mode(mode)
+    xn = layer_norm(m.r(x.float()), w["layernorm.weight"], w["layernorm.bias"], eps, mode)
+    u1, u2 = m.linear(xn, w["swiglu.linear.weight"]).chunk(2, dim=-1)
+    h = m.r(F.silu(u1) * u2)
+    return m.linear(h, w["linear_out.weight"])
+
+
+def conditioned_transition(a, s, w: dict, mode: str = "fp32"):
+    """``ConditionedTransitionBlock.forward`` --
+    model/layers/folding/diffusion_transformer.py:73-81: AdaLN prologue, SwiGLU,
+    output projection gated by sigmoid(Linear(s))."""
+    m = _Mode(mode)
+    an = adaln(a, s, sub(w, "adaln"), mode)
+    u1, u2 = m.linear(an, w["swiglu.linear.weight"]).chunk(2, dim=-1)
+    h = m.r(F.silu(u1) * u2)
+    gate = torch.sigmoid(m.linear(m.r(s.float()), w["linear_g.weight"], w["linear_g.bias"]))
+    return m.r(gate * m.linear(h, w["linear_out.weight"]))
+
+
+def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
+    """``TriangularBlock.forward`` (eval) -- model/modules/tri_stack.py:130-151."""
+    m = _Mode(mode)
+    z = m.r(z.float())
+    z = m.r(z + triangle_multiplication(z, pair_mask, sub(w, "tri_mul_out"), "outgoing", mode))
+    z = m.r(z + triangle_multiplication(z, pair_mask, sub(w, "tri_mul_in"), "incoming", mode))
+    z = m.r(z + transition(z, sub(w, "transition_z"), mode))
+    return z
+
+
+def pairformer_block(z, s, pair_mask, mask, w: dict, tri_heads: int = 4, single_heads: int = 16,
+                     mode: str = "fp32", final_pair_mask: bool = False):
+    """The composite AF3-shaped Pairformer block, assembled from reference modules only.
+
+    Pair track in ``PairformerBlock.forward`` order (model/modules/apo_module.py:145-172:
+    tri-mult out, tri-mult in, tri-att start, tri-att end, transition) and the single
+    track of ``ConfidencePairSingleBlock.forward`` (model/modules/confidence_head.py:152-175:
+    bias = Linear(LN(z)) moved to (B,H,L,L); s += SelfAttentionPairBias(s, None, bias, mask);
+    s += Transition(s)).  All residual adds are the in-place eval adds of
+    model/primitives/utils.py:30-50.
+    """
+    m = _Mode(mode)
+    z = m.r(z.float())
+    s = m.r(s.float())
+    z = m.r(z + triangle_multiplication(z, pair_mask, sub(w, "tri_mul_out"), "outgoing", mode))
+    z = m.r(z + triangle_multiplication(z, pair_mask, sub(w, "tri_mul_in"), "incoming", mode))
+    z = m.r(z + triangle_attention(z, pair_mask, sub(w, "tri_att_start"), tri_heads, True, mode))
+    z = m.r(z + triangle_attention(z, pair_mask, sub(w, "tri_att_end"), tri_heads, False, mode))
+    z = m.r(z + transition(z, sub(w, "transition_z"), mode))
+    if final_pair_mask:
+        z = z * pair_mask[..., None].to(z.dtype)
+    zn = layer_norm(z, w["layernorm_z.weight"], w["layernorm_z.bias"], 1e-5, mode)
+    pair_bias = m.linear(zn, w["linear_pair_bias.weight"]).movedim(-1, -3)
+    s = m.r(s + self_attention_pair_bias(s, None, pair_bias, mask, sub(w, "attention"), single_heads, mode))
+    s = m.r(s + transition(s, sub(w, "transition"), mode))
+    return z, s

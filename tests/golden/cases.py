@@ -1,0 +1,85 @@
+"""The list of golden cases: which reference module, which sizes, which seed.
+
+Shared by ``make_golden.py`` (runs the real reference) and by the tests (run the
+oracle / the CUDA path on the same seeded inputs and compare with the stored
+reference output).  Inputs and weights are regenerated from the seed with
+``kfold_b200.synth``; only reference *outputs* are stored.
+"""
+from __future__ import annotations
+
+import torch
+
+from kfold_b200 import synth
+
+# pair outputs with N >= 48 are stored as out[:, ::SUB_STRIDE, ::SUB_STRIDE] plus checksums
+SUB_STRIDE = 3
+
+# name -> dict(kind=..., seed=..., dims...)
+CASES = {
+    # triangle multiplication: ragged N with a padding tail, and batch>1 with a general block mask
+    "trimul_out_n24": dict(kind="trimul", direction="outgoing", seed=11, n=24, c=128, batch=1, valid=20),
+    "trimul_in_n24": dict(kind="trimul", direction="incoming", seed=12, n=24, c=128, batch=1, valid=20),
+    "trimul_out_b2": dict(kind="trimul", direction="outgoing", seed=13, n=16, c=128, batch=2, blockmask=True),
+    "trimul_in_b2": dict(kind="trimul", direction="incoming", seed=14, n=16, c=128, batch=2, blockmask=True),
+    "trimul_out_n64": dict(kind="trimul", direction="outgoing", seed=15, n=64, c=128, batch=1, valid=58),
+    "trimul_in_n64": dict(kind="trimul", direction="incoming", seed=16, n=64, c=128, batch=1, valid=58),
+    # triangle attention
+    "triatt_start_n24": dict(kind="triatt", starting=True, seed=21, n=24, c=128, heads=4, batch=1, valid=20),
+    "triatt_end_n24": dict(kind="triatt", starting=False, seed=22, n=24, c=128, heads=4, batch=1, valid=20),
+    "triatt_start_b2": dict(kind="triatt", starting=True, seed=23, n=16, c=128, heads=4, batch=2, blockmask=True),
+    "triatt_end_b2": dict(kind="triatt", starting=False, seed=24, n=16, c=128, heads=4, batch=2, blockmask=True),
+    "triatt_start_n64": dict(kind="triatt", starting=True, seed=25, n=64, c=128, heads=4, batch=1, valid=58),
+    "triatt_end_n64": dict(kind="triatt", starting=False, seed=26, n=64, c=128, heads=4, batch=1, valid=58),
+    "triatt_start_c64": dict(kind="triatt", starting=True, seed=27, n=32, c=64, heads=4, batch=1, valid=30),
+    # pair-bias attention (single track, LayerNorm prologue) and diffusion form (AdaLN + shared bias)
+    "apb_single": dict(kind="apb", seed=31, l=40, c=384, heads=16, c_s=None, batch=1, samples=1, valid=36),
+    "apb_diffusion": dict(kind="apb", seed=32, l=24, c=768, heads=16, c_s=384, batch=1, samples=3, valid=20),
+    # transitions
+    "transition_pair": dict(kind="transition", seed=41, rows=96, c=128, factor=4),
+    "transition_single": dict(kind="transition", seed=42, rows=40, c=384, factor=4),
+    "cond_transition": dict(kind="cond_transition", seed=43, rows=24, c=768, c_s=384, samples=2),
+    # layer norm
+    "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
+    # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
+    "block_cfg1_n64": dict(kind="block", seed=0, n=64, c_z=128, c_s=384, valid=64),
+    "block_n32": dict(kind="block", seed=5, n=32, c_z=128, c_s=384, valid=28),
+}
+
+
+def build_inputs(name: str) -> dict:
+    """Seeded inputs + weights of one case (all float32 / bool CPU tensors)."""
+    cs = CASES[name]
+    kind, seed = cs["kind"], cs["seed"]
+    rng = synth._Rng(seed)
+    out: dict = {"case": cs}
+    if kind in ("trimul", "triatt"):
+        x, pm, _ = synth.pair_inputs(seed, cs["n"], cs["c"], cs["batch"], valid=cs.get("valid"))
+        if cs.get("blockmask"):
+            pm = synth.block_mask(seed, cs["batch"], cs["n"])
+        out["x"], out["mask"] = x, pm
+        out["w"] = synth.trimul_weights(rng, cs["c"]) if kind == "trimul" else synth.triatt_weights(rng, cs["c"], cs["heads"])
+    elif kind == "apb":
+        l, c, h = cs["l"], cs["c"], cs["heads"]
+        out["w"] = synth.apb_weights(rng, c, cs["c_s"])
+        out["a"] = rng.normal(cs["batch"], cs["samples"], l, c)
+        out["s"] = None if cs["c_s"] is None else rng.normal(cs["batch"], 1, l, cs["c_s"])
+        out["pair_bias"] = rng.normal(cs["batch"], 1, h, l, l)
+        out["mask"] = synth.token_mask(l, cs["valid"]).view(1, 1, l).expand(cs["batch"], 1, l).contiguous()
+    elif kind == "transition":
+        out["w"] = synth.transition_weights(rng, cs["c"], cs["factor"])
+        out["x"] = rng.normal(cs["rows"], cs["c"])
+    elif kind == "cond_transition":
+        out["w"] = synth.conditioned_transition_weights(rng, cs["c"], cs["c_s"])
+        out["a"] = rng.normal(1, cs["samples"], cs["rows"], cs["c"])
+        out["s"] = rng.normal(1, 1, cs["rows"], cs["c_s"])
+    elif kind == "layernorm":
+        out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
+        out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}
+    elif kind == "block":
+        z, pm, m = synth.pair_inputs(seed, cs["n"], cs["c_z"], 1, valid=cs["valid"])
+        out["z"], out["pair_mask"], out["mask"] = z, pm, m
+        out["s"] = synth.single_inputs(seed, cs["n"], cs["c_s"], 1)
+        out["w"] = synth.pairformer_block_weights(seed, cs["c_z"], cs["c_s"])
+    else:
+        raise ValueError(kind)
+    return out

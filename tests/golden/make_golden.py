@@ -1,0 +1,106 @@
+"""Generate tests/golden/*.npz by running the REAL K-Fold reference modules.
+
+Run in a container where the reference source tree is present:
+
+    python tests/golden/make_golden.py
+
+For every case in ``cases.py`` the reference module (torch backend, CPU, fp32,
+eval mode, no grad) is instantiated at the case's sizes, loaded with the seeded
+synthetic weights via ``load_state_dict(strict=True)``, run on the seeded inputs,
+and its output stored.  The composite Pairformer block has no single reference
+class; it is assembled here from reference modules only, in the order of
+``PairformerBlock.forward`` (model/modules/apo_module.py:145-172) followed by the
+single track of ``ConfidencePairSingleBlock.forward``
+(model/modules/confidence_head.py:152-175).
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+import cases  # noqa: E402
+import ref_shim  # noqa: E402
+from oracle.pairformer_oracle import sub  # noqa: E402  (prefix helper only)
+
+
+def _load(mod, w):
+    mod.load_state_dict(w, strict=True)
+    return mod.eval()
+
+
+@torch.no_grad()
+def run_reference(ns, name: str) -> dict:
+    inp = cases.build_inputs(name)
+    cs = inp["case"]
+    kind = cs["kind"]
+    if kind == "trimul":
+        cls = ns.TriangleMultiplicationOutgoing if cs["direction"] == "outgoing" else ns.TriangleMultiplicationIncoming
+        return {"out": _load(cls(cs["c"]), inp["w"])(inp["x"], inp["mask"])}
+    if kind == "triatt":
+        cls = ns.TriangleAttentionStartingNode if cs["starting"] else ns.TriangleAttentionEndingNode
+        return {"out": _load(cls(cs["c"], cs["heads"]), inp["w"])(inp["x"], inp["mask"])}
+    if kind == "apb":
+        site = "confidence" if cs["c_s"] is None else "diffusion_global"
+        mod = _load(ns.SelfAttentionPairBias(cs["c"], cs["heads"], cs["c_s"], site, kernel_backend="torch"), inp["w"])
+        return {"out": mod(inp["a"], inp["s"], inp["pair_bias"], inp["mask"])}
+    if kind == "transition":
+        return {"out": _load(ns.Transition(cs["c"], cs["factor"]), inp["w"])(inp["x"])}
+    if kind == "cond_transition":
+        import importlib
+        dt = importlib.import_module("kfold.model.layers.folding.diffusion_transformer")
+        return {"out": _load(dt.ConditionedTransitionBlock(cs["c"], cs["c_s"]), inp["w"])(inp["a"], inp["s"])}
+    if kind == "layernorm":
+        return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
+    if kind == "block":
+        w, c_z, c_s = inp["w"], cs["c_z"], cs["c_s"]
+        z, s, pm, m = inp["z"].clone(), inp["s"].clone(), inp["pair_mask"], inp["mask"]
+        z.add_(_load(ns.TriangleMultiplicationOutgoing(c_z), sub(w, "tri_mul_out"))(z, pm))
+        z.add_(_load(ns.TriangleMultiplicationIncoming(c_z), sub(w, "tri_mul_in"))(z, pm))
+        z.add_(_load(ns.TriangleAttentionStartingNode(c_z, 4), sub(w, "tri_att_start"))(z, pm))
+        z.add_(_load(ns.TriangleAttentionEndingNode(c_z, 4), sub(w, "tri_att_end"))(z, pm))
+        z.add_(_load(ns.Transition(c_z, 4), sub(w, "transition_z"))(z))
+        zn = _load(ns.LayerNorm(c_z), sub(w, "layernorm_z"))(z)
+        lin = _load(ns.LinearNoBias(c_z, 16), sub(w, "linear_pair_bias"))
+        pair_bias = lin(zn).movedim(-1, -3)
+        att = _load(ns.SelfAttentionPairBias(c_s, 16, None, "confidence", kernel_backend="torch"), sub(w, "attention"))
+        s.add_(att(s, None, pair_bias, m))
+        s.add_(_load(ns.Transition(c_s, 4), sub(w, "transition"))(s))
+        res = {"s": s, "z_sum": z.double().sum().reshape(1), "z_sumsq": (z.double() ** 2).sum().reshape(1)}
+        if cs["n"] > 32:
+            res["z_sub"] = z[:, ::cases.SUB_STRIDE, ::cases.SUB_STRIDE].contiguous()
+        else:
+            res["z"] = z
+        return res
+    raise ValueError(kind)
+
+
+def _thin(res: dict) -> dict:
+    """Keep big pair outputs small: a strided sample plus float64 checksums."""
+    out = res.get("out")
+    if out is not None and out.dim() == 4 and out.shape[1] >= 48:
+        return {"out_sub": out[:, ::cases.SUB_STRIDE, ::cases.SUB_STRIDE].contiguous(),
+                "out_sum": out.double().sum().reshape(1),
+                "out_sumsq": (out.double() ** 2).sum().reshape(1)}
+    return res
+
+
+def main() -> None:
+    ns = ref_shim.load_reference()
+    torch.manual_seed(0)
+    for name in cases.CASES:
+        res = _thin(run_reference(ns, name))
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **{k: v.detach().cpu().numpy() for k, v in res.items()})
+        print(f"{name}: " + ", ".join(f"{k}{tuple(v.shape)}" for k, v in res.items()),
+              f"-> {os.path.getsize(path) / 1024:.0f} KB")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,60 @@
+"""The CPU oracle against the golden vectors produced by the real reference modules."""
+import pytest
+import torch
+
+import cases
+from helpers import compare_pair_output, err_stats, load_golden
+from oracle import pairformer_oracle as O
+
+FP32_TOL = 2e-5  # max-abs / RMS(ref); both sides are fp32 CPU, only op order differs
+
+
+def run_oracle(name: str, mode: str = "fp32") -> dict:
+    inp = cases.build_inputs(name)
+    cs, w = inp["case"], inp.get("w")
+    kind = cs["kind"]
+    if kind == "trimul":
+        return {"out": O.triangle_multiplication(inp["x"], inp["mask"], w, cs["direction"], mode)}
+    if kind == "triatt":
+        return {"out": O.triangle_attention(inp["x"], inp["mask"], w, cs["heads"], cs["starting"], mode)}
+    if kind == "apb":
+        return {"out": O.self_attention_pair_bias(inp["a"], inp["s"], inp["pair_bias"], inp["mask"], w, cs["heads"], mode)}
+    if kind == "transition":
+        return {"out": O.transition(inp["x"], w, mode)}
+    if kind == "cond_transition":
+        return {"out": O.conditioned_transition(inp["a"], inp["s"], w, mode)}
+    if kind == "layernorm":
+        return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
+    if kind == "block":
+        z, s = O.pairformer_block(inp["z"], inp["s"], inp["pair_mask"], inp["mask"], w, mode=mode)
+        return {"z": z, "s": s}
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_oracle_matches_reference_golden(name):
+    gold = load_golden(name)
+    got = run_oracle(name)
+    if cases.CASES[name]["kind"] == "block":
+        assert err_stats(got["s"], gold["s"])[0] < 5 * FP32_TOL
+        assert compare_pair_output(got["z"], gold, "z")[0] < 5 * FP32_TOL
+        zs = float(got["z"].double().sum())
+        assert abs(zs - float(gold["z_sum"])) <= 1e-3 * float(gold["z_sumsq"]) ** 0.5
+    else:
+        out = got["out"]
+        if out.dim() == 4 and ("out" not in gold):
+            mx, _ = compare_pair_output(out, gold)
+            assert abs(float(out.double().sum()) - float(gold["out_sum"])) <= 1e-3 * float(gold["out_sumsq"]) ** 0.5
+        else:
+            mx, _ = err_stats(out, gold["out"])
+        assert mx < FP32_TOL, f"{name}: max-abs/RMS {mx:.3e}"
+
+
+@pytest.mark.parametrize("name", ["trimul_out_n24", "triatt_start_n24", "transition_pair", "apb_single"])
+def test_oracle_bf16_mode_is_within_bf16_noise(name):
+    """bf16-emulating mode stays within the reference's own bf16-vs-fp32 noise (RMS error < 2e-2 RMS)."""
+    gold = load_golden(name)
+    inp_mode = run_oracle(name, "bf16")["out"]
+    _, r = err_stats(inp_mode, gold["out"])
+    assert r < 2e-2
+    assert r > 1e-4  # it really rounds
