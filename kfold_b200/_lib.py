@@ -1,0 +1,82 @@
+"""ctypes binding of the C ABI in include/kfold_b200.h.
+
+The shared library is built in-tree by ``python -m kfold_b200.build``.  There is no
+fallback: if the library is missing, importing this module's ``lib()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "_C", "libkfold_b200.so")
+
+KFB_BF16, KFB_FP32 = 0, 1
+_lib = None
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+class KfbError(RuntimeError):
+    pass
+
+
+# name -> argtypes; every function returns int except where noted
+_SIGNATURES = {
+    "kfb_version": [],
+    "kfb_device_status": [ctypes.POINTER(c_int)],
+    "kfb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_float, c_int, c_int, c_void_p],
+    "kfb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll,
+                      c_ll, c_int, c_void_p],
+}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise KfbError(
+                f"{LIB_PATH} not found: the CUDA extension is not built "
+                "(run `python -m kfold_b200.build`); there is no fallback path")
+        l = ctypes.CDLL(LIB_PATH)
+        for name, args in _SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        l.kfb_last_error.argtypes = []
+        l.kfb_last_error.restype = ctypes.c_char_p
+        _lib = l
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        msg = lib().kfb_last_error().decode()
+        if status == 1:
+            raise ValueError(f"kfold_b200: {msg}")
+        raise KfbError(f"kfold_b200 (status {status}): {msg}")
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return KFB_BF16
+    if dt == torch.float32:
+        return KFB_FP32
+    raise ValueError(f"kfold_b200 supports bfloat16 and float32 activations, got {dt}")
+
+
+def device_status() -> int:
+    """Synchronise and return the device-side status word (0 = ok); raises if a bounded wait gave up."""
+    code = c_int(0)
+    check(lib().kfb_device_status(ctypes.byref(code)))
+    return code.value

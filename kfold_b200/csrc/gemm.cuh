@@ -1,0 +1,348 @@
+// Persistent, warp-specialised tcgen05 GEMM:  D[row, col] = sum_k A[row, k] * B[col, k]
+//
+// Both operands are bf16 and K-major in global memory.  One CTA per SM walks a
+// static list of 128 x BN output tiles.  Per tile:
+//   warp 0 (one lane)  TMA producer: A and B k-blocks (64 wide = one 128-byte swizzle span)
+//                      into a ring of shared-memory stages;
+//   warp 1 (one lane)  issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
+//                      accumulator buffers (2 x BN fp32 columns), so the epilogue of
+//                      tile t overlaps the main loop of tile t+1;
+//   warps 2..5         epilogue: each thread owns one accumulator row (one TMEM lane),
+//                      reads it 32 columns at a time with tcgen05.ld and applies the
+//                      fused element-wise tail (gated linear unit, row mask, sigmoid
+//                      gate from memory, residual) before storing.
+//
+// Rows of A are addressed as (batch, o, n) with tiles running along n, so the same
+// kernel serves flat [M, K] activations, a transposed walk over an (N x N) pair
+// tensor (swap the o / n strides in the tensor map), and the batched per-channel
+// triangle contraction.  Out-of-range rows/columns/k are zero-filled by TMA and
+// the stores are predicated, so no size needs to be a multiple of the tile.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+
+namespace kfb {
+
+enum GluMode : int { GLU_NONE = 0, GLU_SIGMOID = 1, GLU_SWIGLU = 2 };
+
+// One segment of output columns.  Element (row=(b,o,n), col) of the segment goes to
+//   dst + b*s_b + o*s_o + n*s_n + (col - col_begin)*s_col      (strides in elements)
+struct EpiSeg {
+  int col_begin;    // first output column of the segment (multiple of 32)
+  int ncols;        // valid columns in the segment; columns beyond are dropped
+  int out_fp32;     // 0: bf16 output, 1: fp32 output
+  int vec;          // 1: s_col == 1 and every row start is 16-byte aligned -> vector stores
+  void* dst;
+  long long s_col, s_n, s_o, s_b;
+};
+
+struct GemmParams {
+  int n_extent, o_extent, batch;  // A rows = batch x o_extent x n_extent
+  int n_cols;                     // GEMM columns (rows of B) before GLU pairing
+  int k_extent;
+  int b_batched;                  // B carries the batch dimension too
+  int n_blocks, num_m_tiles, num_n_tiles;
+  int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
+  int nseg;
+  EpiSeg seg[3];
+  const unsigned char* rowmask;   // optional 0/1 mask multiplied into segment rows flagged below
+  long long m_n, m_o, m_b;
+  int mask_segs;                  // bit i: apply rowmask to segment i
+  const float* col_bias;          // optional, per output column, added before everything else
+  const __nv_bfloat16* gate;      // optional: seg 0 value *= sigmoid(gate[...]), addressed with seg 0 strides
+  long long g_col, g_n, g_o, g_b;
+  const void* resid;              // optional: seg 0 value += resid[...] (same dtype and strides as seg 0 dst)
+  float alpha;                    // value scale (applied to the accumulator first)
+};
+
+static constexpr int kBM = 128;
+static constexpr int kBK = 64;   // bf16 elements = 128 bytes = one swizzle span
+static constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kAStage = kBM * kBK * 2;
+  static constexpr int kBStage = BN * kBK * 2;
+  static constexpr int kStageBytes = kAStage + kBStage;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Store 32 consecutive output values of one row.
+__device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_off, int col_local, const float (&v)[32],
+                                                bool row_ok) {
+  if (!row_ok) return;
+  const int nvalid = min(32, sg.ncols - col_local);
+  if (nvalid <= 0) return;
+  if (sg.vec && nvalid == 32) {
+    if (sg.out_fp32) {
+      float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(sg.dst) + row_off + col_local);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+      uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(sg.dst) + row_off + col_local);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        d[i] = make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                          pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+    }
+    return;
+  }
+  // scalar path: per column; coalesced across the warp's lanes when s_n == 1 (channel-major output)
+  if (sg.out_fp32) {
+    float* d = reinterpret_cast<float*>(sg.dst) + row_off + static_cast<long long>(col_local) * sg.s_col;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid) d[static_cast<long long>(i) * sg.s_col] = v[i];
+  } else {
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(sg.dst) + row_off + static_cast<long long>(col_local) * sg.s_col;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid) d[static_cast<long long>(i) * sg.s_col] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int OUT_BN_GLU = BN / 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_a = smem;
+  uint8_t* s_b = smem + kStages * Cfg::kAStage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_k = (p.k_extent + kBK - 1) / kBK;
+  const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tmap(&tm_a);
+    ptx::prefetch_tmap(&tm_b);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&tmem_full[a], 1);
+      ptx::mbar_init(&tmem_empty[a], 128);
+    }
+    ptx::fence_barrier_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int m_tile = tile / p.num_n_tiles;
+        const int n_tile = tile - m_tile * p.num_n_tiles;
+        const int nb = m_tile % p.n_blocks;
+        const int rest = m_tile / p.n_blocks;
+        const int o = rest % p.o_extent;
+        const int b = rest / p.o_extent;
+        const int bb = p.b_batched ? b : 0;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int stage = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1, 101)) { ok = false; break; }
+          ptx::mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], kb * kBK, nb * kBM, o, b);
+          ptx::tma_load_3d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], kb * kBK, n_tile * BN, bb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(kBM, BN, /*bf16*/ 1);
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1;
+        const uint32_t acc_phase = (tile_iter >> 1) & 1;
+        if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, 102)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int stage = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          if (!ptx::mbar_wait(&full_bar[stage], phase, 103)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(s_a + stage * Cfg::kAStage);
+          const uint32_t b_addr = ptx::smem_u32(s_b + stage * Cfg::kBStage);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            ptx::mma_f16_ss(d_tmem, ptx::make_kmajor_desc<128>(a_addr + k * 32),
+                            ptx::make_kmajor_desc<128>(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+        }
+        if (ok) ptx::tc_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int r = quad * 32 + lane;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+      const int m_tile = tile / p.num_n_tiles;
+      const int n_tile = tile - m_tile * p.num_n_tiles;
+      const int nb = m_tile % p.n_blocks;
+      const int rest = m_tile / p.n_blocks;
+      const int o = rest % p.o_extent;
+      const int b = rest / p.o_extent;
+      const int n = nb * kBM + r;
+      const bool row_ok = n < p.n_extent;
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t acc_phase = (tile_iter >> 1) & 1;
+      if (!ptx::mbar_wait(&tmem_full[acc], acc_phase, 104)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+
+      float mask_v = 1.0f;
+      if (p.rowmask != nullptr && row_ok)
+        mask_v = p.rowmask[static_cast<long long>(b) * p.m_b + static_cast<long long>(o) * p.m_o +
+                           static_cast<long long>(n) * p.m_n] ? 1.0f : 0.0f;
+
+      const int out_bn = p.glu ? OUT_BN_GLU : BN;
+      const int out_col_tile = n_tile * out_bn;
+#pragma unroll 1
+      for (int c = 0; c < out_bn; c += 32) {
+        const int out_col = out_col_tile + c;
+        float v[32];
+        {
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32b_x32(t_row + c, raw);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * p.alpha;
+        }
+        if (p.glu) {
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32b_x32(t_row + OUT_BN_GLU + c, raw);
+          ptx::tmem_ld_wait();
+          if (p.glu == GLU_SIGMOID) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= sigmoidf_fast(__uint_as_float(raw[i]) * p.alpha);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = v[i] * sigmoidf_fast(v[i]) * (__uint_as_float(raw[i]) * p.alpha);
+          }
+        }
+        // which segment does this chunk belong to
+        int si = 0;
+        if (p.nseg > 1 && out_col >= p.seg[1].col_begin) si = 1;
+        if (p.nseg > 2 && out_col >= p.seg[2].col_begin) si = 2;
+        const EpiSeg& sg = p.seg[si];
+        const int col_local = out_col - sg.col_begin;
+        if (col_local >= sg.ncols) continue;  // uniform across the warp
+        if (p.col_bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += (col_local + i < sg.ncols) ? p.col_bias[out_col + i] : 0.0f;
+        }
+        if ((p.mask_segs >> si) & 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= mask_v;
+        }
+        const long long row_off = static_cast<long long>(b) * sg.s_b + static_cast<long long>(o) * sg.s_o +
+                                  static_cast<long long>(n) * sg.s_n;
+        if (si == 0 && row_ok) {
+          if (p.gate != nullptr) {
+            const __nv_bfloat16* g = p.gate + static_cast<long long>(b) * p.g_b + static_cast<long long>(o) * p.g_o +
+                                     static_cast<long long>(n) * p.g_n + static_cast<long long>(col_local) * p.g_col;
+            if (p.g_col == 1 && col_local + 32 <= sg.ncols) {
+              const uint4* g4 = reinterpret_cast<const uint4*>(g);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 u = g4[q];
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                  v[q * 8 + j * 2] *= sigmoidf_fast(f.x);
+                  v[q * 8 + j * 2 + 1] *= sigmoidf_fast(f.y);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col_local + i < sg.ncols) v[i] *= sigmoidf_fast(__bfloat162float(g[static_cast<long long>(i) * p.g_col]));
+            }
+          }
+          if (p.resid != nullptr) {
+            if (sg.out_fp32) {
+              const float* rs = reinterpret_cast<const float*>(p.resid) + row_off + static_cast<long long>(col_local) * sg.s_col;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col_local + i < sg.ncols) v[i] += rs[static_cast<long long>(i) * sg.s_col];
+            } else {
+              const __nv_bfloat16* rs =
+                  reinterpret_cast<const __nv_bfloat16*>(p.resid) + row_off + static_cast<long long>(col_local) * sg.s_col;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col_local + i < sg.ncols) v[i] += __bfloat162float(rs[static_cast<long long>(i) * sg.s_col]);
+            }
+          }
+        }
+        epi_store_chunk(sg, row_off, col_local, v, row_ok);
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct GemmOperandA {  // A[(b,o,n), k], strides in elements
+  const void* ptr;
+  long long s_n, s_o, s_b;
+};
+struct GemmOperandB {  // B[(b), col, k]
+  const void* ptr;
+  long long s_col, s_b;
+};
+
+// Fills the tile bookkeeping of `p`, builds the tensor maps and launches on `stream`.
+int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn = 0);
+
+}  // namespace kfb

@@ -1,0 +1,202 @@
+// LayerNorm kernels.  Pure HBM traffic: every element is read once and written once,
+// statistics are taken in fp32 with warp-shuffle reductions (two-pass: mean, then
+// variance of the centred values, which is what torch's layer_norm computes).
+#include "layernorm.cuh"
+
+namespace kfb {
+
+template <typename T>
+__device__ __forceinline__ float2 load2(const T* p);
+template <>
+__device__ __forceinline__ float2 load2<float>(const float* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+template <>
+__device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename T>
+__device__ __forceinline__ void store2(T* p, float a, float b);
+template <>
+__device__ __forceinline__ void store2<float>(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+template <>
+__device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per row; lane l holds channel pairs (l + 32 g) * 2, g < G.
+template <typename TI, typename TO, int G>
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restrict__ x, TO* __restrict__ y,
+                                                             const float* __restrict__ w, const float* __restrict__ b,
+                                                             long long rows, int c, long long xs, long long ys, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warps_per_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += warps_per_grid) {
+    const TI* xr = x + row * xs;
+    float2 v[G];
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int ch = (lane + 32 * g) * 2;
+      v[g] = ch < c ? load2<TI>(xr + ch) : make_float2(0.f, 0.f);
+      s += v[g].x + v[g].y;
+    }
+    const float mean = warp_sum(s) / static_cast<float>(c);
+    float q = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int ch = (lane + 32 * g) * 2;
+      if (ch < c) {
+        v[g].x -= mean;
+        v[g].y -= mean;
+        q += v[g].x * v[g].x + v[g].y * v[g].y;
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
+    TO* yr = y + row * ys;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int ch = (lane + 32 * g) * 2;
+      if (ch < c) {
+        float a0 = v[g].x * rstd, a1 = v[g].y * rstd;
+        if (w != nullptr) {
+          const float2 ww = *reinterpret_cast<const float2*>(w + ch);
+          a0 *= ww.x;
+          a1 *= ww.y;
+        }
+        if (b != nullptr) {
+          const float2 bb = *reinterpret_cast<const float2*>(b + ch);
+          a0 += bb.x;
+          a1 += bb.y;
+        }
+        store2<TO>(yr + ch, a0, a1);
+      }
+    }
+  }
+}
+
+template <typename TI, typename TO, int G>
+static int launch_rows(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
+                       long long xs, long long ys, float eps) {
+  const int warps = 8;
+  long long blocks = (rows + warps - 1) / warps;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  layernorm_rows_kernel<TI, TO, G><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(
+      static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+template <typename TI, typename TO>
+static int dispatch_g(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
+                      long long xs, long long ys, float eps) {
+  const int g = cdiv(c, 64);
+  if (g <= 1) return launch_rows<TI, TO, 1>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (g <= 2) return launch_rows<TI, TO, 2>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (g <= 4) return launch_rows<TI, TO, 4>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (g <= 6) return launch_rows<TI, TO, 6>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (g <= 12) return launch_rows<TI, TO, 12>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (g <= 16) return launch_rows<TI, TO, 16>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  set_error("layernorm: channel count %d above 1024 is not supported", c);
+  return KFB_ERR_UNSUPPORTED;
+}
+
+int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
+                     long long xs, long long ys, float eps, int in_dtype, int out_dtype) {
+  KFB_CHECK_ARG(rows >= 0 && c > 0 && c % 2 == 0, "layernorm: rows %lld, channels %d (must be even)", rows, c);
+  KFB_CHECK_ARG(xs % 2 == 0 && ys % 2 == 0, "layernorm: row strides must be even");
+  if (rows == 0) return KFB_OK;
+  if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16)
+    return dispatch_g<__nv_bfloat16, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (in_dtype == KFB_FP32 && out_dtype == KFB_BF16)
+    return dispatch_g<float, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (in_dtype == KFB_FP32 && out_dtype == KFB_FP32)
+    return dispatch_g<float, float>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (in_dtype == KFB_BF16 && out_dtype == KFB_FP32)
+    return dispatch_g<__nv_bfloat16, float>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  set_error("layernorm: bad dtype");
+  return KFB_ERR_INVALID_ARGUMENT;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Channel-major in, position-major out.  A block stages a [c][64 positions] slab in shared memory
+// (row pitch 65 floats, so the per-position column reads below are bank-conflict free), then each
+// warp normalises 8 positions.
+// ------------------------------------------------------------------------------------------------
+static constexpr int kCmPos = 64;
+
+template <typename TI>
+__global__ void __launch_bounds__(256) layernorm_cm_kernel(const TI* __restrict__ t, __nv_bfloat16* __restrict__ y,
+                                                           const float* __restrict__ w, const float* __restrict__ b,
+                                                           long long npos, int c, long long chan_stride,
+                                                           long long batch_stride, float eps, int blocks_per_batch) {
+  extern __shared__ float slab[];  // [c][65]
+  const int batch = blockIdx.x / blocks_per_batch;
+  const long long p0 = static_cast<long long>(blockIdx.x % blocks_per_batch) * kCmPos;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const TI* tb = t + batch * batch_stride;
+  for (int ch = warp; ch < c; ch += 8) {
+    const long long p = p0 + lane * 2;
+    float2 v = make_float2(0.f, 0.f);
+    if (p + 1 < npos) v = load2<TI>(tb + ch * chan_stride + p);
+    else if (p < npos) v.x = static_cast<float>(tb[ch * chan_stride + p]);
+    slab[ch * 65 + lane * 2] = v.x;
+    slab[ch * 65 + lane * 2 + 1] = v.y;
+  }
+  __syncthreads();
+  for (int pp = warp; pp < kCmPos; pp += 8) {
+    const long long p = p0 + pp;
+    if (p >= npos) break;
+    float s = 0.f;
+    for (int ch = lane; ch < c; ch += 32) s += slab[ch * 65 + pp];
+    const float mean = warp_sum(s) / static_cast<float>(c);
+    float q = 0.f;
+    for (int ch = lane; ch < c; ch += 32) {
+      const float d = slab[ch * 65 + pp] - mean;
+      q += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
+    __nv_bfloat16* yr = y + (static_cast<long long>(batch) * npos + p) * c;
+    for (int ch = lane * 2; ch < c; ch += 64) {
+      float a0 = (slab[ch * 65 + pp] - mean) * rstd;
+      float a1 = (slab[(ch + 1) * 65 + pp] - mean) * rstd;
+      if (w != nullptr) { a0 *= w[ch]; a1 *= w[ch + 1]; }
+      if (b != nullptr) { a0 += b[ch]; a1 += b[ch + 1]; }
+      *reinterpret_cast<__nv_bfloat162*>(yr + ch) = __floats2bfloat162_rn(a0, a1);
+    }
+  }
+}
+
+int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, const float* w, const float* b, int batch,
+                        long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype) {
+  KFB_CHECK_ARG(c > 0 && c % 2 == 0 && c <= 512, "layernorm_cm: channels %d", c);
+  KFB_CHECK_ARG(chan_stride % 2 == 0 && batch_stride % 2 == 0, "layernorm_cm: strides must be even");
+  if (npos == 0 || batch == 0) return KFB_OK;
+  const int bpb = static_cast<int>((npos + kCmPos - 1) / kCmPos);
+  const size_t smem = static_cast<size_t>(c) * 65 * sizeof(float);
+  if (in_dtype == KFB_BF16) {
+    if (smem > 48 * 1024)
+      KFB_CUDA(cudaFuncSetAttribute(layernorm_cm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    layernorm_cm_kernel<__nv_bfloat16><<<bpb * batch, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(t), y, w, b, npos,
+                                                                        c, chan_stride, batch_stride, eps, bpb);
+  } else {
+    if (smem > 48 * 1024)
+      KFB_CUDA(cudaFuncSetAttribute(layernorm_cm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    layernorm_cm_kernel<float><<<bpb * batch, 256, smem, stream>>>(static_cast<const float*>(t), y, w, b, npos, c, chan_stride,
+                                                                batch_stride, eps, bpb);
+  }
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+}  // namespace kfb
