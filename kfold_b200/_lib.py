@@ -30,6 +30,11 @@ _SIGNATURES = {
     "kfb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_float, c_int, c_int, c_void_p],
     "kfb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll,
                       c_ll, c_int, c_void_p],
+    "kfb_trimul_fwd": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_float, c_int, c_void_p],
+}
+_SIZE_FUNCS = {
+    "kfb_trimul_workspace_bytes": [c_int, c_int, c_int],
 }
 
 
@@ -45,6 +50,10 @@ def lib() -> ctypes.CDLL:
             fn = getattr(l, name)
             fn.argtypes = args
             fn.restype = c_int
+        for name, args in _SIZE_FUNCS.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = ctypes.c_size_t
         l.kfb_last_error.argtypes = []
         l.kfb_last_error.restype = ctypes.c_char_p
         _lib = l

@@ -1,11 +1,7 @@
 // extern "C" entry points: argument checking and kernel sequencing.
-#include "common.cuh"
-#include "gemm.cuh"
-#include "layernorm.cuh"
+#include "ops_common.cuh"
 
 using namespace kfb;
-
-static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 extern "C" {
 

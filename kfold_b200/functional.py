@@ -1,0 +1,96 @@
+"""Functional entry points: torch tensors in, torch tensors out, CUDA kernels in between.
+
+Each function checks shapes, pads the token dimension to the kernels' granularity,
+takes a workspace from a per-device cache, and calls the C ABI on the current
+stream.  There is no CPU path and no PyTorch fallback: inputs must be CUDA tensors
+and the extension must be built.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib as L
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = None
+        _workspaces.pop(key, None)
+        ws = torch.empty(int(nbytes * 1.05) + 4096, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("kfold_b200 kernels require CUDA tensors (there is no CPU path)")
+
+
+def _pad_pair(x: torch.Tensor, mask: torch.Tensor, mult: int = 8):
+    n = x.shape[-2]
+    npad = (n + mult - 1) // mult * mult
+    if npad == n:
+        return x, mask, n
+    xp = x.new_zeros(x.shape[0], npad, npad, x.shape[-1])
+    xp[:, :n, :n] = x
+    mp = mask.new_zeros(mask.shape[0], npad, npad)
+    mp[:, :n, :n] = mask
+    return xp, mp, n
+
+
+def layer_norm(x: torch.Tensor, weight, bias, eps: float = 1e-5, out_dtype=None) -> torch.Tensor:
+    """LayerNorm over the last dim (model/primitives/normalization.py:61-91)."""
+    _require_cuda(x)
+    c = x.shape[-1]
+    x2 = x.reshape(-1, c)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty(x2.shape, dtype=out_dtype or x.dtype, device=x.device)
+    w = None if weight is None else weight.detach().float().contiguous()
+    b = None if bias is None else bias.detach().float().contiguous()
+    with torch.cuda.device(x.device):
+        L.check(L.lib().kfb_layernorm(L.ptr(x2), L.ptr(out), L.ptr(w), L.ptr(b), x2.shape[0], c, x2.stride(0), c, eps,
+                                      L.dtype_code(x2.dtype), L.dtype_code(out.dtype), L.stream_ptr()))
+    return out.view(*x.shape[:-1], c)
+
+
+def triangle_multiplication(x: torch.Tensor, mask: torch.Tensor, packed: dict, direction: str, eps: float = 1e-5,
+                            residual: bool = False) -> torch.Tensor:
+    """Triangle multiplicative update (model/primitives/triangle_multiplication.py:179-229, :263-313).
+
+    x (B,N,N,C) bf16 or fp32; mask (B,N,N).  Returns the update, or x + update when
+    ``residual`` is set (the add is fused into the last kernel).
+    """
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"unknown direction {direction!r}")
+    _require_cuda(x, mask)
+    if x.dim() != 4 or x.shape[1] != x.shape[2] or mask.shape != x.shape[:-1]:
+        raise ValueError(f"triangle_multiplication: x {tuple(x.shape)} / mask {tuple(mask.shape)}")
+    c = x.shape[-1]
+    if c != packed["c"]:
+        raise ValueError(f"triangle_multiplication: channel mismatch {c} vs {packed['c']}")
+    xp, mp, n = _pad_pair(x.contiguous(), mask.to(torch.bool).contiguous())
+    b, npad = xp.shape[0], xp.shape[1]
+    mp8 = mp.view(torch.uint8)
+    out = torch.empty_like(xp)
+    lib = L.lib()
+    with torch.cuda.device(x.device):
+        need = lib.kfb_trimul_workspace_bytes(b, npad, c)
+        ws = _workspace(x.device, need)
+        L.check(lib.kfb_trimul_fwd(1 if direction == "incoming" else 0, L.ptr(xp), L.ptr(mp8), L.ptr(packed["ln_in_w"]),
+                                   L.ptr(packed["ln_in_b"]), L.ptr(packed["w_in"]), L.ptr(packed["w_gout"]),
+                                   L.ptr(packed["ln_out_w"]), L.ptr(packed["ln_out_b"]), L.ptr(packed["w_pout"]),
+                                   L.ptr(out), L.ptr(xp) if residual else None, L.ptr(ws), ws.numel(), b, npad, c, eps,
+                                   L.dtype_code(xp.dtype), L.stream_ptr()))
+    return out if npad == n else out[:, :n, :n].contiguous()
