@@ -32,8 +32,14 @@ _SIGNATURES = {
                       c_ll, c_int, c_void_p],
     "kfb_trimul_fwd": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_triatt_fwd": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       ctypes.c_size_t, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                    ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
 }
 _SIZE_FUNCS = {
+    "kfb_triatt_workspace_bytes": [c_int, c_int, c_int, c_int],
+    "kfb_apb_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_trimul_workspace_bytes": [c_int, c_int, c_int],
 }
 

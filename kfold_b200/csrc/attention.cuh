@@ -1,0 +1,46 @@
+// Flash-style attention with an additive pair bias and a key mask, on tcgen05/TMEM.
+//
+//   S = Q K^T + bias[h, q, k] + (mask[k] ? 0 : -1e9)       (Q arrives pre-scaled by 1/sqrt(D))
+//   O = softmax_k(S) V                                     then optionally O *= sigmoid(G)
+//
+// One CTA handles 128 queries of one (batch row, head) and walks the keys in blocks of
+// 128 with an online softmax; the L x L x H logits never exist in memory.  Per key block:
+//   warp 0      TMA: K tile, V^T tile and the 128 x 128 bias tile into shared memory
+//   warp 1      tcgen05.mma  S = Q K^T  (accumulator in TMEM), later  O_blk = P V
+//   warps 2..5  one query row per thread: read its S row from TMEM, add the bias tile
+//               (from shared memory) and the key mask, update the running max / sum,
+//               write P = exp(S - max) as bf16 into a swizzled shared-memory tile (the
+//               A operand of the second MMA), and fold O_blk into register accumulators.
+//
+// Used for triangle attention (batch row = pair row i, bias shared by all rows, mask
+// per row) and for pair-bias attention on the single / token track (bias shared by
+// `bias_div` consecutive batch entries, mask per batch entry).
+#pragma once
+#include "common.cuh"
+
+namespace kfb {
+
+struct AttnParams {
+  int batch;      // independent attention problems (tri-att: B * N rows)
+  int heads;
+  int lq, lk;
+  int d;          // real head dim (<= DPAD); output packs heads at stride d
+  int dpad;       // padded head dim of q/k/v/g buffers: 32 or 64
+  // q / k / g : position-major bf16, row index = batch * L + position, element stride ld*, head h at col0 + h*dpad
+  const void* q; long long ldq; int q_col0;
+  const void* k; long long ldk; int k_col0;
+  // v^T : [batch][heads*dpad][ldv] bf16 (keys contiguous)
+  const void* vt; long long ldv;
+  // bias : [bias_batches][heads][lq][ldb] bf16 ; batch entry b uses bias batch b / bias_div
+  const void* bias; long long ldb; int bias_div;
+  // key mask (0/1 bytes): element (b, k) at mask + b_hi*m_hi + b_lo*m_lo + k*m_k with b_hi = b / mask_lo_extent
+  const unsigned char* mask; long long m_hi, m_lo, m_k; int mask_lo_extent;
+  // optional gate logits, addressed like q
+  const void* g; long long ldg; int g_col0;
+  // output bf16: row (b, q) at out + (b*lq + q)*ldo, head h at column h*d
+  void* out; long long ldo;
+};
+
+int launch_attention(cudaStream_t stream, const AttnParams& p);
+
+}  // namespace kfb

@@ -1,0 +1,236 @@
+// Triangle attention (starting / ending node) and pair-bias self-attention as kernel sequences.
+//
+// Triangle attention:
+//   1. LayerNorm                         x -> xn (bf16)
+//   2. one projection GEMM of xn with [Wq/sqrt(D) | Wk | Wg | Wv | Wz]:
+//        q, k, g      position-major                       (row-major segment)
+//        v            transposed per pair row, V^T[h*D+d][k] (channel-major segment) so that it is the
+//                     K-major B operand of the P V product
+//        triangle bias channel-major [h][j][k]               (channel-major segment)
+//   3. flash attention with the bias tile streamed through shared memory, output gated by sigmoid(g)
+//   4. output projection GEMM (+ optional residual)
+// The ending node is the starting node on the transposed pair tensor: step 2 walks xn with its two
+// position strides swapped (a tensor-map change, no data movement), the key mask is read transposed,
+// and step 4 scatters its rows back to the untransposed positions.
+#include "attention.cuh"
+#include "ops_common.cuh"
+
+using namespace kfb;
+
+namespace {
+
+inline int dpad_of(int d) { return d <= 32 ? 32 : 64; }
+
+struct TriattWs {
+  __nv_bfloat16 *xn, *qkg, *vt, *bias, *og;
+};
+size_t carve_triatt(TriattWs& w, void* base, int batch, int n, int c, int heads) {
+  Carver cv(base);
+  const size_t pos = static_cast<size_t>(batch) * n * n;
+  const int hdp = heads * dpad_of(c / heads);
+  w.xn = cv.take<__nv_bfloat16>(pos * c);
+  w.qkg = cv.take<__nv_bfloat16>(pos * 3 * hdp);
+  w.vt = cv.take<__nv_bfloat16>(pos * hdp);
+  w.bias = cv.take<__nv_bfloat16>(pos * heads);
+  w.og = cv.take<__nv_bfloat16>(pos * c);
+  return cv.off;
+}
+
+struct ApbWs {
+  __nv_bfloat16 *qkg, *vt, *og;
+};
+size_t carve_apb(ApbWs& w, void* base, int batch, int l, int c, int heads) {
+  Carver cv(base);
+  const size_t rows = static_cast<size_t>(batch) * l;
+  const int hdp = heads * dpad_of(c / heads);
+  w.qkg = cv.take<__nv_bfloat16>(rows * 3 * hdp);
+  w.vt = cv.take<__nv_bfloat16>(rows * hdp);
+  w.og = cv.take<__nv_bfloat16>(rows * c);
+  return cv.off;
+}
+
+}  // namespace
+
+extern "C" {
+
+KFB_API size_t kfb_triatt_workspace_bytes(int batch, int n, int c, int heads) {
+  TriattWs w;
+  return carve_triatt(w, nullptr, batch, n, c, heads);
+}
+
+KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask, const float* ln_w, const float* ln_b,
+                           const void* w_proj_packed, const void* w_out, void* out, const void* resid, void* workspace,
+                           size_t workspace_bytes, int batch, int n, int c, int heads, float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(x && mask && w_proj_packed && w_out && out && workspace, "triatt: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "triatt: bad dtype %d", dtype);
+  KFB_CHECK_ARG(batch >= 1 && n >= 8 && n % 8 == 0, "triatt: N=%d must be a positive multiple of 8 (pad in the caller)", n);
+  KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "triatt: C=%d heads=%d", c, heads);
+  const int d = c / heads;
+  KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "triatt: head dim %d not in {16, 24, ..., 64}", d);
+  KFB_CHECK_ARG(static_cast<long long>(batch) * n <= 65535, "triatt: batch*N = %lld exceeds 65535", static_cast<long long>(batch) * n);
+  const int dp = dpad_of(d), hdp = heads * dp;
+  TriattWs w;
+  const size_t need = carve_triatt(w, workspace, batch, n, c, heads);
+  KFB_CHECK_ARG(workspace_bytes >= need, "triatt: workspace %zu < %zu bytes", workspace_bytes, need);
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "triatt: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  const long long nn = static_cast<long long>(n) * n;
+  const long long pos = nn * batch;
+
+  KFB_TRY(launch_layernorm(stream, x, w.xn, ln_w, ln_b, pos, c, c, c, eps, dtype, KFB_BF16));
+  // projection: rows walked as (b, o, n); for the ending node (o, n) = (second, first) pair index
+  {
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = n;
+    p.batch = batch;
+    p.n_cols = 4 * hdp + 32;
+    p.k_extent = c;
+    p.nseg = 3;
+    p.seg[0] = row_major_seg(w.qkg, 3 * hdp, 3 * hdp, static_cast<long long>(n) * 3 * hdp, nn * 3 * hdp, 0, 0);
+    EpiSeg& sv = p.seg[1];
+    sv = {};
+    sv.col_begin = 3 * hdp;
+    sv.ncols = hdp;
+    sv.dst = w.vt;
+    sv.s_col = n;
+    sv.s_n = 1;
+    sv.s_o = static_cast<long long>(hdp) * n;
+    sv.s_b = static_cast<long long>(hdp) * nn;
+    EpiSeg& sb = p.seg[2];
+    sb = {};
+    sb.col_begin = 4 * hdp;
+    sb.ncols = heads;
+    sb.dst = w.bias;
+    sb.s_col = nn;
+    sb.s_n = 1;
+    sb.s_o = n;
+    sb.s_b = static_cast<long long>(heads) * nn;
+    GemmOperandA a = {w.xn, ending ? static_cast<long long>(n) * c : c, ending ? c : static_cast<long long>(n) * c, nn * c};
+    GemmOperandB b = {w_proj_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128));
+  }
+  {
+    AttnParams p = {};
+    p.batch = batch * n;
+    p.heads = heads;
+    p.lq = n;
+    p.lk = n;
+    p.d = d;
+    p.dpad = dp;
+    p.q = w.qkg; p.ldq = 3 * hdp; p.q_col0 = 0;
+    p.k = w.qkg; p.ldk = 3 * hdp; p.k_col0 = hdp;
+    p.g = w.qkg; p.ldg = 3 * hdp; p.g_col0 = 2 * hdp;
+    p.vt = w.vt; p.ldv = n;
+    p.bias = w.bias; p.ldb = n; p.bias_div = n;
+    p.mask = mask;
+    p.mask_lo_extent = n;
+    p.m_hi = nn;
+    p.m_lo = ending ? 1 : n;
+    p.m_k = ending ? n : 1;
+    p.out = w.og; p.ldo = c;
+    KFB_TRY(launch_attention(stream, p));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = n;
+    p.batch = batch;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    // row (b, o, n) goes back to pair position (o, n) for the starting node, (n, o) for the ending node
+    p.seg[0] = row_major_seg(out, c, ending ? static_cast<long long>(n) * c : c, ending ? c : static_cast<long long>(n) * c,
+                             nn * c, dtype == KFB_FP32);
+    p.resid = resid;
+    GemmOperandA a = {w.og, c, static_cast<long long>(n) * c, nn * c};
+    GemmOperandB b = {w_out, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+  }
+  return KFB_OK;
+}
+
+KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads) {
+  ApbWs w;
+  return carve_apb(w, nullptr, batch, l, c, heads);
+}
+
+KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
+                        const float* proj_bias, const void* w_out, const float* out_bias, void* out, const void* resid,
+                        void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_div,
+                        int out_dtype, void* stream_) {
+  KFB_CHECK_ARG(x && pair_bias && mask && w_proj_packed && w_out && out && workspace, "apb: null pointer");
+  KFB_CHECK_ARG(is_dtype(out_dtype), "apb: bad dtype %d", out_dtype);
+  KFB_CHECK_ARG(batch >= 1 && l >= 8 && l % 8 == 0, "apb: L=%d must be a positive multiple of 8 (pad in the caller)", l);
+  KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "apb: c=%d heads=%d", c, heads);
+  KFB_CHECK_ARG(bias_div >= 1 && batch % bias_div == 0, "apb: batch %d not a multiple of bias_div %d", batch, bias_div);
+  const int d = c / heads;
+  KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "apb: head dim %d not in {16, 24, ..., 64}", d);
+  const int dp = dpad_of(d), hdp = heads * dp;
+  ApbWs w;
+  const size_t need = carve_apb(w, workspace, batch, l, c, heads);
+  KFB_CHECK_ARG(workspace_bytes >= need, "apb: workspace %zu < %zu bytes", workspace_bytes, need);
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "apb: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  {
+    GemmParams p = {};
+    p.n_extent = l;
+    p.o_extent = batch;
+    p.batch = 1;
+    p.n_cols = 4 * hdp;
+    p.k_extent = c;
+    p.nseg = 2;
+    p.seg[0] = row_major_seg(w.qkg, 3 * hdp, 3 * hdp, static_cast<long long>(l) * 3 * hdp, 0, 0, 0);
+    EpiSeg& sv = p.seg[1];
+    sv = {};
+    sv.col_begin = 3 * hdp;
+    sv.ncols = hdp;
+    sv.dst = w.vt;
+    sv.s_col = l;
+    sv.s_n = 1;
+    sv.s_o = static_cast<long long>(hdp) * l;
+    p.col_bias = proj_bias;
+    GemmOperandA a = {x, c, static_cast<long long>(l) * c, 0};
+    GemmOperandB b = {w_proj_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128));
+  }
+  {
+    AttnParams p = {};
+    p.batch = batch;
+    p.heads = heads;
+    p.lq = l;
+    p.lk = l;
+    p.d = d;
+    p.dpad = dp;
+    p.q = w.qkg; p.ldq = 3 * hdp; p.q_col0 = 0;
+    p.k = w.qkg; p.ldk = 3 * hdp; p.k_col0 = hdp;
+    p.g = w.qkg; p.ldg = 3 * hdp; p.g_col0 = 2 * hdp;
+    p.vt = w.vt; p.ldv = l;
+    p.bias = pair_bias; p.ldb = l; p.bias_div = bias_div;
+    p.mask = mask;
+    p.mask_lo_extent = 1;
+    p.m_hi = l;
+    p.m_lo = 0;
+    p.m_k = 1;
+    p.out = w.og; p.ldo = c;
+    KFB_TRY(launch_attention(stream, p));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = batch * l;
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, 0, 0, out_dtype == KFB_FP32);
+    p.col_bias = out_bias;
+    p.resid = resid;
+    GemmOperandA a = {w.og, c, 0, 0};
+    GemmOperandB b = {w_out, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+  }
+  return KFB_OK;
+}
+
+}  // extern "C"

@@ -94,3 +94,80 @@ def triangle_multiplication(x: torch.Tensor, mask: torch.Tensor, packed: dict, d
                                    L.ptr(out), L.ptr(xp) if residual else None, L.ptr(ws), ws.numel(), b, npad, c, eps,
                                    L.dtype_code(xp.dtype), L.stream_ptr()))
     return out if npad == n else out[:, :n, :n].contiguous()
+
+
+def triangle_attention(x: torch.Tensor, mask: torch.Tensor | None, packed: dict, starting: bool, eps: float = 1e-5,
+                       residual: bool = False) -> torch.Tensor:
+    """Triangle attention around the starting / ending node
+    (model/primitives/triangle_attention.py:375-434).  x (B,N,N,C); mask (B,N,N) or None."""
+    _require_cuda(x, mask)
+    if x.dim() != 4 or x.shape[1] != x.shape[2]:
+        raise ValueError(f"triangle_attention: x {tuple(x.shape)}")
+    if mask is None:
+        mask = torch.ones(x.shape[:-1], dtype=torch.bool, device=x.device)
+    if mask.shape != x.shape[:-1]:
+        raise ValueError(f"triangle_attention: mask {tuple(mask.shape)} vs x {tuple(x.shape)}")
+    c, heads = x.shape[-1], packed["heads"]
+    if c != packed["c"]:
+        raise ValueError(f"triangle_attention: channel mismatch {c} vs {packed['c']}")
+    xp, mp, n = _pad_pair(x.contiguous(), mask.to(torch.bool).contiguous())
+    b, npad = xp.shape[0], xp.shape[1]
+    out = torch.empty_like(xp)
+    lib = L.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, lib.kfb_triatt_workspace_bytes(b, npad, c, heads))
+        L.check(lib.kfb_triatt_fwd(0 if starting else 1, L.ptr(xp), L.ptr(mp.view(torch.uint8)), L.ptr(packed["ln_w"]),
+                                   L.ptr(packed["ln_b"]), L.ptr(packed["w_proj"]), L.ptr(packed["w_out"]), L.ptr(out),
+                                   L.ptr(xp) if residual else None, L.ptr(ws), ws.numel(), b, npad, c, heads, eps,
+                                   L.dtype_code(xp.dtype), L.stream_ptr()))
+    return out if npad == n else out[:, :n, :n].contiguous()
+
+
+def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor, packed: dict,
+                        out_dtype=None) -> torch.Tensor:
+    """Gated self-attention with pair bias on already-normalised inputs
+    (model/primitives/attention.py:28-94 with x_q is x_k).
+
+    x (*, L, c); pair_bias broadcastable to (*, H, L, L) -- entries that share a bias (the
+    diffusion samples) must be adjacent in the flattened batch; mask broadcastable to (*, L).
+    """
+    _require_cuda(x, pair_bias, mask)
+    c, heads = x.shape[-1], packed["heads"]
+    l = x.shape[-2]
+    lead = x.shape[:-2]
+    batch = 1
+    for s in lead:
+        batch *= s
+    pb = pair_bias
+    # leading dims of the bias that are 1 where x's are not -> shared bias
+    pb_lead = pb.shape[:-3]
+    pb_lead = (1,) * (len(lead) - len(pb_lead)) + tuple(pb_lead)
+    nb = 1
+    for s in pb_lead:
+        nb *= s
+    # sharing must be over trailing leading-dims so that sharers are adjacent
+    k = len(lead)
+    while k > 0 and pb_lead[k - 1] == 1:
+        k -= 1
+    if tuple(pb_lead[:k]) != tuple(lead[:k]):
+        pb = pb.expand(*lead, heads, l, l)
+        pb_lead, nb = tuple(lead), batch
+    bias_div = batch // nb
+    lp = (l + 7) // 8 * 8
+    xb = x.reshape(batch, l, c).to(torch.bfloat16)
+    pbb = pb.reshape(nb, heads, l, l).to(torch.bfloat16)
+    mb = mask.to(torch.bool).expand(*lead, l).reshape(batch, l)
+    if lp != l:
+        xb = torch.nn.functional.pad(xb, (0, 0, 0, lp - l))
+        pbb = torch.nn.functional.pad(pbb, (0, lp - l, 0, lp - l))
+        mb = torch.nn.functional.pad(mb, (0, lp - l))
+    xb, pbb, mb = xb.contiguous(), pbb.contiguous(), mb.contiguous()
+    out = torch.empty(batch, lp, c, dtype=out_dtype or x.dtype, device=x.device)
+    lib = L.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, lib.kfb_apb_workspace_bytes(batch, lp, c, heads))
+        L.check(lib.kfb_apb_fwd(L.ptr(xb), L.ptr(pbb), L.ptr(mb.view(torch.uint8)), L.ptr(packed["w_proj"]),
+                                L.ptr(packed["proj_bias"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(out),
+                                None, L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div, L.dtype_code(out.dtype),
+                                L.stream_ptr()))
+    return out[:, :l].reshape(*lead, l, c)

@@ -38,3 +38,65 @@ def pack_trimul(w: dict, device, dtype=torch.bfloat16) -> dict:
         "w_pout": _dev(w["linear_p_out.weight"], device, dtype),
         "c": int(w["linear_p_out.weight"].shape[0]),
     }
+
+
+def head_dim_pad(d: int) -> int:
+    """Head dims are padded to one swizzle span of the attention kernel: 32 or 64 elements."""
+    if d % 8 != 0 or d < 16 or d > 64:
+        raise ValueError(f"head dim {d} is not supported (multiples of 8 in [16, 64])")
+    return 32 if d <= 32 else 64
+
+
+def _pad_heads(w: torch.Tensor, heads: int, d: int, dp: int, scale: float = 1.0) -> torch.Tensor:
+    """[heads*d, k] (or [heads*d]) -> [heads*dp, k] with zero rows after each head's d rows."""
+    tail = w.shape[1:]
+    out = w.new_zeros((heads, dp) + tuple(tail))
+    out[:, :d] = w.reshape((heads, d) + tuple(tail)) * scale
+    return out.reshape((heads * dp,) + tuple(tail))
+
+
+def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
+    """Weights of TriangleAttention (model/primitives/triangle_attention.py:338-373).
+
+    One projection matrix [q / sqrt(D) | k | g | v | triangle-bias] with every head padded to the
+    kernel's head stride and the bias rows padded to 32.
+    """
+    c = int(w["mha.linear_q.weight"].shape[1])
+    d = c // heads
+    dp = head_dim_pad(d)
+    f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
+    wz = w["linear.weight"].detach().float()
+    wz_pad = wz.new_zeros(32, c)
+    wz_pad[:heads] = wz
+    proj = torch.cat([f("mha.linear_q.weight", d ** -0.5), f("mha.linear_k.weight"), f("mha.linear_g.weight"),
+                      f("mha.linear_v.weight"), wz_pad], dim=0)
+    return {
+        "ln_w": _dev(w["layer_norm.weight"], device, torch.float32),
+        "ln_b": _dev(w["layer_norm.bias"], device, torch.float32),
+        "w_proj": _dev(proj, device, dtype),
+        "w_out": _dev(w["mha.linear_o.weight"], device, dtype),
+        "c": c, "heads": heads,
+    }
+
+
+def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
+    """Projections of AttentionPairBias (model/layers/folding/attention_pair_bias.py:30-67):
+    [q / sqrt(D) (+ scaled bias) | k | g | v], heads padded; output projection as is."""
+    c = int(w["linear_q.weight"].shape[1])
+    d = c // heads
+    dp = head_dim_pad(d)
+    f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
+    proj = torch.cat([f("linear_q.weight", d ** -0.5), f("linear_k.weight"), f("linear_g.weight"), f("linear_v.weight")], dim=0)
+    pb = torch.zeros(4 * heads * dp, dtype=torch.float32)
+    if w.get("linear_q.bias") is not None:
+        pb[: heads * dp] = _pad_heads(w["linear_q.bias"].detach().float(), heads, d, dp, d ** -0.5)
+    if w.get("linear_g.bias") is not None:
+        pb[2 * heads * dp: 3 * heads * dp] = _pad_heads(w["linear_g.bias"].detach().float(), heads, d, dp)
+    ob = w.get("linear_out.bias")
+    return {
+        "w_proj": _dev(proj, device, dtype),
+        "proj_bias": _dev(pb, device, torch.float32),
+        "w_out": _dev(w["linear_out.weight"], device, dtype),
+        "out_bias": None if ob is None else _dev(ob, device, torch.float32),
+        "c": c, "heads": heads,
+    }
