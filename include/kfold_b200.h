@@ -57,6 +57,93 @@ KFB_API const char* kfb_last_error(void);
  * (then also resets it).  For tests and post-mortems; not on the hot path. */
 KFB_API int kfb_device_status(int* code_out);
 
+/* Number of kernels this library has launched in the calling process so far. */
+KFB_API long long kfb_launch_count(void);
+
+/* Per-launch timing with CUDA events on the launch stream.  enable(1) clears old records and starts
+ * recording, enable(0) stops.  report() waits for the recorded events and writes one text line per
+ * launch tag: "<tag> <launches> <total_ms>\n".  Creates events while enabled; off by default. */
+KFB_API int kfb_profile_enable(int on);
+KFB_API int kfb_profile_report(char* buf, size_t cap);
+
+/*
+ * Triangle multiplicative update, outgoing (incoming = 0) or incoming (incoming = 1).
+ * Replaces TriangleMultiplicationOutgoing.forward / TriangleMultiplicationIncoming.forward
+ * (src/kfold/model/primitives/triangle_multiplication.py:179-229 and :263-313) and the Triton
+ * entry point `forward(x, cached, direction, mask, eps)` called at :138-144.
+ *   x, out : (batch, n, n, c) contiguous, `dtype`; n a multiple of 8, c a multiple of 64.
+ *   mask   : (batch, n, n) bytes, non-zero = valid.
+ *   w_in_packed : bf16 [4c, c], linear_p_in / linear_g_in interleaved in blocks of 128 rows
+ *                 (value rows of 128 channels, then their gate rows).
+ *   w_gout, w_pout : bf16 [c, c] (linear_g_out, linear_p_out);  ln_* : fp32 [c].
+ *   resid  : NULL, or a (batch, n, n, c) tensor of `dtype` added to the update (may equal x and out).
+ * Writes out = update (+ resid).  Arithmetic: bf16 operands, fp32 accumulation and statistics.
+ */
+KFB_API size_t kfb_trimul_workspace_bytes(int batch, int n, int c);
+KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mask, const float* ln_in_w,
+                           const float* ln_in_b, const void* w_in_packed, const void* w_gout, const float* ln_out_w,
+                           const float* ln_out_b, const void* w_pout, void* out, const void* resid, void* workspace,
+                           size_t workspace_bytes, int batch, int n, int c, float eps, int dtype, void* stream);
+
+/*
+ * Triangle attention around the starting node (ending = 0) or the ending node (ending = 1).
+ * Replaces TriangleAttention.forward + MultiHeadAttention.forward
+ * (src/kfold/model/primitives/triangle_attention.py:375-434, :285-335) and the Triton entry
+ * `triton_triangular_attn(module, x, mask)` (:63-129).  The ending node is handled inside: pass
+ * the untransposed x and mask.
+ *   x, out : (batch, n, n, c) contiguous, `dtype`;  mask : (batch, n, n) bytes.
+ *   w_proj_packed : bf16 [4*heads*dp + 32, c] = [Wq/sqrt(d) | Wk | Wg | Wv | Wz], every head padded
+ *                   from d = c/heads to dp (32 if d <= 32 else 64) rows, Wz padded to 32 rows.
+ *   w_out  : bf16 [c, c] (mha.linear_o);  resid as for kfb_trimul_fwd.
+ * Masked keys get an additive -1e9 (the reference's `inf`), so a fully masked row yields the
+ * uniform average of V, exactly as the reference does.  batch*n must not exceed 65535.
+ */
+KFB_API size_t kfb_triatt_workspace_bytes(int batch, int n, int c, int heads);
+KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask, const float* ln_w, const float* ln_b,
+                           const void* w_proj_packed, const void* w_out, void* out, const void* resid, void* workspace,
+                           size_t workspace_bytes, int batch, int n, int c, int heads, float eps, int dtype, void* stream);
+
+/*
+ * bias[b, h, i, j] = sum_c LayerNorm(z)[b, i, j, c] * w[h, c], written bf16 as (batch, heads, n, n).
+ * Replaces `linear_pair_bias(layernorm_z(z)).movedim(-1, -3)`
+ * (src/kfold/model/modules/confidence_head.py:162-163) and DiffusionStack.get_pair_bias
+ * (src/kfold/model/layers/folding/diffusion.py:411-416).  w : bf16 [heads, c].
+ */
+KFB_API size_t kfb_pair_bias_workspace_bytes(int batch, int n, int c);
+KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                              void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, float eps,
+                              int dtype, void* stream);
+
+/*
+ * Gated self-attention with pair bias on already-normalised input.
+ * Replaces `attention_pair_bias(module, x_q, x_k, pair_bias, mask, kernel_backend=..., call_site=...)`
+ * with x_q is x_k (src/kfold/model/primitives/attention.py:28-94; torch kernel :239-271).
+ *   x : bf16 (batch, l, c);  pair_bias : bf16 (batch / bias_div, heads, l, l) -- `bias_div` consecutive
+ *   batch entries share one bias (the diffusion samples);  mask : (batch, l) bytes;  l multiple of 8.
+ *   w_proj_packed : bf16 [4*heads*dp, c] = [Wq/sqrt(d) | Wk | Wg | Wv], heads padded to dp;
+ *   proj_bias : fp32 [4*heads*dp] (scaled q bias in the first quarter) or NULL;
+ *   w_out : bf16 [c, c];  out_bias : fp32 [c] or NULL;  out : (batch, l, c) of `out_dtype`;
+ *   resid : NULL or a tensor like out that is added.
+ */
+KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads);
+KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
+                        const float* proj_bias, const void* w_out, const float* out_bias, void* out, const void* resid,
+                        void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_div,
+                        int out_dtype, void* stream);
+
+/*
+ * Transition: out = Linear_out(silu(u_a) * u_b), [u_a, u_b] = Linear(LayerNorm(x))  (+ resid).
+ * Replaces Transition.forward (src/kfold/model/layers/folding/transition.py:48-68) with SwiGLU.forward
+ * (src/kfold/model/primitives/activation.py:27-29).
+ *   x, out : (rows, c) of `dtype`;  w_swiglu_packed : bf16 [2*hidden, c], the silu half and the linear
+ *   half interleaved in blocks of 128 rows;  w_out : bf16 [c, hidden];  hidden a multiple of 128.
+ */
+KFB_API size_t kfb_transition_workspace_bytes(long long rows, int c, int hidden);
+KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu_packed,
+                               const void* w_out, void* out, const void* resid, void* workspace, size_t workspace_bytes,
+                               long long rows, int c, int hidden, float eps, int dtype, void* stream);
+
+
 /*
  * LayerNorm over the last dimension: y = (x - mean) * rstd * weight + bias, statistics in fp32.
  * Replaces LayerNorm.forward (src/kfold/model/primitives/normalization.py:61-91).

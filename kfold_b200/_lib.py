@@ -27,6 +27,8 @@ class KfbError(RuntimeError):
 _SIGNATURES = {
     "kfb_version": [],
     "kfb_device_status": [ctypes.POINTER(c_int)],
+    "kfb_profile_enable": [c_int],
+    "kfb_profile_report": [ctypes.c_char_p, ctypes.c_size_t],
     "kfb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_float, c_int, c_int, c_void_p],
     "kfb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll,
                       c_ll, c_int, c_void_p],
@@ -36,8 +38,14 @@ _SIGNATURES = {
                        ctypes.c_size_t, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t,
+                           c_ll, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_pair_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int,
+                          c_int, c_float, c_int, c_void_p],
 }
 _SIZE_FUNCS = {
+    "kfb_pair_bias_workspace_bytes": [c_int, c_int, c_int],
+    "kfb_transition_workspace_bytes": [c_ll, c_int, c_int],
     "kfb_triatt_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_trimul_workspace_bytes": [c_int, c_int, c_int],
@@ -60,6 +68,8 @@ def lib() -> ctypes.CDLL:
             fn = getattr(l, name)
             fn.argtypes = args
             fn.restype = ctypes.c_size_t
+        l.kfb_launch_count.argtypes = []
+        l.kfb_launch_count.restype = c_ll
         l.kfb_last_error.argtypes = []
         l.kfb_last_error.restype = ctypes.c_char_p
         _lib = l
@@ -95,3 +105,24 @@ def device_status() -> int:
     code = c_int(0)
     check(lib().kfb_device_status(ctypes.byref(code)))
     return code.value
+
+
+def launch_count() -> int:
+    """Number of kernels this library has launched in this process."""
+    return int(lib().kfb_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    """Start (and clear) or stop per-launch CUDA-event timing inside the library."""
+    check(lib().kfb_profile_enable(1 if on else 0))
+
+
+def profile_report() -> dict:
+    """{tag: (launches, total_ms)} for the launches recorded since profile_enable(True)."""
+    buf = ctypes.create_string_buffer(16384)
+    check(lib().kfb_profile_report(buf, len(buf)))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        tag, n, ms = line.split()
+        out[tag] = (int(n), float(ms))
+    return out

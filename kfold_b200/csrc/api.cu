@@ -25,7 +25,19 @@ KFB_API int kfb_device_status(int* code_out) {
   return KFB_OK;
 }
 
-KFB_API int kfb_layernorm(const void* x, void* y, const float* weight, const float* bias, long long rows, int c,
+KFB_API KFB_API long long kfb_launch_count(void) { return launch_count(); }
+
+KFB_API int kfb_profile_enable(int on) {
+  profile_enable(on != 0);
+  return KFB_OK;
+}
+
+KFB_API int kfb_profile_report(char* buf, size_t cap) {
+  KFB_CHECK_ARG(buf != nullptr && cap > 0, "profile_report: empty buffer");
+  return profile_report(buf, cap) >= 0 ? KFB_OK : KFB_ERR_CUDA;
+}
+
+int kfb_layernorm(const void* x, void* y, const float* weight, const float* bias, long long rows, int c,
                   long long x_row_stride, long long y_row_stride, float eps, int in_dtype, int out_dtype, void* stream) {
   KFB_CHECK_ARG(x != nullptr && y != nullptr, "layernorm: null tensor");
   return launch_layernorm(as_stream(stream), x, y, weight, bias, rows, c, x_row_stride, y_row_stride, eps, in_dtype,

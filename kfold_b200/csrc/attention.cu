@@ -349,7 +349,10 @@ static int launch_dpad(cudaStream_t stream, const AttnParams& p) {
     KFB_TRY(make_tmap(&tb, p.bias, 2, 3, dims, str, box, 128));
   }
   dim3 grid(cdiv(p.lq, kBQ), p.heads, p.batch);
-  attention_bias_kernel<DPAD><<<grid, kAttThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tb, p);
+  {
+    LaunchScope scope(stream, p.tag ? p.tag : "attention");
+    attention_bias_kernel<DPAD><<<grid, kAttThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tb, p);
+  }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }

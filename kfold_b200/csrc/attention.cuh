@@ -39,6 +39,7 @@ struct AttnParams {
   const void* g; long long ldg; int g_col0;
   // output bf16: row (b, q) at out + (b*lq + q)*ldo, head h at column h*d
   void* out; long long ldo;
+  const char* tag;  // name of the launch in the profile report (string literal), may be null
 };
 
 int launch_attention(cudaStream_t stream, const AttnParams& p);

@@ -3,7 +3,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -21,6 +23,73 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 const char* get_error() { return t_error; }
+
+// ------------------------------------------------------------------------------------------------
+// launch counter + optional per-launch event timing
+// ------------------------------------------------------------------------------------------------
+namespace {
+struct ProfRec {
+  cudaEvent_t e0, e1;
+  const char* tag;
+};
+std::mutex g_prof_mu;
+std::vector<ProfRec> g_prof;
+bool g_prof_on = false;
+std::atomic<long long> g_launches{0};
+}  // namespace
+
+LaunchScope::LaunchScope(cudaStream_t stream, const char* tag) : stream_(stream), slot_(-1) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!g_prof_on) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  ProfRec r;
+  r.tag = tag;
+  if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+  cudaEventRecord(r.e0, stream);
+  g_prof.push_back(r);
+  slot_ = static_cast<int>(g_prof.size()) - 1;
+}
+LaunchScope::~LaunchScope() {
+  if (slot_ < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (slot_ < static_cast<int>(g_prof.size())) cudaEventRecord(g_prof[slot_].e1, stream_);
+}
+
+long long launch_count() { return g_launches.load(); }
+
+void profile_enable(bool on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) {
+    cudaEventDestroy(r.e0);
+    cudaEventDestroy(r.e1);
+  }
+  g_prof.clear();
+  g_prof_on = on;
+}
+
+// Writes one line per tag: "<tag> <launches> <total_ms>\n".  Synchronises on the recorded events.
+int profile_report(char* buf, size_t cap) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  struct Agg { const char* tag; long long n; double ms; };
+  std::vector<Agg> agg;
+  for (auto& r : g_prof) {
+    if (cudaEventSynchronize(r.e1) != cudaSuccess) continue;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
+    bool found = false;
+    for (auto& a : agg)
+      if (strcmp(a.tag, r.tag) == 0) { a.n++; a.ms += ms; found = true; break; }
+    if (!found) agg.push_back({r.tag, 1, ms});
+  }
+  size_t off = 0;
+  for (auto& a : agg) {
+    int w = snprintf(buf + off, off < cap ? cap - off : 0, "%s %lld %.6f\n", a.tag, a.n, a.ms);
+    if (w < 0 || off + w >= cap) break;
+    off += w;
+  }
+  if (cap) buf[off < cap ? off : cap - 1] = 0;
+  return static_cast<int>(agg.size());
+}
 
 int sm_count() {
   static int cached[64];

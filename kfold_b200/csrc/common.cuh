@@ -40,6 +40,19 @@ const char* get_error();
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+// Launch accounting.  Every kernel launch goes through a LaunchScope: it bumps the global launch
+// counter and, while profiling is enabled, brackets the launch with CUDA events on its stream.
+struct LaunchScope {
+  LaunchScope(cudaStream_t stream, const char* tag);
+  ~LaunchScope();
+  cudaStream_t stream_;
+  int slot_;
+};
+
+long long launch_count();
+void profile_enable(bool on);
+int profile_report(char* buf, size_t cap);
+
 int sm_count();  // multiprocessors of the current device (cached per device)
 
 // Encode a tiled tensor map.  dims/strides are given innermost first; strides[i] is the

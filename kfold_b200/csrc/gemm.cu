@@ -7,7 +7,7 @@
 namespace kfb {
 
 template <int BN>
-static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p) {
+static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, const char* tag) {
   using Cfg = GemmCfg<BN>;
   static std::once_flag once[64];
   int dev = 0;
@@ -19,12 +19,16 @@ static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorM
   KFB_CUDA(attr_err);
   const int total = p.num_m_tiles * p.num_n_tiles;
   const int grid = total < sm_count() ? total : sm_count();
-  gemm_bf16_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  {
+    LaunchScope scope(stream, tag);
+    gemm_bf16_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }
 
-int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn) {
+int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn,
+                     const char* tag) {
   KFB_CHECK_ARG(p.n_extent > 0 && p.o_extent > 0 && p.batch > 0 && p.n_cols > 0 && p.k_extent > 0, "empty GEMM");
   KFB_CHECK_ARG(p.nseg >= 1 && p.nseg <= 3, "GEMM needs 1..3 output segments");
   int bn = force_bn;
@@ -51,9 +55,9 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
     KFB_TRY(make_tmap(&tb, b.ptr, 2, 3, dims, str, box, 128));
   }
   switch (bn) {
-    case 64: return launch_bn<64>(stream, ta, tb, p);
-    case 128: return launch_bn<128>(stream, ta, tb, p);
-    default: return launch_bn<256>(stream, ta, tb, p);
+    case 64: return launch_bn<64>(stream, ta, tb, p, tag);
+    case 128: return launch_bn<128>(stream, ta, tb, p, tag);
+    default: return launch_bn<256>(stream, ta, tb, p, tag);
   }
 }
 

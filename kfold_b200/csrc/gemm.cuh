@@ -343,6 +343,8 @@ struct GemmOperandB {  // B[(b), col, k]
 };
 
 // Fills the tile bookkeeping of `p`, builds the tensor maps and launches on `stream`.
-int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn = 0);
+// `tag` names the launch in the profile report (a string literal).
+int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn = 0,
+                     const char* tag = "gemm");
 
 }  // namespace kfb

@@ -91,6 +91,7 @@ static int launch_rows(cudaStream_t stream, const void* x, void* y, const float*
   long long blocks = (rows + warps - 1) / warps;
   const long long cap = static_cast<long long>(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
+  LaunchScope scope(stream, "layernorm_rows");
   layernorm_rows_kernel<TI, TO, G><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(
       static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps);
   KFB_CUDA(cudaGetLastError());
@@ -184,6 +185,7 @@ int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, co
   if (npos == 0 || batch == 0) return KFB_OK;
   const int bpb = static_cast<int>((npos + kCmPos - 1) / kCmPos);
   const size_t smem = static_cast<size_t>(c) * 65 * sizeof(float);
+  LaunchScope scope(stream, "layernorm_cm");
   if (in_dtype == KFB_BF16) {
     if (smem > 48 * 1024)
       KFB_CUDA(cudaFuncSetAttribute(layernorm_cm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

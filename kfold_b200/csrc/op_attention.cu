@@ -108,7 +108,7 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
     sb.s_b = static_cast<long long>(heads) * nn;
     GemmOperandA a = {w.xn, ending ? static_cast<long long>(n) * c : c, ending ? c : static_cast<long long>(n) * c, nn * c};
     GemmOperandB b = {w_proj_packed, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "triatt_proj"));
   }
   {
     AttnParams p = {};
@@ -129,6 +129,7 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
     p.m_lo = ending ? 1 : n;
     p.m_k = ending ? n : 1;
     p.out = w.og; p.ldo = c;
+    p.tag = "triatt_attention";
     KFB_TRY(launch_attention(stream, p));
   }
   {
@@ -145,9 +146,47 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
     p.resid = resid;
     GemmOperandA a = {w.og, c, static_cast<long long>(n) * c, nn * c};
     GemmOperandB b = {w_out, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "triatt_out_proj"));
   }
   return KFB_OK;
+}
+
+KFB_API size_t kfb_pair_bias_workspace_bytes(int batch, int n, int c) {
+  return align_up(static_cast<size_t>(batch) * n * n * c * sizeof(__nv_bfloat16), 256);
+}
+
+// bias[b][h][i][j] = sum_c LN(z)[b][i][j][c] * W[h][c], stored bf16 channel(head)-major.
+KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                              void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, float eps,
+                              int dtype, void* stream_) {
+  KFB_CHECK_ARG(z && w && bias_out && workspace, "pair_bias: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "pair_bias: bad dtype %d", dtype);
+  KFB_CHECK_ARG(batch >= 1 && n >= 8 && n % 8 == 0 && c % 8 == 0 && heads >= 1, "pair_bias: batch %d n %d c %d heads %d",
+                batch, n, c, heads);
+  KFB_CHECK_ARG(workspace_bytes >= kfb_pair_bias_workspace_bytes(batch, n, c), "pair_bias: workspace too small");
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "pair_bias: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  const long long nn = static_cast<long long>(n) * n;
+  __nv_bfloat16* zn = static_cast<__nv_bfloat16*>(workspace);
+  KFB_TRY(launch_layernorm(stream, z, zn, ln_w, ln_b, nn * batch, c, c, c, eps, dtype, KFB_BF16));
+  GemmParams p = {};
+  p.n_extent = n;
+  p.o_extent = n;
+  p.batch = batch;
+  p.n_cols = heads;
+  p.k_extent = c;
+  p.nseg = 1;
+  EpiSeg& s = p.seg[0];
+  s.col_begin = 0;
+  s.ncols = heads;
+  s.dst = bias_out;
+  s.s_col = nn;
+  s.s_n = 1;
+  s.s_o = n;
+  s.s_b = static_cast<long long>(heads) * nn;
+  GemmOperandA a = {zn, c, static_cast<long long>(n) * c, nn * c};
+  GemmOperandB b = {w, c, 0};
+  return launch_gemm_bf16(stream, a, b, p, 0, "pair_bias_proj");
 }
 
 KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads) {
@@ -192,7 +231,7 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     p.col_bias = proj_bias;
     GemmOperandA a = {x, c, static_cast<long long>(l) * c, 0};
     GemmOperandB b = {w_proj_packed, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "apb_proj"));
   }
   {
     AttnParams p = {};
@@ -213,6 +252,7 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     p.m_lo = 0;
     p.m_k = 1;
     p.out = w.og; p.ldo = c;
+    p.tag = "apb_attention";
     KFB_TRY(launch_attention(stream, p));
   }
   {
@@ -228,7 +268,7 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     p.resid = resid;
     GemmOperandA a = {w.og, c, 0, 0};
     GemmOperandB b = {w_out, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "apb_out_proj"));
   }
   return KFB_OK;
 }

@@ -86,7 +86,7 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
     GemmOperandA a = {w.xn, incoming ? static_cast<long long>(n) * c : c, incoming ? c : static_cast<long long>(n) * c,
                       nn * c};
     GemmOperandB b = {w_in_packed, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 256));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 256, "trimul_in_proj"));
   }
   // 3. output gate logits (natural order)
   {
@@ -100,7 +100,7 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
     p.seg[0] = row_major_seg(w.gl, c, c, 0, 0, 0);
     GemmOperandA a = {w.xn, c, 0, 0};
     GemmOperandB b = {w_gout, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_gate_proj"));
   }
   // 4. contraction: t[ch*B+b][i][j] = sum_k A[i][k] B[j][k]
   {
@@ -115,7 +115,7 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
     p.seg[0] = row_major_seg(w.t, n, n, 0, nn, 0);
     GemmOperandA a = {w.ab, n, 0, nn};
     GemmOperandB b = {w.ab + static_cast<long long>(c) * pos, n, nn};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_contraction"));
   }
   // 5. LayerNorm_out: channel-major t -> position-major tn (reuses xn's storage)
   __nv_bfloat16* tn = w.xn;
@@ -136,7 +136,7 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
     p.resid = resid;
     GemmOperandA a = {tn, c, 0, 0};
     GemmOperandB b = {w_pout, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p));
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_out_proj"));
   }
   return KFB_OK;
 }

@@ -171,3 +171,40 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
                                 None, L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div, L.dtype_code(out.dtype),
                                 L.stream_ptr()))
     return out[:, :l].reshape(*lead, l, c)
+
+
+def transition(x: torch.Tensor, packed: dict, eps: float = 1e-5, residual: bool = False) -> torch.Tensor:
+    """Transition layer (model/layers/folding/transition.py:48-68).  x (..., C)."""
+    _require_cuda(x)
+    c, hidden = packed["c"], packed["hidden"]
+    if x.shape[-1] != c:
+        raise ValueError(f"transition: channel mismatch {x.shape[-1]} vs {c}")
+    x2 = x.reshape(-1, c).contiguous()
+    rows = x2.shape[0]
+    out = torch.empty_like(x2)
+    lib = L.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, lib.kfb_transition_workspace_bytes(rows, c, hidden))
+        L.check(lib.kfb_transition_fwd(L.ptr(x2), L.ptr(packed["ln_w"]), L.ptr(packed["ln_b"]), L.ptr(packed["w_swiglu"]),
+                                       L.ptr(packed["w_out"]), L.ptr(out), L.ptr(x2) if residual else None, L.ptr(ws),
+                                       ws.numel(), rows, c, hidden, eps, L.dtype_code(x2.dtype), L.stream_ptr()))
+    return out.view(x.shape)
+
+
+def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """bias = Linear(LayerNorm(z)) moved to (B, H, N, N), bf16
+    (model/modules/confidence_head.py:162-163; model/layers/folding/diffusion.py:411-416).
+    z (B,N,N,C); w (H,C) already on the device in bf16; N must be a multiple of 8."""
+    _require_cuda(z, w)
+    b, n, _, c = z.shape
+    if n % 8 != 0:
+        raise ValueError("pair_bias: N must be a multiple of 8")
+    heads = w.shape[0]
+    out = torch.empty(b, heads, n, n, dtype=torch.bfloat16, device=z.device)
+    zc = z.contiguous()
+    lib = L.lib()
+    with torch.cuda.device(z.device):
+        ws = _workspace(z.device, lib.kfb_pair_bias_workspace_bytes(b, n, c))
+        L.check(lib.kfb_pair_bias_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), b, n,
+                                      c, heads, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
+    return out

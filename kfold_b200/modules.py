@@ -1,0 +1,328 @@
+"""Host-side mirror of the reference modules on the hot path.
+
+Same class names, constructor arguments, parameter names (so a reference
+``state_dict`` loads with ``strict=True``) and ``forward`` signatures as the K-Fold
+modules they stand in for, with the CUDA kernels behind them:
+
+  TriangleMultiplicationOutgoing / Incoming   model/primitives/triangle_multiplication.py:148-313
+  TriangleAttentionStartingNode / EndingNode  model/primitives/triangle_attention.py:338-465
+  Transition                                  model/layers/folding/transition.py:20-68
+  SelfAttentionPairBias (channel_s=None)      model/layers/folding/attention_pair_bias.py:70-158
+  TriangularBlock                             model/modules/tri_stack.py:86-151
+  PairformerBlock (pair + single track)       model/modules/apo_module.py:107-172 +
+                                              model/modules/confidence_head.py:125-175
+
+Conventions copied from the reference's Triton backend
+(model/primitives/triangle_multiplication.py:94-145): inference only (``RuntimeError``
+when autograd is recording or the input is not on a CUDA device), compute dtype =
+autocast dtype if autocast is on else the input dtype, result returned in the input
+dtype, weights packed once per module and re-packed when a parameter's storage or
+version changes.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from . import functional as F
+from . import packing
+
+__all__ = [
+    "LayerNorm", "LinearNoBias", "Linear",
+    "TriangleMultiplicationOutgoing", "TriangleMultiplicationIncoming",
+    "TriangleAttentionStartingNode", "TriangleAttentionEndingNode",
+    "Transition", "SelfAttentionPairBias", "TriangularBlock", "PairformerBlock",
+]
+
+
+# --------------------------------------------------------------------------------------------
+# parameter holders (names match the reference so that state dicts are interchangeable)
+# --------------------------------------------------------------------------------------------
+class LayerNorm(nn.Module):
+    """LayerNorm with fp32 statistics (model/primitives/normalization.py:24-91)."""
+
+    def __init__(self, normalized_shape: int, create_scale: bool = True, create_offset: bool = True, eps: float = 1e-5):
+        super().__init__()
+        self.normalized_shape = normalized_shape
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(normalized_shape)) if create_scale else None
+        self.bias = nn.Parameter(torch.zeros(normalized_shape)) if create_offset else None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        _check_inference(x)
+        return F.layer_norm(x, self.weight, self.bias, self.eps)
+
+
+class Linear(nn.Module):
+    """Parameter holder for a projection; N(0, 1/fan_in) init (model/primitives/linear.py:25-107)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True):
+        super().__init__()
+        self.weight = nn.Parameter(torch.randn(out_features, in_features) * in_features ** -0.5)
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_features))
+        else:
+            self.register_parameter("bias", None)
+
+
+class LinearNoBias(Linear):
+    def __init__(self, in_features: int, out_features: int):
+        super().__init__(in_features, out_features, bias=False)
+
+
+class _SwiGLU(nn.Module):
+    def __init__(self, channel_in: int, channel_out: int):
+        super().__init__()
+        self.linear = LinearNoBias(channel_in, channel_out * 2)
+
+
+# --------------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------------
+def _check_inference(x: torch.Tensor) -> None:
+    if torch.is_grad_enabled():
+        raise RuntimeError("The kfold_b200 kernel backend is inference-only (run under torch.no_grad()).")
+    if not x.is_cuda:
+        raise RuntimeError("The kfold_b200 kernel backend requires CUDA tensors.")
+
+
+def compute_dtype(x: torch.Tensor) -> torch.dtype:
+    """Autocast dtype when autocast is on, else the input dtype
+    (model/primitives/triangle_multiplication.py:67-70)."""
+    if torch.is_autocast_enabled(x.device.type):
+        return torch.get_autocast_dtype(x.device.type)
+    return x.dtype
+
+
+def _require_bf16(dt: torch.dtype, what: str) -> None:
+    if dt != torch.bfloat16:
+        raise NotImplementedError(
+            f"{what}: compute dtype {dt} is not available in this build; run under "
+            "torch.autocast('cuda', dtype=torch.bfloat16) or pass bfloat16 inputs")
+
+
+class _PackedMixin:
+    """Packs the module's weights once and re-packs when any parameter changes
+    (same cache key as model/primitives/triangle_multiplication.py:73-91)."""
+
+    _pack_cache = None
+    _pack_key = None
+
+    def _packed(self, device: torch.device, dtype: torch.dtype, pack_fn):
+        key = (device.type, device.index, dtype) + tuple(
+            v for p in self.parameters() for v in (p.data_ptr(), None if torch.is_inference(p) else p._version))
+        if self._pack_cache is None or self._pack_key != key:
+            sd = {k: v for k, v in self.state_dict().items()}
+            self._pack_cache = pack_fn(sd, device)
+            self._pack_key = key
+        return self._pack_cache
+
+
+# --------------------------------------------------------------------------------------------
+# primitives
+# --------------------------------------------------------------------------------------------
+class _TriangleMultiplication(nn.Module, _PackedMixin):
+    direction = "outgoing"
+
+    def __init__(self, dim: int = 128, kernel_backend: str = "b200") -> None:
+        super().__init__()
+        self.kernel_backend = kernel_backend
+        self.layernorm_in = LayerNorm(dim)
+        self.linear_p_in = LinearNoBias(dim, 2 * dim)
+        self.linear_g_in = LinearNoBias(dim, 2 * dim)
+        self.layernorm_out = LayerNorm(dim)
+        self.linear_p_out = LinearNoBias(dim, dim)
+        self.linear_g_out = LinearNoBias(dim, dim)
+
+    @torch.compiler.disable
+    def forward(self, x: torch.Tensor, mask: torch.Tensor, residual: bool = False) -> torch.Tensor:
+        """x (B,N,N,D), mask (B,N,N) -> update (B,N,N,D); with ``residual`` returns x + update."""
+        _check_inference(x)
+        cd = compute_dtype(x)
+        _require_bf16(cd, type(self).__name__)
+        pk = self._packed(x.device, cd, packing.pack_trimul)
+        with torch.autocast(x.device.type, enabled=False):
+            out = F.triangle_multiplication(x, mask, pk, self.direction, eps=self.layernorm_in.eps, residual=residual)
+        return out.to(x.dtype)
+
+
+class TriangleMultiplicationOutgoing(_TriangleMultiplication):
+    direction = "outgoing"
+
+
+class TriangleMultiplicationIncoming(_TriangleMultiplication):
+    direction = "incoming"
+
+
+class _MHAParams(nn.Module):
+    def __init__(self, c_in: int, c_hidden: int, no_heads: int):
+        super().__init__()
+        self.linear_q = LinearNoBias(c_in, c_hidden * no_heads)
+        self.linear_k = LinearNoBias(c_in, c_hidden * no_heads)
+        self.linear_v = LinearNoBias(c_in, c_hidden * no_heads)
+        self.linear_o = LinearNoBias(c_hidden * no_heads, c_in)
+        self.linear_g = LinearNoBias(c_in, c_hidden * no_heads)
+
+
+class _TriangleAttention(nn.Module, _PackedMixin):
+    starting = True
+
+    def __init__(self, c_in: int, no_heads: int, inf: float = 1e9, kernel_backend: str = "b200") -> None:
+        super().__init__()
+        assert c_in % no_heads == 0, f"c_in ({c_in}) must be divisible by no_heads ({no_heads})"
+        if inf != 1e9:
+            raise ValueError("the kernel's key-mask offset is fixed at 1e9 (the reference default)")
+        self.c_in, self.no_heads, self.c_hidden, self.inf = c_in, no_heads, c_in // no_heads, inf
+        self.kernel_backend = kernel_backend
+        self.layer_norm = LayerNorm(c_in)
+        self.linear = LinearNoBias(c_in, no_heads)
+        self.mha = _MHAParams(c_in, self.c_hidden, no_heads)
+
+    @torch.compiler.disable
+    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, residual: bool = False) -> torch.Tensor:
+        """x (*,I,J,C), mask (*,I,J) or None -> update (*,I,J,C)."""
+        _check_inference(x)
+        cd = compute_dtype(x)
+        _require_bf16(cd, type(self).__name__)
+        pk = self._packed(x.device, cd, lambda sd, dev: packing.pack_triatt(sd, self.no_heads, dev))
+        lead = x.shape[:-3]
+        x4 = x.reshape(-1, *x.shape[-3:])
+        m4 = None if mask is None else mask.reshape(-1, *mask.shape[-2:])
+        with torch.autocast(x.device.type, enabled=False):
+            out = F.triangle_attention(x4, m4, pk, self.starting, eps=self.layer_norm.eps, residual=residual)
+        return out.reshape(*lead, *x.shape[-3:]).to(x.dtype)
+
+
+class TriangleAttentionStartingNode(_TriangleAttention):
+    starting = True
+
+
+class TriangleAttentionEndingNode(_TriangleAttention):
+    starting = False
+
+
+class Transition(nn.Module, _PackedMixin):
+    def __init__(self, channel: int, expansion_factor: int) -> None:
+        super().__init__()
+        self.model_dim = channel * expansion_factor
+        self.layernorm = LayerNorm(channel)
+        self.swiglu = _SwiGLU(channel, self.model_dim)
+        self.linear_out = LinearNoBias(self.model_dim, channel)
+
+    @torch.compiler.disable
+    def forward(self, x: torch.Tensor, residual: bool = False) -> torch.Tensor:
+        _check_inference(x)
+        cd = compute_dtype(x)
+        _require_bf16(cd, "Transition")
+        pk = self._packed(x.device, cd, packing.pack_transition)
+        with torch.autocast(x.device.type, enabled=False):
+            out = F.transition(x, pk, eps=self.layernorm.eps, residual=residual)
+        return out.to(x.dtype)
+
+
+class SelfAttentionPairBias(nn.Module, _PackedMixin):
+    """Single-track form (``channel_s=None``: LayerNorm prologue, no conditioning)."""
+
+    def __init__(self, channel_a: int, num_heads: int, channel_s: int | None, call_site: str, inf: float = 1e9,
+                 kernel_backend: str = "b200") -> None:
+        super().__init__()
+        if call_site not in {"diffusion_global", "confidence"}:
+            raise ValueError(f"Unsupported self APB call site: {call_site!r}")
+        if channel_s is not None:
+            raise NotImplementedError("the AdaLN-conditioned (diffusion) form is not available in this build")
+        if inf != 1e9:
+            raise ValueError("the kernel's key-mask offset is fixed at 1e9 (the reference default)")
+        assert channel_a % num_heads == 0
+        self.channel_a, self.num_heads, self.head_dim, self.inf = channel_a, num_heads, channel_a // num_heads, inf
+        self.call_site, self.kernel_backend, self.use_single_conditioning = call_site, kernel_backend, False
+        self.linear_q = Linear(channel_a, channel_a)
+        self.linear_k = LinearNoBias(channel_a, channel_a)
+        self.linear_v = LinearNoBias(channel_a, channel_a)
+        self.linear_g = LinearNoBias(channel_a, channel_a)
+        self.linear_out = LinearNoBias(channel_a, channel_a)
+        self.layernorm_a = LayerNorm(channel_a, create_offset=True)
+
+    @torch.compiler.disable
+    def forward(self, a: torch.Tensor, s: torch.Tensor | None, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """a (...,L,c_a); s must be None; pair_bias (...,H,L,L); mask (...,L) -> (...,L,c_a)."""
+        assert s is None
+        _check_inference(a)
+        cd = compute_dtype(a)
+        _require_bf16(cd, "SelfAttentionPairBias")
+        pk = self._packed(a.device, cd, lambda sd, dev: packing.pack_apb(sd, self.num_heads, dev))
+        with torch.autocast(a.device.type, enabled=False):
+            an = F.layer_norm(a, self.layernorm_a.weight, self.layernorm_a.bias, self.layernorm_a.eps, out_dtype=torch.bfloat16)
+            out = F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype)
+        return out
+
+
+# --------------------------------------------------------------------------------------------
+# blocks
+# --------------------------------------------------------------------------------------------
+class TriangularBlock(nn.Module):
+    """K-Fold trunk block: tri-mult out, tri-mult in, transition, residual adds fused into the kernels."""
+
+    def __init__(self, channel_z: int = 256, dropout: float = 0.25, kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend, self.channel_z, self.dropout = kernel_backend, channel_z, dropout
+        self.tri_mul_out = TriangleMultiplicationOutgoing(channel_z)
+        self.tri_mul_in = TriangleMultiplicationIncoming(channel_z)
+        self.transition_z = Transition(channel_z, expansion_factor=4)
+
+    def forward(self, z: torch.Tensor, pair_mask: torch.Tensor) -> torch.Tensor:
+        z = self.tri_mul_out(z, pair_mask, residual=True)
+        z = self.tri_mul_in(z, pair_mask, residual=True)
+        return self.transition_z(z, residual=True)
+
+
+class PairformerBlock(nn.Module):
+    """AF3-shaped Pairformer block assembled from the reference's modules: the pair track in the order of
+    ``PairformerBlock.forward`` (tri-mult out/in, tri-att start/end, transition x4) and the single track of
+    ``ConfidencePairSingleBlock.forward`` (pair bias from LN(z), single attention with pair bias, transition x4)."""
+
+    def __init__(self, channel_z: int = 128, channel_s: int = 384, num_tri_heads: int = 4, num_heads: int = 16,
+                 kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend = kernel_backend
+        self.tri_mul_out = TriangleMultiplicationOutgoing(channel_z)
+        self.tri_mul_in = TriangleMultiplicationIncoming(channel_z)
+        self.tri_att_start = TriangleAttentionStartingNode(channel_z, num_tri_heads)
+        self.tri_att_end = TriangleAttentionEndingNode(channel_z, num_tri_heads)
+        self.transition_z = Transition(channel_z, expansion_factor=4)
+        self.layernorm_z = LayerNorm(channel_z)
+        self.linear_pair_bias = LinearNoBias(channel_z, num_heads)
+        self.attention = SelfAttentionPairBias(channel_s, num_heads, None, "confidence")
+        self.transition = Transition(channel_s, expansion_factor=4)
+        self._bias_w = None
+        self._bias_key = None
+
+    def _pair_bias(self, z: torch.Tensor) -> torch.Tensor:
+        p = self.linear_pair_bias.weight
+        key = (z.device, p.data_ptr(), None if torch.is_inference(p) else p._version)
+        if self._bias_key != key:
+            self._bias_w = p.detach().to(z.device, torch.bfloat16).contiguous()
+            self._bias_key = key
+        n = z.shape[1]
+        if n % 8 != 0:  # rare: pad the pair tensor so that bias rows stay 16-byte aligned
+            npad = (n + 7) // 8 * 8
+            zp = z.new_zeros(z.shape[0], npad, npad, z.shape[-1])
+            zp[:, :n, :n] = z
+            return F.pair_bias(zp, self.layernorm_z.weight.detach().float(), self.layernorm_z.bias.detach().float(),
+                               self._bias_w, self.layernorm_z.eps)[:, :, :n, :n]
+        return F.pair_bias(z, self.layernorm_z.weight.detach().float(), self.layernorm_z.bias.detach().float(),
+                           self._bias_w, self.layernorm_z.eps)
+
+    @torch.compiler.disable
+    def forward(self, z: torch.Tensor, s: torch.Tensor, pair_mask: torch.Tensor, mask: torch.Tensor):
+        """z (B,N,N,c_z), s (B,N,c_s), pair_mask (B,N,N), mask (B,N) -> (z, s)."""
+        _check_inference(z)
+        z = self.tri_mul_out(z, pair_mask, residual=True)
+        z = self.tri_mul_in(z, pair_mask, residual=True)
+        z = self.tri_att_start(z, pair_mask, residual=True)
+        z = self.tri_att_end(z, pair_mask, residual=True)
+        z = self.transition_z(z, residual=True)
+        with torch.autocast(z.device.type, enabled=False):
+            bias = self._pair_bias(z)
+        s = s + self.attention(s, None, bias, mask)
+        s = self.transition(s, residual=True)
+        return z, s

@@ -100,3 +100,17 @@ def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
         "out_bias": None if ob is None else _dev(ob, device, torch.float32),
         "c": c, "heads": heads,
     }
+
+
+def pack_transition(w: dict, device, dtype=torch.bfloat16) -> dict:
+    """Weights of Transition (model/layers/folding/transition.py:27-46): the SwiGLU matrix is split into
+    its silu half and its linear half (model/primitives/activation.py:27-29) and interleaved per GEMM tile."""
+    sw = w["swiglu.linear.weight"].detach().float()
+    hidden = sw.shape[0] // 2
+    return {
+        "ln_w": _dev(w["layernorm.weight"], device, torch.float32),
+        "ln_b": _dev(w["layernorm.bias"], device, torch.float32),
+        "w_swiglu": _dev(interleave_glu(sw[:hidden], sw[hidden:]), device, dtype),
+        "w_out": _dev(w["linear_out.weight"], device, dtype),
+        "c": int(sw.shape[1]), "hidden": int(hidden),
+    }

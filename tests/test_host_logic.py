@@ -1,0 +1,117 @@
+"""Host-side logic that needs no GPU: weight packing, module/state-dict compatibility, error behaviour."""
+import pytest
+import torch
+
+from kfold_b200 import functional as F
+from kfold_b200 import modules as M
+from kfold_b200 import packing, synth
+
+
+def test_interleave_glu_layout():
+    v = torch.arange(256 * 4, dtype=torch.float32).reshape(256, 4)
+    g = -v
+    p = packing.interleave_glu(v, g)
+    assert p.shape == (512, 4)
+    assert torch.equal(p[:128], v[:128]) and torch.equal(p[128:256], g[:128])
+    assert torch.equal(p[256:384], v[128:]) and torch.equal(p[384:], g[128:])
+
+
+def test_pad_heads_scales_and_zero_fills():
+    w = torch.ones(16 * 24, 8)
+    p = packing._pad_heads(w, 16, 24, 32, 0.5)
+    assert p.shape == (16 * 32, 8)
+    p = p.reshape(16, 32, 8)
+    assert torch.all(p[:, :24] == 0.5) and torch.all(p[:, 24:] == 0)
+
+
+def test_head_dim_pad():
+    assert packing.head_dim_pad(16) == 32 and packing.head_dim_pad(24) == 32 and packing.head_dim_pad(32) == 32
+    assert packing.head_dim_pad(48) == 64 and packing.head_dim_pad(64) == 64
+    with pytest.raises(ValueError):
+        packing.head_dim_pad(20)
+
+
+def test_pack_triatt_projection_matches_unpacked_math():
+    w = synth.triatt_weights(synth._Rng(3), 128, 4)
+    pk = packing.pack_triatt(w, 4, "cpu", torch.float32)
+    x = torch.randn(5, 128)
+    y = x @ pk["w_proj"].T
+    q = (x @ w["mha.linear_q.weight"].T) / 32 ** 0.5
+    assert torch.allclose(y[:, :128], q, atol=1e-5)
+    assert torch.allclose(y[:, 128:256], x @ w["mha.linear_k.weight"].T, atol=1e-5)
+    assert torch.allclose(y[:, 256:384], x @ w["mha.linear_g.weight"].T, atol=1e-5)
+    assert torch.allclose(y[:, 384:512], x @ w["mha.linear_v.weight"].T, atol=1e-5)
+    assert torch.allclose(y[:, 512:516], x @ w["linear.weight"].T, atol=1e-5)
+    assert torch.all(y[:, 516:] == 0)
+
+
+def test_pack_apb_pads_d24_to_32():
+    w = synth.apb_weights(synth._Rng(4), 384, None)
+    pk = packing.pack_apb(w, 16, "cpu", torch.float32)
+    assert pk["w_proj"].shape == (4 * 16 * 32, 384)
+    assert pk["proj_bias"].shape == (4 * 16 * 32,)
+    x = torch.randn(3, 384)
+    y = (x @ pk["w_proj"].T + pk["proj_bias"]).reshape(3, 4, 16, 32)
+    q = ((x @ w["linear_q.weight"].T + w["linear_q.bias"]) / 24 ** 0.5).reshape(3, 16, 24)
+    assert torch.allclose(y[:, 0, :, :24], q, atol=1e-5)
+    assert torch.all(y[:, 0, :, 24:] == 0)
+
+
+@pytest.mark.parametrize("cls,gen", [
+    (lambda: M.TriangleMultiplicationOutgoing(128), lambda r: synth.trimul_weights(r, 128)),
+    (lambda: M.TriangleMultiplicationIncoming(128), lambda r: synth.trimul_weights(r, 128)),
+    (lambda: M.TriangleAttentionStartingNode(128, 4), lambda r: synth.triatt_weights(r, 128, 4)),
+    (lambda: M.TriangleAttentionEndingNode(128, 4), lambda r: synth.triatt_weights(r, 128, 4)),
+    (lambda: M.Transition(128, 4), lambda r: synth.transition_weights(r, 128, 4)),
+    (lambda: M.SelfAttentionPairBias(384, 16, None, "confidence"), lambda r: synth.apb_weights(r, 384, None)),
+])
+def test_modules_accept_reference_state_dicts(cls, gen):
+    """synth.*_weights are keyed like the reference modules' state_dict(); strict loading must succeed."""
+    mod = cls()
+    mod.load_state_dict(gen(synth._Rng(0)), strict=True)
+
+
+def test_block_state_dict_keys():
+    blk = M.PairformerBlock()
+    blk.load_state_dict(synth.pairformer_block_weights(0), strict=True)
+
+
+def test_inference_only_and_cuda_only():
+    mod = M.TriangleMultiplicationOutgoing(128)
+    x = torch.zeros(1, 8, 8, 128)
+    m = torch.ones(1, 8, 8, dtype=torch.bool)
+    with pytest.raises(RuntimeError, match="inference-only"):
+        mod(x, m)
+    with torch.no_grad(), pytest.raises(RuntimeError, match="CUDA"):
+        mod(x, m)
+
+
+def test_functional_rejects_cpu_tensors_and_bad_shapes():
+    pk = {"c": 128}
+    with pytest.raises(RuntimeError, match="CUDA"):
+        F.triangle_multiplication(torch.zeros(1, 8, 8, 128), torch.ones(1, 8, 8, dtype=torch.bool), pk, "outgoing")
+    with pytest.raises(ValueError):
+        F.triangle_multiplication(torch.zeros(1, 8, 8, 128), torch.ones(1, 8, 8, dtype=torch.bool), pk, "sideways")
+
+
+def test_unsupported_variants_fail_loudly():
+    with pytest.raises(NotImplementedError):
+        M.SelfAttentionPairBias(768, 16, 384, "diffusion_global")
+    with pytest.raises(ValueError):
+        M.SelfAttentionPairBias(768, 16, None, "somewhere")
+
+
+def test_missing_extension_fails_loudly(monkeypatch, tmp_path):
+    from kfold_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(_lib.KfbError, match="no fallback"):
+        _lib.lib()
+
+
+def test_pad_pair():
+    x = torch.randn(2, 10, 10, 4)
+    m = torch.ones(2, 10, 10, dtype=torch.bool)
+    xp, mp, n = F._pad_pair(x, m)
+    assert xp.shape == (2, 16, 16, 4) and mp.shape == (2, 16, 16) and n == 10
+    assert torch.equal(xp[:, :10, :10], x) and not mp[:, 10:].any() and not mp[:, :, 10:].any()
