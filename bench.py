@@ -1,0 +1,352 @@
+"""Benchmark of the hot path: one composite Pairformer block forward at N=768, bf16.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one forward of the AF3-shaped Pairformer block (triangle multiplication out/in,
+triangle attention start/end, pair transition, single-track pair-bias attention, single
+transition) on synthetic z ~ N(0,1) (1,768,768,128), s ~ N(0,1) (1,768,384), 10 % padding tail,
+random-init weights -- the unit BASELINE's headline "Pairformer-block fwd ms @N=768 bf16" names.
+
+With N > 1 ranks (launched by torch.distributed.run) every rank runs its own block on its own
+GPU -- independent complexes, the way the reference distributes work across GPUs
+(src/kfold/cli/multigpu.py:22-77) -- with no data-path collective; `value` is then the
+whole-job time per block (step time / blocks processed by all ranks).
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_TOKENS = 768
+C_Z, C_S = 128, 384
+PAD_FRAC = 0.1
+SEED = 3
+METRIC = "pairformer_block_fwd_ms_n768_bf16"
+
+
+# ------------------------------------------------------------------------------------------------
+# algorithmic work per launch tag at N=768, C=128 (2 flops per multiply-add; bf16 bytes, each tensor touched once)
+# ------------------------------------------------------------------------------------------------
+def algorithmic_work(n: int = N_TOKENS, c: int = C_Z, h: int = 4, cs: int = C_S, hs: int = 16) -> dict:
+    p = n * n
+    d = c // h
+    return {
+        # tensor-bound kernels: flops per launch
+        "trimul_contraction": ("tensor", 2.0 * n * n * n * c),
+        "trimul_in_proj": ("tensor", 2.0 * p * c * 4 * c),
+        "trimul_gate_proj": ("tensor", 2.0 * p * c * c),
+        "trimul_out_proj": ("tensor", 2.0 * p * c * c),
+        "triatt_proj": ("tensor", 2.0 * p * c * (4 * c + h)),
+        "triatt_attention": ("tensor", 4.0 * n * n * n * h * d),
+        "triatt_out_proj": ("tensor", 2.0 * p * c * c),
+        "transition_swiglu": ("tensor", 2.0 * p * c * 8 * c),
+        "transition_out": ("tensor", 2.0 * p * 4 * c * c),
+        "pair_bias_proj": ("tensor", 2.0 * p * c * hs),
+        "apb_proj": ("tensor", 2.0 * n * cs * 4 * cs),
+        "apb_attention": ("tensor", 4.0 * n * n * cs),
+        "apb_out_proj": ("tensor", 2.0 * n * cs * cs),
+        # HBM-bound kernels: bytes per launch (read + write once)
+        "layernorm_rows": ("hbm", 2.0 * p * c * 2),
+        "layernorm_cm": ("hbm", 2.0 * p * c * 2),
+    }
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+
+
+def load_traffic() -> dict:
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        try:
+            rows = [r.strip().split(", ") for r in open(self.path).read().splitlines() if r.strip()]
+            os.unlink(self.path)
+            sm = [float(r[0]) for r in rows if len(r) >= 6]
+            if sm:
+                out["sm_mhz"] = statistics.median(sm)
+                out["sm_max_mhz"] = float(rows[0][1])
+                names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+                out["reasons"] = [nm for i, nm in enumerate(names) if any(r[2 + i].strip() == "Active" for r in rows if len(r) >= 6)]
+                out["samples"] = len(sm)
+        except Exception:
+            pass
+        return out
+
+
+def make_inputs():
+    from kfold_b200 import synth
+    z, pm, m = synth.pair_inputs(SEED, N_TOKENS, C_Z, 1, pad_frac=PAD_FRAC)
+    s = synth.single_inputs(SEED, N_TOKENS, C_S, 1)
+    w = synth.pairformer_block_weights(SEED, C_Z, C_S)
+    return z, s, pm, m, w
+
+
+def config_dict(n_gpus: int) -> dict:
+    return {
+        "workload": "composite Pairformer block forward (BASELINE config 4's block): N_token=768, c_z=128, c_s=384, "
+                    "tri-mult out+in, tri-att start+end (4x32), transition x4, single pair-bias attention (16x24), transition x4",
+        "n_token": N_TOKENS, "c_z": C_Z, "c_s": C_S, "padding_tail": PAD_FRAC, "seed": SEED,
+        "blocks_per_step": n_gpus,
+        "parallelism": "independent blocks, one per GPU, no collective" if n_gpus > 1 else "single GPU",
+        "l2": "not flushed between steps: the pair tensor alone (151 MB bf16) and every intermediate exceed the 126 MB L2",
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's torch path on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_block_time(n: int, repeats: int, warmup: int):
+    """Times the CPU oracle's composite block at `n` tokens in fp32; returns (best_ms, cores)."""
+    from kfold_b200 import synth
+    from oracle import pairformer_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    z, pm, m = synth.pair_inputs(SEED, n, C_Z, 1, pad_frac=PAD_FRAC)
+    s = synth.single_inputs(SEED, n, C_S, 1)
+    w = synth.pairformer_block_weights(SEED, C_Z, C_S)
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + repeats):
+            t0 = time.perf_counter()
+            O.pairformer_block(z, s, pm, m, w, row_chunk=64)
+            dt = (time.perf_counter() - t0) * 1e3
+            if i >= warmup:
+                times.append(dt)
+    return times, cores
+
+
+def block_flops(n: int) -> float:
+    w = algorithmic_work(n)
+    per = {k: v for k, (kind, v) in w.items() if kind == "tensor"}
+    return (2 * (per["trimul_contraction"] + per["trimul_in_proj"] + per["trimul_gate_proj"] + per["trimul_out_proj"]) +
+            2 * (per["triatt_proj"] + per["triatt_attention"] + per["triatt_out_proj"]) +
+            per["transition_swiglu"] + per["transition_out"] + per["pair_bias_proj"] + per["apb_proj"] +
+            per["apb_attention"] + per["apb_out_proj"] + 2.0 * n * 384 * 12 * 384)
+
+
+CPU_SAMPLE_N = 256
+
+
+def run_reference_arm(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    times, cores = cpu_block_time(CPU_SAMPLE_N, args.steps, args.warmup)
+    scale = block_flops(N_TOKENS) / block_flops(CPU_SAMPLE_N)
+    ms_sample = sum(times) / len(times)
+    value = ms_sample * scale
+    sample = (f"CPU port of the reference torch path (fp32, {cores} threads): one block at N={CPU_SAMPLE_N} per step "
+              f"({ms_sample:.1f} ms), scaled to N={N_TOKENS} by the algorithmic FLOP ratio {scale:.2f}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config_dict(1),
+        "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, rank: int, local_rank: int, world: int) -> None:
+    import torch.distributed as dist
+    from kfold_b200 import _lib as L
+    from kfold_b200 import modules as M
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    z, s, pm, m, w = make_inputs()
+    blk = M.PairformerBlock(C_Z, C_S).to(dev)
+    blk.load_state_dict(w, strict=True)
+    z_host = z.bfloat16().pin_memory()
+    s_host = s.bfloat16().pin_memory()
+    z_dev, s_dev = z_host.to(dev), s_host.to(dev)
+    pm_dev, m_dev = pm.to(dev), m.to(dev)
+    z_out_host = torch.empty_like(z_host).pin_memory()
+    s_out_host = torch.empty_like(s_host).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def step_resident():
+        return blk(z_dev, s_dev, pm_dev, m_dev)
+
+    def step_e2e():
+        zd = z_host.to(dev, non_blocking=True)
+        sd = s_host.to(dev, non_blocking=True)
+        zo, so = blk(zd, sd, pm_dev, m_dev)
+        z_out_host.copy_(zo, non_blocking=True)
+        s_out_host.copy_(so, non_blocking=True)
+
+    with torch.no_grad():
+        # ---- device-resident timing (with per-launch events recorded by the library)
+        for _ in range(args.warmup):
+            step_resident()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        L.profile_enable(True)
+        launches0 = L.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step_resident()
+        e1.record(stream)
+        barrier()
+        launches = L.launch_count() - launches0
+        ms_step = e0.elapsed_time(e1) / args.steps
+        prof = L.profile_report()
+        L.profile_enable(False)
+        clocks = sampler.stop() if rank == 0 else {}
+        status = L.device_status()
+        # ---- end to end: host buffers in, host buffers out, copies inside the timed region
+        for _ in range(max(1, min(args.warmup, 2))):
+            step_e2e()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record(stream)
+        barrier()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+
+    if world > 1:
+        t = torch.tensor([ms_step, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks = load_peaks()
+        work = algorithmic_work()
+        traffic = load_traffic()
+        total_ms = sum(v[1] for v in prof.values()) or 1.0
+        kernels = {}
+        for tag, (cnt, ms) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
+            avg_ms = ms / cnt
+            ent = {"launches": cnt, "total_ms": round(ms, 4), "avg_ms": round(avg_ms, 5), "share": round(ms / total_ms, 4)}
+            if tag in work:
+                kind, amount = work[tag]
+                if kind == "tensor":
+                    ent.update(bound="tensor", achieved=round(amount / (avg_ms * 1e-3) / 1e12, 2), unit="TFLOP/s",
+                               frac=round(amount / (avg_ms * 1e-3) / 1e12 / peaks["tflops"], 4))
+                else:
+                    ent.update(bound="hbm", achieved=round(amount / (avg_ms * 1e-3) / 1e9, 1), unit="GB/s",
+                               frac=round(amount / (avg_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4))
+            kernels[tag] = ent
+        top = next(iter(kernels)) if kernels else None
+        roofline = None
+        if top and "bound" in kernels[top]:
+            k = kernels[top]
+            roofline = {"kernel": top, "bound": k["bound"], "achieved": k["achieved"],
+                        "peak": peaks["tflops"] if k["bound"] == "tensor" else peaks["hbm_gbs"], "unit": k["unit"],
+                        "frac": k["frac"], "traffic": traffic.get(top), "peak_source": peaks["source"],
+                        "share_of_step": k["share"]}
+        # CPU baseline: the oracle port on this box's host cores, one bounded sample
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            times, cores = cpu_block_time(CPU_SAMPLE_N, 2, 1)
+            scale = block_flops(N_TOKENS) / block_flops(CPU_SAMPLE_N)
+            best = min(times)
+            cpu = {"value": best * scale, "unit": "ms", "cores": cores, "kind": "port",
+                   "sample": f"oracle (CPU port of the reference torch path, fp32) on one block at N={CPU_SAMPLE_N}: best of 2 = "
+                             f"{best:.1f} ms, scaled to N={N_TOKENS} by the algorithmic FLOP ratio {scale:.2f}"}
+        h2d = z_host.numel() * 2 + s_host.numel() * 2
+        d2h = z_out_host.numel() * 2 + s_out_host.numel() * 2
+        line = {
+            "metric": METRIC, "value": ms_step / world, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world),
+            "block_tflops": round(block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12, 2),
+            "block_frac_of_tensor_peak": round(block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": ms_e2e / world, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches, "clocks": clocks, "device_status": status, "kernels": kernels,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if world == 1 and args.gpus > 1:
+        raise SystemExit("launch multi-GPU runs with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

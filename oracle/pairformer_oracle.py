@@ -103,12 +103,14 @@ def triangle_multiplication(x, mask, w: dict, direction: str, mode: str = "fp32"
 
 
 def triangle_attention(x, mask, w: dict, num_heads: int, starting: bool, mode: str = "fp32",
-                       inf: float = 1e9, eps: float = 1e-5):
+                       inf: float = 1e9, eps: float = 1e-5, row_chunk: int | None = None):
     """``TriangleAttention.forward`` + ``MultiHeadAttention.forward`` --
     model/primitives/triangle_attention.py:375-434 and :285-335.
 
     x (*,I,J,C); mask (*,I,J) or None.  Ending node = starting node on the
     transposed pair representation (:400-402), transposed back (:431-432).
+    ``row_chunk`` only bounds memory: the rows I are independent attention problems and
+    are processed ``row_chunk`` at a time with identical arithmetic.
     """
     m = _Mode(mode)
     x = m.r(x.float())
@@ -129,11 +131,21 @@ def triangle_attention(x, mask, w: dict, num_heads: int, starting: bool, mode: s
     q, k, v = (t.unflatten(-1, (H, D)).transpose(-2, -3) for t in (q, k, v))   # (*,I,H,J,D)
     q = m.r(q / math.sqrt(D))                                                    # :264-265
     mask_bias = -inf * (~mask.bool()).to(q.dtype)[..., :, None, None, :]        # (*,I,1,1,J)  :328
-    a = m.r(torch.matmul(q, k.transpose(-1, -2)))                               # (*,I,H,J,J)  :139
-    a = m.r(a + mask_bias)
-    a = m.r(a + tri_bias)
-    a = a.softmax(dim=-1)       # CUDA autocast runs softmax in fp32 and keeps it fp32
-    o = m.r(torch.matmul(m.r(a), v))                                            # :149
+
+    def core(q, k, v, mask_bias):
+        a = m.r(torch.matmul(q, k.transpose(-1, -2)))                           # (*,I,H,J,J)  :139
+        a = m.r(a + mask_bias)
+        a = m.r(a + tri_bias)
+        a = a.softmax(dim=-1)   # CUDA autocast runs softmax in fp32 and keeps it fp32
+        return m.r(torch.matmul(m.r(a), v))                                     # :149
+
+    n_rows = q.shape[-4]
+    if row_chunk is None or row_chunk >= n_rows:
+        o = core(q, k, v, mask_bias)
+    else:
+        o = torch.cat([core(q[..., i:i + row_chunk, :, :, :], k[..., i:i + row_chunk, :, :, :],
+                            v[..., i:i + row_chunk, :, :, :], mask_bias[..., i:i + row_chunk, :, :, :])
+                       for i in range(0, n_rows, row_chunk)], dim=-4)
     o = o.transpose(-2, -3)                                                      # (*,I,J,H,D)
     g = torch.sigmoid(m.linear(xn, w["mha.linear_g.weight"])).unflatten(-1, (H, D))
     o = m.r(o * g).flatten(-2)                                                   # :269-278
@@ -233,7 +245,7 @@ def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
 
 
 def pairformer_block(z, s, pair_mask, mask, w: dict, tri_heads: int = 4, single_heads: int = 16,
-                     mode: str = "fp32", final_pair_mask: bool = False):
+                     mode: str = "fp32", final_pair_mask: bool = False, row_chunk: int | None = None):
     """The composite AF3-shaped Pairformer block, assembled from reference modules only.
 
     Pair track in ``PairformerBlock.forward`` order (model/modules/apo_module.py:145-172:
@@ -248,8 +260,10 @@ def pairformer_block(z, s, pair_mask, mask, w: dict, tri_heads: int = 4, single_
     s = m.r(s.float())
     z = m.r(z + triangle_multiplication(z, pair_mask, sub(w, "tri_mul_out"), "outgoing", mode))
     z = m.r(z + triangle_multiplication(z, pair_mask, sub(w, "tri_mul_in"), "incoming", mode))
-    z = m.r(z + triangle_attention(z, pair_mask, sub(w, "tri_att_start"), tri_heads, True, mode))
-    z = m.r(z + triangle_attention(z, pair_mask, sub(w, "tri_att_end"), tri_heads, False, mode))
+    z = m.r(z + triangle_attention(z, pair_mask, sub(w, "tri_att_start"), tri_heads, True, mode,
+                                     row_chunk=row_chunk))
+    z = m.r(z + triangle_attention(z, pair_mask, sub(w, "tri_att_end"), tri_heads, False, mode,
+                                     row_chunk=row_chunk))
     z = m.r(z + transition(z, sub(w, "transition_z"), mode))
     if final_pair_mask:
         z = z * pair_mask[..., None].to(z.dtype)
