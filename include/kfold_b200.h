@@ -145,6 +145,28 @@ KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln
 
 
 /*
+ * Transition for callers that cannot provide scratch memory (no counterpart in the reference).
+ * Same arguments and result as kfb_transition_fwd minus the workspace: the two temporaries live in
+ * a fixed 8 MiB device array inside the library (kfb_transition_static_max_bytes()), which every
+ * GPU that loads the library holds until the process exits.  Meant for hosts where device
+ * allocation is off-limits while they run -- a server whose memory pool was sized and frozen at
+ * start-up, or a plugin callback that must not call cudaMalloc because it synchronises the device.
+ * The function itself allocates nothing on the device or through any library.
+ *   - Sizes whose temporaries exceed the array (rows * (c + hidden) * 2 bytes, each part rounded up
+ *     to 256) are refused with KFB_ERR_UNSUPPORTED and a message naming the limit; e.g. c=384,
+ *     hidden=1536 fits up to 2184 rows.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams without ordering) race on it.  Nothing needs clearing between calls -- the
+ *     temporaries are fully rewritten before use.
+ */
+KFB_API size_t kfb_transition_static_max_bytes(void);
+KFB_API int kfb_transition_fwd_static(const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu_packed,
+                                      const void* w_out, void* out, const void* resid, long long rows, int c, int hidden,
+                                      float eps, int dtype, void* stream);
+
+/*
  * LayerNorm over the last dimension: y = (x - mean) * rstd * weight + bias, statistics in fp32.
  * Replaces LayerNorm.forward (src/kfold/model/primitives/normalization.py:61-91).
  * x, y: `rows` rows of `c` channels; row r starts at x + r*x_row_stride (elements).

@@ -42,8 +42,11 @@ _SIGNATURES = {
                            c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_pair_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int,
                           c_int, c_float, c_int, c_void_p],
+    "kfb_transition_fwd_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
+                                  c_float, c_int, c_void_p],
 }
 _SIZE_FUNCS = {
+    "kfb_transition_static_max_bytes": [],
     "kfb_pair_bias_workspace_bytes": [c_int, c_int, c_int],
     "kfb_transition_workspace_bytes": [c_ll, c_int, c_int],
     "kfb_triatt_workspace_bytes": [c_int, c_int, c_int, c_int],

@@ -70,3 +70,66 @@ KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Transition without a caller-provided workspace.
+//
+// Some hosts of this library cannot hand over scratch memory: a serving process whose device pool
+// was sized and frozen at start-up, or a plugin callback that is not allowed to call cudaMalloc
+// (the call synchronises the whole device and would stall every other stream of the process).
+// For them the two temporaries of the transition (the normalised input and the SwiGLU hidden
+// activations) live in the fixed device array below instead.  Every GPU that loads the library
+// carries these 8 MiB until the process exits.
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+static constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_transition_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of g_transition_scratch per device ordinal.  In host code the array's name is only
+// a handle for the runtime, not an address a kernel could use; cudaGetSymbolAddress translates it
+// for the device that is current at the time of the call.
+std::mutex g_scratch_mu;
+void* g_scratch_ptr[64] = {};
+
+int static_scratch(void** out) {
+  int dev = 0;
+  KFB_CUDA(cudaGetDevice(&dev));
+  KFB_CHECK_ARG(dev >= 0 && dev < 64, "transition_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    KFB_CUDA(cudaGetSymbolAddress(&p, g_transition_scratch));
+    KFB_CHECK_ARG(p != nullptr && (reinterpret_cast<uintptr_t>(p) & 255) == 0, "transition_static: bad scratch address %p", p);
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return KFB_OK;
+}
+}  // namespace
+
+extern "C" {
+
+KFB_API size_t kfb_transition_static_max_bytes(void) { return kStaticScratchBytes; }
+
+KFB_API int kfb_transition_fwd_static(const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu_packed,
+                                      const void* w_out, void* out, const void* resid, long long rows, int c, int hidden,
+                                      float eps, int dtype, void* stream) {
+  KFB_CHECK_ARG(rows >= 1 && c >= 8 && hidden >= 128, "transition_static: rows %lld c %d hidden %d", rows, c, hidden);
+  const size_t need = kfb_transition_workspace_bytes(rows, c, hidden);
+  if (need > kStaticScratchBytes) {
+    set_error("transition_static: %lld rows x (c=%d + hidden=%d) need %zu bytes of scratch, the built-in array holds %zu; "
+              "use kfb_transition_fwd with a caller-provided workspace for this size",
+              rows, c, hidden, need, kStaticScratchBytes);
+    return KFB_ERR_UNSUPPORTED;
+  }
+  void* scratch = nullptr;
+  KFB_TRY(static_scratch(&scratch));
+  // Both temporaries are written in full (for the rows in use) before they are read, so nothing in
+  // the array has to start at zero and stale contents of an earlier call are never observed.
+  return kfb_transition_fwd(x, ln_w, ln_b, w_swiglu_packed, w_out, out, resid, scratch, kStaticScratchBytes, rows, c,
+                            hidden, eps, dtype, stream);
+}
+
+}  // extern "C"
