@@ -41,7 +41,8 @@ METRIC = "pairformer_block_fwd_ms_n768_bf16"
 # ------------------------------------------------------------------------------------------------
 # algorithmic work per launch tag at N=768, C=128 (2 flops per multiply-add; bf16 bytes, each tensor touched once)
 # ------------------------------------------------------------------------------------------------
-def algorithmic_work(n: int = N_TOKENS, c: int = C_Z, h: int = 4, cs: int = C_S, hs: int = 16) -> dict:
+def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C_S, hs: int = 16) -> dict:
+    n = N_TOKENS if n is None else n
     p = n * n
     d = c // h
     return {
@@ -135,7 +136,7 @@ def make_inputs():
 
 def config_dict(n_gpus: int) -> dict:
     return {
-        "workload": "composite Pairformer block forward (BASELINE config 4's block): N_token=768, c_z=128, c_s=384, "
+        "workload": f"composite Pairformer block forward (BASELINE config 4's block): N_token={N_TOKENS}, c_z=128, c_s=384, "
                     "tri-mult out+in, tri-att start+end (4x32), transition x4, single pair-bias attention (16x24), transition x4",
         "n_token": N_TOKENS, "c_z": C_Z, "c_s": C_S, "padding_tail": PAD_FRAC, "seed": SEED,
         "blocks_per_step": n_gpus,
@@ -335,8 +336,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=N_TOKENS,
+                    help="profiling aid: run the block at another N (the reported line is then NOT the benchmark workload)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.tokens == N_TOKENS else args.warmup
+    if args.tokens != N_TOKENS:
+        globals()["N_TOKENS"] = args.tokens
+        globals()["METRIC"] = f"pairformer_block_fwd_ms_n{args.tokens}_bf16_PROFILING_SIZE"
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

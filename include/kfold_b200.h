@@ -108,11 +108,12 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
  * Replaces `linear_pair_bias(layernorm_z(z)).movedim(-1, -3)`
  * (src/kfold/model/modules/confidence_head.py:162-163) and DiffusionStack.get_pair_bias
  * (src/kfold/model/layers/folding/diffusion.py:411-416).  w : bf16 [heads, c].
+ * With transposed != 0 the result is written as bias_out[b, h, j, i].
  */
 KFB_API size_t kfb_pair_bias_workspace_bytes(int batch, int n, int c);
 KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
-                              void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, float eps,
-                              int dtype, void* stream);
+                              void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, int transposed,
+                              float eps, int dtype, void* stream);
 
 /*
  * Gated self-attention with pair bias on already-normalised input.

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "kfb_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t,
                            c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_pair_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int,
-                          c_int, c_float, c_int, c_void_p],
+                          c_int, c_int, c_float, c_int, c_void_p],
     "kfb_transition_fwd_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
                                   c_float, c_int, c_void_p],
 }

@@ -9,59 +9,78 @@
 
 namespace kfb {
 
-static constexpr int kAttThreads = 192;
 static constexpr int kBQ = 128;   // queries per CTA
 static constexpr int kBKV = 128;  // keys per block
 static constexpr float kLog2e = 1.4426950408889634f;
-static constexpr float kMaskInf = 1e9f;
+static constexpr float kMasked = -1e9f;         // additive value of a masked key (finite, as in the reference)
+static constexpr float kAbsent = -1e30f;        // keys beyond lk
+static constexpr float kRaiseThreshold = 5.5f;  // raise the stabiliser when the running max moved by more than e^5.5
+static constexpr float kRedoThreshold = 60.f;   // redo a block whose exponents would approach fp32 overflow
 
-template <int DPAD>
+template <int DPAD, int R>
 struct AttCfg {
+  static constexpr int kThreads = 64 + 128 * R;
   static constexpr int kSpan = DPAD * 2;                 // bytes per q/k row = swizzle span
-  static constexpr int kQBytes = kBQ * kSpan;
+  static constexpr int kQBytes = kBQ * kSpan;            // per row group
   static constexpr int kKBytes = kBKV * kSpan;
   static constexpr int kVBytes = 2 * DPAD * 128;         // two boxes of [DPAD rows x 64 keys]
   static constexpr int kKvStages = 2;
-  static constexpr int kBiasBytes = 2 * kBQ * 128;       // two boxes of [128 rows x 64 keys] bf16
-  static constexpr int kPBytes = 2 * kBQ * 128;
-  static constexpr int kTmemCols = 256;                  // S: 128 columns, O: DPAD columns at offset 128
-  static constexpr int kSmemBytes = kQBytes + kKvStages * (kKBytes + kVBytes) + kBiasBytes + kPBytes + 1024 /*align*/ +
-                                    2 * kBKV * 4 /*mask*/ + 256 /*barriers*/;
+  static constexpr int kTileBytes = 2 * 128 * 128;       // a 128 x 128 bf16 tile as two 64-wide swizzled halves
+  static constexpr int kSmallBytes = 128 * 32;           // a 128 x 16 bf16 K-major operand without swizzle
+  static constexpr int kTmemCols = (R == 1) ? 256 : 512; // S_g at g*128, O_g at R*128 + g*DPAD
+  static constexpr int kSmemBytes = R * kQBytes + R * kKvStages * (kKBytes + kVBytes) + kTileBytes /*bias*/ +
+                                    R * kTileBytes /*P*/ + kTileBytes /*identity*/ + kSmallBytes /*e0*/ +
+                                    R * kSmallBytes /*mask rows*/ + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int DPAD>
-__global__ void __launch_bounds__(kAttThreads, 1)
+// K-major operand without swizzle: 8 x 8 core matrices (8 rows of 16 bytes); the two K halves of a K=16
+// slice are 128 bytes apart (leading byte offset), groups of 8 rows 256 bytes apart (stride byte offset).
+__device__ __forceinline__ uint64_t make_noswizzle_desc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4) | (static_cast<uint64_t>(128 >> 4) << 16) |
+         (static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 46);
+}
+// MN-major operand tile made of 128-byte swizzled rows: row = one K index holding 64 contiguous MN elements
+// (what a TMA box of 64 x rows with 128B swizzle writes).  Groups of 8 K-rows are 1024 bytes apart (stride
+// byte offset); the next 64 MN elements live in the next box, `mn_group_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t make_mnmajor_desc(uint32_t smem_addr, uint32_t mn_group_bytes) {
+  return static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4) | (static_cast<uint64_t>(mn_group_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint32_t small_operand_row_offset(int r) { return (r >> 3) * 256 + (r & 7) * 16; }
+
+template <int DPAD, int R>
+__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads, 1)
 attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
                       const AttnParams p) {
-  using Cfg = AttCfg<DPAD>;
+  using Cfg = AttCfg<DPAD, R>;
   constexpr int kStages = Cfg::kKvStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* s_q = smem;
-  uint8_t* s_k = s_q + Cfg::kQBytes;
-  uint8_t* s_v = s_k + kStages * Cfg::kKBytes;
-  uint8_t* s_bias = s_v + kStages * Cfg::kVBytes;
-  uint8_t* s_p = s_bias + Cfg::kBiasBytes;
-  float* s_mask = reinterpret_cast<float*>(s_p + Cfg::kPBytes);  // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_mask + 2 * kBKV);
-  uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;            // [kStages]
-  uint64_t* kv_empty = kv_full + kStages;  // [kStages]
-  uint64_t* bias_full = kv_empty + kStages;
+  uint8_t* s_q = smem;                                            // [R]
+  uint8_t* s_k = s_q + R * Cfg::kQBytes;                          // [R][stages]
+  uint8_t* s_v = s_k + R * kStages * Cfg::kKBytes;                // [R][stages]
+  uint8_t* s_bias = s_v + R * kStages * Cfg::kVBytes;
+  uint8_t* s_p = s_bias + Cfg::kTileBytes;                        // [R]
+  uint8_t* s_ident = s_p + R * Cfg::kTileBytes;
+  uint8_t* s_e0 = s_ident + Cfg::kTileBytes;
+  uint8_t* s_maskrow = s_e0 + Cfg::kSmallBytes;                   // [R]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_maskrow + R * Cfg::kSmallBytes);
+  uint64_t* q_full = bars;                           // [R]
+  uint64_t* kv_full = q_full + R;                    // [R][stages]
+  uint64_t* kv_empty = kv_full + R * kStages;        // [R][stages]
+  uint64_t* bias_full = kv_empty + R * kStages;
   uint64_t* bias_empty = bias_full + 1;
-  uint64_t* s_full = bias_empty + 1;
-  uint64_t* s_empty = s_full + 1;
-  uint64_t* p_full = s_empty + 1;
-  uint64_t* o_full = p_full + 1;
-  uint64_t* mask_bar = o_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mask_bar + 1);
+  uint64_t* s_full = bias_empty + 1;                 // [R]
+  uint64_t* ready = s_full + R;                      // [R]  (128 arrivals)
+  uint64_t* o_full = ready + R;                      // [R]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + R);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int qb = blockIdx.x;
   const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  const int b0 = blockIdx.z * R;  // first batch entry of this CTA
   const int nkv = (p.lk + kBKV - 1) / kBKV;
 
   if (threadIdx.x == 0) {
@@ -69,208 +88,265 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     ptx::prefetch_tmap(&tm_k);
     ptx::prefetch_tmap(&tm_v);
     ptx::prefetch_tmap(&tm_b);
-    ptx::mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(&kv_full[s], 1);
-      ptx::mbar_init(&kv_empty[s], 1);
+    for (int g = 0; g < R; ++g) {
+      ptx::mbar_init(&q_full[g], 1);
+      ptx::mbar_init(&s_full[g], 1);
+      ptx::mbar_init(&ready[g], 128);
+      ptx::mbar_init(&o_full[g], 1);
+      for (int s = 0; s < kStages; ++s) {
+        ptx::mbar_init(&kv_full[g * kStages + s], 1);
+        ptx::mbar_init(&kv_empty[g * kStages + s], 1);
+      }
     }
     ptx::mbar_init(bias_full, 1);
-    ptx::mbar_init(bias_empty, 128);
-    ptx::mbar_init(s_full, 1);
-    ptx::mbar_init(s_empty, 128);
-    ptx::mbar_init(p_full, 128);
-    ptx::mbar_init(o_full, 1);
-    ptx::mbar_init(mask_bar, 128);
+    ptx::mbar_init(bias_empty, 1);
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
     ptx::tmem_relinquish();
   }
+  // constant operands: identity (128 x 128, swizzled K-major halves) and e0 (128 x 16, first column ones)
+  if (warp >= 2 && warp < 6) {
+    const int r = (warp - 2) * 32 + lane;
+    const uint32_t one_at = 0x3F80u << (16 * (r & 1));  // bf16 1.0 in the low or high half of a 32-bit word
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+      for (int ci = 0; ci < 8; ++ci) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (half == (r >> 6) && ci == ((r & 63) >> 3)) {
+          const int w = (r & 7) >> 1;
+          if (w == 0) v.x = one_at; else if (w == 1) v.y = one_at; else if (w == 2) v.z = one_at; else v.w = one_at;
+        }
+        *reinterpret_cast<uint4*>(s_ident + half * 16384 + r * 128 + ((ci ^ (r & 7)) << 4)) = v;
+      }
+    }
+    const uint32_t off = small_operand_row_offset(r);
+    *reinterpret_cast<uint4*>(s_e0 + off) = make_uint4(0x3F80u, 0, 0, 0);
+    *reinterpret_cast<uint4*>(s_e0 + off + 128) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int g = 0; g < R; ++g)
+      *reinterpret_cast<uint4*>(s_maskrow + g * Cfg::kSmallBytes + off + 128) = make_uint4(0, 0, 0, 0);
+    ptx::fence_proxy_async_smem();
+  }
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + 128;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      ptx::mbar_expect_tx(q_full, Cfg::kQBytes);
-      ptx::tma_load_3d(s_q, &tm_q, q_full, p.q_col0 + h * DPAD, qb * kBQ, b);
-      const int bias_z = (b / p.bias_div) * p.heads + h;
-      for (int j = 0; j < nkv; ++j) {
-        const int st = j % kStages;
-        if (!ptx::mbar_wait(&kv_empty[st], ((j / kStages) & 1) ^ 1, 201)) break;
-        ptx::mbar_expect_tx(&kv_full[st], Cfg::kKBytes + Cfg::kVBytes);
-        ptx::tma_load_3d(s_k + st * Cfg::kKBytes, &tm_k, &kv_full[st], p.k_col0 + h * DPAD, j * kBKV, b);
-        ptx::tma_load_3d(s_v + st * Cfg::kVBytes, &tm_v, &kv_full[st], j * kBKV, h * DPAD, b);
-        ptx::tma_load_3d(s_v + st * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[st], j * kBKV + 64, h * DPAD, b);
+      for (int g = 0; g < R; ++g) {
+        ptx::mbar_expect_tx(&q_full[g], Cfg::kQBytes);
+        ptx::tma_load_3d(s_q + g * Cfg::kQBytes, &tm_q, &q_full[g], p.q_col0 + h * DPAD, qb * kBQ, b0 + g);
+      }
+      const int bias_z = (b0 / p.bias_div) * p.heads + h;
+      bool ok = true;
+      for (int j = 0; ok && j < nkv; ++j) {
         if (!ptx::mbar_wait(bias_empty, (j & 1) ^ 1, 202)) break;
-        ptx::mbar_expect_tx(bias_full, Cfg::kBiasBytes);
+        ptx::mbar_expect_tx(bias_full, Cfg::kTileBytes);
         ptx::tma_load_3d(s_bias, &tm_b, bias_full, j * kBKV, qb * kBQ, bias_z);
-        ptx::tma_load_3d(s_bias + kBQ * 128, &tm_b, bias_full, j * kBKV + 64, qb * kBQ, bias_z);
+        ptx::tma_load_3d(s_bias + 16384, &tm_b, bias_full, j * kBKV + 64, qb * kBQ, bias_z);
+        const int st = j % kStages;
+        for (int g = 0; g < R; ++g) {
+          const int slot = g * kStages + st;
+          if (!ptx::mbar_wait(&kv_empty[slot], ((j / kStages) & 1) ^ 1, 201)) { ok = false; break; }
+          ptx::mbar_expect_tx(&kv_full[slot], Cfg::kKBytes + Cfg::kVBytes);
+          ptx::tma_load_3d(s_k + slot * Cfg::kKBytes, &tm_k, &kv_full[slot], p.k_col0 + h * DPAD, j * kBKV, b0 + g);
+          ptx::tma_load_3d(s_v + slot * Cfg::kVBytes, &tm_v, &kv_full[slot], j * kBKV, h * DPAD, b0 + g);
+          ptx::tma_load_3d(s_v + slot * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[slot], j * kBKV + 64, h * DPAD, b0 + g);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = ptx::make_idesc(kBQ, kBKV, 1);
+      constexpr uint32_t idesc_s_bmn = idesc_s | (1u << 16);  // B operand MN-major (the bias tile as it lies in memory)
       constexpr uint32_t idesc_o = ptx::make_idesc(kBQ, DPAD, 1);
-      bool ok = ptx::mbar_wait(q_full, 0, 203);
-      const uint32_t q_addr = ptx::smem_u32(s_q);
-      const uint32_t p_addr = ptx::smem_u32(s_p);
-      for (int j = 0; ok && j < nkv; ++j) {
-        const int st = j % kStages;
-        if (!ptx::mbar_wait(&kv_full[st], (j / kStages) & 1, 204)) break;
-        if (!ptx::mbar_wait(s_empty, (j & 1) ^ 1, 205)) break;
+      const uint32_t ident_addr = ptx::smem_u32(s_ident);
+      const uint32_t bias_addr = ptx::smem_u32(s_bias);
+      const uint32_t e0_addr = ptx::smem_u32(s_e0);
+      bool ok = true;
+
+      // S_g(j) = Q_g K_g(j)^T + I biasT(j)^T + e0 maskrow_g(j)^T
+      auto issue_s = [&](int g, int j) -> bool {
+        const int slot = g * kStages + (j % kStages);
+        if (g == 0 && !ptx::mbar_wait(bias_full, j & 1, 203)) return false;
+        if (!ptx::mbar_wait(&kv_full[slot], (j / kStages) & 1, 204)) return false;
         ptx::tc_fence_after_sync();
-        const uint32_t k_addr = ptx::smem_u32(s_k + st * Cfg::kKBytes);
+        const uint32_t tmem_s = tmem_base + g * 128;
+        const uint32_t q_addr = ptx::smem_u32(s_q + g * Cfg::kQBytes);
+        const uint32_t k_addr = ptx::smem_u32(s_k + slot * Cfg::kKBytes);
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk)
           ptx::mma_f16_ss(tmem_s, ptx::make_kmajor_desc<Cfg::kSpan>(q_addr + kk * 32),
                           ptx::make_kmajor_desc<Cfg::kSpan>(k_addr + kk * 32), idesc_s, kk != 0 ? 1u : 0u);
-        ptx::tc_commit(s_full);
-        if (!ptx::mbar_wait(p_full, j & 1, 206)) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t v_addr = ptx::smem_u32(s_v + st * Cfg::kVBytes);
 #pragma unroll
-        for (int kk = 0; kk < kBKV / 16; ++kk) {
-          const uint32_t pa = p_addr + (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
-          const uint32_t va = v_addr + (kk >> 2) * (DPAD * 128) + (kk & 3) * 32;
-          ptx::mma_f16_ss(tmem_o, ptx::make_kmajor_desc<128>(pa), ptx::make_kmajor_desc<128>(va), idesc_o,
-                          kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) {  // K runs over the 128 queries of the tile, 16 per step
+          const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          ptx::mma_f16_ss(tmem_s, ptx::make_kmajor_desc<128>(ident_addr + a_off),
+                          make_mnmajor_desc(bias_addr + kk * 2048, 16384), idesc_s_bmn, 1u);
         }
-        ptx::tc_commit(o_full);
-        ptx::tc_commit(&kv_empty[st]);
+        ptx::mma_f16_ss(tmem_s, make_noswizzle_desc(e0_addr),
+                        make_noswizzle_desc(ptx::smem_u32(s_maskrow + g * Cfg::kSmallBytes)), idesc_s, 1u);
+        ptx::tc_commit(&s_full[g]);
+        if (g == R - 1) ptx::tc_commit(bias_empty);
+        return true;
+      };
+
+      for (int g = 0; ok && g < R; ++g) {
+        ok = ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&ready[g], 0, 206) && issue_s(g, 0);
+      }
+      for (int j = 0; ok && j < nkv; ++j) {
+        for (int g = 0; ok && g < R; ++g) {
+          // P_g(j) written, S_g(j) consumed, O_g(j-1) folded, mask row of block j+1 written
+          if (!ptx::mbar_wait(&ready[g], (j + 1) & 1, 207)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const int slot = g * kStages + (j % kStages);
+          const uint32_t p_addr = ptx::smem_u32(s_p + g * Cfg::kTileBytes);
+          const uint32_t v_addr = ptx::smem_u32(s_v + slot * Cfg::kVBytes);
+          const uint32_t tmem_o = tmem_base + R * 128 + g * DPAD;
+#pragma unroll
+          for (int kk = 0; kk < kBKV / 16; ++kk) {
+            const uint32_t pa = p_addr + (kk >> 2) * 16384 + (kk & 3) * 32;
+            const uint32_t va = v_addr + (kk >> 2) * (DPAD * 128) + (kk & 3) * 32;
+            ptx::mma_f16_ss(tmem_o, ptx::make_kmajor_desc<128>(pa), ptx::make_kmajor_desc<128>(va), idesc_o,
+                            kk != 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(&o_full[g]);
+          ptx::tc_commit(&kv_empty[slot]);
+          if (j + 1 < nkv) ok = issue_s(g, j + 1);
+        }
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax + accumulation (warps 2..5)
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;   // row inside the query block == TMEM lane
-    const int sm_tid = threadIdx.x - 64;  // 0..127
+    // ---------------------------------------------------------------- softmax + accumulation
+    const int g = (warp - 2) >> 2;          // row group
+    const int quad = warp & 3;              // TMEM lane quadrant of this warp
+    const int r = quad * 32 + lane;         // row inside the query block == TMEM lane
     const int q_idx = qb * kBQ + r;
+    const int b = b0 + g;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + g * 128 + lane_base;
+    const uint32_t tmem_o = tmem_base + R * 128 + g * DPAD + lane_base;
     const int b_hi = b / p.mask_lo_extent, b_lo = b - b_hi * p.mask_lo_extent;
     const unsigned char* mrow = p.mask + static_cast<long long>(b_hi) * p.m_hi + static_cast<long long>(b_lo) * p.m_lo;
+    uint8_t* my_maskrow = s_maskrow + g * Cfg::kSmallBytes + small_operand_row_offset(r);
+    uint8_t* p_tile = s_p + g * Cfg::kTileBytes;
+
+    auto write_mask_row = [&](int j) {  // this thread provides key j*128 + r of its group's mask operand
+      const int key = j * kBKV + r;
+      float mv = kAbsent;
+      if (key < p.lk) mv = mrow[static_cast<long long>(key) * p.m_k] ? 0.f : kMasked;
+      const uint32_t bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(mv)));
+      *reinterpret_cast<uint4*>(my_maskrow) = make_uint4(bits, 0, 0, 0);
+    };
+
+    write_mask_row(0);
+    ptx::fence_proxy_async_smem();
+    ptx::mbar_arrive(&ready[g]);
 
     float acc[DPAD];
 #pragma unroll
     for (int i = 0; i < DPAD; ++i) acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float s_cur = 0.f, l_run = 0.f, s_next = 0.f;
     bool ok = true;
 
     for (int j = 0; j < nkv; ++j) {
-      // additive key mask of this block, shared by all rows of the CTA
-      {
-        const int key = j * kBKV + sm_tid;
-        float mv = -INFINITY;  // keys beyond lk do not exist
-        if (key < p.lk) mv = mrow[static_cast<long long>(key) * p.m_k] ? 0.f : -kMaskInf;
-        s_mask[(j & 1) * kBKV + sm_tid] = mv;
-      }
-      // a bounded mbarrier instead of bar.sync: a thread that gave up elsewhere can never strand the others here
-      ptx::mbar_arrive(mask_bar);
-      if (!ptx::mbar_wait(mask_bar, j & 1, 211)) { ok = false; break; }
-      const float* mk = s_mask + (j & 1) * kBKV;
-      if (!ptx::mbar_wait(s_full, j & 1, 207)) { ok = false; break; }
-      if (!ptx::mbar_wait(bias_full, j & 1, 208)) { ok = false; break; }
+      if (!ptx::mbar_wait(&s_full[g], j & 1, 208)) { ok = false; break; }
       ptx::tc_fence_after_sync();
+      if (j + 1 < nkv) write_mask_row(j + 1);  // S(j) is complete, so the MMA no longer reads the mask operand
 
-      // ---- pass 1: row maximum of (S + mask + bias) in log2 units
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, raw);
-        const uint8_t* brow = s_bias + (c >> 1) * (kBQ * 128) + r * 128;
-        float bv[32];
+      if (j == 0) {  // stabiliser of the first block: its true row maximum
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        uint32_t raw[2][16];
+        ptx::tmem_ld_32x32b_x16(tmem_s, raw[0]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int ci = ((c & 1) * 4 + i) ^ (r & 7);
-          const uint4 u = *reinterpret_cast<const uint4*>(brow + (ci << 4));
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        for (int c = 0; c < 8; ++c) {
+          ptx::tmem_ld_wait();
+          if (c < 7) ptx::tmem_ld_32x32b_x16(tmem_s + (c + 1) * 16, raw[(c + 1) & 1]);
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[t]));
-            bv[i * 8 + t * 2] = f.x;
-            bv[i * 8 + t * 2 + 1] = f.y;
-          }
+          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw[c & 1][i]));
         }
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float t = ((__uint_as_float(raw[i]) + mk[c * 32 + i]) + bv[i]) * kLog2e;
-          mx = fmaxf(mx, t);
-        }
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = exp2f(m_run - m_new);  // m_run = -inf on the first block -> 0
-      // ---- fold the previous block's P V product (still in the previous scale) and rescale
-      if (j > 0) {
-        if (!ptx::mbar_wait(o_full, (j - 1) & 1, 209)) { ok = false; break; }
+        s_next = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        s_cur = s_next;
+      } else {
+        // fold the previous block's P V product (same scale as acc)
+        if (!ptx::mbar_wait(&o_full[g], (j - 1) & 1, 209)) { ok = false; break; }
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < DPAD / 32; ++c) {
           uint32_t raw[32];
-          ptx::tmem_ld_32x32b_x32(tmem_o + lane_base + c * 32, raw);
+          ptx::tmem_ld_32x32b_x32(tmem_o + c * 32, raw);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(raw[i])) * alpha;
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(raw[i]);
         }
       }
-      l_run *= alpha;
-      // ---- pass 2: P = exp2(t - m_new), written as bf16 into the swizzled A-operand tile
+
+      // single pass: P = exp(S - s_use) = exp2(S * log2e - s_use * log2e), four independent sum / max chains
+      float s_use = s_next, l_blk = 0.f, mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32b_x32(tmem_s + lane_base + c * 32, raw);
-        const uint8_t* brow = s_bias + (c >> 1) * (kBQ * 128) + r * 128;
-        uint8_t* prow = s_p + (c >> 1) * (kBQ * 128) + r * 128;
-        float bv[32];
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float neg_s = -s_use * kLog2e;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        // 16 columns at a time, the next TMEM load in flight while the current one is processed
+        auto process = [&](const uint32_t (&raw)[16], int c) {
+          float pv[16];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int ci = ((c & 1) * 4 + i) ^ (r & 7);
-          const uint4 u = *reinterpret_cast<const uint4*>(brow + (ci << 4));
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[t]));
-            bv[i * 8 + t * 2] = f.x;
-            bv[i * 8 + t * 2 + 1] = f.y;
+          for (int i = 0; i < 16; ++i) {
+            const float t = __uint_as_float(raw[i]);
+            m4[i & 3] = fmaxf(m4[i & 3], t);
+            pv[i] = exp2f(fmaf(t, kLog2e, neg_s));
+            l4[i & 3] += pv[i];
           }
-        }
-        ptx::tmem_ld_wait();
-        float pv[32];
+          uint8_t* prow = p_tile + (c >> 2) * 16384 + r * 128;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float t = ((__uint_as_float(raw[i]) + mk[c * 32 + i]) + bv[i]) * kLog2e;
-          pv[i] = exp2f(t - m_new);
-          l_run += pv[i];
+          for (int i = 0; i < 2; ++i) {
+            const int ci = ((c & 3) * 2 + i) ^ (r & 7);
+            *reinterpret_cast<uint4*>(prow + (ci << 4)) =
+                make_uint4(pack_bf16x2(pv[i * 8], pv[i * 8 + 1]), pack_bf16x2(pv[i * 8 + 2], pv[i * 8 + 3]),
+                           pack_bf16x2(pv[i * 8 + 4], pv[i * 8 + 5]), pack_bf16x2(pv[i * 8 + 6], pv[i * 8 + 7]));
+          }
+        };
+        uint32_t raw0[16], raw1[16];
+        ptx::tmem_ld_32x32b_x16(tmem_s, raw0);
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          ptx::tmem_ld_wait();
+          ptx::tmem_ld_32x32b_x16(tmem_s + cc * 32 + 16, raw1);
+          process(raw0, cc * 2);
+          ptx::tmem_ld_wait();
+          if (cc < 3) ptx::tmem_ld_32x32b_x16(tmem_s + cc * 32 + 32, raw0);
+          process(raw1, cc * 2 + 1);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int ci = ((c & 1) * 4 + i) ^ (r & 7);
-          *reinterpret_cast<uint4*>(prow + (ci << 4)) =
-              make_uint4(pack_bf16x2(pv[i * 8], pv[i * 8 + 1]), pack_bf16x2(pv[i * 8 + 2], pv[i * 8 + 3]),
-                         pack_bf16x2(pv[i * 8 + 4], pv[i * 8 + 5]), pack_bf16x2(pv[i * 8 + 6], pv[i * 8 + 7]));
-        }
+        l_blk = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        if (mx - s_use <= kRedoThreshold) break;
+        s_use = mx;  // exponents too large for comfort: redo this block against its own maximum
       }
-      m_run = m_new;
+      const float alpha = exp2f((s_cur - s_use) * kLog2e);
+#pragma unroll
+      for (int i = 0; i < DPAD; ++i) acc[i] *= alpha;
+      l_run = l_run * alpha + l_blk;
+      s_cur = s_use;
+      s_next = (mx > s_cur + kRaiseThreshold) ? mx : s_cur;
+
       ptx::tc_fence_before_sync();
       ptx::fence_proxy_async_smem();
-      ptx::mbar_arrive(p_full);
-      ptx::mbar_arrive(s_empty);
-      ptx::mbar_arrive(bias_empty);
+      ptx::mbar_arrive(&ready[g]);
     }
-    if (ok && ptx::mbar_wait(o_full, (nkv - 1) & 1, 210)) {
+    if (ok && ptx::mbar_wait(&o_full[g], (nkv - 1) & 1, 210)) {
       ptx::tc_fence_after_sync();
       const float inv_l = 1.0f / l_run;
 #pragma unroll
       for (int c = 0; c < DPAD / 32; ++c) {
         uint32_t raw[32];
-        ptx::tmem_ld_32x32b_x32(tmem_o + lane_base + c * 32, raw);
+        ptx::tmem_ld_32x32b_x32(tmem_o + c * 32, raw);
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(raw[i])) * inv_l;
@@ -278,10 +354,10 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (q_idx < p.lq) {
         const long long row = static_cast<long long>(b) * p.lq + q_idx;
         if (p.g != nullptr) {
-          const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD;
+          const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD;
 #pragma unroll
           for (int i = 0; i < DPAD; i += 8) {
-            const uint4 u = *reinterpret_cast<const uint4*>(g + i);
+            const uint4 u = *reinterpret_cast<const uint4*>(gp + i);
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
@@ -311,15 +387,16 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
 }
 
-template <int DPAD>
-static int launch_dpad(cudaStream_t stream, const AttnParams& p) {
-  using Cfg = AttCfg<DPAD>;
+template <int DPAD, int R>
+static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
+  using Cfg = AttCfg<DPAD, R>;
   static std::once_flag once[64];
   int dev = 0;
   KFB_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(attention_bias_kernel<DPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    attr_err = cudaFuncSetAttribute(attention_bias_kernel<DPAD, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes);
   });
   KFB_CUDA(attr_err);
   CUtensorMap tq, tk, tv, tb;
@@ -348,10 +425,10 @@ static int launch_dpad(cudaStream_t stream, const AttnParams& p) {
     const uint32_t box[3] = {64, kBQ, 1};
     KFB_TRY(make_tmap(&tb, p.bias, 2, 3, dims, str, box, 128));
   }
-  dim3 grid(cdiv(p.lq, kBQ), p.heads, p.batch);
+  dim3 grid(cdiv(p.lq, kBQ), p.heads, p.batch / R);
   {
     LaunchScope scope(stream, p.tag ? p.tag : "attention");
-    attention_bias_kernel<DPAD><<<grid, kAttThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tb, p);
+    attention_bias_kernel<DPAD, R><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tb, p);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
@@ -359,14 +436,17 @@ static int launch_dpad(cudaStream_t stream, const AttnParams& p) {
 
 int launch_attention(cudaStream_t stream, const AttnParams& p) {
   KFB_CHECK_ARG(p.batch > 0 && p.heads > 0 && p.lq > 0 && p.lk > 0, "attention: empty problem");
-  KFB_CHECK_ARG(p.batch <= 65535 * 32, "attention: batch %d too large", p.batch);
   KFB_CHECK_ARG(p.d % 8 == 0 && p.d <= p.dpad, "attention: head dim %d must be a multiple of 8 and <= %d", p.d, p.dpad);
   KFB_CHECK_ARG(p.ldq % 8 == 0 && p.ldk % 8 == 0 && p.ldv % 8 == 0 && p.ldb % 8 == 0 && p.ldo % 8 == 0,
                 "attention: leading dimensions must be multiples of 8 elements");
   KFB_CHECK_ARG(p.bias_div >= 1 && p.mask_lo_extent >= 1, "attention: bad divisors");
   KFB_CHECK_ARG(p.batch <= 65535, "attention: batch %d exceeds the grid z limit", p.batch);
-  if (p.dpad == 32) return launch_dpad<32>(stream, p);
-  if (p.dpad == 64) return launch_dpad<64>(stream, p);
+  if (p.dpad == 32) {
+    // two batch rows per CTA when consecutive rows share their bias tile
+    if (p.batch % 2 == 0 && p.bias_div % 2 == 0) return launch_cfg<32, 2>(stream, p);
+    return launch_cfg<32, 1>(stream, p);
+  }
+  if (p.dpad == 64) return launch_cfg<64, 1>(stream, p);
   set_error("attention: padded head dim %d not supported (32 or 64)", p.dpad);
   return KFB_ERR_UNSUPPORTED;
 }

@@ -1,20 +1,27 @@
 // Flash-style attention with an additive pair bias and a key mask, on tcgen05/TMEM.
 //
-//   S = Q K^T + bias[h, q, k] + (mask[k] ? 0 : -1e9)       (Q arrives pre-scaled by 1/sqrt(D))
-//   O = softmax_k(S) V                                     then optionally O *= sigmoid(G)
+//   S = Q K^T + bias[h, q, k] + (mask[k] ? 0 : -1e9)        O = softmax_k(S) V   (optionally O *= sigmoid(G))
 //
-// One CTA handles 128 queries of one (batch row, head) and walks the keys in blocks of
-// 128 with an online softmax; the L x L x H logits never exist in memory.  Per key block:
-//   warp 0      TMA: K tile, V^T tile and the 128 x 128 bias tile into shared memory
-//   warp 1      tcgen05.mma  S = Q K^T  (accumulator in TMEM), later  O_blk = P V
-//   warps 2..5  one query row per thread: read its S row from TMEM, add the bias tile
-//               (from shared memory) and the key mask, update the running max / sum,
-//               write P = exp(S - max) as bf16 into a swizzled shared-memory tile (the
-//               A operand of the second MMA), and fold O_blk into register accumulators.
+// Q arrives pre-scaled by 1/sqrt(D).  One CTA handles 128 queries of one head for R (1 or 2) batch
+// rows that share the same bias tile, walking the keys in blocks of 128 with an online softmax;
+// the L x L x H logits never exist in memory.  Per key block:
+//   warp 0        TMA: K and V^T tiles per row, and the 128 x 128 bias tile (once for all R rows)
+//   warp 1        tcgen05.mma into TMEM:  S  = Q K^T            (K = D)
+//                                         S += I  bias          (identity x bias tile, read MN-major as it
+//                                                                lies in memory: the bias is added by the
+//                                                                otherwise idle tensor core)
+//                                         S += e0 maskrow^T     (rank-1: the key mask, one K=16 step)
+//                 later  O_blk = P V
+//   warps 2..     one query row per thread: a single pass over its S row from TMEM computes
+//                 P = exp(S - s) (one FFMA + one ex2 per element) against a lagging stabiliser s
+//                 (raised only when the running maximum has moved by more than e^5.5; an
+//                 overflow-safe redo exists), writes P as
+//                 bf16 into the swizzled A-operand tile of the second MMA and folds the previous
+//                 block's O_blk into register accumulators.
 //
-// Used for triangle attention (batch row = pair row i, bias shared by all rows, mask
-// per row) and for pair-bias attention on the single / token track (bias shared by
-// `bias_div` consecutive batch entries, mask per batch entry).
+// Used for triangle attention (batch row = pair row i, bias shared by all rows, mask per row) and
+// for pair-bias attention on the single / token track (bias shared by `bias_div` consecutive
+// batch entries, mask per batch entry).
 #pragma once
 #include "common.cuh"
 

@@ -7,7 +7,8 @@
 //   warp 1 (one lane)  issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
 //                      accumulator buffers (2 x BN fp32 columns), so the epilogue of
 //                      tile t overlaps the main loop of tile t+1;
-//   warps 2..5         epilogue: each thread owns one accumulator row (one TMEM lane),
+//   warps 2..9         epilogue: each thread owns one accumulator row (one TMEM lane) and every
+//                      other 32-column chunk of it,
 //                      reads it 32 columns at a time with tcgen05.ld and applies the
 //                      fused element-wise tail (gated linear unit, row mask, sigmoid
 //                      gate from memory, residual) before storing.
@@ -58,7 +59,8 @@ struct GemmParams {
 
 static constexpr int kBM = 128;
 static constexpr int kBK = 64;   // bf16 elements = 128 bytes = one swizzle span
-static constexpr int kGemmThreads = 192;
+static constexpr int kEpiWarps = 8;  // two warps per TMEM lane quadrant, each taking every other 32-column chunk
+static constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 
 template <int BN>
 struct GemmCfg {
@@ -144,7 +146,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&tmem_full[a], 1);
-      ptx::mbar_init(&tmem_empty[a], 128);
+      ptx::mbar_init(&tmem_empty[a], 32 * kEpiWarps);
     }
     ptx::fence_barrier_init();
   }
@@ -210,8 +212,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int chunk_phase = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
     const int r = quad * 32 + lane;
     uint32_t tile_iter = 0;
     bool ok = true;
@@ -238,7 +241,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int out_bn = p.glu ? OUT_BN_GLU : BN;
       const int out_col_tile = n_tile * out_bn;
 #pragma unroll 1
-      for (int c = 0; c < out_bn; c += 32) {
+      for (int c = chunk_phase * 32; c < out_bn; c += 32 * (kEpiWarps / 4)) {
         const int out_col = out_col_tile + c;
         float v[32];
         {
@@ -300,7 +303,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (col_local + i < sg.ncols) v[i] *= sigmoidf_fast(__bfloat162float(g[static_cast<long long>(i) * p.g_col]));
             }
           }
-          if (p.resid != nullptr) {
+          if (p.resid != nullptr && sg.vec && col_local + 32 <= sg.ncols) {
+            if (sg.out_fp32) {
+              const float4* rs = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.resid) + row_off + col_local);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 f = rs[q];
+                v[q * 4] += f.x; v[q * 4 + 1] += f.y; v[q * 4 + 2] += f.z; v[q * 4 + 3] += f.w;
+              }
+            } else {
+              const uint4* rs = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.resid) + row_off + col_local);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 u = rs[q];
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                  v[q * 8 + j * 2] += f.x;
+                  v[q * 8 + j * 2 + 1] += f.y;
+                }
+              }
+            }
+          } else if (p.resid != nullptr) {
             if (sg.out_fp32) {
               const float* rs = reinterpret_cast<const float*>(p.resid) + row_off + static_cast<long long>(col_local) * sg.s_col;
 #pragma unroll

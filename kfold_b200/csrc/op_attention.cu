@@ -155,10 +155,11 @@ KFB_API size_t kfb_pair_bias_workspace_bytes(int batch, int n, int c) {
   return align_up(static_cast<size_t>(batch) * n * n * c * sizeof(__nv_bfloat16), 256);
 }
 
-// bias[b][h][i][j] = sum_c LN(z)[b][i][j][c] * W[h][c], stored bf16 channel(head)-major.
+// bias[b][h][i][j] = sum_c LN(z)[b][i][j][c] * W[h][c], stored bf16 head-major; with `transposed` the
+// last two indices are swapped (bias_out[b][h][j][i]), the layout the attention kernel consumes.
 KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
-                              void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, float eps,
-                              int dtype, void* stream_) {
+                              void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, int transposed,
+                              float eps, int dtype, void* stream_) {
   KFB_CHECK_ARG(z && w && bias_out && workspace, "pair_bias: null pointer");
   KFB_CHECK_ARG(is_dtype(dtype), "pair_bias: bad dtype %d", dtype);
   KFB_CHECK_ARG(batch >= 1 && n >= 8 && n % 8 == 0 && c % 8 == 0 && heads >= 1, "pair_bias: batch %d n %d c %d heads %d",
@@ -181,8 +182,8 @@ KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_
   s.ncols = heads;
   s.dst = bias_out;
   s.s_col = nn;
-  s.s_n = 1;
-  s.s_o = n;
+  s.s_n = transposed ? n : 1;
+  s.s_o = transposed ? 1 : n;
   s.s_b = static_cast<long long>(heads) * nn;
   GemmOperandA a = {zn, c, static_cast<long long>(n) * c, nn * c};
   GemmOperandB b = {w, c, 0};

@@ -191,10 +191,12 @@ def transition(x: torch.Tensor, packed: dict, eps: float = 1e-5, residual: bool 
     return out.view(x.shape)
 
 
-def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.Tensor, eps: float = 1e-5,
+              transposed: bool = False) -> torch.Tensor:
     """bias = Linear(LayerNorm(z)) moved to (B, H, N, N), bf16
     (model/modules/confidence_head.py:162-163; model/layers/folding/diffusion.py:411-416).
-    z (B,N,N,C); w (H,C) already on the device in bf16; N must be a multiple of 8."""
+    z (B,N,N,C); w (H,C) already on the device in bf16; N must be a multiple of 8.
+    ``transposed`` swaps the last two dims of the result."""
     _require_cuda(z, w)
     b, n, _, c = z.shape
     if n % 8 != 0:
@@ -206,5 +208,5 @@ def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.
     with torch.cuda.device(z.device):
         ws = _workspace(z.device, lib.kfb_pair_bias_workspace_bytes(b, n, c))
         L.check(lib.kfb_pair_bias_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), b, n,
-                                      c, heads, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
+                                      c, heads, 1 if transposed else 0, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
     return out

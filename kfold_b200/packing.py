@@ -81,15 +81,16 @@ def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
 
 def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
     """Projections of AttentionPairBias (model/layers/folding/attention_pair_bias.py:30-67):
-    [q / sqrt(D) (+ scaled bias) | k | g | v], heads padded; output projection as is."""
+    [q / sqrt(D) (+ bias, same scale) | k | g | v], heads padded; output projection as is."""
     c = int(w["linear_q.weight"].shape[1])
     d = c // heads
     dp = head_dim_pad(d)
     f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
-    proj = torch.cat([f("linear_q.weight", d ** -0.5), f("linear_k.weight"), f("linear_g.weight"), f("linear_v.weight")], dim=0)
+    qs = d ** -0.5
+    proj = torch.cat([f("linear_q.weight", qs), f("linear_k.weight"), f("linear_g.weight"), f("linear_v.weight")], dim=0)
     pb = torch.zeros(4 * heads * dp, dtype=torch.float32)
     if w.get("linear_q.bias") is not None:
-        pb[: heads * dp] = _pad_heads(w["linear_q.bias"].detach().float(), heads, d, dp, d ** -0.5)
+        pb[: heads * dp] = _pad_heads(w["linear_q.bias"].detach().float(), heads, d, dp, qs)
     if w.get("linear_g.bias") is not None:
         pb[2 * heads * dp: 3 * heads * dp] = _pad_heads(w["linear_g.bias"].detach().float(), heads, d, dp)
     ob = w.get("linear_out.bias")
