@@ -66,6 +66,10 @@ KFB_API long long kfb_launch_count(void);
 KFB_API int kfb_profile_enable(int on);
 KFB_API int kfb_profile_report(char* buf, size_t cap);
 
+/* Debugging aid (off by default): a device buffer of at least 512 int64 that receives clock stamps of the
+ * attention kernel's pipeline events for its first CTA; pass NULL to switch it off again. */
+KFB_API int kfb_debug_attention_trace(void* device_buffer_512_i64);
+
 /*
  * Triangle multiplicative update, outgoing (incoming = 0) or incoming (incoming = 1).
  * Replaces TriangleMultiplicationOutgoing.forward / TriangleMultiplicationIncoming.forward

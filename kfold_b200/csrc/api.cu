@@ -1,4 +1,5 @@
 // extern "C" entry points: argument checking and kernel sequencing.
+#include "attention.cuh"
 #include "ops_common.cuh"
 
 using namespace kfb;
@@ -26,6 +27,11 @@ KFB_API int kfb_device_status(int* code_out) {
 }
 
 KFB_API KFB_API long long kfb_launch_count(void) { return launch_count(); }
+
+KFB_API int kfb_debug_attention_trace(void* device_buffer_512_i64) {
+  set_attention_trace(static_cast<long long*>(device_buffer_512_i64));
+  return KFB_OK;
+}
 
 KFB_API int kfb_profile_enable(int on) {
   profile_enable(on != 0);

@@ -27,9 +27,15 @@ struct AttCfg {
   static constexpr int kKvStages = 2;
   static constexpr int kTileBytes = 2 * 128 * 128;       // a 128 x 128 bf16 tile as two 64-wide swizzled halves
   static constexpr int kSmallBytes = 128 * 32;           // a 128 x 16 bf16 K-major operand without swizzle
-  static constexpr int kTmemCols = (R == 1) ? 256 : 512; // S_g at g*128, O_g at R*128 + g*DPAD
-  static constexpr int kSmemBytes = R * kQBytes + R * kKvStages * (kKBytes + kVBytes) + kTileBytes /*bias*/ +
-                                    R * kTileBytes /*P*/ + kTileBytes /*identity*/ + kSmallBytes /*e0*/ +
+  static constexpr int kBiasStages = 2;
+  // tensor memory columns: S_g at g*128 (fp32), O_g at R*128 + g*DPAD (fp32), P_g at R*(128+DPAD) + g*64 (bf16 pairs),
+  // then the constant identity matrix
+  static constexpr int kTmemO = R * 128;
+  static constexpr int kTmemP = R * (128 + DPAD);
+  static constexpr int kTmemI = R * (128 + DPAD + 64);   // identity (128 x 128 bf16 = 64 columns), A operand of the bias MMA
+  static constexpr int kTmemCols = (kTmemI + 64 <= 256) ? 256 : 512;
+  static constexpr int kSmemBytes = R * kQBytes + R * kKvStages * (kKBytes + kVBytes) + kBiasStages * kTileBytes /*bias*/ +
+                                    kSmallBytes /*e0*/ +
                                     R * kSmallBytes /*mask rows*/ + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -49,7 +55,7 @@ __device__ __forceinline__ uint64_t make_mnmajor_desc(uint32_t smem_addr, uint32
 __device__ __forceinline__ uint32_t small_operand_row_offset(int r) { return (r >> 3) * 256 + (r & 7) * 16; }
 
 template <int DPAD, int R>
-__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads, 1)
+__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads) __maxnreg__((R == 1) ? 255 : 168)
 attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
                       const AttnParams p) {
@@ -61,17 +67,15 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   uint8_t* s_k = s_q + R * Cfg::kQBytes;                          // [R][stages]
   uint8_t* s_v = s_k + R * kStages * Cfg::kKBytes;                // [R][stages]
   uint8_t* s_bias = s_v + R * kStages * Cfg::kVBytes;
-  uint8_t* s_p = s_bias + Cfg::kTileBytes;                        // [R]
-  uint8_t* s_ident = s_p + R * Cfg::kTileBytes;
-  uint8_t* s_e0 = s_ident + Cfg::kTileBytes;
+  uint8_t* s_e0 = s_bias + Cfg::kBiasStages * Cfg::kTileBytes;
   uint8_t* s_maskrow = s_e0 + Cfg::kSmallBytes;                   // [R]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_maskrow + R * Cfg::kSmallBytes);
   uint64_t* q_full = bars;                           // [R]
   uint64_t* kv_full = q_full + R;                    // [R][stages]
   uint64_t* kv_empty = kv_full + R * kStages;        // [R][stages]
   uint64_t* bias_full = kv_empty + R * kStages;
-  uint64_t* bias_empty = bias_full + 1;
-  uint64_t* s_full = bias_empty + 1;                 // [R]
+  uint64_t* bias_empty = bias_full + Cfg::kBiasStages;
+  uint64_t* s_full = bias_empty + Cfg::kBiasStages;  // [R]
   uint64_t* ready = s_full + R;                      // [R]  (128 arrivals)
   uint64_t* o_full = ready + R;                      // [R]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + R);
@@ -82,8 +86,11 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int h = blockIdx.y;
   const int b0 = blockIdx.z * R;  // first batch entry of this CTA
   const int nkv = (p.lk + kBKV - 1) / kBKV;
+  long long* trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+#define KFB_STAMP(slot) do { if (trace != nullptr) trace[slot] = clock64(); } while (0)
 
   if (threadIdx.x == 0) {
+    KFB_STAMP(0);
     ptx::prefetch_tmap(&tm_q);
     ptx::prefetch_tmap(&tm_k);
     ptx::prefetch_tmap(&tm_v);
@@ -98,30 +105,19 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ptx::mbar_init(&kv_empty[g * kStages + s], 1);
       }
     }
-    ptx::mbar_init(bias_full, 1);
-    ptx::mbar_init(bias_empty, 1);
+    for (int s = 0; s < Cfg::kBiasStages; ++s) {
+      ptx::mbar_init(&bias_full[s], 1);
+      ptx::mbar_init(&bias_empty[s], 1);
+    }
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
     ptx::tmem_relinquish();
   }
-  // constant operands: identity (128 x 128, swizzled K-major halves) and e0 (128 x 16, first column ones)
+  // constant operand e0 (128 x 16, first column ones) and the zero halves of the mask-row operands
   if (warp >= 2 && warp < 6) {
     const int r = (warp - 2) * 32 + lane;
-    const uint32_t one_at = 0x3F80u << (16 * (r & 1));  // bf16 1.0 in the low or high half of a 32-bit word
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-#pragma unroll
-      for (int ci = 0; ci < 8; ++ci) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (half == (r >> 6) && ci == ((r & 63) >> 3)) {
-          const int w = (r & 7) >> 1;
-          if (w == 0) v.x = one_at; else if (w == 1) v.y = one_at; else if (w == 2) v.z = one_at; else v.w = one_at;
-        }
-        *reinterpret_cast<uint4*>(s_ident + half * 16384 + r * 128 + ((ci ^ (r & 7)) << 4)) = v;
-      }
-    }
     const uint32_t off = small_operand_row_offset(r);
     *reinterpret_cast<uint4*>(s_e0 + off) = make_uint4(0x3F80u, 0, 0, 0);
     *reinterpret_cast<uint4*>(s_e0 + off + 128) = make_uint4(0, 0, 0, 0);
@@ -135,6 +131,23 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // the identity matrix in tensor memory: row r holds a single bf16 1.0 at K index r (column r/2, half r&1)
+  if (warp >= 2 && warp < 6) {
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t base = tmem_base + Cfg::kTmemI + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = (c * 8 + i == (r >> 1)) ? (0x3F80u << (16 * (r & 1))) : 0u;
+      ptx::tmem_st_32x32b_x8(base + c * 8, v);
+    }
+    ptx::tmem_st_wait();
+    ptx::tc_fence_before_sync();
+  }
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -145,10 +158,11 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int bias_z = (b0 / p.bias_div) * p.heads + h;
       bool ok = true;
       for (int j = 0; ok && j < nkv; ++j) {
-        if (!ptx::mbar_wait(bias_empty, (j & 1) ^ 1, 202)) break;
-        ptx::mbar_expect_tx(bias_full, Cfg::kTileBytes);
-        ptx::tma_load_3d(s_bias, &tm_b, bias_full, j * kBKV, qb * kBQ, bias_z);
-        ptx::tma_load_3d(s_bias + 16384, &tm_b, bias_full, j * kBKV + 64, qb * kBQ, bias_z);
+        const int bs = j % Cfg::kBiasStages;
+        if (!ptx::mbar_wait(&bias_empty[bs], ((j / Cfg::kBiasStages) & 1) ^ 1, 202)) break;
+        ptx::mbar_expect_tx(&bias_full[bs], Cfg::kTileBytes);
+        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes, &tm_b, &bias_full[bs], j * kBKV, qb * kBQ, bias_z);
+        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes + 16384, &tm_b, &bias_full[bs], j * kBKV + 64, qb * kBQ, bias_z);
         const int st = j % kStages;
         for (int g = 0; g < R; ++g) {
           const int slot = g * kStages + st;
@@ -164,36 +178,41 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = ptx::make_idesc(kBQ, kBKV, 1);
-      constexpr uint32_t idesc_s_bmn = idesc_s | (1u << 16);  // B operand MN-major (the bias tile as it lies in memory)
       constexpr uint32_t idesc_o = ptx::make_idesc(kBQ, DPAD, 1);
-      const uint32_t ident_addr = ptx::smem_u32(s_ident);
-      const uint32_t bias_addr = ptx::smem_u32(s_bias);
-      const uint32_t e0_addr = ptx::smem_u32(s_e0);
+      constexpr uint32_t idesc_s_bmn = idesc_s | (1u << 16);  // B operand MN-major (the bias tile as it lies in memory)
+      const uint64_t e0_desc = make_noswizzle_desc(ptx::smem_u32(s_e0));
+      uint64_t maskrow_desc[R];
+#pragma unroll
+      for (int g = 0; g < R; ++g) maskrow_desc[g] = make_noswizzle_desc(ptx::smem_u32(s_maskrow + g * Cfg::kSmallBytes));
+      const uint64_t bias_desc0 = make_mnmajor_desc(ptx::smem_u32(s_bias), 16384);
+      const uint32_t tmem_ident = tmem_base + Cfg::kTmemI;
       bool ok = true;
 
-      // S_g(j) = Q_g K_g(j)^T + I biasT(j)^T + e0 maskrow_g(j)^T
+      // S_g(j) = Q_g K_g(j)^T + I bias(j) + e0 maskrow_g(j)^T
       auto issue_s = [&](int g, int j) -> bool {
         const int slot = g * kStages + (j % kStages);
-        if (g == 0 && !ptx::mbar_wait(bias_full, j & 1, 203)) return false;
+        const int bs = j % Cfg::kBiasStages;
         if (!ptx::mbar_wait(&kv_full[slot], (j / kStages) & 1, 204)) return false;
+        if (g == 0 && !ptx::mbar_wait(&bias_full[bs], (j / Cfg::kBiasStages) & 1, 203)) return false;
         ptx::tc_fence_after_sync();
+        // descriptors are built once per tile; inside a tile only the 16-byte-unit address field advances, so
+        // the single issuing thread spends a couple of instructions per MMA rather than a dependent chain
         const uint32_t tmem_s = tmem_base + g * 128;
-        const uint32_t q_addr = ptx::smem_u32(s_q + g * Cfg::kQBytes);
-        const uint32_t k_addr = ptx::smem_u32(s_k + slot * Cfg::kKBytes);
+        const uint64_t q_desc = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_q + g * Cfg::kQBytes));
+        const uint64_t k_desc = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_k + slot * Cfg::kKBytes));
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk)
-          ptx::mma_f16_ss(tmem_s, ptx::make_kmajor_desc<Cfg::kSpan>(q_addr + kk * 32),
-                          ptx::make_kmajor_desc<Cfg::kSpan>(k_addr + kk * 32), idesc_s, kk != 0 ? 1u : 0u);
+          ptx::mma_f16_ss(tmem_s, q_desc + kk * 2, k_desc + kk * 2, idesc_s, kk != 0 ? 1u : 0u);
+        ptx::mma_f16_ss(tmem_s, e0_desc, maskrow_desc[g], idesc_s, 1u);
+        // identity (from tensor memory) x bias tile (MN-major, as it lies in memory): the otherwise idle tensor
+        // core adds the pair bias; K runs over the 128 queries of the tile, 16 per step
+        const uint64_t bias_desc = bias_desc0 + static_cast<uint64_t>(bs) * (Cfg::kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // K runs over the 128 queries of the tile, 16 per step
-          const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          ptx::mma_f16_ss(tmem_s, ptx::make_kmajor_desc<128>(ident_addr + a_off),
-                          make_mnmajor_desc(bias_addr + kk * 2048, 16384), idesc_s_bmn, 1u);
-        }
-        ptx::mma_f16_ss(tmem_s, make_noswizzle_desc(e0_addr),
-                        make_noswizzle_desc(ptx::smem_u32(s_maskrow + g * Cfg::kSmallBytes)), idesc_s, 1u);
+        for (int kk = 0; kk < 8; ++kk)
+          ptx::mma_f16_ts(tmem_s, tmem_ident + kk * 8, bias_desc + kk * (2048 >> 4), idesc_s_bmn, 1u);
         ptx::tc_commit(&s_full[g]);
-        if (g == R - 1) ptx::tc_commit(bias_empty);
+        if (g == R - 1) ptx::tc_commit(&bias_empty[bs]);
+        KFB_STAMP(16 + j * 8 + g * 4 + 0);
         return true;
       };
 
@@ -202,23 +221,22 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
       for (int j = 0; ok && j < nkv; ++j) {
         for (int g = 0; ok && g < R; ++g) {
-          // P_g(j) written, S_g(j) consumed, O_g(j-1) folded, mask row of block j+1 written
+          // P_g(j) is in tensor memory, S_g(j) consumed, O_g(j-1) folded, mask row of block j+1 written
           if (!ptx::mbar_wait(&ready[g], (j + 1) & 1, 207)) { ok = false; break; }
+          KFB_STAMP(16 + j * 8 + g * 4 + 1);
           ptx::tc_fence_after_sync();
+          // the next S first: it is short and lets the group's next softmax pass start while P V runs
+          if (j + 1 < nkv && !issue_s(g, j + 1)) { ok = false; break; }
           const int slot = g * kStages + (j % kStages);
-          const uint32_t p_addr = ptx::smem_u32(s_p + g * Cfg::kTileBytes);
-          const uint32_t v_addr = ptx::smem_u32(s_v + slot * Cfg::kVBytes);
-          const uint32_t tmem_o = tmem_base + R * 128 + g * DPAD;
+          const uint64_t v_desc = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_v + slot * Cfg::kVBytes));
+          const uint32_t tmem_o = tmem_base + Cfg::kTmemO + g * DPAD;
+          const uint32_t tmem_p = tmem_base + Cfg::kTmemP + g * 64;
 #pragma unroll
-          for (int kk = 0; kk < kBKV / 16; ++kk) {
-            const uint32_t pa = p_addr + (kk >> 2) * 16384 + (kk & 3) * 32;
-            const uint32_t va = v_addr + (kk >> 2) * (DPAD * 128) + (kk & 3) * 32;
-            ptx::mma_f16_ss(tmem_o, ptx::make_kmajor_desc<128>(pa), ptx::make_kmajor_desc<128>(va), idesc_o,
+          for (int kk = 0; kk < kBKV / 16; ++kk)  // A = P straight from tensor memory, 8 columns per K=16 slice
+            ptx::mma_f16_ts(tmem_o, tmem_p + kk * 8, v_desc + ((kk >> 2) * (DPAD * 128 >> 4) + (kk & 3) * 2), idesc_o,
                             kk != 0 ? 1u : 0u);
-          }
           ptx::tc_commit(&o_full[g]);
           ptx::tc_commit(&kv_empty[slot]);
-          if (j + 1 < nkv) ok = issue_s(g, j + 1);
         }
       }
     }
@@ -231,21 +249,24 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int b = b0 + g;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem_base + g * 128 + lane_base;
-    const uint32_t tmem_o = tmem_base + R * 128 + g * DPAD + lane_base;
+    const uint32_t tmem_o = tmem_base + Cfg::kTmemO + g * DPAD + lane_base;
+    const uint32_t tmem_p = tmem_base + Cfg::kTmemP + g * 64 + lane_base;
     const int b_hi = b / p.mask_lo_extent, b_lo = b - b_hi * p.mask_lo_extent;
     const unsigned char* mrow = p.mask + static_cast<long long>(b_hi) * p.m_hi + static_cast<long long>(b_lo) * p.m_lo;
     uint8_t* my_maskrow = s_maskrow + g * Cfg::kSmallBytes + small_operand_row_offset(r);
-    uint8_t* p_tile = s_p + g * Cfg::kTileBytes;
 
-    auto write_mask_row = [&](int j) {  // this thread provides key j*128 + r of its group's mask operand
+    // this thread provides key j*128 + r of its group's mask operand
+    auto load_mask_value = [&](int j) -> float {
       const int key = j * kBKV + r;
-      float mv = kAbsent;
-      if (key < p.lk) mv = mrow[static_cast<long long>(key) * p.m_k] ? 0.f : kMasked;
+      if (key >= p.lk) return kAbsent;
+      return mrow[static_cast<long long>(key) * p.m_k] ? 0.f : kMasked;
+    };
+    auto store_mask_value = [&](float mv) {
       const uint32_t bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(mv)));
       *reinterpret_cast<uint4*>(my_maskrow) = make_uint4(bits, 0, 0, 0);
     };
 
-    write_mask_row(0);
+    store_mask_value(load_mask_value(0));
     ptx::fence_proxy_async_smem();
     ptx::mbar_arrive(&ready[g]);
 
@@ -256,79 +277,103 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     bool ok = true;
 
     for (int j = 0; j < nkv; ++j) {
+      // the mask byte of the next block is fetched before the wait so that its latency hides behind it
+      const float mask_next = (j + 1 < nkv) ? load_mask_value(j + 1) : 0.f;
       if (!ptx::mbar_wait(&s_full[g], j & 1, 208)) { ok = false; break; }
+      if (r == 0) KFB_STAMP(256 + g * 128 + j * 8 + 0);
       ptx::tc_fence_after_sync();
-      if (j + 1 < nkv) write_mask_row(j + 1);  // S(j) is complete, so the MMA no longer reads the mask operand
+      if (j + 1 < nkv) store_mask_value(mask_next);  // S(j) is complete, the MMA no longer reads the mask operand
 
       if (j == 0) {  // stabiliser of the first block: its true row maximum
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        uint32_t raw[2][16];
-        ptx::tmem_ld_32x32b_x16(tmem_s, raw[0]);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          ptx::tmem_ld_wait();
-          if (c < 7) ptx::tmem_ld_32x32b_x16(tmem_s + (c + 1) * 16, raw[(c + 1) & 1]);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw[c & 1][i]));
-        }
-        s_next = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        s_cur = s_next;
-      } else {
-        // fold the previous block's P V product (same scale as acc)
-        if (!ptx::mbar_wait(&o_full[g], (j - 1) & 1, 209)) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < DPAD / 32; ++c) {
-          uint32_t raw[32];
-          ptx::tmem_ld_32x32b_x32(tmem_o + c * 32, raw);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(raw[i]);
-        }
-      }
-
-      // single pass: P = exp(S - s_use) = exp2(S * log2e - s_use * log2e), four independent sum / max chains
-      float s_use = s_next, l_blk = 0.f, mx = -INFINITY;
-#pragma unroll 1
-      for (int attempt = 0; attempt < 2; ++attempt) {
-        const float neg_s = -s_use * kLog2e;
-        float l4[4] = {0.f, 0.f, 0.f, 0.f};
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        // 16 columns at a time, the next TMEM load in flight while the current one is processed
-        auto process = [&](const uint32_t (&raw)[16], int c) {
-          float pv[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float t = __uint_as_float(raw[i]);
-            m4[i & 3] = fmaxf(m4[i & 3], t);
-            pv[i] = exp2f(fmaf(t, kLog2e, neg_s));
-            l4[i & 3] += pv[i];
-          }
-          uint8_t* prow = p_tile + (c >> 2) * 16384 + r * 128;
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int ci = ((c & 3) * 2 + i) ^ (r & 7);
-            *reinterpret_cast<uint4*>(prow + (ci << 4)) =
-                make_uint4(pack_bf16x2(pv[i * 8], pv[i * 8 + 1]), pack_bf16x2(pv[i * 8 + 2], pv[i * 8 + 3]),
-                           pack_bf16x2(pv[i * 8 + 4], pv[i * 8 + 5]), pack_bf16x2(pv[i * 8 + 6], pv[i * 8 + 7]));
-          }
-        };
         uint32_t raw0[16], raw1[16];
         ptx::tmem_ld_32x32b_x16(tmem_s, raw0);
 #pragma unroll 1
         for (int cc = 0; cc < 4; ++cc) {
           ptx::tmem_ld_wait();
           ptx::tmem_ld_32x32b_x16(tmem_s + cc * 32 + 16, raw1);
-          process(raw0, cc * 2);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw0[i]));
           ptx::tmem_ld_wait();
           if (cc < 3) ptx::tmem_ld_32x32b_x16(tmem_s + cc * 32 + 32, raw0);
-          process(raw1, cc * 2 + 1);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw1[i]));
+        }
+        s_next = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        s_cur = s_next;
+      }
+
+      // single pass: P = exp(S - s_use) = exp2(S * log2e - s_use * log2e).  The first quarter of P
+      // waits in registers (packed bf16) until the previous block's P V product has finished reading the P
+      // columns of tensor memory; by the second half that is long done and P is stored as it is produced.
+      float s_use = s_next, l_blk = 0.f, mx = -INFINITY;
+      bool folded = (j == 0);
+#pragma unroll 1
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float neg_s = -s_use * kLog2e;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        auto process = [&](const uint32_t (&raw)[16], int c, uint32_t (&out)[8]) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float t0 = __uint_as_float(raw[i]);
+            const float t1 = __uint_as_float(raw[i + 1]);
+            m4[i & 3] = fmaxf(m4[i & 3], t0);
+            m4[(i + 1) & 3] = fmaxf(m4[(i + 1) & 3], t1);
+            const float p0 = exp2f(fmaf(t0, kLog2e, neg_s));
+            const float p1 = exp2f(fmaf(t1, kLog2e, neg_s));
+            l4[i & 3] += p0;
+            l4[(i + 1) & 3] += p1;
+            out[i >> 1] = pack_bf16x2(p0, p1);
+          }
+        };
+        uint32_t raw0[16], raw1[16];
+        {
+          // keys 0..31: P waits in registers until the previous block's P V product has released the P columns
+          uint32_t held0[8], held1[8];
+          ptx::tmem_ld_32x32b_x16(tmem_s, raw0);
+          ptx::tmem_ld_wait();
+          ptx::tmem_ld_32x32b_x16(tmem_s + 16, raw1);
+          process(raw0, 0, held0);
+          ptx::tmem_ld_wait();
+          ptx::tmem_ld_32x32b_x16(tmem_s + 32, raw0);
+          process(raw1, 1, held1);
+          if (!folded) {
+            // fold the previous block's P V product (same scale as acc)
+            if (!ptx::mbar_wait(&o_full[g], (j - 1) & 1, 209)) { ok = false; break; }
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int cb = 0; cb < DPAD / 32; ++cb) {
+              uint32_t raw[32];
+              ptx::tmem_ld_32x32b_x32(tmem_o + cb * 32, raw);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[cb * 32 + i] += __uint_as_float(raw[i]);
+            }
+            folded = true;
+          }
+          ptx::tmem_st_32x32b_x8(tmem_p, held0);
+          ptx::tmem_st_32x32b_x8(tmem_p + 8, held1);
+        }
+#pragma unroll 1
+        for (int c = 2; c < 8; c += 2) {  // keys 32..127: stored as produced
+          uint32_t out[8];
+          ptx::tmem_ld_wait();
+          ptx::tmem_ld_32x32b_x16(tmem_s + c * 16 + 16, raw1);
+          process(raw0, c, out);
+          ptx::tmem_st_32x32b_x8(tmem_p + c * 8, out);
+          ptx::tmem_ld_wait();
+          if (c + 2 < 8) ptx::tmem_ld_32x32b_x16(tmem_s + c * 16 + 32, raw0);
+          process(raw1, c + 1, out);
+          ptx::tmem_st_32x32b_x8(tmem_p + c * 8 + 8, out);
         }
         l_blk = (l4[0] + l4[1]) + (l4[2] + l4[3]);
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         if (mx - s_use <= kRedoThreshold) break;
         s_use = mx;  // exponents too large for comfort: redo this block against its own maximum
       }
+      if (!ok) break;
+      if (r == 0) KFB_STAMP(256 + g * 128 + j * 8 + 1);
       const float alpha = exp2f((s_cur - s_use) * kLog2e);
 #pragma unroll
       for (int i = 0; i < DPAD; ++i) acc[i] *= alpha;
@@ -336,8 +381,10 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       s_cur = s_use;
       s_next = (mx > s_cur + kRaiseThreshold) ? mx : s_cur;
 
+      if (r == 0) KFB_STAMP(256 + g * 128 + j * 8 + 2);
+      ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
-      ptx::fence_proxy_async_smem();
+      ptx::fence_proxy_async_smem();  // the mask row of the next block was written through the generic proxy
       ptx::mbar_arrive(&ready[g]);
     }
     if (ok && ptx::mbar_wait(&o_full[g], (nkv - 1) & 1, 210)) {
@@ -381,11 +428,16 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) KFB_STAMP(1);
+#undef KFB_STAMP
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
+
+static long long* g_attention_trace = nullptr;
+void set_attention_trace(long long* device_buffer) { g_attention_trace = device_buffer; }
 
 template <int DPAD, int R>
 static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
@@ -434,7 +486,9 @@ static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
   return KFB_OK;
 }
 
-int launch_attention(cudaStream_t stream, const AttnParams& p) {
+int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
+  AttnParams p = p_in;
+  p.trace = g_attention_trace;
   KFB_CHECK_ARG(p.batch > 0 && p.heads > 0 && p.lq > 0 && p.lk > 0, "attention: empty problem");
   KFB_CHECK_ARG(p.d % 8 == 0 && p.d <= p.dpad, "attention: head dim %d must be a multiple of 8 and <= %d", p.d, p.dpad);
   KFB_CHECK_ARG(p.ldq % 8 == 0 && p.ldk % 8 == 0 && p.ldv % 8 == 0 && p.ldb % 8 == 0 && p.ldo % 8 == 0,

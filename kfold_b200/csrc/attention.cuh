@@ -16,8 +16,8 @@
 //                 P = exp(S - s) (one FFMA + one ex2 per element) against a lagging stabiliser s
 //                 (raised only when the running maximum has moved by more than e^5.5; an
 //                 overflow-safe redo exists), writes P as
-//                 bf16 into the swizzled A-operand tile of the second MMA and folds the previous
-//                 block's O_blk into register accumulators.
+//                 packed bf16 into tensor memory (the A operand of the second MMA is read from there)
+//                 and folds the previous block's O_blk into register accumulators.
 //
 // Used for triangle attention (batch row = pair row i, bias shared by all rows, mask per row) and
 // for pair-bias attention on the single / token track (bias shared by `bias_div` consecutive
@@ -46,9 +46,13 @@ struct AttnParams {
   const void* g; long long ldg; int g_col0;
   // output bf16: row (b, q) at out + (b*lq + q)*ldo, head h at column h*d
   void* out; long long ldo;
+  long long* trace;  // debugging aid: when non-null, CTA (0,0,0) stores clock64() stamps of its pipeline events here
   const char* tag;  // name of the launch in the profile report (string literal), may be null
 };
 
 int launch_attention(cudaStream_t stream, const AttnParams& p);
+
+// Debugging aid: a device buffer of >= 512 long longs that receives pipeline time stamps (nullptr = off).
+void set_attention_trace(long long* device_buffer);
 
 }  // namespace kfb

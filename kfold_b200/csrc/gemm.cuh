@@ -199,13 +199,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const uint32_t phase = (it / kStages) & 1;
           if (!ptx::mbar_wait(&full_bar[stage], phase, 103)) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          const uint32_t a_addr = ptx::smem_u32(s_a + stage * Cfg::kAStage);
-          const uint32_t b_addr = ptx::smem_u32(s_b + stage * Cfg::kBStage);
+          // one descriptor per stage; inside the 128-byte swizzle span only the address field advances
+          const uint64_t a_desc = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_a + stage * Cfg::kAStage));
+          const uint64_t b_desc = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_b + stage * Cfg::kBStage));
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            ptx::mma_f16_ss(d_tmem, ptx::make_kmajor_desc<128>(a_addr + k * 32),
-                            ptx::make_kmajor_desc<128>(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < kBK / 16; ++k)
+            ptx::mma_f16_ss(d_tmem, a_desc + k * 2, b_desc + k * 2, idesc, (kb | k) != 0 ? 1u : 0u);
           ptx::tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
         }
         if (ok) ptx::tc_commit(&tmem_full[acc]);
