@@ -69,6 +69,8 @@ KFB_API int kfb_profile_report(char* buf, size_t cap);
 /* Debugging aid (off by default): a device buffer of at least 512 int64 that receives clock stamps of the
  * attention kernel's pipeline events for its first CTA; pass NULL to switch it off again. */
 KFB_API int kfb_debug_attention_trace(void* device_buffer_512_i64);
+/* Same for the GEMM launches whose profile tag equals `tag` (per-tile stamps of the first CTA). */
+KFB_API int kfb_debug_gemm_trace(void* device_buffer_512_i64, const char* tag);
 
 /*
  * Triangle multiplicative update, outgoing (incoming = 0) or incoming (incoming = 1).

@@ -33,6 +33,11 @@ KFB_API int kfb_debug_attention_trace(void* device_buffer_512_i64) {
   return KFB_OK;
 }
 
+KFB_API int kfb_debug_gemm_trace(void* device_buffer_512_i64, const char* tag) {
+  set_gemm_trace(static_cast<long long*>(device_buffer_512_i64), tag);
+  return KFB_OK;
+}
+
 KFB_API int kfb_profile_enable(int on) {
   profile_enable(on != 0);
   return KFB_OK;

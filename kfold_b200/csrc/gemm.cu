@@ -1,4 +1,7 @@
 // Host launcher of the persistent tcgen05 GEMM (see gemm.cuh for the kernel).
+#include <stdio.h>
+#include <string.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -6,25 +9,46 @@
 
 namespace kfb {
 
-template <int BN>
-static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, const char* tag) {
+template <int BN, bool GLU, bool AUX>
+static int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* tout,
+                          const GemmParams& p, const char* tag) {
   using Cfg = GemmCfg<BN>;
   static std::once_flag once[64];
   int dev = 0;
   KFB_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, GLU, AUX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   });
   KFB_CUDA(attr_err);
   const int total = p.num_m_tiles * p.num_n_tiles;
   const int grid = total < sm_count() ? total : sm_count();
   {
     LaunchScope scope(stream, tag);
-    gemm_bf16_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+    gemm_bf16_kernel<BN, GLU, AUX><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], p);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
+}
+
+template <int BN>
+static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* tout,
+                     GemmParams p, const char* tag) {
+  using Cfg = GemmCfg<BN>;
+  if (p.aux && Cfg::stages_for(Cfg::kAuxBytes) < 2) p.aux = 0;  // no room (BN = 256): fall back to direct loads
+  p.stages = Cfg::stages_for(p.aux ? Cfg::kAuxBytes : Cfg::kStagingBytes);
+  if (p.glu) return launch_variant<BN, true, false>(stream, ta, tb, tout, p, tag);
+  if constexpr (BN <= 128) {
+    if (p.aux) return launch_variant<BN, false, true>(stream, ta, tb, tout, p, tag);
+  }
+  return launch_variant<BN, false, false>(stream, ta, tb, tout, p, tag);
+}
+
+static long long* g_trace_buf = nullptr;
+static char g_trace_tag[64] = "";
+void set_gemm_trace(long long* device_buffer, const char* tag) {
+  g_trace_buf = device_buffer;
+  snprintf(g_trace_tag, sizeof(g_trace_tag), "%s", tag ? tag : "");
 }
 
 int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn,
@@ -36,10 +60,10 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   KFB_CHECK_ARG(bn == 64 || bn == 128 || bn == 256, "unsupported BN %d", bn);
   if (p.glu) KFB_CHECK_ARG(p.n_cols % bn == 0, "GLU GEMM needs n_cols (%d) to be a multiple of the N tile (%d)", p.n_cols, bn);
   for (int i = 0; i < p.nseg; ++i) KFB_CHECK_ARG(p.seg[i].col_begin % 32 == 0, "segment start must be a multiple of 32");
+  p.trace = (g_trace_buf != nullptr && strcmp(g_trace_tag, tag) == 0) ? g_trace_buf : nullptr;
   p.n_blocks = cdiv(p.n_extent, kBM);
   p.num_m_tiles = p.n_blocks * p.o_extent * p.batch;
   p.num_n_tiles = cdiv(p.n_cols, bn);
-  if (p.alpha == 0.0f) p.alpha = 1.0f;
 
   CUtensorMap ta, tb;
   {
@@ -54,10 +78,56 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
     const uint32_t box[3] = {kBK, (uint32_t)bn, 1};
     KFB_TRY(make_tmap(&tb, b.ptr, 2, 3, dims, str, box, 128));
   }
+  // channel-major bf16 segments that satisfy the TMA alignment rules are stored through shared memory
+  CUtensorMap tout[2];
+  tout[0] = ta;  // placeholders (never dereferenced unless a segment selects them)
+  tout[1] = ta;
+  int next_slot = 0;
+  for (int i = 0; i < p.nseg; ++i) {
+    EpiSeg& sg = p.seg[i];
+    sg.tma_slot = -1;
+    const bool aligned = (reinterpret_cast<uintptr_t>(sg.dst) & 15) == 0 && sg.s_o % 8 == 0 && sg.s_col % 8 == 0 &&
+                         (sg.s_b % 8 == 0 || p.batch == 1) && (sg.s_o != 0 || p.o_extent == 1);
+    if (sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && aligned && next_slot < 2) {
+      const uint64_t dims[4] = {(uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)sg.ncols, (uint64_t)p.batch};
+      const uint64_t str[3] = {(uint64_t)sg.s_o * 2, (uint64_t)sg.s_col * 2, (uint64_t)sg.s_b * 2};
+      const uint32_t box[4] = {32, 1, 32, 1};
+      KFB_TRY(make_tmap(&tout[next_slot], sg.dst, 2, 4, dims, str, box, 0));
+      sg.tma_slot = next_slot++;
+    }
+  }
+  // gate / residual prefetch: only without staged segments, bf16 tensors, full 32-column chunks, aligned strides
+  p.aux = 0;
+  p.aux_gate = 0;
+  p.aux_resid = 0;
+  if (next_slot == 0 && p.nseg == 1 && p.seg[0].vec && (p.gate != nullptr || p.resid != nullptr) && bn >= 64 &&
+      p.n_cols % 32 == 0 && !p.glu) {
+    const EpiSeg& sg = p.seg[0];
+    bool ok_g = true, ok_r = true;
+    if (p.gate != nullptr)
+      ok_g = p.g_col == 1 && (reinterpret_cast<uintptr_t>(p.gate) & 15) == 0 && p.g_n % 8 == 0 && p.g_o % 8 == 0 && p.g_b % 8 == 0;
+    if (p.resid != nullptr)
+      ok_r = !sg.out_fp32 && (reinterpret_cast<uintptr_t>(p.resid) & 15) == 0 && sg.s_n % 8 == 0 && sg.s_o % 8 == 0 && sg.s_b % 8 == 0;
+    if (ok_g && ok_r) {
+      const uint32_t box[4] = {64, kBM, 1, 1};
+      const uint64_t dims[4] = {(uint64_t)p.n_cols, (uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)p.batch};
+      if (p.gate != nullptr) {
+        const uint64_t str[3] = {(uint64_t)p.g_n * 2, (uint64_t)p.g_o * 2, (uint64_t)p.g_b * 2};
+        KFB_TRY(make_tmap(&tout[0], p.gate, 2, 4, dims, str, box, 128));
+        p.aux_gate = 1;
+      }
+      if (p.resid != nullptr) {
+        const uint64_t str[3] = {(uint64_t)sg.s_n * 2, (uint64_t)sg.s_o * 2, (uint64_t)sg.s_b * 2};
+        KFB_TRY(make_tmap(&tout[1], p.resid, 2, 4, dims, str, box, 128));
+        p.aux_resid = 1;
+      }
+      p.aux = 1;
+    }
+  }
   switch (bn) {
-    case 64: return launch_bn<64>(stream, ta, tb, p, tag);
-    case 128: return launch_bn<128>(stream, ta, tb, p, tag);
-    default: return launch_bn<256>(stream, ta, tb, p, tag);
+    case 64: return launch_bn<64>(stream, ta, tb, tout, p, tag);
+    case 128: return launch_bn<128>(stream, ta, tb, tout, p, tag);
+    default: return launch_bn<256>(stream, ta, tb, tout, p, tag);
   }
 }
 

@@ -34,6 +34,7 @@ struct EpiSeg {
   int ncols;        // valid columns in the segment; columns beyond are dropped
   int out_fp32;     // 0: bf16 output, 1: fp32 output
   int vec;          // 1: s_col == 1 and every row start is 16-byte aligned -> vector stores
+  int tma_slot;     // >= 0: channel-major bf16 segment stored through shared memory with TMA store map `tma_slot`
   void* dst;
   long long s_col, s_n, s_o, s_b;
 };
@@ -53,8 +54,11 @@ struct GemmParams {
   const float* col_bias;          // optional, per output column, added before everything else
   const __nv_bfloat16* gate;      // optional: seg 0 value *= sigmoid(gate[...]), addressed with seg 0 strides
   long long g_col, g_n, g_o, g_b;
+  int stages;                     // depth of the operand ring (launcher)
+  int aux;                        // 1: gate / residual tiles are prefetched into shared memory by TMA (launcher)
+  int aux_gate, aux_resid;        // which of the two the prefetch covers
+  long long* trace;               // debugging aid: CTA 0 stores clock64() stamps per tile here when non-null
   const void* resid;              // optional: seg 0 value += resid[...] (same dtype and strides as seg 0 dst)
-  float alpha;                    // value scale (applied to the accumulator first)
 };
 
 static constexpr int kBM = 128;
@@ -67,12 +71,27 @@ struct GemmCfg {
   static constexpr int kAStage = kBM * kBK * 2;
   static constexpr int kBStage = BN * kBK * 2;
   static constexpr int kStageBytes = kAStage + kBStage;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kMaxStages = 8;
+  static constexpr int kStagingBytes = kEpiWarps * 2 * 32 * 32 * 2;  // per epilogue warp: 2 slabs of [32 channels][32 rows] bf16
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kSmemBytes = 232448 - 1024;        // everything an SM offers one CTA
+  // after the operand ring comes EITHER the channel-major staging slabs OR two buffers of prefetched
+  // gate + residual tiles (128 rows x BN columns bf16 each); the launcher picks the ring depth accordingly
+  static constexpr int kAuxTileBytes = kBM * BN * 2;
+  static constexpr int kAuxBytes = 2 * 2 * kAuxTileBytes;
+  static constexpr int stages_for(int extra_bytes) {
+    const int fit = (kSmemBytes - 1024 - extra_bytes - kBarrierBytes) / kStageBytes;
+    return fit < kMaxStages ? fit : kMaxStages;
+  }
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+// sigmoid(x) = 0.5 tanh(x / 2) + 0.5: one MUFU op instead of an exp2 and a reciprocal
+__device__ __forceinline__ float sigmoidf_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(t, 0.5f, 0.5f);
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -113,31 +132,43 @@ __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_
   }
 }
 
-template <int BN>
+// GLU and AUX are compile-time so that each variant carries only its own epilogue code (and registers):
+//   GLU  the tile holds values and gates (p.glu says which activation);
+//   AUX  gate logits / residual come from shared-memory tiles prefetched by the producer.
+template <int BN, bool GLU, bool AUX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_out0, const __grid_constant__ CUtensorMap tm_out1,
                  const GemmParams p) {
+  // tm_out0 / tm_out1: TMA-store maps of channel-major segments, or (p.aux) the gate / residual load maps
   using Cfg = GemmCfg<BN>;
-  constexpr int kStages = Cfg::kStages;
+  const int kStages = p.stages;
   constexpr int OUT_BN_GLU = BN / 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_a = smem;
   uint8_t* s_b = smem + kStages * Cfg::kAStage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint8_t* s_stage_out = smem + kStages * Cfg::kStageBytes;  // [epilogue warp][2][32 channels][32 rows] bf16 ...
+  uint8_t* s_aux = s_stage_out;                               // ... or [2 buffers][gate, resid][2 halves? BN/64][128 x 64] bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stage_out + (AUX ? Cfg::kAuxBytes : Cfg::kStagingBytes));
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + kStages;
-  uint64_t* tmem_full = bars + 2 * kStages;
-  uint64_t* tmem_empty = bars + 2 * kStages + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* empty_bar = bars + Cfg::kMaxStages;
+  uint64_t* tmem_full = bars + 2 * Cfg::kMaxStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint64_t* aux_full = tmem_empty + 2;   // [2]
+  uint64_t* aux_empty = aux_full + 2;    // [2], one arrival per epilogue warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_empty + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_k = (p.k_extent + kBK - 1) / kBK;
   const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+  long long* trace = (p.trace != nullptr && blockIdx.x == 0) ? p.trace : nullptr;
+#define KFB_GSTAMP(slot) do { if (trace != nullptr && (slot) < 512) trace[slot] = clock64(); } while (0)
 
   if (threadIdx.x == 0) {
+    KFB_GSTAMP(0);
     ptx::prefetch_tmap(&tm_a);
     ptx::prefetch_tmap(&tm_b);
     for (int s = 0; s < kStages; ++s) {
@@ -147,6 +178,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&tmem_full[a], 1);
       ptx::mbar_init(&tmem_empty[a], 32 * kEpiWarps);
+      ptx::mbar_init(&aux_full[a], 1);
+      ptx::mbar_init(&aux_empty[a], kEpiWarps);
     }
     ptx::fence_barrier_init();
   }
@@ -162,7 +195,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      int stage = 0;
+      uint32_t phase = 0;  // ring position, advanced without divisions (the ring depth is a run-time value)
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const int m_tile = tile / p.num_n_tiles;
@@ -172,21 +206,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int o = rest % p.o_extent;
         const int b = rest / p.o_extent;
         const int bb = p.b_batched ? b : 0;
-        for (int kb = 0; kb < num_k; ++kb, ++it) {
-          const int stage = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
+        if (AUX) {
+          // gate / residual tiles of this output tile, one tile ahead of the epilogue
+          const uint32_t ti = (tile - blockIdx.x) / gridDim.x;
+          const int ab = ti & 1;
+          if (!ptx::mbar_wait(&aux_empty[ab], ((ti >> 1) & 1) ^ 1, 106)) { ok = false; break; }
+          uint8_t* dst = s_aux + ab * (2 * Cfg::kAuxTileBytes);
+          ptx::mbar_expect_tx(&aux_full[ab], (p.aux_gate + p.aux_resid) * Cfg::kAuxTileBytes);
+#pragma unroll
+          for (int hcol = 0; hcol < BN / 64; ++hcol) {
+            if (p.aux_gate)
+              ptx::tma_load_4d(dst + hcol * (kBM * 128), &tm_out0, &aux_full[ab], n_tile * BN + hcol * 64, nb * kBM, o, b);
+            if (p.aux_resid)
+              ptx::tma_load_4d(dst + Cfg::kAuxTileBytes + hcol * (kBM * 128), &tm_out1, &aux_full[ab], n_tile * BN + hcol * 64,
+                               nb * kBM, o, b);
+          }
+        }
+        for (int kb = 0; kb < num_k; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1, 101)) { ok = false; break; }
           ptx::mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], kb * kBK, nb * kBM, o, b);
           ptx::tma_load_3d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], kb * kBK, n_tile * BN, bb);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
+        KFB_GSTAMP(4 + (tile / gridDim.x) * 4 + 3);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::make_idesc(kBM, BN, /*bf16*/ 1);
-      uint32_t it = 0, tile_iter = 0;
+      uint32_t tile_iter = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
         const uint32_t acc = tile_iter & 1;
@@ -194,9 +246,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, 102)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_k; ++kb, ++it) {
-          const int stage = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
+        for (int kb = 0; kb < num_k; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, 103)) { ok = false; break; }
           ptx::tc_fence_after_sync();
           // one descriptor per stage; inside the 128-byte swizzle span only the address field advances
@@ -206,14 +256,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           for (int k = 0; k < kBK / 16; ++k)
             ptx::mma_f16_ss(d_tmem, a_desc + k * 2, b_desc + k * 2, idesc, (kb | k) != 0 ? 1u : 0u);
           ptx::tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (ok) ptx::tc_commit(&tmem_full[acc]);
+        KFB_GSTAMP(4 + tile_iter * 4 + 2);
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int chunk_phase = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
+    uint32_t staging_use = 0;
     const int r = quad * 32 + lane;
     uint32_t tile_iter = 0;
     bool ok = true;
@@ -229,7 +282,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_phase = (tile_iter >> 1) & 1;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_phase, 104)) { ok = false; break; }
+      if (threadIdx.x == 64) KFB_GSTAMP(4 + tile_iter * 4 + 0);
       ptx::tc_fence_after_sync();
+      const uint8_t* aux_tile = s_aux + (tile_iter & 1) * (2 * Cfg::kAuxTileBytes);
+      if (AUX && !ptx::mbar_wait(&aux_full[tile_iter & 1], (tile_iter >> 1) & 1, 107)) { ok = false; break; }
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
 
       float mask_v = 1.0f;
@@ -237,7 +293,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         mask_v = p.rowmask[static_cast<long long>(b) * p.m_b + static_cast<long long>(o) * p.m_o +
                            static_cast<long long>(n) * p.m_n] ? 1.0f : 0.0f;
 
-      const int out_bn = p.glu ? OUT_BN_GLU : BN;
+      constexpr int out_bn = GLU ? OUT_BN_GLU : BN;
       const int out_col_tile = n_tile * out_bn;
 #pragma unroll 1
       for (int c = chunk_phase * 32; c < out_bn; c += 32 * (kEpiWarps / 4)) {
@@ -248,18 +304,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ptx::tmem_ld_32x32b_x32(t_row + c, raw);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * p.alpha;
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
         }
-        if (p.glu) {
+        if (GLU) {
           uint32_t raw[32];
           ptx::tmem_ld_32x32b_x32(t_row + OUT_BN_GLU + c, raw);
           ptx::tmem_ld_wait();
           if (p.glu == GLU_SIGMOID) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= sigmoidf_fast(__uint_as_float(raw[i]) * p.alpha);
+            for (int i = 0; i < 32; ++i) v[i] *= sigmoidf_fast(__uint_as_float(raw[i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = v[i] * sigmoidf_fast(v[i]) * (__uint_as_float(raw[i]) * p.alpha);
+            for (int i = 0; i < 32; ++i) v[i] = v[i] * sigmoidf_fast(v[i]) * __uint_as_float(raw[i]);
           }
         }
         // which segment does this chunk belong to
@@ -277,9 +333,57 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] *= mask_v;
         }
+        if (sg.tma_slot >= 0) {
+          // channel-major segment: the warp transposes its 32 x 32 piece into a private [32 channels][32 rows]
+          // shared-memory slab (two slabs, used alternately) and one lane hands it to a TMA store; rows and
+          // channels outside the tensor are clipped by the copy engine.  No cross-warp synchronisation.
+          uint8_t* slab = s_stage_out + ((warp - 2) * 2 + (staging_use & 1)) * (32 * 32 * 2);
+          __nv_bfloat16* col0 = reinterpret_cast<__nv_bfloat16*>(slab) + lane;
+          if (lane == 0) ptx::tma_store_wait_read_le1();  // the store that last read this slab (two uses ago) is done
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) col0[i * 32] = __float2bfloat16_rn(v[i]);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_4d(sg.tma_slot == 0 ? &tm_out0 : &tm_out1, slab, nb * kBM + quad * 32, o, col_local, b);
+            ptx::tma_store_commit();
+          }
+          ++staging_use;
+          continue;
+        }
         const long long row_off = static_cast<long long>(b) * sg.s_b + static_cast<long long>(o) * sg.s_o +
                                   static_cast<long long>(n) * sg.s_n;
-        if (si == 0 && row_ok) {
+        if (AUX && si == 0) {
+          // gate logits and residual come from the tiles the producer prefetched (128-byte swizzled rows)
+          const uint8_t* rowp = aux_tile + (c >> 6) * (kBM * 128) + r * 128;
+          const int cbase = ((c >> 5) & 1) * 4;
+          if (p.aux_gate) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 u = *reinterpret_cast<const uint4*>(rowp + (((cbase + q) ^ (r & 7)) << 4));
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[q * 8 + j * 2] *= sigmoidf_fast(__uint_as_float(w[j] << 16));
+                v[q * 8 + j * 2 + 1] *= sigmoidf_fast(__uint_as_float(w[j] & 0xffff0000u));
+              }
+            }
+          }
+          if (p.aux_resid) {
+            const uint8_t* rrow = rowp + Cfg::kAuxTileBytes;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 u = *reinterpret_cast<const uint4*>(rrow + (((cbase + q) ^ (r & 7)) << 4));
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[q * 8 + j * 2] += __uint_as_float(w[j] << 16);
+                v[q * 8 + j * 2 + 1] += __uint_as_float(w[j] & 0xffff0000u);
+              }
+            }
+          }
+        } else if (!AUX && si == 0 && row_ok) {
           if (p.gate != nullptr) {
             const __nv_bfloat16* g = p.gate + static_cast<long long>(b) * p.g_b + static_cast<long long>(o) * p.g_o +
                                      static_cast<long long>(n) * p.g_n + static_cast<long long>(col_local) * p.g_col;
@@ -341,13 +445,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         epi_store_chunk(sg, row_off, col_local, v, row_ok);
       }
+      if (!ok) break;
+      if (AUX) {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&aux_empty[tile_iter & 1]);
+      }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&tmem_empty[acc]);
+      if (threadIdx.x == 64) KFB_GSTAMP(4 + tile_iter * 4 + 1);
     }
+    if (lane == 0) ptx::tma_store_wait_all();
   }
 
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) KFB_GSTAMP(1);
+#undef KFB_GSTAMP
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -368,7 +481,13 @@ struct GemmOperandB {  // B[(b), col, k]
 
 // Fills the tile bookkeeping of `p`, builds the tensor maps and launches on `stream`.
 // `tag` names the launch in the profile report (a string literal).
+// A segment whose rows are contiguous along n (s_n == 1) and whose other strides and base are 16-byte
+// aligned can go through the TMA-store path; the launcher decides and fills `tma_slot`.
 int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOperandB& b, GemmParams p, int force_bn = 0,
                      const char* tag = "gemm");
+
+// Debugging aid: launches whose tag equals `tag` store per-tile clock stamps of CTA 0 into `device_buffer`
+// (>= 512 long longs); nullptr switches it off.
+void set_gemm_trace(long long* device_buffer, const char* tag);
 
 }  // namespace kfb

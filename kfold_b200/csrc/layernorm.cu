@@ -130,72 +130,90 @@ int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w
 }
 
 // ------------------------------------------------------------------------------------------------
-// Channel-major in, position-major out.  A block stages a [c][64 positions] slab in shared memory
-// (row pitch 65 floats, so the per-position column reads below are bank-conflict free), then each
-// warp normalises 8 positions.
+// Channel-major in, position-major out.  A block of 128 threads stages a [c][128 positions] slab in shared
+// memory as bf16 (each warp copies whole channel rows: 256 contiguous bytes per row), then every thread
+// owns ONE position: it walks down its column of the slab (neighbouring lanes read neighbouring 2-byte
+// cells, so the column walk is bank-conflict free), takes mean and variance in two passes and writes its
+// normalised row of c channels with 16-byte stores.
 // ------------------------------------------------------------------------------------------------
-static constexpr int kCmPos = 64;
+static constexpr int kCmPos = 128;
+
+__device__ __forceinline__ float cm_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float cm_to_float(float v) { return v; }
+__device__ __forceinline__ uint32_t cm_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
 template <typename TI>
-__global__ void __launch_bounds__(256) layernorm_cm_kernel(const TI* __restrict__ t, __nv_bfloat16* __restrict__ y,
-                                                           const float* __restrict__ w, const float* __restrict__ b,
-                                                           long long npos, int c, long long chan_stride,
-                                                           long long batch_stride, float eps, int blocks_per_batch) {
-  extern __shared__ float slab[];  // [c][65]
+__global__ void __launch_bounds__(kCmPos) layernorm_cm_kernel(const TI* __restrict__ t, __nv_bfloat16* __restrict__ y,
+                                                              const float* __restrict__ w, const float* __restrict__ b,
+                                                              long long npos, int c, long long chan_stride,
+                                                              long long batch_stride, float eps, int blocks_per_batch) {
+  extern __shared__ __align__(16) unsigned char slab_raw[];
+  __nv_bfloat16* slab = reinterpret_cast<__nv_bfloat16*>(slab_raw);  // [c][128]
   const int batch = blockIdx.x / blocks_per_batch;
   const long long p0 = static_cast<long long>(blockIdx.x % blocks_per_batch) * kCmPos;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const TI* tb = t + batch * batch_stride;
-  for (int ch = warp; ch < c; ch += 8) {
-    const long long p = p0 + lane * 2;
-    float2 v = make_float2(0.f, 0.f);
-    if (p + 1 < npos) v = load2<TI>(tb + ch * chan_stride + p);
-    else if (p < npos) v.x = static_cast<float>(tb[ch * chan_stride + p]);
-    slab[ch * 65 + lane * 2] = v.x;
-    slab[ch * 65 + lane * 2 + 1] = v.y;
+  const TI* tb = t + batch * batch_stride + p0;
+  const bool full = (p0 + kCmPos <= npos) && ((chan_stride & 3) == 0) && ((reinterpret_cast<uintptr_t>(tb) & 7) == 0);
+  for (int ch = warp; ch < c; ch += kCmPos / 32) {
+    const TI* src = tb + ch * chan_stride + lane * 4;
+    __nv_bfloat16* dst = slab + ch * kCmPos + lane * 4;
+    if (full && sizeof(TI) == 2) {
+      *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        dst[i] = (p0 + lane * 4 + i < npos) ? __float2bfloat16_rn(cm_to_float(src[i])) : __float2bfloat16_rn(0.f);
+    }
   }
   __syncthreads();
-  for (int pp = warp; pp < kCmPos; pp += 8) {
-    const long long p = p0 + pp;
-    if (p >= npos) break;
-    float s = 0.f;
-    for (int ch = lane; ch < c; ch += 32) s += slab[ch * 65 + pp];
-    const float mean = warp_sum(s) / static_cast<float>(c);
-    float q = 0.f;
-    for (int ch = lane; ch < c; ch += 32) {
-      const float d = slab[ch * 65 + pp] - mean;
-      q += d * d;
+  const long long p = p0 + threadIdx.x;
+  if (p >= npos) return;
+  const __nv_bfloat16* col = slab + threadIdx.x;
+  float s = 0.f;
+#pragma unroll 8
+  for (int ch = 0; ch < c; ++ch) s += __bfloat162float(col[ch * kCmPos]);
+  const float mean = s / static_cast<float>(c);
+  float q = 0.f;
+#pragma unroll 8
+  for (int ch = 0; ch < c; ++ch) {
+    const float d = __bfloat162float(col[ch * kCmPos]) - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(q / static_cast<float>(c) + eps);
+  __nv_bfloat16* yr = y + (static_cast<long long>(batch) * npos + p) * c;
+  for (int ch = 0; ch < c; ch += 8) {
+    float a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] = (__bfloat162float(col[(ch + i) * kCmPos]) - mean) * rstd;
+      if (w != nullptr) a[i] *= w[ch + i];
+      if (b != nullptr) a[i] += b[ch + i];
     }
-    const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
-    __nv_bfloat16* yr = y + (static_cast<long long>(batch) * npos + p) * c;
-    for (int ch = lane * 2; ch < c; ch += 64) {
-      float a0 = (slab[ch * 65 + pp] - mean) * rstd;
-      float a1 = (slab[(ch + 1) * 65 + pp] - mean) * rstd;
-      if (w != nullptr) { a0 *= w[ch]; a1 *= w[ch + 1]; }
-      if (b != nullptr) { a0 += b[ch]; a1 += b[ch + 1]; }
-      *reinterpret_cast<__nv_bfloat162*>(yr + ch) = __floats2bfloat162_rn(a0, a1);
-    }
+    *reinterpret_cast<uint4*>(yr + ch) = make_uint4(cm_pack(a[0], a[1]), cm_pack(a[2], a[3]), cm_pack(a[4], a[5]), cm_pack(a[6], a[7]));
   }
 }
 
 int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, const float* w, const float* b, int batch,
                         long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype) {
-  KFB_CHECK_ARG(c > 0 && c % 2 == 0 && c <= 512, "layernorm_cm: channels %d", c);
-  KFB_CHECK_ARG(chan_stride % 2 == 0 && batch_stride % 2 == 0, "layernorm_cm: strides must be even");
+  KFB_CHECK_ARG(c > 0 && c % 8 == 0 && c <= 512, "layernorm_cm: channels %d (multiple of 8, at most 512)", c);
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(y) & 15) == 0, "layernorm_cm: output must be 16-byte aligned");
   if (npos == 0 || batch == 0) return KFB_OK;
   const int bpb = static_cast<int>((npos + kCmPos - 1) / kCmPos);
-  const size_t smem = static_cast<size_t>(c) * 65 * sizeof(float);
+  const size_t smem = static_cast<size_t>(c) * kCmPos * sizeof(__nv_bfloat16);
   LaunchScope scope(stream, "layernorm_cm");
   if (in_dtype == KFB_BF16) {
     if (smem > 48 * 1024)
       KFB_CUDA(cudaFuncSetAttribute(layernorm_cm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    layernorm_cm_kernel<__nv_bfloat16><<<bpb * batch, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(t), y, w, b, npos,
-                                                                        c, chan_stride, batch_stride, eps, bpb);
+    layernorm_cm_kernel<__nv_bfloat16><<<bpb * batch, kCmPos, smem, stream>>>(static_cast<const __nv_bfloat16*>(t), y, w, b, npos,
+                                                                           c, chan_stride, batch_stride, eps, bpb);
   } else {
     if (smem > 48 * 1024)
       KFB_CUDA(cudaFuncSetAttribute(layernorm_cm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    layernorm_cm_kernel<float><<<bpb * batch, 256, smem, stream>>>(static_cast<const float*>(t), y, w, b, npos, c, chan_stride,
-                                                                batch_stride, eps, bpb);
+    layernorm_cm_kernel<float><<<bpb * batch, kCmPos, smem, stream>>>(static_cast<const float*>(t), y, w, b, npos, c, chan_stride,
+                                                                   batch_stride, eps, bpb);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
