@@ -130,13 +130,39 @@ KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_
  *   w_proj_packed : bf16 [4*heads*dp, c] = [Wq/sqrt(d) | Wk | Wg | Wv], heads padded to dp;
  *   proj_bias : fp32 [4*heads*dp] (scaled q bias in the first quarter) or NULL;
  *   w_out : bf16 [c, c];  out_bias : fp32 [c] or NULL;  out : (batch, l, c) of `out_dtype`;
+ *   out_gate : NULL, or bf16 logits (batch / gate_share, l, c): out *= sigmoid(out_gate) -- the AdaLN-Zero output
+ *   gate sigmoid(Linear(s)) of SelfAttentionPairBias.forward (src/kfold/model/layers/folding/
+ *   attention_pair_bias.py:155-157), shared by `gate_share` consecutive batch entries;
  *   resid : NULL or a tensor like out that is added.
  */
 KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads);
 KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
-                        const float* proj_bias, const void* w_out, const float* out_bias, void* out, const void* resid,
-                        void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_div,
-                        int out_dtype, void* stream);
+                        const float* proj_bias, const void* w_out, const float* out_bias, const void* out_gate,
+                        int gate_share, void* out, const void* resid, void* workspace, size_t workspace_bytes, int batch,
+                        int l, int c, int heads, int bias_div, int out_dtype, void* stream);
+
+/*
+ * Adaptive LayerNorm: out = sigmoid(g) * LayerNorm(a) + v, LayerNorm without affine (fp32 statistics).
+ * Replaces the last line of AdaLN.forward (src/kfold/model/primitives/normalization.py:117-125); the two
+ * small projections of the conditioning, g = Linear(LN_s(s)) and v = LinearNoBias(LN_s(s)), are computed by
+ * the caller (kfb_layernorm + kfb_gemm_bf16) once per token and passed as `gate_shift`: bf16 [rows / samples, 2c]
+ * (logits g, then v).  a : (rows, c) of `in_dtype`, rows ordered (group, sample, position) with `l` positions;
+ * the `samples` diffusion samples of a group share one conditioning row per position.  out : bf16 (rows, c).
+ */
+KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, void* out, long long rows, int c, int samples, int l,
+                          float eps, int in_dtype, void* stream);
+
+/*
+ * Conditioned transition: out = sigmoid(gate) * Linear_out(silu(u_a) * u_b) (+ resid), [u_a, u_b] = Linear(x).
+ * Replaces lines 2-3 of ConditionedTransitionBlock.forward
+ * (src/kfold/model/layers/folding/diffusion_transformer.py:73-81); x is the AdaLN output (kfb_adaln_fwd),
+ * out_gate : bf16 logits [rows / samples, c] = Linear(s) + bias, shared by the samples of a group.
+ */
+KFB_API size_t kfb_cond_transition_workspace_bytes(long long rows, int hidden);
+KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_packed, const void* w_out,
+                                    const void* out_gate, void* out, const void* resid, void* workspace,
+                                    size_t workspace_bytes, long long rows, int c, int hidden, int samples, int l, int dtype,
+                                    void* stream);
 
 /*
  * Transition: out = Linear_out(silu(u_a) * u_b), [u_a, u_b] = Linear(LayerNorm(x))  (+ resid).

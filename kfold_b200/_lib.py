@@ -38,8 +38,11 @@ _SIGNATURES = {
                        c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_triatt_fwd": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        ctypes.c_size_t, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                    ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                    c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_adaln_fwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_cond_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
+                                c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t,
                            c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_pair_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int,
@@ -48,6 +51,7 @@ _SIGNATURES = {
                                   c_float, c_int, c_void_p],
 }
 _SIZE_FUNCS = {
+    "kfb_cond_transition_workspace_bytes": [c_ll, c_int],
     "kfb_transition_static_max_bytes": [],
     "kfb_pair_bias_workspace_bytes": [c_int, c_int, c_int],
     "kfb_transition_workspace_bytes": [c_ll, c_int, c_int],

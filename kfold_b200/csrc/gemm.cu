@@ -105,9 +105,11 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
     const EpiSeg& sg = p.seg[0];
     bool ok_g = true, ok_r = true;
     if (p.gate != nullptr)
-      ok_g = p.g_col == 1 && (reinterpret_cast<uintptr_t>(p.gate) & 15) == 0 && p.g_n % 8 == 0 && p.g_o % 8 == 0 && p.g_b % 8 == 0;
+      ok_g = p.g_col == 1 && (reinterpret_cast<uintptr_t>(p.gate) & 15) == 0 && p.g_n % 8 == 0 && p.g_n != 0 &&
+             p.g_o % 8 == 0 && (p.g_o != 0 || p.o_extent == 1) && p.g_b % 8 == 0 && (p.g_b != 0 || p.batch == 1);
     if (p.resid != nullptr)
-      ok_r = !sg.out_fp32 && (reinterpret_cast<uintptr_t>(p.resid) & 15) == 0 && sg.s_n % 8 == 0 && sg.s_o % 8 == 0 && sg.s_b % 8 == 0;
+      ok_r = !sg.out_fp32 && (reinterpret_cast<uintptr_t>(p.resid) & 15) == 0 && sg.s_n % 8 == 0 && sg.s_o % 8 == 0 &&
+             (sg.s_o != 0 || p.o_extent == 1) && sg.s_b % 8 == 0 && (sg.s_b != 0 || p.batch == 1);
     if (ok_g && ok_r) {
       const uint32_t box[4] = {64, kBM, 1, 1};
       const uint64_t dims[4] = {(uint64_t)p.n_cols, (uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)p.batch};

@@ -130,6 +130,93 @@ int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w
 }
 
 // ------------------------------------------------------------------------------------------------
+// Adaptive LayerNorm (AdaLN): one warp per row, same register layout as layernorm_rows_kernel.
+// ------------------------------------------------------------------------------------------------
+template <typename TI, typename TO, int G>
+__global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ a, TO* __restrict__ y,
+                                                         const __nv_bfloat16* __restrict__ gv, long long rows, int c,
+                                                         int samples, int l, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warps_per_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += warps_per_grid) {
+    const TI* xr = a + row * c;
+    const long long srow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
+    const __nv_bfloat16* gr = gv + srow * 2 * c;
+    float2 v[G];
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int ch = (lane + 32 * g) * 2;
+      v[g] = ch < c ? load2<TI>(xr + ch) : make_float2(0.f, 0.f);
+      s += v[g].x + v[g].y;
+    }
+    const float mean = warp_sum(s) / static_cast<float>(c);
+    float q = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int ch = (lane + 32 * g) * 2;
+      if (ch < c) {
+        v[g].x -= mean;
+        v[g].y -= mean;
+        q += v[g].x * v[g].x + v[g].y * v[g].y;
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
+    TO* yr = y + row * c;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int ch = (lane + 32 * g) * 2;
+      if (ch < c) {
+        const float2 gate = load2<__nv_bfloat16>(gr + ch);
+        const float2 shift = load2<__nv_bfloat16>(gr + c + ch);
+        const float s0 = 1.f / (1.f + __expf(-gate.x)), s1 = 1.f / (1.f + __expf(-gate.y));
+        store2<TO>(yr + ch, s0 * (v[g].x * rstd) + shift.x, s1 * (v[g].y * rstd) + shift.y);
+      }
+    }
+  }
+}
+
+template <typename TI, typename TO>
+static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const __nv_bfloat16* gv, long long rows, int c,
+                          int samples, int l, float eps) {
+  const int warps = 8;
+  long long blocks = (rows + warps - 1) / warps;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  const int g = cdiv(c, 64);
+  LaunchScope scope(stream, "adaln_rows");
+#define KFB_ADALN(GG)                                                                                          \
+  adaln_rows_kernel<TI, TO, GG><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(                      \
+      static_cast<const TI*>(a), static_cast<TO*>(y), gv, rows, c, samples, l, eps)
+  if (g <= 2) KFB_ADALN(2);
+  else if (g <= 6) KFB_ADALN(6);
+  else if (g <= 12) KFB_ADALN(12);
+  else if (g <= 16) KFB_ADALN(16);
+  else {
+    set_error("adaln: channel count %d above 1024 is not supported", c);
+    return KFB_ERR_UNSUPPORTED;
+  }
+#undef KFB_ADALN
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+int launch_adaln(cudaStream_t stream, const void* a, void* y, const __nv_bfloat16* gv, long long rows, int c, int samples,
+                 int l, float eps, int in_dtype, int out_dtype) {
+  KFB_CHECK_ARG(rows >= 0 && c > 0 && c % 2 == 0 && samples >= 1 && l >= 1, "adaln: rows %lld c %d samples %d l %d", rows, c,
+                samples, l);
+  KFB_CHECK_ARG(rows % (static_cast<long long>(samples) * l) == 0, "adaln: rows %lld is not a multiple of samples*l", rows);
+  if (rows == 0) return KFB_OK;
+  if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16)
+    return adaln_dispatch<__nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+  if (in_dtype == KFB_FP32 && out_dtype == KFB_BF16)
+    return adaln_dispatch<float, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+  set_error("adaln: unsupported dtype combination");
+  return KFB_ERR_INVALID_ARGUMENT;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Channel-major in, position-major out.  A block of 128 threads stages a [c][128 positions] slab in shared
 // memory as bf16 (each warp copies whole channel rows: 256 contiguous bytes per row), then every thread
 // owns ONE position: it walks down its column of the slab (neighbouring lanes read neighbouring 2-byte

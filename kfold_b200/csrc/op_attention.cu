@@ -196,14 +196,18 @@ KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads) {
 }
 
 KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
-                        const float* proj_bias, const void* w_out, const float* out_bias, void* out, const void* resid,
-                        void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_div,
-                        int out_dtype, void* stream_) {
+                        const float* proj_bias, const void* w_out, const float* out_bias, const void* out_gate,
+                        int gate_share, void* out, const void* resid, void* workspace, size_t workspace_bytes, int batch,
+                        int l, int c, int heads, int bias_div, int out_dtype, void* stream_) {
   KFB_CHECK_ARG(x && pair_bias && mask && w_proj_packed && w_out && out && workspace, "apb: null pointer");
   KFB_CHECK_ARG(is_dtype(out_dtype), "apb: bad dtype %d", out_dtype);
   KFB_CHECK_ARG(batch >= 1 && l >= 8 && l % 8 == 0, "apb: L=%d must be a positive multiple of 8 (pad in the caller)", l);
   KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "apb: c=%d heads=%d", c, heads);
   KFB_CHECK_ARG(bias_div >= 1 && batch % bias_div == 0, "apb: batch %d not a multiple of bias_div %d", batch, bias_div);
+  if (out_gate != nullptr)
+    KFB_CHECK_ARG(gate_share >= 1 && batch % gate_share == 0, "apb: batch %d not a multiple of gate_share %d", batch, gate_share);
+  else
+    gate_share = 1;
   const int d = c / heads;
   KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "apb: head dim %d not in {16, 24, ..., 64}", d);
   const int dp = dpad_of(d), hdp = heads * dp;
@@ -257,17 +261,26 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     KFB_TRY(launch_attention(stream, p));
   }
   {
+    // rows walked as (group, member, position): `gate_share` consecutive batch entries share one gate row set
     GemmParams p = {};
-    p.n_extent = batch * l;
-    p.o_extent = 1;
-    p.batch = 1;
+    p.n_extent = l;
+    p.o_extent = gate_share;
+    p.batch = batch / gate_share;
     p.n_cols = c;
     p.k_extent = c;
     p.nseg = 1;
-    p.seg[0] = row_major_seg(out, c, c, 0, 0, out_dtype == KFB_FP32);
+    const long long lc = static_cast<long long>(l) * c;
+    p.seg[0] = row_major_seg(out, c, c, lc, lc * gate_share, out_dtype == KFB_FP32);
     p.col_bias = out_bias;
     p.resid = resid;
-    GemmOperandA a = {w.og, c, 0, 0};
+    if (out_gate != nullptr) {
+      p.gate = static_cast<const __nv_bfloat16*>(out_gate);
+      p.g_col = 1;
+      p.g_n = c;
+      p.g_o = 0;
+      p.g_b = lc;
+    }
+    GemmOperandA a = {w.og, c, lc, lc * gate_share};
     GemmOperandB b = {w_out, c, 0};
     KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "apb_out_proj"));
   }

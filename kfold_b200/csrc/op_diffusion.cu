@@ -1,0 +1,77 @@
+// Conditioned (diffusion) variants: adaptive LayerNorm and the conditioned transition block.
+//
+// The conditioning tensor s is shared by the diffusion samples, so everything derived from it (the AdaLN
+// gate / shift, the output gates) is computed once per token by small GEMMs in the caller and passed in as
+// bf16 logits; the kernels here broadcast those rows over the samples.
+#include "ops_common.cuh"
+
+using namespace kfb;
+
+extern "C" {
+
+// y = sigmoid(gv[:, :c]) * LayerNorm(a) + gv[:, c:]
+KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, void* out, long long rows, int c, int samples, int l,
+                          float eps, int in_dtype, void* stream) {
+  KFB_CHECK_ARG(a && gate_shift && out, "adaln: null pointer");
+  KFB_CHECK_ARG(is_dtype(in_dtype), "adaln: bad dtype %d", in_dtype);
+  return launch_adaln(as_stream(stream), a, out, static_cast<const __nv_bfloat16*>(gate_shift), rows, c, samples, l, eps,
+                      in_dtype, KFB_BF16);
+}
+
+KFB_API size_t kfb_cond_transition_workspace_bytes(long long rows, int hidden) {
+  return align_up(static_cast<size_t>(rows) * hidden * sizeof(__nv_bfloat16), 256);
+}
+
+// out = sigmoid(gate[s(r)]) * (silu(u_a) * u_b) W_out^T  (+ resid),  [u_a, u_b] = x W_swiglu^T,  x already AdaLN-normalised
+KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_packed, const void* w_out,
+                                    const void* out_gate, void* out, const void* resid, void* workspace,
+                                    size_t workspace_bytes, long long rows, int c, int hidden, int samples, int l, int dtype,
+                                    void* stream_) {
+  KFB_CHECK_ARG(x_normed && w_swiglu_packed && w_out && out_gate && out && workspace, "cond_transition: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "cond_transition: bad dtype %d", dtype);
+  KFB_CHECK_ARG(rows >= 1 && rows < (1ll << 31) && samples >= 1 && l >= 1 && rows % (static_cast<long long>(samples) * l) == 0,
+                "cond_transition: rows %lld samples %d l %d", rows, samples, l);
+  KFB_CHECK_ARG(c % 8 == 0 && hidden % 128 == 0, "cond_transition: c=%d (multiple of 8), hidden=%d (multiple of 128)", c, hidden);
+  KFB_CHECK_ARG(workspace_bytes >= kfb_cond_transition_workspace_bytes(rows, hidden), "cond_transition: workspace too small");
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "cond_transition: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  __nv_bfloat16* h = static_cast<__nv_bfloat16*>(workspace);
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(rows);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = 2 * hidden;
+    p.k_extent = c;
+    p.glu = GLU_SWIGLU;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(h, hidden, hidden, 0, 0, 0);
+    GemmOperandA a = {x_normed, c, 0, 0};
+    GemmOperandB b = {w_swiglu_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 256, "cond_transition_swiglu"));
+  }
+  {
+    const int groups = static_cast<int>(rows / (static_cast<long long>(samples) * l));
+    GemmParams p = {};
+    p.n_extent = l;
+    p.o_extent = samples;
+    p.batch = groups;
+    p.n_cols = c;
+    p.k_extent = hidden;
+    p.nseg = 1;
+    const long long lc = static_cast<long long>(l) * c, lh = static_cast<long long>(l) * hidden;
+    p.seg[0] = row_major_seg(out, c, c, lc, lc * samples, dtype == KFB_FP32);
+    p.resid = resid;
+    p.gate = static_cast<const __nv_bfloat16*>(out_gate);
+    p.g_col = 1;
+    p.g_n = c;
+    p.g_o = 0;
+    p.g_b = lc;
+    GemmOperandA a = {h, hidden, lh, lh * samples};
+    GemmOperandB b = {w_out, hidden, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "cond_transition_out"));
+  }
+  return KFB_OK;
+}
+
+}  // extern "C"

@@ -123,13 +123,66 @@ def triangle_attention(x: torch.Tensor, mask: torch.Tensor | None, packed: dict,
     return out if npad == n else out[:, :n, :n].contiguous()
 
 
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """y = x w^T (+ bias) on the tensor-core GEMM.  x (..., k) bf16, w (n, k) bf16, bias fp32 (n,) or None."""
+    _require_cuda(x, w)
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.dtype != torch.bfloat16:
+        x2 = x2.to(torch.bfloat16)
+    x2 = x2.contiguous()
+    n = w.shape[0]
+    out = torch.empty(x2.shape[0], n, dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().kfb_gemm_bf16(L.ptr(x2), L.ptr(w), L.ptr(out), L.ptr(bias), 1, x2.shape[0], n, k, k, k, n, 0, 0, 0,
+                                      L.dtype_code(out_dtype), L.stream_ptr()))
+    return out.view(*x.shape[:-1], n)
+
+
+def adaln(a: torch.Tensor, gate_shift: torch.Tensor, samples: int, eps: float = 1e-5) -> torch.Tensor:
+    """sigmoid(g) * LayerNorm(a) + v  (model/primitives/normalization.py:117-125).
+    a (groups * samples, L, c) flattened as rows; gate_shift (groups, L, 2c) bf16 = [g | v]."""
+    _require_cuda(a, gate_shift)
+    c, l = a.shape[-1], a.shape[-2]
+    a2 = a.reshape(-1, c).contiguous()
+    out = torch.empty(a2.shape, dtype=torch.bfloat16, device=a.device)
+    gs = gate_shift.reshape(-1, 2 * c).contiguous()
+    with torch.cuda.device(a.device):
+        L.check(L.lib().kfb_adaln_fwd(L.ptr(a2), L.ptr(gs), L.ptr(out), a2.shape[0], c, samples, l, eps,
+                                      L.dtype_code(a2.dtype), L.stream_ptr()))
+    return out.view(a.shape)
+
+
+def conditioned_transition(x_normed: torch.Tensor, packed: dict, out_gate: torch.Tensor, samples: int,
+                           resid: torch.Tensor | None = None, out_dtype=None) -> torch.Tensor:
+    """sigmoid(gate) * Linear_out(SwiGLU(x)) (+ resid)  (model/layers/folding/diffusion_transformer.py:73-81).
+    x_normed (rows, L, c) bf16 AdaLN output; out_gate (rows / samples, L, c) bf16 logits."""
+    _require_cuda(x_normed, out_gate)
+    c, hidden, l = packed["c"], packed["hidden"], x_normed.shape[-2]
+    x2 = x_normed.reshape(-1, c).contiguous()
+    rows = x2.shape[0]
+    out = torch.empty(rows, c, dtype=out_dtype or (resid.dtype if resid is not None else x_normed.dtype), device=x2.device)
+    r2 = None if resid is None else resid.reshape(-1, c).contiguous()
+    g2 = out_gate.reshape(-1, c).contiguous()
+    lib = L.lib()
+    with torch.cuda.device(x2.device):
+        ws = _workspace(x2.device, lib.kfb_cond_transition_workspace_bytes(rows, hidden))
+        L.check(lib.kfb_cond_transition_fwd(L.ptr(x2), L.ptr(packed["w_swiglu"]), L.ptr(packed["w_out"]), L.ptr(g2), L.ptr(out),
+                                            L.ptr(r2), L.ptr(ws), ws.numel(), rows, c, hidden, samples, l,
+                                            L.dtype_code(out.dtype), L.stream_ptr()))
+    return out.view(x_normed.shape)
+
+
 def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor, packed: dict,
-                        out_dtype=None) -> torch.Tensor:
+                        out_dtype=None, out_gate: torch.Tensor | None = None, gate_share: int = 1,
+                        resid: torch.Tensor | None = None) -> torch.Tensor:
     """Gated self-attention with pair bias on already-normalised inputs
     (model/primitives/attention.py:28-94 with x_q is x_k).
 
     x (*, L, c); pair_bias broadcastable to (*, H, L, L) -- entries that share a bias (the
     diffusion samples) must be adjacent in the flattened batch; mask broadcastable to (*, L).
+    ``out_gate``: bf16 logits (batch / gate_share, L, c), the result is multiplied by their sigmoid (the
+    AdaLN-Zero output gate); ``resid``: tensor like the result that is added (fused residual).
     """
     _require_cuda(x, pair_bias, mask)
     c, heads = x.shape[-1], packed["heads"]
@@ -161,15 +214,27 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
         xb = torch.nn.functional.pad(xb, (0, 0, 0, lp - l))
         pbb = torch.nn.functional.pad(pbb, (0, lp - l, 0, lp - l))
         mb = torch.nn.functional.pad(mb, (0, lp - l))
+    gate = None
+    if out_gate is not None:
+        gate = out_gate.reshape(-1, l, c).to(torch.bfloat16)
+        if lp != l:
+            gate = torch.nn.functional.pad(gate, (0, 0, 0, lp - l))
+        gate = gate.contiguous()
+    res = None
+    if resid is not None:
+        res = resid.reshape(batch, l, c)
+        if lp != l:
+            res = torch.nn.functional.pad(res, (0, 0, 0, lp - l))
+        res = res.contiguous()
     xb, pbb, mb = xb.contiguous(), pbb.contiguous(), mb.contiguous()
-    out = torch.empty(batch, lp, c, dtype=out_dtype or x.dtype, device=x.device)
+    out = torch.empty(batch, lp, c, dtype=out_dtype or (resid.dtype if resid is not None else x.dtype), device=x.device)
     lib = L.lib()
     with torch.cuda.device(x.device):
         ws = _workspace(x.device, lib.kfb_apb_workspace_bytes(batch, lp, c, heads))
         L.check(lib.kfb_apb_fwd(L.ptr(xb), L.ptr(pbb), L.ptr(mb.view(torch.uint8)), L.ptr(packed["w_proj"]),
-                                L.ptr(packed["proj_bias"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(out),
-                                None, L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div, L.dtype_code(out.dtype),
-                                L.stream_ptr()))
+                                L.ptr(packed["proj_bias"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
+                                gate_share, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div,
+                                L.dtype_code(out.dtype), L.stream_ptr()))
     return out[:, :l].reshape(*lead, l, c)
 
 

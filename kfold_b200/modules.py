@@ -31,7 +31,8 @@ __all__ = [
     "LayerNorm", "LinearNoBias", "Linear",
     "TriangleMultiplicationOutgoing", "TriangleMultiplicationIncoming",
     "TriangleAttentionStartingNode", "TriangleAttentionEndingNode",
-    "Transition", "SelfAttentionPairBias", "TriangularBlock", "PairformerBlock",
+    "Transition", "AdaLN", "SelfAttentionPairBias", "ConditionedTransitionBlock", "CachedGlobalTransformerBlock",
+    "CachedGlobalTransformerStack", "TriangularBlock", "PairformerBlock",
 ]
 
 
@@ -220,40 +221,169 @@ class Transition(nn.Module, _PackedMixin):
         return out.to(x.dtype)
 
 
+class AdaLN(nn.Module, _PackedMixin):
+    """Adaptive LayerNorm (model/primitives/normalization.py:94-125)."""
+
+    def __init__(self, channel_a: int, channel_s: int):
+        super().__init__()
+        self.channel_a, self.channel_s = channel_a, channel_s
+        self.layernorm_s = LayerNorm(channel_s, create_scale=True, create_offset=False)
+        self.linear_g = Linear(channel_s, channel_a)
+        self.linear_bias = LinearNoBias(channel_s, channel_a)
+
+    def gate_shift(self, s: torch.Tensor) -> torch.Tensor:
+        """[sigmoid logits | shift] of the conditioning, bf16 (..., L, 2 c_a): one small LayerNorm + GEMM per token."""
+        pk = self._packed(s.device, torch.bfloat16, packing.pack_adaln)
+        sn = F.layer_norm(s, pk["ln_s_w"], None, self.layernorm_s.eps, out_dtype=torch.bfloat16)
+        return F.linear(sn, pk["w_gs"], pk["b_gs"])
+
+    @torch.compiler.disable
+    def forward(self, a: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+        """a (B, Ns, L, c_a), s (B, 1 or Ns, L, c_s) -> bf16 (B, Ns, L, c_a)."""
+        _check_inference(a)
+        with torch.autocast(a.device.type, enabled=False):
+            samples = _sample_share(a, s)
+            return F.adaln(a, self.gate_shift(s), samples)
+
+
+def _sample_share(a: torch.Tensor, s: torch.Tensor) -> int:
+    """How many consecutive samples of `a` share one conditioning row of `s` (its sample dim is 1 or equal)."""
+    if a.dim() < 3 or s.dim() != a.dim():
+        return 1
+    if s.shape[-3] == 1 and a.shape[-3] != 1:
+        return int(a.shape[-3])
+    return 1
+
+
 class SelfAttentionPairBias(nn.Module, _PackedMixin):
-    """Single-track form (``channel_s=None``: LayerNorm prologue, no conditioning)."""
+    """Pair-bias self-attention: the single-track form (``channel_s=None``, LayerNorm prologue) and the diffusion
+    form (AdaLN prologue and the sigmoid(Linear(s)) output gate), model/layers/folding/attention_pair_bias.py:70-158."""
 
     def __init__(self, channel_a: int, num_heads: int, channel_s: int | None, call_site: str, inf: float = 1e9,
                  kernel_backend: str = "b200") -> None:
         super().__init__()
         if call_site not in {"diffusion_global", "confidence"}:
             raise ValueError(f"Unsupported self APB call site: {call_site!r}")
-        if channel_s is not None:
-            raise NotImplementedError("the AdaLN-conditioned (diffusion) form is not available in this build")
         if inf != 1e9:
             raise ValueError("the kernel's key-mask offset is fixed at 1e9 (the reference default)")
         assert channel_a % num_heads == 0
         self.channel_a, self.num_heads, self.head_dim, self.inf = channel_a, num_heads, channel_a // num_heads, inf
-        self.call_site, self.kernel_backend, self.use_single_conditioning = call_site, kernel_backend, False
+        self.call_site, self.kernel_backend = call_site, kernel_backend
+        self.use_single_conditioning = channel_s is not None
         self.linear_q = Linear(channel_a, channel_a)
         self.linear_k = LinearNoBias(channel_a, channel_a)
         self.linear_v = LinearNoBias(channel_a, channel_a)
         self.linear_g = LinearNoBias(channel_a, channel_a)
         self.linear_out = LinearNoBias(channel_a, channel_a)
-        self.layernorm_a = LayerNorm(channel_a, create_offset=True)
+        if self.use_single_conditioning:
+            self.adaln_a = AdaLN(channel_a, channel_s)
+            self.linear_ada_out = Linear(channel_s, channel_a)
+        else:
+            self.layernorm_a = LayerNorm(channel_a, create_offset=True)
+        self._ada_w = None
+        self._ada_key = None
+
+    def _apb_packed(self, device):
+        keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight",
+                "linear_out.weight")
+        return self._packed(device, torch.bfloat16,
+                            lambda sd, dev: packing.pack_apb({k: sd[k] for k in keys}, self.num_heads, dev))
+
+    def _ada_out(self, device):
+        w, b = self.linear_ada_out.weight, self.linear_ada_out.bias
+        key = (device, w.data_ptr(), b.data_ptr(), None if torch.is_inference(w) else (w._version, b._version))
+        if self._ada_key != key:
+            self._ada_w = (w.detach().to(device, torch.bfloat16).contiguous(), b.detach().to(device, torch.float32).contiguous())
+            self._ada_key = key
+        return self._ada_w
 
     @torch.compiler.disable
-    def forward(self, a: torch.Tensor, s: torch.Tensor | None, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
-        """a (...,L,c_a); s must be None; pair_bias (...,H,L,L); mask (...,L) -> (...,L,c_a)."""
-        assert s is None
+    def forward(self, a: torch.Tensor, s: torch.Tensor | None, pair_bias: torch.Tensor, mask: torch.Tensor,
+                residual: bool = False) -> torch.Tensor:
+        """a (...,L,c_a); s (...,L,c_s) or None; pair_bias (...,H,L,L); mask (...,L) -> (...,L,c_a).
+        With ``residual`` the result is a + update (fused into the last kernel)."""
         _check_inference(a)
-        cd = compute_dtype(a)
-        _require_bf16(cd, "SelfAttentionPairBias")
-        pk = self._packed(a.device, cd, lambda sd, dev: packing.pack_apb(sd, self.num_heads, dev))
+        _require_bf16(compute_dtype(a), "SelfAttentionPairBias")
+        pk = self._apb_packed(a.device)
         with torch.autocast(a.device.type, enabled=False):
+            if self.use_single_conditioning:
+                assert s is not None
+                share = _sample_share(a, s)
+                an = F.adaln(a, self.adaln_a.gate_shift(s), share)
+                w_ada, b_ada = self._ada_out(a.device)
+                gate = F.linear(s, w_ada, b_ada)
+                return F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype, out_gate=gate, gate_share=share,
+                                             resid=a if residual else None)
+            assert s is None
             an = F.layer_norm(a, self.layernorm_a.weight, self.layernorm_a.bias, self.layernorm_a.eps, out_dtype=torch.bfloat16)
-            out = F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype)
-        return out
+            return F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype, resid=a if residual else None)
+
+
+class ConditionedTransitionBlock(nn.Module, _PackedMixin):
+    """model/layers/folding/diffusion_transformer.py:45-81."""
+
+    def __init__(self, channel_a: int, channel_s: int, expansion_factor: int = 2):
+        super().__init__()
+        model_dim = int(channel_a * expansion_factor)
+        self.adaln = AdaLN(channel_a, channel_s)
+        self.swiglu = _SwiGLU(channel_a, model_dim)
+        self.linear_g = Linear(channel_s, channel_a)
+        self.linear_out = LinearNoBias(model_dim, channel_a)
+
+    @torch.compiler.disable
+    def forward(self, a: torch.Tensor, s: torch.Tensor, residual: bool = False) -> torch.Tensor:
+        _check_inference(a)
+        _require_bf16(compute_dtype(a), "ConditionedTransitionBlock")
+        pk = self._packed(a.device, torch.bfloat16, packing.pack_cond_transition)
+        with torch.autocast(a.device.type, enabled=False):
+            share = _sample_share(a, s)
+            an = F.adaln(a, self.adaln.gate_shift(s), share)
+            gate = F.linear(s, pk["w_g"], pk["b_g"])
+            return F.conditioned_transition(an, pk, gate, share, resid=a if residual else None, out_dtype=a.dtype)
+
+
+class CachedGlobalTransformerBlock(nn.Module):
+    """model/layers/folding/diffusion_transformer.py:342-413: a += attention(a, s, bias, mask); a += transition(a, s)."""
+
+    def __init__(self, channel_a: int, channel_s: int, num_heads: int, kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend = kernel_backend
+        self.attention = SelfAttentionPairBias(channel_a, num_heads, channel_s, call_site="diffusion_global")
+        self.transition = ConditionedTransitionBlock(channel_a, channel_s)
+
+    def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        a = self.attention(a, s, pair_bias, mask, residual=True)
+        return self.transition(a, s, residual=True)
+
+
+class CachedGlobalTransformerStack(nn.Module):
+    """model/layers/folding/diffusion_transformer.py:260-339.  pair_bias (*, Nblock, H, L, L), as produced by
+    DiffusionStack.get_pair_bias; it is converted to bf16 once per tensor and reused across sampler steps."""
+
+    def __init__(self, channel_a: int, channel_s: int, num_heads: int, num_blocks: int, blocks_per_ckpt=None,
+                 kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend = kernel_backend
+        self.blocks = nn.ModuleList(
+            [CachedGlobalTransformerBlock(channel_a, channel_s, num_heads) for _ in range(num_blocks)])
+        self._bias_cache = None
+        self._bias_key = None
+
+    def _prepared_bias(self, pair_bias: torch.Tensor):
+        key = (pair_bias.data_ptr(), tuple(pair_bias.shape), pair_bias.dtype, pair_bias._version)
+        if self._bias_key != key:
+            # (*, N, H, L, L) -> N tensors (*, H, L, L) bf16, contiguous
+            pb = pair_bias.movedim(-4, 0).to(torch.bfloat16).contiguous()
+            self._bias_cache, self._bias_key = pb, key
+        return self._bias_cache
+
+    @torch.compiler.disable
+    def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        _check_inference(a)
+        pb = self._prepared_bias(pair_bias)
+        for i, blk in enumerate(self.blocks):
+            a = blk(a, s, pb[i], mask)
+        return a
 
 
 # --------------------------------------------------------------------------------------------
@@ -323,6 +453,6 @@ class PairformerBlock(nn.Module):
         z = self.transition_z(z, residual=True)
         with torch.autocast(z.device.type, enabled=False):
             bias = self._pair_bias(z)
-        s = s + self.attention(s, None, bias, mask)
+        s = self.attention(s, None, bias, mask, residual=True)
         s = self.transition(s, residual=True)
         return z, s

@@ -40,6 +40,7 @@ __all__ = [
     "transition",
     "conditioned_transition",
     "pairformer_block",
+    "global_transformer_stack",
     "triangular_block",
     "sub",
 ]
@@ -232,6 +233,20 @@ def conditioned_transition(a, s, w: dict, mode: str = "fp32"):
     h = m.r(F.silu(u1) * u2)
     gate = torch.sigmoid(m.linear(m.r(s.float()), w["linear_g.weight"], w["linear_g.bias"]))
     return m.r(gate * m.linear(h, w["linear_out.weight"]))
+
+
+def global_transformer_stack(a, s, pair_bias, mask, w: dict, num_heads: int, num_blocks: int, mode: str = "fp32"):
+    """``CachedGlobalTransformerStack.forward`` -- model/layers/folding/diffusion_transformer.py:302-339 with the
+    block of :376-413: a += SelfAttentionPairBias(a, s, bias_n, mask); a += ConditionedTransitionBlock(a, s).
+    pair_bias (*, Nblock, H, L, L)."""
+    m = _Mode(mode)
+    a = a.float()
+    for i in range(num_blocks):
+        wb = sub(w, f"blocks.{i}")
+        a = a + self_attention_pair_bias(a, s, pair_bias[..., i, :, :, :].unsqueeze(-4) if pair_bias.dim() == a.dim() + 1
+                                         else pair_bias[..., i, :, :, :], mask, sub(wb, "attention"), num_heads, mode)
+        a = a + conditioned_transition(a, s, sub(wb, "transition"), mode)
+    return a
 
 
 def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):

@@ -38,6 +38,8 @@ CASES = {
     "transition_pair": dict(kind="transition", seed=41, rows=96, c=128, factor=4),
     "transition_single": dict(kind="transition", seed=42, rows=40, c=384, factor=4),
     "cond_transition": dict(kind="cond_transition", seed=43, rows=24, c=768, c_s=384, samples=2),
+    # two blocks of the diffusion token transformer (AdaLN attention + conditioned transition), shared bias over 3 samples
+    "diffusion_stack": dict(kind="diffusion_stack", seed=44, l=24, c=768, c_s=384, heads=16, blocks=2, samples=3, valid=20),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -72,6 +74,16 @@ def build_inputs(name: str) -> dict:
         out["w"] = synth.conditioned_transition_weights(rng, cs["c"], cs["c_s"])
         out["a"] = rng.normal(1, cs["samples"], cs["rows"], cs["c"])
         out["s"] = rng.normal(1, 1, cs["rows"], cs["c_s"])
+    elif kind == "diffusion_stack":
+        w = {}
+        for i in range(cs["blocks"]):
+            w.update(synth._prefixed(f"blocks.{i}.attention", synth.apb_weights(rng, cs["c"], cs["c_s"])))
+            w.update(synth._prefixed(f"blocks.{i}.transition", synth.conditioned_transition_weights(rng, cs["c"], cs["c_s"])))
+        out["w"] = w
+        out["a"] = rng.normal(1, cs["samples"], cs["l"], cs["c"])
+        out["s"] = rng.normal(1, 1, cs["l"], cs["c_s"])
+        out["pair_bias"] = rng.normal(1, cs["blocks"], cs["heads"], cs["l"], cs["l"])
+        out["mask"] = synth.token_mask(cs["l"], cs["valid"]).view(1, 1, cs["l"]).contiguous()
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

@@ -56,6 +56,14 @@ def run_reference(ns, name: str) -> dict:
         import importlib
         dt = importlib.import_module("kfold.model.layers.folding.diffusion_transformer")
         return {"out": _load(dt.ConditionedTransitionBlock(cs["c"], cs["c_s"]), inp["w"])(inp["a"], inp["s"])}
+    if kind == "diffusion_stack":
+        import importlib
+        dt = importlib.import_module("kfold.model.layers.folding.diffusion_transformer")
+        stack = dt.CachedGlobalTransformerStack(cs["c"], cs["c_s"], cs["heads"], cs["blocks"])
+        for blk in stack.blocks:
+            blk.attention.kernel_backend = "torch"      # the oracle path; the constructor hard-codes "sdpa"
+        _load(stack, inp["w"])
+        return {"out": stack(inp["a"].clone(), inp["s"], inp["pair_bias"], inp["mask"])}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "block":

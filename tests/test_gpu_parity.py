@@ -238,6 +238,55 @@ def test_apb_single_track_size(dev):
     _check(mx, r, "apb single track")
 
 
+def test_diffusion_modules_against_reference_golden(dev):
+    """AdaLN-conditioned pair-bias attention, conditioned transition and a 2-block token-transformer stack
+    (bias shared by the diffusion samples) against the reference outputs; fp32 residual stream, bf16 compute."""
+    from kfold_b200 import modules as M
+    to = lambda t: t.to(dev)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        inp = cases.build_inputs("apb_diffusion")
+        mod = M.SelfAttentionPairBias(768, 16, 384, "diffusion_global").to(dev)
+        mod.load_state_dict(inp["w"], strict=True)
+        out = mod(to(inp["a"]), to(inp["s"]), to(inp["pair_bias"]), to(inp["mask"]))
+        assert out.dtype == torch.float32
+        _check(*err_stats(out.cpu(), load_golden("apb_diffusion")["out"]), "apb_diffusion")
+
+        inp = cases.build_inputs("cond_transition")
+        mod = M.ConditionedTransitionBlock(768, 384).to(dev)
+        mod.load_state_dict(inp["w"], strict=True)
+        out = mod(to(inp["a"]), to(inp["s"]))
+        _check(*err_stats(out.cpu(), load_golden("cond_transition")["out"]), "cond_transition")
+
+        inp = cases.build_inputs("diffusion_stack")
+        stack = M.CachedGlobalTransformerStack(768, 384, 16, 2).to(dev)
+        stack.load_state_dict(inp["w"], strict=True)
+        out = stack(to(inp["a"]), to(inp["s"]), to(inp["pair_bias"]), to(inp["mask"]))
+        _check(*err_stats(out.cpu(), load_golden("diffusion_stack")["out"]), "diffusion_stack")
+
+
+def test_diffusion_stack_config4_shape(dev):
+    """BASELINE config 4's token transformer shape: c=768, 16 heads x 48, L=768, 5 samples sharing the pair bias
+    (2 of the 24 blocks), against the oracle run on the GPU in fp32."""
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    rng = synth._Rng(404)
+    blocks, l, ns = 2, 768, 5
+    w = {}
+    for i in range(blocks):
+        w.update(synth._prefixed(f"blocks.{i}.attention", synth.apb_weights(rng, 768, 384)))
+        w.update(synth._prefixed(f"blocks.{i}.transition", synth.conditioned_transition_weights(rng, 768, 384)))
+    a = rng.normal(1, ns, l, 768)
+    s = rng.normal(1, 1, l, 384)
+    bias = rng.normal(1, blocks, 16, l, l)
+    mask = synth.token_mask(l, pad_frac=0.1).view(1, 1, l)
+    stack = M.CachedGlobalTransformerStack(768, 384, 16, blocks).to(dev)
+    stack.load_state_dict(w, strict=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = stack(a.to(dev), s.to(dev), bias.to(dev), mask.to(dev)).cpu()
+    ref = _oracle_on(dev, O.global_transformer_stack, a, s, bias, mask, w, 16, blocks)
+    _check(*err_stats(out, ref), "diffusion stack L=768 x 5 samples")
+
+
 def test_ragged_and_general_mask_through_module_api(dev):
     """N not a multiple of 8 and a non-separable (B,N,N) mask with batch 3 through the module API."""
     from kfold_b200 import modules as M

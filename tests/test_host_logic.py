@@ -64,6 +64,8 @@ def test_pack_apb_pads_d24_to_32():
     (lambda: M.TriangleAttentionEndingNode(128, 4), lambda r: synth.triatt_weights(r, 128, 4)),
     (lambda: M.Transition(128, 4), lambda r: synth.transition_weights(r, 128, 4)),
     (lambda: M.SelfAttentionPairBias(384, 16, None, "confidence"), lambda r: synth.apb_weights(r, 384, None)),
+    (lambda: M.SelfAttentionPairBias(768, 16, 384, "diffusion_global"), lambda r: synth.apb_weights(r, 768, 384)),
+    (lambda: M.ConditionedTransitionBlock(768, 384), lambda r: synth.conditioned_transition_weights(r, 768, 384)),
 ])
 def test_modules_accept_reference_state_dicts(cls, gen):
     """synth.*_weights are keyed like the reference modules' state_dict(); strict loading must succeed."""
@@ -95,8 +97,6 @@ def test_functional_rejects_cpu_tensors_and_bad_shapes():
 
 
 def test_unsupported_variants_fail_loudly():
-    with pytest.raises(NotImplementedError):
-        M.SelfAttentionPairBias(768, 16, 384, "diffusion_global")
     with pytest.raises(ValueError):
         M.SelfAttentionPairBias(768, 16, None, "somewhere")
 

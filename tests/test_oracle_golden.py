@@ -23,6 +23,9 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
         return {"out": O.transition(inp["x"], w, mode)}
     if kind == "cond_transition":
         return {"out": O.conditioned_transition(inp["a"], inp["s"], w, mode)}
+    if kind == "diffusion_stack":
+        return {"out": O.global_transformer_stack(inp["a"], inp["s"], inp["pair_bias"], inp["mask"], w, cs["heads"],
+                                                  cs["blocks"], mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "block":
