@@ -110,6 +110,43 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
                            size_t workspace_bytes, int batch, int n, int c, int heads, float eps, int dtype, void* stream);
 
 /*
+ * Row-sharded forms (no counterpart in the reference, which never splits a pair tensor across GPUs; they are
+ * the two halves of the functions above, cut where the collective goes).  A rank holds `rows` of the n pair
+ * rows as x (rows, n, c).
+ *   kfb_trimul_project : LayerNorm + gated input projection (if w_in_packed) -> ab_out bf16 [2c][rows][n]
+ *                        (operand a = first c channels, b = last c), + output-gate logits (if w_gout)
+ *                        -> gl_out bf16 [rows*n][c].  xn_scratch: bf16 [rows*n][c].
+ *   (the caller all-gathers operand b: every rank's [c][rows][n] piece, rank after rank)
+ *   kfb_trimul_finish  : contraction of the local a rows against all rows of b, LayerNorm_out, gated output
+ *                        projection (+ resid).  b_gathered: pieces of b_piece_rows rows, b_piece_stride elements
+ *                        apart.  t_scratch / tn_scratch: bf16 [c*rows*n] each.  out/resid: (rows, n, c).
+ * The incoming direction is the same pair of calls with ab taken from the TRANSPOSED shard (the caller
+ * transposes z across ranks with an all-to-all) and gl / resid from the row shard.
+ *   kfb_triatt_project : LayerNorm + projection -> qkg_out bf16 [rows*n][3*heads*dp], vt_out bf16
+ *                        [rows][heads*dp][n], bias_out bf16 [heads][rows][n] (the caller all-gathers it per head
+ *                        into [heads][n][n]).
+ *   kfb_triatt_finish  : attention of the local rows against the full bias, output projection (+ resid).
+ *                        mask: (rows, n) bytes; og_scratch: bf16 [rows*n][c].
+ *   kfb_pair_bias_rows_fwd : kfb_pair_bias_fwd on a shard: z (rows, n, c) -> bf16 [heads][rows][n].
+ */
+KFB_API int kfb_trimul_project(const void* x, const unsigned char* mask, const float* ln_in_w, const float* ln_in_b,
+                               const void* w_in_packed, const void* w_gout, void* xn_scratch, void* ab_out, void* gl_out,
+                               int batch, int rows, int n, int c, float eps, int dtype, void* stream);
+KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride,
+                              const void* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout,
+                              void* t_scratch, void* tn_scratch, void* out, const void* resid, int rows, int n, int c,
+                              float eps, int dtype, void* stream);
+KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln_b, const void* w_proj_packed,
+                               void* xn_scratch, void* qkg_out, void* vt_out, void* bias_out, int rows, int n, int c,
+                               int heads, float eps, int dtype, void* stream);
+KFB_API int kfb_pair_bias_rows_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                                   void* workspace, size_t workspace_bytes, int rows, int n, int c, int heads, float eps,
+                                   int dtype, void* stream);
+KFB_API int kfb_triatt_finish(const void* qkg, const void* vt, const void* bias_full, const unsigned char* mask,
+                              const void* w_out, void* og_scratch, void* out, const void* resid, int rows, int n, int c,
+                              int heads, int dtype, void* stream);
+
+/*
  * bias[b, h, i, j] = sum_c LayerNorm(z)[b, i, j, c] * w[h, c], written bf16 as (batch, heads, n, n).
  * Replaces `linear_pair_bias(layernorm_z(z)).movedim(-1, -3)`
  * (src/kfold/model/modules/confidence_head.py:162-163) and DiffusionStack.get_pair_bias

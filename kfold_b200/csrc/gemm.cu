@@ -73,10 +73,16 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
     KFB_TRY(make_tmap(&ta, a.ptr, 2, 4, dims, str, box, 128));
   }
   {
-    const uint64_t dims[3] = {(uint64_t)p.k_extent, (uint64_t)p.n_cols, (uint64_t)(p.b_batched ? p.batch : 1)};
-    const uint64_t str[2] = {(uint64_t)b.s_col * 2, (uint64_t)b.s_b * 2};
-    const uint32_t box[3] = {kBK, (uint32_t)bn, 1};
-    KFB_TRY(make_tmap(&tb, b.ptr, 2, 3, dims, str, box, 128));
+    const int inner = b.col_inner > 0 ? b.col_inner : p.n_cols;
+    if (b.col_inner > 0)
+      KFB_CHECK_ARG(p.n_cols % inner == 0 && inner % bn == 0, "split B operand: %d columns in pieces of %d, tile %d", p.n_cols,
+                    inner, bn);
+    p.b_col_inner = inner;
+    const uint64_t dims[4] = {(uint64_t)p.k_extent, (uint64_t)inner, (uint64_t)(p.n_cols / inner),
+                              (uint64_t)(p.b_batched ? p.batch : 1)};
+    const uint64_t str[3] = {(uint64_t)b.s_col * 2, (uint64_t)b.s_col_hi * 2, (uint64_t)b.s_b * 2};
+    const uint32_t box[4] = {kBK, (uint32_t)bn, 1, 1};
+    KFB_TRY(make_tmap(&tb, b.ptr, 2, 4, dims, str, box, 128));
   }
   // channel-major bf16 segments that satisfy the TMA alignment rules are stored through shared memory
   CUtensorMap tout[2];

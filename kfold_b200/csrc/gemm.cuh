@@ -44,6 +44,8 @@ struct GemmParams {
   int n_cols;                     // GEMM columns (rows of B) before GLU pairing
   int k_extent;
   int b_batched;                  // B carries the batch dimension too
+  int b_col_inner;                // rows of B are addressed as (col / b_col_inner, col % b_col_inner): an all-gathered
+                                  // operand whose pieces lie rank after rank (launcher; = n_cols when not split)
   int n_blocks, num_m_tiles, num_n_tiles;
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
   int nseg;
@@ -206,6 +208,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int o = rest % p.o_extent;
         const int b = rest / p.o_extent;
         const int bb = p.b_batched ? b : 0;
+        const int b_col_hi = (n_tile * BN) / p.b_col_inner;
+        const int b_col_lo = n_tile * BN - b_col_hi * p.b_col_inner;
         if (AUX) {
           // gate / residual tiles of this output tile, one tile ahead of the epilogue
           const uint32_t ti = (tile - blockIdx.x) / gridDim.x;
@@ -226,7 +230,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1, 101)) { ok = false; break; }
           ptx::mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], kb * kBK, nb * kBM, o, b);
-          ptx::tma_load_3d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], kb * kBK, n_tile * BN, bb);
+          ptx::tma_load_4d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], kb * kBK, b_col_lo, b_col_hi, bb);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         KFB_GSTAMP(4 + (tile / gridDim.x) * 4 + 3);
@@ -474,9 +478,11 @@ struct GemmOperandA {  // A[(b,o,n), k], strides in elements
   const void* ptr;
   long long s_n, s_o, s_b;
 };
-struct GemmOperandB {  // B[(b), col, k]
+struct GemmOperandB {  // B[(b), col, k]; optionally col = hi * col_inner + lo with its own stride for hi
   const void* ptr;
   long long s_col, s_b;
+  int col_inner = 0;       // 0: plain rows
+  long long s_col_hi = 0;
 };
 
 // Fills the tile bookkeeping of `p`, builds the tensor maps and launches on `stream`.

@@ -151,12 +151,133 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
   return KFB_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Row-sharded triangle attention (starting-node form on a shard of `rows` of the n pair rows; the ending
+// node is the same on the transposed shard).  "project" is local; the triangle bias it produces covers only
+// the shard's rows [h][rows][n] and the caller all-gathers it per head into [h][n][n]; "finish" runs the
+// attention of the local rows against the full bias and projects the result.
+// ------------------------------------------------------------------------------------------------
+KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln_b, const void* w_proj_packed,
+                               void* xn_scratch, void* qkg_out, void* vt_out, void* bias_out, int rows, int n, int c,
+                               int heads, float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(x && w_proj_packed && xn_scratch && qkg_out && vt_out && bias_out, "triatt_project: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "triatt_project: bad dtype %d", dtype);
+  KFB_CHECK_ARG(rows >= 1 && rows <= n && n >= 8 && n % 8 == 0, "triatt_project: rows=%d N=%d", rows, n);
+  KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "triatt_project: C=%d heads=%d", c, heads);
+  const int d = c / heads;
+  KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "triatt_project: head dim %d not in {16, 24, ..., 64}", d);
+  const int dp = dpad_of(d), hdp = heads * dp;
+  cudaStream_t stream = as_stream(stream_);
+  const long long rn = static_cast<long long>(rows) * n;
+  __nv_bfloat16* xn = static_cast<__nv_bfloat16*>(xn_scratch);
+  KFB_TRY(launch_layernorm(stream, x, xn, ln_w, ln_b, rn, c, c, c, eps, dtype, KFB_BF16));
+  GemmParams p = {};
+  p.n_extent = n;
+  p.o_extent = rows;
+  p.batch = 1;
+  p.n_cols = 4 * hdp + 32;
+  p.k_extent = c;
+  p.nseg = 3;
+  p.seg[0] = row_major_seg(qkg_out, 3 * hdp, 3 * hdp, static_cast<long long>(n) * 3 * hdp, 0, 0, 0);
+  EpiSeg& sv = p.seg[1];
+  sv = {};
+  sv.col_begin = 3 * hdp;
+  sv.ncols = hdp;
+  sv.dst = vt_out;
+  sv.s_col = n;
+  sv.s_n = 1;
+  sv.s_o = static_cast<long long>(hdp) * n;
+  EpiSeg& sb = p.seg[2];
+  sb = {};
+  sb.col_begin = 4 * hdp;
+  sb.ncols = heads;
+  sb.dst = bias_out;
+  sb.s_col = rn;
+  sb.s_n = 1;
+  sb.s_o = n;
+  GemmOperandA a = {xn, c, static_cast<long long>(n) * c, 0};
+  GemmOperandB b = {w_proj_packed, c, 0};
+  return launch_gemm_bf16(stream, a, b, p, 128, "triatt_proj");
+}
+
+KFB_API int kfb_triatt_finish(const void* qkg, const void* vt, const void* bias_full, const unsigned char* mask,
+                              const void* w_out, void* og_scratch, void* out, const void* resid, int rows, int n, int c,
+                              int heads, int dtype, void* stream_) {
+  KFB_CHECK_ARG(qkg && vt && bias_full && mask && w_out && og_scratch && out, "triatt_finish: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "triatt_finish: bad dtype %d", dtype);
+  KFB_CHECK_ARG(rows >= 1 && rows <= n && rows <= 65535 && n >= 8 && n % 8 == 0, "triatt_finish: rows=%d N=%d", rows, n);
+  const int d = c / heads;
+  const int dp = dpad_of(d), hdp = heads * dp;
+  cudaStream_t stream = as_stream(stream_);
+  {
+    AttnParams p = {};
+    p.batch = rows;
+    p.heads = heads;
+    p.lq = n;
+    p.lk = n;
+    p.d = d;
+    p.dpad = dp;
+    p.q = qkg; p.ldq = 3 * hdp; p.q_col0 = 0;
+    p.k = qkg; p.ldk = 3 * hdp; p.k_col0 = hdp;
+    p.g = qkg; p.ldg = 3 * hdp; p.g_col0 = 2 * hdp;
+    p.vt = vt; p.ldv = n;
+    p.bias = bias_full; p.ldb = n; p.bias_div = rows;
+    p.mask = mask;
+    p.mask_lo_extent = rows;
+    p.m_hi = 0;
+    p.m_lo = n;
+    p.m_k = 1;
+    p.out = og_scratch; p.ldo = c;
+    p.tag = "triatt_attention";
+    KFB_TRY(launch_attention(stream, p));
+  }
+  GemmParams p = {};
+  p.n_extent = static_cast<int>(static_cast<long long>(rows) * n);
+  p.o_extent = 1;
+  p.batch = 1;
+  p.n_cols = c;
+  p.k_extent = c;
+  p.nseg = 1;
+  p.seg[0] = row_major_seg(out, c, c, 0, 0, dtype == KFB_FP32);
+  p.resid = resid;
+  GemmOperandA a = {og_scratch, c, 0, 0};
+  GemmOperandB b = {w_out, c, 0};
+  return launch_gemm_bf16(stream, a, b, p, 0, "triatt_out_proj");
+}
+
 KFB_API size_t kfb_pair_bias_workspace_bytes(int batch, int n, int c) {
   return align_up(static_cast<size_t>(batch) * n * n * c * sizeof(__nv_bfloat16), 256);
 }
 
 // bias[b][h][i][j] = sum_c LN(z)[b][i][j][c] * W[h][c], stored bf16 head-major; with `transposed` the
-// last two indices are swapped (bias_out[b][h][j][i]), the layout the attention kernel consumes.
+// last two indices are swapped (bias_out[b][h][j][i]).  z is (batch, rows, n, c): square on one GPU,
+// a row shard (rows < n) otherwise.
+static int pair_bias_impl(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                          void* workspace, int batch, int rows, int n, int c, int heads, int transposed, float eps,
+                          int dtype, cudaStream_t stream) {
+  const long long rn = static_cast<long long>(rows) * n;
+  __nv_bfloat16* zn = static_cast<__nv_bfloat16*>(workspace);
+  KFB_TRY(launch_layernorm(stream, z, zn, ln_w, ln_b, rn * batch, c, c, c, eps, dtype, KFB_BF16));
+  GemmParams p = {};
+  p.n_extent = n;
+  p.o_extent = rows;
+  p.batch = batch;
+  p.n_cols = heads;
+  p.k_extent = c;
+  p.nseg = 1;
+  EpiSeg& s = p.seg[0];
+  s.col_begin = 0;
+  s.ncols = heads;
+  s.dst = bias_out;
+  s.s_col = rn;
+  s.s_n = transposed ? rows : 1;
+  s.s_o = transposed ? 1 : n;
+  s.s_b = static_cast<long long>(heads) * rn;
+  GemmOperandA a = {zn, c, static_cast<long long>(n) * c, rn * c};
+  GemmOperandB b = {w, c, 0};
+  return launch_gemm_bf16(stream, a, b, p, 0, "pair_bias_proj");
+}
+
 KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
                               void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, int transposed,
                               float eps, int dtype, void* stream_) {
@@ -166,28 +287,20 @@ KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_
                 batch, n, c, heads);
   KFB_CHECK_ARG(workspace_bytes >= kfb_pair_bias_workspace_bytes(batch, n, c), "pair_bias: workspace too small");
   KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "pair_bias: workspace must be 256-byte aligned");
-  cudaStream_t stream = as_stream(stream_);
-  const long long nn = static_cast<long long>(n) * n;
-  __nv_bfloat16* zn = static_cast<__nv_bfloat16*>(workspace);
-  KFB_TRY(launch_layernorm(stream, z, zn, ln_w, ln_b, nn * batch, c, c, c, eps, dtype, KFB_BF16));
-  GemmParams p = {};
-  p.n_extent = n;
-  p.o_extent = n;
-  p.batch = batch;
-  p.n_cols = heads;
-  p.k_extent = c;
-  p.nseg = 1;
-  EpiSeg& s = p.seg[0];
-  s.col_begin = 0;
-  s.ncols = heads;
-  s.dst = bias_out;
-  s.s_col = nn;
-  s.s_n = transposed ? n : 1;
-  s.s_o = transposed ? 1 : n;
-  s.s_b = static_cast<long long>(heads) * nn;
-  GemmOperandA a = {zn, c, static_cast<long long>(n) * c, nn * c};
-  GemmOperandB b = {w, c, 0};
-  return launch_gemm_bf16(stream, a, b, p, 0, "pair_bias_proj");
+  return pair_bias_impl(z, ln_w, ln_b, w, bias_out, workspace, batch, n, n, c, heads, transposed, eps, dtype, as_stream(stream_));
+}
+
+// Row-shard form: z (rows, n, c) -> bias_out bf16 [heads][rows][n].  workspace: rows*n*c bf16.
+KFB_API int kfb_pair_bias_rows_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                                   void* workspace, size_t workspace_bytes, int rows, int n, int c, int heads, float eps,
+                                   int dtype, void* stream_) {
+  KFB_CHECK_ARG(z && w && bias_out && workspace, "pair_bias_rows: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "pair_bias_rows: bad dtype %d", dtype);
+  KFB_CHECK_ARG(rows >= 1 && rows <= n && n >= 8 && n % 8 == 0 && c % 8 == 0 && heads >= 1,
+                "pair_bias_rows: rows %d n %d c %d heads %d", rows, n, c, heads);
+  KFB_CHECK_ARG(workspace_bytes >= static_cast<size_t>(rows) * n * c * sizeof(__nv_bfloat16), "pair_bias_rows: workspace too small");
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "pair_bias_rows: workspace must be 256-byte aligned");
+  return pair_bias_impl(z, ln_w, ln_b, w, bias_out, workspace, 1, rows, n, c, heads, 0, eps, dtype, as_stream(stream_));
 }
 
 KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads) {

@@ -1,23 +1,29 @@
 // Triangle multiplication (outgoing / incoming) as a sequence of sm_100a kernels.
 //
+//   phase "project"  (per position, local to a row shard)
 //   1. LayerNorm_in                      x -> xn (bf16, position-major)             [HBM bound]
 //   2. input projection + gate + mask    ab[ch] = (xn Wp^T) * sigmoid(xn Wg^T) * m  [tcgen05 GEMM, GLU epilogue,
-//                                        stored CHANNEL-major so each channel is      channel-major store]
-//                                        a dense N x N matrix
+//                                        stored CHANNEL-major so each channel is      channel-major TMA store]
+//                                        a dense rows x N matrix
 //   3. output gate logits                gl = xn Wg_out^T                            [tcgen05 GEMM]
+//   phase "finish"
 //   4. triangle contraction              t[ch] = A_ch * B_ch^T, batch over channels   [tcgen05 batched GEMM]
 //   5. LayerNorm_out, channel-major in   t -> tn (bf16, position-major)             [HBM bound]
 //   6. output projection * sigmoid(gl)   out = (tn Wp_out^T) * sigmoid(gl) (+ resid) [tcgen05 GEMM, gated epilogue]
 //
-// The incoming direction needs t[i,j] = sum_k a[k,i] b[k,j].  Instead of a second,
-// MN-major contraction kernel, step 2 walks the pair tensor transposed (the TMA map
-// of xn swaps its two position strides) so that it writes a^T and b^T; step 4 is
-// then the very same K-major contraction for both directions.
+// The incoming direction needs t[i,j] = sum_k a[k,i] b[k,j].  Instead of a second, MN-major contraction
+// kernel, step 2 walks the pair tensor transposed (the TMA map of xn swaps its two position strides) so that
+// it writes a^T and b^T; step 4 is then the very same K-major contraction for both directions.
+//
+// Row sharding across GPUs: a rank holds `rows` of the n token rows.  "project" runs on the shard, the caller
+// all-gathers the b operand (every rank needs all rows j of b), and "finish" takes the gathered operand in the
+// layout the collective leaves it in: rank after rank, each piece [channel][rows][n].
 #include "ops_common.cuh"
 
 using namespace kfb;
 
 namespace {
+
 struct TrimulWs {
   __nv_bfloat16 *xn, *ab, *gl, *t;
 };
@@ -30,6 +36,115 @@ size_t carve(TrimulWs& w, void* base, int batch, int n, int c) {
   w.t = cv.take<__nv_bfloat16>(pos * c);
   return cv.off;
 }
+
+int check_shape(const char* what, int batch, int rows, int n, int c) {
+  KFB_CHECK_ARG(batch >= 1 && n >= 8 && n % 8 == 0, "%s: N=%d must be a positive multiple of 8 (pad in the caller)", what, n);
+  KFB_CHECK_ARG(rows >= 1 && rows <= n, "%s: rows=%d out of range for N=%d", what, rows, n);
+  KFB_CHECK_ARG(c % 64 == 0 && c >= 64 && c <= 512, "%s: C=%d must be a multiple of 64 in [64, 512]", what, c);
+  return KFB_OK;
+}
+
+// steps 1-3 on a (batch, rows, n, c) tensor.  transposed_walk (square tensors only) writes a^T, b^T.
+int project(cudaStream_t stream, int transposed_walk, const void* x, const unsigned char* mask, const float* ln_w,
+            const float* ln_b, const void* w_in_packed, const void* w_gout, __nv_bfloat16* xn, __nv_bfloat16* ab,
+            __nv_bfloat16* gl, int batch, int rows, int n, int c, float eps, int dtype) {
+  const long long rn = static_cast<long long>(rows) * n;
+  const long long pos = rn * batch;
+  KFB_TRY(launch_layernorm(stream, x, xn, ln_w, ln_b, pos, c, c, c, eps, dtype, KFB_BF16));
+  if (w_in_packed != nullptr) {
+    // ab[ch][b][o][n_]: o = row of the shard, n_ = position inside the row (swapped for the transposed walk)
+    GemmParams p = {};
+    p.n_extent = transposed_walk ? rows : n;
+    p.o_extent = transposed_walk ? n : rows;
+    p.batch = batch;
+    p.n_cols = 4 * c;
+    p.k_extent = c;
+    p.glu = GLU_SIGMOID;
+    p.nseg = 1;
+    EpiSeg& s = p.seg[0];
+    s.col_begin = 0;
+    s.ncols = 2 * c;
+    s.out_fp32 = 0;
+    s.vec = 0;
+    s.dst = ab;
+    s.s_col = pos;
+    s.s_n = 1;
+    s.s_o = p.n_extent;
+    s.s_b = rn;
+    p.rowmask = mask;
+    p.mask_segs = 1;
+    p.m_b = rn;
+    p.m_o = transposed_walk ? 1 : n;
+    p.m_n = transposed_walk ? n : 1;
+    GemmOperandA a = {xn, transposed_walk ? static_cast<long long>(n) * c : c,
+                      transposed_walk ? c : static_cast<long long>(n) * c, rn * c};
+    GemmOperandB b = {w_in_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 256, "trimul_in_proj"));
+  }
+  if (w_gout != nullptr) {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(pos);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(gl, c, c, 0, 0, 0);
+    GemmOperandA a = {xn, c, 0, 0};
+    GemmOperandB b = {w_gout, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_gate_proj"));
+  }
+  return KFB_OK;
+}
+
+// steps 4-6.  a: [c][batch][rows][n]; b: pieces of [c][batch][b_piece_rows][n], `b_piece_stride` elements apart.
+int finish(cudaStream_t stream, const __nv_bfloat16* a, const __nv_bfloat16* b, int b_piece_rows, long long b_piece_stride,
+           const __nv_bfloat16* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout, __nv_bfloat16* t,
+           __nv_bfloat16* tn, void* out, const void* resid, int batch, int rows, int n, int c, float eps, int dtype) {
+  const long long rn = static_cast<long long>(rows) * n;
+  const long long pos = rn * batch;
+  {
+    // t[ch*B+b][i][j] = sum_k A[i][k] B[j][k]
+    GemmParams p = {};
+    p.n_extent = rows;
+    p.o_extent = 1;
+    p.batch = c * batch;
+    p.n_cols = n;
+    p.k_extent = n;
+    p.b_batched = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(t, n, n, 0, rn, 0);
+    GemmOperandA oa = {a, n, 0, rn};
+    GemmOperandB ob = {b, n, static_cast<long long>(b_piece_rows) * n};
+    int force_bn = 0;
+    if (b_piece_rows != n) {
+      ob.col_inner = b_piece_rows;
+      ob.s_col_hi = b_piece_stride;
+      force_bn = b_piece_rows % 256 == 0 ? 256 : (b_piece_rows % 128 == 0 ? 128 : 64);
+    }
+    KFB_TRY(launch_gemm_bf16(stream, oa, ob, p, force_bn, "trimul_contraction"));
+  }
+  KFB_TRY(launch_layernorm_cm(stream, t, tn, ln_out_w, ln_out_b, batch, rn, c, pos, rn, eps, KFB_BF16));
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(pos);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, 0, 0, dtype == KFB_FP32);
+    p.gate = gl;
+    p.g_col = 1;
+    p.g_n = c;
+    p.resid = resid;
+    GemmOperandA oa = {tn, c, 0, 0};
+    GemmOperandB ob = {w_pout, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, oa, ob, p, 0, "trimul_out_proj"));
+  }
+  return KFB_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -45,100 +160,44 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
                            int batch, int n, int c, float eps, int dtype, void* stream_) {
   KFB_CHECK_ARG(x && mask && w_in_packed && w_gout && w_pout && out && workspace, "trimul: null pointer");
   KFB_CHECK_ARG(is_dtype(dtype), "trimul: bad dtype %d", dtype);
-  KFB_CHECK_ARG(batch >= 1 && n >= 8 && n % 8 == 0, "trimul: N=%d must be a positive multiple of 8 (pad in the caller)", n);
-  KFB_CHECK_ARG(c % 64 == 0 && c >= 64 && c <= 512, "trimul: C=%d must be a multiple of 64 in [64, 512]", c);
+  KFB_TRY(check_shape("trimul", batch, n, n, c));
   TrimulWs w;
   const size_t need = carve(w, workspace, batch, n, c);
   KFB_CHECK_ARG(workspace_bytes >= need, "trimul: workspace %zu < %zu bytes", workspace_bytes, need);
   KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "trimul: workspace must be 256-byte aligned");
   cudaStream_t stream = as_stream(stream_);
-  const long long nn = static_cast<long long>(n) * n;
-  const long long pos = nn * batch;
+  const long long pos = static_cast<long long>(batch) * n * n;
+  KFB_TRY(project(stream, incoming, x, mask, ln_in_w, ln_in_b, w_in_packed, w_gout, w.xn, w.ab, w.gl, batch, n, n, c, eps, dtype));
+  return finish(stream, w.ab, w.ab + static_cast<long long>(c) * pos, n, 0, w.gl, ln_out_w, ln_out_b, w_pout, w.t, w.xn, out,
+                resid, batch, n, n, c, eps, dtype);
+}
 
-  // 1. LayerNorm_in
-  KFB_TRY(launch_layernorm(stream, x, w.xn, ln_in_w, ln_in_b, pos, c, c, c, eps, dtype, KFB_BF16));
+KFB_API int kfb_trimul_project(const void* x, const unsigned char* mask, const float* ln_in_w, const float* ln_in_b,
+                               const void* w_in_packed, const void* w_gout, void* xn_scratch, void* ab_out, void* gl_out,
+                               int batch, int rows, int n, int c, float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(x && xn_scratch, "trimul_project: null pointer");
+  KFB_CHECK_ARG((w_in_packed == nullptr) == (ab_out == nullptr) && (w_gout == nullptr) == (gl_out == nullptr),
+                "trimul_project: each weight needs its output buffer and vice versa");
+  KFB_CHECK_ARG(w_in_packed == nullptr || mask != nullptr, "trimul_project: the input projection needs the mask");
+  KFB_CHECK_ARG(is_dtype(dtype), "trimul_project: bad dtype %d", dtype);
+  KFB_TRY(check_shape("trimul_project", batch, rows, n, c));
+  return project(as_stream(stream_), 0, x, mask, ln_in_w, ln_in_b, w_in_packed, w_gout, static_cast<__nv_bfloat16*>(xn_scratch),
+                 static_cast<__nv_bfloat16*>(ab_out), static_cast<__nv_bfloat16*>(gl_out), batch, rows, n, c, eps, dtype);
+}
 
-  // 2. input projection, gated, masked, channel-major.  ab[ch][b][o][n]
-  {
-    GemmParams p = {};
-    p.n_extent = n;
-    p.o_extent = n;
-    p.batch = batch;
-    p.n_cols = 4 * c;
-    p.k_extent = c;
-    p.glu = GLU_SIGMOID;
-    p.nseg = 1;
-    EpiSeg& s = p.seg[0];
-    s.col_begin = 0;
-    s.ncols = 2 * c;
-    s.out_fp32 = 0;
-    s.vec = 0;
-    s.dst = w.ab;
-    s.s_col = pos;
-    s.s_n = 1;
-    s.s_o = n;
-    s.s_b = nn;
-    p.rowmask = mask;
-    p.mask_segs = 1;
-    p.m_b = nn;
-    p.m_o = incoming ? 1 : n;
-    p.m_n = incoming ? n : 1;
-    GemmOperandA a = {w.xn, incoming ? static_cast<long long>(n) * c : c, incoming ? c : static_cast<long long>(n) * c,
-                      nn * c};
-    GemmOperandB b = {w_in_packed, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 256, "trimul_in_proj"));
-  }
-  // 3. output gate logits (natural order)
-  {
-    GemmParams p = {};
-    p.n_extent = static_cast<int>(pos);
-    p.o_extent = 1;
-    p.batch = 1;
-    p.n_cols = c;
-    p.k_extent = c;
-    p.nseg = 1;
-    p.seg[0] = row_major_seg(w.gl, c, c, 0, 0, 0);
-    GemmOperandA a = {w.xn, c, 0, 0};
-    GemmOperandB b = {w_gout, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_gate_proj"));
-  }
-  // 4. contraction: t[ch*B+b][i][j] = sum_k A[i][k] B[j][k]
-  {
-    GemmParams p = {};
-    p.n_extent = n;
-    p.o_extent = 1;
-    p.batch = c * batch;
-    p.n_cols = n;
-    p.k_extent = n;
-    p.b_batched = 1;
-    p.nseg = 1;
-    p.seg[0] = row_major_seg(w.t, n, n, 0, nn, 0);
-    GemmOperandA a = {w.ab, n, 0, nn};
-    GemmOperandB b = {w.ab + static_cast<long long>(c) * pos, n, nn};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_contraction"));
-  }
-  // 5. LayerNorm_out: channel-major t -> position-major tn (reuses xn's storage)
-  __nv_bfloat16* tn = w.xn;
-  KFB_TRY(launch_layernorm_cm(stream, w.t, tn, ln_out_w, ln_out_b, batch, nn, c, pos, nn, eps, KFB_BF16));
-  // 6. output projection with sigmoid gate (and optional residual)
-  {
-    GemmParams p = {};
-    p.n_extent = static_cast<int>(pos);
-    p.o_extent = 1;
-    p.batch = 1;
-    p.n_cols = c;
-    p.k_extent = c;
-    p.nseg = 1;
-    p.seg[0] = row_major_seg(out, c, c, 0, 0, dtype == KFB_FP32);
-    p.gate = w.gl;
-    p.g_col = 1;
-    p.g_n = c;
-    p.resid = resid;
-    GemmOperandA a = {tn, c, 0, 0};
-    GemmOperandB b = {w_pout, c, 0};
-    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_out_proj"));
-  }
-  return KFB_OK;
+KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride,
+                              const void* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout,
+                              void* t_scratch, void* tn_scratch, void* out, const void* resid, int rows, int n, int c,
+                              float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(a && b_gathered && gl && w_pout && t_scratch && tn_scratch && out, "trimul_finish: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "trimul_finish: bad dtype %d", dtype);
+  KFB_TRY(check_shape("trimul_finish", 1, rows, n, c));
+  KFB_CHECK_ARG(b_piece_rows >= 64 && n % b_piece_rows == 0 && b_piece_rows % 64 == 0 && b_piece_stride % 8 == 0,
+                "trimul_finish: pieces of %d rows (multiple of 64 dividing N=%d), stride %lld", b_piece_rows, n, b_piece_stride);
+  return finish(as_stream(stream_), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b_gathered),
+                b_piece_rows, b_piece_stride, static_cast<const __nv_bfloat16*>(gl), ln_out_w, ln_out_b, w_pout,
+                static_cast<__nv_bfloat16*>(t_scratch), static_cast<__nv_bfloat16*>(tn_scratch), out, resid, 1, rows, n, c, eps,
+                dtype);
 }
 
 }  // extern "C"

@@ -275,3 +275,18 @@ def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.
         L.check(lib.kfb_pair_bias_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), b, n,
                                       c, heads, 1 if transposed else 0, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
     return out
+
+
+def pair_bias_rows(z_rows: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """pair_bias on a row shard: z_rows (rows, N, C) -> (H, rows, N) bf16."""
+    _require_cuda(z_rows, w)
+    rows, n, c = z_rows.shape
+    heads = w.shape[0]
+    out = torch.empty(heads, rows, n, dtype=torch.bfloat16, device=z_rows.device)
+    zc = z_rows.contiguous()
+    lib = L.lib()
+    with torch.cuda.device(zc.device):
+        ws = _workspace(zc.device, rows * n * c * 2 + 256)
+        L.check(lib.kfb_pair_bias_rows_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), rows,
+                                           n, c, heads, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
+    return out

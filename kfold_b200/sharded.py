@@ -1,0 +1,190 @@
+"""Row-sharded pair track across the GPUs of one node (one process per GPU, torch.distributed / NCCL).
+
+The reference never splits a pair tensor: its multi-GPU mode hands whole complexes to different GPUs
+(src/kfold/cli/multigpu.py:22-77).  For complexes too large or too slow for one GPU this module shards the
+pair representation z (N, N, C) by rows: rank r owns rows [r*N/P, (r+1)*N/P).  Per operator:
+
+  pointwise (LayerNorm, projections, gates, transition, residual)   local
+  triangle multiplication, outgoing   t[i,j] = sum_k a[i,k] b[j,k]    rows i local for a; ALL-GATHER b
+  triangle multiplication, incoming   t[i,j] = sum_k a[k,i] b[k,j]    a, b are taken from the TRANSPOSED shard
+                                      (all-to-all transpose of z), where it is the outgoing form; the
+                                      output gate and the residual use the row shard
+  triangle attention, starting node   rows local; ALL-GATHER of the projected triangle bias only (N*N*H)
+  triangle attention, ending node     starting node on the transposed shard, result transposed back
+  single track / pair bias            bias rows all-gathered per head, single track replicated
+
+Everything here is host-side orchestration: the kernels are the same ones the single-GPU path uses, called
+through the two-phase C entry points (kfb_trimul_project / _finish, kfb_triatt_project / _finish).
+The data movement helpers (`transpose_shard`, `gather_rows`) work on CPU tensors with the gloo backend too,
+which is how they are unit-tested.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import functional as F
+from . import packing
+
+
+def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
+    """[start, stop) of the rows rank `rank` owns; n must divide evenly (pad the complex otherwise)."""
+    if n % world != 0:
+        raise ValueError(f"N={n} is not divisible by the number of ranks {world}")
+    rows = n // world
+    return rank * rows, (rank + 1) * rows
+
+
+def transpose_shard(x_loc: torch.Tensor, group=None) -> torch.Tensor:
+    """Row shard of z -> row shard of z^T with one all-to-all.
+
+    x_loc (rows, N, *tail) holds z[r*rows : (r+1)*rows, :]; the result holds z^T[r*rows : (r+1)*rows, :],
+    i.e. out[i, k] = z[k, r*rows + i].
+    """
+    world = dist.get_world_size(group)
+    rows, n = x_loc.shape[0], x_loc.shape[1]
+    tail = x_loc.shape[2:]
+    if rows * world != n:
+        raise ValueError(f"shard of {rows} rows x {n} columns does not match {world} ranks")
+    # send[q] = the block of my rows that lies in rank q's columns
+    send = x_loc.reshape(rows, world, rows, *tail).transpose(0, 1).contiguous()      # [q][i_loc][j_q]
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    # recv[q][i_q][j_loc] = z[q*rows + i_q, r*rows + j_loc]  ->  out[j_loc][q*rows + i_q]
+    return recv.permute(2, 0, 1, *range(3, recv.dim())).reshape(rows, n, *tail).contiguous()
+
+
+def gather_rows(x_loc: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather along the first dimension: (rows, ...) on every rank -> (world*rows, ...)."""
+    world = dist.get_world_size(group)
+    out = torch.empty((world * x_loc.shape[0],) + tuple(x_loc.shape[1:]), dtype=x_loc.dtype, device=x_loc.device)
+    dist.all_gather_into_tensor(out, x_loc.contiguous(), group=group)
+    return out
+
+
+def _bf16(shape, device):
+    return torch.empty(shape, dtype=torch.bfloat16, device=device)
+
+
+class ShardedPairOps:
+    """The pair-track operators on a row shard.  `group` is the process group whose ranks share one complex."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    # ------------------------------------------------------------------ triangle multiplication
+    def _trimul(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
+        """a, b from (x_ab, mask_ab); gate logits and residual from x_row.  All (rows, N, ...) shards."""
+        rows, n, c = x_row.shape
+        dev = x_row.device
+        lib = L.lib()
+        dt = L.dtype_code(x_row.dtype)
+        xn = _bf16((rows * n, c), dev)
+        ab = _bf16((2 * c, rows, n), dev)
+        gl = _bf16((rows * n, c), dev)
+        m8 = mask_ab.to(torch.bool).contiguous().view(torch.uint8)
+        x_ab = x_ab.contiguous()
+        x_row = x_row.contiguous()
+        with torch.cuda.device(dev):
+            st = L.stream_ptr()
+            same = x_ab.data_ptr() == x_row.data_ptr()
+            L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
+                                           L.ptr(pk["w_gout"]) if same else None, L.ptr(xn), L.ptr(ab),
+                                           L.ptr(gl) if same else None, 1, rows, n, c, eps, dt, st))
+            if not same:
+                L.check(lib.kfb_trimul_project(L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
+                                               L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, eps, dt, st))
+            b_full = gather_rows(ab[c:], self.group)          # [world][c][rows][n]: rank after rank
+            t = _bf16((c, rows, n), dev)
+            out = torch.empty_like(x_row)
+            L.check(lib.kfb_trimul_finish(L.ptr(ab), L.ptr(b_full), rows, c * rows * n, L.ptr(gl), L.ptr(pk["ln_out_w"]),
+                                          L.ptr(pk["ln_out_b"]), L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out),
+                                          L.ptr(x_row), rows, n, c, eps, dt, L.stream_ptr()))
+        return out
+
+    def trimul_outgoing(self, x_loc, mask_loc, pk, eps: float = 1e-5):
+        """x + TriangleMultiplicationOutgoing(x) on the row shard (rows, N, C); mask_loc (rows, N)."""
+        return self._trimul(x_loc, mask_loc, x_loc, pk, eps)
+
+    def trimul_incoming(self, x_loc, mask_loc, pk, eps: float = 1e-5):
+        """x + TriangleMultiplicationIncoming(x): operands from the transposed shard."""
+        xt = transpose_shard(x_loc, self.group)
+        mt = transpose_shard(mask_loc.to(torch.uint8), self.group)
+        return self._trimul(xt, mt, x_loc, pk, eps)
+
+    # ------------------------------------------------------------------ triangle attention
+    def _triatt_start(self, x_loc, mask_loc, pk, eps: float, resid: bool):
+        rows, n, c = x_loc.shape
+        heads = pk["heads"]
+        dp = packing.head_dim_pad(c // heads)
+        hdp = heads * dp
+        dev = x_loc.device
+        lib = L.lib()
+        dt = L.dtype_code(x_loc.dtype)
+        x_loc = x_loc.contiguous()
+        xn = _bf16((rows * n, c), dev)
+        qkg = _bf16((rows * n, 3 * hdp), dev)
+        vt = _bf16((rows, hdp, n), dev)
+        bias_loc = _bf16((heads, rows, n), dev)
+        m8 = mask_loc.to(torch.bool).contiguous().view(torch.uint8)
+        with torch.cuda.device(dev):
+            L.check(lib.kfb_triatt_project(L.ptr(x_loc), L.ptr(pk["ln_w"]), L.ptr(pk["ln_b"]), L.ptr(pk["w_proj"]), L.ptr(xn),
+                                           L.ptr(qkg), L.ptr(vt), L.ptr(bias_loc), rows, n, c, heads, eps, dt, L.stream_ptr()))
+            bias_full = _bf16((heads, n, n), dev)
+            for h in range(heads):   # per head, so that the gathered rows land in their natural [n][n] order
+                dist.all_gather_into_tensor(bias_full[h], bias_loc[h], group=self.group)
+            out = torch.empty_like(x_loc)
+            L.check(lib.kfb_triatt_finish(L.ptr(qkg), L.ptr(vt), L.ptr(bias_full), L.ptr(m8), L.ptr(pk["w_out"]), L.ptr(xn),
+                                          L.ptr(out), L.ptr(x_loc) if resid else None, rows, n, c, heads, dt, L.stream_ptr()))
+        return out
+
+    def triatt_starting(self, x_loc, mask_loc, pk, eps: float = 1e-5):
+        return self._triatt_start(x_loc, mask_loc, pk, eps, resid=True)
+
+    def triatt_ending(self, x_loc, mask_loc, pk, eps: float = 1e-5):
+        xt = transpose_shard(x_loc, self.group)
+        mt = transpose_shard(mask_loc.to(torch.uint8), self.group)
+        upd_t = self._triatt_start(xt, mt, pk, eps, resid=False)
+        return x_loc + transpose_shard(upd_t, self.group)
+
+    # ------------------------------------------------------------------ pair bias for the single track
+    def pair_bias(self, x_loc, ln_w, ln_b, w, eps: float = 1e-5):
+        """(H, N, N) bias from the row shard: local projection, then all-gather per head."""
+        rows, n, c = x_loc.shape
+        heads = w.shape[0]
+        # the 1-GPU op expects square tensors; project the shard as `rows` independent 1 x n rows
+        loc = F.pair_bias_rows(x_loc, ln_w, ln_b, w, eps)                     # (heads, rows, n)
+        full = _bf16((heads, n, n), x_loc.device)
+        for h in range(heads):
+            dist.all_gather_into_tensor(full[h], loc[h], group=self.group)
+        return full
+
+
+class ShardedPairformerBlock:
+    """The composite Pairformer block on a row shard.  Wraps the weights of a `modules.PairformerBlock`."""
+
+    def __init__(self, block, group=None):
+        self.block = block
+        self.ops = ShardedPairOps(group)
+
+    @torch.no_grad()
+    def __call__(self, z_loc: torch.Tensor, s: torch.Tensor, pair_mask_loc: torch.Tensor, mask: torch.Tensor):
+        """z_loc (rows, N, c_z) row shard; s (1, N, c_s) replicated; pair_mask_loc (rows, N); mask (1, N)."""
+        b, ops = self.block, self.ops
+        dev = z_loc.device
+        bf = torch.bfloat16
+        z = ops.trimul_outgoing(z_loc, pair_mask_loc, b.tri_mul_out._packed(dev, bf, packing.pack_trimul))
+        z = ops.trimul_incoming(z, pair_mask_loc, b.tri_mul_in._packed(dev, bf, packing.pack_trimul))
+        pk_s = b.tri_att_start._packed(dev, bf, lambda sd, d: packing.pack_triatt(sd, b.tri_att_start.no_heads, d))
+        pk_e = b.tri_att_end._packed(dev, bf, lambda sd, d: packing.pack_triatt(sd, b.tri_att_end.no_heads, d))
+        z = ops.triatt_starting(z, pair_mask_loc, pk_s)
+        z = ops.triatt_ending(z, pair_mask_loc, pk_e)
+        z = b.transition_z(z, residual=True)
+        bias = ops.pair_bias(z, b.layernorm_z.weight.detach().float(), b.layernorm_z.bias.detach().float(),
+                             b.linear_pair_bias.weight.detach().to(dev, bf).contiguous(), b.layernorm_z.eps)
+        s = b.attention(s, None, bias.unsqueeze(0), mask, residual=True)
+        s = b.transition(s, residual=True)
+        return z, s
