@@ -134,13 +134,15 @@ def make_inputs():
     return z, s, pm, m, w
 
 
-def config_dict(n_gpus: int) -> dict:
+def config_dict(n_gpus: int, sharded_mode: bool = False) -> dict:
     return {
         "workload": f"composite Pairformer block forward (BASELINE config 4's block): N_token={N_TOKENS}, c_z=128, c_s=384, "
                     "tri-mult out+in, tri-att start+end (4x32), transition x4, single pair-bias attention (16x24), transition x4",
         "n_token": N_TOKENS, "c_z": C_Z, "c_s": C_S, "padding_tail": PAD_FRAC, "seed": SEED,
-        "blocks_per_step": n_gpus,
-        "parallelism": "independent blocks, one per GPU, no collective" if n_gpus > 1 else "single GPU",
+        "blocks_per_step": 1 if sharded_mode else n_gpus,
+        "parallelism": ("one pair tensor row-sharded over the GPUs: all-gather for triangle multiplication and the "
+                        "triangle bias, all-to-all transposes for the incoming / ending-node operators") if sharded_mode
+        else ("independent blocks, one per GPU, no collective" if n_gpus > 1 else "single GPU"),
         "l2": "not flushed between steps: the pair tensor alone (151 MB bf16) and every intermediate exceed the 126 MB L2",
     }
 
@@ -221,6 +223,13 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     z, s, pm, m, w = make_inputs()
     blk = M.PairformerBlock(C_Z, C_S).to(dev)
     blk.load_state_dict(w, strict=True)
+    sharded_mode = args.sharded and world > 1
+    if sharded_mode:
+        # strong scaling: all ranks share ONE pair tensor, row-sharded (BASELINE config 5's layout)
+        from kfold_b200 import sharded as SH
+        r0, r1 = SH.shard_rows(N_TOKENS, world, rank)
+        z, pm = z[:, r0:r1].contiguous(), pm[:, r0:r1].contiguous()
+        sblk = SH.ShardedPairformerBlock(blk)
     z_host = z.bfloat16().pin_memory()
     s_host = s.bfloat16().pin_memory()
     z_dev, s_dev = z_host.to(dev), s_host.to(dev)
@@ -229,13 +238,19 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     s_out_host = torch.empty_like(s_host).pin_memory()
     stream = torch.cuda.current_stream()
 
+    def run_block(zd, sd):
+        if sharded_mode:
+            return sblk(zd[0], sd, pm_dev[0], m_dev)
+        return blk(zd, sd, pm_dev, m_dev)
+
     def step_resident():
-        return blk(z_dev, s_dev, pm_dev, m_dev)
+        return run_block(z_dev, s_dev)
 
     def step_e2e():
         zd = z_host.to(dev, non_blocking=True)
         sd = s_host.to(dev, non_blocking=True)
-        zo, so = blk(zd, sd, pm_dev, m_dev)
+        zo, so = run_block(zd, sd)
+        zo = zo.reshape(z_out_host.shape)
         z_out_host.copy_(zo, non_blocking=True)
         s_out_host.copy_(so, non_blocking=True)
 
@@ -315,9 +330,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         h2d = z_host.numel() * 2 + s_host.numel() * 2
         d2h = z_out_host.numel() * 2 + s_out_host.numel() * 2
         line = {
-            "metric": METRIC, "value": ms_step / world, "unit": "ms", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world),
+            "metric": METRIC, "value": ms_step if sharded_mode else ms_step / world, "unit": "ms", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
+            "scaling": "strong" if sharded_mode else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world, sharded_mode),
             "block_tflops": round(block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12, 2),
             "block_frac_of_tensor_peak": round(block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
             "roofline": roofline, "cpu_baseline": cpu,
@@ -336,6 +352,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharded", action="store_true",
+                    help="with N > 1 ranks: row-shard ONE pair tensor over the GPUs (strong scaling) instead of one block per GPU")
     ap.add_argument("--tokens", type=int, default=N_TOKENS,
                     help="profiling aid: run the block at another N (the reported line is then NOT the benchmark workload)")
     args = ap.parse_args()

@@ -59,5 +59,6 @@ def test_sharded_block_matches_single_gpu(n):
     results = [q.get(timeout=10) for _ in range(world)]
     for rank, status, ez, es, exact in results:
         assert status == 0
-        # same kernels, same operands; only the tile walk over the gathered operand differs
-        assert ez < 2e-3 and es < 2e-3, f"rank {rank}: z {ez:.3e} s {es:.3e} (bit-exact: {exact})"
+        # same kernels and operands; the ending-node update is rounded to bf16 once more before it is added (it travels
+            # through the all-to-all), hence a few 1e-3 of RMS rather than bit equality
+        assert ez < 6e-3 and es < 6e-3, f"rank {rank}: z {ez:.3e} s {es:.3e} (bit-exact: {exact})"
