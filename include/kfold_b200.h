@@ -44,7 +44,14 @@ enum {
   KFB_ERR_DEVICE_WAIT = 4 /* a bounded device-side wait ran out; see kfb_device_status */
 };
 
-enum { KFB_BF16 = 0, KFB_FP32 = 1 };
+/* Activation dtype / arithmetic of an operator call:
+ *   KFB_BF16          bf16 tensors, bf16 tensor-core arithmetic with fp32 accumulation;
+ *   KFB_FP32          fp32 tensors in and out, same bf16 arithmetic inside (what autocast(bf16) on fp32 inputs gives);
+ *   KFB_FP32_PRECISE  fp32 tensors and fp32-accurate arithmetic: every GEMM operand is split into three bf16 parts
+ *                     (x = x0 + x1 + x2, 24 mantissa bits) and the six significant partial products are accumulated
+ *                     in fp32 on the same tensor-core kernels; weights come from the `precise` packing.  Needs the
+ *                     larger workspaces reported by the *_workspace_bytes_precise functions. */
+enum { KFB_BF16 = 0, KFB_FP32 = 1, KFB_FP32_PRECISE = 2 };
 
 /* Library version (major*10000 + minor*100 + patch). */
 KFB_API int kfb_version(void);
@@ -209,6 +216,7 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
  *   half interleaved in blocks of 128 rows;  w_out : bf16 [c, hidden];  hidden a multiple of 128.
  */
 KFB_API size_t kfb_transition_workspace_bytes(long long rows, int c, int hidden);
+KFB_API size_t kfb_transition_workspace_bytes_precise(long long rows, int c, int hidden);
 KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu_packed,
                                const void* w_out, void* out, const void* resid, void* workspace, size_t workspace_bytes,
                                long long rows, int c, int hidden, float eps, int dtype, void* stream);

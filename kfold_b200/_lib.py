@@ -13,7 +13,7 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "_C", "libkfold_b200.so")
 
-KFB_BF16, KFB_FP32 = 0, 1
+KFB_BF16, KFB_FP32, KFB_FP32_PRECISE = 0, 1, 2
 _lib = None
 
 c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
@@ -58,6 +58,7 @@ _SIGNATURES = {
                                   c_float, c_int, c_void_p],
 }
 _SIZE_FUNCS = {
+    "kfb_transition_workspace_bytes_precise": [c_ll, c_int, c_int],
     "kfb_cond_transition_workspace_bytes": [c_ll, c_int],
     "kfb_transition_static_max_bytes": [],
     "kfb_pair_bias_workspace_bytes": [c_int, c_int, c_int],

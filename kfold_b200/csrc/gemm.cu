@@ -9,7 +9,7 @@
 
 namespace kfb {
 
-template <int BN, bool GLU, bool AUX>
+template <int BN, bool GLU, bool AUX, bool PRECISE>
 static int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* tout,
                           const GemmParams& p, const char* tag) {
   using Cfg = GemmCfg<BN>;
@@ -18,14 +18,14 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUte
   KFB_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, GLU, AUX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, GLU, AUX, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   });
   KFB_CUDA(attr_err);
   const int total = p.num_m_tiles * p.num_n_tiles;
   const int grid = total < sm_count() ? total : sm_count();
   {
     LaunchScope scope(stream, tag);
-    gemm_bf16_kernel<BN, GLU, AUX><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], p);
+    gemm_bf16_kernel<BN, GLU, AUX, PRECISE><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], p);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
@@ -37,11 +37,18 @@ static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorM
   using Cfg = GemmCfg<BN>;
   if (p.aux && Cfg::stages_for(Cfg::kAuxBytes) < 2) p.aux = 0;  // no room (BN = 256): fall back to direct loads
   p.stages = Cfg::stages_for(p.aux ? Cfg::kAuxBytes : Cfg::kStagingBytes);
-  if (p.glu) return launch_variant<BN, true, false>(stream, ta, tb, tout, p, tag);
   if constexpr (BN <= 128) {
-    if (p.aux) return launch_variant<BN, false, true>(stream, ta, tb, tout, p, tag);
+    if (p.precise) {
+      p.k_main_blocks = (p.k_extent / 6) / kBK;
+      if (p.glu) return launch_variant<BN, true, false, true>(stream, ta, tb, tout, p, tag);
+      return launch_variant<BN, false, false, true>(stream, ta, tb, tout, p, tag);
+    }
   }
-  return launch_variant<BN, false, false>(stream, ta, tb, tout, p, tag);
+  if (p.glu) return launch_variant<BN, true, false, false>(stream, ta, tb, tout, p, tag);
+  if constexpr (BN <= 128) {
+    if (p.aux) return launch_variant<BN, false, true, false>(stream, ta, tb, tout, p, tag);
+  }
+  return launch_variant<BN, false, false, false>(stream, ta, tb, tout, p, tag);
 }
 
 static long long* g_trace_buf = nullptr;
@@ -57,7 +64,9 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   KFB_CHECK_ARG(p.nseg >= 1 && p.nseg <= 3, "GEMM needs 1..3 output segments");
   int bn = force_bn;
   if (bn == 0) bn = p.n_cols >= 256 ? 256 : (p.n_cols > 64 ? 128 : 64);
+  if (p.precise && bn > 128) bn = 128;  // the fp32-accurate variant keeps four accumulators in tensor memory
   KFB_CHECK_ARG(bn == 64 || bn == 128 || bn == 256, "unsupported BN %d", bn);
+  if (p.precise) KFB_CHECK_ARG(p.k_extent % 6 == 0, "precise GEMM: K=%d is not six equal parts", p.k_extent);
   if (p.glu) KFB_CHECK_ARG(p.n_cols % bn == 0, "GLU GEMM needs n_cols (%d) to be a multiple of the N tile (%d)", p.n_cols, bn);
   for (int i = 0; i < p.nseg; ++i) KFB_CHECK_ARG(p.seg[i].col_begin % 32 == 0, "segment start must be a multiple of 32");
   p.trace = (g_trace_buf != nullptr && strcmp(g_trace_tag, tag) == 0) ? g_trace_buf : nullptr;
@@ -94,7 +103,7 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
     sg.tma_slot = -1;
     const bool aligned = (reinterpret_cast<uintptr_t>(sg.dst) & 15) == 0 && sg.s_o % 8 == 0 && sg.s_col % 8 == 0 &&
                          (sg.s_b % 8 == 0 || p.batch == 1) && (sg.s_o != 0 || p.o_extent == 1);
-    if (sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && aligned && next_slot < 2) {
+    if (sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && aligned && next_slot < 2 && !p.precise) {
       const uint64_t dims[4] = {(uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)sg.ncols, (uint64_t)p.batch};
       const uint64_t str[3] = {(uint64_t)sg.s_o * 2, (uint64_t)sg.s_col * 2, (uint64_t)sg.s_b * 2};
       const uint32_t box[4] = {32, 1, 32, 1};
@@ -106,7 +115,7 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   p.aux = 0;
   p.aux_gate = 0;
   p.aux_resid = 0;
-  if (next_slot == 0 && p.nseg == 1 && p.seg[0].vec && (p.gate != nullptr || p.resid != nullptr) && bn >= 64 &&
+  if (!p.precise && next_slot == 0 && p.nseg == 1 && p.seg[0].vec && (p.gate != nullptr || p.resid != nullptr) && bn >= 64 &&
       p.n_cols % 32 == 0 && !p.glu) {
     const EpiSeg& sg = p.seg[0];
     bool ok_g = true, ok_r = true;

@@ -35,6 +35,9 @@ struct EpiSeg {
   int out_fp32;     // 0: bf16 output, 1: fp32 output
   int vec;          // 1: s_col == 1 and every row start is 16-byte aligned -> vector stores
   int tma_slot;     // >= 0: channel-major bf16 segment stored through shared memory with TMA store map `tma_slot`
+  int split;        // precise mode: 0 plain store; 1 / 2: the value is split into three bf16 parts x0+x1+x2 and stored
+                    // six times, s_part elements apart, as [x0 x0 x1 x1 x0 x2] (1) or [x0 x1 x0 x1 x2 x0] (2)
+  long long s_part;
   void* dst;
   long long s_col, s_n, s_o, s_b;
 };
@@ -54,7 +57,13 @@ struct GemmParams {
   long long m_n, m_o, m_b;
   int mask_segs;                  // bit i: apply rowmask to segment i
   const float* col_bias;          // optional, per output column, added before everything else
+  int precise;                    // fp32-accurate mode: exact sigmoid, fp32 gate logits, split stores
+  int k_main_blocks;              // precise: the first k_main_blocks k-blocks (the x0*w0 products) accumulate in their own
+                                  // TMEM accumulator, the five correction blocks in a second one; the epilogue adds the
+                                  // two in fp32.  The tensor core truncates on every accumulation step, relative to the
+                                  // accumulator's magnitude: keeping the small corrections apart keeps their error small
   const __nv_bfloat16* gate;      // optional: seg 0 value *= sigmoid(gate[...]), addressed with seg 0 strides
+                                  // (points at float logits when `precise`)
   long long g_col, g_n, g_o, g_b;
   int stages;                     // depth of the operand ring (launcher)
   int aux;                        // 1: gate / residual tiles are prefetched into shared memory by TMA (launcher)
@@ -100,6 +109,36 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float sigmoidf_exact(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// x = x0 + x1 + x2 with three bf16 parts (24 mantissa bits): the operands of the fp32-accurate GEMMs.
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& x0, __nv_bfloat16& x1, __nv_bfloat16& x2) {
+  x0 = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(x0);
+  x1 = __float2bfloat16_rn(r1);
+  x2 = __float2bfloat16_rn(r1 - __bfloat162float(x1));
+}
+
+// Split store of 32 values of one row: six copies, s_part elements apart (see EpiSeg::split).
+__device__ __forceinline__ void epi_store_split(const EpiSeg& sg, long long row_off, int col_local, const float (&v)[32],
+                                                bool row_ok) {
+  if (!row_ok) return;
+  const int nvalid = min(32, sg.ncols - col_local);
+  __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(sg.dst) + row_off + static_cast<long long>(col_local) * sg.s_col;
+#pragma unroll 4
+  for (int i = 0; i < 32; ++i) {
+    if (i >= nvalid) break;
+    __nv_bfloat16 x0, x1, x2;
+    split3(v[i], x0, x1, x2);
+    __nv_bfloat16* e = d + static_cast<long long>(i) * sg.s_col;
+    if (sg.split == 1) {
+      e[0] = x0; e[sg.s_part] = x0; e[2 * sg.s_part] = x1; e[3 * sg.s_part] = x1; e[4 * sg.s_part] = x0; e[5 * sg.s_part] = x2;
+    } else {
+      e[0] = x0; e[sg.s_part] = x1; e[2 * sg.s_part] = x0; e[3 * sg.s_part] = x1; e[4 * sg.s_part] = x2; e[5 * sg.s_part] = x0;
+    }
+  }
+}
+
 // Store 32 consecutive output values of one row.
 __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_off, int col_local, const float (&v)[32],
                                                 bool row_ok) {
@@ -137,7 +176,9 @@ __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_
 // GLU and AUX are compile-time so that each variant carries only its own epilogue code (and registers):
 //   GLU  the tile holds values and gates (p.glu says which activation);
 //   AUX  gate logits / residual come from shared-memory tiles prefetched by the producer.
-template <int BN, bool GLU, bool AUX>
+//   PRECISE  fp32-accurate mode (operands are bf16 triple splits concatenated along K, see split3): exact
+//            sigmoid, fp32 gate logits, split stores.
+template <int BN, bool GLU, bool AUX, bool PRECISE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_out0, const __grid_constant__ CUtensorMap tm_out1,
@@ -146,6 +187,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   using Cfg = GemmCfg<BN>;
   const int kStages = p.stages;
   constexpr int OUT_BN_GLU = BN / 2;
+  constexpr int ACC_COLS = PRECISE ? 2 * BN : BN;  // precise: main accumulator, then the correction accumulator
+  static_assert(!PRECISE || BN <= 128, "the fp32-accurate variant needs four accumulators of BN columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -186,7 +229,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_alloc(tmem_slot, PRECISE ? 2 * Cfg::kTmemCols : Cfg::kTmemCols);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before_sync();
@@ -249,16 +292,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const uint32_t acc_phase = (tile_iter >> 1) & 1;
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, 102)) { ok = false; break; }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, 103)) { ok = false; break; }
           ptx::tc_fence_after_sync();
           // one descriptor per stage; inside the 128-byte swizzle span only the address field advances
           const uint64_t a_desc = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_a + stage * Cfg::kAStage));
           const uint64_t b_desc = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_b + stage * Cfg::kBStage));
+          const bool corr = PRECISE && kb >= p.k_main_blocks;
+          const uint32_t d_acc = corr ? d_tmem + BN : d_tmem;
+          const bool first = corr ? (kb == p.k_main_blocks) : (kb == 0);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k)
-            ptx::mma_f16_ss(d_tmem, a_desc + k * 2, b_desc + k * 2, idesc, (kb | k) != 0 ? 1u : 0u);
+            ptx::mma_f16_ss(d_acc, a_desc + k * 2, b_desc + k * 2, idesc, (first && k == 0) ? 0u : 1u);
           ptx::tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -290,7 +336,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       ptx::tc_fence_after_sync();
       const uint8_t* aux_tile = s_aux + (tile_iter & 1) * (2 * Cfg::kAuxTileBytes);
       if (AUX && !ptx::mbar_wait(&aux_full[tile_iter & 1], (tile_iter >> 1) & 1, 107)) { ok = false; break; }
-      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t t_row = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quad * 32) << 16);
 
       float mask_v = 1.0f;
       if (p.rowmask != nullptr && row_ok)
@@ -309,17 +355,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+          if (PRECISE) {
+            ptx::tmem_ld_32x32b_x32(t_row + BN + c, raw);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(raw[i]);
+          }
         }
         if (GLU) {
           uint32_t raw[32];
           ptx::tmem_ld_32x32b_x32(t_row + OUT_BN_GLU + c, raw);
           ptx::tmem_ld_wait();
+          if (PRECISE) {
+            uint32_t raw2[32];
+            ptx::tmem_ld_32x32b_x32(t_row + BN + OUT_BN_GLU + c, raw2);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) + __uint_as_float(raw2[i]));
+          }
           if (p.glu == GLU_SIGMOID) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= sigmoidf_fast(__uint_as_float(raw[i]));
+            for (int i = 0; i < 32; ++i)
+              v[i] *= PRECISE ? sigmoidf_exact(__uint_as_float(raw[i])) : sigmoidf_fast(__uint_as_float(raw[i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = v[i] * sigmoidf_fast(v[i]) * __uint_as_float(raw[i]);
+            for (int i = 0; i < 32; ++i)
+              v[i] = v[i] * (PRECISE ? sigmoidf_exact(v[i]) : sigmoidf_fast(v[i])) * __uint_as_float(raw[i]);
           }
         }
         // which segment does this chunk belong to
@@ -388,7 +449,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
           }
         } else if (!AUX && si == 0 && row_ok) {
-          if (p.gate != nullptr) {
+          if (PRECISE && p.gate != nullptr) {
+            const float* g = reinterpret_cast<const float*>(p.gate) + static_cast<long long>(b) * p.g_b +
+                             static_cast<long long>(o) * p.g_o + static_cast<long long>(n) * p.g_n +
+                             static_cast<long long>(col_local) * p.g_col;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col_local + i < sg.ncols) v[i] *= sigmoidf_exact(g[static_cast<long long>(i) * p.g_col]);
+          } else if (p.gate != nullptr) {
             const __nv_bfloat16* g = p.gate + static_cast<long long>(b) * p.g_b + static_cast<long long>(o) * p.g_o +
                                      static_cast<long long>(n) * p.g_n + static_cast<long long>(col_local) * p.g_col;
             if (p.g_col == 1 && col_local + 32 <= sg.ncols) {
@@ -447,7 +515,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
           }
         }
-        epi_store_chunk(sg, row_off, col_local, v, row_ok);
+        if (PRECISE && sg.split)
+          epi_store_split(sg, row_off, col_local, v, row_ok);
+        else
+          epi_store_chunk(sg, row_off, col_local, v, row_ok);
       }
       if (!ok) break;
       if (AUX) {
@@ -467,7 +538,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #undef KFB_GSTAMP
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    ptx::tmem_dealloc(tmem_base, PRECISE ? 2 * Cfg::kTmemCols : Cfg::kTmemCols);
   }
 }
 

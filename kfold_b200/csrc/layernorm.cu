@@ -130,6 +130,97 @@ int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w
 }
 
 // ------------------------------------------------------------------------------------------------
+// fp32-accurate mode: LayerNorm (or a plain copy) of fp32 rows, written as the bf16 triple split.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split3_store(__nv_bfloat16* y6, int c, int ch, float v) {
+  const __nv_bfloat16 x0 = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(x0);
+  const __nv_bfloat16 x1 = __float2bfloat16_rn(r1);
+  const __nv_bfloat16 x2 = __float2bfloat16_rn(r1 - __bfloat162float(x1));
+  y6[ch] = x0; y6[c + ch] = x0; y6[2 * c + ch] = x1; y6[3 * c + ch] = x1; y6[4 * c + ch] = x0; y6[5 * c + ch] = x2;
+}
+
+__global__ void __launch_bounds__(256) layernorm_split_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y6,
+                                                              const float* __restrict__ w, const float* __restrict__ b,
+                                                              long long rows, int c, long long xs, float eps, int normalise) {
+  const int lane = threadIdx.x & 31;
+  const long long warps_per_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += warps_per_grid) {
+    const float* xr = x + row * xs;
+    float mean = 0.f, rstd = 1.f;
+    if (normalise) {
+      float s = 0.f;
+      for (int ch = lane; ch < c; ch += 32) s += xr[ch];
+      mean = warp_sum(s) / static_cast<float>(c);
+      float q = 0.f;
+      for (int ch = lane; ch < c; ch += 32) {
+        const float d = xr[ch] - mean;
+        q += d * d;
+      }
+      rstd = 1.0f / sqrtf(warp_sum(q) / static_cast<float>(c) + eps);
+    }
+    __nv_bfloat16* yr = y6 + row * 6 * c;
+    for (int ch = lane; ch < c; ch += 32) {
+      float v = (xr[ch] - mean) * rstd;
+      if (w != nullptr) v *= w[ch];
+      if (b != nullptr) v += b[ch];
+      split3_store(yr, c, ch, v);
+    }
+  }
+}
+
+int launch_layernorm_split(cudaStream_t stream, const float* x, __nv_bfloat16* y6, const float* w, const float* b, long long rows,
+                           int c, long long xs, float eps, int normalise) {
+  KFB_CHECK_ARG(rows >= 0 && c > 0, "layernorm_split: rows %lld, channels %d", rows, c);
+  if (rows == 0) return KFB_OK;
+  const int warps = 8;
+  long long blocks = (rows + warps - 1) / warps;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  LaunchScope scope(stream, "layernorm_split");
+  layernorm_split_kernel<<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(x, y6, w, b, rows, c, xs, eps, normalise);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+// Channel-major fp32 in, position-major triple split out (fp32-accurate mode): fp32 slab, one thread per position.
+__global__ void __launch_bounds__(128) layernorm_cm_split_kernel(const float* __restrict__ t, __nv_bfloat16* __restrict__ y6,
+                                                                 const float* __restrict__ w, const float* __restrict__ b,
+                                                                 long long npos, int c, long long chan_stride,
+                                                                 long long batch_stride, float eps, int blocks_per_batch) {
+  extern __shared__ __align__(16) unsigned char slab_raw_f[];
+  float* slab = reinterpret_cast<float*>(slab_raw_f);  // [c][128]
+  const int batch = blockIdx.x / blocks_per_batch;
+  const long long p0 = static_cast<long long>(blockIdx.x % blocks_per_batch) * 128;
+  const float* tb = t + batch * batch_stride + p0;
+  for (int idx = threadIdx.x; idx < c * 128; idx += 128) {
+    const int ch = idx >> 7, pp = idx & 127;
+    slab[idx] = (p0 + pp < npos) ? tb[ch * chan_stride + pp] : 0.f;
+  }
+  __syncthreads();
+  const long long p = p0 + threadIdx.x;
+  if (p >= npos) return;
+  const float* col = slab + threadIdx.x;
+  float s = 0.f;
+  for (int ch = 0; ch < c; ++ch) s += col[ch * 128];
+  const float mean = s / static_cast<float>(c);
+  float q = 0.f;
+  for (int ch = 0; ch < c; ++ch) {
+    const float d = col[ch * 128] - mean;
+    q += d * d;
+  }
+  const float rstd = 1.0f / sqrtf(q / static_cast<float>(c) + eps);
+  __nv_bfloat16* yr = y6 + (static_cast<long long>(batch) * npos + p) * 6 * c;
+  for (int ch = 0; ch < c; ++ch) {
+    float v = (col[ch * 128] - mean) * rstd;
+    if (w != nullptr) v *= w[ch];
+    if (b != nullptr) v += b[ch];
+    split3_store(yr, c, ch, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Adaptive LayerNorm (AdaLN): one warp per row, same register layout as layernorm_rows_kernel.
 // ------------------------------------------------------------------------------------------------
 template <typename TI, typename TO, int G>
@@ -284,8 +375,22 @@ __global__ void __launch_bounds__(kCmPos) layernorm_cm_kernel(const TI* __restri
 }
 
 int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, const float* w, const float* b, int batch,
-                        long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype) {
+                        long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype,
+                        int split_out) {
   KFB_CHECK_ARG(c > 0 && c % 8 == 0 && c <= 512, "layernorm_cm: channels %d (multiple of 8, at most 512)", c);
+  if (split_out) {
+    KFB_CHECK_ARG(in_dtype == KFB_FP32 && c <= 256, "layernorm_cm: the split output takes fp32 input and at most 256 channels");
+    if (npos == 0 || batch == 0) return KFB_OK;
+    const int bpb = static_cast<int>((npos + 127) / 128);
+    const size_t smem = static_cast<size_t>(c) * 128 * sizeof(float);
+    if (smem > 48 * 1024)
+      KFB_CUDA(cudaFuncSetAttribute(layernorm_cm_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope scope(stream, "layernorm_cm_split");
+    layernorm_cm_split_kernel<<<bpb * batch, 128, smem, stream>>>(static_cast<const float*>(t), y, w, b, npos, c, chan_stride,
+                                                                 batch_stride, eps, bpb);
+    KFB_CUDA(cudaGetLastError());
+    return KFB_OK;
+  }
   KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(y) & 15) == 0, "layernorm_cm: output must be 16-byte aligned");
   if (npos == 0 || batch == 0) return KFB_OK;
   const int bpb = static_cast<int>((npos + kCmPos - 1) / kCmPos);

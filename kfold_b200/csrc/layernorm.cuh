@@ -8,11 +8,18 @@ namespace kfb {
 int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
                      long long xs, long long ys, float eps, int in_dtype, int out_dtype);
 
+// Row-wise LayerNorm of fp32 rows written as the bf16 triple split [x0 x0 x1 x1 x0 x2] (six blocks of c columns,
+// row stride 6c): the A operand of the fp32-accurate GEMMs.  With w == b == nullptr and `normalise` == 0 it only
+// splits (used for operands that are not normalised).
+int launch_layernorm_split(cudaStream_t stream, const float* x, __nv_bfloat16* y6, const float* w, const float* b, long long rows,
+                           int c, long long xs, float eps, int normalise);
+
 // LayerNorm over channels of a CHANNEL-major tensor t[batch][c][pos] (pos contiguous, channel stride
 // `chan_stride`, batch stride `batch_stride`), written POSITION-major y[batch*npos + pos][c] in bf16.
 // `in_dtype` is the element type of t.  Used on the triangle contraction's output.
 int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, const float* w, const float* b, int batch,
-                        long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype);
+                        long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype,
+                        int split_out = 0);  // split_out: y is the [x0 x0 x1 x1 x0 x2] split, row stride 6c
 
 // Adaptive LayerNorm: y[r] = sigmoid(g[s(r)]) * LN(a[r]) + v[s(r)], LN without affine, fp32 statistics.
 // a, y: `rows` rows of c channels; gv: rows_s rows of [2c] (gate logits | shift), bf16.  Row r of a uses row

@@ -25,6 +25,54 @@ KFB_API size_t kfb_transition_workspace_bytes(long long rows, int c, int hidden)
   return carve(w, nullptr, rows, c, hidden);
 }
 
+KFB_API size_t kfb_transition_workspace_bytes_precise(long long rows, int c, int hidden) {
+  return align_up(static_cast<size_t>(rows) * 6 * c * 2, 256) + align_up(static_cast<size_t>(rows) * 6 * hidden * 2, 256);
+}
+
+// fp32-accurate transition: every operand is the bf16 triple split, concatenated along K (see kfold_b200.h)
+static int transition_precise(cudaStream_t stream, const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu6,
+                              const void* w_out6, void* out, const void* resid, void* workspace, long long rows, int c,
+                              int hidden, float eps) {
+  Carver cv(workspace);
+  __nv_bfloat16* xn6 = cv.take<__nv_bfloat16>(static_cast<size_t>(rows) * 6 * c);
+  __nv_bfloat16* h6 = cv.take<__nv_bfloat16>(static_cast<size_t>(rows) * 6 * hidden);
+  KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x), xn6, ln_w, ln_b, rows, c, c, eps, 1));
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(rows);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = 2 * hidden;
+    p.k_extent = 6 * c;
+    p.glu = GLU_SWIGLU;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(h6, hidden, 6ll * hidden, 0, 0, 0);
+    p.seg[0].vec = 0;
+    p.seg[0].split = 1;
+    p.seg[0].s_part = hidden;
+    GemmOperandA a = {xn6, 6ll * c, 0, 0};
+    GemmOperandB b = {w_swiglu6, 6ll * c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "transition_swiglu_precise"));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(rows);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = 6 * hidden;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, 0, 0, 1);
+    p.resid = resid;
+    GemmOperandA a = {h6, 6ll * hidden, 0, 0};
+    GemmOperandB b = {w_out6, 6ll * hidden, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "transition_out_precise"));
+  }
+  return KFB_OK;
+}
+
 KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu_packed,
                                const void* w_out, void* out, const void* resid, void* workspace, size_t workspace_bytes,
                                long long rows, int c, int hidden, float eps, int dtype, void* stream_) {
@@ -32,6 +80,12 @@ KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln
   KFB_CHECK_ARG(is_dtype(dtype), "transition: bad dtype %d", dtype);
   KFB_CHECK_ARG(rows >= 1 && rows < (1ll << 31), "transition: rows %lld", rows);
   KFB_CHECK_ARG(c % 8 == 0 && hidden % 128 == 0, "transition: c=%d (multiple of 8), hidden=%d (multiple of 128)", c, hidden);
+  if (dtype == KFB_FP32_PRECISE) {
+    KFB_CHECK_ARG(workspace_bytes >= kfb_transition_workspace_bytes_precise(rows, c, hidden), "transition: workspace too small");
+    KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "transition: workspace must be 256-byte aligned");
+    return transition_precise(as_stream(stream_), x, ln_w, ln_b, w_swiglu_packed, w_out, out, resid, workspace, rows, c, hidden,
+                              eps);
+  }
   TransWs w;
   const size_t need = carve(w, workspace, rows, c, hidden);
   KFB_CHECK_ARG(workspace_bytes >= need, "transition: workspace %zu < %zu bytes", workspace_bytes, need);
@@ -60,7 +114,7 @@ KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln
     p.n_cols = c;
     p.k_extent = hidden;
     p.nseg = 1;
-    p.seg[0] = row_major_seg(out, c, c, 0, 0, dtype == KFB_FP32);
+    p.seg[0] = row_major_seg(out, c, c, 0, 0, is_fp32_io(dtype));
     p.resid = resid;
     GemmOperandA a = {w.h, hidden, 0, 0};
     GemmOperandB b = {w_out, hidden, 0};

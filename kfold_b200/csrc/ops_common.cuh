@@ -7,8 +7,9 @@
 namespace kfb {
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
-inline bool is_dtype(int d) { return d == KFB_BF16 || d == KFB_FP32; }
-inline size_t dtype_bytes(int d) { return d == KFB_FP32 ? 4 : 2; }
+inline bool is_dtype(int d) { return d == KFB_BF16 || d == KFB_FP32 || d == KFB_FP32_PRECISE; }
+inline bool is_fp32_io(int d) { return d == KFB_FP32 || d == KFB_FP32_PRECISE; }
+inline size_t dtype_bytes(int d) { return d == KFB_BF16 ? 2 : 4; }
 
 // Carves 256-byte aligned pieces out of a caller-provided workspace.
 struct Carver {

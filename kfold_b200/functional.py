@@ -248,11 +248,16 @@ def transition(x: torch.Tensor, packed: dict, eps: float = 1e-5, residual: bool 
     rows = x2.shape[0]
     out = torch.empty_like(x2)
     lib = L.lib()
+    precise = bool(packed.get("precise"))
+    if precise and x2.dtype != torch.float32:
+        raise ValueError("the fp32-accurate mode takes float32 tensors")
     with torch.cuda.device(x.device):
-        ws = _workspace(x.device, lib.kfb_transition_workspace_bytes(rows, c, hidden))
+        need = (lib.kfb_transition_workspace_bytes_precise if precise else lib.kfb_transition_workspace_bytes)(rows, c, hidden)
+        ws = _workspace(x.device, need)
         L.check(lib.kfb_transition_fwd(L.ptr(x2), L.ptr(packed["ln_w"]), L.ptr(packed["ln_b"]), L.ptr(packed["w_swiglu"]),
                                        L.ptr(packed["w_out"]), L.ptr(out), L.ptr(x2) if residual else None, L.ptr(ws),
-                                       ws.numel(), rows, c, hidden, eps, L.dtype_code(x2.dtype), L.stream_ptr()))
+                                       ws.numel(), rows, c, hidden, eps,
+                                       L.KFB_FP32_PRECISE if precise else L.dtype_code(x2.dtype), L.stream_ptr()))
     return out.view(x.shape)
 
 

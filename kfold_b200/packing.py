@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 GLU_HALF = 128  # value (or gate) columns per 256-wide GEMM tile
+GLU_HALF_PRECISE = 64  # the fp32-accurate GEMM variant uses 128-wide tiles
 
 
 def interleave_glu(value_w: torch.Tensor, gate_w: torch.Tensor, half: int = GLU_HALF) -> torch.Tensor:
@@ -19,6 +20,24 @@ def interleave_glu(value_w: torch.Tensor, gate_w: torch.Tensor, half: int = GLU_
     v = value_w.reshape(n // half, half, k)
     g = gate_w.reshape(n // half, half, k)
     return torch.stack((v, g), dim=1).reshape(2 * n, k).contiguous()
+
+
+def split3_weights(w: torch.Tensor) -> torch.Tensor:
+    """fp32 [n, k] -> bf16 [n, 6k] = [w0 | w1 | w0 | w1 | w2 | w0] with w = w0 + w1 + w2 (bf16 parts): the B operand of
+    the fp32-accurate GEMMs, matching activations stored as [x0 | x0 | x1 | x1 | x0 | x2]."""
+    w = w.detach().float()
+    w0 = w.to(torch.bfloat16)
+    r1 = w - w0.float()
+    w1 = r1.to(torch.bfloat16)
+    w2 = (r1 - w1.float()).to(torch.bfloat16)
+    return torch.cat([w0, w1, w0, w1, w2, w0], dim=-1).contiguous()
+
+
+def _w(t: torch.Tensor, device, precise: bool) -> torch.Tensor:
+    """A projection weight on the device: bf16, or its triple split for the fp32-accurate mode."""
+    if precise:
+        return split3_weights(t).to(device)
+    return t.detach().to(device=device, dtype=torch.bfloat16).contiguous()
 
 
 def _dev(t: torch.Tensor, device, dtype) -> torch.Tensor:
@@ -103,7 +122,7 @@ def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
     }
 
 
-def pack_transition(w: dict, device, dtype=torch.bfloat16) -> dict:
+def pack_transition(w: dict, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Weights of Transition (model/layers/folding/transition.py:27-46): the SwiGLU matrix is split into
     its silu half and its linear half (model/primitives/activation.py:27-29) and interleaved per GEMM tile."""
     sw = w["swiglu.linear.weight"].detach().float()
@@ -111,9 +130,9 @@ def pack_transition(w: dict, device, dtype=torch.bfloat16) -> dict:
     return {
         "ln_w": _dev(w["layernorm.weight"], device, torch.float32),
         "ln_b": _dev(w["layernorm.bias"], device, torch.float32),
-        "w_swiglu": _dev(interleave_glu(sw[:hidden], sw[hidden:]), device, dtype),
-        "w_out": _dev(w["linear_out.weight"], device, dtype),
-        "c": int(sw.shape[1]), "hidden": int(hidden),
+        "w_swiglu": _w(interleave_glu(sw[:hidden], sw[hidden:], GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_out": _w(w["linear_out.weight"], device, precise),
+        "c": int(sw.shape[1]), "hidden": int(hidden), "precise": precise,
     }
 
 
