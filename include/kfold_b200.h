@@ -93,6 +93,7 @@ KFB_API int kfb_debug_gemm_trace(void* device_buffer_512_i64, const char* tag);
  * Writes out = update (+ resid).  Arithmetic: bf16 operands, fp32 accumulation and statistics.
  */
 KFB_API size_t kfb_trimul_workspace_bytes(int batch, int n, int c);
+KFB_API size_t kfb_trimul_workspace_bytes_precise(int batch, int n, int c);
 KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mask, const float* ln_in_w,
                            const float* ln_in_b, const void* w_in_packed, const void* w_gout, const float* ln_out_w,
                            const float* ln_out_b, const void* w_pout, void* out, const void* resid, void* workspace,

@@ -40,6 +40,7 @@ static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorM
   if constexpr (BN <= 128) {
     if (p.precise) {
       p.k_main_blocks = (p.k_extent / 6) / kBK;
+      if (p.k_main_blocks == 0) p.k_main_blocks = 1;  // short K: the first block mixes parts, harmless
       if (p.glu) return launch_variant<BN, true, false, true>(stream, ta, tb, tout, p, tag);
       return launch_variant<BN, false, false, true>(stream, ta, tb, tout, p, tag);
     }

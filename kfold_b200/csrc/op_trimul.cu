@@ -145,9 +145,125 @@ int finish(cudaStream_t stream, const __nv_bfloat16* a, const __nv_bfloat16* b, 
   return KFB_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// fp32-accurate variant (KFB_FP32_PRECISE): same six steps, every GEMM operand stored as the bf16 triple split
+// concatenated along K, fp32 intermediates (gate logits, contraction result).
+// ------------------------------------------------------------------------------------------------
+struct TrimulWsPrecise {
+  __nv_bfloat16 *xn6, *ab6;
+  float *gl, *t;
+};
+size_t carve_precise(TrimulWsPrecise& w, void* base, int batch, int n, int c) {
+  Carver cv(base);
+  const size_t pos = static_cast<size_t>(batch) * n * n;
+  w.xn6 = cv.take<__nv_bfloat16>(pos * 6 * c);  // reused as tn6
+  w.ab6 = cv.take<__nv_bfloat16>(pos * 6 * 2 * c);
+  w.gl = cv.take<float>(pos * c);
+  w.t = cv.take<float>(pos * c);
+  return cv.off;
+}
+
+int trimul_precise(cudaStream_t stream, int incoming, const void* x, const unsigned char* mask, const float* ln_in_w,
+                   const float* ln_in_b, const void* w_in6, const void* w_gout6, const float* ln_out_w, const float* ln_out_b,
+                   const void* w_pout6, void* out, const void* resid, const TrimulWsPrecise& w, int batch, int n, int c,
+                   float eps) {
+  const long long nn = static_cast<long long>(n) * n;
+  const long long pos = nn * batch;
+  KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x), w.xn6, ln_in_w, ln_in_b, pos, c, c, eps, 1));
+  {
+    // a -> split pattern 1, b -> pattern 2, both channel-major with the six parts along k: ab6[ch][b][o][6n]
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = n;
+    p.batch = batch;
+    p.n_cols = 4 * c;
+    p.k_extent = 6 * c;
+    p.glu = GLU_SIGMOID;
+    p.precise = 1;
+    p.nseg = 2;
+    for (int i = 0; i < 2; ++i) {
+      EpiSeg& s = p.seg[i];
+      s = {};
+      s.col_begin = i * c;
+      s.ncols = c;
+      s.dst = w.ab6 + static_cast<long long>(i) * c * pos * 6;
+      s.s_col = 6 * pos;
+      s.s_n = 1;
+      s.s_o = 6ll * n;
+      s.s_b = 6 * nn;
+      s.split = i + 1;
+      s.s_part = n;
+    }
+    p.rowmask = mask;
+    p.mask_segs = 3;
+    p.m_b = nn;
+    p.m_o = incoming ? 1 : n;
+    p.m_n = incoming ? n : 1;
+    const long long c6 = 6ll * c;
+    GemmOperandA a = {w.xn6, incoming ? n * c6 : c6, incoming ? c6 : n * c6, nn * c6};
+    GemmOperandB b = {w_in6, c6, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "trimul_in_proj_precise"));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(pos);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(w.gl, c, c, 0, 0, 1);
+    GemmOperandA a = {w.xn6, 6ll * c, 0, 0};
+    GemmOperandB b = {w_gout6, 6ll * c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_gate_proj_precise"));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = 1;
+    p.batch = c * batch;
+    p.n_cols = n;
+    p.k_extent = 6 * n;
+    p.b_batched = 1;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(w.t, n, n, 0, nn, 1);
+    GemmOperandA a = {w.ab6, 6ll * n, 0, 6 * nn};
+    GemmOperandB b = {w.ab6 + static_cast<long long>(c) * pos * 6, 6ll * n, 6 * nn};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_contraction_precise"));
+  }
+  __nv_bfloat16* tn6 = w.xn6;
+  KFB_TRY(launch_layernorm_cm(stream, w.t, tn6, ln_out_w, ln_out_b, batch, nn, c, pos, nn, eps, KFB_FP32, 1));
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(pos);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, 0, 0, 1);
+    p.gate = reinterpret_cast<const __nv_bfloat16*>(w.gl);  // fp32 logits in precise mode
+    p.g_col = 1;
+    p.g_n = c;
+    p.resid = resid;
+    GemmOperandA a = {tn6, 6ll * c, 0, 0};
+    GemmOperandB b = {w_pout6, 6ll * c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "trimul_out_proj_precise"));
+  }
+  return KFB_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+KFB_API size_t kfb_trimul_workspace_bytes_precise(int batch, int n, int c) {
+  TrimulWsPrecise w;
+  return carve_precise(w, nullptr, batch, n, c);
+}
 
 KFB_API size_t kfb_trimul_workspace_bytes(int batch, int n, int c) {
   TrimulWs w;
@@ -161,6 +277,15 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
   KFB_CHECK_ARG(x && mask && w_in_packed && w_gout && w_pout && out && workspace, "trimul: null pointer");
   KFB_CHECK_ARG(is_dtype(dtype), "trimul: bad dtype %d", dtype);
   KFB_TRY(check_shape("trimul", batch, n, n, c));
+  if (dtype == KFB_FP32_PRECISE) {
+    KFB_CHECK_ARG(c <= 256, "trimul: the fp32-accurate mode supports at most 256 channels");
+    TrimulWsPrecise wp;
+    const size_t need_p = carve_precise(wp, workspace, batch, n, c);
+    KFB_CHECK_ARG(workspace_bytes >= need_p, "trimul: workspace %zu < %zu bytes", workspace_bytes, need_p);
+    KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "trimul: workspace must be 256-byte aligned");
+    return trimul_precise(as_stream(stream_), incoming, x, mask, ln_in_w, ln_in_b, w_in_packed, w_gout, ln_out_w, ln_out_b,
+                          w_pout, out, resid, wp, batch, n, c, eps);
+  }
   TrimulWs w;
   const size_t need = carve(w, workspace, batch, n, c);
   KFB_CHECK_ARG(workspace_bytes >= need, "trimul: workspace %zu < %zu bytes", workspace_bytes, need);

@@ -85,14 +85,17 @@ def triangle_multiplication(x: torch.Tensor, mask: torch.Tensor, packed: dict, d
     mp8 = mp.view(torch.uint8)
     out = torch.empty_like(xp)
     lib = L.lib()
+    precise = bool(packed.get("precise"))
+    if precise and xp.dtype != torch.float32:
+        raise ValueError("the fp32-accurate mode takes float32 tensors")
     with torch.cuda.device(x.device):
-        need = lib.kfb_trimul_workspace_bytes(b, npad, c)
+        need = (lib.kfb_trimul_workspace_bytes_precise if precise else lib.kfb_trimul_workspace_bytes)(b, npad, c)
         ws = _workspace(x.device, need)
         L.check(lib.kfb_trimul_fwd(1 if direction == "incoming" else 0, L.ptr(xp), L.ptr(mp8), L.ptr(packed["ln_in_w"]),
                                    L.ptr(packed["ln_in_b"]), L.ptr(packed["w_in"]), L.ptr(packed["w_gout"]),
                                    L.ptr(packed["ln_out_w"]), L.ptr(packed["ln_out_b"]), L.ptr(packed["w_pout"]),
                                    L.ptr(out), L.ptr(xp) if residual else None, L.ptr(ws), ws.numel(), b, npad, c, eps,
-                                   L.dtype_code(xp.dtype), L.stream_ptr()))
+                                   L.KFB_FP32_PRECISE if precise else L.dtype_code(xp.dtype), L.stream_ptr()))
     return out if npad == n else out[:, :n, :n].contiguous()
 
 

@@ -44,18 +44,19 @@ def _dev(t: torch.Tensor, device, dtype) -> torch.Tensor:
     return t.detach().to(device=device, dtype=dtype).contiguous()
 
 
-def pack_trimul(w: dict, device, dtype=torch.bfloat16) -> dict:
+def pack_trimul(w: dict, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Weights of TriangleMultiplication{Outgoing,Incoming}: keys as in the reference state_dict
     (model/primitives/triangle_multiplication.py:171-177).  LayerNorm affine stays fp32."""
     return {
         "ln_in_w": _dev(w["layernorm_in.weight"], device, torch.float32),
         "ln_in_b": _dev(w["layernorm_in.bias"], device, torch.float32),
-        "w_in": _dev(interleave_glu(w["linear_p_in.weight"], w["linear_g_in.weight"]), device, dtype),
-        "w_gout": _dev(w["linear_g_out.weight"], device, dtype),
+        "w_in": _w(interleave_glu(w["linear_p_in.weight"].detach().float(), w["linear_g_in.weight"].detach().float(),
+                                  GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_gout": _w(w["linear_g_out.weight"], device, precise),
         "ln_out_w": _dev(w["layernorm_out.weight"], device, torch.float32),
         "ln_out_b": _dev(w["layernorm_out.bias"], device, torch.float32),
-        "w_pout": _dev(w["linear_p_out.weight"], device, dtype),
-        "c": int(w["linear_p_out.weight"].shape[0]),
+        "w_pout": _w(w["linear_p_out.weight"], device, precise),
+        "c": int(w["linear_p_out.weight"].shape[0]), "precise": precise,
     }
 
 
