@@ -113,6 +113,7 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
  * uniform average of V, exactly as the reference does.  batch*n must not exceed 65535.
  */
 KFB_API size_t kfb_triatt_workspace_bytes(int batch, int n, int c, int heads);
+KFB_API size_t kfb_triatt_workspace_bytes_precise(int batch, int n, int c, int heads);
 KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask, const float* ln_w, const float* ln_b,
                            const void* w_proj_packed, const void* w_out, void* out, const void* resid, void* workspace,
                            size_t workspace_bytes, int batch, int n, int c, int heads, float eps, int dtype, void* stream);
@@ -162,6 +163,7 @@ KFB_API int kfb_triatt_finish(const void* qkg, const void* vt, const void* bias_
  * With transposed != 0 the result is written as bias_out[b, h, j, i].
  */
 KFB_API size_t kfb_pair_bias_workspace_bytes(int batch, int n, int c);
+KFB_API size_t kfb_pair_bias_workspace_bytes_precise(int batch, int n, int c);
 KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
                               void* workspace, size_t workspace_bytes, int batch, int n, int c, int heads, int transposed,
                               float eps, int dtype, void* stream);
@@ -179,8 +181,11 @@ KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_
  *   gate sigmoid(Linear(s)) of SelfAttentionPairBias.forward (src/kfold/model/layers/folding/
  *   attention_pair_bias.py:155-157), shared by `gate_share` consecutive batch entries;
  *   resid : NULL or a tensor like out that is added.
+ * With out_dtype = KFB_FP32_PRECISE every tensor argument (x, pair_bias, out_gate, out, resid) is fp32, the weights
+ * come from the precise packing (heads not padded) and the attention core runs on the fp32 CUDA-core kernel.
  */
 KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads);
+KFB_API size_t kfb_apb_workspace_bytes_precise(int batch, int l, int c);
 KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
                         const float* proj_bias, const void* w_out, const float* out_bias, const void* out_gate,
                         int gate_share, void* out, const void* resid, void* workspace, size_t workspace_bytes, int batch,

@@ -58,6 +58,9 @@ _SIGNATURES = {
                                   c_float, c_int, c_void_p],
 }
 _SIZE_FUNCS = {
+    "kfb_triatt_workspace_bytes_precise": [c_int, c_int, c_int, c_int],
+    "kfb_apb_workspace_bytes_precise": [c_int, c_int, c_int],
+    "kfb_pair_bias_workspace_bytes_precise": [c_int, c_int, c_int],
     "kfb_trimul_workspace_bytes_precise": [c_int, c_int, c_int],
     "kfb_transition_workspace_bytes_precise": [c_ll, c_int, c_int],
     "kfb_cond_transition_workspace_bytes": [c_ll, c_int],

@@ -40,10 +40,13 @@ def _compute_dtype(x: torch.Tensor) -> torch.dtype:
     return x.dtype
 
 
-def _require_bf16(dt: torch.dtype, what: str) -> None:
-    if dt != torch.bfloat16:
-        raise NotImplementedError(f"The B200 {what} backend computes in bfloat16; got compute dtype {dt} "
-                                  "(run under torch.autocast('cuda', dtype=torch.bfloat16))")
+def _is_precise(dt: torch.dtype, what: str) -> bool:
+    """bfloat16 compute -> the tensor-core path; float32 compute -> the fp32-accurate path."""
+    if dt == torch.bfloat16:
+        return False
+    if dt == torch.float32:
+        return True
+    raise NotImplementedError(f"The B200 {what} backend computes in bfloat16 or float32; got compute dtype {dt}")
 
 
 def _cached_pack(module: torch.nn.Module, x: torch.Tensor, dtype: torch.dtype, slot: str, pack_fn):
@@ -67,10 +70,10 @@ def b200_triangular_mult(module: torch.nn.Module, x: torch.Tensor, mask: torch.T
     """Stands where ``triton_triangluar_mult(module, x, mask, direction)`` stands."""
     _check(x, "triangle multiplication")
     cd = _compute_dtype(x)
-    _require_bf16(cd, "triangle multiplication")
-    pk = _cached_pack(module, x, cd, "trimul", packing.pack_trimul)
+    precise = _is_precise(cd, "triangle multiplication")
+    pk = _cached_pack(module, x, cd, "trimul", lambda sd, dev: packing.pack_trimul(sd, dev, precise=precise))
     with torch.autocast(x.device.type, enabled=False):
-        out = F.triangle_multiplication(x, mask.bool(), pk, direction, eps=module.layernorm_in.eps)
+        out = F.triangle_multiplication(x.float() if precise else x, mask.bool(), pk, direction, eps=module.layernorm_in.eps)
     return out.to(x.dtype)
 
 
@@ -80,11 +83,13 @@ def b200_triangular_attn(module: torch.nn.Module, x: torch.Tensor, mask: torch.T
     the ending node is handled inside the kernels."""
     _check(x, "triangle attention")
     cd = _compute_dtype(x)
-    _require_bf16(cd, "triangle attention")
+    precise = _is_precise(cd, "triangle attention")
     heads = module.no_heads
-    pk = _cached_pack(module, x, cd, "triatt", lambda sd, dev: packing.pack_triatt(sd, heads, dev))
+    pk = _cached_pack(module, x, cd, "triatt", lambda sd, dev: packing.pack_triatt(sd, heads, dev, precise=precise))
     lead = x.shape[:-3]
     x4 = x.reshape(-1, *x.shape[-3:])
+    if precise:
+        x4 = x4.float()
     m4 = None if mask is None else mask.reshape(-1, *mask.shape[-2:]).bool()
     with torch.autocast(x.device.type, enabled=False):
         out = F.triangle_attention(x4, m4, pk, starting, eps=module.layer_norm.eps)
@@ -105,17 +110,17 @@ def b200_attention_pair_bias(module, x_q, x_k, pair_bias, mask, *, call_site: st
     if x_q is not x_k:
         raise NotImplementedError("The B200 pair-bias attention backend handles self-attention call sites only")
     cd = _compute_dtype(x_q)
-    _require_bf16(cd, "pair-bias attention")
+    precise = _is_precise(cd, "pair-bias attention")
     heads = module.num_heads
     keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight",
             "linear_g.bias", "linear_out.weight", "linear_out.bias")
 
     def pack(sd, dev):
-        return packing.pack_apb({k: sd[k] for k in keys if k in sd}, heads, dev)
+        return packing.pack_apb({k: sd[k] for k in keys if k in sd}, heads, dev, precise=precise)
 
     pk = _cached_pack(module, x_q, cd, "apb", pack)
     with torch.autocast(x_q.device.type, enabled=False):
-        out = F.attention_pair_bias(x_q, pair_bias, mask, pk, out_dtype=x_q.dtype)
+        out = F.attention_pair_bias(x_q.float() if precise else x_q, pair_bias, mask, pk, out_dtype=x_q.dtype)
     return out
 
 
@@ -192,9 +197,10 @@ def install() -> None:
 def convert(model: torch.nn.Module, diffusion: bool = False) -> int:
     """Switch every supported module of a constructed model to the ``"b200"`` backend; returns how many.
 
-    The sampler's token transformer runs in float32 in K-Fold (model/model.py:409-429); the kernels compute in
-    bfloat16 and refuse float32 compute, so its attention modules (call site "diffusion_global") are left alone
-    unless ``diffusion`` is set (for callers that run the sampler under bf16 autocast).
+    The sampler's token transformer runs in float32 in K-Fold (model/model.py:409-429).  Under float32 compute the
+    backend takes its fp32-accurate path (split-operand GEMMs around a CUDA-core attention kernel), which is
+    correct but slow; its attention modules (call site "diffusion_global") are therefore left alone unless
+    ``diffusion`` is set.
     """
     n = 0
     for m in model.modules():

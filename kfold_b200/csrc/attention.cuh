@@ -23,6 +23,8 @@
 // for pair-bias attention on the single / token track (bias shared by `bias_div` consecutive
 // batch entries, mask per batch entry).
 #pragma once
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace kfb {
@@ -51,6 +53,21 @@ struct AttnParams {
 };
 
 int launch_attention(cudaStream_t stream, const AttnParams& p);
+
+// fp32-accurate mode: q, k, v, g are columns of ONE fp32 row-major buffer (row = batch * L + position, `ld`
+// floats per row, head h at col0 + h*d, no padding); bias fp32 [bias_batches][heads][lq][ldb]; the result is the
+// bf16 triple split [rows][6 * heads * d].
+struct AttnFp32Params {
+  int batch, heads, lq, lk, d;
+  const float *q, *k, *v, *g;  // same base pointer allowed; g may be null
+  long long ld;
+  int q_col0, k_col0, v_col0, g_col0;
+  const float* bias; long long ldb; int bias_div;
+  const unsigned char* mask; long long m_hi, m_lo, m_k; int mask_lo_extent;
+  __nv_bfloat16* out6;
+  const char* tag;
+};
+int launch_attention_fp32(cudaStream_t stream, const AttnFp32Params& p);
 
 // Debugging aid: a device buffer of >= 512 long longs that receives pipeline time stamps (nullptr = off).
 void set_attention_trace(long long* device_buffer);

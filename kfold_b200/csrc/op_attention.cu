@@ -49,9 +49,125 @@ size_t carve_apb(ApbWs& w, void* base, int batch, int l, int c, int heads) {
   return cv.off;
 }
 
+// ------------------------------------------------------------------------------------------------
+// fp32-accurate variants (KFB_FP32_PRECISE): split-operand GEMMs around the fp32 attention kernel.
+// ------------------------------------------------------------------------------------------------
+struct TriattWsPrecise {
+  __nv_bfloat16 *xn6, *og6;
+  float *qkgv, *bias;
+};
+size_t carve_triatt_precise(TriattWsPrecise& w, void* base, int batch, int n, int c, int heads) {
+  Carver cv(base);
+  const size_t pos = static_cast<size_t>(batch) * n * n;
+  w.xn6 = cv.take<__nv_bfloat16>(pos * 6 * c);
+  w.og6 = cv.take<__nv_bfloat16>(pos * 6 * c);
+  w.qkgv = cv.take<float>(pos * 4 * c);
+  w.bias = cv.take<float>(pos * heads);
+  return cv.off;
+}
+
+int triatt_precise(cudaStream_t stream, int ending, const void* x, const unsigned char* mask, const float* ln_w,
+                   const float* ln_b, const void* w_proj6, const void* w_out6, void* out, const void* resid,
+                   const TriattWsPrecise& w, int batch, int n, int c, int heads, float eps) {
+  const int d = c / heads;
+  const long long nn = static_cast<long long>(n) * n;
+  const long long pos = nn * batch;
+  KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x), w.xn6, ln_w, ln_b, pos, c, c, eps, 1));
+  {
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = n;
+    p.batch = batch;
+    p.n_cols = 4 * c + 32;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 2;
+    p.seg[0] = row_major_seg(w.qkgv, 4 * c, 4 * c, static_cast<long long>(n) * 4 * c, nn * 4 * c, 1, 0);
+    EpiSeg& sb = p.seg[1];
+    sb = {};
+    sb.col_begin = 4 * c;
+    sb.ncols = heads;
+    sb.out_fp32 = 1;
+    sb.dst = w.bias;
+    sb.s_col = nn;
+    sb.s_n = 1;
+    sb.s_o = n;
+    sb.s_b = static_cast<long long>(heads) * nn;
+    const long long c6 = 6ll * c;
+    GemmOperandA a = {w.xn6, ending ? n * c6 : c6, ending ? c6 : n * c6, nn * c6};
+    GemmOperandB b = {w_proj6, c6, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "triatt_proj_precise"));
+  }
+  {
+    AttnFp32Params p = {};
+    p.batch = batch * n;
+    p.heads = heads;
+    p.lq = n;
+    p.lk = n;
+    p.d = d;
+    p.q = p.k = p.v = p.g = w.qkgv;
+    p.ld = 4 * c;
+    p.q_col0 = 0; p.k_col0 = c; p.g_col0 = 2 * c; p.v_col0 = 3 * c;
+    p.bias = w.bias; p.ldb = n; p.bias_div = n;
+    p.mask = mask;
+    p.mask_lo_extent = n;
+    p.m_hi = nn;
+    p.m_lo = ending ? 1 : n;
+    p.m_k = ending ? n : 1;
+    p.out6 = w.og6;
+    p.tag = "triatt_attention_fp32";
+    KFB_TRY(launch_attention_fp32(stream, p));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = n;
+    p.batch = batch;
+    p.n_cols = c;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, ending ? static_cast<long long>(n) * c : c, ending ? c : static_cast<long long>(n) * c,
+                             nn * c, 1);
+    p.resid = resid;
+    const long long c6 = 6ll * c;
+    GemmOperandA a = {w.og6, c6, n * c6, nn * c6};
+    GemmOperandB b = {w_out6, c6, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "triatt_out_proj_precise"));
+  }
+  return KFB_OK;
+}
+
+struct ApbWsPrecise {
+  __nv_bfloat16 *x6, *og6;
+  float* qkgv;
+};
+size_t carve_apb_precise(ApbWsPrecise& w, void* base, int batch, int l, int c) {
+  Carver cv(base);
+  const size_t rows = static_cast<size_t>(batch) * l;
+  w.x6 = cv.take<__nv_bfloat16>(rows * 6 * c);
+  w.og6 = cv.take<__nv_bfloat16>(rows * 6 * c);
+  w.qkgv = cv.take<float>(rows * 4 * c);
+  return cv.off;
+}
+
 }  // namespace
 
 extern "C" {
+
+KFB_API size_t kfb_triatt_workspace_bytes_precise(int batch, int n, int c, int heads) {
+  TriattWsPrecise w;
+  return carve_triatt_precise(w, nullptr, batch, n, c, heads);
+}
+
+KFB_API size_t kfb_apb_workspace_bytes_precise(int batch, int l, int c) {
+  ApbWsPrecise w;
+  return carve_apb_precise(w, nullptr, batch, l, c);
+}
+
+KFB_API size_t kfb_pair_bias_workspace_bytes_precise(int batch, int n, int c) {
+  return align_up(static_cast<size_t>(batch) * n * n * 6 * c * sizeof(__nv_bfloat16), 256);
+}
 
 KFB_API size_t kfb_triatt_workspace_bytes(int batch, int n, int c, int heads) {
   TriattWs w;
@@ -68,6 +184,14 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
   const int d = c / heads;
   KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "triatt: head dim %d not in {16, 24, ..., 64}", d);
   KFB_CHECK_ARG(static_cast<long long>(batch) * n <= 65535, "triatt: batch*N = %lld exceeds 65535", static_cast<long long>(batch) * n);
+  if (dtype == KFB_FP32_PRECISE) {
+    TriattWsPrecise wp;
+    const size_t need_p = carve_triatt_precise(wp, workspace, batch, n, c, heads);
+    KFB_CHECK_ARG(workspace_bytes >= need_p, "triatt: workspace %zu < %zu bytes", workspace_bytes, need_p);
+    KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "triatt: workspace must be 256-byte aligned");
+    return triatt_precise(as_stream(stream_), ending, x, mask, ln_w, ln_b, w_proj_packed, w_out, out, resid, wp, batch, n, c,
+                          heads, eps);
+  }
   const int dp = dpad_of(d), hdp = heads * dp;
   TriattWs w;
   const size_t need = carve_triatt(w, workspace, batch, n, c, heads);
@@ -285,8 +409,37 @@ KFB_API int kfb_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_
   KFB_CHECK_ARG(is_dtype(dtype), "pair_bias: bad dtype %d", dtype);
   KFB_CHECK_ARG(batch >= 1 && n >= 8 && n % 8 == 0 && c % 8 == 0 && heads >= 1, "pair_bias: batch %d n %d c %d heads %d",
                 batch, n, c, heads);
-  KFB_CHECK_ARG(workspace_bytes >= kfb_pair_bias_workspace_bytes(batch, n, c), "pair_bias: workspace too small");
   KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "pair_bias: workspace must be 256-byte aligned");
+  if (dtype == KFB_FP32_PRECISE) {
+    // fp32 in, fp32 bias out, split-operand GEMM
+    KFB_CHECK_ARG(workspace_bytes >= kfb_pair_bias_workspace_bytes_precise(batch, n, c), "pair_bias: workspace too small");
+    cudaStream_t stream = as_stream(stream_);
+    const long long nn = static_cast<long long>(n) * n;
+    __nv_bfloat16* zn6 = static_cast<__nv_bfloat16*>(workspace);
+    KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(z), zn6, ln_w, ln_b, nn * batch, c, c, eps, 1));
+    GemmParams p = {};
+    p.n_extent = n;
+    p.o_extent = n;
+    p.batch = batch;
+    p.n_cols = heads;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 1;
+    EpiSeg& sg = p.seg[0];
+    sg.col_begin = 0;
+    sg.ncols = heads;
+    sg.out_fp32 = 1;
+    sg.dst = bias_out;
+    sg.s_col = nn;
+    sg.s_n = transposed ? n : 1;
+    sg.s_o = transposed ? 1 : n;
+    sg.s_b = static_cast<long long>(heads) * nn;
+    const long long c6 = 6ll * c;
+    GemmOperandA a = {zn6, c6, n * c6, nn * c6};
+    GemmOperandB b = {w, c6, 0};
+    return launch_gemm_bf16(stream, a, b, p, 0, "pair_bias_proj_precise");
+  }
+  KFB_CHECK_ARG(workspace_bytes >= kfb_pair_bias_workspace_bytes(batch, n, c), "pair_bias: workspace too small");
   return pair_bias_impl(z, ln_w, ln_b, w, bias_out, workspace, batch, n, n, c, heads, transposed, eps, dtype, as_stream(stream_));
 }
 
@@ -323,6 +476,74 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     gate_share = 1;
   const int d = c / heads;
   KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "apb: head dim %d not in {16, 24, ..., 64}", d);
+  if (out_dtype == KFB_FP32_PRECISE) {
+    // everything fp32: x, pair_bias, out_gate logits, out, resid; weights from the precise packing
+    ApbWsPrecise wp;
+    const size_t need_p = carve_apb_precise(wp, workspace, batch, l, c);
+    KFB_CHECK_ARG(workspace_bytes >= need_p, "apb: workspace %zu < %zu bytes", workspace_bytes, need_p);
+    KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "apb: workspace must be 256-byte aligned");
+    cudaStream_t stream = as_stream(stream_);
+    const long long rows = static_cast<long long>(batch) * l;
+    const long long c6 = 6ll * c;
+    KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x), wp.x6, nullptr, nullptr, rows, c, c, 0.f, 0));
+    {
+      GemmParams p = {};
+      p.n_extent = static_cast<int>(rows);
+      p.o_extent = 1;
+      p.batch = 1;
+      p.n_cols = 4 * c;
+      p.k_extent = 6 * c;
+      p.precise = 1;
+      p.nseg = 1;
+      p.seg[0] = row_major_seg(wp.qkgv, 4 * c, 4 * c, 0, 0, 1);
+      p.col_bias = proj_bias;
+      GemmOperandA a = {wp.x6, c6, 0, 0};
+      GemmOperandB b = {w_proj_packed, c6, 0};
+      KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "apb_proj_precise"));
+    }
+    {
+      AttnFp32Params p = {};
+      p.batch = batch;
+      p.heads = heads;
+      p.lq = l;
+      p.lk = l;
+      p.d = d;
+      p.q = p.k = p.v = p.g = wp.qkgv;
+      p.ld = 4 * c;
+      p.q_col0 = 0; p.k_col0 = c; p.g_col0 = 2 * c; p.v_col0 = 3 * c;
+      p.bias = static_cast<const float*>(pair_bias); p.ldb = l; p.bias_div = bias_div;
+      p.mask = mask;
+      p.mask_lo_extent = 1;
+      p.m_hi = l;
+      p.m_lo = 0;
+      p.m_k = 1;
+      p.out6 = wp.og6;
+      p.tag = "apb_attention_fp32";
+      KFB_TRY(launch_attention_fp32(stream, p));
+    }
+    GemmParams p = {};
+    p.n_extent = l;
+    p.o_extent = gate_share;
+    p.batch = batch / gate_share;
+    p.n_cols = c;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 1;
+    const long long lc = static_cast<long long>(l) * c;
+    p.seg[0] = row_major_seg(out, c, c, lc, lc * gate_share, 1);
+    p.col_bias = out_bias;
+    p.resid = resid;
+    if (out_gate != nullptr) {
+      p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // fp32 logits in this mode
+      p.g_col = 1;
+      p.g_n = c;
+      p.g_o = 0;
+      p.g_b = lc;
+    }
+    GemmOperandA a = {wp.og6, c6, l * c6, l * c6 * gate_share};
+    GemmOperandB b = {w_out, c6, 0};
+    return launch_gemm_bf16(stream, a, b, p, 0, "apb_out_proj_precise");
+  }
   const int dp = dpad_of(d), hdp = heads * dp;
   ApbWs w;
   const size_t need = carve_apb(w, workspace, batch, l, c, heads);

@@ -117,12 +117,16 @@ def triangle_attention(x: torch.Tensor, mask: torch.Tensor | None, packed: dict,
     b, npad = xp.shape[0], xp.shape[1]
     out = torch.empty_like(xp)
     lib = L.lib()
+    precise = bool(packed.get("precise"))
+    if precise and xp.dtype != torch.float32:
+        raise ValueError("the fp32-accurate mode takes float32 tensors")
     with torch.cuda.device(x.device):
-        ws = _workspace(x.device, lib.kfb_triatt_workspace_bytes(b, npad, c, heads))
+        need = (lib.kfb_triatt_workspace_bytes_precise if precise else lib.kfb_triatt_workspace_bytes)(b, npad, c, heads)
+        ws = _workspace(x.device, need)
         L.check(lib.kfb_triatt_fwd(0 if starting else 1, L.ptr(xp), L.ptr(mp.view(torch.uint8)), L.ptr(packed["ln_w"]),
                                    L.ptr(packed["ln_b"]), L.ptr(packed["w_proj"]), L.ptr(packed["w_out"]), L.ptr(out),
                                    L.ptr(xp) if residual else None, L.ptr(ws), ws.numel(), b, npad, c, heads, eps,
-                                   L.dtype_code(xp.dtype), L.stream_ptr()))
+                                   L.KFB_FP32_PRECISE if precise else L.dtype_code(xp.dtype), L.stream_ptr()))
     return out if npad == n else out[:, :n, :n].contiguous()
 
 
@@ -210,8 +214,10 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
         pb_lead, nb = tuple(lead), batch
     bias_div = batch // nb
     lp = (l + 7) // 8 * 8
-    xb = x.reshape(batch, l, c).to(torch.bfloat16)
-    pbb = pb.reshape(nb, heads, l, l).to(torch.bfloat16)
+    precise = bool(packed.get("precise"))
+    act = torch.float32 if precise else torch.bfloat16     # dtype of the activations handed to the kernels
+    xb = x.reshape(batch, l, c).to(act)
+    pbb = pb.reshape(nb, heads, l, l).to(act)
     mb = mask.to(torch.bool).expand(*lead, l).reshape(batch, l)
     if lp != l:
         xb = torch.nn.functional.pad(xb, (0, 0, 0, lp - l))
@@ -219,26 +225,30 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
         mb = torch.nn.functional.pad(mb, (0, lp - l))
     gate = None
     if out_gate is not None:
-        gate = out_gate.reshape(-1, l, c).to(torch.bfloat16)
+        gate = out_gate.reshape(-1, l, c).to(act)
         if lp != l:
             gate = torch.nn.functional.pad(gate, (0, 0, 0, lp - l))
         gate = gate.contiguous()
     res = None
     if resid is not None:
         res = resid.reshape(batch, l, c)
+        if precise:
+            res = res.float()
         if lp != l:
             res = torch.nn.functional.pad(res, (0, 0, 0, lp - l))
         res = res.contiguous()
     xb, pbb, mb = xb.contiguous(), pbb.contiguous(), mb.contiguous()
-    out = torch.empty(batch, lp, c, dtype=out_dtype or (resid.dtype if resid is not None else x.dtype), device=x.device)
+    want = out_dtype or (resid.dtype if resid is not None else x.dtype)
+    out = torch.empty(batch, lp, c, dtype=torch.float32 if precise else want, device=x.device)
     lib = L.lib()
     with torch.cuda.device(x.device):
-        ws = _workspace(x.device, lib.kfb_apb_workspace_bytes(batch, lp, c, heads))
+        need = lib.kfb_apb_workspace_bytes_precise(batch, lp, c) if precise else lib.kfb_apb_workspace_bytes(batch, lp, c, heads)
+        ws = _workspace(x.device, need)
         L.check(lib.kfb_apb_fwd(L.ptr(xb), L.ptr(pbb), L.ptr(mb.view(torch.uint8)), L.ptr(packed["w_proj"]),
                                 L.ptr(packed["proj_bias"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
                                 gate_share, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div,
-                                L.dtype_code(out.dtype), L.stream_ptr()))
-    return out[:, :l].reshape(*lead, l, c)
+                                L.KFB_FP32_PRECISE if precise else L.dtype_code(out.dtype), L.stream_ptr()))
+    return out[:, :l].reshape(*lead, l, c).to(want)
 
 
 def transition(x: torch.Tensor, packed: dict, eps: float = 1e-5, residual: bool = False) -> torch.Tensor:
@@ -275,13 +285,18 @@ def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.
     if n % 8 != 0:
         raise ValueError("pair_bias: N must be a multiple of 8")
     heads = w.shape[0]
-    out = torch.empty(b, heads, n, n, dtype=torch.bfloat16, device=z.device)
+    precise = w.shape[1] == 6 * c          # the weight as a bf16 triple split (packing.split3_weights)
+    if precise and z.dtype != torch.float32:
+        raise ValueError("the fp32-accurate mode takes float32 tensors")
+    out = torch.empty(b, heads, n, n, dtype=torch.float32 if precise else torch.bfloat16, device=z.device)
     zc = z.contiguous()
     lib = L.lib()
     with torch.cuda.device(z.device):
-        ws = _workspace(z.device, lib.kfb_pair_bias_workspace_bytes(b, n, c))
+        need = (lib.kfb_pair_bias_workspace_bytes_precise if precise else lib.kfb_pair_bias_workspace_bytes)(b, n, c)
+        ws = _workspace(z.device, need)
         L.check(lib.kfb_pair_bias_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), b, n,
-                                      c, heads, 1 if transposed else 0, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
+                                      c, heads, 1 if transposed else 0, eps,
+                                      L.KFB_FP32_PRECISE if precise else L.dtype_code(zc.dtype), L.stream_ptr()))
     return out
 
 

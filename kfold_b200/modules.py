@@ -102,6 +102,15 @@ def _require_bf16(dt: torch.dtype, what: str) -> None:
             "torch.autocast('cuda', dtype=torch.bfloat16) or pass bfloat16 inputs")
 
 
+def _is_precise(dt: torch.dtype, what: str) -> bool:
+    """bfloat16 compute -> the tensor-core path; float32 compute -> the fp32-accurate path (split operands)."""
+    if dt == torch.bfloat16:
+        return False
+    if dt == torch.float32:
+        return True
+    raise NotImplementedError(f"{what}: compute dtype {dt} is not available (bfloat16 and float32 are)")
+
+
 class _PackedMixin:
     """Packs the module's weights once and re-packs when any parameter changes
     (same cache key as model/primitives/triangle_multiplication.py:73-91)."""
@@ -140,10 +149,11 @@ class _TriangleMultiplication(nn.Module, _PackedMixin):
         """x (B,N,N,D), mask (B,N,N) -> update (B,N,N,D); with ``residual`` returns x + update."""
         _check_inference(x)
         cd = compute_dtype(x)
-        _require_bf16(cd, type(self).__name__)
-        pk = self._packed(x.device, cd, packing.pack_trimul)
+        precise = _is_precise(cd, type(self).__name__)
+        pk = self._packed(x.device, cd, lambda sd, dev: packing.pack_trimul(sd, dev, precise=precise))
         with torch.autocast(x.device.type, enabled=False):
-            out = F.triangle_multiplication(x, mask, pk, self.direction, eps=self.layernorm_in.eps, residual=residual)
+            out = F.triangle_multiplication(x.float() if precise else x, mask, pk, self.direction,
+                                            eps=self.layernorm_in.eps, residual=residual)
         return out.to(x.dtype)
 
 
@@ -184,10 +194,12 @@ class _TriangleAttention(nn.Module, _PackedMixin):
         """x (*,I,J,C), mask (*,I,J) or None -> update (*,I,J,C)."""
         _check_inference(x)
         cd = compute_dtype(x)
-        _require_bf16(cd, type(self).__name__)
-        pk = self._packed(x.device, cd, lambda sd, dev: packing.pack_triatt(sd, self.no_heads, dev))
+        precise = _is_precise(cd, type(self).__name__)
+        pk = self._packed(x.device, cd, lambda sd, dev: packing.pack_triatt(sd, self.no_heads, dev, precise=precise))
         lead = x.shape[:-3]
         x4 = x.reshape(-1, *x.shape[-3:])
+        if precise:
+            x4 = x4.float()
         m4 = None if mask is None else mask.reshape(-1, *mask.shape[-2:])
         with torch.autocast(x.device.type, enabled=False):
             out = F.triangle_attention(x4, m4, pk, self.starting, eps=self.layer_norm.eps, residual=residual)
@@ -214,10 +226,10 @@ class Transition(nn.Module, _PackedMixin):
     def forward(self, x: torch.Tensor, residual: bool = False) -> torch.Tensor:
         _check_inference(x)
         cd = compute_dtype(x)
-        _require_bf16(cd, "Transition")
-        pk = self._packed(x.device, cd, packing.pack_transition)
+        precise = _is_precise(cd, "Transition")
+        pk = self._packed(x.device, cd, lambda sd, dev: packing.pack_transition(sd, dev, precise=precise))
         with torch.autocast(x.device.type, enabled=False):
-            out = F.transition(x, pk, eps=self.layernorm.eps, residual=residual)
+            out = F.transition(x.float() if precise else x, pk, eps=self.layernorm.eps, residual=residual)
         return out.to(x.dtype)
 
 
@@ -283,11 +295,11 @@ class SelfAttentionPairBias(nn.Module, _PackedMixin):
         self._ada_w = None
         self._ada_key = None
 
-    def _apb_packed(self, device):
+    def _apb_packed(self, device, precise: bool = False):
         keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight",
                 "linear_out.weight")
-        return self._packed(device, torch.bfloat16,
-                            lambda sd, dev: packing.pack_apb({k: sd[k] for k in keys}, self.num_heads, dev))
+        return self._packed(device, torch.float32 if precise else torch.bfloat16,
+                            lambda sd, dev: packing.pack_apb({k: sd[k] for k in keys}, self.num_heads, dev, precise=precise))
 
     def _ada_out(self, device):
         w, b = self.linear_ada_out.weight, self.linear_ada_out.bias
@@ -303,9 +315,16 @@ class SelfAttentionPairBias(nn.Module, _PackedMixin):
         """a (...,L,c_a); s (...,L,c_s) or None; pair_bias (...,H,L,L); mask (...,L) -> (...,L,c_a).
         With ``residual`` the result is a + update (fused into the last kernel)."""
         _check_inference(a)
-        _require_bf16(compute_dtype(a), "SelfAttentionPairBias")
-        pk = self._apb_packed(a.device)
+        precise = _is_precise(compute_dtype(a), "SelfAttentionPairBias")
+        if precise and self.use_single_conditioning:
+            raise NotImplementedError("SelfAttentionPairBias with single conditioning computes in bfloat16 only; run the "
+                                      "sampler's token transformer under torch.autocast('cuda', dtype=torch.bfloat16)")
+        pk = self._apb_packed(a.device, precise)
         with torch.autocast(a.device.type, enabled=False):
+            if precise:
+                an = F.layer_norm(a.float(), self.layernorm_a.weight, self.layernorm_a.bias, self.layernorm_a.eps,
+                                  out_dtype=torch.float32)
+                return F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype, resid=a if residual else None)
             if self.use_single_conditioning:
                 assert s is not None
                 share = _sample_share(a, s)
@@ -428,9 +447,10 @@ class PairformerBlock(nn.Module):
 
     def _pair_bias(self, z: torch.Tensor) -> torch.Tensor:
         p = self.linear_pair_bias.weight
-        key = (z.device, p.data_ptr(), None if torch.is_inference(p) else p._version)
+        precise = z.dtype == torch.float32
+        key = (z.device, precise, p.data_ptr(), None if torch.is_inference(p) else p._version)
         if self._bias_key != key:
-            self._bias_w = p.detach().to(z.device, torch.bfloat16).contiguous()
+            self._bias_w = packing.split3_weights(p).to(z.device) if precise else p.detach().to(z.device, torch.bfloat16).contiguous()
             self._bias_key = key
         n = z.shape[1]
         if n % 8 != 0:  # rare: pad the pair tensor so that bias rows stay 16-byte aligned
@@ -452,7 +472,7 @@ class PairformerBlock(nn.Module):
         z = self.tri_att_end(z, pair_mask, residual=True)
         z = self.transition_z(z, residual=True)
         with torch.autocast(z.device.type, enabled=False):
-            bias = self._pair_bias(z)
+            bias = self._pair_bias(z if compute_dtype(z) == z.dtype else z.to(compute_dtype(z)))
         s = self.attention(s, None, bias, mask, residual=True)
         s = self.transition(s, residual=True)
         return z, s

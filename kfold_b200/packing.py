@@ -75,14 +75,28 @@ def _pad_heads(w: torch.Tensor, heads: int, d: int, dp: int, scale: float = 1.0)
     return out.reshape((heads * dp,) + tuple(tail))
 
 
-def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
+def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Weights of TriangleAttention (model/primitives/triangle_attention.py:338-373).
 
     One projection matrix [q / sqrt(D) | k | g | v | triangle-bias] with every head padded to the
-    kernel's head stride and the bias rows padded to 32.
+    kernel's head stride and the bias rows padded to 32.  The fp32-accurate packing keeps the heads unpadded
+    and stores every matrix as its bf16 triple split.
     """
     c = int(w["mha.linear_q.weight"].shape[1])
     d = c // heads
+    if precise:
+        g = lambda k, s=1.0: w[k].detach().float() * s
+        wz_p = torch.zeros(32, c)
+        wz_p[:heads] = w["linear.weight"].detach().float()
+        proj = torch.cat([g("mha.linear_q.weight", d ** -0.5), g("mha.linear_k.weight"), g("mha.linear_g.weight"),
+                          g("mha.linear_v.weight"), wz_p.to(w["linear.weight"].device)], dim=0)
+        return {
+            "ln_w": _dev(w["layer_norm.weight"], device, torch.float32),
+            "ln_b": _dev(w["layer_norm.bias"], device, torch.float32),
+            "w_proj": _w(proj, device, True),
+            "w_out": _w(w["mha.linear_o.weight"], device, True),
+            "c": c, "heads": heads, "precise": True,
+        }
     dp = head_dim_pad(d)
     f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
     wz = w["linear.weight"].detach().float()
@@ -99,11 +113,29 @@ def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
     }
 
 
-def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16) -> dict:
+def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Projections of AttentionPairBias (model/layers/folding/attention_pair_bias.py:30-67):
-    [q / sqrt(D) (+ bias, same scale) | k | g | v], heads padded; output projection as is."""
+    [q / sqrt(D) (+ bias, same scale) | k | g | v], heads padded; output projection as is.
+    The fp32-accurate packing keeps the heads unpadded and stores the matrices as bf16 triple splits."""
     c = int(w["linear_q.weight"].shape[1])
     d = c // heads
+    if precise:
+        qs = d ** -0.5
+        g = lambda k, s=1.0: w[k].detach().float() * s
+        proj = torch.cat([g("linear_q.weight", qs), g("linear_k.weight"), g("linear_g.weight"), g("linear_v.weight")], dim=0)
+        pb = torch.zeros(4 * c, dtype=torch.float32)
+        if w.get("linear_q.bias") is not None:
+            pb[:c] = w["linear_q.bias"].detach().float().cpu() * qs
+        if w.get("linear_g.bias") is not None:
+            pb[2 * c: 3 * c] = w["linear_g.bias"].detach().float().cpu()
+        ob = w.get("linear_out.bias")
+        return {
+            "w_proj": _w(proj, device, True),
+            "proj_bias": _dev(pb, device, torch.float32),
+            "w_out": _w(w["linear_out.weight"], device, True),
+            "out_bias": None if ob is None else _dev(ob, device, torch.float32),
+            "c": c, "heads": heads, "precise": True,
+        }
     dp = head_dim_pad(d)
     f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
     qs = d ** -0.5

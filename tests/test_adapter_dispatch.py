@@ -25,7 +25,6 @@ def recorder(monkeypatch):
     from kfold_b200 import adapter
     calls = []
     monkeypatch.setattr(adapter, "_check", lambda x, what: None)
-    monkeypatch.setattr(adapter, "_require_bf16", lambda dt, what: None)
     monkeypatch.setattr(adapter, "_cached_pack", lambda module, x, dt, slot, fn: {"slot": slot})
 
     def rec(name):

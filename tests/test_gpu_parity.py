@@ -124,6 +124,61 @@ def test_block_against_reference_golden(dev):
         _check(mx, r, name + " z")
 
 
+# ----------------------------------------------------------------------------- fp32-accurate mode (float32 compute)
+# Tolerance of the fp32-accurate path against the reference's float32 outputs: max-abs error <= 2e-4 x RMS(ref),
+# RMS error <= 5e-5 x RMS(ref) (observed: about 1e-5 and 2e-6).
+PRECISE_MAX_TOL = 2e-4
+PRECISE_RMS_TOL = 5e-5
+
+
+def _run_case_precise(name, dev):
+    from kfold_b200 import functional as F
+    from kfold_b200 import packing
+    inp = cases.build_inputs(name)
+    cs, w = inp["case"], inp.get("w")
+    kind = cs["kind"]
+    if kind == "trimul":
+        pk = packing.pack_trimul(w, dev, precise=True)
+        return F.triangle_multiplication(inp["x"].to(dev), inp["mask"].to(dev), pk, cs["direction"])
+    if kind == "triatt":
+        pk = packing.pack_triatt(w, cs["heads"], dev, precise=True)
+        return F.triangle_attention(inp["x"].to(dev), inp["mask"].to(dev), pk, cs["starting"])
+    if kind == "transition":
+        return F.transition(inp["x"].to(dev), packing.pack_transition(w, dev, precise=True))
+    if kind == "apb":
+        pk = packing.pack_apb(w, cs["heads"], dev, precise=True)
+        an = F.layer_norm(inp["a"].to(dev), w["layernorm_a.weight"].to(dev), w["layernorm_a.bias"].to(dev))
+        return F.attention_pair_bias(an, inp["pair_bias"].to(dev), inp["mask"].to(dev), pk)
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("name", [n for n in GOLDEN_GPU_CASES if cases.CASES[n]["kind"] != "layernorm"])
+def test_fp32_accurate_against_reference_golden(dev, name):
+    gold = load_golden(name)
+    out = _run_case_precise(name, dev)
+    assert out.dtype == torch.float32
+    out = out.cpu()
+    assert torch.isfinite(out).all()
+    mx, r = err_stats(out, gold["out"]) if "out" in gold else compare_pair_output(out, gold)
+    assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"{name}: max-abs/RMS {mx:.3e}, RMS/RMS {r:.3e}"
+
+
+def test_fp32_accurate_block_against_reference_golden(dev):
+    """The N=64 float32 block (the reference's CPU-runnable configuration) through the module API, float32 compute."""
+    from kfold_b200 import modules as M
+    for name in ("block_n32", "block_cfg1_n64"):
+        inp = cases.build_inputs(name)
+        gold = load_golden(name)
+        blk = M.PairformerBlock().to(dev)
+        blk.load_state_dict(inp["w"], strict=True)
+        z, s = blk(inp["z"].to(dev), inp["s"].to(dev), inp["pair_mask"].to(dev), inp["mask"].to(dev))
+        assert z.dtype == torch.float32 and s.dtype == torch.float32
+        mx, r = err_stats(s.cpu(), gold["s"])
+        assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"{name} s: {mx:.3e} {r:.3e}"
+        mx, r = compare_pair_output(z.cpu(), gold, "z")
+        assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"{name} z: {mx:.3e} {r:.3e}"
+
+
 # ----------------------------------------------------------------------------- oracle at BASELINE sizes (oracle run on the GPU in fp32)
 def _oracle_on(dev, fn, *args, **kw):
     prev = torch.backends.cuda.matmul.allow_tf32
@@ -322,5 +377,11 @@ def test_autocast_fp32_input_returns_fp32(dev):
     with torch.autocast("cuda", dtype=torch.bfloat16):
         y = mod(x)
     assert y.dtype == torch.float32
+    # float32 compute takes the fp32-accurate path: no silent downgrade to bf16
+    from oracle import pairformer_oracle as O
+    y32 = mod(x)
+    ref = O.transition(x.cpu(), {k: v.cpu() for k, v in mod.state_dict().items()})
+    mx, r = err_stats(y32.cpu(), ref)
+    assert y32.dtype == torch.float32 and mx < PRECISE_MAX_TOL, f"{mx:.3e} {r:.3e}"
     with pytest.raises(NotImplementedError):
-        mod(x)  # fp32 compute is not built yet: must refuse, not silently downgrade
+        mod(x.half())
