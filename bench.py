@@ -48,22 +48,35 @@ def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C
     return {
         # tensor-bound kernels: flops per launch
         "trimul_contraction": ("tensor", 2.0 * n * n * n * c),
-        "trimul_in_proj": ("tensor", 2.0 * p * c * 4 * c),
-        "trimul_gate_proj": ("tensor", 2.0 * p * c * c),
-        "trimul_out_proj": ("tensor", 2.0 * p * c * c),
-        "triatt_proj": ("tensor", 2.0 * p * c * (4 * c + h)),
         "triatt_attention": ("tensor", 4.0 * n * n * n * h * d),
-        "triatt_out_proj": ("tensor", 2.0 * p * c * c),
         "transition_swiglu": ("tensor", 2.0 * p * c * 8 * c),
         "transition_out": ("tensor", 2.0 * p * 4 * c * c),
-        "pair_bias_proj": ("tensor", 2.0 * p * c * hs),
         "apb_proj": ("tensor", 2.0 * n * cs * 4 * cs),
         "apb_attention": ("tensor", 4.0 * n * n * cs),
         "apb_out_proj": ("tensor", 2.0 * n * cs * cs),
-        # HBM-bound kernels: bytes per launch (read + write once)
+        # HBM-bound kernels: bytes per launch (every tensor read or written once, bf16).  The K = c projections do
+        # 8 tensor-core instructions per 128-row tile: their time is the traffic of the tensors around them.
         "layernorm_rows": ("hbm", 2.0 * p * c * 2),
         "layernorm_cm": ("hbm", 2.0 * p * c * 2),
+        "trimul_in_proj": ("hbm", 3.0 * p * c * 2),            # read x~, write a and b
+        "trimul_gate_proj": ("hbm", 2.0 * p * c * 2),          # read x~, write the gate logits
+        "trimul_out_proj": ("hbm", 4.0 * p * c * 2),           # read LN(t), gate logits, residual; write out
+        "triatt_proj": ("hbm", 5.0 * p * c * 2 + p * h * 2),   # read x~; write q, k, g, v^T and the bias
+        "triatt_out_proj": ("hbm", 3.0 * p * c * 2),           # read gated o, residual; write out
+        "pair_bias_proj": ("hbm", p * c * 2 + p * hs * 2),
     }
+
+
+# DRAM traffic of the triangle-attention kernel from its ncu capture at N=384 (dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch: 152.4 MB + 25.3 MB); it grows with the number of pair positions.
+NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 152.378112e6 + 25.317120e6}}
+
+
+def ncu_traffic(tag: str, n: int):
+    ent = NCU_TRAFFIC.get(tag)
+    if ent is None:
+        return None
+    return round(ent["bytes"] * (n / ent["n"]) ** 2)
 
 
 def load_peaks() -> dict:
@@ -73,14 +86,6 @@ def load_peaks() -> dict:
             d = json.load(f)
         return {"hbm_gbs": d["hbm_gbs"], "tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
     return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
-
-
-def load_traffic() -> dict:
-    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            return json.load(f)
-    return {}
 
 
 class ClockSampler:
@@ -170,13 +175,15 @@ def cpu_block_time(n: int, repeats: int, warmup: int):
     return times, cores
 
 
-def block_flops(n: int) -> float:
-    w = algorithmic_work(n)
-    per = {k: v for k, (kind, v) in w.items() if kind == "tensor"}
-    return (2 * (per["trimul_contraction"] + per["trimul_in_proj"] + per["trimul_gate_proj"] + per["trimul_out_proj"]) +
-            2 * (per["triatt_proj"] + per["triatt_attention"] + per["triatt_out_proj"]) +
-            per["transition_swiglu"] + per["transition_out"] + per["pair_bias_proj"] + per["apb_proj"] +
-            per["apb_attention"] + per["apb_out_proj"] + 2.0 * n * 384 * 12 * 384)
+def block_flops(n: int, c: int = C_Z, h: int = 4, cs: int = C_S, hs: int = 16) -> float:
+    """Algorithmic flops of one composite block (2 per multiply-add), every GEMM and both attention cores."""
+    p = n * n
+    d = c // h
+    trimul = 2.0 * n * n * n * c + 2.0 * p * c * 4 * c + 2 * (2.0 * p * c * c)
+    triatt = 2.0 * p * c * (4 * c + h) + 4.0 * n * n * n * h * d + 2.0 * p * c * c
+    transition_z = 2.0 * p * c * 8 * c + 2.0 * p * 4 * c * c
+    single = 2.0 * p * c * hs + 2.0 * n * cs * 4 * cs + 4.0 * n * n * cs + 2.0 * n * cs * cs + 2.0 * n * cs * 12 * cs
+    return 2 * trimul + 2 * triatt + transition_z + single
 
 
 CPU_SAMPLE_N = 256
@@ -295,7 +302,6 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if rank == 0:
         peaks = load_peaks()
         work = algorithmic_work()
-        traffic = load_traffic()
         total_ms = sum(v[1] for v in prof.values()) or 1.0
         kernels = {}
         for tag, (cnt, ms) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
@@ -316,7 +322,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             k = kernels[top]
             roofline = {"kernel": top, "bound": k["bound"], "achieved": k["achieved"],
                         "peak": peaks["tflops"] if k["bound"] == "tensor" else peaks["hbm_gbs"], "unit": k["unit"],
-                        "frac": k["frac"], "traffic": traffic.get(top), "peak_source": peaks["source"],
+                        "frac": k["frac"], "traffic": ncu_traffic(top, N_TOKENS),
+                        "traffic_source": "ncu capture at N=384 scaled by pair positions (profiles/triatt_attention_n384_ncu.md)", "peak_source": peaks["source"],
                         "share_of_step": k["share"]}
         # CPU baseline: the oracle port on this box's host cores, one bounded sample
         cpu = None

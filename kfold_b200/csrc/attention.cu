@@ -12,31 +12,38 @@ namespace kfb {
 static constexpr int kBQ = 128;   // queries per CTA
 static constexpr int kBKV = 128;  // keys per block
 static constexpr float kLog2e = 1.4426950408889634f;
-static constexpr float kMasked = -1e9f;         // additive value of a masked key (finite, as in the reference)
+// Logits are kept in log2 units: the packed query projection carries log2(e) / sqrt(D), the bias is multiplied by
+// log2(e) as it is added, so that P = exp2(x - s) needs no further scaling and the subtraction is exact.
+static constexpr float kMasked = -1e9f * 1.4426950408889634f;  // a masked key: the reference's finite -1e9, in log2 units
 static constexpr float kAbsent = -1e30f;        // keys beyond lk
-static constexpr float kRaiseThreshold = 5.5f;  // raise the stabiliser when the running max moved by more than e^5.5
-static constexpr float kRedoThreshold = 60.f;   // redo a block whose exponents would approach fp32 overflow
+static constexpr float kRedoSum = 1.2676506e30f;  // 2^100: a half-tile row sum above this moves the stabiliser
 
 template <int DPAD, int R>
 struct AttCfg {
-  static constexpr int kThreads = 64 + 128 * R;
+  // warp 0: TMA producer; warps 1..R: one MMA-issuing warp per row group (they sit on different schedulers, so
+  // neither queues behind the other's waits); warp 3 (and 2 when R == 1): idle; then 8 softmax warps per row group
+  static constexpr int kThreads = 128 + 256 * R;
   static constexpr int kSpan = DPAD * 2;                 // bytes per q/k row = swizzle span
   static constexpr int kQBytes = kBQ * kSpan;            // per row group
   static constexpr int kKBytes = kBKV * kSpan;
   static constexpr int kVBytes = 2 * DPAD * 128;         // two boxes of [DPAD rows x 64 keys]
-  static constexpr int kKvStages = 2;
-  static constexpr int kTileBytes = 2 * 128 * 128;       // a 128 x 128 bf16 tile as two 64-wide swizzled halves
+  static constexpr int kKvStages = 3;
+  static constexpr int kTileBytes = 2 * 128 * 128;       // a 128 x 128 bf16 bias tile as two 64-key halves of 128-byte rows
   static constexpr int kSmallBytes = 128 * 32;           // a 128 x 16 bf16 K-major operand without swizzle
   static constexpr int kBiasStages = 2;
-  // tensor memory columns: S_g at g*128 (fp32), O_g at R*128 + g*DPAD (fp32), P_g at R*(128+DPAD) + g*64 (bf16 pairs),
-  // then the constant identity matrix
-  static constexpr int kTmemO = R * 128;
-  static constexpr int kTmemP = R * (128 + DPAD);
-  static constexpr int kTmemI = R * (128 + DPAD + 64);   // identity (128 x 128 bf16 = 64 columns), A operand of the bias MMA
-  static constexpr int kTmemCols = (kTmemI + 64 <= 256) ? 256 : 512;
+  // tensor memory columns.  Keys are processed in half tiles of 64 (t = 0, 1, ...; buf = t % 3); the 64 columns
+  // of a half tile are shared between two independent softmax streams (c = 0: keys 0..31, c = 1: keys 32..63):
+  //   S[g][buf]  64 fp32 columns at (g*3 + buf) * 64; stream c overwrites the first 16 of its 32 columns
+  //              with P (64 bf16 = 16 columns) in place, so a buffer is busy from S(t) until P V(t) has read it
+  //   O[g][c]    DPAD fp32 columns at R*192 + (g*2 + c) * DPAD  (one accumulator per stream)
+  static constexpr int kSBufs = 3;
+  static constexpr int kTmemO = R * 192;
+  static constexpr int kTmemUsed = R * (192 + 2 * DPAD);
+  static constexpr int kTmemCols = kTmemUsed <= 256 ? 256 : 512;
+  static constexpr int kXchgStride = DPAD + 3;           // floats per row of the end-of-kernel exchange (odd: no bank conflicts)
   static constexpr int kSmemBytes = R * kQBytes + R * kKvStages * (kKBytes + kVBytes) + kBiasStages * kTileBytes /*bias*/ +
-                                    kSmallBytes /*e0*/ +
-                                    R * kSmallBytes /*mask rows*/ + 1024 /*align*/ + 256 /*barriers*/;
+                                    kSmallBytes /*e0*/ + R * 3 * kSmallBytes /*mask rows, three buffers*/ + 1024 /*align*/ +
+                                    256 /*barriers*/;
 };
 
 // K-major operand without swizzle: 8 x 8 core matrices (8 rows of 16 bytes); the two K halves of a K=16
@@ -45,17 +52,21 @@ __device__ __forceinline__ uint64_t make_noswizzle_desc(uint32_t smem_addr) {
   return static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4) | (static_cast<uint64_t>(128 >> 4) << 16) |
          (static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 46);
 }
-// MN-major operand tile made of 128-byte swizzled rows: row = one K index holding 64 contiguous MN elements
-// (what a TMA box of 64 x rows with 128B swizzle writes).  Groups of 8 K-rows are 1024 bytes apart (stride
-// byte offset); the next 64 MN elements live in the next box, `mn_group_bytes` further (leading byte offset).
-__device__ __forceinline__ uint64_t make_mnmajor_desc(uint32_t smem_addr, uint32_t mn_group_bytes) {
-  return static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4) | (static_cast<uint64_t>(mn_group_bytes >> 4) << 16) |
-         (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
 __device__ __forceinline__ uint32_t small_operand_row_offset(int r) { return (r >> 3) * 256 + (r & 7) * 16; }
 
+// Pipeline.  A CTA owns 128 queries of R pair rows ("row groups", they share the bias tile).  Keys go by in half
+// tiles of 64 (t = 0, 1, ...).  Each row group has two softmax streams of four warps: stream c owns 32 of the 64
+// key columns of every half tile and keeps its own stabiliser, row sum and output accumulator O[g][c] (in tensor
+// memory, accumulated by the tensor core); the two partial results are merged once at the end.
+//   MMA warp g:  S(t) = Q K(t)^T + e0 maskrow(t)^T -> S[g][t % 3]                   commit s_full[g][t % 3]
+//   stream c:    wait s_full; x = S_c(t) + bias_c(t) (own bias row from shared memory); P_c(t) = exp2(x - s) against a
+//                lagging stabiliser, written over the stream's own S columns; arrive p_ready[g][t % 3] (both streams)
+//   MMA warp g:  wait p_ready[g][t % 3] -> O[g][c] += P_c(t) V_c(t), then S(t+3) into the same buffer (the tensor
+//                core executes in order, so S(t+3) cannot overtake the P V product that reads the buffer)
+// S runs up to three half tiles ahead of the softmax, so the softmax warps never wait for the tensor core or for the
+// issuing warp, and four independent softmax warps per scheduler hide each other's tensor-memory and MUFU latencies.
 template <int DPAD, int R>
-__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads) __maxnreg__((R == 1) ? 255 : 168)
+__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads) __maxnreg__((R == 1) ? 168 : 96)
 attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
                       const AttnParams p) {
@@ -66,19 +77,20 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   uint8_t* s_q = smem;                                            // [R]
   uint8_t* s_k = s_q + R * Cfg::kQBytes;                          // [R][stages]
   uint8_t* s_v = s_k + R * kStages * Cfg::kKBytes;                // [R][stages]
-  uint8_t* s_bias = s_v + R * kStages * Cfg::kVBytes;
+  uint8_t* s_bias = s_v + R * kStages * Cfg::kVBytes;             // [stages][2 halves][128 rows][128 B]
   uint8_t* s_e0 = s_bias + Cfg::kBiasStages * Cfg::kTileBytes;
-  uint8_t* s_maskrow = s_e0 + Cfg::kSmallBytes;                   // [R]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_maskrow + R * Cfg::kSmallBytes);
+  uint8_t* s_maskrow = s_e0 + Cfg::kSmallBytes;                   // [R][3]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_maskrow + R * 3 * Cfg::kSmallBytes);
   uint64_t* q_full = bars;                           // [R]
   uint64_t* kv_full = q_full + R;                    // [R][stages]
   uint64_t* kv_empty = kv_full + R * kStages;        // [R][stages]
-  uint64_t* bias_full = kv_empty + R * kStages;
-  uint64_t* bias_empty = bias_full + Cfg::kBiasStages;
-  uint64_t* s_full = bias_empty + Cfg::kBiasStages;  // [R]
-  uint64_t* ready = s_full + R;                      // [R]  (128 arrivals)
-  uint64_t* o_full = ready + R;                      // [R]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + R);
+  uint64_t* bias_full = kv_empty + R * kStages;      // [stages]
+  uint64_t* bias_empty = bias_full + Cfg::kBiasStages;  // [stages]  (one arrival per softmax warp)
+  uint64_t* s_full = bias_empty + Cfg::kBiasStages;  // [R][3]
+  uint64_t* p_ready = s_full + R * 3;                // [R][3]  (256 arrivals: both streams)
+  uint64_t* o_full = p_ready + R * 3;                // [R][3]
+  uint64_t* init_ready = o_full + R * 3;             // [R]     (128 arrivals, used once)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(init_ready + R);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -86,6 +98,7 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int h = blockIdx.y;
   const int b0 = blockIdx.z * R;  // first batch entry of this CTA
   const int nkv = (p.lk + kBKV - 1) / kBKV;
+  const int nhalf = 2 * nkv;
   long long* trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
 #define KFB_STAMP(slot) do { if (trace != nullptr) trace[slot] = clock64(); } while (0)
 
@@ -97,9 +110,12 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     ptx::prefetch_tmap(&tm_b);
     for (int g = 0; g < R; ++g) {
       ptx::mbar_init(&q_full[g], 1);
-      ptx::mbar_init(&s_full[g], 1);
-      ptx::mbar_init(&ready[g], 128);
-      ptx::mbar_init(&o_full[g], 1);
+      ptx::mbar_init(&init_ready[g], 128);
+      for (int u = 0; u < 3; ++u) {
+        ptx::mbar_init(&o_full[g * 3 + u], 1);
+        ptx::mbar_init(&s_full[g * 3 + u], 1);
+        ptx::mbar_init(&p_ready[g * 3 + u], 256);
+      }
       for (int s = 0; s < kStages; ++s) {
         ptx::mbar_init(&kv_full[g * kStages + s], 1);
         ptx::mbar_init(&kv_empty[g * kStages + s], 1);
@@ -107,7 +123,7 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     for (int s = 0; s < Cfg::kBiasStages; ++s) {
       ptx::mbar_init(&bias_full[s], 1);
-      ptx::mbar_init(&bias_empty[s], 1);
+      ptx::mbar_init(&bias_empty[s], R * 8);
     }
     ptx::fence_barrier_init();
   }
@@ -116,37 +132,20 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     ptx::tmem_relinquish();
   }
   // constant operand e0 (128 x 16, first column ones) and the zero halves of the mask-row operands
-  if (warp >= 2 && warp < 6) {
-    const int r = (warp - 2) * 32 + lane;
+  if (warp >= 4 && warp < 8) {
+    const int r = (warp - 4) * 32 + lane;
     const uint32_t off = small_operand_row_offset(r);
     *reinterpret_cast<uint4*>(s_e0 + off) = make_uint4(0x3F80u, 0, 0, 0);
     *reinterpret_cast<uint4*>(s_e0 + off + 128) = make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int g = 0; g < R; ++g)
-      *reinterpret_cast<uint4*>(s_maskrow + g * Cfg::kSmallBytes + off + 128) = make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < R * 3; ++u)
+      *reinterpret_cast<uint4*>(s_maskrow + u * Cfg::kSmallBytes + off + 128) = make_uint4(0, 0, 0, 0);
     ptx::fence_proxy_async_smem();
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-
-  // the identity matrix in tensor memory: row r holds a single bf16 1.0 at K index r (column r/2, half r&1)
-  if (warp >= 2 && warp < 6) {
-    const int r = (warp & 3) * 32 + lane;
-    const uint32_t base = tmem_base + Cfg::kTmemI + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint32_t v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = (c * 8 + i == (r >> 1)) ? (0x3F80u << (16 * (r & 1))) : 0u;
-      ptx::tmem_st_32x32b_x8(base + c * 8, v);
-    }
-    ptx::tmem_st_wait();
-    ptx::tc_fence_before_sync();
-  }
-  __syncthreads();
-  ptx::tc_fence_after_sync();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -158,11 +157,6 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int bias_z = (b0 / p.bias_div) * p.heads + h;
       bool ok = true;
       for (int j = 0; ok && j < nkv; ++j) {
-        const int bs = j % Cfg::kBiasStages;
-        if (!ptx::mbar_wait(&bias_empty[bs], ((j / Cfg::kBiasStages) & 1) ^ 1, 202)) break;
-        ptx::mbar_expect_tx(&bias_full[bs], Cfg::kTileBytes);
-        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes, &tm_b, &bias_full[bs], j * kBKV, qb * kBQ, bias_z);
-        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes + 16384, &tm_b, &bias_full[bs], j * kBKV + 64, qb * kBQ, bias_z);
         const int st = j % kStages;
         for (int g = 0; g < R; ++g) {
           const int slot = g * kStages + st;
@@ -172,255 +166,306 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           ptx::tma_load_3d(s_v + slot * Cfg::kVBytes, &tm_v, &kv_full[slot], j * kBKV, h * DPAD, b0 + g);
           ptx::tma_load_3d(s_v + slot * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[slot], j * kBKV + 64, h * DPAD, b0 + g);
         }
+        if (!ok) break;
+        const int bs = j % Cfg::kBiasStages;
+        if (!ptx::mbar_wait(&bias_empty[bs], ((j / Cfg::kBiasStages) & 1) ^ 1, 202)) break;
+        ptx::mbar_expect_tx(&bias_full[bs], Cfg::kTileBytes);
+        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes, &tm_b, &bias_full[bs], j * kBKV, qb * kBQ, bias_z);
+        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes + 16384, &tm_b, &bias_full[bs], j * kBKV + 64, qb * kBQ, bias_z);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp <= R) {
+    // ---------------------------------------------------------------- MMA issuer of row group g
     if (lane == 0) {
-      constexpr uint32_t idesc_s = ptx::make_idesc(kBQ, kBKV, 1);
+      const int g = warp - 1;
+      constexpr uint32_t idesc_s = ptx::make_idesc(kBQ, 64, 1);
       constexpr uint32_t idesc_o = ptx::make_idesc(kBQ, DPAD, 1);
-      constexpr uint32_t idesc_s_bmn = idesc_s | (1u << 16);  // B operand MN-major (the bias tile as it lies in memory)
+      // operand descriptors are built once; inside the loop only their 16-byte-unit address field advances
       const uint64_t e0_desc = make_noswizzle_desc(ptx::smem_u32(s_e0));
-      uint64_t maskrow_desc[R];
-#pragma unroll
-      for (int g = 0; g < R; ++g) maskrow_desc[g] = make_noswizzle_desc(ptx::smem_u32(s_maskrow + g * Cfg::kSmallBytes));
-      const uint64_t bias_desc0 = make_mnmajor_desc(ptx::smem_u32(s_bias), 16384);
-      const uint32_t tmem_ident = tmem_base + Cfg::kTmemI;
+      const uint64_t q_desc = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_q + g * Cfg::kQBytes));
+      const uint64_t k_desc0 = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_k + g * kStages * Cfg::kKBytes));
+      const uint64_t v_desc0 = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_v + g * kStages * Cfg::kVBytes));
+      const uint64_t m_desc0 = make_noswizzle_desc(ptx::smem_u32(s_maskrow + g * 3 * Cfg::kSmallBytes));
+      const uint32_t tmem_s0 = tmem_base + g * 192;
+      const uint32_t tmem_o0 = tmem_base + Cfg::kTmemO + g * 2 * DPAD;
       bool ok = true;
 
-      // S_g(j) = Q_g K_g(j)^T + I bias(j) + e0 maskrow_g(j)^T
-      auto issue_s = [&](int g, int j) -> bool {
-        const int slot = g * kStages + (j % kStages);
-        const int bs = j % Cfg::kBiasStages;
-        if (!ptx::mbar_wait(&kv_full[slot], (j / kStages) & 1, 204)) return false;
-        if (g == 0 && !ptx::mbar_wait(&bias_full[bs], (j / Cfg::kBiasStages) & 1, 203)) return false;
+      // S_g(t) = Q_g K_g(t)^T + e0 maskrow_g(t)^T for the 64 keys of half tile t = 2j + hf, into S buffer `buf`;
+      // `st` = j % kv stages, `mb` = j % 3 (mask operand buffer)
+      auto issue_s = [&](int hf, int buf, int st, uint32_t kv_parity, int mb) -> bool {
+        if (hf == 0 && !ptx::mbar_wait(&kv_full[g * kStages + st], kv_parity, 204)) return false;
         ptx::tc_fence_after_sync();
-        // descriptors are built once per tile; inside a tile only the 16-byte-unit address field advances, so
-        // the single issuing thread spends a couple of instructions per MMA rather than a dependent chain
-        const uint32_t tmem_s = tmem_base + g * 128;
-        const uint64_t q_desc = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_q + g * Cfg::kQBytes));
-        const uint64_t k_desc = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_k + slot * Cfg::kKBytes));
+        const uint32_t tmem_s = tmem_s0 + buf * 64;
+        const uint64_t k_desc = k_desc0 + static_cast<uint32_t>((st * Cfg::kKBytes + hf * 64 * Cfg::kSpan) >> 4);
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk)
           ptx::mma_f16_ss(tmem_s, q_desc + kk * 2, k_desc + kk * 2, idesc_s, kk != 0 ? 1u : 0u);
-        ptx::mma_f16_ss(tmem_s, e0_desc, maskrow_desc[g], idesc_s, 1u);
-        // identity (from tensor memory) x bias tile (MN-major, as it lies in memory): the otherwise idle tensor
-        // core adds the pair bias; K runs over the 128 queries of the tile, 16 per step
-        const uint64_t bias_desc = bias_desc0 + static_cast<uint64_t>(bs) * (Cfg::kTileBytes >> 4);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          ptx::mma_f16_ts(tmem_s, tmem_ident + kk * 8, bias_desc + kk * (2048 >> 4), idesc_s_bmn, 1u);
-        ptx::tc_commit(&s_full[g]);
-        if (g == R - 1) ptx::tc_commit(&bias_empty[bs]);
-        KFB_STAMP(16 + j * 8 + g * 4 + 0);
+        ptx::mma_f16_ss(tmem_s, e0_desc, m_desc0 + static_cast<uint32_t>((mb * Cfg::kSmallBytes + hf * 2048) >> 4), idesc_s, 1u);
+        ptx::tc_commit(&s_full[g * 3 + buf]);
         return true;
       };
+      static_assert(kStages == 3, "the stage and mask-buffer counters below assume three K/V stages");
 
-      for (int g = 0; ok && g < R; ++g) {
-        ok = ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&ready[g], 0, 206) && issue_s(g, 0);
-      }
-      for (int j = 0; ok && j < nkv; ++j) {
-        for (int g = 0; ok && g < R; ++g) {
-          // P_g(j) is in tensor memory, S_g(j) consumed, O_g(j-1) folded, mask row of block j+1 written
-          if (!ptx::mbar_wait(&ready[g], (j + 1) & 1, 207)) { ok = false; break; }
-          KFB_STAMP(16 + j * 8 + g * 4 + 1);
-          ptx::tc_fence_after_sync();
-          // the next S first: it is short and lets the group's next softmax pass start while P V runs
-          if (j + 1 < nkv && !issue_s(g, j + 1)) { ok = false; break; }
-          const int slot = g * kStages + (j % kStages);
-          const uint64_t v_desc = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_v + slot * Cfg::kVBytes));
-          const uint32_t tmem_o = tmem_base + Cfg::kTmemO + g * DPAD;
-          const uint32_t tmem_p = tmem_base + Cfg::kTmemP + g * 64;
+      ok = ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&init_ready[g], 0, 206) && issue_s(0, 0, 0, 0, 0) &&
+           issue_s(1, 1, 0, 0, 0);
+      if (ok && nkv > 1) ok = issue_s(0, 2, 1, 0, 1);
+      // half tile t lives in S buffer `buf` = t % 3 (use number `use` = t / 3) and in K/V stage `st` = (t / 2) % 3;
+      // half tile t + 3 (issued below) belongs to tile j3 = (t + 3) / 2: stage st3 = j3 % 3, parity par3 = (j3 / 3) & 1
+      int buf = 0, st = 0;
+      uint32_t use_par = 0;
+      int st3 = 1, j3 = 1;
+      uint32_t par3 = 0;
+      for (int t = 0; ok && t < nhalf; ++t) {
+        const int hf = t & 1;
+        // both streams' P(t) are in tensor memory, the mask rows needed by S(t+3) are written
+        if (!ptx::mbar_wait(&p_ready[g * 3 + buf], use_par, 207)) { ok = false; break; }
+        KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 1);
+        ptx::tc_fence_after_sync();
+        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>((st * Cfg::kVBytes + hf * (DPAD * 128)) >> 4);
+        const uint32_t tmem_p = tmem_s0 + buf * 64;
+        const uint32_t acc_flag = t > 0 ? 1u : 0u;
 #pragma unroll
-          for (int kk = 0; kk < kBKV / 16; ++kk)  // A = P straight from tensor memory, 8 columns per K=16 slice
-            ptx::mma_f16_ts(tmem_o, tmem_p + kk * 8, v_desc + ((kk >> 2) * (DPAD * 128 >> 4) + (kk & 3) * 2), idesc_o,
-                            kk != 0 ? 1u : 0u);
-          ptx::tc_commit(&o_full[g]);
-          ptx::tc_commit(&kv_empty[slot]);
-        }
+        for (int kk = 0; kk < 4; ++kk)  // A = P straight from tensor memory: stream c's 16 columns start at c * 32
+          ptx::mma_f16_ts(tmem_o0 + (kk >> 1) * DPAD, tmem_p + (kk >> 1) * 32 + (kk & 1) * 8, v_desc + kk * 2, idesc_o,
+                          ((kk & 1) != 0) ? 1u : acc_flag);
+        ptx::tc_commit(&o_full[g * 3 + buf]);
+        if (hf == 1) ptx::tc_commit(&kv_empty[g * kStages + st]);
+        // S(t+3): half (t+3) & 1 = hf ^ 1 of tile j3
+        if (t + 3 < nhalf && !issue_s(hf ^ 1, buf, st3, par3, st3)) { ok = false; break; }
+        KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 0);
+        if (++buf == 3) { buf = 0; use_par ^= 1u; }
+        if (hf == 1) { if (++st == 3) st = 0; }
+        // t + 4 belongs to the next tile when t + 4 is even
+        if (hf == 0) { ++j3; if (++st3 == 3) { st3 = 0; par3 ^= 1u; } }
       }
+      (void)j3;
     }
-  } else {
-    // ---------------------------------------------------------------- softmax + accumulation
-    const int g = (warp - 2) >> 2;          // row group
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- softmax streams
+    const int w = warp - 4;
+    const int g = w >> 3;                   // row group
+    const int u = (w >> 2) & 1;             // stream: key columns u*32 .. u*32+31 of every half tile
     const int quad = warp & 3;              // TMEM lane quadrant of this warp
     const int r = quad * 32 + lane;         // row inside the query block == TMEM lane
     const int q_idx = qb * kBQ + r;
     const int b = b0 + g;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t tmem_s = tmem_base + g * 128 + lane_base;
-    const uint32_t tmem_o = tmem_base + Cfg::kTmemO + g * DPAD + lane_base;
-    const uint32_t tmem_p = tmem_base + Cfg::kTmemP + g * 64 + lane_base;
+    const uint32_t tmem_s0 = tmem_base + g * 192 + u * 32 + lane_base;
+    const uint32_t tmem_o = tmem_base + Cfg::kTmemO + (g * 2 + u) * DPAD + lane_base;
     const int b_hi = b / p.mask_lo_extent, b_lo = b - b_hi * p.mask_lo_extent;
     const unsigned char* mrow = p.mask + static_cast<long long>(b_hi) * p.m_hi + static_cast<long long>(b_lo) * p.m_lo;
-    uint8_t* my_maskrow = s_maskrow + g * Cfg::kSmallBytes + small_operand_row_offset(r);
+    uint8_t* my_maskrow = s_maskrow + g * 3 * Cfg::kSmallBytes + small_operand_row_offset(r);
+    const uint8_t* my_bias = s_bias + r * 128;
+    const int swz = r & 7;
 
-    // this thread provides key j*128 + r of its group's mask operand
-    auto load_mask_value = [&](int j) -> float {
+    // stream 0 provides the mask operand: this thread writes key j*128 + r of tile j
+    auto load_mask_byte = [&](int j) -> int {
       const int key = j * kBKV + r;
-      if (key >= p.lk) return kAbsent;
-      return mrow[static_cast<long long>(key) * p.m_k] ? 0.f : kMasked;
+      if (key >= p.lk) return 2;
+      return mrow[static_cast<long long>(key) * p.m_k] ? 1 : 0;
     };
-    auto store_mask_value = [&](float mv) {
+    auto store_mask_value = [&](int buf, int code) {
+      const float mv = code == 2 ? kAbsent : (code == 1 ? 0.f : kMasked);
       const uint32_t bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(mv)));
-      *reinterpret_cast<uint4*>(my_maskrow) = make_uint4(bits, 0, 0, 0);
+      *reinterpret_cast<uint4*>(my_maskrow + buf * Cfg::kSmallBytes) = make_uint4(bits, 0, 0, 0);
     };
+    if (u == 0) {
+      store_mask_value(0, load_mask_byte(0));
+      if (nkv > 1) store_mask_value(1, load_mask_byte(1));
+      ptx::fence_proxy_async_smem();
+      ptx::mbar_arrive(&init_ready[g]);
+    }
 
-    store_mask_value(load_mask_value(0));
-    ptx::fence_proxy_async_smem();
-    ptx::mbar_arrive(&ready[g]);
-
-    float acc[DPAD];
-#pragma unroll
-    for (int i = 0; i < DPAD; ++i) acc[i] = 0.f;
-    float s_cur = 0.f, l_run = 0.f, s_next = 0.f;
+    float s_cur = 0.f, l_run = 0.f;
     bool ok = true;
+    int buf = 0, mbuf = 2;        // S buffer of half tile t (t % 3); mask buffer of tile t/2 + 2
+    uint32_t use_par = 0;
 
-    for (int j = 0; j < nkv; ++j) {
-      // the mask byte of the next block is fetched before the wait so that its latency hides behind it
-      const float mask_next = (j + 1 < nkv) ? load_mask_value(j + 1) : 0.f;
-      if (!ptx::mbar_wait(&s_full[g], j & 1, 208)) { ok = false; break; }
-      if (r == 0) KFB_STAMP(256 + g * 128 + j * 8 + 0);
+#pragma unroll 1
+    for (int t = 0; t < nhalf; ++t) {
+      const int j = t >> 1, hf = t & 1;
+      const int bs = j % Cfg::kBiasStages;
+      // the mask byte of the next tile is fetched now and used at the end of the pass: its latency hides behind the pass
+      int mask_next = 0;
+      if (u == 0 && hf == 0 && j + 2 < nkv) mask_next = load_mask_byte(j + 2);
+      if (!ptx::mbar_wait(&s_full[g * 3 + buf], use_par, 208)) { ok = false; break; }
+      if (r == 0) KFB_STAMP(256 + (g * 2 + u) * 64 + (t & 7) * 8 + 0);
       ptx::tc_fence_after_sync();
-      if (j + 1 < nkv) store_mask_value(mask_next);  // S(j) is complete, the MMA no longer reads the mask operand
-
-      if (j == 0) {  // stabiliser of the first block: its true row maximum
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        uint32_t raw0[16], raw1[16];
-        ptx::tmem_ld_32x32b_x16(tmem_s, raw0);
-#pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
-          ptx::tmem_ld_wait();
-          ptx::tmem_ld_32x32b_x16(tmem_s + cc * 32 + 16, raw1);
+      float x[32];
+      const uint32_t tmem_s = tmem_s0 + buf * 64;
+      ptx::tmem_ld_32x32b_x32(tmem_s, reinterpret_cast<uint32_t(&)[32]>(x));
+      if (hf == 0 && !ptx::mbar_wait(&bias_full[bs], (j / Cfg::kBiasStages) & 1, 203)) { ok = false; break; }
+      // the thread's own 64 bytes of its 128-byte row of the bias half tile (16-byte chunks swizzled by the row index)
+      const uint8_t* brow = my_bias + bs * Cfg::kTileBytes + hf * 16384;
+      uint4 bw[4];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw0[i]));
-          ptx::tmem_ld_wait();
-          if (cc < 3) ptx::tmem_ld_32x32b_x16(tmem_s + cc * 32 + 32, raw0);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw1[i]));
-        }
-        s_next = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        s_cur = s_next;
+      for (int c = 0; c < 4; ++c) bw[c] = *reinterpret_cast<const uint4*>(brow + (((u * 4 + c) ^ swz) << 4));
+      if (hf == 1) {  // both halves of the bias tile have been read by this warp
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bias_empty[bs]);
       }
-
-      // single pass: P = exp(S - s_use) = exp2(S * log2e - s_use * log2e).  The first quarter of P
-      // waits in registers (packed bf16) until the previous block's P V product has finished reading the P
-      // columns of tensor memory; by the second half that is long done and P is stored as it is produced.
-      float s_use = s_next, l_blk = 0.f, mx = -INFINITY;
-      bool folded = (j == 0);
-#pragma unroll 1
-      for (int attempt = 0; attempt < 2; ++attempt) {
-        const float neg_s = -s_use * kLog2e;
-        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      ptx::tmem_ld_wait();
+      // x = S + log2(e) * bias
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t wv[4] = {bw[c].x, bw[c].y, bw[c].z, bw[c].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          x[c * 8 + q * 2] = fmaf(__uint_as_float(wv[q] << 16), kLog2e, x[c * 8 + q * 2]);
+          x[c * 8 + q * 2 + 1] = fmaf(__uint_as_float(wv[q] & 0xffff0000u), kLog2e, x[c * 8 + q * 2 + 1]);
+        }
+      }
+      auto row_max = [&]() -> float {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        auto process = [&](const uint32_t (&raw)[16], int c, uint32_t (&out)[8]) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          m4[0] = fmaxf(m4[0], x[i]);
+          m4[1] = fmaxf(m4[1], x[i + 1]);
+          m4[2] = fmaxf(m4[2], x[i + 2]);
+          m4[3] = fmaxf(m4[3], x[i + 3]);
+        }
+        return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      };
+      // P = exp2(x - s) over the first 16 of this stream's own 32 S columns (all of x is in registers); returns the row sum
+      const uint32_t tmem_s_w = tmem_s;
+      auto exp_pass = [&](float s) -> float {
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t out[8];
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
-            const float t0 = __uint_as_float(raw[i]);
-            const float t1 = __uint_as_float(raw[i + 1]);
-            m4[i & 3] = fmaxf(m4[i & 3], t0);
-            m4[(i + 1) & 3] = fmaxf(m4[(i + 1) & 3], t1);
-            const float p0 = exp2f(fmaf(t0, kLog2e, neg_s));
-            const float p1 = exp2f(fmaf(t1, kLog2e, neg_s));
+            const float p0 = exp2f(x[c * 16 + i] - s);
+            const float p1 = exp2f(x[c * 16 + i + 1] - s);
             l4[i & 3] += p0;
             l4[(i + 1) & 3] += p1;
             out[i >> 1] = pack_bf16x2(p0, p1);
           }
-        };
-        uint32_t raw0[16], raw1[16];
-        {
-          // keys 0..31: P waits in registers until the previous block's P V product has released the P columns
-          uint32_t held0[8], held1[8];
-          ptx::tmem_ld_32x32b_x16(tmem_s, raw0);
-          ptx::tmem_ld_wait();
-          ptx::tmem_ld_32x32b_x16(tmem_s + 16, raw1);
-          process(raw0, 0, held0);
-          ptx::tmem_ld_wait();
-          ptx::tmem_ld_32x32b_x16(tmem_s + 32, raw0);
-          process(raw1, 1, held1);
-          if (!folded) {
-            // fold the previous block's P V product (same scale as acc)
-            if (!ptx::mbar_wait(&o_full[g], (j - 1) & 1, 209)) { ok = false; break; }
-            ptx::tc_fence_after_sync();
+          ptx::tmem_st_32x32b_x8(tmem_s_w + c * 8, out);
+        }
+        return (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      };
+      // The stabiliser s lags: it is the row maximum of the stream's first half tile and is raised only when a half
+      // tile's exponentials threaten to overflow (row sum above 2^100: some logit exceeds s by about 95 in log2
+      // units).  Any s gives the same result as long as P, the row sum and the accumulator use the same one; the
+      // common path therefore needs no row maximum at all.
+      float s_use = s_cur;
+      if (t == 0) s_use = row_max();
+      if (r == 0) KFB_STAMP(256 + (g * 2 + u) * 64 + (t & 7) * 8 + 1);
+      float l_blk = exp_pass(s_use);
+      if (t > 0 && __any_sync(0xffffffffu, !(l_blk < kRedoSum))) {
+        // rare: redo this half tile against its own maximum and move the stream's accumulator and row sum to it,
+        // once the P V product issued after the previous pass has completed
+        // (o_full[buf] completes one phase per three half tiles: S(t) complete implies P V(t-3) and everything before
+        // it complete, and P V(t+2) cannot be issued before this pass and the next two end, so the barrier of
+        // half tile t-1 is exactly in the phase waited for: the parity test is unambiguous)
+        if (!ptx::mbar_wait(&o_full[g * 3 + (buf == 0 ? 2 : buf - 1)], buf == 0 ? (use_par ^ 1u) : use_par, 209)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        if (!(l_blk < kRedoSum)) s_use = fmaxf(row_max(), s_cur);
+        const float alpha = exp2f(s_cur - s_use);  // 1 for the lanes whose stabiliser stays
 #pragma unroll
-            for (int cb = 0; cb < DPAD / 32; ++cb) {
-              uint32_t raw[32];
-              ptx::tmem_ld_32x32b_x32(tmem_o + cb * 32, raw);
-              ptx::tmem_ld_wait();
+        for (int cb = 0; cb < DPAD / 16; ++cb) {
+          uint32_t o16[16];
+          ptx::tmem_ld_32x32b_x16(tmem_o + cb * 16, o16);
+          ptx::tmem_ld_wait();
+          uint32_t lo[8], hi[8];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) acc[cb * 32 + i] += __uint_as_float(raw[i]);
-            }
-            folded = true;
+          for (int i = 0; i < 8; ++i) {
+            lo[i] = __float_as_uint(__uint_as_float(o16[i]) * alpha);
+            hi[i] = __float_as_uint(__uint_as_float(o16[8 + i]) * alpha);
           }
-          ptx::tmem_st_32x32b_x8(tmem_p, held0);
-          ptx::tmem_st_32x32b_x8(tmem_p + 8, held1);
+          ptx::tmem_st_32x32b_x8(tmem_o + cb * 16, lo);
+          ptx::tmem_st_32x32b_x8(tmem_o + cb * 16 + 8, hi);
         }
-#pragma unroll 1
-        for (int c = 2; c < 8; c += 2) {  // keys 32..127: stored as produced
-          uint32_t out[8];
-          ptx::tmem_ld_wait();
-          ptx::tmem_ld_32x32b_x16(tmem_s + c * 16 + 16, raw1);
-          process(raw0, c, out);
-          ptx::tmem_st_32x32b_x8(tmem_p + c * 8, out);
-          ptx::tmem_ld_wait();
-          if (c + 2 < 8) ptx::tmem_ld_32x32b_x16(tmem_s + c * 16 + 32, raw0);
-          process(raw1, c + 1, out);
-          ptx::tmem_st_32x32b_x8(tmem_p + c * 8 + 8, out);
-        }
-        l_blk = (l4[0] + l4[1]) + (l4[2] + l4[3]);
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        if (mx - s_use <= kRedoThreshold) break;
-        s_use = mx;  // exponents too large for comfort: redo this block against its own maximum
+        l_run *= alpha;
+        l_blk = exp_pass(s_use);
       }
-      if (!ok) break;
-      if (r == 0) KFB_STAMP(256 + g * 128 + j * 8 + 1);
-      const float alpha = exp2f((s_cur - s_use) * kLog2e);
-#pragma unroll
-      for (int i = 0; i < DPAD; ++i) acc[i] *= alpha;
-      l_run = l_run * alpha + l_blk;
+      l_run += l_blk;
       s_cur = s_use;
-      s_next = (mx > s_cur + kRaiseThreshold) ? mx : s_cur;
-
-      if (r == 0) KFB_STAMP(256 + g * 128 + j * 8 + 2);
+      if (r == 0) KFB_STAMP(256 + (g * 2 + u) * 64 + (t & 7) * 8 + 2);
+      if (u == 0 && hf == 0 && j + 2 < nkv) {
+        // S(2j) is complete, so every earlier S is too: the mask operand buffer of tile j+2 (last read by tile j-1)
+        // is free.  Its first reader, S(2j+4), is issued after the p_ready arrival of half tile 2j+1.
+        store_mask_value(mbuf, mask_next);
+        ptx::fence_proxy_async_smem();
+      }
+      if (hf == 0 && ++mbuf == 3) mbuf = 0;
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
-      ptx::fence_proxy_async_smem();  // the mask row of the next block was written through the generic proxy
-      ptx::mbar_arrive(&ready[g]);
+      ptx::mbar_arrive(&p_ready[g * 3 + buf]);
+      if (++buf == 3) { buf = 0; use_par ^= 1u; }
+      if (r == 0) KFB_STAMP(256 + (g * 2 + u) * 64 + (t & 7) * 8 + 3);
     }
-    if (ok && ptx::mbar_wait(&o_full[g], (nkv - 1) & 1, 210)) {
-      ptx::tc_fence_after_sync();
-      const float inv_l = 1.0f / l_run;
+
+    // ---- merge the two streams of the row group and write the result
+    // The K stages of this row group are free once both streams have seen their last P V product.
+    float* xchg = reinterpret_cast<float*>(s_k + g * kStages * Cfg::kKBytes) + r * Cfg::kXchgStride;
+    static_assert(128 * (DPAD + 3) * 4 <= kStages * Cfg::kKBytes, "exchange area does not fit in the K stages");
+    // the last P V product: then all of them are complete
+    ok = ok && ptx::mbar_wait(&o_full[g * 3 + (nhalf - 1) % 3], ((nhalf - 1) / 3) & 1, 210);
+    ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-wide: decide per warp
+    if (u == 1) {
+      if (ok) {
+        ptx::tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < DPAD / 32; ++c) {
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32b_x32(tmem_o + c * 32, raw);
-        ptx::tmem_ld_wait();
+        for (int cb = 0; cb < DPAD / 16; ++cb) {
+          uint32_t o16[16];
+          ptx::tmem_ld_32x32b_x16(tmem_o + cb * 16, o16);
+          ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(raw[i])) * inv_l;
+          for (int i = 0; i < 16; ++i) xchg[cb * 16 + i] = __uint_as_float(o16[i]);
+        }
+        xchg[DPAD] = s_cur;
+        xchg[DPAD + 1] = l_run;
+      } else {
+        xchg[DPAD + 1] = -1.f;  // tells the partner that this stream gave up
       }
-      if (q_idx < p.lq) {
-        const long long row = static_cast<long long>(b) * p.lq + q_idx;
-        if (p.g != nullptr) {
-          const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD;
+    }
+    // all 8 warps of the row group meet here exactly once, whatever happened above
+    asm volatile("bar.sync %0, 256;" ::"r"(1 + g) : "memory");
+    if (u == 0 && __all_sync(0xffffffffu, ok && xchg[DPAD + 1] >= 0.f)) {
+      ptx::tc_fence_after_sync();
+      const float s_o = xchg[DPAD], l_o = xchg[DPAD + 1];
+      const float s_m = fmaxf(s_cur, s_o);
+      const float w_e = exp2f(s_cur - s_m), w_o = exp2f(s_o - s_m);
+      const float inv_l = 1.0f / (l_run * w_e + l_o * w_o);
+      const float c_e = w_e * inv_l, c_o = w_o * inv_l;
+      const bool row_ok = q_idx < p.lq;  // rows past the end still take part in the warp-wide loads
+      const long long row = static_cast<long long>(b) * p.lq + (row_ok ? q_idx : 0);
+      const __nv_bfloat16* gp =
+          p.g != nullptr ? reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD : nullptr;
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + h * p.d;
+      {
 #pragma unroll
-          for (int i = 0; i < DPAD; i += 8) {
-            const uint4 u = *reinterpret_cast<const uint4*>(gp + i);
-            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        for (int cb = 0; cb < DPAD / 16; ++cb) {
+          uint32_t o16[16];
+          ptx::tmem_ld_32x32b_x16(tmem_o + cb * 16, o16);
+          ptx::tmem_ld_wait();
+          float v[16];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[t]));
-              acc[i + t * 2] *= sigmoidf_fast(f.x);
-              acc[i + t * 2 + 1] *= sigmoidf_fast(f.y);
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(o16[i]) * c_e + xchg[cb * 16 + i] * c_o;
+          if (gp != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              const uint4 gu = *reinterpret_cast<const uint4*>(gp + cb * 16 + i);
+              const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                v[i + k * 2] *= sigmoidf_fast(__uint_as_float(gw[k] << 16));
+                v[i + k * 2 + 1] *= sigmoidf_fast(__uint_as_float(gw[k] & 0xffff0000u));
+              }
             }
           }
-        }
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + h * p.d;
 #pragma unroll
-        for (int i = 0; i < DPAD; i += 8) {
-          if (i < p.d)  // d is a multiple of 8
-            *reinterpret_cast<uint4*>(o + i) =
-                make_uint4(pack_bf16x2(acc[i], acc[i + 1]), pack_bf16x2(acc[i + 2], acc[i + 3]),
-                           pack_bf16x2(acc[i + 4], acc[i + 5]), pack_bf16x2(acc[i + 6], acc[i + 7]));
+          for (int i = 0; i < 16; i += 8) {
+            if (row_ok && cb * 16 + i < p.d)  // d is a multiple of 8
+              *reinterpret_cast<uint4*>(o + cb * 16 + i) =
+                  make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                             pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+          }
         }
       }
     }

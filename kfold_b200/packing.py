@@ -22,6 +22,10 @@ def interleave_glu(value_w: torch.Tensor, gate_w: torch.Tensor, half: int = GLU_
     return torch.stack((v, g), dim=1).reshape(2 * n, k).contiguous()
 
 
+# The tensor-core attention kernel keeps its logits in log2 units: the query projection carries log2(e) / sqrt(D).
+LOG2E = 1.4426950408889634
+
+
 def split3_weights(w: torch.Tensor) -> torch.Tensor:
     """fp32 [n, k] -> bf16 [n, 6k] = [w0 | w1 | w0 | w1 | w2 | w0] with w = w0 + w1 + w2 (bf16 parts): the B operand of
     the fp32-accurate GEMMs, matching activations stored as [x0 | x0 | x1 | x1 | x0 | x2]."""
@@ -78,7 +82,7 @@ def _pad_heads(w: torch.Tensor, heads: int, d: int, dp: int, scale: float = 1.0)
 def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Weights of TriangleAttention (model/primitives/triangle_attention.py:338-373).
 
-    One projection matrix [q / sqrt(D) | k | g | v | triangle-bias] with every head padded to the
+    One projection matrix [q * log2(e) / sqrt(D) | k | g | v | triangle-bias] with every head padded to the
     kernel's head stride and the bias rows padded to 32.  The fp32-accurate packing keeps the heads unpadded
     and stores every matrix as its bf16 triple split.
     """
@@ -102,7 +106,7 @@ def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool
     wz = w["linear.weight"].detach().float()
     wz_pad = wz.new_zeros(32, c)
     wz_pad[:heads] = wz
-    proj = torch.cat([f("mha.linear_q.weight", d ** -0.5), f("mha.linear_k.weight"), f("mha.linear_g.weight"),
+    proj = torch.cat([f("mha.linear_q.weight", d ** -0.5 * LOG2E), f("mha.linear_k.weight"), f("mha.linear_g.weight"),
                       f("mha.linear_v.weight"), wz_pad], dim=0)
     return {
         "ln_w": _dev(w["layer_norm.weight"], device, torch.float32),
@@ -115,7 +119,7 @@ def pack_triatt(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool
 
 def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Projections of AttentionPairBias (model/layers/folding/attention_pair_bias.py:30-67):
-    [q / sqrt(D) (+ bias, same scale) | k | g | v], heads padded; output projection as is.
+    [q * log2(e) / sqrt(D) (+ bias, same scale) | k | g | v], heads padded; output projection as is.
     The fp32-accurate packing keeps the heads unpadded and stores the matrices as bf16 triple splits."""
     c = int(w["linear_q.weight"].shape[1])
     d = c // heads
@@ -138,7 +142,7 @@ def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = 
         }
     dp = head_dim_pad(d)
     f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
-    qs = d ** -0.5
+    qs = d ** -0.5 * LOG2E
     proj = torch.cat([f("linear_q.weight", qs), f("linear_k.weight"), f("linear_g.weight"), f("linear_v.weight")], dim=0)
     pb = torch.zeros(4 * heads * dp, dtype=torch.float32)
     if w.get("linear_q.bias") is not None:

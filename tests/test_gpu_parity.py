@@ -293,6 +293,31 @@ def test_apb_single_track_size(dev):
     _check(mx, r, "apb single track")
 
 
+def test_attention_stabiliser_moves_when_later_keys_dominate(dev):
+    """The attention kernel keeps a lagging stabiliser (the row maximum of the first 64 keys of a stream) and moves it
+    only when a later half tile would overflow.  A pair bias that grows by 100 per 64 keys (144 in log2 units, beyond
+    the 2^100 row-sum limit) forces that path on every half tile; rows whose first keys are masked start from -1e9."""
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    rng = synth._Rng(78)
+    L = 320
+    w = synth.apb_weights(rng, 384, None)
+    s = rng.normal(1, L, 384).bfloat16()
+    ramp = (torch.arange(L) // 64).float() * 100.0
+    bias = (rng.normal(1, 16, L, L) + ramp).bfloat16()
+    bias[:, ::2, 200:, :] = rng.normal(1, 8, L - 200, L).bfloat16()      # and rows without the ramp
+    mask = torch.ones(1, L, dtype=torch.bool)
+    mask[:, :70] = False                                                   # first half tile fully masked
+    mask[:, 300:] = False
+    mod = M.SelfAttentionPairBias(384, 16, None, "confidence").to(dev)
+    mod.load_state_dict(w, strict=True)
+    out = mod(s.to(dev), None, bias.to(dev), mask.to(dev)).float().cpu()
+    assert torch.isfinite(out).all()
+    ref = _oracle_on(dev, O.self_attention_pair_bias, s.float(), None, bias.float(), mask, w, 16)
+    mx, r = err_stats(out, ref)
+    _check(mx, r, "stabiliser moves")
+
+
 def test_diffusion_modules_against_reference_golden(dev):
     """AdaLN-conditioned pair-bias attention, conditioned transition and a 2-block token-transformer stack
     (bias shared by the diffusion samples) against the reference outputs; fp32 residual stream, bf16 compute."""

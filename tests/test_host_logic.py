@@ -36,7 +36,7 @@ def test_pack_triatt_projection_matches_unpacked_math():
     pk = packing.pack_triatt(w, 4, "cpu", torch.float32)
     x = torch.randn(5, 128)
     y = x @ pk["w_proj"].T
-    q = (x @ w["mha.linear_q.weight"].T) / 32 ** 0.5
+    q = (x @ w["mha.linear_q.weight"].T) / 32 ** 0.5 * packing.LOG2E   # the kernel keeps logits in log2 units
     assert torch.allclose(y[:, :128], q, atol=1e-5)
     assert torch.allclose(y[:, 128:256], x @ w["mha.linear_k.weight"].T, atol=1e-5)
     assert torch.allclose(y[:, 256:384], x @ w["mha.linear_g.weight"].T, atol=1e-5)
@@ -52,7 +52,7 @@ def test_pack_apb_pads_d24_to_32():
     assert pk["proj_bias"].shape == (4 * 16 * 32,)
     x = torch.randn(3, 384)
     y = (x @ pk["w_proj"].T + pk["proj_bias"]).reshape(3, 4, 16, 32)
-    q = ((x @ w["linear_q.weight"].T + w["linear_q.bias"]) / 24 ** 0.5).reshape(3, 16, 24)
+    q = ((x @ w["linear_q.weight"].T + w["linear_q.bias"]) / 24 ** 0.5 * packing.LOG2E).reshape(3, 16, 24)
     assert torch.allclose(y[:, 0, :, :24], q, atol=1e-5)
     assert torch.all(y[:, 0, :, 24:] == 0)
 
