@@ -209,6 +209,15 @@ KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, void* out, long
  * out_gate : bf16 logits [rows / samples, c] = Linear(s) + bias, shared by the samples of a group.
  */
 KFB_API size_t kfb_cond_transition_workspace_bytes(long long rows, int hidden);
+KFB_API size_t kfb_cond_transition_workspace_bytes_precise(long long rows, int c, int hidden);
+
+/* y = x W^T (+ bias) at fp32 accuracy on the tensor core: x fp32 [rows, k], w6 = the bf16 triple split of W
+ * [n, 6k] (kfold_b200.packing.split3_weights), bias fp32 [n] or NULL, out fp32 [rows, n].  The small projections of
+ * the conditioning in the float32 sampler (src/kfold/model/primitives/normalization.py:117-125,
+ * src/kfold/model/layers/folding/attention_pair_bias.py:151-156). */
+KFB_API size_t kfb_linear_fp32_workspace_bytes(long long rows, int k);
+KFB_API int kfb_linear_fp32(const void* x, const void* w6, const float* bias, void* out, void* workspace,
+                            size_t workspace_bytes, long long rows, int n, int k, void* stream);
 KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_packed, const void* w_out,
                                     const void* out_gate, void* out, const void* resid, void* workspace,
                                     size_t workspace_bytes, long long rows, int c, int hidden, int samples, int l, int dtype,

@@ -47,6 +47,7 @@ _SIGNATURES = {
     "kfb_triatt_finish": [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_pair_bias_rows_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int,
                                c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_linear_fp32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll, c_int, c_int, c_void_p],
     "kfb_adaln_fwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_cond_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -64,6 +65,8 @@ _SIZE_FUNCS = {
     "kfb_trimul_workspace_bytes_precise": [c_int, c_int, c_int],
     "kfb_transition_workspace_bytes_precise": [c_ll, c_int, c_int],
     "kfb_cond_transition_workspace_bytes": [c_ll, c_int],
+    "kfb_cond_transition_workspace_bytes_precise": [c_ll, c_int, c_int],
+    "kfb_linear_fp32_workspace_bytes": [c_ll, c_int],
     "kfb_transition_static_max_bytes": [],
     "kfb_pair_bias_workspace_bytes": [c_int, c_int, c_int],
     "kfb_transition_workspace_bytes": [c_ll, c_int, c_int],

@@ -212,7 +212,7 @@ def convert(model: torch.nn.Module, diffusion: bool = False) -> int:
                 n += 1
         elif name in ("TriangleAttentionStartingNode", "TriangleAttentionEndingNode", "TriangleAttention"):
             d = m.c_hidden
-            if d % 8 == 0 and 24 <= d <= 64 and m.inf == 1e9:
+            if d % 8 == 0 and 16 <= d <= 64 and m.inf == 1e9:
                 m.kernel_backend = BACKEND
                 n += 1
         elif name == "SelfAttentionPairBias" and apb_supported(m):

@@ -223,9 +223,9 @@ __global__ void __launch_bounds__(128) layernorm_cm_split_kernel(const float* __
 // ------------------------------------------------------------------------------------------------
 // Adaptive LayerNorm (AdaLN): one warp per row, same register layout as layernorm_rows_kernel.
 // ------------------------------------------------------------------------------------------------
-template <typename TI, typename TO, int G>
+template <typename TI, typename TO, typename TG, int G>
 __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ a, TO* __restrict__ y,
-                                                         const __nv_bfloat16* __restrict__ gv, long long rows, int c,
+                                                         const TG* __restrict__ gv, long long rows, int c,
                                                          int samples, int l, float eps) {
   const int lane = threadIdx.x & 31;
   const long long warps_per_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
        row += warps_per_grid) {
     const TI* xr = a + row * c;
     const long long srow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
-    const __nv_bfloat16* gr = gv + srow * 2 * c;
+    const TG* gr = gv + srow * 2 * c;
     float2 v[G];
     float s = 0.f;
 #pragma unroll
@@ -259,8 +259,8 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
     for (int g = 0; g < G; ++g) {
       const int ch = (lane + 32 * g) * 2;
       if (ch < c) {
-        const float2 gate = load2<__nv_bfloat16>(gr + ch);
-        const float2 shift = load2<__nv_bfloat16>(gr + c + ch);
+        const float2 gate = load2<TG>(gr + ch);
+        const float2 shift = load2<TG>(gr + c + ch);
         const float s0 = 1.f / (1.f + __expf(-gate.x)), s1 = 1.f / (1.f + __expf(-gate.y));
         store2<TO>(yr + ch, s0 * (v[g].x * rstd) + shift.x, s1 * (v[g].y * rstd) + shift.y);
       }
@@ -268,9 +268,10 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
   }
 }
 
-template <typename TI, typename TO>
-static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const __nv_bfloat16* gv, long long rows, int c,
+template <typename TI, typename TO, typename TG>
+static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const void* gv_, long long rows, int c,
                           int samples, int l, float eps) {
+  const TG* gv = static_cast<const TG*>(gv_);
   const int warps = 8;
   long long blocks = (rows + warps - 1) / warps;
   const long long cap = static_cast<long long>(sm_count()) * 16;
@@ -278,7 +279,7 @@ static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const __n
   const int g = cdiv(c, 64);
   LaunchScope scope(stream, "adaln_rows");
 #define KFB_ADALN(GG)                                                                                          \
-  adaln_rows_kernel<TI, TO, GG><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(                      \
+  adaln_rows_kernel<TI, TO, TG, GG><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(                  \
       static_cast<const TI*>(a), static_cast<TO*>(y), gv, rows, c, samples, l, eps)
   if (g <= 2) KFB_ADALN(2);
   else if (g <= 6) KFB_ADALN(6);
@@ -293,16 +294,18 @@ static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const __n
   return KFB_OK;
 }
 
-int launch_adaln(cudaStream_t stream, const void* a, void* y, const __nv_bfloat16* gv, long long rows, int c, int samples,
+int launch_adaln(cudaStream_t stream, const void* a, void* y, const void* gv, long long rows, int c, int samples,
                  int l, float eps, int in_dtype, int out_dtype) {
   KFB_CHECK_ARG(rows >= 0 && c > 0 && c % 2 == 0 && samples >= 1 && l >= 1, "adaln: rows %lld c %d samples %d l %d", rows, c,
                 samples, l);
   KFB_CHECK_ARG(rows % (static_cast<long long>(samples) * l) == 0, "adaln: rows %lld is not a multiple of samples*l", rows);
   if (rows == 0) return KFB_OK;
   if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16)
-    return adaln_dispatch<__nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+    return adaln_dispatch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
   if (in_dtype == KFB_FP32 && out_dtype == KFB_BF16)
-    return adaln_dispatch<float, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+    return adaln_dispatch<float, __nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+  if (in_dtype == KFB_FP32_PRECISE && out_dtype == KFB_FP32)  // everything fp32, gate / shift rows included
+    return adaln_dispatch<float, float, float>(stream, a, y, gv, rows, c, samples, l, eps);
   set_error("adaln: unsupported dtype combination");
   return KFB_ERR_INVALID_ARGUMENT;
 }

@@ -24,7 +24,7 @@ int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, co
 // Adaptive LayerNorm: y[r] = sigmoid(g[s(r)]) * LN(a[r]) + v[s(r)], LN without affine, fp32 statistics.
 // a, y: `rows` rows of c channels; gv: rows_s rows of [2c] (gate logits | shift), bf16.  Row r of a uses row
 // (r / (samples * l)) * l + r % l of gv: the conditioning is shared by the `samples` diffusion samples.
-int launch_adaln(cudaStream_t stream, const void* a, void* y, const __nv_bfloat16* gv, long long rows, int c, int samples,
+int launch_adaln(cudaStream_t stream, const void* a, void* y, const void* gv, long long rows, int c, int samples,
                  int l, float eps, int in_dtype, int out_dtype);
 
 }  // namespace kfb

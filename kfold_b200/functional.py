@@ -146,17 +146,38 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, o
     return out.view(*x.shape[:-1], n)
 
 
+def linear_fp32(x: torch.Tensor, w6: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x w^T (+ bias) at float32 accuracy: x (..., k) float32, w6 (n, 6k) the bf16 triple split of w
+    (packing.split3_weights), bias float32 (n,) or None; float32 result."""
+    _require_cuda(x, w6)
+    k = x.shape[-1]
+    if w6.shape[1] != 6 * k:
+        raise ValueError(f"linear_fp32: weight {tuple(w6.shape)} is not the triple split of a (n, {k}) matrix")
+    x2 = x.reshape(-1, k).float().contiguous()
+    n = w6.shape[0]
+    out = torch.empty(x2.shape[0], n, dtype=torch.float32, device=x.device)
+    lib = L.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, lib.kfb_linear_fp32_workspace_bytes(x2.shape[0], k))
+        L.check(lib.kfb_linear_fp32(L.ptr(x2), L.ptr(w6), L.ptr(bias), L.ptr(out), L.ptr(ws), ws.numel(), x2.shape[0], n, k,
+                                    L.stream_ptr()))
+    return out.view(*x.shape[:-1], n)
+
+
 def adaln(a: torch.Tensor, gate_shift: torch.Tensor, samples: int, eps: float = 1e-5) -> torch.Tensor:
     """sigmoid(g) * LayerNorm(a) + v  (model/primitives/normalization.py:117-125).
     a (groups * samples, L, c) flattened as rows; gate_shift (groups, L, 2c) bf16 = [g | v]."""
     _require_cuda(a, gate_shift)
     c, l = a.shape[-1], a.shape[-2]
     a2 = a.reshape(-1, c).contiguous()
-    out = torch.empty(a2.shape, dtype=torch.bfloat16, device=a.device)
+    precise = gate_shift.dtype == torch.float32     # float32 gate / shift rows: everything stays float32
+    if precise:
+        a2 = a2.float()
+    out = torch.empty(a2.shape, dtype=torch.float32 if precise else torch.bfloat16, device=a.device)
     gs = gate_shift.reshape(-1, 2 * c).contiguous()
     with torch.cuda.device(a.device):
         L.check(L.lib().kfb_adaln_fwd(L.ptr(a2), L.ptr(gs), L.ptr(out), a2.shape[0], c, samples, l, eps,
-                                      L.dtype_code(a2.dtype), L.stream_ptr()))
+                                      L.KFB_FP32_PRECISE if precise else L.dtype_code(a2.dtype), L.stream_ptr()))
     return out.view(a.shape)
 
 
@@ -168,16 +189,23 @@ def conditioned_transition(x_normed: torch.Tensor, packed: dict, out_gate: torch
     c, hidden, l = packed["c"], packed["hidden"], x_normed.shape[-2]
     x2 = x_normed.reshape(-1, c).contiguous()
     rows = x2.shape[0]
-    out = torch.empty(rows, c, dtype=out_dtype or (resid.dtype if resid is not None else x_normed.dtype), device=x2.device)
+    precise = bool(packed.get("precise"))
+    want = out_dtype or (resid.dtype if resid is not None else x_normed.dtype)
+    out = torch.empty(rows, c, dtype=torch.float32 if precise else want, device=x2.device)
     r2 = None if resid is None else resid.reshape(-1, c).contiguous()
     g2 = out_gate.reshape(-1, c).contiguous()
+    if precise:
+        x2, g2 = x2.float(), g2.float()
+        r2 = None if r2 is None else r2.float()
     lib = L.lib()
     with torch.cuda.device(x2.device):
-        ws = _workspace(x2.device, lib.kfb_cond_transition_workspace_bytes(rows, hidden))
+        need = (lib.kfb_cond_transition_workspace_bytes_precise(rows, c, hidden) if precise
+                else lib.kfb_cond_transition_workspace_bytes(rows, hidden))
+        ws = _workspace(x2.device, need)
         L.check(lib.kfb_cond_transition_fwd(L.ptr(x2), L.ptr(packed["w_swiglu"]), L.ptr(packed["w_out"]), L.ptr(g2), L.ptr(out),
                                             L.ptr(r2), L.ptr(ws), ws.numel(), rows, c, hidden, samples, l,
-                                            L.dtype_code(out.dtype), L.stream_ptr()))
-    return out.view(x_normed.shape)
+                                            L.KFB_FP32_PRECISE if precise else L.dtype_code(out.dtype), L.stream_ptr()))
+    return out.view(x_normed.shape).to(want)
 
 
 def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor, packed: dict,

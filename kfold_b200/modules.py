@@ -95,13 +95,6 @@ def compute_dtype(x: torch.Tensor) -> torch.dtype:
     return x.dtype
 
 
-def _require_bf16(dt: torch.dtype, what: str) -> None:
-    if dt != torch.bfloat16:
-        raise NotImplementedError(
-            f"{what}: compute dtype {dt} is not available in this build; run under "
-            "torch.autocast('cuda', dtype=torch.bfloat16) or pass bfloat16 inputs")
-
-
 def _is_precise(dt: torch.dtype, what: str) -> bool:
     """bfloat16 compute -> the tensor-core path; float32 compute -> the fp32-accurate path (split operands)."""
     if dt == torch.bfloat16:
@@ -243,19 +236,26 @@ class AdaLN(nn.Module, _PackedMixin):
         self.linear_g = Linear(channel_s, channel_a)
         self.linear_bias = LinearNoBias(channel_s, channel_a)
 
-    def gate_shift(self, s: torch.Tensor) -> torch.Tensor:
-        """[sigmoid logits | shift] of the conditioning, bf16 (..., L, 2 c_a): one small LayerNorm + GEMM per token."""
+    def gate_shift(self, s: torch.Tensor, precise: bool = False) -> torch.Tensor:
+        """[sigmoid logits | shift] of the conditioning, (..., L, 2 c_a): one small LayerNorm + GEMM per token.
+        bf16, or float32 from the split-operand GEMM when ``precise``."""
+        if precise:
+            pk = self._packed(s.device, torch.float32, lambda sd, dev: packing.pack_adaln(sd, dev, precise=True))
+            sn = F.layer_norm(s.float(), pk["ln_s_w"], None, self.layernorm_s.eps, out_dtype=torch.float32)
+            return F.linear_fp32(sn, pk["w_gs"], pk["b_gs"])
         pk = self._packed(s.device, torch.bfloat16, packing.pack_adaln)
         sn = F.layer_norm(s, pk["ln_s_w"], None, self.layernorm_s.eps, out_dtype=torch.bfloat16)
         return F.linear(sn, pk["w_gs"], pk["b_gs"])
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
-        """a (B, Ns, L, c_a), s (B, 1 or Ns, L, c_s) -> bf16 (B, Ns, L, c_a)."""
+        """a (B, Ns, L, c_a), s (B, 1 or Ns, L, c_s) -> (B, Ns, L, c_a): bf16 under bfloat16 compute, float32 under
+        float32 compute."""
         _check_inference(a)
+        precise = _is_precise(compute_dtype(a), "AdaLN")
         with torch.autocast(a.device.type, enabled=False):
             samples = _sample_share(a, s)
-            return F.adaln(a, self.gate_shift(s), samples)
+            return F.adaln(a, self.gate_shift(s, precise), samples)
 
 
 def _sample_share(a: torch.Tensor, s: torch.Tensor) -> int:
@@ -301,11 +301,12 @@ class SelfAttentionPairBias(nn.Module, _PackedMixin):
         return self._packed(device, torch.float32 if precise else torch.bfloat16,
                             lambda sd, dev: packing.pack_apb({k: sd[k] for k in keys}, self.num_heads, dev, precise=precise))
 
-    def _ada_out(self, device):
+    def _ada_out(self, device, precise: bool = False):
         w, b = self.linear_ada_out.weight, self.linear_ada_out.bias
-        key = (device, w.data_ptr(), b.data_ptr(), None if torch.is_inference(w) else (w._version, b._version))
+        key = (device, precise, w.data_ptr(), b.data_ptr(), None if torch.is_inference(w) else (w._version, b._version))
         if self._ada_key != key:
-            self._ada_w = (w.detach().to(device, torch.bfloat16).contiguous(), b.detach().to(device, torch.float32).contiguous())
+            wd = packing.split3_weights(w).to(device) if precise else w.detach().to(device, torch.bfloat16).contiguous()
+            self._ada_w = (wd, b.detach().to(device, torch.float32).contiguous())
             self._ada_key = key
         return self._ada_w
 
@@ -316,11 +317,16 @@ class SelfAttentionPairBias(nn.Module, _PackedMixin):
         With ``residual`` the result is a + update (fused into the last kernel)."""
         _check_inference(a)
         precise = _is_precise(compute_dtype(a), "SelfAttentionPairBias")
-        if precise and self.use_single_conditioning:
-            raise NotImplementedError("SelfAttentionPairBias with single conditioning computes in bfloat16 only; run the "
-                                      "sampler's token transformer under torch.autocast('cuda', dtype=torch.bfloat16)")
         pk = self._apb_packed(a.device, precise)
         with torch.autocast(a.device.type, enabled=False):
+            if precise and self.use_single_conditioning:
+                assert s is not None
+                share = _sample_share(a, s)
+                an = F.adaln(a.float(), self.adaln_a.gate_shift(s, True), share)
+                w6, b_ada = self._ada_out(a.device, True)
+                gate = F.linear_fp32(s.float(), w6, b_ada)
+                return F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype, out_gate=gate, gate_share=share,
+                                             resid=a if residual else None)
             if precise:
                 an = F.layer_norm(a.float(), self.layernorm_a.weight, self.layernorm_a.bias, self.layernorm_a.eps,
                                   out_dtype=torch.float32)
@@ -352,12 +358,17 @@ class ConditionedTransitionBlock(nn.Module, _PackedMixin):
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor, residual: bool = False) -> torch.Tensor:
         _check_inference(a)
-        _require_bf16(compute_dtype(a), "ConditionedTransitionBlock")
-        pk = self._packed(a.device, torch.bfloat16, packing.pack_cond_transition)
+        precise = _is_precise(compute_dtype(a), "ConditionedTransitionBlock")
+        pk = self._packed(a.device, torch.float32 if precise else torch.bfloat16,
+                          lambda sd, dev: packing.pack_cond_transition(sd, dev, precise=precise))
         with torch.autocast(a.device.type, enabled=False):
             share = _sample_share(a, s)
-            an = F.adaln(a, self.adaln.gate_shift(s), share)
-            gate = F.linear(s, pk["w_g"], pk["b_g"])
+            if precise:
+                an = F.adaln(a.float(), self.adaln.gate_shift(s, True), share)
+                gate = F.linear_fp32(s.float(), pk["w_g"], pk["b_g"])
+            else:
+                an = F.adaln(a, self.adaln.gate_shift(s), share)
+                gate = F.linear(s, pk["w_g"], pk["b_g"])
             return F.conditioned_transition(an, pk, gate, share, resid=a if residual else None, out_dtype=a.dtype)
 
 
@@ -388,18 +399,19 @@ class CachedGlobalTransformerStack(nn.Module):
         self._bias_cache = None
         self._bias_key = None
 
-    def _prepared_bias(self, pair_bias: torch.Tensor):
-        key = (pair_bias.data_ptr(), tuple(pair_bias.shape), pair_bias.dtype, pair_bias._version)
+    def _prepared_bias(self, pair_bias: torch.Tensor, precise: bool = False):
+        key = (pair_bias.data_ptr(), tuple(pair_bias.shape), pair_bias.dtype, pair_bias._version, precise)
         if self._bias_key != key:
-            # (*, N, H, L, L) -> N tensors (*, H, L, L) bf16, contiguous
-            pb = pair_bias.movedim(-4, 0).to(torch.bfloat16).contiguous()
+            # (*, N, H, L, L) -> N tensors (*, H, L, L), contiguous: bf16 for the tensor-core kernel, float32 for the
+            # fp32-accurate one
+            pb = pair_bias.movedim(-4, 0).to(torch.float32 if precise else torch.bfloat16).contiguous()
             self._bias_cache, self._bias_key = pb, key
         return self._bias_cache
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
         _check_inference(a)
-        pb = self._prepared_bias(pair_bias)
+        pb = self._prepared_bias(pair_bias, _is_precise(compute_dtype(a), "CachedGlobalTransformerStack"))
         for i, blk in enumerate(self.blocks):
             a = blk(a, s, pb[i], mask)
         return a

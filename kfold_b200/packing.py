@@ -173,7 +173,7 @@ def pack_transition(w: dict, device, dtype=torch.bfloat16, precise: bool = False
     }
 
 
-def pack_adaln(w: dict, device, dtype=torch.bfloat16) -> dict:
+def pack_adaln(w: dict, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """AdaLN (model/primitives/normalization.py:99-115): the gate and shift projections of the conditioning
     stacked into one [2 c_a, c_s] matrix (bias only on the gate half)."""
     wg, wb = w["linear_g.weight"].detach().float(), w["linear_bias.weight"].detach().float()
@@ -182,21 +182,21 @@ def pack_adaln(w: dict, device, dtype=torch.bfloat16) -> dict:
     bias[:c_a] = w["linear_g.bias"].detach().float()
     return {
         "ln_s_w": _dev(w["layernorm_s.weight"], device, torch.float32),
-        "w_gs": _dev(torch.cat([wg, wb], dim=0), device, dtype),
+        "w_gs": _w(torch.cat([wg, wb], dim=0), device, precise),
         "b_gs": _dev(bias, device, torch.float32),
-        "c_a": int(c_a), "c_s": int(wg.shape[1]),
+        "c_a": int(c_a), "c_s": int(wg.shape[1]), "precise": precise,
     }
 
 
-def pack_cond_transition(w: dict, device, dtype=torch.bfloat16) -> dict:
+def pack_cond_transition(w: dict, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """ConditionedTransitionBlock (model/layers/folding/diffusion_transformer.py:50-71)."""
     sw = w["swiglu.linear.weight"].detach().float()
     hidden = sw.shape[0] // 2
     return {
-        "adaln": pack_adaln({k[len("adaln."):]: v for k, v in w.items() if k.startswith("adaln.")}, device, dtype),
-        "w_swiglu": _dev(interleave_glu(sw[:hidden], sw[hidden:]), device, dtype),
-        "w_out": _dev(w["linear_out.weight"], device, dtype),
-        "w_g": _dev(w["linear_g.weight"], device, dtype),
+        "adaln": pack_adaln({k[len("adaln."):]: v for k, v in w.items() if k.startswith("adaln.")}, device, dtype, precise),
+        "w_swiglu": _w(interleave_glu(sw[:hidden], sw[hidden:], GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_out": _w(w["linear_out.weight"], device, precise),
+        "w_g": _w(w["linear_g.weight"], device, precise),
         "b_g": _dev(w["linear_g.bias"], device, torch.float32),
-        "c": int(sw.shape[1]), "hidden": int(hidden),
+        "c": int(sw.shape[1]), "hidden": int(hidden), "precise": precise,
     }

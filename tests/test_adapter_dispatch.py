@@ -82,9 +82,9 @@ def test_attention_pair_bias_routes_after_convert(ref, recorder):
     holder = torch.nn.ModuleList([mod, ref.TriangleMultiplicationOutgoing(128), ref.TriangleAttentionEndingNode(128, 4),
                                   ref.SelfAttentionPairBias(768, 16, 384, "diffusion_global", kernel_backend="sdpa"),
                                   ref.TriangleAttentionStartingNode(64, 4)])
-    assert adapter.convert(holder) == 3          # the fp32 diffusion attention and the D=16 tri-att stay as they were
-    assert holder[3].kernel_backend == "sdpa" and holder[4].kernel_backend == "torch"
-    assert adapter.convert(holder, diffusion=True) == 4
+    assert adapter.convert(holder) == 4          # the float32 diffusion attention stays as it was unless asked for
+    assert holder[3].kernel_backend == "sdpa" and holder[4].kernel_backend == "b200"   # D=16 tri-att is taken
+    assert adapter.convert(holder, diffusion=True) == 5
     s = torch.randn(1, 12, 384)
     bias = torch.randn(1, 16, 12, 12)
     mask = torch.ones(1, 12, dtype=torch.bool)

@@ -97,8 +97,6 @@ GOLDEN_GPU_CASES = [n for n, c in cases.CASES.items()
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16io", "fp32io"])
 @pytest.mark.parametrize("name", GOLDEN_GPU_CASES)
 def test_against_reference_golden(dev, name, dtype):
-    if name == "triatt_start_c64":
-        pytest.skip("head dim 16 (apo stack shape) is not built yet")
     gold = load_golden(name)
     out = _run_case(name, dev, dtype).float().cpu()
     assert torch.isfinite(out).all()
@@ -342,6 +340,31 @@ def test_diffusion_modules_against_reference_golden(dev):
         stack.load_state_dict(inp["w"], strict=True)
         out = stack(to(inp["a"]), to(inp["s"]), to(inp["pair_bias"]), to(inp["mask"]))
         _check(*err_stats(out.cpu(), load_golden("diffusion_stack")["out"]), "diffusion_stack")
+
+
+def test_diffusion_modules_float32_compute(dev):
+    """The same three golden cases under float32 compute (how the reference runs its sampler): the fp32-accurate path."""
+    from kfold_b200 import modules as M
+    to = lambda t: t.to(dev)
+
+    def check(out, name):
+        mx, r = err_stats(out.cpu(), load_golden(name)["out"])
+        assert out.dtype == torch.float32 and mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"{name}: {mx:.3e} {r:.3e}"
+
+    inp = cases.build_inputs("apb_diffusion")
+    mod = M.SelfAttentionPairBias(768, 16, 384, "diffusion_global").to(dev)
+    mod.load_state_dict(inp["w"], strict=True)
+    check(mod(to(inp["a"]), to(inp["s"]), to(inp["pair_bias"]), to(inp["mask"])), "apb_diffusion")
+
+    inp = cases.build_inputs("cond_transition")
+    mod = M.ConditionedTransitionBlock(768, 384).to(dev)
+    mod.load_state_dict(inp["w"], strict=True)
+    check(mod(to(inp["a"]), to(inp["s"])), "cond_transition")
+
+    inp = cases.build_inputs("diffusion_stack")
+    stack = M.CachedGlobalTransformerStack(768, 384, 16, 2).to(dev)
+    stack.load_state_dict(inp["w"], strict=True)
+    check(stack(to(inp["a"]), to(inp["s"]), to(inp["pair_bias"]), to(inp["mask"])), "diffusion_stack")
 
 
 def test_diffusion_stack_config4_shape(dev):
