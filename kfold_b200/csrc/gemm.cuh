@@ -139,6 +139,14 @@ __device__ __forceinline__ void epi_store_split(const EpiSeg& sg, long long row_
   }
 }
 
+// 32-byte global store (one full sector per thread and instruction)
+__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4,
+                                             uint32_t a5, uint32_t a6, uint32_t a7) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a0), "r"(a1), "r"(a2), "r"(a3),
+               "r"(a4), "r"(a5), "r"(a6), "r"(a7)
+               : "memory");
+}
+
 // Store 32 consecutive output values of one row.
 __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_off, int col_local, const float (&v)[32],
                                                 bool row_ok) {
@@ -147,15 +155,31 @@ __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_
   if (nvalid <= 0) return;
   if (sg.vec && nvalid == 32) {
     if (sg.out_fp32) {
-      float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(sg.dst) + row_off + col_local);
+      float* d = reinterpret_cast<float*>(sg.dst) + row_off + col_local;
+      if ((reinterpret_cast<uintptr_t>(d) & 31) == 0) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        for (int i = 0; i < 4; ++i)
+          st_global_v8(d + 8 * i, __float_as_uint(v[8 * i]), __float_as_uint(v[8 * i + 1]), __float_as_uint(v[8 * i + 2]),
+                       __float_as_uint(v[8 * i + 3]), __float_as_uint(v[8 * i + 4]), __float_as_uint(v[8 * i + 5]),
+                       __float_as_uint(v[8 * i + 6]), __float_as_uint(v[8 * i + 7]));
+      } else {
+        float4* d4 = reinterpret_cast<float4*>(d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      }
     } else {
-      uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(sg.dst) + row_off + col_local);
+      __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(sg.dst) + row_off + col_local;
+      uint32_t w[16];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        d[i] = make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
-                          pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+      for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+      if ((reinterpret_cast<uintptr_t>(d) & 31) == 0) {
+        st_global_v8(d, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+        st_global_v8(d + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+      } else {
+        uint4* d4 = reinterpret_cast<uint4*>(d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      }
     }
     return;
   }
