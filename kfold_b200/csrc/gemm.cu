@@ -107,7 +107,7 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
     if (sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && aligned && next_slot < 2 && !p.precise) {
       const uint64_t dims[4] = {(uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)sg.ncols, (uint64_t)p.batch};
       const uint64_t str[3] = {(uint64_t)sg.s_o * 2, (uint64_t)sg.s_col * 2, (uint64_t)sg.s_b * 2};
-      const uint32_t box[4] = {32, 1, 32, 1};
+      const uint32_t box[4] = {kBM, 1, 32, 1};
       KFB_TRY(make_tmap(&tout[next_slot], sg.dst, 2, 4, dims, str, box, 0));
       sg.tma_slot = next_slot++;
     }

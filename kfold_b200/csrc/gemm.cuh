@@ -83,7 +83,7 @@ struct GemmCfg {
   static constexpr int kBStage = BN * kBK * 2;
   static constexpr int kStageBytes = kAStage + kBStage;
   static constexpr int kMaxStages = 8;
-  static constexpr int kStagingBytes = kEpiWarps * 2 * 32 * 32 * 2;  // per epilogue warp: 2 slabs of [32 channels][32 rows] bf16
+  static constexpr int kStagingBytes = (kEpiWarps / 4) * 2 * 32 * kBM * 2;  // per group of 4 epilogue warps: 2 slabs of [32 channels][128 rows] bf16
   static constexpr int kBarrierBytes = 512;
   static constexpr int kSmemBytes = 232448 - 1024;        // everything an SM offers one CTA
   // after the operand ring comes EITHER the channel-major staging slabs OR two buffers of prefetched
@@ -218,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_a = smem;
   uint8_t* s_b = smem + kStages * Cfg::kAStage;
-  uint8_t* s_stage_out = smem + kStages * Cfg::kStageBytes;  // [epilogue warp][2][32 channels][32 rows] bf16 ...
+  uint8_t* s_stage_out = smem + kStages * Cfg::kStageBytes;  // [group of 4 epilogue warps][2][32 channels][128 rows] bf16 ...
   uint8_t* s_aux = s_stage_out;                               // ... or [2 buffers][gate, resid][2 halves? BN/64][128 x 64] bf16
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_stage_out + (AUX ? Cfg::kAuxBytes : Cfg::kStagingBytes));
   uint64_t* full_bar = bars;
@@ -227,7 +227,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* aux_full = tmem_empty + 2;   // [2]
   uint64_t* aux_empty = aux_full + 2;    // [2], one arrival per epilogue warp
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_empty + 2);
+  uint64_t* cm_bar = aux_empty + 2;      // [2 groups][slab free, slab written], 128 arrivals each
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cm_bar + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -250,6 +251,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       ptx::mbar_init(&aux_full[a], 1);
       ptx::mbar_init(&aux_empty[a], kEpiWarps);
     }
+    for (int a = 0; a < 4; ++a) ptx::mbar_init(&cm_bar[a], 128);
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
@@ -344,6 +346,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int r = quad * 32 + lane;
     uint32_t tile_iter = 0;
     bool ok = true;
+    // the row-mask byte of a tile is fetched one tile ahead, so that its latency never shows in the epilogue
+    auto load_mask = [&](int tile) -> float {
+      if (p.rowmask == nullptr || tile >= total_tiles) return 1.0f;
+      const int m_tile = tile / p.num_n_tiles;
+      const int nb = m_tile % p.n_blocks;
+      const int rest = m_tile / p.n_blocks;
+      const int o = rest % p.o_extent;
+      const int b = rest / p.o_extent;
+      const int n = nb * kBM + r;
+      if (n >= p.n_extent) return 1.0f;
+      return p.rowmask[static_cast<long long>(b) * p.m_b + static_cast<long long>(o) * p.m_o +
+                       static_cast<long long>(n) * p.m_n] ? 1.0f : 0.0f;
+    };
+    float mask_next = load_mask(blockIdx.x);
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
       const int m_tile = tile / p.num_n_tiles;
       const int n_tile = tile - m_tile * p.num_n_tiles;
@@ -353,6 +369,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int b = rest / p.o_extent;
       const int n = nb * kBM + r;
       const bool row_ok = n < p.n_extent;
+      const float mask_v = mask_next;
+      mask_next = load_mask(tile + gridDim.x);
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_phase = (tile_iter >> 1) & 1;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_phase, 104)) { ok = false; break; }
@@ -362,49 +380,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (AUX && !ptx::mbar_wait(&aux_full[tile_iter & 1], (tile_iter >> 1) & 1, 107)) { ok = false; break; }
       const uint32_t t_row = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quad * 32) << 16);
 
-      float mask_v = 1.0f;
-      if (p.rowmask != nullptr && row_ok)
-        mask_v = p.rowmask[static_cast<long long>(b) * p.m_b + static_cast<long long>(o) * p.m_o +
-                           static_cast<long long>(n) * p.m_n] ? 1.0f : 0.0f;
-
       constexpr int out_bn = GLU ? OUT_BN_GLU : BN;
       const int out_col_tile = n_tile * out_bn;
 #pragma unroll 1
       for (int c = chunk_phase * 32; c < out_bn; c += 32 * (kEpiWarps / 4)) {
         const int out_col = out_col_tile + c;
         float v[32];
-        {
-          uint32_t raw[32];
+        if (GLU && !PRECISE) {
+          // value and gate columns are fetched together: one round trip to tensor memory per chunk
+          uint32_t raw[32], rawg[32];
           ptx::tmem_ld_32x32b_x32(t_row + c, raw);
+          ptx::tmem_ld_32x32b_x32(t_row + OUT_BN_GLU + c, rawg);
           ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-          if (PRECISE) {
-            ptx::tmem_ld_32x32b_x32(t_row + BN + c, raw);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(raw[i]);
-          }
-        }
-        if (GLU) {
-          uint32_t raw[32];
-          ptx::tmem_ld_32x32b_x32(t_row + OUT_BN_GLU + c, raw);
-          ptx::tmem_ld_wait();
-          if (PRECISE) {
-            uint32_t raw2[32];
-            ptx::tmem_ld_32x32b_x32(t_row + BN + OUT_BN_GLU + c, raw2);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) + __uint_as_float(raw2[i]));
-          }
           if (p.glu == GLU_SIGMOID) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              v[i] *= PRECISE ? sigmoidf_exact(__uint_as_float(raw[i])) : sigmoidf_fast(__uint_as_float(raw[i]));
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * sigmoidf_fast(__uint_as_float(rawg[i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              v[i] = v[i] * (PRECISE ? sigmoidf_exact(v[i]) : sigmoidf_fast(v[i])) * __uint_as_float(raw[i]);
+            for (int i = 0; i < 32; ++i) {
+              const float a = __uint_as_float(raw[i]);
+              v[i] = a * sigmoidf_fast(a) * __uint_as_float(rawg[i]);
+            }
+          }
+        } else {
+          {
+            uint32_t raw[32];
+            ptx::tmem_ld_32x32b_x32(t_row + c, raw);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+            if (PRECISE) {
+              ptx::tmem_ld_32x32b_x32(t_row + BN + c, raw);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(raw[i]);
+            }
+          }
+          if (GLU) {
+            uint32_t raw[32];
+            ptx::tmem_ld_32x32b_x32(t_row + OUT_BN_GLU + c, raw);
+            ptx::tmem_ld_wait();
+            if (PRECISE) {
+              uint32_t raw2[32];
+              ptx::tmem_ld_32x32b_x32(t_row + BN + OUT_BN_GLU + c, raw2);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) + __uint_as_float(raw2[i]));
+            }
+            if (p.glu == GLU_SIGMOID) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                v[i] *= PRECISE ? sigmoidf_exact(__uint_as_float(raw[i])) : sigmoidf_fast(__uint_as_float(raw[i]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                v[i] = v[i] * (PRECISE ? sigmoidf_exact(v[i]) : sigmoidf_fast(v[i])) * __uint_as_float(raw[i]);
+            }
           }
         }
         // which segment does this chunk belong to
@@ -423,19 +454,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           for (int i = 0; i < 32; ++i) v[i] *= mask_v;
         }
         if (sg.tma_slot >= 0) {
-          // channel-major segment: the warp transposes its 32 x 32 piece into a private [32 channels][32 rows]
-          // shared-memory slab (two slabs, used alternately) and one lane hands it to a TMA store; rows and
-          // channels outside the tensor are clipped by the copy engine.  No cross-warp synchronisation.
-          uint8_t* slab = s_stage_out + ((warp - 2) * 2 + (staging_use & 1)) * (32 * 32 * 2);
-          __nv_bfloat16* col0 = reinterpret_cast<__nv_bfloat16*>(slab) + lane;
-          if (lane == 0) ptx::tma_store_wait_read_le1();  // the store that last read this slab (two uses ago) is done
-          __syncwarp();
+          // channel-major segment: the four warps that hold the same 32 columns of the tile (one per TMEM lane
+          // quadrant) transpose their pieces into one [32 channels][128 rows] shared-memory slab (two slabs per
+          // group, used alternately) and one thread hands it to a TMA store: 32 pieces of 256 contiguous bytes.
+          // Rows and channels outside the tensor are clipped by the copy engine.
+          const int grp = chunk_phase;
+          uint8_t* slab = s_stage_out + (grp * 2 + (staging_use & 1)) * (32 * kBM * 2);
+          __nv_bfloat16* col0 = reinterpret_cast<__nv_bfloat16*>(slab) + r;
+          const bool issuer = (quad == 0 && lane == 0);
+          uint64_t* bar_free = &cm_bar[grp * 2];
+          uint64_t* bar_done = &cm_bar[grp * 2 + 1];
+          const uint32_t par = staging_use & 1;
+          if (issuer) ptx::tma_store_wait_read_le1();  // the store that last read this slab (two uses ago) is done
+          ptx::mbar_arrive(bar_free);
+          if (!ptx::mbar_wait(bar_free, par, 108)) { ok = false; break; }
+          // packed conversions (two values per instruction), then the halves go to their channels' rows
+          unsigned short* col0u = reinterpret_cast<unsigned short*>(col0);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) col0[i * 32] = __float2bfloat16_rn(v[i]);
+          for (int i = 0; i < 32; i += 2) {
+            const uint32_t w2 = pack_bf16x2(v[i], v[i + 1]);
+            col0u[i * kBM] = static_cast<unsigned short>(w2 & 0xffffu);
+            col0u[(i + 1) * kBM] = static_cast<unsigned short>(w2 >> 16);
+          }
           ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_4d(sg.tma_slot == 0 ? &tm_out0 : &tm_out1, slab, nb * kBM + quad * 32, o, col_local, b);
+          ptx::mbar_arrive(bar_done);
+          if (issuer) {
+            if (!ptx::mbar_wait(bar_done, par, 109)) { ok = false; break; }
+            ptx::tma_store_4d(sg.tma_slot == 0 ? &tm_out0 : &tm_out1, slab, nb * kBM, o, col_local, b);
             ptx::tma_store_commit();
           }
           ++staging_use;
@@ -553,7 +598,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       ptx::mbar_arrive(&tmem_empty[acc]);
       if (threadIdx.x == 64) KFB_GSTAMP(4 + tile_iter * 4 + 1);
     }
-    if (lane == 0) ptx::tma_store_wait_all();
+    if (quad == 0 && lane == 0) ptx::tma_store_wait_all();
   }
 
   ptx::tc_fence_before_sync();

@@ -365,6 +365,23 @@ __global__ void __launch_bounds__(kCmPos) layernorm_cm_kernel(const TI* __restri
   }
   const float rstd = rsqrtf(q / static_cast<float>(c) + eps);
   __nv_bfloat16* yr = y + (static_cast<long long>(batch) * npos + p) * c;
+  if ((c & 15) == 0 && (reinterpret_cast<uintptr_t>(yr) & 31) == 0) {
+    for (int ch = 0; ch < c; ch += 16) {   // 32-byte stores: one full sector per instruction
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float a0 = (__bfloat162float(col[(ch + 2 * i) * kCmPos]) - mean) * rstd;
+        float a1 = (__bfloat162float(col[(ch + 2 * i + 1) * kCmPos]) - mean) * rstd;
+        if (w != nullptr) { a0 *= w[ch + 2 * i]; a1 *= w[ch + 2 * i + 1]; }
+        if (b != nullptr) { a0 += b[ch + 2 * i]; a1 += b[ch + 2 * i + 1]; }
+        o[i] = cm_pack(a0, a1);
+      }
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yr + ch), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                   "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                   : "memory");
+    }
+    return;
+  }
   for (int ch = 0; ch < c; ch += 8) {
     float a[8];
 #pragma unroll
