@@ -145,6 +145,10 @@ KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece
                               const void* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout,
                               void* t_scratch, void* tn_scratch, void* out, const void* resid, int rows, int n, int c,
                               float eps, int dtype, void* stream);
+/* Channel-sharded contraction for the row-sharded pair track (the cheaper exchange: an all-to-all of a and b to a
+ * channel-sharded layout, this call, an all-to-all of t back; kfb_trimul_finish is then called with a = b = NULL and
+ * t_scratch = the received t).  ab_recv: bf16 [world][2][cl][rows][n] as received; t_send: bf16 [world][cl][rows][n]. */
+KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world, int rows, int n, int cl, void* stream);
 KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln_b, const void* w_proj_packed,
                                void* xn_scratch, void* qkg_out, void* vt_out, void* bias_out, int rows, int n, int c,
                                int heads, float eps, int dtype, void* stream);

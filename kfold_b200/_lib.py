@@ -40,6 +40,7 @@ _SIGNATURES = {
                        ctypes.c_size_t, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                     c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_finish": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],

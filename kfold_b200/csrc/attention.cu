@@ -459,12 +459,20 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
               }
             }
           }
+          uint32_t ow[8];
 #pragma unroll
-          for (int i = 0; i < 16; i += 8) {
-            if (row_ok && cb * 16 + i < p.d)  // d is a multiple of 8
-              *reinterpret_cast<uint4*>(o + cb * 16 + i) =
-                  make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
-                             pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+          for (int i = 0; i < 8; ++i) ow[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+          if (row_ok && cb * 16 + 16 <= p.d && (reinterpret_cast<uintptr_t>(o + cb * 16) & 31) == 0) {
+            // 32-byte store: one full sector per instruction
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o + cb * 16), "r"(ow[0]), "r"(ow[1]),
+                         "r"(ow[2]), "r"(ow[3]), "r"(ow[4]), "r"(ow[5]), "r"(ow[6]), "r"(ow[7])
+                         : "memory");
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              if (row_ok && cb * 16 + i < p.d)  // d is a multiple of 8
+                *reinterpret_cast<uint4*>(o + cb * 16 + i) = make_uint4(ow[i / 2], ow[i / 2 + 1], ow[i / 2 + 2], ow[i / 2 + 3]);
+            }
           }
         }
       }

@@ -103,7 +103,7 @@ int finish(cudaStream_t stream, const __nv_bfloat16* a, const __nv_bfloat16* b, 
            __nv_bfloat16* tn, void* out, const void* resid, int batch, int rows, int n, int c, float eps, int dtype) {
   const long long rn = static_cast<long long>(rows) * n;
   const long long pos = rn * batch;
-  {
+  if (a != nullptr) {
     // t[ch*B+b][i][j] = sum_k A[i][k] B[j][k]
     GemmParams p = {};
     p.n_extent = rows;
@@ -314,7 +314,9 @@ KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece
                               const void* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout,
                               void* t_scratch, void* tn_scratch, void* out, const void* resid, int rows, int n, int c,
                               float eps, int dtype, void* stream_) {
-  KFB_CHECK_ARG(a && b_gathered && gl && w_pout && t_scratch && tn_scratch && out, "trimul_finish: null pointer");
+  KFB_CHECK_ARG(gl && w_pout && t_scratch && tn_scratch && out, "trimul_finish: null pointer");
+  KFB_CHECK_ARG((a == nullptr) == (b_gathered == nullptr), "trimul_finish: pass both operands, or neither when t_scratch "
+                "already holds the contraction result");
   KFB_CHECK_ARG(is_dtype(dtype), "trimul_finish: bad dtype %d", dtype);
   KFB_TRY(check_shape("trimul_finish", 1, rows, n, c));
   KFB_CHECK_ARG(b_piece_rows >= 64 && n % b_piece_rows == 0 && b_piece_rows % 64 == 0 && b_piece_stride % 8 == 0,
@@ -323,6 +325,33 @@ KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece
                 b_piece_rows, b_piece_stride, static_cast<const __nv_bfloat16*>(gl), ln_out_w, ln_out_b, w_pout,
                 static_cast<__nv_bfloat16*>(t_scratch), static_cast<__nv_bfloat16*>(tn_scratch), out, resid, 1, rows, n, c, eps,
                 dtype);
+}
+
+// Channel-sharded contraction.  After an all-to-all of the ranks' projections this rank holds ALL pair rows of a and b
+// for `cl` of the channels: ab_recv [world (source rank q)][2 (a, b)][cl][rows][n], rows q*rows .. q*rows+rows-1 of the pair
+// tensor coming from rank q.  Result t_send [world (q)][cl][rows][n]: the rows of t that belong to rank q, laid out for
+// the all-to-all back (after which every rank holds t [c][rows][n] for its own rows, channel-major).
+KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world, int rows, int n, int cl, void* stream_) {
+  KFB_CHECK_ARG(ab_recv && t_send, "trimul_contract_cs: null pointer");
+  KFB_CHECK_ARG(world >= 1 && rows >= 64 && rows % 64 == 0 && static_cast<long long>(world) * rows == n && cl >= 1,
+                "trimul_contract_cs: world %d x rows %d (multiple of 64) must equal N=%d; channels %d", world, rows, n, cl);
+  const long long rn = static_cast<long long>(rows) * n;
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(ab_recv);
+  GemmParams p = {};
+  p.n_extent = rows;     // pair row inside the source rank's shard
+  p.o_extent = world;    // source rank
+  p.batch = cl;          // channel
+  p.n_cols = n;
+  p.k_extent = n;
+  p.b_batched = 1;
+  p.nseg = 1;
+  p.seg[0] = row_major_seg(t_send, n, n, static_cast<long long>(cl) * rn, rn, 0);
+  GemmOperandA oa = {a, n, 2ll * cl * rn, rn};
+  GemmOperandB ob = {a + static_cast<long long>(cl) * rn, n, rn};
+  ob.col_inner = rows;
+  ob.s_col_hi = 2ll * cl * rn;
+  const int force_bn = rows % 256 == 0 ? 256 : (rows % 128 == 0 ? 128 : 64);
+  return launch_gemm_bf16(as_stream(stream_), oa, ob, p, force_bn, "trimul_contraction");
 }
 
 }  // extern "C"

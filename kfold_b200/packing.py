@@ -48,14 +48,26 @@ def _dev(t: torch.Tensor, device, dtype) -> torch.Tensor:
     return t.detach().to(device=device, dtype=dtype).contiguous()
 
 
-def pack_trimul(w: dict, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
+def channel_shard_order(c: int, world: int) -> torch.Tensor:
+    """Order of the 2c operand channels [a | b] in which rank q's share comes first for q = 0, 1, ...:
+    [q][a, b][c / world].  Position (q, s, i) holds source channel s*c + q*(c/world) + i."""
+    cl = c // world
+    q, s_, i = torch.meshgrid(torch.arange(world), torch.arange(2), torch.arange(cl), indexing="ij")
+    return (s_ * c + q * cl + i).reshape(-1)
+
+
+def pack_trimul(w: dict, device, dtype=torch.bfloat16, precise: bool = False, shard_world: int = 0) -> dict:
     """Weights of TriangleMultiplication{Outgoing,Incoming}: keys as in the reference state_dict
-    (model/primitives/triangle_multiplication.py:171-177).  LayerNorm affine stays fp32."""
+    (model/primitives/triangle_multiplication.py:171-177).  LayerNorm affine stays fp32.
+    ``shard_world`` > 1 orders the operand channels for the channel-sharded exchange (channel_shard_order)."""
+    wp, wg = w["linear_p_in.weight"].detach().float(), w["linear_g_in.weight"].detach().float()
+    if shard_world > 1:
+        order = channel_shard_order(wp.shape[0] // 2, shard_world).to(wp.device)
+        wp, wg = wp[order], wg[order]
     return {
         "ln_in_w": _dev(w["layernorm_in.weight"], device, torch.float32),
         "ln_in_b": _dev(w["layernorm_in.bias"], device, torch.float32),
-        "w_in": _w(interleave_glu(w["linear_p_in.weight"].detach().float(), w["linear_g_in.weight"].detach().float(),
-                                  GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_in": _w(interleave_glu(wp, wg, GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
         "w_gout": _w(w["linear_g_out.weight"], device, precise),
         "ln_out_w": _dev(w["layernorm_out.weight"], device, torch.float32),
         "ln_out_b": _dev(w["layernorm_out.bias"], device, torch.float32),

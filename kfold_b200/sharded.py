@@ -5,7 +5,11 @@ The reference never splits a pair tensor: its multi-GPU mode hands whole complex
 pair representation z (N, N, C) by rows: rank r owns rows [r*N/P, (r+1)*N/P).  Per operator:
 
   pointwise (LayerNorm, projections, gates, transition, residual)   local
-  triangle multiplication, outgoing   t[i,j] = sum_k a[i,k] b[j,k]    rows i local for a; ALL-GATHER b
+  triangle multiplication, outgoing   t[i,j] = sum_k a[i,k] b[j,k]    the contraction is independent per channel:
+                                      ALL-TO-ALL of a and b to a channel-sharded layout (every rank gets all rows of
+                                      C/P channels), local contraction, ALL-TO-ALL of t back to row shards.  That moves
+                                      3 N^2 C / P values per rank instead of the (P-1) N^2 C / P of an all-gather of b
+                                      (the all-gather form is kept for C not divisible by P)
   triangle multiplication, incoming   t[i,j] = sum_k a[k,i] b[k,j]    a, b are taken from the TRANSPOSED shard
                                       (all-to-all transpose of z), where it is the outgoing form; the
                                       output gate and the residual use the row shard
@@ -76,8 +80,45 @@ class ShardedPairOps:
         self.rank = dist.get_rank(group)
 
     # ------------------------------------------------------------------ triangle multiplication
+    def _trimul_cs(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
+        """Channel-sharded exchange.  `pk` must come from pack_trimul(..., shard_world=world): the projection then writes
+        the operand channels rank by rank, [q][a, b][C/P], which is the send buffer of the all-to-all as it lies."""
+        rows, n, c = x_row.shape
+        world, cl = self.world, c // self.world
+        dev = x_row.device
+        lib = L.lib()
+        dt = L.dtype_code(x_row.dtype)
+        xn = _bf16((rows * n, c), dev)
+        ab = _bf16((world, 2, cl, rows, n), dev)
+        gl = _bf16((rows * n, c), dev)
+        m8 = mask_ab.to(torch.bool).contiguous().view(torch.uint8)
+        x_ab = x_ab.contiguous()
+        x_row = x_row.contiguous()
+        with torch.cuda.device(dev):
+            st = L.stream_ptr()
+            same = x_ab.data_ptr() == x_row.data_ptr()
+            L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
+                                           L.ptr(pk["w_gout"]) if same else None, L.ptr(xn), L.ptr(ab),
+                                           L.ptr(gl) if same else None, 1, rows, n, c, eps, dt, st))
+            ab_recv = torch.empty_like(ab)
+            dist.all_to_all_single(ab_recv, ab, group=self.group)       # [source rank][a, b][cl][rows][n]
+            if not same:   # gate logits of the row shard while the exchange is in flight
+                L.check(lib.kfb_trimul_project(L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
+                                               L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, eps, dt, st))
+            t_send = _bf16((world, cl, rows, n), dev)
+            L.check(lib.kfb_trimul_contract_cs(L.ptr(ab_recv), L.ptr(t_send), world, rows, n, cl, L.stream_ptr()))
+            t = torch.empty_like(t_send)
+            dist.all_to_all_single(t, t_send, group=self.group)         # [channel group][cl][rows][n] = t [c][rows][n]
+            out = torch.empty_like(x_row)
+            L.check(lib.kfb_trimul_finish(None, None, rows, 0, L.ptr(gl), L.ptr(pk["ln_out_w"]), L.ptr(pk["ln_out_b"]),
+                                          L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out), L.ptr(x_row), rows, n, c, eps,
+                                          dt, L.stream_ptr()))
+        return out
+
     def _trimul(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
         """a, b from (x_ab, mask_ab); gate logits and residual from x_row.  All (rows, N, ...) shards."""
+        if pk.get("shard_world", 0) == self.world and self.world > 1:
+            return self._trimul_cs(x_ab, mask_ab, x_row, pk, eps)
         rows, n, c = x_row.shape
         dev = x_row.device
         lib = L.lib()
@@ -169,6 +210,20 @@ class ShardedPairformerBlock:
     def __init__(self, block, group=None):
         self.block = block
         self.ops = ShardedPairOps(group)
+        self._trimul_packs = {}
+
+    def _pack_trimul(self, mod, dev):
+        """Weights for the channel-sharded exchange when C divides by the number of ranks (packed once per module)."""
+        world = self.ops.world
+        c = mod.layernorm_in.normalized_shape
+        if world == 1 or c % world != 0:
+            return mod._packed(dev, torch.bfloat16, packing.pack_trimul)
+        key = (id(mod), dev)
+        if key not in self._trimul_packs:
+            pk = packing.pack_trimul(mod.state_dict(), dev, shard_world=world)
+            pk["shard_world"] = world
+            self._trimul_packs[key] = pk
+        return self._trimul_packs[key]
 
     @torch.no_grad()
     def __call__(self, z_loc: torch.Tensor, s: torch.Tensor, pair_mask_loc: torch.Tensor, mask: torch.Tensor):
@@ -176,8 +231,8 @@ class ShardedPairformerBlock:
         b, ops = self.block, self.ops
         dev = z_loc.device
         bf = torch.bfloat16
-        z = ops.trimul_outgoing(z_loc, pair_mask_loc, b.tri_mul_out._packed(dev, bf, packing.pack_trimul))
-        z = ops.trimul_incoming(z, pair_mask_loc, b.tri_mul_in._packed(dev, bf, packing.pack_trimul))
+        z = ops.trimul_outgoing(z_loc, pair_mask_loc, self._pack_trimul(b.tri_mul_out, dev))
+        z = ops.trimul_incoming(z, pair_mask_loc, self._pack_trimul(b.tri_mul_in, dev))
         pk_s = b.tri_att_start._packed(dev, bf, lambda sd, d: packing.pack_triatt(sd, b.tri_att_start.no_heads, d))
         pk_e = b.tri_att_end._packed(dev, bf, lambda sd, d: packing.pack_triatt(sd, b.tri_att_end.no_heads, d))
         z = ops.triatt_starting(z, pair_mask_loc, pk_s)

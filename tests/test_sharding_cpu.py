@@ -54,3 +54,50 @@ def test_shard_rows_rejects_uneven_split():
     with pytest.raises(ValueError):
         sharded.shard_rows(10, 4, 0)
     assert sharded.shard_rows(2048, 8, 3) == (768, 1024)
+
+
+def _worker_channel_sharded(rank: int, world: int, port: int, n: int, c: int):
+    """The channel-sharded triangle contraction, with torch standing in for the kernels: operand channels written in
+    packing.channel_shard_order, all-to-all, per-channel contraction read through the strides the kernel uses,
+    all-to-all back; the result must be the row shard of the full einsum."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from kfold_b200 import packing, sharded
+        g = torch.Generator().manual_seed(11)
+        a = torch.randn(c, n, n, generator=g)          # a[ch][i][k]
+        b = torch.randn(c, n, n, generator=g)          # b[ch][j][k]
+        t_full = torch.einsum("cik,cjk->cij", a, b)
+        r0, r1 = sharded.shard_rows(n, world, rank)
+        rows, cl = r1 - r0, c // world
+        # what kfb_trimul_project writes with the permuted weights: [2c in shard order][rows][n] = [q][a, b][cl][rows][n]
+        ab_nat = torch.cat([a[:, r0:r1], b[:, r0:r1]], dim=0)                 # natural order [a | b]
+        order = packing.channel_shard_order(c, world)
+        send = ab_nat[order].contiguous().view(world, 2, cl, rows, n)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        # kfb_trimul_contract_cs: rows (q, r) of a / b for this rank's channels, result laid out [q][cl][rows][n]
+        a_cs = recv[:, 0].permute(1, 0, 2, 3).reshape(cl, n, n)
+        b_cs = recv[:, 1].permute(1, 0, 2, 3).reshape(cl, n, n)
+        assert torch.equal(a_cs, a[rank * cl:(rank + 1) * cl]) and torch.equal(b_cs, b[rank * cl:(rank + 1) * cl])
+        t_cs = torch.einsum("cik,cjk->cij", a_cs, b_cs)                       # [cl][N][N]
+        t_send = t_cs.view(cl, world, rows, n).permute(1, 0, 2, 3).contiguous()
+        t_recv = torch.empty_like(t_send)
+        dist.all_to_all_single(t_recv, t_send)
+        t_loc = t_recv.view(c, rows, n)                                       # channel-major rows of this rank
+        assert torch.allclose(t_loc, t_full[:, r0:r1], atol=1e-5)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n,c", [(2, 8, 4), (4, 16, 8)])
+def test_channel_sharded_contraction_algebra(world, n, c):
+    mp.spawn(_worker_channel_sharded, args=(world, _free_port(), n, c), nprocs=world, join=True)
+
+
+def test_channel_shard_order_is_a_permutation():
+    from kfold_b200 import packing
+    o = packing.channel_shard_order(128, 8)
+    assert sorted(o.tolist()) == list(range(256))
+    assert o[:3].tolist() == [0, 1, 2] and o[16] == 128 and o[32] == 16     # rank 0: a[0:16], b[0:16]; rank 1: a[16:32]
