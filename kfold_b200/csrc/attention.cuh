@@ -2,22 +2,19 @@
 //
 //   S = Q K^T + bias[h, q, k] + (mask[k] ? 0 : -1e9)        O = softmax_k(S) V   (optionally O *= sigmoid(G))
 //
-// Q arrives pre-scaled by 1/sqrt(D).  One CTA handles 128 queries of one head for R (1 or 2) batch
-// rows that share the same bias tile, walking the keys in blocks of 128 with an online softmax;
-// the L x L x H logits never exist in memory.  Per key block:
-//   warp 0        TMA: K and V^T tiles per row, and the 128 x 128 bias tile (once for all R rows)
-//   warp 1        tcgen05.mma into TMEM:  S  = Q K^T            (K = D)
-//                                         S += I  bias          (identity x bias tile, read MN-major as it
-//                                                                lies in memory: the bias is added by the
-//                                                                otherwise idle tensor core)
-//                                         S += e0 maskrow^T     (rank-1: the key mask, one K=16 step)
-//                 later  O_blk = P V
-//   warps 2..     one query row per thread: a single pass over its S row from TMEM computes
-//                 P = exp(S - s) (one FFMA + one ex2 per element) against a lagging stabiliser s
-//                 (raised only when the running maximum has moved by more than e^5.5; an
-//                 overflow-safe redo exists), writes P as
-//                 packed bf16 into tensor memory (the A operand of the second MMA is read from there)
-//                 and folds the previous block's O_blk into register accumulators.
+// Q arrives pre-scaled by log2(e)/sqrt(D): logits live in log2 units, the bias is multiplied by log2(e) as it is
+// added.  One CTA handles 128 queries of one head for R (1 or 2) batch rows ("row groups") that share the same bias
+// tile, walking the keys in half tiles of 64 with an online softmax; the L x L x H logits never exist in memory.
+//   warp 0        TMA: K and V^T tiles per row group (3 stages), the 128 x 128 bias tile once for all R (2 stages)
+//   warps 1..R    one MMA-issuing warp per row group, tcgen05.mma into tensor memory:
+//                    S(t)  = Q K(t)^T + e0 maskrow(t)^T     (the key mask as a rank-1 K=16 step), triple-buffered
+//                    O[c] += P_c(t) V_c(t)                   (A = P read from tensor memory), c = 0, 1
+//   8 warps per row group = two softmax streams of four warps; stream c owns 32 of the 64 key columns of every half
+//                 tile, one query row per thread: x = S + log2(e) bias (bias row from the swizzled shared-memory
+//                 tile), P = exp2(x - s) against a lagging stabiliser s (the row maximum of the stream's first half
+//                 tile, moved only when a half tile's row sum exceeds 2^100), P written as packed bf16 over the
+//                 stream's own S columns.  Each stream has its own s, row sum and accumulator O[c] in tensor
+//                 memory; the two are merged once at the end.
 //
 // Used for triangle attention (batch row = pair row i, bias shared by all rows, mask per row) and
 // for pair-bias attention on the single / token track (bias shared by `bias_div` consecutive
