@@ -210,6 +210,54 @@ def run_reference_arm(args, rank: int, world: int) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
+# optional second workload (--diffusion-step): one pass of the sampler's token transformer of BASELINE config 4
+# (24 conditioned blocks, c=768, 16 heads x 48, L=768 tokens, 5 samples sharing the pair bias), bf16 compute.
+# Not the headline metric; printed as its own JSON line when asked for.
+# ------------------------------------------------------------------------------------------------
+def run_diffusion_step(args) -> None:
+    from kfold_b200 import _lib as L
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    blocks, l, ns, c, cs, heads = 24, N_TOKENS, 5, 768, 384, 16
+    rng = synth._Rng(SEED)
+    w = {}
+    for i in range(blocks):
+        w.update(synth._prefixed(f"blocks.{i}.attention", synth.apb_weights(rng, c, cs)))
+        w.update(synth._prefixed(f"blocks.{i}.transition", synth.conditioned_transition_weights(rng, c, cs)))
+    a = rng.normal(1, ns, l, c).to(dev)
+    s = rng.normal(1, 1, l, cs).to(dev)
+    bias = rng.normal(1, blocks, heads, l, l).to(dev)
+    mask = synth.token_mask(l, pad_frac=PAD_FRAC).view(1, 1, l).to(dev)
+    stack = M.CachedGlobalTransformerStack(c, cs, heads, blocks).to(dev)
+    stack.load_state_dict(w, strict=True)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for _ in range(max(args.warmup, 3)):
+            stack(a, s, bias, mask)
+        torch.cuda.synchronize()
+        launches0 = L.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            stack(a, s, bias, mask)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # per block: projections 4 c^2 + c^2, AdaLN / gate projections of the conditioning (per token, not per sample),
+    # attention 4 L c per row, conditioned transition 3 * 2c * c
+    rows = ns * l
+    flops = blocks * (2.0 * rows * c * 5 * c + 4.0 * ns * l * l * c + 2.0 * rows * c * 6 * c + 2.0 * l * cs * 6 * c)
+    emit({"metric": f"diffusion_token_transformer_step_ms_l{l}_s{ns}_bf16", "value": ms, "unit": "ms", "n_gpus": 1,
+          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+          "config": {"workload": f"sampler token transformer (BASELINE config 4): {blocks} blocks, c={c}, {heads} heads, "
+                                 f"L={l}, {ns} samples sharing the pair bias, one pass = one sampler step"},
+          "tflops": round(flops / (ms * 1e-3) / 1e12, 1), "gpu_launches": L.launch_count() - launches0,
+          "device_status": L.device_status()})
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
@@ -382,7 +430,12 @@ def main() -> None:
                     help="with N > 1 ranks: row-shard ONE pair tensor over the GPUs (strong scaling) instead of one block per GPU")
     ap.add_argument("--tokens", type=int, default=N_TOKENS,
                     help="profiling aid: run the block at another N (the reported line is then NOT the benchmark workload)")
+    ap.add_argument("--diffusion-step", action="store_true",
+                    help="second workload: one pass of the sampler's token transformer of BASELINE config 4 (its own JSON line)")
     args = ap.parse_args()
+    if args.diffusion_step:
+        run_diffusion_step(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.tokens == N_TOKENS else args.warmup
     if args.tokens != N_TOKENS:
         globals()["N_TOKENS"] = args.tokens

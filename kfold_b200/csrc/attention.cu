@@ -1,6 +1,7 @@
 // Flash-style pair-bias attention kernel (see attention.cuh for the contract).
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "attention.cuh"
@@ -27,10 +28,13 @@ struct AttCfg {
   static constexpr int kQBytes = kBQ * kSpan;            // per row group
   static constexpr int kKBytes = kBKV * kSpan;
   static constexpr int kVBytes = 2 * DPAD * 128;         // two boxes of [DPAD rows x 64 keys]
-  static constexpr int kKvStages = 3;
-  static constexpr int kTileBytes = 2 * 128 * 128;       // a 128 x 128 bf16 bias tile as two 64-key halves of 128-byte rows
+  // one row group per CTA (R == 1) at head dim <= 32 is sized so that TWO CTAs fit an SM (shared memory <= 113 KB, 256
+  // tensor-memory columns, 80 registers): two K/V stages there, three otherwise
+  static constexpr bool kTwoPerSm = (R == 1 && DPAD == 32);
+  static constexpr int kKvStages = kTwoPerSm ? 2 : 3;
+  static constexpr int kTileBytes = 128 * 128;           // a bias half tile: 128 query rows x 64 keys bf16 (128-byte rows)
   static constexpr int kSmallBytes = 128 * 32;           // a 128 x 16 bf16 K-major operand without swizzle
-  static constexpr int kBiasStages = 2;
+  static constexpr int kBiasStages = 3;                  // ring of bias half tiles
   // tensor memory columns.  Keys are processed in half tiles of 64 (t = 0, 1, ...; buf = t % 3); the 64 columns
   // of a half tile are shared between two independent softmax streams (c = 0: keys 0..31, c = 1: keys 32..63):
   //   S[g][buf]  64 fp32 columns at (g*3 + buf) * 64; stream c overwrites the first 16 of its 32 columns
@@ -66,7 +70,7 @@ __device__ __forceinline__ uint32_t small_operand_row_offset(int r) { return (r 
 // S runs up to three half tiles ahead of the softmax, so the softmax warps never wait for the tensor core or for the
 // issuing warp, and four independent softmax warps per scheduler hide each other's tensor-memory and MUFU latencies.
 template <int DPAD, int R>
-__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads) __maxnreg__((R == 1) ? 168 : 96)
+__global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads, AttCfg<DPAD, R>::kTwoPerSm ? 2 : 1)
 attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
                       const AttnParams p) {
@@ -156,6 +160,8 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
       const int bias_z = (b0 / p.bias_div) * p.heads + h;
       bool ok = true;
+      int bst = 0;
+      uint32_t bpar = 0;   // ring position of the bias half tiles
       for (int j = 0; ok && j < nkv; ++j) {
         const int st = j % kStages;
         for (int g = 0; g < R; ++g) {
@@ -166,12 +172,12 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           ptx::tma_load_3d(s_v + slot * Cfg::kVBytes, &tm_v, &kv_full[slot], j * kBKV, h * DPAD, b0 + g);
           ptx::tma_load_3d(s_v + slot * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[slot], j * kBKV + 64, h * DPAD, b0 + g);
         }
-        if (!ok) break;
-        const int bs = j % Cfg::kBiasStages;
-        if (!ptx::mbar_wait(&bias_empty[bs], ((j / Cfg::kBiasStages) & 1) ^ 1, 202)) break;
-        ptx::mbar_expect_tx(&bias_full[bs], Cfg::kTileBytes);
-        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes, &tm_b, &bias_full[bs], j * kBKV, qb * kBQ, bias_z);
-        ptx::tma_load_3d(s_bias + bs * Cfg::kTileBytes + 16384, &tm_b, &bias_full[bs], j * kBKV + 64, qb * kBQ, bias_z);
+        for (int hf = 0; ok && hf < 2; ++hf) {
+          if (!ptx::mbar_wait(&bias_empty[bst], bpar ^ 1, 202)) { ok = false; break; }
+          ptx::mbar_expect_tx(&bias_full[bst], Cfg::kTileBytes);
+          ptx::tma_load_3d(s_bias + bst * Cfg::kTileBytes, &tm_b, &bias_full[bst], j * kBKV + hf * 64, qb * kBQ, bias_z);
+          if (++bst == Cfg::kBiasStages) { bst = 0; bpar ^= 1u; }
+        }
       }
     }
   } else if (warp <= R) {
@@ -204,17 +210,16 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ptx::tc_commit(&s_full[g * 3 + buf]);
         return true;
       };
-      static_assert(kStages == 3, "the stage and mask-buffer counters below assume three K/V stages");
 
       ok = ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&init_ready[g], 0, 206) && issue_s(0, 0, 0, 0, 0) &&
            issue_s(1, 1, 0, 0, 0);
-      if (ok && nkv > 1) ok = issue_s(0, 2, 1, 0, 1);
+      if (ok && nkv > 1) ok = issue_s(0, 2, 1 % kStages, (1 / kStages) & 1, 1);
       // half tile t lives in S buffer `buf` = t % 3 (use number `use` = t / 3) and in K/V stage `st` = (t / 2) % 3;
       // half tile t + 3 (issued below) belongs to tile j3 = (t + 3) / 2: stage st3 = j3 % 3, parity par3 = (j3 / 3) & 1
       int buf = 0, st = 0;
       uint32_t use_par = 0;
-      int st3 = 1, j3 = 1;
-      uint32_t par3 = 0;
+      int st3 = 1 % kStages, mb3 = 1;             // K/V stage and mask buffer (j3 % 3) of tile j3
+      uint32_t par3 = (1 / kStages) & 1;
       for (int t = 0; ok && t < nhalf; ++t) {
         const int hf = t & 1;
         // both streams' P(t) are in tensor memory, the mask rows needed by S(t+3) are written
@@ -231,14 +236,16 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ptx::tc_commit(&o_full[g * 3 + buf]);
         if (hf == 1) ptx::tc_commit(&kv_empty[g * kStages + st]);
         // S(t+3): half (t+3) & 1 = hf ^ 1 of tile j3
-        if (t + 3 < nhalf && !issue_s(hf ^ 1, buf, st3, par3, st3)) { ok = false; break; }
+        if (t + 3 < nhalf && !issue_s(hf ^ 1, buf, st3, par3, mb3)) { ok = false; break; }
         KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 0);
         if (++buf == 3) { buf = 0; use_par ^= 1u; }
-        if (hf == 1) { if (++st == 3) st = 0; }
+        if (hf == 1) { if (++st == kStages) st = 0; }
         // t + 4 belongs to the next tile when t + 4 is even
-        if (hf == 0) { ++j3; if (++st3 == 3) { st3 = 0; par3 ^= 1u; } }
+        if (hf == 0) {
+          if (++mb3 == 3) mb3 = 0;
+          if (++st3 == kStages) { st3 = 0; par3 ^= 1u; }
+        }
       }
-      (void)j3;
     }
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- softmax streams
@@ -280,30 +287,29 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     bool ok = true;
     int buf = 0, mbuf = 2;        // S buffer of half tile t (t % 3); mask buffer of tile t/2 + 2
     uint32_t use_par = 0;
+    static_assert(Cfg::kBiasStages == 3, "the bias ring is indexed like the S buffers: half tile t sits in stage t % 3");
 
 #pragma unroll 1
     for (int t = 0; t < nhalf; ++t) {
       const int j = t >> 1, hf = t & 1;
-      const int bs = j % Cfg::kBiasStages;
       // the mask byte of the next tile is fetched now and used at the end of the pass: its latency hides behind the pass
       int mask_next = 0;
       if (u == 0 && hf == 0 && j + 2 < nkv) mask_next = load_mask_byte(j + 2);
-      if (!ptx::mbar_wait(&s_full[g * 3 + buf], use_par, 208)) { ok = false; break; }
+      // (waits of the softmax warps are made warp-uniform: the lanes meet again at the warp-level barriers below)
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&s_full[g * 3 + buf], use_par, 208))) { ok = false; break; }
       if (r == 0) KFB_STAMP(256 + (g * 2 + u) * 64 + (t & 7) * 8 + 0);
       ptx::tc_fence_after_sync();
       float x[32];
       const uint32_t tmem_s = tmem_s0 + buf * 64;
       ptx::tmem_ld_32x32b_x32(tmem_s, reinterpret_cast<uint32_t(&)[32]>(x));
-      if (hf == 0 && !ptx::mbar_wait(&bias_full[bs], (j / Cfg::kBiasStages) & 1, 203)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bias_full[buf], use_par, 203))) { ok = false; break; }
       // the thread's own 64 bytes of its 128-byte row of the bias half tile (16-byte chunks swizzled by the row index)
-      const uint8_t* brow = my_bias + bs * Cfg::kTileBytes + hf * 16384;
+      const uint8_t* brow = my_bias + buf * Cfg::kTileBytes;
       uint4 bw[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) bw[c] = *reinterpret_cast<const uint4*>(brow + (((u * 4 + c) ^ swz) << 4));
-      if (hf == 1) {  // both halves of the bias tile have been read by this warp
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bias_empty[bs]);
-      }
+      __syncwarp();  // this warp has read its part of the bias half tile
+      if (lane == 0) ptx::mbar_arrive(&bias_empty[buf]);
       ptx::tmem_ld_wait();
       // x = S + log2(e) * bias
 #pragma unroll
@@ -359,7 +365,8 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         // (o_full[buf] completes one phase per three half tiles: S(t) complete implies P V(t-3) and everything before
         // it complete, and P V(t+2) cannot be issued before this pass and the next two end, so the barrier of
         // half tile t-1 is exactly in the phase waited for: the parity test is unambiguous)
-        if (!ptx::mbar_wait(&o_full[g * 3 + (buf == 0 ? 2 : buf - 1)], buf == 0 ? (use_par ^ 1u) : use_par, 209)) {
+        if (!__all_sync(0xffffffffu,
+                        ptx::mbar_wait(&o_full[g * 3 + (buf == 0 ? 2 : buf - 1)], buf == 0 ? (use_par ^ 1u) : use_par, 209))) {
           ok = false;
           break;
         }
@@ -403,7 +410,9 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // ---- merge the two streams of the row group and write the result
     // The K stages of this row group are free once both streams have seen their last P V product.
     float* xchg = reinterpret_cast<float*>(s_k + g * kStages * Cfg::kKBytes) + r * Cfg::kXchgStride;
-    static_assert(128 * (DPAD + 3) * 4 <= kStages * Cfg::kKBytes, "exchange area does not fit in the K stages");
+    // (with one row group per CTA the V stages follow the K stages directly and are just as free)
+    static_assert(128 * (DPAD + 3) * 4 <= (R == 1 ? kStages * (Cfg::kKBytes + Cfg::kVBytes) : kStages * Cfg::kKBytes),
+                  "exchange area does not fit in the K (and V) stages");
     // the last P V product: then all of them are complete
     ok = ok && ptx::mbar_wait(&o_full[g * 3 + (nhalf - 1) % 3], ((nhalf - 1) / 3) & 1, 210);
     ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-wide: decide per warp
@@ -550,7 +559,8 @@ int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
   KFB_CHECK_ARG(p.batch <= 65535, "attention: batch %d exceeds the grid z limit", p.batch);
   if (p.dpad == 32) {
     // two batch rows per CTA when consecutive rows share their bias tile
-    if (p.batch % 2 == 0 && p.bias_div % 2 == 0) return launch_cfg<32, 2>(stream, p);
+    static const bool force_r1 = getenv("KFB_ATT_R1") != nullptr;   // debugging aid: one row group per CTA, two CTAs per SM
+    if (!force_r1 && p.batch % 2 == 0 && p.bias_div % 2 == 0) return launch_cfg<32, 2>(stream, p);
     return launch_cfg<32, 1>(stream, p);
   }
   if (p.dpad == 64) return launch_cfg<64, 1>(stream, p);
