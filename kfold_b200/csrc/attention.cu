@@ -182,8 +182,10 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
   } else if (warp <= R) {
     // ---------------------------------------------------------------- MMA issuer of row group g
-    if (lane == 0) {
+    // The whole warp runs this loop with warp-uniform values; one elected lane issues the tensor-core instructions.
+    {
       const int g = warp - 1;
+      const uint32_t tmem_base_u = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc_s = ptx::make_idesc(kBQ, 64, 1);
       constexpr uint32_t idesc_o = ptx::make_idesc(kBQ, DPAD, 1);
       // operand descriptors are built once; inside the loop only their 16-byte-unit address field advances
@@ -192,26 +194,27 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const uint64_t k_desc0 = ptx::make_kmajor_desc<Cfg::kSpan>(ptx::smem_u32(s_k + g * kStages * Cfg::kKBytes));
       const uint64_t v_desc0 = ptx::make_kmajor_desc<128>(ptx::smem_u32(s_v + g * kStages * Cfg::kVBytes));
       const uint64_t m_desc0 = make_noswizzle_desc(ptx::smem_u32(s_maskrow + g * 3 * Cfg::kSmallBytes));
-      const uint32_t tmem_s0 = tmem_base + g * 192;
-      const uint32_t tmem_o0 = tmem_base + Cfg::kTmemO + g * 2 * DPAD;
+      const uint32_t tmem_s0 = tmem_base_u + g * 192;
+      const uint32_t tmem_o0 = tmem_base_u + Cfg::kTmemO + g * 2 * DPAD;
       bool ok = true;
 
       // S_g(t) = Q_g K_g(t)^T + e0 maskrow_g(t)^T for the 64 keys of half tile t = 2j + hf, into S buffer `buf`;
       // `st` = j % kv stages, `mb` = j % 3 (mask operand buffer)
       auto issue_s = [&](int hf, int buf, int st, uint32_t kv_parity, int mb) -> bool {
-        if (hf == 0 && !ptx::mbar_wait(&kv_full[g * kStages + st], kv_parity, 204)) return false;
+        if (hf == 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(&kv_full[g * kStages + st], kv_parity, 204))) return false;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_s = tmem_s0 + buf * 64;
         const uint64_t k_desc = k_desc0 + static_cast<uint32_t>((st * Cfg::kKBytes + hf * 64 * Cfg::kSpan) >> 4);
 #pragma unroll
         for (int kk = 0; kk < DPAD / 16; ++kk)
-          ptx::mma_f16_ss(tmem_s, q_desc + kk * 2, k_desc + kk * 2, idesc_s, kk != 0 ? 1u : 0u);
-        ptx::mma_f16_ss(tmem_s, e0_desc, m_desc0 + static_cast<uint32_t>((mb * Cfg::kSmallBytes + hf * 2048) >> 4), idesc_s, 1u);
-        ptx::tc_commit(&s_full[g * 3 + buf]);
+          ptx::mma_f16_ss_warp(tmem_s, q_desc + kk * 2, k_desc + kk * 2, idesc_s, kk != 0 ? 1u : 0u);
+        ptx::mma_f16_ss_warp(tmem_s, e0_desc, m_desc0 + static_cast<uint32_t>((mb * Cfg::kSmallBytes + hf * 2048) >> 4), idesc_s, 1u);
+        ptx::tc_commit_warp(&s_full[g * 3 + buf]);
         return true;
       };
 
-      ok = ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&init_ready[g], 0, 206) && issue_s(0, 0, 0, 0, 0) &&
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&init_ready[g], 0, 206)) &&
+           issue_s(0, 0, 0, 0, 0) &&
            issue_s(1, 1, 0, 0, 0);
       if (ok && nkv > 1) ok = issue_s(0, 2, 1 % kStages, (1 / kStages) & 1, 1);
       // half tile t lives in S buffer `buf` = t % 3 (use number `use` = t / 3) and in K/V stage `st` = (t / 2) % 3;
@@ -223,21 +226,21 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       for (int t = 0; ok && t < nhalf; ++t) {
         const int hf = t & 1;
         // both streams' P(t) are in tensor memory, the mask rows needed by S(t+3) are written
-        if (!ptx::mbar_wait(&p_ready[g * 3 + buf], use_par, 207)) { ok = false; break; }
-        KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 1);
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&p_ready[g * 3 + buf], use_par, 207))) { ok = false; break; }
+        if (lane == 0) KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 1);
         ptx::tc_fence_after_sync();
         const uint64_t v_desc = v_desc0 + static_cast<uint32_t>((st * Cfg::kVBytes + hf * (DPAD * 128)) >> 4);
         const uint32_t tmem_p = tmem_s0 + buf * 64;
         const uint32_t acc_flag = t > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // A = P straight from tensor memory: stream c's 16 columns start at c * 32
-          ptx::mma_f16_ts(tmem_o0 + (kk >> 1) * DPAD, tmem_p + (kk >> 1) * 32 + (kk & 1) * 8, v_desc + kk * 2, idesc_o,
+          ptx::mma_f16_ts_warp(tmem_o0 + (kk >> 1) * DPAD, tmem_p + (kk >> 1) * 32 + (kk & 1) * 8, v_desc + kk * 2, idesc_o,
                           ((kk & 1) != 0) ? 1u : acc_flag);
-        ptx::tc_commit(&o_full[g * 3 + buf]);
-        if (hf == 1) ptx::tc_commit(&kv_empty[g * kStages + st]);
+        ptx::tc_commit_warp(&o_full[g * 3 + buf]);
+        if (hf == 1) ptx::tc_commit_warp(&kv_empty[g * kStages + st]);
         // S(t+3): half (t+3) & 1 = hf ^ 1 of tile j3
         if (t + 3 < nhalf && !issue_s(hf ^ 1, buf, st3, par3, mb3)) { ok = false; break; }
-        KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 0);
+        if (lane == 0) KFB_STAMP(16 + (t & 15) * 8 + g * 4 + 0);
         if (++buf == 3) { buf = 0; use_par ^= 1u; }
         if (hf == 1) { if (++st == kStages) st = 0; }
         // t + 4 belongs to the next tile when t + 4 is even
