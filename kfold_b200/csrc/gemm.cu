@@ -9,7 +9,7 @@
 
 namespace kfb {
 
-template <int BN, bool GLU, bool AUX, bool PRECISE>
+template <int BN, bool GLU, bool AUX, bool PRECISE, bool SWAP = false>
 static int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap* tout,
                           const GemmParams& p, const char* tag) {
   using Cfg = GemmCfg<BN>;
@@ -18,14 +18,15 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUte
   KFB_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, GLU, AUX, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<BN, GLU, AUX, PRECISE, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes);
   });
   KFB_CUDA(attr_err);
   const int total = p.num_m_tiles * p.num_n_tiles;
   const int grid = total < sm_count() ? total : sm_count();
   {
     LaunchScope scope(stream, tag);
-    gemm_bf16_kernel<BN, GLU, AUX, PRECISE><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], p);
+    gemm_bf16_kernel<BN, GLU, AUX, PRECISE, SWAP><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], p);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
@@ -44,6 +45,9 @@ static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorM
       if (p.glu) return launch_variant<BN, true, false, true>(stream, ta, tb, tout, p, tag);
       return launch_variant<BN, false, false, true>(stream, ta, tb, tout, p, tag);
     }
+  }
+  if constexpr (BN == 256) {
+    if (p.glu && p.swap) return launch_variant<BN, true, false, false, true>(stream, ta, tb, tout, p, tag);
   }
   if (p.glu) return launch_variant<BN, true, false, false>(stream, ta, tb, tout, p, tag);
   if constexpr (BN <= 128) {
@@ -99,9 +103,15 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   tout[0] = ta;  // placeholders (never dereferenced unless a segment selects them)
   tout[1] = ta;
   int next_slot = 0;
+  // a sigmoid-GLU GEMM whose only output is channel-major bf16 is computed in the swapped orientation
+  p.swap = (p.glu == GLU_SIGMOID && bn == 256 && p.nseg == 1 && !p.precise && p.seg[0].s_n == 1 && p.seg[0].s_col != 1 &&
+            !p.seg[0].out_fp32 && p.seg[0].col_begin == 0 && p.n_cols % 256 == 0 && p.col_bias == nullptr &&
+            p.gate == nullptr && p.resid == nullptr && (p.rowmask == nullptr || (p.mask_segs & 1)))
+               ? 1 : 0;
   for (int i = 0; i < p.nseg; ++i) {
     EpiSeg& sg = p.seg[i];
     sg.tma_slot = -1;
+    if (p.swap) continue;
     const bool aligned = (reinterpret_cast<uintptr_t>(sg.dst) & 15) == 0 && sg.s_o % 8 == 0 && sg.s_col % 8 == 0 &&
                          (sg.s_b % 8 == 0 || p.batch == 1) && (sg.s_o != 0 || p.o_extent == 1);
     if (sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && aligned && next_slot < 2 && !p.precise) {

@@ -51,6 +51,7 @@ struct GemmParams {
                                   // operand whose pieces lie rank after rank (launcher; = n_cols when not split)
   int n_blocks, num_m_tiles, num_n_tiles;
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
+  int swap;                       // launcher: channel-major GLU output computed in the swapped orientation (see SWAP)
   int nseg;
   EpiSeg seg[3];
   const unsigned char* rowmask;   // optional 0/1 mask multiplied into segment rows flagged below
@@ -202,7 +203,11 @@ __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_
 //   AUX  gate logits / residual come from shared-memory tiles prefetched by the producer.
 //   PRECISE  fp32-accurate mode (operands are bf16 triple splits concatenated along K, see split3): exact
 //            sigmoid, fp32 gate logits, split stores.
-template <int BN, bool GLU, bool AUX, bool PRECISE>
+//   SWAP  channel-major GLU output (the triangle-multiplication operands): the tensor core computes the TRANSPOSED tile,
+//         D[channel][position] = W[channel][:] . X[position][:], i.e. the 128 value rows and the 128 gate rows of the weight
+//         tile are the M operands of two N=128 MMAs and the 128 positions are the N operand.  A thread then holds
+//         consecutive positions of ONE channel and writes them with 32-byte stores: no transpose through shared memory.
+template <int BN, bool GLU, bool AUX, bool PRECISE, bool SWAP = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_out0, const __grid_constant__ CUtensorMap tm_out1,
@@ -213,6 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   constexpr int OUT_BN_GLU = BN / 2;
   constexpr int ACC_COLS = PRECISE ? 2 * BN : BN;  // precise: main accumulator, then the correction accumulator
   static_assert(!PRECISE || BN <= 128, "the fp32-accurate variant needs four accumulators of BN columns");
+  static_assert(!SWAP || (BN == 256 && GLU && !AUX && !PRECISE), "the swapped orientation exists for the BN = 256 GLU tile");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -328,9 +334,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const bool corr = PRECISE && kb >= p.k_main_blocks;
           const uint32_t d_acc = corr ? d_tmem + BN : d_tmem;
           const bool first = corr ? (kb == p.k_main_blocks) : (kb == 0);
+          if constexpr (SWAP) {
+            // value rows (first 128 rows of the weight stage) -> columns 0..127, gate rows -> columns 128..255
+            constexpr uint32_t idesc_sw = ptx::make_idesc(kBM, 128, /*bf16*/ 1);
+            const uint64_t g_desc = b_desc + ((128 * 128) >> 4);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            ptx::mma_f16_ss(d_acc, a_desc + k * 2, b_desc + k * 2, idesc, (first && k == 0) ? 0u : 1u);
+            for (int k = 0; k < kBK / 16; ++k) {
+              ptx::mma_f16_ss(d_acc, b_desc + k * 2, a_desc + k * 2, idesc_sw, (first && k == 0) ? 0u : 1u);
+              ptx::mma_f16_ss(d_acc + 128, g_desc + k * 2, a_desc + k * 2, idesc_sw, (first && k == 0) ? 0u : 1u);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              ptx::mma_f16_ss(d_acc, a_desc + k * 2, b_desc + k * 2, idesc, (first && k == 0) ? 0u : 1u);
+          }
           ptx::tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -382,6 +399,53 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
       constexpr int out_bn = GLU ? OUT_BN_GLU : BN;
       const int out_col_tile = n_tile * out_bn;
+      if constexpr (SWAP) {
+        // lanes are channels, columns are the tile's 128 positions.  The position mask of the tile goes through shared
+        // memory: thread r of the first four epilogue warps holds the mask of position r (fetched a tile ahead).
+        float* s_maskf = reinterpret_cast<float*>(s_stage_out) + acc * kBM;
+        if (chunk_phase == 0) {
+          s_maskf[r] = mask_v;
+          ptx::mbar_arrive(&cm_bar[acc]);
+        }
+        if (!ptx::mbar_wait(&cm_bar[acc], acc_phase, 108)) { ok = false; break; }
+        const EpiSeg& sg = p.seg[0];
+        const int ch = out_col_tile + r;  // output channel of this lane
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(sg.dst) + static_cast<long long>(ch) * sg.s_col +
+                              static_cast<long long>(b) * sg.s_b + static_cast<long long>(o) * sg.s_o;
+#pragma unroll 1
+        for (int c = chunk_phase * 32; c < kBM; c += 32 * (kEpiWarps / 4)) {
+          uint32_t raw[32], rawg[32];
+          ptx::tmem_ld_32x32b_x32(t_row + c, raw);
+          ptx::tmem_ld_32x32b_x32(t_row + 128 + c, rawg);
+          float mk[32];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 m4 = *reinterpret_cast<const float4*>(s_maskf + c + 4 * q);
+            mk[4 * q] = m4.x; mk[4 * q + 1] = m4.y; mk[4 * q + 2] = m4.z; mk[4 * q + 3] = m4.w;
+          }
+          ptx::tmem_ld_wait();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float v0 = __uint_as_float(raw[i]) * sigmoidf_fast(__uint_as_float(rawg[i])) * mk[i];
+            const float v1 = __uint_as_float(raw[i + 1]) * sigmoidf_fast(__uint_as_float(rawg[i + 1])) * mk[i + 1];
+            w[i >> 1] = pack_bf16x2(v0, v1);
+          }
+          const int n0 = nb * kBM + c;
+          if (ch < sg.ncols) {
+            __nv_bfloat16* d = drow + n0;
+            if (n0 + 32 <= p.n_extent && (reinterpret_cast<uintptr_t>(d) & 31) == 0) {
+              st_global_v8(d, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+              st_global_v8(d + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.n_extent)
+                  d[i] = __ushort_as_bfloat16(static_cast<unsigned short>((i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xffffu)));
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = chunk_phase * 32; c < out_bn; c += 32 * (kEpiWarps / 4)) {
         const int out_col = out_col_tile + c;
