@@ -353,16 +353,19 @@ __global__ void __launch_bounds__(kCmPos) layernorm_cm_kernel(const TI* __restri
   const long long p = p0 + threadIdx.x;
   if (p >= npos) return;
   const __nv_bfloat16* col = slab + threadIdx.x;
-  float s = 0.f;
-#pragma unroll 8
-  for (int ch = 0; ch < c; ++ch) s += __bfloat162float(col[ch * kCmPos]);
-  const float mean = s / static_cast<float>(c);
-  float q = 0.f;
+  // mean and variance in one walk down the column, as sums of (x - x0) and (x - x0)^2 with x0 the first channel:
+  // the shift keeps the subtraction of the squared mean harmless
+  const float x0 = __bfloat162float(col[0]);
+  float s = 0.f, q2 = 0.f;
 #pragma unroll 8
   for (int ch = 0; ch < c; ++ch) {
-    const float d = __bfloat162float(col[ch * kCmPos]) - mean;
-    q += d * d;
+    const float d = __bfloat162float(col[ch * kCmPos]) - x0;
+    s += d;
+    q2 = fmaf(d, d, q2);
   }
+  const float ms = s / static_cast<float>(c);
+  const float mean = x0 + ms;
+  const float q = fmaxf(q2 - s * ms, 0.f);
   const float rstd = rsqrtf(q / static_cast<float>(c) + eps);
   __nv_bfloat16* yr = y + (static_cast<long long>(batch) * npos + p) * c;
   if ((c & 15) == 0 && (reinterpret_cast<uintptr_t>(yr) & 31) == 0) {

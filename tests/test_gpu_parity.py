@@ -367,6 +367,31 @@ def test_diffusion_modules_float32_compute(dev):
     check(stack(to(inp["a"]), to(inp["s"]), to(inp["pair_bias"]), to(inp["mask"])), "diffusion_stack")
 
 
+def test_graphed_call_replays_the_token_transformer(dev):
+    """A CUDA-graph replay of the token transformer gives the result of the eager call, also after the inputs change."""
+    from kfold_b200 import modules as M
+    from kfold_b200.graphs import GraphedCall
+    inp = cases.build_inputs("diffusion_stack")
+    stack = M.CachedGlobalTransformerStack(768, 384, 16, 2).to(dev)
+    stack.load_state_dict(inp["w"], strict=True)
+    a, s, bias, mask = (inp[k].to(dev) for k in ("a", "s", "pair_bias", "mask"))
+
+    def step(a_, s_):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            return stack(a_, s_, bias, mask)
+
+    with torch.no_grad():
+        graphed = GraphedCall(step, a, s)
+        for scale in (1.0, 0.5):
+            a2, s2 = a * scale, s * scale
+            eager = step(a2, s2).clone()
+            replay = graphed(a2, s2)
+            torch.cuda.synchronize()
+            assert torch.equal(eager, replay)
+    with pytest.raises(ValueError):
+        graphed(a[:, :1], s)
+
+
 def test_diffusion_stack_config4_shape(dev):
     """BASELINE config 4's token transformer shape: c=768, 16 heads x 48, L=768, 5 samples sharing the pair bias
     (2 of the 24 blocks), against the oracle run on the GPU in fp32."""
