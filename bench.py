@@ -68,8 +68,8 @@ def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C
 
 
 # DRAM traffic of the triangle-attention kernel from its ncu capture at N=384 (dram__bytes_read.sum +
-# dram__bytes_write.sum of one launch: 152.4 MB + 24.2 MB); it grows with the number of pair positions.
-NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 152.368384e6 + 24.240896e6}}
+# dram__bytes_write.sum of one launch: 152.4 MB + 25.8 MB); it grows with the number of pair positions.
+NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 152.377600e6 + 25.842688e6}}
 
 
 def ncu_traffic(tag: str, n: int):
@@ -102,7 +102,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None

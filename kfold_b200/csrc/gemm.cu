@@ -1,4 +1,5 @@
 // Host launcher of the persistent tcgen05 GEMM (see gemm.cuh for the kernel).
+#include <limits.h>
 #include <stdio.h>
 #include <string.h>
 
@@ -108,10 +109,22 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
             !p.seg[0].out_fp32 && p.seg[0].col_begin == 0 && p.n_cols % 256 == 0 && p.col_bias == nullptr &&
             p.gate == nullptr && p.resid == nullptr && (p.rowmask == nullptr || (p.mask_segs & 1)))
                ? 1 : 0;
+  // trailing channel-major bf16 segments that start on a tile boundary are computed in the swapped orientation as well
+  // (plain BN = 128 kernel): the threads then store runs of consecutive positions directly
+  p.swap_col_begin = INT_MAX;
+  if (bn == 128 && !p.glu && !p.precise) {
+    for (int i = p.nseg - 1; i >= 0; --i) {
+      const EpiSeg& sg = p.seg[i];
+      const bool cm = sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && !sg.split && sg.col_begin % 128 == 0 &&
+                      !((p.mask_segs >> i) & 1) && (i > 0 || (p.gate == nullptr && p.resid == nullptr));
+      if (!cm) break;
+      p.swap_col_begin = sg.col_begin;
+    }
+  }
   for (int i = 0; i < p.nseg; ++i) {
     EpiSeg& sg = p.seg[i];
     sg.tma_slot = -1;
-    if (p.swap) continue;
+    if (p.swap || sg.col_begin >= p.swap_col_begin) continue;
     const bool aligned = (reinterpret_cast<uintptr_t>(sg.dst) & 15) == 0 && sg.s_o % 8 == 0 && sg.s_col % 8 == 0 &&
                          (sg.s_b % 8 == 0 || p.batch == 1) && (sg.s_o != 0 || p.o_extent == 1);
     if (sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && aligned && next_slot < 2 && !p.precise) {

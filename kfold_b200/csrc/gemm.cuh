@@ -52,6 +52,8 @@ struct GemmParams {
   int n_blocks, num_m_tiles, num_n_tiles;
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
   int swap;                       // launcher: channel-major GLU output computed in the swapped orientation (see SWAP)
+  int swap_col_begin;             // launcher (BN = 128, plain epilogue): tiles whose first column is >= this hold channel-major
+                                  // segments only and are computed in the swapped orientation too (INT_MAX: none)
   int nseg;
   EpiSeg seg[3];
   const unsigned char* rowmask;   // optional 0/1 mask multiplied into segment rows flagged below
@@ -219,6 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   constexpr int ACC_COLS = PRECISE ? 2 * BN : BN;  // precise: main accumulator, then the correction accumulator
   static_assert(!PRECISE || BN <= 128, "the fp32-accurate variant needs four accumulators of BN columns");
   static_assert(!SWAP || (BN == 256 && GLU && !AUX && !PRECISE), "the swapped orientation exists for the BN = 256 GLU tile");
+  constexpr bool kPlain128 = (BN == 128 && !GLU && !AUX && !PRECISE);  // the variant that may swap single tiles
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -322,6 +325,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
         const uint32_t acc = tile_iter & 1;
         const uint32_t acc_phase = (tile_iter >> 1) & 1;
+        const int n_tile_mma = tile % p.num_n_tiles;
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, 102)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
@@ -344,9 +348,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               ptx::mma_f16_ss(d_acc + 128, g_desc + k * 2, a_desc + k * 2, idesc_sw, (first && k == 0) ? 0u : 1u);
             }
           } else {
+            // (plain BN = 128 tiles of channel-major segments: operands exchanged, D[channel][position])
+            const bool sw = kPlain128 && n_tile_mma * BN >= p.swap_col_begin;
+            const uint64_t m_desc = sw ? b_desc : a_desc, n_desc = sw ? a_desc : b_desc;
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k)
-              ptx::mma_f16_ss(d_acc, a_desc + k * 2, b_desc + k * 2, idesc, (first && k == 0) ? 0u : 1u);
+              ptx::mma_f16_ss(d_acc, m_desc + k * 2, n_desc + k * 2, idesc, (first && k == 0) ? 0u : 1u);
           }
           ptx::tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -433,6 +440,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
           const int n0 = nb * kBM + c;
           if (ch < sg.ncols) {
+            __nv_bfloat16* d = drow + n0;
+            if (n0 + 32 <= p.n_extent && (reinterpret_cast<uintptr_t>(d) & 31) == 0) {
+              st_global_v8(d, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+              st_global_v8(d + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.n_extent)
+                  d[i] = __ushort_as_bfloat16(static_cast<unsigned short>((i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xffffu)));
+            }
+          }
+        }
+      } else if (kPlain128 && out_col_tile >= p.swap_col_begin) {
+        // a tile of channel-major segments, computed swapped: this lane is output column (channel) out_col_tile + r, the
+        // tile's columns are its 128 positions.  The launcher guarantees that the tile lies inside one segment.
+        int si = 0;
+        if (p.nseg > 1 && out_col_tile >= p.seg[1].col_begin) si = 1;
+        if (p.nseg > 2 && out_col_tile >= p.seg[2].col_begin) si = 2;
+        const EpiSeg& sg = p.seg[si];
+        const int ch_local = out_col_tile + r - sg.col_begin;
+        const bool lane_ok = ch_local < sg.ncols;
+        const float bias_v = (p.col_bias != nullptr && lane_ok) ? p.col_bias[out_col_tile + r] : 0.0f;
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(sg.dst) + static_cast<long long>(lane_ok ? ch_local : 0) * sg.s_col +
+                              static_cast<long long>(b) * sg.s_b + static_cast<long long>(o) * sg.s_o;
+#pragma unroll 1
+        for (int c = chunk_phase * 32; c < kBM; c += 32 * (kEpiWarps / 4)) {
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32b_x32(t_row + c, raw);
+          ptx::tmem_ld_wait();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            w[i >> 1] = pack_bf16x2(__uint_as_float(raw[i]) + bias_v, __uint_as_float(raw[i + 1]) + bias_v);
+          const int n0 = nb * kBM + c;
+          if (lane_ok) {
             __nv_bfloat16* d = drow + n0;
             if (n0 + 32 <= p.n_extent && (reinterpret_cast<uintptr_t>(d) & 31) == 0) {
               st_global_v8(d, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
