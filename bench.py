@@ -58,6 +58,7 @@ def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C
         # 8 tensor-core instructions per 128-row tile: their time is the traffic of the tensors around them.
         "layernorm_rows": ("hbm", 2.0 * p * c * 2),
         "layernorm_cm": ("hbm", 2.0 * p * c * 2),
+        "layernorm_cm_stats": ("hbm", 1.0 * p * c * 2 + p * 8),   # read t, write (mean, rstd) per position
         "trimul_in_proj": ("hbm", 3.0 * p * c * 2),            # read x~, write a and b
         "trimul_gate_proj": ("hbm", 2.0 * p * c * 2),          # read x~, write the gate logits
         "trimul_out_proj": ("hbm", 4.0 * p * c * 2),           # read LN(t), gate logits, residual; write out

@@ -81,7 +81,15 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   p.num_n_tiles = cdiv(p.n_cols, bn);
 
   CUtensorMap ta, tb;
-  {
+  p.a_mn_major = a.s_k != 0 ? 1 : 0;
+  if (p.a_mn_major) {
+    KFB_CHECK_ARG(a.s_n == 1 && p.k_extent % kBK == 0 && !p.precise && !p.glu, "K-outer A operand: rows must be contiguous, K a "
+                  "multiple of %d, plain bf16 GEMM", kBK);
+    const uint64_t dims[4] = {(uint64_t)p.n_extent, (uint64_t)p.k_extent, (uint64_t)p.o_extent, (uint64_t)p.batch};
+    const uint64_t str[3] = {(uint64_t)a.s_k * 2, (uint64_t)a.s_o * 2, (uint64_t)a.s_b * 2};
+    const uint32_t box[4] = {64, kBK, 1, 1};
+    KFB_TRY(make_tmap(&ta, a.ptr, 2, 4, dims, str, box, 128));
+  } else {
     const uint64_t dims[4] = {(uint64_t)p.k_extent, (uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)p.batch};
     const uint64_t str[3] = {(uint64_t)a.s_n * 2, (uint64_t)a.s_o * 2, (uint64_t)a.s_b * 2};
     const uint32_t box[4] = {kBK, kBM, 1, 1};
@@ -112,7 +120,7 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   // trailing channel-major bf16 segments that start on a tile boundary are computed in the swapped orientation as well
   // (plain BN = 128 kernel): the threads then store runs of consecutive positions directly
   p.swap_col_begin = INT_MAX;
-  if (bn == 128 && !p.glu && !p.precise) {
+  if (bn == 128 && !p.glu && !p.precise && !p.a_mn_major) {
     for (int i = p.nseg - 1; i >= 0; --i) {
       const EpiSeg& sg = p.seg[i];
       const bool cm = sg.s_n == 1 && sg.s_col != 1 && !sg.out_fp32 && !sg.split && sg.col_begin % 128 == 0 &&

@@ -52,6 +52,10 @@ struct GemmParams {
   int n_blocks, num_m_tiles, num_n_tiles;
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
   int swap;                       // launcher: channel-major GLU output computed in the swapped orientation (see SWAP)
+  int a_mn_major;                 // launcher: the A operand is stored K-outer ([k][row], rows contiguous) and read MN-major
+  const float2* row_stats;        // optional LayerNorm fold: out = rstd[row] * (acc - mean[row] * col_s1[col]) + col_s0[col]
+  const float* col_s1;            //   (mean, rstd) per flat row; col_s1 = sum_k W'[col][k], col_s0 = sum_k beta[k] W[col][k]
+  const float* col_s0;            //   with W' = gamma * W the matrix actually multiplied (applied before gate / residual)
   int swap_col_begin;             // launcher (BN = 128, plain epilogue): tiles whose first column is >= this hold channel-major
                                   // segments only and are computed in the swapped orientation too (INT_MAX: none)
   int nseg;
@@ -307,6 +311,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int kb = 0; kb < num_k; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1, 101)) { ok = false; break; }
           ptx::mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          if (p.a_mn_major) {
+            // two boxes of [64 k][64 rows]: 128-byte rows of consecutive rows (positions), one per k index
+            ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], nb * kBM, kb * kBK, o, b);
+            ptx::tma_load_4d(s_a + stage * Cfg::kAStage + Cfg::kAStage / 2, &tm_a, &full_bar[stage], nb * kBM + 64, kb * kBK, o, b);
+          } else
           ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], kb * kBK, nb * kBM, o, b);
           ptx::tma_load_4d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], kb * kBK, b_col_lo, b_col_hi, bb);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -347,6 +356,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               ptx::mma_f16_ss(d_acc, b_desc + k * 2, a_desc + k * 2, idesc_sw, (first && k == 0) ? 0u : 1u);
               ptx::mma_f16_ss(d_acc + 128, g_desc + k * 2, a_desc + k * 2, idesc_sw, (first && k == 0) ? 0u : 1u);
             }
+          } else if (p.a_mn_major) {
+            // A as [k][rows]: MN-major, 128-byte swizzled rows; 8 k-rows are 1024 bytes apart, the next 64 rows
+            // (positions) half a stage further; a K=16 step advances by 16 k-rows = 2048 bytes
+            const uint64_t am_desc = static_cast<uint64_t>((ptx::smem_u32(s_a + stage * Cfg::kAStage) & 0x3ffff) >> 4) |
+                                     (static_cast<uint64_t>((Cfg::kAStage / 2) >> 4) << 16) |
+                                     (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              ptx::mma_f16_ss(d_acc, am_desc + k * (2048 >> 4), b_desc + k * 2, idesc | (1u << 15), (first && k == 0) ? 0u : 1u);
           } else {
             // (plain BN = 128 tiles of channel-major segments: operands exchanged, D[channel][position])
             const bool sw = kPlain128 && n_tile_mma * BN >= p.swap_col_begin;
@@ -555,6 +573,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] += (col_local + i < sg.ncols) ? p.col_bias[out_col + i] : 0.0f;
         }
+        if (p.row_stats != nullptr && si == 0) {
+          // folded LayerNorm of the A rows: acc was computed on the raw rows with gamma folded into the weights
+          const float2 st = row_ok ? p.row_stats[(static_cast<long long>(b) * p.o_extent + o) * p.n_extent + n] : make_float2(0.f, 1.f);
+          const float4* s1 = reinterpret_cast<const float4*>(p.col_s1 + out_col);
+          const float4* s0 = reinterpret_cast<const float4*>(p.col_s0 + out_col);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 a1 = __ldg(s1 + q), a0 = __ldg(s0 + q);
+            v[4 * q] = fmaf(st.y, fmaf(-st.x, a1.x, v[4 * q]), a0.x);
+            v[4 * q + 1] = fmaf(st.y, fmaf(-st.x, a1.y, v[4 * q + 1]), a0.y);
+            v[4 * q + 2] = fmaf(st.y, fmaf(-st.x, a1.z, v[4 * q + 2]), a0.z);
+            v[4 * q + 3] = fmaf(st.y, fmaf(-st.x, a1.w, v[4 * q + 3]), a0.w);
+          }
+        }
         if ((p.mask_segs >> si) & 1) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] *= mask_v;
@@ -723,6 +755,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 struct GemmOperandA {  // A[(b,o,n), k], strides in elements
   const void* ptr;
   long long s_n, s_o, s_b;
+  long long s_k = 0;       // != 0: K-outer storage, element (row, k) at ptr + k * s_k + row (rows contiguous, s_n = 1):
+                           // the operand is then read MN-major (n_extent must cover whole 64-row boxes in memory)
 };
 struct GemmOperandB {  // B[(b), col, k]; optionally col = hi * col_inner + lo with its own stride for hi
   const void* ptr;

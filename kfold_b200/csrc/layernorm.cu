@@ -397,6 +397,92 @@ __global__ void __launch_bounds__(kCmPos) layernorm_cm_kernel(const TI* __restri
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// LayerNorm folded into the GEMM that follows it.  For rows x (c channels) and a projection W,
+//   LN(x) W^T = rstd * (x W'^T - mean * s1) + s0,   W' = gamma * W,  s1[n] = sum_k W'[n][k],  s0[n] = sum_k beta[k] W[n][k],
+// so the GEMM can read the raw rows (here: channel-major, as the triangle contraction leaves them) and the epilogue
+// applies the per-row (mean, rstd) and the per-column s1, s0.  Two small kernels prepare those.
+// ------------------------------------------------------------------------------------------------
+// (mean, rstd) over the channels of every position of a channel-major tensor t[c][npos]; two positions per thread
+__global__ void __launch_bounds__(256) cm_stats_kernel(const __nv_bfloat16* __restrict__ t, float2* __restrict__ stats,
+                                                       long long npos, int c, long long chan_stride, float eps) {
+  const long long p2 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+  if (p2 >= npos) return;
+  const bool pair = p2 + 1 < npos;
+  float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+  // shifted sums (by the first channel's value) keep E[x^2] - E[x]^2 harmless
+  float x00, x01;
+  {
+    const __nv_bfloat16* src = t + p2;
+    x00 = __bfloat162float(src[0]);
+    x01 = pair ? __bfloat162float(src[1]) : 0.f;
+  }
+#pragma unroll 8
+  for (int ch = 0; ch < c; ++ch) {
+    const __nv_bfloat16* src = t + ch * chan_stride + p2;
+    float a, b2;
+    if (pair) {
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(src);
+      a = __uint_as_float(w << 16);
+      b2 = __uint_as_float(w & 0xffff0000u);
+    } else {
+      a = __bfloat162float(src[0]);
+      b2 = 0.f;
+    }
+    const float d0 = a - x00, d1 = b2 - x01;
+    s0 += d0; q0 = fmaf(d0, d0, q0);
+    s1 += d1; q1 = fmaf(d1, d1, q1);
+  }
+  const float inv_c = 1.0f / static_cast<float>(c);
+  const float m0 = s0 * inv_c, m1 = s1 * inv_c;
+  stats[p2] = make_float2(x00 + m0, rsqrtf(fmaxf(q0 - s0 * m0, 0.f) * inv_c + eps));
+  if (pair) stats[p2 + 1] = make_float2(x01 + m1, rsqrtf(fmaxf(q1 - s1 * m1, 0.f) * inv_c + eps));
+}
+
+int launch_cm_stats(cudaStream_t stream, const __nv_bfloat16* t, float2* stats, long long npos, int c, long long chan_stride,
+                    float eps) {
+  KFB_CHECK_ARG(npos > 0 && npos % 2 == 0 && c > 0 && chan_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(t) & 3) == 0,
+                "cm_stats: npos %lld (even), c %d, channel stride %lld (even)", npos, c, chan_stride);
+  const long long threads = npos / 2;
+  LaunchScope scope(stream, "layernorm_cm_stats");
+  cm_stats_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(t, stats, npos, c, chan_stride, eps);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+// W'[n][k] = bf16(gamma[k] W[n][k]); s1[n] = sum_k W'[n][k] (of the rounded values); s0[n] = sum_k beta[k] W[n][k]
+__global__ void __launch_bounds__(128) ln_fold_weights_kernel(const __nv_bfloat16* __restrict__ w, const float* __restrict__ gamma,
+                                                              const float* __restrict__ beta, __nv_bfloat16* __restrict__ wf,
+                                                              float* __restrict__ s1, float* __restrict__ s0, int k) {
+  const int n = blockIdx.x;
+  float a1 = 0.f, a0 = 0.f;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const float wv = __bfloat162float(w[static_cast<long long>(n) * k + i]);
+    const __nv_bfloat16 f = __float2bfloat16_rn(wv * (gamma != nullptr ? gamma[i] : 1.0f));
+    wf[static_cast<long long>(n) * k + i] = f;
+    a1 += __bfloat162float(f);
+    a0 += (beta != nullptr ? beta[i] : 0.0f) * wv;
+  }
+  __shared__ float r1[4], r0[4];
+  a1 = warp_sum(a1);
+  a0 = warp_sum(a0);
+  if ((threadIdx.x & 31) == 0) { r1[threadIdx.x >> 5] = a1; r0[threadIdx.x >> 5] = a0; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s1[n] = (r1[0] + r1[1]) + (r1[2] + r1[3]);
+    s0[n] = (r0[0] + r0[1]) + (r0[2] + r0[3]);
+  }
+}
+
+int launch_ln_fold_weights(cudaStream_t stream, const __nv_bfloat16* w, const float* gamma, const float* beta, __nv_bfloat16* wf,
+                           float* s1, float* s0, int n, int k) {
+  KFB_CHECK_ARG(n > 0 && k > 0, "ln_fold_weights: n %d k %d", n, k);
+  LaunchScope scope(stream, "layernorm_fold_weights");
+  ln_fold_weights_kernel<<<n, 128, 0, stream>>>(w, gamma, beta, wf, s1, s0, k);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
 int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, const float* w, const float* b, int batch,
                         long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype,
                         int split_out) {

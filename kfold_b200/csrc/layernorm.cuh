@@ -27,4 +27,11 @@ int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, co
 int launch_adaln(cudaStream_t stream, const void* a, void* y, const void* gv, long long rows, int c, int samples,
                  int l, float eps, int in_dtype, int out_dtype);
 
+// LayerNorm folded into the following GEMM (see layernorm.cu): per-position (mean, rstd) of a channel-major tensor, and the
+// folded weights W' = gamma * W (bf16) with s1[n] = sum_k W'[n][k], s0[n] = sum_k beta[k] W[n][k].
+int launch_cm_stats(cudaStream_t stream, const __nv_bfloat16* t, float2* stats, long long npos, int c, long long chan_stride,
+                    float eps);
+int launch_ln_fold_weights(cudaStream_t stream, const __nv_bfloat16* w, const float* gamma, const float* beta, __nv_bfloat16* wf,
+                           float* s1, float* s0, int n, int k);
+
 }  // namespace kfb

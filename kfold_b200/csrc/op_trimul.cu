@@ -124,6 +124,39 @@ int finish(cudaStream_t stream, const __nv_bfloat16* a, const __nv_bfloat16* b, 
     }
     KFB_TRY(launch_gemm_bf16(stream, oa, ob, p, force_bn, "trimul_contraction"));
   }
+  // LayerNorm_out folded into the output projection: the GEMM reads t as it lies (channel-major, read MN-major), the
+  // epilogue applies the per-position statistics.  The scratch buffer tn holds the folded weights and the statistics.
+  const bool fold = (c % kBK == 0) && (pos % 8 == 0) &&
+                    pos * static_cast<long long>(c) * 2 >= static_cast<long long>(c) * c * 2 + 256 + 2ll * c * 4 + 256 + pos * 8;
+  if (fold) {
+    uint8_t* base = reinterpret_cast<uint8_t*>(tn);
+    __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(base);
+    float* s1 = reinterpret_cast<float*>(base + align_up(static_cast<size_t>(c) * c * 2, 256));
+    float* s0 = s1 + c;
+    float2* stats = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(s1) + align_up(static_cast<size_t>(2) * c * 4, 256));
+    KFB_TRY(launch_ln_fold_weights(stream, static_cast<const __nv_bfloat16*>(w_pout), ln_out_w, ln_out_b, wf, s1, s0, c, c));
+    KFB_TRY(launch_cm_stats(stream, t, stats, pos, c, pos, eps));
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(pos);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, 0, 0, dtype == KFB_FP32);
+    p.gate = gl;
+    p.g_col = 1;
+    p.g_n = c;
+    p.resid = resid;
+    p.row_stats = stats;
+    p.col_s1 = s1;
+    p.col_s0 = s0;
+    GemmOperandA oa = {t, 1, 0, 0};
+    oa.s_k = pos;
+    GemmOperandB ob = {wf, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, oa, ob, p, 0, "trimul_out_proj"));
+    return KFB_OK;
+  }
   KFB_TRY(launch_layernorm_cm(stream, t, tn, ln_out_w, ln_out_b, batch, rn, c, pos, rn, eps, KFB_BF16));
   {
     GemmParams p = {};

@@ -9,7 +9,7 @@ pair representation z (N, N, C) by rows: rank r owns rows [r*N/P, (r+1)*N/P).  P
                                       ALL-TO-ALL of a and b to a channel-sharded layout (every rank gets all rows of
                                       C/P channels), local contraction, ALL-TO-ALL of t back to row shards.  That moves
                                       3 N^2 C / P values per rank instead of the (P-1) N^2 C / P of an all-gather of b
-                                      (the all-gather form is kept for C not divisible by P)
+                                      (the all-gather form is kept below four ranks and for C not divisible by P)
   triangle multiplication, incoming   t[i,j] = sum_k a[k,i] b[k,j]    a, b are taken from the TRANSPOSED shard
                                       (all-to-all transpose of z), where it is the outgoing form; the
                                       output gate and the residual use the row shard
@@ -216,7 +216,9 @@ class ShardedPairformerBlock:
         """Weights for the channel-sharded exchange when C divides by the number of ranks (packed once per module)."""
         world = self.ops.world
         c = mod.layernorm_in.normalized_shape
-        if world == 1 or c % world != 0:
+        # the channel-sharded exchange moves 3 N^2 C / P values per rank, the all-gather of b (P - 1) N^2 C / P: it pays from
+        # four ranks on
+        if world < 4 or c % world != 0:
             return mod._packed(dev, torch.bfloat16, packing.pack_trimul)
         key = (id(mod), dev)
         if key not in self._trimul_packs:
