@@ -207,9 +207,14 @@ class ShardedPairOps:
 class ShardedPairformerBlock:
     """The composite Pairformer block on a row shard.  Wraps the weights of a `modules.PairformerBlock`."""
 
-    def __init__(self, block, group=None):
+    def __init__(self, block, group=None, exchange: str = "auto"):
+        """``exchange``: how the triangle multiplication moves its operands: "channel" (all-to-all to a channel-sharded
+        layout), "gather" (all-gather of b) or "auto" (channel from four ranks on)."""
+        if exchange not in ("auto", "channel", "gather"):
+            raise ValueError(f"unknown exchange {exchange!r}")
         self.block = block
         self.ops = ShardedPairOps(group)
+        self.exchange = exchange
         self._trimul_packs = {}
 
     def _pack_trimul(self, mod, dev):
@@ -218,7 +223,8 @@ class ShardedPairformerBlock:
         c = mod.layernorm_in.normalized_shape
         # the channel-sharded exchange moves 3 N^2 C / P values per rank, the all-gather of b (P - 1) N^2 C / P: it pays from
         # four ranks on
-        if world < 4 or c % world != 0:
+        channel = self.exchange == "channel" or (self.exchange == "auto" and world >= 4)
+        if world == 1 or not channel or c % world != 0:
             return mod._packed(dev, torch.bfloat16, packing.pack_trimul)
         key = (id(mod), dev)
         if key not in self._trimul_packs:

@@ -16,7 +16,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, n: int, q):
+def _worker(rank: int, world: int, port: int, n: int, exchange: str, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -36,7 +36,7 @@ def _worker(rank: int, world: int, port: int, n: int, q):
         with torch.no_grad():
             z_ref, s_ref = blk(zb.clone(), sb.clone(), pm.to(dev), m.to(dev))
             r0, r1 = sharded.shard_rows(n, world, rank)
-            sblk = sharded.ShardedPairformerBlock(blk)
+            sblk = sharded.ShardedPairformerBlock(blk, exchange=exchange)
             z_loc, s_out = sblk(zb[0, r0:r1].contiguous(), sb.clone(), pm[0, r0:r1].to(dev).contiguous(), m.to(dev))
         torch.cuda.synchronize()
         status = L.device_status()
@@ -50,12 +50,14 @@ def _worker(rank: int, world: int, port: int, n: int, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("exchange", ["gather", "channel"])
 @pytest.mark.parametrize("n", [256, 384])
-def test_sharded_block_matches_single_gpu(n):
+def test_sharded_block_matches_single_gpu(n, exchange):
+    """Both exchanges of the triangle multiplication: the all-gather of b and the channel-sharded all-to-all."""
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    mp.spawn(_worker, args=(world, _free_port(), n, q), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), n, exchange, q), nprocs=world, join=True)
     results = [q.get(timeout=10) for _ in range(world)]
     for rank, status, ez, es, exact in results:
         assert status == 0
