@@ -561,9 +561,12 @@ int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
   KFB_CHECK_ARG(p.bias_div >= 1 && p.mask_lo_extent >= 1, "attention: bad divisors");
   KFB_CHECK_ARG(p.batch <= 65535, "attention: batch %d exceeds the grid z limit", p.batch);
   if (p.dpad == 32) {
-    // two batch rows per CTA when consecutive rows share their bias tile
-    static const bool force_r1 = getenv("KFB_ATT_R1") != nullptr;   // debugging aid: one row group per CTA, two CTAs per SM
-    if (!force_r1 && p.batch % 2 == 0 && p.bias_div % 2 == 0) return launch_cfg<32, 2>(stream, p);
+    // One row group per CTA with two CTAs resident per SM is the default: the two CTAs interleave their
+    // softmax and tensor-core phases better than two row groups inside one CTA do (measured 6% faster at
+    // N=768), and the bias tile both read stays in L2.  KFB_ATT_R2 selects the variant with two batch rows
+    // per CTA sharing one bias tile in shared memory (needs consecutive rows to share their bias).
+    static const bool two_rows = getenv("KFB_ATT_R2") != nullptr;
+    if (two_rows && p.batch % 2 == 0 && p.bias_div % 2 == 0) return launch_cfg<32, 2>(stream, p);
     return launch_cfg<32, 1>(stream, p);
   }
   if (p.dpad == 64) return launch_cfg<64, 1>(stream, p);
