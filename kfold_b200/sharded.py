@@ -15,7 +15,7 @@ pair representation z (N, N, C) by rows: rank r owns rows [r*N/P, (r+1)*N/P).  P
                                       output gate and the residual use the row shard
   triangle attention, starting node   rows local; ALL-GATHER of the projected triangle bias only (N*N*H)
   triangle attention, ending node     starting node on the transposed shard, result transposed back
-  single track / pair bias            bias rows all-gathered per head, single track replicated
+  single track / pair bias            bias rows all-gathered (one collective for all heads), single track replicated
 
 Everything here is host-side orchestration: the kernels are the same ones the single-GPU path uses, called
 through the two-phase C entry points (kfb_trimul_project / _finish, kfb_triatt_project / _finish).
@@ -40,11 +40,12 @@ def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
     return rank * rows, (rank + 1) * rows
 
 
-def transpose_shard(x_loc: torch.Tensor, group=None) -> torch.Tensor:
+def transpose_shard(x_loc: torch.Tensor, group=None, add_to: torch.Tensor | None = None) -> torch.Tensor:
     """Row shard of z -> row shard of z^T with one all-to-all.
 
     x_loc (rows, N, *tail) holds z[r*rows : (r+1)*rows, :]; the result holds z^T[r*rows : (r+1)*rows, :],
-    i.e. out[i, k] = z[k, r*rows + i].
+    i.e. out[i, k] = z[k, r*rows + i].  With `add_to` (same shape as the result) the sum add_to + z^T shard is
+    returned, formed in the pass that reorders the received blocks.
     """
     world = dist.get_world_size(group)
     rows, n = x_loc.shape[0], x_loc.shape[1]
@@ -56,6 +57,8 @@ def transpose_shard(x_loc: torch.Tensor, group=None) -> torch.Tensor:
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
     # recv[q][i_q][j_loc] = z[q*rows + i_q, r*rows + j_loc]  ->  out[j_loc][q*rows + i_q]
+    if add_to is not None:
+        return add_to + recv.permute(2, 0, 1, *range(3, recv.dim())).reshape(rows, n, *tail)
     return recv.permute(2, 0, 1, *range(3, recv.dim())).reshape(rows, n, *tail).contiguous()
 
 
@@ -65,6 +68,19 @@ def gather_rows(x_loc: torch.Tensor, group=None) -> torch.Tensor:
     out = torch.empty((world * x_loc.shape[0],) + tuple(x_loc.shape[1:]), dtype=x_loc.dtype, device=x_loc.device)
     dist.all_gather_into_tensor(out, x_loc.contiguous(), group=group)
     return out
+
+
+def gather_head_rows(x_loc: torch.Tensor, group=None) -> torch.Tensor:
+    """(H, rows, n) on every rank -> (H, world*rows, n) with ONE all-gather and one local permute.
+
+    The gathered buffer arrives rank after rank, [world][H][rows][n]; the attention kernels want each head's rows in
+    their natural order, so the heads are moved to the front afterwards (a copy of N*N*H values, far cheaper than one
+    collective per head)."""
+    world = dist.get_world_size(group)
+    h, rows, n = x_loc.shape
+    buf = torch.empty((world * h, rows, n), dtype=x_loc.dtype, device=x_loc.device)
+    dist.all_gather_into_tensor(buf, x_loc.contiguous(), group=group)
+    return buf.view(world, h, rows, n).permute(1, 0, 2, 3).reshape(h, world * rows, n).contiguous()
 
 
 def _bf16(shape, device):
@@ -78,6 +94,15 @@ class ShardedPairOps:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        self._mask_t = None   # (key, transposed mask shard): the pair mask of a complex is the same for every block
+
+    def _transposed_mask(self, mask_loc: torch.Tensor) -> torch.Tensor:
+        """Row shard of the transposed pair mask, exchanged once per mask tensor and reused by every later call."""
+        key = (mask_loc.data_ptr(), mask_loc._version, tuple(mask_loc.shape), mask_loc.dtype)
+        if self._mask_t is None or self._mask_t[0] != key:
+            # the cache keeps `mask_loc` alive so that its address cannot be reused by another tensor
+            self._mask_t = (key, transpose_shard(mask_loc.to(torch.uint8), self.group), mask_loc)
+        return self._mask_t[1]
 
     # ------------------------------------------------------------------ triangle multiplication
     def _trimul_cs(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
@@ -101,10 +126,11 @@ class ShardedPairOps:
                                            L.ptr(pk["w_gout"]) if same else None, L.ptr(xn), L.ptr(ab),
                                            L.ptr(gl) if same else None, 1, rows, n, c, eps, dt, st))
             ab_recv = torch.empty_like(ab)
-            dist.all_to_all_single(ab_recv, ab, group=self.group)       # [source rank][a, b][cl][rows][n]
+            work = dist.all_to_all_single(ab_recv, ab, group=self.group, async_op=True)   # [source rank][a, b][cl][rows][n]
             if not same:   # gate logits of the row shard while the exchange is in flight
                 L.check(lib.kfb_trimul_project(L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
                                                L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, eps, dt, st))
+            work.wait()
             t_send = _bf16((world, cl, rows, n), dev)
             L.check(lib.kfb_trimul_contract_cs(L.ptr(ab_recv), L.ptr(t_send), world, rows, n, cl, L.stream_ptr()))
             t = torch.empty_like(t_send)
@@ -153,8 +179,7 @@ class ShardedPairOps:
     def trimul_incoming(self, x_loc, mask_loc, pk, eps: float = 1e-5):
         """x + TriangleMultiplicationIncoming(x): operands from the transposed shard."""
         xt = transpose_shard(x_loc, self.group)
-        mt = transpose_shard(mask_loc.to(torch.uint8), self.group)
-        return self._trimul(xt, mt, x_loc, pk, eps)
+        return self._trimul(xt, self._transposed_mask(mask_loc), x_loc, pk, eps)
 
     # ------------------------------------------------------------------ triangle attention
     def _triatt_start(self, x_loc, mask_loc, pk, eps: float, resid: bool):
@@ -174,9 +199,7 @@ class ShardedPairOps:
         with torch.cuda.device(dev):
             L.check(lib.kfb_triatt_project(L.ptr(x_loc), L.ptr(pk["ln_w"]), L.ptr(pk["ln_b"]), L.ptr(pk["w_proj"]), L.ptr(xn),
                                            L.ptr(qkg), L.ptr(vt), L.ptr(bias_loc), rows, n, c, heads, eps, dt, L.stream_ptr()))
-            bias_full = _bf16((heads, n, n), dev)
-            for h in range(heads):   # per head, so that the gathered rows land in their natural [n][n] order
-                dist.all_gather_into_tensor(bias_full[h], bias_loc[h], group=self.group)
+            bias_full = gather_head_rows(bias_loc, self.group)
             out = torch.empty_like(x_loc)
             L.check(lib.kfb_triatt_finish(L.ptr(qkg), L.ptr(vt), L.ptr(bias_full), L.ptr(m8), L.ptr(pk["w_out"]), L.ptr(xn),
                                           L.ptr(out), L.ptr(x_loc) if resid else None, rows, n, c, heads, dt, L.stream_ptr()))
@@ -187,9 +210,8 @@ class ShardedPairOps:
 
     def triatt_ending(self, x_loc, mask_loc, pk, eps: float = 1e-5):
         xt = transpose_shard(x_loc, self.group)
-        mt = transpose_shard(mask_loc.to(torch.uint8), self.group)
-        upd_t = self._triatt_start(xt, mt, pk, eps, resid=False)
-        return x_loc + transpose_shard(upd_t, self.group)
+        upd_t = self._triatt_start(xt, self._transposed_mask(mask_loc), pk, eps, resid=False)
+        return transpose_shard(upd_t, self.group, add_to=x_loc)
 
     # ------------------------------------------------------------------ pair bias for the single track
     def pair_bias(self, x_loc, ln_w, ln_b, w, eps: float = 1e-5):
@@ -198,10 +220,7 @@ class ShardedPairOps:
         heads = w.shape[0]
         # the 1-GPU op expects square tensors; project the shard as `rows` independent 1 x n rows
         loc = F.pair_bias_rows(x_loc, ln_w, ln_b, w, eps)                     # (heads, rows, n)
-        full = _bf16((heads, n, n), x_loc.device)
-        for h in range(heads):
-            dist.all_gather_into_tensor(full[h], loc[h], group=self.group)
-        return full
+        return gather_head_rows(loc, self.group)
 
 
 class ShardedPairformerBlock:

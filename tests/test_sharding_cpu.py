@@ -32,6 +32,7 @@ def _worker(rank: int, world: int, port: int, n: int, c: int):
         assert torch.equal(mt.bool(), mask.t()[r0:r1])
         # transposing twice is the identity on the shard
         assert torch.equal(sharded.transpose_shard(zt), z[r0:r1])
+        assert torch.equal(sharded.transpose_shard(zt, add_to=z[r0:r1]), 2 * z[r0:r1])
         full = sharded.gather_rows(z[r0:r1].contiguous())
         assert torch.equal(full, z)
         # the gathered-operand layout the contraction consumes: rank after rank, each piece [channel][rows][n]
@@ -40,6 +41,17 @@ def _worker(rank: int, world: int, port: int, n: int, c: int):
         for q in range(world):
             q0, q1 = sharded.shard_rows(n, world, q)
             assert torch.equal(gathered[q], z[q0:q1].permute(2, 0, 1))
+        # per-head rows gathered with one collective: (H, rows, n) -> (H, N, n)
+        heads = z.permute(2, 0, 1)                                             # [c][n][n] stands in for [H][N][N]
+        assert torch.equal(sharded.gather_head_rows(heads[:, r0:r1].contiguous()), heads)
+        # the transposed mask is exchanged once per mask tensor and reused
+        ops = sharded.ShardedPairOps()
+        m_loc = mask[r0:r1].contiguous()
+        mt1 = ops._transposed_mask(m_loc)
+        assert torch.equal(mt1.bool(), mask.t()[r0:r1])
+        assert ops._transposed_mask(m_loc) is mt1
+        m_loc[0, 0] = ~m_loc[0, 0]                                             # an in-place edit invalidates the cache
+        assert ops._transposed_mask(m_loc) is not mt1
     finally:
         dist.destroy_process_group()
 
