@@ -196,6 +196,49 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
                         int l, int c, int heads, int bias_div, int out_dtype, void* stream);
 
 /*
+ * Gated cross attention with pair bias on already-normalised inputs: queries from x_q, keys and values from x_k.
+ * Replaces `attention_pair_bias(module, x_q, x_k, pair_bias, mask, kernel_backend=..., call_site="diffusion_local")`
+ * (src/kfold/model/primitives/attention.py:28-94; torch kernel :239-271) as CrossAttentionPairBias.forward calls it
+ * on the atom windows (src/kfold/model/layers/folding/attention_pair_bias.py:206-260; windows of 32 queries and
+ * 128 keys built by src/kfold/model/layers/folding/utils.py:97-188).
+ *   x_q : bf16 (batch, lq, c);  x_k : bf16 (batch, lk, c);  mask : (batch, lk) bytes;  lq, lk multiples of 8.
+ *   pair_bias : bf16 (bias batches, heads, lq, lk).  Batch entry b uses bias batch b / bias_div when bias_mod == 0;
+ *   with bias_mod > 0 the batch is ordered (group, sample, window), bias_mod = windows, bias_div = samples * windows,
+ *   and entry b uses bias batch (b / bias_div) * bias_mod + b % bias_mod: one bias per (group, window), shared by the
+ *   diffusion samples.  bias_head_major = 0: stored as above; n > 0: stored (heads, n bias batches, lq, lk), the layout
+ *   kfb_window_bias_fwd writes.
+ *   w_q_packed : bf16 [2*heads*dp, c] = [Wq * log2(e)/sqrt(d) | Wg], heads padded to dp;  q_bias : fp32 [2*heads*dp]
+ *   (scaled q bias, gate bias) or NULL;  w_kv_packed : bf16 [2*heads*dp, c] = [Wk | Wv];
+ *   w_out : bf16 [c, c];  out_bias : fp32 [c] or NULL;  out : (batch, lq, c) of `out_dtype`;
+ *   out_gate : NULL, or bf16 logits (gate_rows, c): row r of the batch * lq query rows is multiplied by
+ *   sigmoid(out_gate[r % gate_rows]) -- the output gate sigmoid(Linear(s_q)) of CrossAttentionPairBias.forward
+ *   (:258-259), stored once when the samples share their conditioning;  resid : NULL or a tensor like out that is added.
+ * With out_dtype = KFB_FP32_PRECISE every tensor argument is fp32, the weights are bf16 triple splits with unpadded
+ * heads ([2c, 6c] each) and the attention core runs on the fp32 CUDA-core kernel.
+ */
+KFB_API size_t kfb_apb_cross_workspace_bytes(int batch, int lq, int lk, int c, int heads);
+KFB_API size_t kfb_apb_cross_workspace_bytes_precise(int batch, int lq, int lk, int c);
+KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
+                              const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
+                              const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
+                              void* workspace, size_t workspace_bytes, int batch, int lq, int lk, int c, int heads,
+                              int bias_div, int bias_mod, int bias_head_major, int out_dtype, void* stream);
+
+/*
+ * Pair bias of the atom windows for every block of a local transformer at once:
+ * bias[h, p] = sum_k LayerNorm(z[p])[k] * w[h, k].  Replaces `self.layernorm_z(z)` of LocalTransformerStack.forward
+ * (src/kfold/model/layers/folding/diffusion_transformer.py:496) and the `linear_z_to_bias` of each block (:590-591)
+ * with their weights stacked into w [heads = blocks * H, c].
+ *   z : (positions, c) with positions = windows * 32 * 128, c in {16, 32, 64};  ln_w / ln_b : fp32 [c] or NULL;
+ *   bias_out : (heads, positions), head-major (the `bias_head_major` layout of kfb_apb_cross_fwd).
+ *   dtype KFB_BF16: z, w, bias_out bf16 (the normalised value is rounded to bf16 before the projection, fp32
+ *   accumulation); KFB_FP32 or KFB_FP32_PRECISE: all three fp32.  normalise == 0 skips the LayerNorm (z already
+ *   normalised: the per-block form of LocalTransformerBlock.forward).
+ */
+KFB_API int kfb_window_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                                long long positions, int c, int heads, float eps, int normalise, int dtype, void* stream);
+
+/*
  * Adaptive LayerNorm: out = sigmoid(g) * LayerNorm(a) + v, LayerNorm without affine (fp32 statistics).
  * Replaces the last line of AdaLN.forward (src/kfold/model/primitives/normalization.py:117-125); the two
  * small projections of the conditioning, g = Linear(LN_s(s)) and v = LinearNoBias(LN_s(s)), are computed by

@@ -40,6 +40,9 @@ _SIGNATURES = {
                        ctypes.c_size_t, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                     c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_apb_cross_fwd": [c_void_p] * 10 + [c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_window_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_finish": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -73,6 +76,8 @@ _SIZE_FUNCS = {
     "kfb_transition_workspace_bytes": [c_ll, c_int, c_int],
     "kfb_triatt_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_workspace_bytes": [c_int, c_int, c_int, c_int],
+    "kfb_apb_cross_workspace_bytes": [c_int, c_int, c_int, c_int, c_int],
+    "kfb_apb_cross_workspace_bytes_precise": [c_int, c_int, c_int, c_int],
     "kfb_trimul_workspace_bytes": [c_int, c_int, c_int],
 }
 

@@ -104,16 +104,23 @@ def apb_supported(module: torch.nn.Module) -> bool:
 
 @torch.compiler.disable
 def b200_attention_pair_bias(module, x_q, x_k, pair_bias, mask, *, call_site: str) -> torch.Tensor:
-    """Stands where ``triton_attention_pair_bias(module, x_q, x_k, pair_bias, mask, call_site=...)`` stands.
-    Self-attention only (x_q is x_k): the token-level call sites "diffusion_global" and "confidence"."""
+    """Stands where ``triton_attention_pair_bias(module, x_q, x_k, pair_bias, mask, call_site=...)`` stands: the
+    token-level self-attention call sites "diffusion_global" and "confidence" (x_q is x_k), and the windowed cross
+    attention of the atom transformers, "diffusion_local" (x_q (..., W, 32, c), x_k (..., W, 128, c))."""
     _check(x_q, "pair-bias attention")
-    if x_q is not x_k:
-        raise NotImplementedError("The B200 pair-bias attention backend handles self-attention call sites only")
     cd = _compute_dtype(x_q)
     precise = _is_precise(cd, "pair-bias attention")
     heads = module.num_heads
     keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight",
             "linear_g.bias", "linear_out.weight", "linear_out.bias")
+    if x_q is not x_k:
+        def pack_cross(sd, dev):
+            return packing.pack_apb_cross({k: sd[k] for k in keys if k in sd}, heads, dev, precise=precise)
+
+        pkc = _cached_pack(module, x_q, cd, "apb_cross", pack_cross)
+        with torch.autocast(x_q.device.type, enabled=False):
+            return F.attention_pair_bias_cross_bcast(x_q.float() if precise else x_q, x_k.float() if precise else x_k, pair_bias,
+                                                     mask, pkc, out_dtype=x_q.dtype)
 
     def pack(sd, dev):
         return packing.pack_apb({k: sd[k] for k in keys if k in sd}, heads, dev, precise=precise)
@@ -218,6 +225,10 @@ def convert(model: torch.nn.Module, diffusion: bool = False) -> int:
         elif name == "SelfAttentionPairBias" and apb_supported(m):
             if getattr(m, "call_site", "") == "diffusion_global" and not diffusion:
                 continue
+            m.kernel_backend = BACKEND
+            n += 1
+        elif name == "CrossAttentionPairBias" and apb_supported(m) and diffusion:
+            # the atom transformers of the sampler and of the input embedder ("diffusion_local"); float32 there too
             m.kernel_backend = BACKEND
             n += 1
     return n

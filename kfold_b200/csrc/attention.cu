@@ -158,7 +158,9 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ptx::mbar_expect_tx(&q_full[g], Cfg::kQBytes);
         ptx::tma_load_3d(s_q + g * Cfg::kQBytes, &tm_q, &q_full[g], p.q_col0 + h * DPAD, qb * kBQ, b0 + g);
       }
-      const int bias_z = (b0 / p.bias_div) * p.heads + h;
+      const int bias_g = b0 / p.bias_div;
+      const int bias_b = p.bias_mod > 0 ? bias_g * p.bias_mod + b0 % p.bias_mod : bias_g;
+      const int bias_z = p.bias_head_major > 0 ? h * p.bias_head_major + bias_b : bias_b * p.heads + h;
       bool ok = true;
       int bst = 0;
       uint32_t bpar = 0;   // ring position of the bias half tiles
@@ -536,7 +538,7 @@ static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
     KFB_TRY(make_tmap(&tv, p.vt, 2, 3, dims, str, box, 128));
   }
   {
-    const int bias_batches = cdiv(p.batch, p.bias_div);
+    const int bias_batches = p.bias_head_major > 0 ? p.bias_head_major : cdiv(p.batch, p.bias_div) * (p.bias_mod > 0 ? p.bias_mod : 1);
     const uint64_t dims[3] = {(uint64_t)p.lk, (uint64_t)p.lq, (uint64_t)bias_batches * p.heads};
     const uint64_t str[2] = {(uint64_t)p.ldb * 2, (uint64_t)p.lq * p.ldb * 2};
     const uint32_t box[3] = {64, kBQ, 1};
@@ -558,7 +560,9 @@ int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
   KFB_CHECK_ARG(p.d % 8 == 0 && p.d <= p.dpad, "attention: head dim %d must be a multiple of 8 and <= %d", p.d, p.dpad);
   KFB_CHECK_ARG(p.ldq % 8 == 0 && p.ldk % 8 == 0 && p.ldv % 8 == 0 && p.ldb % 8 == 0 && p.ldo % 8 == 0,
                 "attention: leading dimensions must be multiples of 8 elements");
-  KFB_CHECK_ARG(p.bias_div >= 1 && p.mask_lo_extent >= 1, "attention: bad divisors");
+  KFB_CHECK_ARG(p.bias_div >= 1 && p.bias_mod >= 0 && p.mask_lo_extent >= 1, "attention: bad divisors");
+  KFB_CHECK_ARG(p.bias_head_major == 0 || p.bias_head_major >= cdiv(p.batch, p.bias_div) * (p.bias_mod > 0 ? p.bias_mod : 1),
+                "attention: head-major bias with %d batches is too small", p.bias_head_major);
   KFB_CHECK_ARG(p.batch <= 65535, "attention: batch %d exceeds the grid z limit", p.batch);
   if (p.dpad == 32) {
     // One row group per CTA with two CTAs resident per SM is the default: the two CTAs interleave their
@@ -566,7 +570,7 @@ int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
     // N=768), and the bias tile both read stays in L2.  KFB_ATT_R2 selects the variant with two batch rows
     // per CTA sharing one bias tile in shared memory (needs consecutive rows to share their bias).
     static const bool two_rows = getenv("KFB_ATT_R2") != nullptr;
-    if (two_rows && p.batch % 2 == 0 && p.bias_div % 2 == 0) return launch_cfg<32, 2>(stream, p);
+    if (two_rows && p.batch % 2 == 0 && p.bias_div % 2 == 0 && p.bias_mod == 0) return launch_cfg<32, 2>(stream, p);
     return launch_cfg<32, 1>(stream, p);
   }
   if (p.dpad == 64) return launch_cfg<64, 1>(stream, p);

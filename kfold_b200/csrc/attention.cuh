@@ -37,8 +37,13 @@ struct AttnParams {
   const void* k; long long ldk; int k_col0;
   // v^T : [batch][heads*dpad][ldv] bf16 (keys contiguous)
   const void* vt; long long ldv;
-  // bias : [bias_batches][heads][lq][ldb] bf16 ; batch entry b uses bias batch b / bias_div
-  const void* bias; long long ldb; int bias_div;
+  // bias : [bias_batches][heads][lq][ldb] bf16 ; batch entry b uses bias batch b / bias_div, or, with bias_mod > 0,
+  // (b / bias_div) * bias_mod + b % bias_mod: batch entries ordered (group, sample, window) with bias_mod windows and
+  // bias_div = samples * windows, one bias per (group, window) that every sample of the group reuses
+  const void* bias; long long ldb; int bias_div; int bias_mod;
+  // 0: bias stored [bias_batches][heads][lq][ldb]; n > 0: stored [heads][n bias batches][lq][ldb] (head-major, as one
+  // projection of all heads of several layers at once writes it)
+  int bias_head_major;
   // key mask (0/1 bytes): element (b, k) at mask + b_hi*m_hi + b_lo*m_lo + k*m_k with b_hi = b / mask_lo_extent
   const unsigned char* mask; long long m_hi, m_lo, m_k; int mask_lo_extent;
   // optional gate logits, addressed like q
@@ -51,15 +56,16 @@ struct AttnParams {
 
 int launch_attention(cudaStream_t stream, const AttnParams& p);
 
-// fp32-accurate mode: q, k, v, g are columns of ONE fp32 row-major buffer (row = batch * L + position, `ld`
+// fp32-accurate mode: q, g and k, v are columns of fp32 row-major buffers (row = batch * L + position, `ld` / `ld_kv`
 // floats per row, head h at col0 + h*d, no padding); bias fp32 [bias_batches][heads][lq][ldb]; the result is the
 // bf16 triple split [rows][6 * heads * d].
 struct AttnFp32Params {
   int batch, heads, lq, lk, d;
   const float *q, *k, *v, *g;  // same base pointer allowed; g may be null
-  long long ld;
+  long long ld;                // row stride of q and g
+  long long ld_kv;             // row stride of k and v (0: same as ld)
   int q_col0, k_col0, v_col0, g_col0;
-  const float* bias; long long ldb; int bias_div;
+  const float* bias; long long ldb; int bias_div; int bias_mod; int bias_head_major;  // as in AttnParams
   const unsigned char* mask; long long m_hi, m_lo, m_k; int mask_lo_extent;
   __nv_bfloat16* out6;
   const char* tag;

@@ -34,7 +34,11 @@ __global__ void __launch_bounds__(kFq) attention_fp32_kernel(const AttnFp32Param
   const int b_hi = b / p.mask_lo_extent, b_lo = b - b_hi * p.mask_lo_extent;
   const unsigned char* mrow =
       p.mask == nullptr ? nullptr : p.mask + static_cast<long long>(b_hi) * p.m_hi + static_cast<long long>(b_lo) * p.m_lo;
-  const float* bias_base = p.bias + (static_cast<long long>(b / p.bias_div) * p.heads + h) * static_cast<long long>(p.lq) * p.ldb;
+  const int bias_b = p.bias_mod > 0 ? (b / p.bias_div) * p.bias_mod + b % p.bias_mod : b / p.bias_div;
+  const long long bias_z = p.bias_head_major > 0 ? static_cast<long long>(h) * p.bias_head_major + bias_b
+                                                 : static_cast<long long>(bias_b) * p.heads + h;
+  const float* bias_base = p.bias + bias_z * static_cast<long long>(p.lq) * p.ldb;
+  const long long ld_kv = p.ld_kv > 0 ? p.ld_kv : p.ld;
 
   for (int k0 = 0; k0 < p.lk; k0 += kFk) {
     __syncthreads();
@@ -45,8 +49,8 @@ __global__ void __launch_bounds__(kFq) attention_fp32_kernel(const AttnFp32Param
       float kv = 0.f, vv = 0.f;
       if (key < p.lk) {
         const long long krow = static_cast<long long>(b) * p.lk + key;
-        kv = p.k[krow * p.ld + p.k_col0 + h * D + d];
-        vv = p.v[krow * p.ld + p.v_col0 + h * D + d];
+        kv = p.k[krow * ld_kv + p.k_col0 + h * D + d];
+        vv = p.v[krow * ld_kv + p.v_col0 + h * D + d];
       }
       s_k[kk][d] = kv;
       s_v[kk][d] = vv;

@@ -483,6 +483,95 @@ int launch_ln_fold_weights(cudaStream_t stream, const __nv_bfloat16* w, const fl
   return KFB_OK;
 }
 
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_float(float v) { return v; }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+
+// LayerNorm over a few channels followed by a projection to `nh` head values, one thread per position: the pair
+// bias of the atom windows (16 channels in, heads x layers out).  x [npos][C]; w [nh][C]; y [nh][npos] (head-major,
+// positions contiguous).  bf16 mode rounds the normalised value to bf16 as the reference's LayerNorm does and
+// accumulates in fp32; fp32 mode keeps everything in fp32.
+template <int C, typename T>
+__global__ void __launch_bounds__(256) window_bias_kernel(const T* __restrict__ x, const float* __restrict__ ln_w,
+                                                          const float* __restrict__ ln_b, const T* __restrict__ w,
+                                                          T* __restrict__ y, long long npos, int nh, float eps, int normalise) {
+  extern __shared__ float s_w[];  // [nh][C] fp32, then gamma[C], beta[C]
+  float* s_g = s_w + nh * C;
+  float* s_b = s_g + C;
+  for (int i = threadIdx.x; i < nh * C; i += blockDim.x) s_w[i] = to_float(w[i]);
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    s_g[i] = ln_w != nullptr ? ln_w[i] : 1.0f;
+    s_b[i] = ln_b != nullptr ? ln_b[i] : 0.0f;
+  }
+  __syncthreads();
+  const long long pos = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (pos >= npos) return;
+  float v[C];
+  const T* xr = x + pos * C;
+  constexpr int kVec = 16 / sizeof(T);
+#pragma unroll
+  for (int i = 0; i < C; i += kVec) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) v[i + j] = to_float(e[j]);
+  }
+  if (normalise) {
+    float mean = 0.f;
+#pragma unroll
+    for (int i = 0; i < C; ++i) mean += v[i];
+    mean *= 1.0f / C;
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < C; ++i) var += (v[i] - mean) * (v[i] - mean);
+    const float rstd = rsqrtf(var * (1.0f / C) + eps);
+#pragma unroll
+    for (int i = 0; i < C; ++i) v[i] = to_float(from_float<T>((v[i] - mean) * rstd * s_g[i] + s_b[i]));
+  }
+  for (int h = 0; h < nh; ++h) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < C; ++i) acc = fmaf(v[i], s_w[h * C + i], acc);
+    y[static_cast<long long>(h) * npos + pos] = from_float<T>(acc);
+  }
+}
+
+template <int C>
+static int launch_window_bias_c(cudaStream_t stream, const void* x, const float* ln_w, const float* ln_b, const void* w, void* y,
+                                long long npos, int nh, float eps, int normalise, int dtype) {
+  const size_t smem = (static_cast<size_t>(nh) * C + 2 * C) * sizeof(float);
+  const unsigned blocks = static_cast<unsigned>((npos + 255) / 256);
+  LaunchScope scope(stream, "window_bias");
+  if (dtype == KFB_BF16)
+    window_bias_kernel<C, __nv_bfloat16><<<blocks, 256, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ln_w, ln_b, static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+        npos, nh, eps, normalise);
+  else
+    window_bias_kernel<C, float><<<blocks, 256, smem, stream>>>(static_cast<const float*>(x), ln_w, ln_b,
+                                                                static_cast<const float*>(w), static_cast<float*>(y), npos, nh, eps,
+                                                                normalise);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+int launch_window_bias(cudaStream_t stream, const void* x, const float* ln_w, const float* ln_b, const void* w, void* y,
+                       long long npos, int c, int nh, float eps, int normalise, int dtype) {
+  KFB_CHECK_ARG(dtype == KFB_BF16 || dtype == KFB_FP32, "window_bias: dtype %d (bf16 or fp32)", dtype);
+  KFB_CHECK_ARG(nh >= 1 && nh * c <= 8192, "window_bias: %d heads x %d channels exceed the shared-memory weight table", nh, c);
+  KFB_CHECK_ARG(npos < (1ll << 31) * 256, "window_bias: too many positions");
+  if (npos == 0) return KFB_OK;
+  switch (c) {
+    case 16: return launch_window_bias_c<16>(stream, x, ln_w, ln_b, w, y, npos, nh, eps, normalise, dtype);
+    case 32: return launch_window_bias_c<32>(stream, x, ln_w, ln_b, w, y, npos, nh, eps, normalise, dtype);
+    case 64: return launch_window_bias_c<64>(stream, x, ln_w, ln_b, w, y, npos, nh, eps, normalise, dtype);
+    default:
+      set_error("window_bias: %d channels not supported (16, 32 or 64)", c);
+      return KFB_ERR_UNSUPPORTED;
+  }
+}
+
 int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, const float* w, const float* b, int batch,
                         long long npos, int c, long long chan_stride, long long batch_stride, float eps, int in_dtype,
                         int split_out) {

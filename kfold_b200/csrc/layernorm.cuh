@@ -34,4 +34,9 @@ int launch_cm_stats(cudaStream_t stream, const __nv_bfloat16* t, float2* stats, 
 int launch_ln_fold_weights(cudaStream_t stream, const __nv_bfloat16* w, const float* gamma, const float* beta, __nv_bfloat16* wf,
                            float* s1, float* s0, int n, int k);
 
+// LayerNorm over c (16, 32 or 64) channels and projection to nh values per position: x [npos][c], w [nh][c] of `dtype`
+// (KFB_BF16 or KFB_FP32), y [nh][npos] of the same type.  normalise == 0: projection only.
+int launch_window_bias(cudaStream_t stream, const void* x, const float* ln_w, const float* ln_b, const void* w, void* y,
+                       long long npos, int c, int nh, float eps, int normalise, int dtype);
+
 }  // namespace kfb

@@ -49,6 +49,35 @@ size_t carve_apb(ApbWs& w, void* base, int batch, int l, int c, int heads) {
   return cv.off;
 }
 
+// cross attention (queries and keys from different tensors): [q | g] of the query rows, k and v^T of the key rows
+struct ApbCrossWs {
+  __nv_bfloat16 *qg, *kk, *vt, *og;
+};
+size_t carve_apb_cross(ApbCrossWs& w, void* base, int batch, int lq, int lk, int c, int heads) {
+  Carver cv(base);
+  const size_t rows_q = static_cast<size_t>(batch) * lq, rows_k = static_cast<size_t>(batch) * lk;
+  const int hdp = heads * dpad_of(c / heads);
+  w.qg = cv.take<__nv_bfloat16>(rows_q * 2 * hdp);
+  w.kk = cv.take<__nv_bfloat16>(rows_k * hdp);
+  w.vt = cv.take<__nv_bfloat16>(rows_k * hdp);
+  w.og = cv.take<__nv_bfloat16>(rows_q * c);
+  return cv.off;
+}
+struct ApbCrossWsPrecise {
+  __nv_bfloat16 *xq6, *xk6, *og6;
+  float *qg, *kv;
+};
+size_t carve_apb_cross_precise(ApbCrossWsPrecise& w, void* base, int batch, int lq, int lk, int c) {
+  Carver cv(base);
+  const size_t rows_q = static_cast<size_t>(batch) * lq, rows_k = static_cast<size_t>(batch) * lk;
+  w.xq6 = cv.take<__nv_bfloat16>(rows_q * 6 * c);
+  w.xk6 = cv.take<__nv_bfloat16>(rows_k * 6 * c);
+  w.og6 = cv.take<__nv_bfloat16>(rows_q * 6 * c);
+  w.qg = cv.take<float>(rows_q * 2 * c);
+  w.kv = cv.take<float>(rows_k * 2 * c);
+  return cv.off;
+}
+
 // ------------------------------------------------------------------------------------------------
 // fp32-accurate variants (KFB_FP32_PRECISE): split-operand GEMMs around the fp32 attention kernel.
 // ------------------------------------------------------------------------------------------------
@@ -617,6 +646,192 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     GemmOperandA a = {w.og, c, lc, lc * gate_share};
     GemmOperandB b = {w_out, c, 0};
     KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "apb_out_proj"));
+  }
+  return KFB_OK;
+}
+
+KFB_API size_t kfb_apb_cross_workspace_bytes(int batch, int lq, int lk, int c, int heads) {
+  ApbCrossWs w;
+  return carve_apb_cross(w, nullptr, batch, lq, lk, c, heads);
+}
+
+KFB_API size_t kfb_apb_cross_workspace_bytes_precise(int batch, int lq, int lk, int c) {
+  ApbCrossWsPrecise w;
+  return carve_apb_cross_precise(w, nullptr, batch, lq, lk, c);
+}
+
+KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
+                              const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
+                              const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
+                              void* workspace, size_t workspace_bytes, int batch, int lq, int lk, int c, int heads,
+                              int bias_div, int bias_mod, int bias_head_major, int out_dtype, void* stream_) {
+  KFB_CHECK_ARG(x_q && x_k && pair_bias && mask && w_q_packed && w_kv_packed && w_out && out && workspace,
+                "apb_cross: null pointer");
+  KFB_CHECK_ARG(is_dtype(out_dtype), "apb_cross: bad dtype %d", out_dtype);
+  KFB_CHECK_ARG(batch >= 1 && lq >= 8 && lq % 8 == 0 && lk >= 8 && lk % 8 == 0,
+                "apb_cross: Lq=%d and Lk=%d must be positive multiples of 8 (pad in the caller)", lq, lk);
+  KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "apb_cross: c=%d heads=%d", c, heads);
+  KFB_CHECK_ARG(bias_div >= 1 && bias_mod >= 0 && bias_head_major >= 0, "apb_cross: bias_div %d bias_mod %d bias_head_major %d",
+                bias_div, bias_mod, bias_head_major);
+  const int d = c / heads;
+  KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "apb_cross: head dim %d not in {16, 24, ..., 64}", d);
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "apb_cross: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  const long long rows_q = static_cast<long long>(batch) * lq, rows_k = static_cast<long long>(batch) * lk;
+  if (out_gate == nullptr || gate_rows <= 0) gate_rows = rows_q;
+  KFB_CHECK_ARG(rows_q % gate_rows == 0 && gate_rows < (1ll << 31), "apb_cross: %lld query rows are not a multiple of gate_rows %lld",
+                rows_q, gate_rows);
+  const int gate_reps = static_cast<int>(rows_q / gate_rows);
+  if (out_dtype == KFB_FP32_PRECISE) {
+    ApbCrossWsPrecise wp;
+    const size_t need_p = carve_apb_cross_precise(wp, workspace, batch, lq, lk, c);
+    KFB_CHECK_ARG(workspace_bytes >= need_p, "apb_cross: workspace %zu < %zu bytes", workspace_bytes, need_p);
+    const long long c6 = 6ll * c;
+    KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x_q), wp.xq6, nullptr, nullptr, rows_q, c, c, 0.f, 0));
+    KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x_k), wp.xk6, nullptr, nullptr, rows_k, c, c, 0.f, 0));
+    for (int side = 0; side < 2; ++side) {
+      GemmParams p = {};
+      p.n_extent = static_cast<int>(side == 0 ? rows_q : rows_k);
+      p.o_extent = 1;
+      p.batch = 1;
+      p.n_cols = 2 * c;
+      p.k_extent = 6 * c;
+      p.precise = 1;
+      p.nseg = 1;
+      p.seg[0] = row_major_seg(side == 0 ? wp.qg : wp.kv, 2 * c, 2 * c, 0, 0, 1);
+      p.col_bias = side == 0 ? q_bias : nullptr;
+      GemmOperandA a = {side == 0 ? wp.xq6 : wp.xk6, c6, 0, 0};
+      GemmOperandB b = {side == 0 ? w_q_packed : w_kv_packed, c6, 0};
+      KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, side == 0 ? "apb_cross_q_proj_precise" : "apb_cross_kv_proj_precise"));
+    }
+    {
+      AttnFp32Params p = {};
+      p.batch = batch;
+      p.heads = heads;
+      p.lq = lq;
+      p.lk = lk;
+      p.d = d;
+      p.q = p.g = wp.qg;
+      p.k = p.v = wp.kv;
+      p.ld = 2 * c;
+      p.ld_kv = 2 * c;
+      p.q_col0 = 0; p.g_col0 = c; p.k_col0 = 0; p.v_col0 = c;
+      p.bias = static_cast<const float*>(pair_bias); p.ldb = lk; p.bias_div = bias_div; p.bias_mod = bias_mod; p.bias_head_major = bias_head_major;
+      p.mask = mask;
+      p.mask_lo_extent = 1;
+      p.m_hi = lk;
+      p.m_lo = 0;
+      p.m_k = 1;
+      p.out6 = wp.og6;
+      p.tag = "apb_cross_attention_fp32";
+      KFB_TRY(launch_attention_fp32(stream, p));
+    }
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(gate_rows);
+    p.o_extent = gate_reps;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = 6 * c;
+    p.precise = 1;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, gate_rows * c, 0, 1);
+    p.col_bias = out_bias;
+    p.resid = resid;
+    if (out_gate != nullptr) {
+      p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // fp32 logits in this mode; query row r uses row r % gate_rows
+      p.g_col = 1;
+      p.g_n = c;
+      p.g_o = 0;
+      p.g_b = 0;
+    }
+    GemmOperandA a = {wp.og6, c6, gate_rows * c6, 0};
+    GemmOperandB b = {w_out, c6, 0};
+    return launch_gemm_bf16(stream, a, b, p, 0, "apb_cross_out_proj_precise");
+  }
+  const int dp = dpad_of(d), hdp = heads * dp;
+  ApbCrossWs w;
+  const size_t need = carve_apb_cross(w, workspace, batch, lq, lk, c, heads);
+  KFB_CHECK_ARG(workspace_bytes >= need, "apb_cross: workspace %zu < %zu bytes", workspace_bytes, need);
+  {
+    // query side: [q * log2(e)/sqrt(d) | gate logits]
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(rows_q);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = 2 * hdp;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(w.qg, 2 * hdp, 2 * hdp, 0, 0, 0);
+    p.col_bias = q_bias;
+    GemmOperandA a = {x_q, c, 0, 0};
+    GemmOperandB b = {w_q_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "apb_cross_q_proj"));
+  }
+  {
+    // key side: k position-major, v transposed per batch entry (keys contiguous)
+    GemmParams p = {};
+    p.n_extent = lk;
+    p.o_extent = batch;
+    p.batch = 1;
+    p.n_cols = 2 * hdp;
+    p.k_extent = c;
+    p.nseg = 2;
+    p.seg[0] = row_major_seg(w.kk, hdp, hdp, static_cast<long long>(lk) * hdp, 0, 0, 0);
+    EpiSeg& sv = p.seg[1];
+    sv = {};
+    sv.col_begin = hdp;
+    sv.ncols = hdp;
+    sv.dst = w.vt;
+    sv.s_col = lk;
+    sv.s_n = 1;
+    sv.s_o = static_cast<long long>(hdp) * lk;
+    GemmOperandA a = {x_k, c, static_cast<long long>(lk) * c, 0};
+    GemmOperandB b = {w_kv_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "apb_cross_kv_proj"));
+  }
+  {
+    AttnParams p = {};
+    p.batch = batch;
+    p.heads = heads;
+    p.lq = lq;
+    p.lk = lk;
+    p.d = d;
+    p.dpad = dp;
+    p.q = w.qg; p.ldq = 2 * hdp; p.q_col0 = 0;
+    p.g = w.qg; p.ldg = 2 * hdp; p.g_col0 = hdp;
+    p.k = w.kk; p.ldk = hdp; p.k_col0 = 0;
+    p.vt = w.vt; p.ldv = lk;
+    p.bias = pair_bias; p.ldb = lk; p.bias_div = bias_div; p.bias_mod = bias_mod; p.bias_head_major = bias_head_major;
+    p.mask = mask;
+    p.mask_lo_extent = 1;
+    p.m_hi = lk;
+    p.m_lo = 0;
+    p.m_k = 1;
+    p.out = w.og; p.ldo = c;
+    p.tag = "apb_cross_attention";
+    KFB_TRY(launch_attention(stream, p));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(gate_rows);
+    p.o_extent = gate_reps;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, gate_rows * c, 0, out_dtype == KFB_FP32);
+    p.col_bias = out_bias;
+    p.resid = resid;
+    if (out_gate != nullptr) {
+      p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // query row r uses logits row r % gate_rows
+      p.g_col = 1;
+      p.g_n = c;
+      p.g_o = 0;
+      p.g_b = 0;
+    }
+    GemmOperandA a = {w.og, c, gate_rows * c, 0};
+    GemmOperandB b = {w_out, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "apb_cross_out_proj"));
   }
   return KFB_OK;
 }

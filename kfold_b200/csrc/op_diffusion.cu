@@ -155,4 +155,14 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
   return KFB_OK;
 }
 
+KFB_API int kfb_window_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
+                                long long positions, int c, int heads, float eps, int normalise, int dtype, void* stream_) {
+  KFB_CHECK_ARG(z && w && bias_out, "window_bias: null pointer");
+  KFB_CHECK_ARG(is_dtype(dtype), "window_bias: bad dtype %d", dtype);
+  KFB_CHECK_ARG(positions >= 0 && heads >= 1, "window_bias: positions %lld heads %d", positions, heads);
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(z) & 15) == 0, "window_bias: z must be 16-byte aligned");
+  return launch_window_bias(as_stream(stream_), z, ln_w, ln_b, w, bias_out, positions, c, heads, eps, normalise,
+                            dtype == KFB_FP32_PRECISE ? KFB_FP32 : dtype);
+}
+
 }  // extern "C"

@@ -279,6 +279,136 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
     return out[:, :l].reshape(*lead, l, c).to(want)
 
 
+def window_bias(z: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | None, w: torch.Tensor,
+                eps: float = 1e-5, normalise: bool = True) -> torch.Tensor:
+    """Pair bias of the atom windows for all blocks of a local transformer at once
+    (model/layers/folding/diffusion_transformer.py:496 and :590-591 with the blocks' weights stacked).
+    z (..., Lq, Lk, c_z) bf16 or float32; w (heads_total, c_z) of the same dtype -> (heads_total, ..., Lq, Lk).
+    ``normalise=False`` skips the LayerNorm (z already normalised): projection only."""
+    _require_cuda(z, w)
+    c = z.shape[-1]
+    if z.dtype not in (torch.bfloat16, torch.float32) or w.dtype != z.dtype:
+        raise TypeError("window_bias: z and w must both be bfloat16 or both float32")
+    z2 = z.reshape(-1, c).contiguous()
+    nh = w.shape[0]
+    out = torch.empty((nh,) + tuple(z.shape[:-1]), dtype=z.dtype, device=z.device)
+    with torch.cuda.device(z.device):
+        L.check(L.lib().kfb_window_bias_fwd(L.ptr(z2), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w.contiguous()), L.ptr(out), z2.shape[0], c,
+                                            nh, eps, 1 if normalise else 0, L.dtype_code(z.dtype), L.stream_ptr()))
+    return out
+
+
+def attention_pair_bias_cross(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor, packed: dict,
+                              bias_div: int = 1, bias_mod: int = 0, bias_head_major: bool = False, out_dtype=None,
+                              out_gate: torch.Tensor | None = None, resid: torch.Tensor | None = None) -> torch.Tensor:
+    """Gated cross attention with pair bias on already-normalised inputs (model/primitives/attention.py:28-94 with
+    x_q and x_k different tensors, as CrossAttentionPairBias.forward calls it on the atom windows).
+
+    Flattened form: x_q (batch, Lq, c); x_k (batch, Lk, c); mask (batch, Lk); Lq, Lk multiples of 8;
+    pair_bias (bias batches, H, Lq, Lk), or (H, bias batches, Lq, Lk) with ``bias_head_major``.  Batch entry b uses
+    bias batch b // bias_div, or with ``bias_mod`` > 0 (batch ordered (group, sample, window), bias_mod windows,
+    bias_div = samples * windows) (b // bias_div) * bias_mod + b % bias_mod.
+    ``out_gate``: logits (gate_rows, c); query row r is multiplied by sigmoid(out_gate[r % gate_rows]).
+    ``resid``: (batch, Lq, c), added.  With a float32 packing every tensor is float32."""
+    _require_cuda(x_q, x_k, pair_bias, mask)
+    batch, lq, c = x_q.shape
+    lk = x_k.shape[1]
+    heads = packed["heads"]
+    precise = bool(packed.get("precise"))
+    act = torch.float32 if precise else torch.bfloat16
+    if x_k.shape[0] != batch or x_k.shape[2] != c or tuple(mask.shape) != (batch, lk):
+        raise ValueError(f"attention_pair_bias_cross: x_q {tuple(x_q.shape)}, x_k {tuple(x_k.shape)}, mask {tuple(mask.shape)}")
+    if lq % 8 or lk % 8:
+        raise ValueError("attention_pair_bias_cross: Lq and Lk must be multiples of 8")
+    nbb = pair_bias.shape[1] if bias_head_major else pair_bias.shape[0]
+    want_nbb = (batch + bias_div - 1) // bias_div * (bias_mod if bias_mod > 0 else 1)
+    exp_shape = (heads, nbb, lq, lk) if bias_head_major else (nbb, heads, lq, lk)
+    if tuple(pair_bias.shape) != exp_shape or nbb < want_nbb:
+        raise ValueError(f"attention_pair_bias_cross: pair_bias {tuple(pair_bias.shape)}, expected {exp_shape} with at least "
+                         f"{want_nbb} bias batches")
+    xq, xk = x_q.to(act).contiguous(), x_k.to(act).contiguous()
+    pb = pair_bias.to(act).contiguous()
+    mb = mask.to(torch.bool).contiguous().view(torch.uint8)
+    gate, gate_rows = None, 0
+    if out_gate is not None:
+        gate = out_gate.reshape(-1, c).to(act).contiguous()
+        gate_rows = gate.shape[0]
+    res = None
+    if resid is not None:
+        res = resid.reshape(batch, lq, c)
+        res = (res.float() if precise else res).contiguous()
+    want = out_dtype or (resid.dtype if resid is not None else x_q.dtype)
+    out = torch.empty(batch, lq, c, dtype=torch.float32 if precise else want, device=x_q.device)
+    if res is not None and res.dtype != out.dtype:
+        res = res.to(out.dtype)
+    lib = L.lib()
+    with torch.cuda.device(x_q.device):
+        need = (lib.kfb_apb_cross_workspace_bytes_precise(batch, lq, lk, c) if precise
+                else lib.kfb_apb_cross_workspace_bytes(batch, lq, lk, c, heads))
+        ws = _workspace(x_q.device, need)
+        L.check(lib.kfb_apb_cross_fwd(L.ptr(xq), L.ptr(xk), L.ptr(pb), L.ptr(mb), L.ptr(packed["w_q"]), L.ptr(packed["q_bias"]),
+                                      L.ptr(packed["w_kv"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
+                                      gate_rows, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lq, lk, c, heads,
+                                      bias_div, bias_mod, nbb if bias_head_major else 0,
+                                      L.KFB_FP32_PRECISE if precise else L.dtype_code(out.dtype), L.stream_ptr()))
+    return out.to(want)
+
+
+def attention_pair_bias_cross_bcast(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor,
+                                    packed: dict, out_dtype=None, out_gate: torch.Tensor | None = None,
+                                    resid: torch.Tensor | None = None) -> torch.Tensor:
+    """The reference's calling convention (model/primitives/attention.py:28-60): x_q (*, Lq, c), x_k (*, Lk, c),
+    pair_bias broadcastable to (*, H, Lq, Lk), mask broadcastable to (*, Lk).  A bias whose missing or size-1 leading
+    dimensions form one block (the sample dimension of the sampler: bias (B, 1, W, H, Lq, Lk) against x (B, S, W, ...))
+    is shared without being expanded; any other broadcast pattern is expanded.  ``out_gate``: logits broadcastable to
+    x_q's shape; the result is multiplied by their sigmoid.  ``resid``: tensor like x_q that is added."""
+    lead = tuple(x_q.shape[:-2])
+    lq, c = x_q.shape[-2:]
+    lk = x_k.shape[-2]
+    heads = packed["heads"]
+    batch = 1
+    for d in lead:
+        batch *= d
+    pl = tuple(pair_bias.shape[:-3])
+    pl = (1,) * (len(lead) - len(pl)) + pl
+    # split the leading dims as (group..., shared..., window...): bias has the group and window dims, 1 in the shared ones
+    i = 0
+    while i < len(lead) and pl[i] == lead[i]:
+        i += 1
+    j = i
+    while j < len(lead) and pl[j] == 1:
+        j += 1
+    if all(pl[k] == lead[k] for k in range(j, len(lead))):
+        shared = 1
+        for d in lead[i:j]:
+            shared *= d
+        windows = 1
+        for d in lead[j:]:
+            windows *= d
+        pb = pair_bias.reshape(-1, heads, lq, lk)
+        bias_div, bias_mod = shared * windows, (windows if shared > 1 and windows > 1 else 0)
+        if bias_mod == 0:
+            bias_div = shared if windows == 1 else 1
+    else:
+        pb = pair_bias.expand(*lead, heads, lq, lk).reshape(batch, heads, lq, lk)
+        bias_div, bias_mod = 1, 0
+    lqp, lkp = (lq + 7) // 8 * 8, (lk + 7) // 8 * 8
+    xq = x_q.reshape(batch, lq, c)
+    xk = x_k.expand(*lead, lk, c).reshape(batch, lk, c)
+    mb = mask.to(torch.bool).expand(*lead, lk).reshape(batch, lk)
+    gate = None if out_gate is None else out_gate.expand(*lead, lq, c).reshape(batch, lq, c)
+    res = None if resid is None else resid.reshape(batch, lq, c)
+    if lqp != lq or lkp != lk:
+        pad = torch.nn.functional.pad
+        xq, xk = pad(xq, (0, 0, 0, lqp - lq)), pad(xk, (0, 0, 0, lkp - lk))
+        pb, mb = pad(pb, (0, lkp - lk, 0, lqp - lq)), pad(mb, (0, lkp - lk))
+        gate = None if gate is None else pad(gate, (0, 0, 0, lqp - lq))
+        res = None if res is None else pad(res, (0, 0, 0, lqp - lq))
+    out = attention_pair_bias_cross(xq, xk, pb, mb, packed, bias_div=bias_div, bias_mod=bias_mod, out_dtype=out_dtype or x_q.dtype,
+                                    out_gate=gate, resid=res)
+    return out[:, :lq].reshape(*lead, lq, c)
+
+
 def transition(x: torch.Tensor, packed: dict, eps: float = 1e-5, residual: bool = False) -> torch.Tensor:
     """Transition layer (model/layers/folding/transition.py:48-68).  x (..., C)."""
     _require_cuda(x)

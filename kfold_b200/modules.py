@@ -418,6 +418,237 @@ class CachedGlobalTransformerStack(nn.Module):
 
 
 # --------------------------------------------------------------------------------------------
+# atom-level local transformer: windows of 32 queries attending 128 keys
+# --------------------------------------------------------------------------------------------
+WINDOW_Q, WINDOW_K = 32, 128
+
+
+def build_atom_to_qk_fn(length: int, device):
+    """Window indexing of the local attention (model/layers/folding/utils.py:97-188): window w holds queries
+    [32 w, 32 w + 32) and keys [32 w - 48, 32 w + 80); keys outside [0, length) are zero-filled.  Returns
+    fn(x, dim) -> (x_q, x_k) that unflattens dimension `dim` into (W, 32) and gathers it into (W, 128)."""
+    if length % WINDOW_Q != 0:
+        raise ValueError("Length must be divisible by 32")
+    windows = length // WINDOW_Q
+    idx = torch.arange(windows, device=device)[:, None] * WINDOW_Q - 48 + torch.arange(WINDOW_K, device=device)[None, :]
+    pad = (idx < 0) | (idx >= length)
+    idx = idx.clamp(0, length - 1).reshape(-1)
+
+    def to_qk(x: torch.Tensor, dim: int):
+        dim = dim % x.ndim
+        x_q = x.unflatten(dim, (windows, WINDOW_Q))
+        x_k = x.index_select(dim, idx).unflatten(dim, (windows, WINDOW_K))
+        shape = [1] * x_k.ndim
+        shape[dim], shape[dim + 1] = windows, WINDOW_K
+        return x_q, x_k.masked_fill(pad.view(shape), 0)
+
+    return to_qk
+
+
+def _bias_sharing(lead: tuple, bias_lead: tuple):
+    """How a bias with leading dims `bias_lead` (1 = broadcast) is shared by a batch with leading dims `lead` ordered
+    (group..., shared..., window...): (bias_div, bias_mod) for the kernels, or None when the pattern is not of that form."""
+    bl = (1,) * (len(lead) - len(bias_lead)) + tuple(bias_lead)
+    i = 0
+    while i < len(lead) and bl[i] == lead[i]:
+        i += 1
+    j = i
+    while j < len(lead) and bl[j] == 1:
+        j += 1
+    if any(bl[k] != lead[k] for k in range(j, len(lead))):
+        return None
+    shared = windows = 1
+    for d in lead[i:j]:
+        shared *= d
+    for d in lead[j:]:
+        windows *= d
+    if shared > 1 and windows > 1:
+        return shared * windows, windows
+    return (shared if windows == 1 else 1), 0
+
+
+class CrossAttentionPairBias(nn.Module, _PackedMixin):
+    """Pair-bias cross attention of the atom windows (model/layers/folding/attention_pair_bias.py:161-260): AdaLN (or
+    LayerNorm) prologues for the query and the key side, attention with `call_site="diffusion_local"`, and the
+    sigmoid(Linear(s_q)) output gate."""
+
+    def __init__(self, channel_a: int, num_heads: int, channel_s: int | None, inf: float = 1e9, kernel_backend: str = "b200"):
+        super().__init__()
+        if inf != 1e9:
+            raise ValueError("the kernel's key-mask offset is fixed at 1e9 (the reference default)")
+        assert channel_a % num_heads == 0
+        self.channel_a, self.num_heads, self.head_dim, self.inf = channel_a, num_heads, channel_a // num_heads, inf
+        self.kernel_backend = kernel_backend
+        self.use_single_conditioning = channel_s is not None
+        self.linear_q = Linear(channel_a, channel_a)
+        self.linear_k = LinearNoBias(channel_a, channel_a)
+        self.linear_v = LinearNoBias(channel_a, channel_a)
+        self.linear_g = LinearNoBias(channel_a, channel_a)
+        self.linear_out = LinearNoBias(channel_a, channel_a)
+        if self.use_single_conditioning:
+            self.adaln_a_q = AdaLN(channel_a, channel_s)
+            self.adaln_a_k = AdaLN(channel_a, channel_s)
+            self.linear_ada_out = Linear(channel_s, channel_a)
+        else:
+            self.layernorm_a_q = LayerNorm(channel_a, create_offset=True)
+            self.layernorm_a_k = LayerNorm(channel_a, create_offset=True)
+        self._ada_w = None
+        self._ada_key = None
+
+    _ada_out = SelfAttentionPairBias._ada_out
+
+    def _cross_packed(self, device, precise: bool = False):
+        keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight", "linear_out.weight")
+        return self._packed(device, torch.float32 if precise else torch.bfloat16,
+                            lambda sd, dev: packing.pack_apb_cross({k: sd[k] for k in keys}, self.num_heads, dev, precise=precise))
+
+    def normed_inputs(self, a: torch.Tensor, s: torch.Tensor | None, precise: bool):
+        """Query-side and key-side prologues on the un-windowed rows a (..., L, c_a), s (..., L, c_s), and the logits of
+        the output gate (or None).  Both prologues are row-wise, so windows can be cut afterwards."""
+        if self.use_single_conditioning:
+            assert s is not None
+            share = _sample_share(a, s)
+            af = a.float() if precise else a
+            xq = F.adaln(af, self.adaln_a_q.gate_shift(s, precise), share)
+            xk = F.adaln(af, self.adaln_a_k.gate_shift(s, precise), share)
+            w_ada, b_ada = self._ada_out(a.device, precise)
+            gate = F.linear_fp32(s.float(), w_ada, b_ada) if precise else F.linear(s, w_ada, b_ada)
+            return xq, xk, gate
+        assert s is None
+        dt = torch.float32 if precise else torch.bfloat16
+        af = a.float() if precise else a
+        lq, lk = self.layernorm_a_q, self.layernorm_a_k
+        return (F.layer_norm(af, lq.weight, lq.bias, lq.eps, out_dtype=dt), F.layer_norm(af, lk.weight, lk.bias, lk.eps, out_dtype=dt),
+                None)
+
+    @torch.compiler.disable
+    def forward(self, a_q: torch.Tensor, a_k: torch.Tensor, s_q: torch.Tensor | None, s_k: torch.Tensor | None,
+                pair_bias: torch.Tensor, mask: torch.Tensor, residual: bool = False) -> torch.Tensor:
+        """The reference's signature on windowed tensors: a_q (..., W, Lq, c_a), a_k (..., W, Lk, c_a), s_q / s_k alike with
+        c_s, pair_bias (..., W, H, Lq, Lk), mask (..., W, Lk) -> (..., W, Lq, c_a).  With ``residual`` the result is
+        a_q + update (fused into the last kernel)."""
+        _check_inference(a_q)
+        precise = _is_precise(compute_dtype(a_q), "CrossAttentionPairBias")
+        pk = self._cross_packed(a_q.device, precise)
+        with torch.autocast(a_q.device.type, enabled=False):
+            flat = lambda t: None if t is None else t.flatten(-3, -2)
+            if self.use_single_conditioning:
+                assert s_q is not None and s_k is not None
+                aqf, akf, sqf, skf = flat(a_q), flat(a_k), flat(s_q), flat(s_k)
+                cast = (lambda t: t.float()) if precise else (lambda t: t)
+                xq = F.adaln(cast(aqf), self.adaln_a_q.gate_shift(sqf, precise), _sample_share(aqf, sqf)).view(a_q.shape)
+                xk = F.adaln(cast(akf), self.adaln_a_k.gate_shift(skf, precise), _sample_share(akf, skf)).view(a_k.shape)
+            else:
+                assert s_q is None and s_k is None
+                dt = torch.float32 if precise else torch.bfloat16
+                lq, lk = self.layernorm_a_q, self.layernorm_a_k
+                xq = F.layer_norm(a_q.float() if precise else a_q, lq.weight, lq.bias, lq.eps, out_dtype=dt)
+                xk = F.layer_norm(a_k.float() if precise else a_k, lk.weight, lk.bias, lk.eps, out_dtype=dt)
+            gate = None
+            if self.use_single_conditioning:
+                w_ada, b_ada = self._ada_out(a_q.device, precise)
+                gate = F.linear_fp32(s_q.float(), w_ada, b_ada) if precise else F.linear(s_q, w_ada, b_ada)
+            return F.attention_pair_bias_cross_bcast(xq, xk, pair_bias, mask, pk, out_dtype=a_q.dtype, out_gate=gate,
+                                                     resid=a_q if residual else None)
+
+
+class LocalTransformerBlock(nn.Module):
+    """model/layers/folding/diffusion_transformer.py:515-597: a_q += attention(a_q, a_k, s_q, s_k, bias(z), mask);
+    a_q += transition(a_q, s_q)."""
+
+    def __init__(self, channel_a: int, channel_s: int, channel_z: int, num_heads: int, kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend = kernel_backend
+        self.linear_z_to_bias = LinearNoBias(channel_z, num_heads)
+        self.attention = CrossAttentionPairBias(channel_a, num_heads, channel_s)
+        self.transition = ConditionedTransitionBlock(channel_a, channel_s)
+
+    @torch.compiler.disable
+    def forward(self, a_q: torch.Tensor, a_k: torch.Tensor, s_q: torch.Tensor, s_k: torch.Tensor, z: torch.Tensor,
+                mask: torch.Tensor) -> torch.Tensor:
+        """Reference signature: windowed a_q / a_k / s_q / s_k, normalised z (..., W, Lq, Lk, c_z), mask (..., W, Lk)."""
+        _check_inference(a_q)
+        precise = _is_precise(compute_dtype(a_q), "LocalTransformerBlock")
+        with torch.autocast(a_q.device.type, enabled=False):
+            dt = torch.float32 if precise else torch.bfloat16
+            w = self.linear_z_to_bias.weight.detach().to(z.device, dt).contiguous()
+            # z arrives normalised: projection only; (H, ..., W, Lq, Lk) -> (..., W, H, Lq, Lk)
+            bias = F.window_bias(z.to(dt), None, None, w, normalise=False).movedim(0, -3)
+        a_q = self.attention(a_q, a_k, s_q, s_k, bias, mask, residual=True)
+        shape = a_q.shape
+        out = self.transition(a_q.flatten(-3, -2), s_q.flatten(-3, -2), residual=True)
+        return out.view(shape)
+
+
+class LocalTransformerStack(nn.Module):
+    """model/layers/folding/diffusion_transformer.py:419-512.  The whole stack works on the un-windowed atoms: the
+    prologues, the query-side projection, the output gate and the transition are row-wise, so only the key side is
+    gathered into windows; the pair biases of all blocks come from one pass over z."""
+
+    def __init__(self, channel_a: int, channel_s: int, channel_z: int, num_heads: int, num_blocks: int,
+                 kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend = kernel_backend
+        self.num_heads = num_heads
+        self.layernorm_z = LayerNorm(channel_z, create_offset=False)
+        self.blocks = nn.ModuleList(
+            [LocalTransformerBlock(channel_a, channel_s, channel_z, num_heads) for _ in range(num_blocks)])
+        self._bias_w = None
+        self._bias_w_key = None
+
+    def _stacked_bias_weights(self, device, dt):
+        ws = [b.linear_z_to_bias.weight for b in self.blocks]
+        key = (device, dt) + tuple(v for w in ws for v in (w.data_ptr(), None if torch.is_inference(w) else w._version))
+        if self._bias_w_key != key:
+            self._bias_w = torch.cat([w.detach() for w in ws], dim=0).to(device, dt).contiguous()
+            self._bias_w_key = key
+        return self._bias_w
+
+    @torch.compiler.disable
+    def forward(self, a: torch.Tensor, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """a (*, L, c_a); s (*, L, c_s) (leading dims may be 1 where a's are not); z (*, W, 32, 128, c_z) likewise;
+        mask (*, L) -> (*, L, c_a)."""
+        _check_inference(a)
+        precise = _is_precise(compute_dtype(a), "LocalTransformerStack")
+        dt = torch.float32 if precise else torch.bfloat16
+        length, c = a.shape[-2:]
+        lead = tuple(a.shape[:-2])
+        to_qk = build_atom_to_qk_fn(length, a.device)
+        windows = length // WINDOW_Q
+        h = self.num_heads
+        with torch.autocast(a.device.type, enabled=False):
+            _, mask_k = to_qk(mask.to(torch.bool), -1)                                  # (*, W, 128)
+            mask_k = mask_k.expand(*lead, windows, WINDOW_K).reshape(-1, WINDOW_K)
+            ln = self.layernorm_z
+            bias_all = F.window_bias(z.to(dt), None if ln.weight is None else ln.weight.detach().float(),
+                                     None if ln.bias is None else ln.bias.detach().float(),
+                                     self._stacked_bias_weights(a.device, dt), ln.eps)      # (blocks*H, *z_lead, W, 32, 128)
+            z_lead = tuple(z.shape[:-3])                                                 # includes the window dim
+            sharing = _bias_sharing(lead + (windows,), z_lead)
+            if sharing is None:
+                bias_all = bias_all.expand(bias_all.shape[0], *lead, windows, WINDOW_Q, WINDOW_K)
+                sharing = (1, 0)
+            bias_all = bias_all.reshape(len(self.blocks), h, -1, WINDOW_Q, WINDOW_K)
+            batch = mask_k.shape[0]
+            for i, blk in enumerate(self.blocks):
+                att = blk.attention
+                xq, xk_flat, gate = att.normed_inputs(a, s, precise)
+                _, xk = to_qk(xk_flat, -2)                                              # (*, W, 128, c)
+                if gate is not None:
+                    gl = tuple(gate.shape[:-2])
+                    while gl and gl[0] == 1:
+                        gl = gl[1:]
+                    if gl != lead[len(lead) - len(gl):]:
+                        gate = gate.expand(*lead, length, c)
+                a = F.attention_pair_bias_cross(
+                    xq.reshape(batch, WINDOW_Q, c), xk.reshape(batch, WINDOW_K, c), bias_all[i], mask_k,
+                    att._cross_packed(a.device, precise), bias_div=sharing[0], bias_mod=sharing[1], bias_head_major=True,
+                    out_dtype=a.dtype, out_gate=gate, resid=a).view(*lead, length, c)
+                a = blk.transition(a, s, residual=True)
+        return a
+
+
+# --------------------------------------------------------------------------------------------
 # blocks
 # --------------------------------------------------------------------------------------------
 class TriangularBlock(nn.Module):

@@ -171,6 +171,49 @@ def pack_apb(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = 
     }
 
 
+def pack_apb_cross(w: dict, heads: int, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
+    """Projections of AttentionPairBias for cross attention (queries and keys from different tensors,
+    model/primitives/attention.py:75-83): the query side [q * log2(e) / sqrt(D) (+ bias) | g] and the key side [k | v]
+    as two matrices, heads padded; the fp32-accurate packing keeps the heads unpadded, scales q by 1 / sqrt(D) only
+    and stores bf16 triple splits."""
+    c = int(w["linear_q.weight"].shape[1])
+    d = c // heads
+    ob = w.get("linear_out.bias")
+    if precise:
+        qs = d ** -0.5
+        g = lambda k, s=1.0: w[k].detach().float() * s
+        qb = torch.zeros(2 * c, dtype=torch.float32)
+        if w.get("linear_q.bias") is not None:
+            qb[:c] = w["linear_q.bias"].detach().float().cpu() * qs
+        if w.get("linear_g.bias") is not None:
+            qb[c:] = w["linear_g.bias"].detach().float().cpu()
+        return {
+            "w_q": _w(torch.cat([g("linear_q.weight", qs), g("linear_g.weight")], dim=0), device, True),
+            "q_bias": _dev(qb, device, torch.float32),
+            "w_kv": _w(torch.cat([g("linear_k.weight"), g("linear_v.weight")], dim=0), device, True),
+            "w_out": _w(w["linear_out.weight"], device, True),
+            "out_bias": None if ob is None else _dev(ob, device, torch.float32),
+            "c": c, "heads": heads, "precise": True,
+        }
+    dp = head_dim_pad(d)
+    hdp = heads * dp
+    f = lambda k, s=1.0: _pad_heads(w[k].detach().float(), heads, d, dp, s)
+    qs = d ** -0.5 * LOG2E
+    qb = torch.zeros(2 * hdp, dtype=torch.float32)
+    if w.get("linear_q.bias") is not None:
+        qb[:hdp] = _pad_heads(w["linear_q.bias"].detach().float(), heads, d, dp, qs)
+    if w.get("linear_g.bias") is not None:
+        qb[hdp:] = _pad_heads(w["linear_g.bias"].detach().float(), heads, d, dp)
+    return {
+        "w_q": _dev(torch.cat([f("linear_q.weight", qs), f("linear_g.weight")], dim=0), device, dtype),
+        "q_bias": _dev(qb, device, torch.float32),
+        "w_kv": _dev(torch.cat([f("linear_k.weight"), f("linear_v.weight")], dim=0), device, dtype),
+        "w_out": _dev(w["linear_out.weight"], device, dtype),
+        "out_bias": None if ob is None else _dev(ob, device, torch.float32),
+        "c": c, "heads": heads,
+    }
+
+
 def pack_transition(w: dict, device, dtype=torch.bfloat16, precise: bool = False) -> dict:
     """Weights of Transition (model/layers/folding/transition.py:27-46): the SwiGLU matrix is split into
     its silu half and its linear half (model/primitives/activation.py:27-29) and interleaved per GEMM tile."""

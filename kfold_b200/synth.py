@@ -96,6 +96,35 @@ def apb_weights(rng: _Rng, c_a: int, c_s: int | None) -> dict:
     return w
 
 
+def cross_apb_weights(rng: _Rng, c_a: int, c_s: int | None) -> dict:
+    """CrossAttentionPairBias (model/layers/folding/attention_pair_bias.py:161-205)."""
+    w = {
+        "linear_q.weight": rng.linear(c_a, c_a), "linear_q.bias": rng.normal(c_a, std=0.1),
+        "linear_k.weight": rng.linear(c_a, c_a), "linear_v.weight": rng.linear(c_a, c_a),
+        "linear_g.weight": rng.linear(c_a, c_a), "linear_out.weight": rng.linear(c_a, c_a),
+    }
+    if c_s is None:
+        for side in ("q", "k"):
+            w[f"layernorm_a_{side}.weight"] = rng.ln_w(c_a)
+            w[f"layernorm_a_{side}.bias"] = rng.ln_b(c_a)
+    else:
+        w.update(_prefixed("adaln_a_q", adaln_weights(rng, c_a, c_s)))
+        w.update(_prefixed("adaln_a_k", adaln_weights(rng, c_a, c_s)))
+        w["linear_ada_out.weight"] = rng.linear(c_a, c_s)
+        w["linear_ada_out.bias"] = rng.normal(c_a, std=0.1) - 2.0
+    return w
+
+
+def local_stack_weights(rng: _Rng, c_a: int, c_s: int, c_z: int, heads: int, blocks: int) -> dict:
+    """LocalTransformerStack (model/layers/folding/diffusion_transformer.py:419-467)."""
+    w = {"layernorm_z.weight": rng.ln_w(c_z)}
+    for i in range(blocks):
+        w[f"blocks.{i}.linear_z_to_bias.weight"] = rng.linear(heads, c_z)
+        w.update(_prefixed(f"blocks.{i}.attention", cross_apb_weights(rng, c_a, c_s)))
+        w.update(_prefixed(f"blocks.{i}.transition", conditioned_transition_weights(rng, c_a, c_s)))
+    return w
+
+
 def conditioned_transition_weights(rng: _Rng, c_a: int, c_s: int, factor: int = 2) -> dict:
     """ConditionedTransitionBlock (model/layers/folding/diffusion_transformer.py:50-71)."""
     w = _prefixed("adaln", adaln_weights(rng, c_a, c_s))

@@ -249,6 +249,58 @@ def global_transformer_stack(a, s, pair_bias, mask, w: dict, num_heads: int, num
     return a
 
 
+def atom_windows(x, dim: int):
+    """Window indexing of the local attention -- model/layers/folding/utils.py:97-188: queries in windows of 32,
+    keys = eight half-blocks of 16 atoms around each window, i.e. atoms [32 w - 48, 32 w + 80); out-of-range keys
+    are zero-filled (:140-147, :184-187)."""
+    dim = dim % x.ndim
+    length = x.shape[dim]
+    if length % 32 != 0:
+        raise ValueError("Length must be divisible by 32")
+    nw = length // 32
+    idx = torch.arange(nw, device=x.device)[:, None] * 32 - 48 + torch.arange(128, device=x.device)[None, :]
+    pad = (idx < 0) | (idx >= length)
+    x_q = x.unflatten(dim, (nw, 32))
+    x_k = x.index_select(dim, idx.clamp(0, length - 1).reshape(-1)).unflatten(dim, (nw, 128))
+    shape = [1] * x_k.ndim
+    shape[dim], shape[dim + 1] = nw, 128
+    return x_q, x_k.masked_fill(pad.view(shape), 0)
+
+
+def cross_attention_pair_bias(a_q, a_k, s_q, s_k, pair_bias, mask, w: dict, num_heads: int, mode: str = "fp32"):
+    """``CrossAttentionPairBias.forward`` -- model/layers/folding/attention_pair_bias.py:206-260."""
+    m = _Mode(mode)
+    if s_q is not None:
+        x_q = adaln(a_q, s_q, sub(w, "adaln_a_q"), mode)
+        x_k = adaln(a_k, s_k, sub(w, "adaln_a_k"), mode)
+    else:
+        x_q = layer_norm(a_q, w["layernorm_a_q.weight"], w["layernorm_a_q.bias"], 1e-5, mode)
+        x_k = layer_norm(a_k, w["layernorm_a_k.weight"], w["layernorm_a_k.bias"], 1e-5, mode)
+    out = attention_pair_bias(x_q, x_k, pair_bias, mask, w, num_heads, mode)
+    if s_q is not None:
+        gate = torch.sigmoid(m.linear(m.r(s_q.float()), w["linear_ada_out.weight"], w["linear_ada_out.bias"]))
+        out = m.r(gate * out)
+    return out
+
+
+def local_transformer_stack(a, s, z, mask, w: dict, num_heads: int, num_blocks: int, mode: str = "fp32"):
+    """``LocalTransformerStack.forward`` -- model/layers/folding/diffusion_transformer.py:469-512 with the block of
+    :564-597.  a (*, L, c_a); s (*, L, c_s); z (*, W, 32, 128, c_z); mask (*, L)."""
+    m = _Mode(mode)
+    a = a.float()
+    s_q, s_k = atom_windows(s, -2)
+    _, mask_k = atom_windows(mask, -1)
+    zn = layer_norm(z, w["layernorm_z.weight"], None, 1e-5, mode)
+    for i in range(num_blocks):
+        wb = sub(w, f"blocks.{i}")
+        a_q, a_k = atom_windows(a, -2)
+        bias = m.linear(zn, wb["linear_z_to_bias.weight"]).movedim(-1, -3)          # (*, W, H, 32, 128)
+        a_q = a_q + cross_attention_pair_bias(a_q, a_k, s_q, s_k, bias, mask_k, sub(wb, "attention"), num_heads, mode)
+        a_q = a_q + conditioned_transition(a_q, s_q, sub(wb, "transition"), mode)
+        a = a_q.flatten(-3, -2)
+    return a
+
+
 def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
     """``TriangularBlock.forward`` (eval) -- model/modules/tri_stack.py:130-151."""
     m = _Mode(mode)

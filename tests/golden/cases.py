@@ -40,6 +40,8 @@ CASES = {
     "cond_transition": dict(kind="cond_transition", seed=43, rows=24, c=768, c_s=384, samples=2),
     # two blocks of the diffusion token transformer (AdaLN attention + conditioned transition), shared bias over 3 samples
     "diffusion_stack": dict(kind="diffusion_stack", seed=44, l=24, c=768, c_s=384, heads=16, blocks=2, samples=3, valid=20),
+    # atom-level local transformer: 3 blocks over 5 windows of 32 atoms (keys: 128 per window), 2 samples sharing z and s
+    "local_stack": dict(kind="local_stack", seed=45, l=160, c=128, c_s=128, c_z=16, heads=4, blocks=3, samples=2, valid=150),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -84,6 +86,13 @@ def build_inputs(name: str) -> dict:
         out["s"] = rng.normal(1, 1, cs["l"], cs["c_s"])
         out["pair_bias"] = rng.normal(1, cs["blocks"], cs["heads"], cs["l"], cs["l"])
         out["mask"] = synth.token_mask(cs["l"], cs["valid"]).view(1, 1, cs["l"]).contiguous()
+    elif kind == "local_stack":
+        l, w_ = cs["l"], cs["l"] // 32
+        out["w"] = synth.local_stack_weights(rng, cs["c"], cs["c_s"], cs["c_z"], cs["heads"], cs["blocks"])
+        out["a"] = rng.normal(1, cs["samples"], l, cs["c"])
+        out["s"] = rng.normal(1, 1, l, cs["c_s"])
+        out["z"] = rng.normal(1, 1, w_, 32, 128, cs["c_z"])
+        out["mask"] = synth.token_mask(l, cs["valid"]).view(1, 1, l).contiguous()
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

@@ -64,6 +64,14 @@ def run_reference(ns, name: str) -> dict:
             blk.attention.kernel_backend = "torch"      # the oracle path; the constructor hard-codes "sdpa"
         _load(stack, inp["w"])
         return {"out": stack(inp["a"].clone(), inp["s"], inp["pair_bias"], inp["mask"])}
+    if kind == "local_stack":
+        import importlib
+        dt = importlib.import_module("kfold.model.layers.folding.diffusion_transformer")
+        stack = dt.LocalTransformerStack(cs["c"], cs["c_s"], cs["c_z"], cs["heads"], cs["blocks"])
+        for blk in stack.blocks:
+            blk.attention.kernel_backend = "torch"      # the oracle path; the constructor hard-codes "sdpa"
+        _load(stack, inp["w"])
+        return {"out": stack(inp["a"].clone(), inp["s"], inp["z"], inp["mask"])}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "block":

@@ -458,3 +458,99 @@ def test_autocast_fp32_input_returns_fp32(dev):
     assert y32.dtype == torch.float32 and mx < PRECISE_MAX_TOL, f"{mx:.3e} {r:.3e}"
     with pytest.raises(NotImplementedError):
         mod(x.half())
+
+
+# ----------------------------------------------------------------------------- atom-level local transformer
+def test_window_bias_against_torch(dev):
+    """LayerNorm over 16 channels + projection to blocks x heads values, head-major output; bf16 and fp32."""
+    from kfold_b200 import functional as F
+    g = torch.Generator().manual_seed(61)
+    z = torch.randn(1, 3, 32, 128, 16, generator=g) * 2.0 + 0.5
+    w = torch.randn(12, 16, generator=g) * 0.25
+    ln_w = 1.0 + 0.1 * torch.randn(16, generator=g)
+    ref = torch.nn.functional.linear(torch.nn.functional.layer_norm(z, (16,), ln_w, None, 1e-5), w).movedim(-1, 0)
+    out32 = F.window_bias(z.to(dev), ln_w.to(dev), None, w.to(dev), 1e-5)
+    assert out32.shape == ref.shape and (out32.cpu() - ref).abs().max() < 2e-5
+    out16 = F.window_bias(z.to(dev, torch.bfloat16), ln_w.to(dev), None, w.to(dev, torch.bfloat16), 1e-5)
+    mx, r = err_stats(out16.float().cpu(), ref)
+    _check(mx, r, "window_bias bf16")
+    proj = F.window_bias(z.to(dev), None, None, w.to(dev), normalise=False)
+    assert (proj.cpu() - torch.nn.functional.linear(z, w).movedim(-1, 0)).abs().max() < 2e-5
+
+
+def _valid_rows(out, ref, mask):
+    """Rows of padding atoms are not compared: a window made only of padding has every key masked, and what a softmax
+    over nothing but -1e9 logits returns is not defined by the reference's arithmetic beyond being finite."""
+    keep = mask.reshape(-1).bool()
+    assert torch.isfinite(out).all()
+    return out[..., keep, :], ref[..., keep, :]
+
+
+def test_local_transformer_stack_against_reference_golden(dev):
+    """LocalTransformerStack (3 blocks, 5 windows, 2 samples sharing z and s) against the reference output, under
+    bfloat16 compute and under float32 compute."""
+    from kfold_b200 import modules as M
+    inp = cases.build_inputs("local_stack")
+    cs = inp["case"]
+    gold = load_golden("local_stack")["out"]
+    stack = M.LocalTransformerStack(cs["c"], cs["c_s"], cs["c_z"], cs["heads"], cs["blocks"]).to(dev)
+    stack.load_state_dict(inp["w"], strict=True)
+    args = [inp[k].to(dev) for k in ("a", "s", "z", "mask")]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = stack(*args)
+    assert out.dtype == torch.float32
+    _check(*err_stats(*_valid_rows(out.cpu(), gold, inp["mask"])), "local_stack bf16")
+    out = stack(*args)
+    mx, r = err_stats(*_valid_rows(out.cpu(), gold, inp["mask"]))
+    assert out.dtype == torch.float32 and mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"local_stack fp32: {mx:.3e} {r:.3e}"
+
+
+def test_local_transformer_block_windowed_signature(dev):
+    """LocalTransformerBlock.forward with the reference's windowed arguments (a_q, a_k, s_q, s_k, normalised z, mask_k):
+    the generic cross-attention entry with a broadcast bias, against the oracle."""
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    rng = synth._Rng(62)
+    l, c, c_z, h, ns = 96, 128, 16, 4, 2
+    w = {"linear_z_to_bias.weight": rng.linear(h, c_z)}
+    w.update(synth._prefixed("attention", synth.cross_apb_weights(rng, c, c)))
+    w.update(synth._prefixed("transition", synth.conditioned_transition_weights(rng, c, c)))
+    a, s = rng.normal(1, ns, l, c), rng.normal(1, 1, l, c)
+    zn = rng.normal(1, 1, l // 32, 32, 128, c_z)
+    mask = synth.token_mask(l, 90).view(1, 1, l)
+    a_q, a_k = O.atom_windows(a, -2)
+    s_q, s_k = O.atom_windows(s, -2)
+    _, mask_k = O.atom_windows(mask, -1)
+    blk = M.LocalTransformerBlock(c, c, c_z, h).to(dev)
+    blk.load_state_dict(w, strict=True)
+    to = lambda t: t.to(dev)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = blk(to(a_q), to(a_k), to(s_q), to(s_k), to(zn), to(mask_k)).float().cpu()
+
+    def ref_block(a_q, a_k, s_q, s_k, zn, mask_k, w):
+        bias = torch.nn.functional.linear(zn, w["linear_z_to_bias.weight"]).movedim(-1, -3)
+        x = a_q + O.cross_attention_pair_bias(a_q, a_k, s_q, s_k, bias, mask_k, O.sub(w, "attention"), h)
+        return x + O.conditioned_transition(x, s_q, O.sub(w, "transition"))
+
+    ref = _oracle_on(dev, ref_block, a_q, a_k, s_q, s_k, zn, mask_k, w)
+    keep = mask.reshape(-1).bool()
+    _check(*err_stats(out.flatten(-3, -2)[..., keep, :], ref.flatten(-3, -2)[..., keep, :]), "local block, windowed arguments")
+
+
+def test_local_transformer_config4_shape(dev):
+    """BASELINE config 4's atom transformer shape: 6 016 atoms = 188 windows, c=128, 4 heads x 32, c_z=16, 5 samples
+    sharing z and s, 3 blocks, against the oracle run on the GPU in fp32."""
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    rng = synth._Rng(63)
+    l, c, c_z, h, blocks, ns = 6016, 128, 16, 4, 3, 5
+    w = synth.local_stack_weights(rng, c, c, c_z, h, blocks)
+    a, s = rng.normal(1, ns, l, c), rng.normal(1, 1, l, c)
+    z = rng.normal(1, 1, l // 32, 32, 128, c_z)
+    mask = synth.token_mask(l, 5900).view(1, 1, l)
+    stack = M.LocalTransformerStack(c, c, c_z, h, blocks).to(dev)
+    stack.load_state_dict(w, strict=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = stack(a.to(dev), s.to(dev), z.to(dev), mask.to(dev)).cpu()
+    ref = _oracle_on(dev, O.local_transformer_stack, a, s, z, mask, w, h, blocks)
+    _check(*err_stats(*_valid_rows(out, ref, mask)), "local stack, 6016 atoms x 5 samples")

@@ -115,3 +115,47 @@ def test_pad_pair():
     xp, mp, n = F._pad_pair(x, m)
     assert xp.shape == (2, 16, 16, 4) and mp.shape == (2, 16, 16) and n == 10
     assert torch.equal(xp[:, :10, :10], x) and not mp[:, 10:].any() and not mp[:, :, 10:].any()
+
+
+def test_atom_window_indexing_matches_the_oracle():
+    """Windows of 32 queries and 128 keys [32 w - 48, 32 w + 80), zero-filled outside (model/layers/folding/utils.py:97-188)."""
+    from kfold_b200.modules import build_atom_to_qk_fn
+    from oracle import pairformer_oracle as O
+    x = torch.arange(1, 96 * 3 + 1, dtype=torch.float32).view(1, 96, 3)
+    to_qk = build_atom_to_qk_fn(96, "cpu")
+    q, k = to_qk(x, -2)
+    oq, ok = O.atom_windows(x, -2)
+    assert torch.equal(q, oq) and torch.equal(k, ok) and k.shape == (1, 3, 128, 3)
+    assert (k[0, 0, :48] == 0).all() and torch.equal(k[0, 0, 48:], x[0, :80])      # first window: 48 keys before atom 0
+    assert torch.equal(k[0, 1], torch.cat([torch.zeros(16, 3), x[0, :96], torch.zeros(16, 3)]))   # second: atoms -16 .. 111
+    m = torch.ones(1, 96, dtype=torch.bool)
+    assert to_qk(m, -1)[1].sum() == O.atom_windows(m, -1)[1].sum() == 80 + 96 + 80
+    with pytest.raises(ValueError):
+        build_atom_to_qk_fn(40, "cpu")
+
+
+def test_bias_sharing_patterns():
+    from kfold_b200.modules import _bias_sharing
+    assert _bias_sharing((1, 5, 188), (1, 1, 188)) == (5 * 188, 188)     # samples share the per-window bias
+    assert _bias_sharing((2, 5, 188), (2, 1, 188)) == (5 * 188, 188)
+    assert _bias_sharing((1, 5, 188), (188,)) == (5 * 188, 188)
+    assert _bias_sharing((1, 5, 188), (1, 5, 188)) == (1, 0)             # nothing shared
+    assert _bias_sharing((1, 5), (1, 1)) == (5, 0)                       # plain sharing by consecutive entries
+    assert _bias_sharing((1, 1, 188), (1, 1, 188)) == (1, 0)
+    assert _bias_sharing((2, 5, 188), (1, 5, 188)) == (2 * 5 * 188, 5 * 188)
+    assert _bias_sharing((2, 5, 188), (2, 5, 1)) == (188, 0)
+    assert _bias_sharing((2, 5, 188), (1, 5, 1)) is None                 # shared dims not in one block
+
+
+def test_pack_apb_cross_layout():
+    from kfold_b200 import packing, synth
+    w = synth.cross_apb_weights(synth._Rng(3), 128, 128)
+    keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight", "linear_out.weight")
+    pk = packing.pack_apb_cross({k: w[k] for k in keys}, 4, "cpu")
+    assert pk["w_q"].shape == (256, 128) and pk["w_kv"].shape == (256, 128) and pk["q_bias"].shape == (256,)
+    scale = 32 ** -0.5 * packing.LOG2E
+    assert torch.allclose(pk["w_q"][:128].float(), (w["linear_q.weight"] * scale).bfloat16().float())
+    assert torch.allclose(pk["q_bias"][:128], w["linear_q.bias"] * scale) and (pk["q_bias"][128:] == 0).all()
+    assert torch.equal(pk["w_kv"][128:].float(), w["linear_v.weight"].bfloat16().float())
+    pkp = packing.pack_apb_cross({k: w[k] for k in keys}, 4, "cpu", precise=True)
+    assert pkp["w_q"].shape == (256, 6 * 128) and pkp["w_kv"].shape == (256, 6 * 128) and pkp["precise"]

@@ -26,6 +26,8 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
     if kind == "diffusion_stack":
         return {"out": O.global_transformer_stack(inp["a"], inp["s"], inp["pair_bias"], inp["mask"], w, cs["heads"],
                                                   cs["blocks"], mode)}
+    if kind == "local_stack":
+        return {"out": O.local_transformer_stack(inp["a"], inp["s"], inp["z"], inp["mask"], w, cs["heads"], cs["blocks"], mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "block":
