@@ -282,6 +282,71 @@ def run_diffusion_step(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
+# optional third workload (--atom-step): one pass of an atom-level local transformer of BASELINE config 4
+# (3 blocks, 6 016 atoms = 188 windows of 32 queries x 128 keys, c=128, 4 heads x 32, pair channels 16, 5 samples
+# sharing the window pair tensor and the conditioning), bf16 compute.  Its own JSON line.
+# ------------------------------------------------------------------------------------------------
+def run_atom_step(args) -> None:
+    from kfold_b200 import _lib as L
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    blocks, l, ns, c, c_z, heads = 3, 6016, 5, 128, 16, 4
+    rng = synth._Rng(SEED)
+    w = synth.local_stack_weights(rng, c, c, c_z, heads, blocks)
+    a = rng.normal(1, ns, l, c).to(dev)
+    s = rng.normal(1, 1, l, c).to(dev)
+    z = rng.normal(1, 1, l // 32, 32, 128, c_z).to(dev)
+    mask = synth.token_mask(l, pad_frac=0.02).view(1, 1, l).to(dev)
+    stack = M.LocalTransformerStack(c, c, c_z, heads, blocks).to(dev)
+    stack.load_state_dict(w, strict=True)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for _ in range(max(args.warmup, 3)):
+            stack(a, s, z, mask)
+        torch.cuda.synchronize()
+        L.profile_enable(True)
+        launches0 = L.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            stack(a, s, z, mask)
+        e1.record()
+        torch.cuda.synchronize()
+        launches_per_step = (L.launch_count() - launches0) // max(args.steps, 1)
+        prof = L.profile_report()
+        L.profile_enable(False)
+        ms_eager = e0.elapsed_time(e1) / args.steps
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            stack(a, s, z, mask)
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            out_g = stack(a, s, z, mask)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_graph = e0.elapsed_time(e1) / args.steps
+        graph_ok = bool(torch.isfinite(out_g.float()).all())
+    ms = min(ms_eager, ms_graph) if graph_ok else ms_eager
+    kernels = {tag: {"launches": cnt, "avg_ms": round(t / cnt, 5)} for tag, (cnt, t) in sorted(prof.items(), key=lambda kv: -kv[1][1])}
+    emit({"metric": f"atom_local_transformer_pass_ms_l{l}_s{ns}_bf16", "value": ms, "unit": "ms", "n_gpus": 1,
+          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+          "config": {"workload": f"atom-level local transformer (BASELINE config 4): {blocks} blocks, {l} atoms in windows of 32 "
+                                 f"queries x 128 keys, c={c}, {heads} heads, {ns} samples sharing the window pair tensor"},
+          "gpu_launches": launches_per_step * args.steps, "ms_eager": round(ms_eager, 3), "ms_cuda_graph": round(ms_graph, 3),
+          "launches_per_step": launches_per_step, "kernels": kernels, "device_status": L.device_status()})
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
@@ -454,11 +519,16 @@ def main() -> None:
                     help="with N > 1 ranks: row-shard ONE pair tensor over the GPUs (strong scaling) instead of one block per GPU")
     ap.add_argument("--tokens", type=int, default=N_TOKENS,
                     help="profiling aid: run the block at another N (the reported line is then NOT the benchmark workload)")
+    ap.add_argument("--atom-step", action="store_true",
+                    help="third workload: one pass of an atom-level local transformer of BASELINE config 4 (its own JSON line)")
     ap.add_argument("--diffusion-step", action="store_true",
                     help="second workload: one pass of the sampler's token transformer of BASELINE config 4 (its own JSON line)")
     args = ap.parse_args()
     if args.diffusion_step:
         run_diffusion_step(args)
+        return
+    if args.atom_step:
+        run_atom_step(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.tokens == N_TOKENS else args.warmup
     if args.tokens != N_TOKENS:

@@ -356,9 +356,12 @@ class ConditionedTransitionBlock(nn.Module, _PackedMixin):
         self.linear_out = LinearNoBias(model_dim, channel_a)
 
     @torch.compiler.disable
-    def forward(self, a: torch.Tensor, s: torch.Tensor, residual: bool = False) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, s: torch.Tensor, residual: bool = False, precise: bool | None = None) -> torch.Tensor:
+        """``precise`` overrides the choice made from the compute dtype (for callers that already run with autocast
+        switched off)."""
         _check_inference(a)
-        precise = _is_precise(compute_dtype(a), "ConditionedTransitionBlock")
+        if precise is None:
+            precise = _is_precise(compute_dtype(a), "ConditionedTransitionBlock")
         pk = self._packed(a.device, torch.float32 if precise else torch.bfloat16,
                           lambda sd, dev: packing.pack_cond_transition(sd, dev, precise=precise))
         with torch.autocast(a.device.type, enabled=False):
@@ -644,7 +647,7 @@ class LocalTransformerStack(nn.Module):
                     xq.reshape(batch, WINDOW_Q, c), xk.reshape(batch, WINDOW_K, c), bias_all[i], mask_k,
                     att._cross_packed(a.device, precise), bias_div=sharing[0], bias_mod=sharing[1], bias_head_major=True,
                     out_dtype=a.dtype, out_gate=gate, resid=a).view(*lead, length, c)
-                a = blk.transition(a, s, residual=True)
+                a = blk.transition(a, s, residual=True, precise=precise)
         return a
 
 

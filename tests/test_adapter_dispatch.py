@@ -36,6 +36,7 @@ def recorder(monkeypatch):
     monkeypatch.setattr(adapter.F, "triangle_multiplication", rec("trimul"))
     monkeypatch.setattr(adapter.F, "triangle_attention", rec("triatt"))
     monkeypatch.setattr(adapter.F, "attention_pair_bias", rec("apb"))
+    monkeypatch.setattr(adapter.F, "attention_pair_bias_cross_bcast", rec("apb_cross"))
     return calls
 
 
@@ -92,6 +93,25 @@ def test_attention_pair_bias_routes_after_convert(ref, recorder):
         out = mod(s, None, bias, mask)
     name, a, k = recorder[-1]
     assert name == "apb" and a[1] is bias and out.shape == s.shape
+
+
+def test_cross_attention_routes_for_the_atom_windows(ref, recorder):
+    """CrossAttentionPairBias (call site "diffusion_local") is converted together with the sampler's other attention
+    modules and hands the windowed query / key tensors to the cross-attention entry."""
+    from kfold_b200 import adapter
+    mod = ref.CrossAttentionPairBias(128, 4, 128, kernel_backend="sdpa")
+    holder = torch.nn.ModuleList([mod])
+    assert adapter.convert(holder) == 0 and mod.kernel_backend == "sdpa"
+    assert adapter.convert(holder, diffusion=True) == 1 and mod.kernel_backend == "b200"
+    a_q, a_k = torch.randn(1, 2, 3, 32, 128), torch.randn(1, 2, 3, 128, 128)
+    s_q, s_k = torch.randn(1, 1, 3, 32, 128), torch.randn(1, 1, 3, 128, 128)
+    bias = torch.randn(1, 1, 3, 4, 32, 128)
+    mask = torch.ones(1, 1, 3, 128, dtype=torch.bool)
+    with torch.no_grad():
+        out = mod(a_q, a_k, s_q, s_k, bias, mask)
+    name, a, k = recorder[-1]
+    assert name == "apb_cross" and a[0].shape == a_q.shape and a[1].shape == a_k.shape and a[2] is bias and a[3] is mask
+    assert a[4] == {"slot": "apb_cross"} and out.shape == a_q.shape
 
 
 def test_backend_refuses_cpu_and_grad(ref):
