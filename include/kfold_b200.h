@@ -239,6 +239,22 @@ KFB_API int kfb_window_bias_fwd(const void* z, const float* ln_w, const float* l
                                 long long positions, int c, int heads, float eps, int normalise, int dtype, void* stream);
 
 /*
+ * Token <-> atom maps of the atom attention encoder / decoder.
+ *   kfb_tokens_to_atoms replaces broadcast_tokens_to_atoms (src/kfold/model/layers/folding/utils.py:25-51):
+ *     out[b, a, :] = x[b, token_index[b / index_div, a], :];  x (batch, n_token, d), out (batch, n_atom, d).
+ *     An index outside [0, n_token) gives a zero row and sets the device status word (kfb_device_status) to 900.
+ *   kfb_atoms_to_tokens replaces aggregate_atoms_to_tokens (:54-93): out[b, t, :] = mean of x[b, a, :] over the atoms
+ *     with mask[a] != 0 and token_index[a] == t, accumulated in fp32 in atom order; a token without atoms gives zeros.
+ *     x (batch, n_atom, d), out (batch, n_token, d).
+ *   token_index : int64 (batch / index_div, n_atom), mask : bytes of the same shape -- `index_div` consecutive batch
+ *   entries (the diffusion samples) share one row.  dtype KFB_BF16 or KFB_FP32 is the element type of x and out.
+ */
+KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, void* out, int batch, int n_token, int n_atom,
+                                int d, int index_div, int dtype, void* stream);
+KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, int batch,
+                                int n_atom, int n_token, int d, int index_div, int dtype, void* stream);
+
+/*
  * Adaptive LayerNorm: out = sigmoid(g) * LayerNorm(a) + v, LayerNorm without affine (fp32 statistics).
  * Replaces the last line of AdaLN.forward (src/kfold/model/primitives/normalization.py:117-125); the two
  * small projections of the conditioning, g = Linear(LN_s(s)) and v = LinearNoBias(LN_s(s)), are computed by

@@ -20,7 +20,7 @@ KFB_API int kfb_device_status(int* code_out) {
   }
   if (code_out) *code_out = code;
   if (code != 0) {
-    set_error("a bounded device-side wait gave up (code %d)", code);
+    set_error("device-side error status %d (900: a token index out of range; otherwise a bounded wait that gave up)", code);
     return KFB_ERR_DEVICE_WAIT;
   }
   return KFB_OK;

@@ -471,3 +471,59 @@ def pair_bias_rows(z_rows: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor,
         L.check(lib.kfb_pair_bias_rows_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), rows,
                                            n, c, heads, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
     return out
+
+
+def _index_sharing(lead: tuple, index_lead: tuple):
+    """index_div such that batch entry b of a tensor with leading dims `lead` uses index row b // index_div, for an
+    index tensor whose leading dims equal `lead` up to trailing 1s; None otherwise."""
+    il = (1,) * (len(lead) - len(index_lead)) + tuple(index_lead)
+    k = len(lead)
+    div = 1
+    while k > 0 and il[k - 1] == 1:
+        div *= lead[k - 1]
+        k -= 1
+    return div if tuple(il[:k]) == tuple(lead[:k]) else None
+
+
+def broadcast_tokens_to_atoms(x: torch.Tensor, token_index: torch.Tensor) -> torch.Tensor:
+    """Token features gathered to their atoms (model/layers/folding/utils.py:25-51): x (*, Ntoken[, D]) bf16 or
+    float32, token_index (*, Natom) int64 (leading dims may be 1 where x's are not) -> (*, Natom[, D])."""
+    if x.ndim == token_index.ndim:
+        return broadcast_tokens_to_atoms(x.unsqueeze(-1), token_index).squeeze(-1)
+    _require_cuda(x, token_index)
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("broadcast_tokens_to_atoms: bfloat16 or float32 features")
+    lead, n_token, d = tuple(x.shape[:-2]), x.shape[-2], x.shape[-1]
+    n_atom = token_index.shape[-1]
+    div = _index_sharing(lead, tuple(token_index.shape[:-1]))
+    idx = token_index.to(torch.int64)
+    if div is None:
+        idx, div = idx.expand(*lead, n_atom), 1
+    idx = idx.reshape(-1, n_atom).contiguous()
+    x2 = x.reshape(-1, n_token, d).contiguous()
+    out = torch.empty(x2.shape[0], n_atom, d, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().kfb_tokens_to_atoms(L.ptr(x2), L.ptr(idx), L.ptr(out), x2.shape[0], n_token, n_atom, d, div,
+                                            L.dtype_code(x.dtype), L.stream_ptr()))
+    return out.view(*lead, n_atom, d)
+
+
+def aggregate_atoms_to_tokens(x: torch.Tensor, token_index: torch.Tensor, mask: torch.Tensor, num_tokens: int) -> torch.Tensor:
+    """Masked mean of the atom features of every token (model/layers/folding/utils.py:54-93): x (*, Natom, D) bf16 or
+    float32, token_index and mask (*, Natom) -> (*, num_tokens, D); fp32 accumulation in atom order."""
+    _require_cuda(x, token_index, mask)
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("aggregate_atoms_to_tokens: bfloat16 or float32 features")
+    lead, n_atom, d = tuple(x.shape[:-2]), x.shape[-2], x.shape[-1]
+    idx, mk = torch.broadcast_tensors(token_index.to(torch.int64), mask.to(torch.bool))
+    div = _index_sharing(lead, tuple(idx.shape[:-1]))
+    if div is None:
+        idx, mk, div = idx.expand(*lead, n_atom), mk.expand(*lead, n_atom), 1
+    idx = idx.reshape(-1, n_atom).contiguous()
+    mk = mk.reshape(-1, n_atom).contiguous().view(torch.uint8)
+    x2 = x.reshape(-1, n_atom, d).contiguous()
+    out = torch.empty(x2.shape[0], num_tokens, d, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().kfb_atoms_to_tokens(L.ptr(x2), L.ptr(idx), L.ptr(mk), L.ptr(out), x2.shape[0], n_atom, num_tokens, d, div,
+                                            L.dtype_code(x.dtype), L.stream_ptr()))
+    return out.view(*lead, num_tokens, d)

@@ -249,6 +249,26 @@ def global_transformer_stack(a, s, pair_bias, mask, w: dict, num_heads: int, num
     return a
 
 
+def broadcast_tokens_to_atoms(x, token_index):
+    """``broadcast_tokens_to_atoms`` -- model/layers/folding/utils.py:25-51: out[..., a, :] = x[..., token_index[a], :]."""
+    if x.ndim == token_index.ndim:
+        return broadcast_tokens_to_atoms(x.unsqueeze(-1), token_index).squeeze(-1)
+    shape = list(x.shape)
+    shape[-2] = token_index.shape[-1]
+    return torch.gather(x, -2, token_index.unsqueeze(-1).expand(*shape))
+
+
+def aggregate_atoms_to_tokens(x, token_index, mask, num_tokens: int):
+    """``aggregate_atoms_to_tokens`` -- model/layers/folding/utils.py:54-93: fp32 mean over the valid atoms of each
+    token (padding atoms go to an extra slot that is dropped); tokens without atoms give zeros."""
+    index = torch.where(mask, token_index, num_tokens).unsqueeze(-1).expand(*x.shape)
+    shape = list(x.shape)
+    shape[-2] = num_tokens + 1
+    out = torch.zeros(*shape, dtype=torch.float32, device=x.device).scatter_reduce_(
+        -2, index, x.float(), reduce="mean", include_self=False)
+    return out[..., :num_tokens, :].to(x.dtype).contiguous()
+
+
 def atom_windows(x, dim: int):
     """Window indexing of the local attention -- model/layers/folding/utils.py:97-188: queries in windows of 32,
     keys = eight half-blocks of 16 atoms around each window, i.e. atoms [32 w - 48, 32 w + 80); out-of-range keys

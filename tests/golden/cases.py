@@ -7,6 +7,7 @@ reference output).  Inputs and weights are regenerated from the seed with
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from kfold_b200 import synth
@@ -42,6 +43,8 @@ CASES = {
     "diffusion_stack": dict(kind="diffusion_stack", seed=44, l=24, c=768, c_s=384, heads=16, blocks=2, samples=3, valid=20),
     # atom-level local transformer: 3 blocks over 5 windows of 32 atoms (keys: 128 per window), 2 samples sharing z and s
     "local_stack": dict(kind="local_stack", seed=45, l=160, c=128, c_s=128, c_z=16, heads=4, blocks=3, samples=2, valid=150),
+    # token <-> atom maps: 40 tokens, 160 atoms (1 to 8 atoms per token, one token without atoms), 2 samples
+    "atom_token_maps": dict(kind="atom_token_maps", seed=46, tokens=40, atoms=160, d=96, samples=2, valid=150),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -93,6 +96,17 @@ def build_inputs(name: str) -> dict:
         out["s"] = rng.normal(1, 1, l, cs["c_s"])
         out["z"] = rng.normal(1, 1, w_, 32, 128, cs["c_z"])
         out["mask"] = synth.token_mask(l, cs["valid"]).view(1, 1, l).contiguous()
+    elif kind == "atom_token_maps":
+        nt, na = cs["tokens"], cs["atoms"]
+        # atoms sorted by token, token nt - 2 left without atoms, sizes 1..8
+        sizes = rng.rs.randint(1, 9, size=nt)
+        sizes[nt - 2] = 0
+        index = np.repeat(np.arange(nt), sizes)[:na]
+        index = np.concatenate([index, np.full(na - len(index), nt - 1)]).astype(np.int64)
+        out["token_index"] = torch.from_numpy(index).view(1, 1, na)
+        out["mask"] = synth.token_mask(na, cs["valid"]).view(1, 1, na)
+        out["x_token"] = rng.normal(1, cs["samples"], nt, cs["d"])
+        out["x_atom"] = rng.normal(1, cs["samples"], na, cs["d"])
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

@@ -72,6 +72,12 @@ def run_reference(ns, name: str) -> dict:
             blk.attention.kernel_backend = "torch"      # the oracle path; the constructor hard-codes "sdpa"
         _load(stack, inp["w"])
         return {"out": stack(inp["a"].clone(), inp["s"], inp["z"], inp["mask"])}
+    if kind == "atom_token_maps":
+        import importlib
+        ut = importlib.import_module("kfold.model.layers.folding.utils")
+        idx = inp["token_index"].expand(1, cs["samples"], cs["atoms"])
+        return {"atoms": ut.broadcast_tokens_to_atoms(inp["x_token"], idx),
+                "tokens": ut.aggregate_atoms_to_tokens(inp["x_atom"], idx, inp["mask"].expand_as(idx), cs["tokens"])}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "block":

@@ -554,3 +554,39 @@ def test_local_transformer_config4_shape(dev):
         out = stack(a.to(dev), s.to(dev), z.to(dev), mask.to(dev)).cpu()
     ref = _oracle_on(dev, O.local_transformer_stack, a, s, z, mask, w, h, blocks)
     _check(*err_stats(*_valid_rows(out, ref, mask)), "local stack, 6016 atoms x 5 samples")
+
+
+def test_token_atom_maps_against_reference_golden(dev):
+    """broadcast_tokens_to_atoms / aggregate_atoms_to_tokens: float32 against the reference outputs (the gather exactly),
+    bf16 against the rounded ones, with the index row shared by the samples and expanded per sample."""
+    from kfold_b200 import _lib as L
+    from kfold_b200 import functional as F
+    inp = cases.build_inputs("atom_token_maps")
+    cs = inp["case"]
+    gold = load_golden("atom_token_maps")
+    idx, mask = inp["token_index"].to(dev), inp["mask"].to(dev)
+    xt, xa = inp["x_token"].to(dev), inp["x_atom"].to(dev)
+    for index, m in ((idx, mask), (idx.expand(1, cs["samples"], -1).contiguous(), mask.expand(1, cs["samples"], -1).contiguous())):
+        atoms = F.broadcast_tokens_to_atoms(xt, index)
+        assert torch.equal(atoms.cpu(), gold["atoms"])
+        tokens = F.aggregate_atoms_to_tokens(xa, index, m, cs["tokens"])
+        assert (tokens.cpu() - gold["tokens"]).abs().max() < 1e-6
+        assert (tokens[..., cs["tokens"] - 2, :] == 0).all()
+    atoms16 = F.broadcast_tokens_to_atoms(xt.bfloat16(), idx)
+    assert torch.equal(atoms16.float().cpu(), gold["atoms"].bfloat16().float())
+    tokens16 = F.aggregate_atoms_to_tokens(xa.bfloat16(), idx, mask, cs["tokens"])
+    ref16 = O.aggregate_atoms_to_tokens(inp["x_atom"].bfloat16(), inp["token_index"].expand(1, cs["samples"], -1),
+                                        inp["mask"].expand(1, cs["samples"], -1), cs["tokens"])
+    assert (tokens16.float().cpu() - ref16.float()).abs().max() < 1e-2
+    # 1-D features (the reference's (*, Ntoken) form)
+    v = F.broadcast_tokens_to_atoms(xt[..., 0].contiguous(), idx)
+    assert torch.equal(v.cpu(), gold["atoms"][..., 0])
+    # an index past the last token: zero row and an error status instead of an out-of-bounds read
+    bad = idx.clone()
+    bad[..., 3] = cs["tokens"] + 5
+    out = F.broadcast_tokens_to_atoms(xt, bad)
+    torch.cuda.synchronize()
+    assert (out[..., 3, :] == 0).all()
+    with pytest.raises(L.KfbError, match="900"):
+        L.device_status()
+    assert L.device_status() == 0

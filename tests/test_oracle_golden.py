@@ -28,6 +28,10 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
                                                   cs["blocks"], mode)}
     if kind == "local_stack":
         return {"out": O.local_transformer_stack(inp["a"], inp["s"], inp["z"], inp["mask"], w, cs["heads"], cs["blocks"], mode)}
+    if kind == "atom_token_maps":
+        idx = inp["token_index"].expand(1, cs["samples"], cs["atoms"])
+        return {"atoms": O.broadcast_tokens_to_atoms(inp["x_token"], idx),
+                "tokens": O.aggregate_atoms_to_tokens(inp["x_atom"], idx, inp["mask"].expand_as(idx), cs["tokens"])}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "block":
@@ -45,6 +49,10 @@ def test_oracle_matches_reference_golden(name):
         assert compare_pair_output(got["z"], gold, "z")[0] < 5 * FP32_TOL
         zs = float(got["z"].double().sum())
         assert abs(zs - float(gold["z_sum"])) <= 1e-3 * float(gold["z_sumsq"]) ** 0.5
+    elif cases.CASES[name]["kind"] == "atom_token_maps":
+        assert torch.equal(got["atoms"], gold["atoms"])                 # a gather: exact
+        assert err_stats(got["tokens"], gold["tokens"])[0] < FP32_TOL
+        assert (got["tokens"][..., cases.CASES[name]["tokens"] - 2, :] == 0).all()   # the token without atoms
     else:
         out = got["out"]
         if out.dim() == 4 and ("out" not in gold):
