@@ -225,6 +225,24 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
                               int bias_div, int bias_mod, int bias_head_major, int out_dtype, void* stream);
 
 /*
+ * The same attention on the UN-windowed atoms (bf16 compute, head dim <= 32): the windows of 32 queries and 128 keys
+ * (atoms 32 w - 48 ... 32 w + 79 for window w, src/kfold/model/layers/folding/utils.py:97-188) are walked by the
+ * kernel itself, so neither queries, keys nor conditionings are gathered and the key / value projection runs once
+ * per atom instead of once per window slot.
+ *   x_q, x_k : bf16 (batch, l, c), the query-side and key-side normalised atoms, l a multiple of 32;
+ *   pair_bias : bf16, one [32][128] bias per window and head: (bias groups * l/32, heads, 32, 128), or head-major
+ *   (heads, n, 32, 128) with bias_head_major = n >= bias groups * l/32;  `bias_share` consecutive batch entries
+ *   (samples) use the same biases;  mask : bytes (batch / mask_share, l), atom validity;
+ *   weights, out_gate / gate_rows, out, resid as in kfb_apb_cross_fwd; out_dtype KFB_BF16 or KFB_FP32 (output only).
+ */
+KFB_API size_t kfb_apb_window_workspace_bytes(int batch, int l, int c, int heads);
+KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
+                               const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
+                               const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
+                               void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_share,
+                               int mask_share, int bias_head_major, int out_dtype, void* stream);
+
+/*
  * Pair bias of the atom windows for every block of a local transformer at once:
  * bias[h, p] = sum_k LayerNorm(z[p])[k] * w[h, k].  Replaces `self.layernorm_z(z)` of LocalTransformerStack.forward
  * (src/kfold/model/layers/folding/diffusion_transformer.py:496) and the `linear_z_to_bias` of each block (:590-591)

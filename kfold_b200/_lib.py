@@ -42,6 +42,8 @@ _SIGNATURES = {
                     c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_apb_cross_fwd": [c_void_p] * 10 + [c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_apb_window_fwd": [c_void_p] * 10 + [c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_void_p],
     "kfb_window_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "kfb_tokens_to_atoms": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_atoms_to_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -79,6 +81,7 @@ _SIZE_FUNCS = {
     "kfb_triatt_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_cross_workspace_bytes": [c_int, c_int, c_int, c_int, c_int],
+    "kfb_apb_window_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_cross_workspace_bytes_precise": [c_int, c_int, c_int, c_int],
     "kfb_trimul_workspace_bytes": [c_int, c_int, c_int],
 }

@@ -69,7 +69,7 @@ __device__ __forceinline__ uint32_t small_operand_row_offset(int r) { return (r 
 //                core executes in order, so S(t+3) cannot overtake the P V product that reads the buffer)
 // S runs up to three half tiles ahead of the softmax, so the softmax warps never wait for the tensor core or for the
 // issuing warp, and four independent softmax warps per scheduler hide each other's tensor-memory and MUFU latencies.
-template <int DPAD, int R>
+template <int DPAD, int R, bool WIN>
 __global__ void __launch_bounds__(AttCfg<DPAD, R>::kThreads, AttCfg<DPAD, R>::kTwoPerSm ? 2 : 1)
 attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
@@ -101,7 +101,8 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int qb = blockIdx.x;
   const int h = blockIdx.y;
   const int b0 = blockIdx.z * R;  // first batch entry of this CTA
-  const int nkv = (p.lk + kBKV - 1) / kBKV;
+  // window mode: a query block of 128 atoms = four windows sees the 256 atoms that start 48 before it (two key tiles)
+  const int nkv = WIN ? 2 : (p.lk + kBKV - 1) / kBKV;
   const int nhalf = 2 * nkv;
   long long* trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
 #define KFB_STAMP(slot) do { if (trace != nullptr) trace[slot] = clock64(); } while (0)
@@ -139,7 +140,10 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   if (warp >= 4 && warp < 8) {
     const int r = (warp - 4) * 32 + lane;
     const uint32_t off = small_operand_row_offset(r);
-    *reinterpret_cast<uint4*>(s_e0 + off) = make_uint4(0x3F80u, 0, 0, 0);
+    // e0: a one in column 0; window mode: a one in column r / 32, the window of query row r (four windows per block)
+    const int e_col = WIN ? (r >> 5) : 0;
+    *reinterpret_cast<uint4*>(s_e0 + off) = make_uint4(e_col == 0 ? 0x3F80u : (e_col == 1 ? 0x3F800000u : 0u),
+                                                      e_col == 2 ? 0x3F80u : (e_col == 3 ? 0x3F800000u : 0u), 0, 0);
     *reinterpret_cast<uint4*>(s_e0 + off + 128) = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int u = 0; u < R * 3; ++u)
@@ -159,8 +163,11 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ptx::tma_load_3d(s_q + g * Cfg::kQBytes, &tm_q, &q_full[g], p.q_col0 + h * DPAD, qb * kBQ, b0 + g);
       }
       const int bias_g = b0 / p.bias_div;
-      const int bias_b = p.bias_mod > 0 ? bias_g * p.bias_mod + b0 % p.bias_mod : bias_g;
+      // window mode: batch entries are samples, bias_mod windows per sample, this block holds windows 4 qb .. 4 qb + 3
+      const int bias_b = WIN ? bias_g * p.bias_mod + qb * 4 : (p.bias_mod > 0 ? bias_g * p.bias_mod + b0 % p.bias_mod : bias_g);
       const int bias_z = p.bias_head_major > 0 ? h * p.bias_head_major + bias_b : bias_b * p.heads + h;
+      const int bias_zstep = p.bias_head_major > 0 ? 1 : p.heads;   // from one window's bias to the next
+      const int key_base = WIN ? qb * kBQ - 48 : 0;               // first key of this block's key range
       bool ok = true;
       int bst = 0;
       uint32_t bpar = 0;   // ring position of the bias half tiles
@@ -170,14 +177,24 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           const int slot = g * kStages + st;
           if (!ptx::mbar_wait(&kv_empty[slot], ((j / kStages) & 1) ^ 1, 201)) { ok = false; break; }
           ptx::mbar_expect_tx(&kv_full[slot], Cfg::kKBytes + Cfg::kVBytes);
-          ptx::tma_load_3d(s_k + slot * Cfg::kKBytes, &tm_k, &kv_full[slot], p.k_col0 + h * DPAD, j * kBKV, b0 + g);
-          ptx::tma_load_3d(s_v + slot * Cfg::kVBytes, &tm_v, &kv_full[slot], j * kBKV, h * DPAD, b0 + g);
-          ptx::tma_load_3d(s_v + slot * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[slot], j * kBKV + 64, h * DPAD, b0 + g);
+          // (window mode: rows before atom 0 or past the last atom are outside the tensor and arrive as zeros)
+          ptx::tma_load_3d(s_k + slot * Cfg::kKBytes, &tm_k, &kv_full[slot], p.k_col0 + h * DPAD, key_base + j * kBKV, b0 + g);
+          ptx::tma_load_3d(s_v + slot * Cfg::kVBytes, &tm_v, &kv_full[slot], key_base + j * kBKV, h * DPAD, b0 + g);
+          ptx::tma_load_3d(s_v + slot * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[slot], key_base + j * kBKV + 64, h * DPAD, b0 + g);
         }
         for (int hf = 0; ok && hf < 2; ++hf) {
           if (!ptx::mbar_wait(&bias_empty[bst], bpar ^ 1, 202)) { ok = false; break; }
           ptx::mbar_expect_tx(&bias_full[bst], Cfg::kTileBytes);
-          ptx::tma_load_3d(s_bias + bst * Cfg::kTileBytes, &tm_b, &bias_full[bst], j * kBKV + hf * 64, qb * kBQ, bias_z);
+          if (WIN) {
+            // four boxes of 32 rows: window w of the block keeps its bias by window-local key, and its key 0 is key
+            // 32 w of the block's range, so the half tile's 64 keys are local keys (j 128 + hf 64 - 32 w) ... + 63; what
+            // falls outside [0, 128) arrives as zeros (those keys are masked as absent for that window)
+            for (int wq = 0; wq < 4; ++wq)
+              ptx::tma_load_3d(s_bias + bst * Cfg::kTileBytes + wq * 4096, &tm_b, &bias_full[bst], j * kBKV + hf * 64 - 32 * wq, 0,
+                               bias_z + wq * bias_zstep);
+          } else {
+            ptx::tma_load_3d(s_bias + bst * Cfg::kTileBytes, &tm_b, &bias_full[bst], j * kBKV + hf * 64, qb * kBQ, bias_z);
+          }
           if (++bst == Cfg::kBiasStages) { bst = 0; bpar ^= 1u; }
         }
       }
@@ -271,15 +288,33 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int swz = r & 7;
 
     // stream 0 provides the mask operand: this thread writes key j*128 + r of tile j
+    // code of a key: 0 masked (the reference's finite -1e9), 1 valid, 2 absent.  Window mode returns four codes, two
+    // bits each, one per window of the block: key `key` of the block's range is atom key_base + key; window w sees it
+    // as its local key (key - 32 w) when that lies in [0, 128), atoms outside the molecule count as masked there.
     auto load_mask_byte = [&](int j) -> int {
       const int key = j * kBKV + r;
+      if (WIN) {
+        const int atom = qb * kBQ - 48 + key;
+        const int in_band = (atom >= 0 && atom < p.lk && mrow[static_cast<long long>(atom) * p.m_k]) ? 1 : 0;
+        int code = 0;
+#pragma unroll
+        for (int wq = 0; wq < 4; ++wq) code |= ((key >= 32 * wq && key < 32 * wq + kBKV) ? in_band : 2) << (2 * wq);
+        return code;
+      }
       if (key >= p.lk) return 2;
       return mrow[static_cast<long long>(key) * p.m_k] ? 1 : 0;
     };
-    auto store_mask_value = [&](int buf, int code) {
+    auto mask_bits = [](int code) -> uint32_t {
       const float mv = code == 2 ? kAbsent : (code == 1 ? 0.f : kMasked);
-      const uint32_t bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(mv)));
-      *reinterpret_cast<uint4*>(my_maskrow + buf * Cfg::kSmallBytes) = make_uint4(bits, 0, 0, 0);
+      return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(mv)));
+    };
+    auto store_mask_value = [&](int buf, int code) {
+      uint4 v = make_uint4(mask_bits(code & 3), 0, 0, 0);
+      if (WIN) {
+        v.x |= mask_bits((code >> 2) & 3) << 16;
+        v.y = mask_bits((code >> 4) & 3) | (mask_bits((code >> 6) & 3) << 16);
+      }
+      *reinterpret_cast<uint4*>(my_maskrow + buf * Cfg::kSmallBytes) = v;
     };
     if (u == 0) {
       store_mask_value(0, load_mask_byte(0));
@@ -506,7 +541,7 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 static long long* g_attention_trace = nullptr;
 void set_attention_trace(long long* device_buffer) { g_attention_trace = device_buffer; }
 
-template <int DPAD, int R>
+template <int DPAD, int R, bool WIN = false>
 static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
   using Cfg = AttCfg<DPAD, R>;
   static std::once_flag once[64];
@@ -514,7 +549,7 @@ static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
   KFB_CUDA(cudaGetDevice(&dev));
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(attention_bias_kernel<DPAD, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(attention_bias_kernel<DPAD, R, WIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::kSmemBytes);
   });
   KFB_CUDA(attr_err);
@@ -539,15 +574,23 @@ static int launch_cfg(cudaStream_t stream, const AttnParams& p) {
   }
   {
     const int bias_batches = p.bias_head_major > 0 ? p.bias_head_major : cdiv(p.batch, p.bias_div) * (p.bias_mod > 0 ? p.bias_mod : 1);
-    const uint64_t dims[3] = {(uint64_t)p.lk, (uint64_t)p.lq, (uint64_t)bias_batches * p.heads};
-    const uint64_t str[2] = {(uint64_t)p.ldb * 2, (uint64_t)p.lq * p.ldb * 2};
-    const uint32_t box[3] = {64, kBQ, 1};
-    KFB_TRY(make_tmap(&tb, p.bias, 2, 3, dims, str, box, 128));
+    if (p.win) {
+      // one bias per window: [z][32 queries][128 local keys], fetched in boxes of 32 rows
+      const uint64_t dims[3] = {128, 32, (uint64_t)bias_batches * p.heads};
+      const uint64_t str[2] = {128 * 2, 32 * 128 * 2};
+      const uint32_t box[3] = {64, 32, 1};
+      KFB_TRY(make_tmap(&tb, p.bias, 2, 3, dims, str, box, 128));
+    } else {
+      const uint64_t dims[3] = {(uint64_t)p.lk, (uint64_t)p.lq, (uint64_t)bias_batches * p.heads};
+      const uint64_t str[2] = {(uint64_t)p.ldb * 2, (uint64_t)p.lq * p.ldb * 2};
+      const uint32_t box[3] = {64, kBQ, 1};
+      KFB_TRY(make_tmap(&tb, p.bias, 2, 3, dims, str, box, 128));
+    }
   }
   dim3 grid(cdiv(p.lq, kBQ), p.heads, p.batch / R);
   {
     LaunchScope scope(stream, p.tag ? p.tag : "attention");
-    attention_bias_kernel<DPAD, R><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tb, p);
+    attention_bias_kernel<DPAD, R, WIN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tb, p);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
@@ -564,6 +607,11 @@ int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
   KFB_CHECK_ARG(p.bias_head_major == 0 || p.bias_head_major >= cdiv(p.batch, p.bias_div) * (p.bias_mod > 0 ? p.bias_mod : 1),
                 "attention: head-major bias with %d batches is too small", p.bias_head_major);
   KFB_CHECK_ARG(p.batch <= 65535, "attention: batch %d exceeds the grid z limit", p.batch);
+  if (p.win) {
+    KFB_CHECK_ARG(p.dpad == 32 && p.lq == p.lk && p.lq % 32 == 0 && p.bias_mod == p.lq / 32,
+                  "attention: window mode needs head dim <= 32, Lq == Lk a multiple of 32 and bias_mod == Lq / 32 windows");
+    return launch_cfg<32, 1, true>(stream, p);
+  }
   if (p.dpad == 32) {
     // One row group per CTA with two CTAs resident per SM is the default: the two CTAs interleave their
     // softmax and tensor-core phases better than two row groups inside one CTA do (measured 6% faster at

@@ -44,6 +44,12 @@ struct AttnParams {
   // 0: bias stored [bias_batches][heads][lq][ldb]; n > 0: stored [heads][n bias batches][lq][ldb] (head-major, as one
   // projection of all heads of several layers at once writes it)
   int bias_head_major;
+  // window mode (atom transformers): batch entries are samples of lq == lk atoms; query q attends the 128 atoms
+  // 32 (q / 32) - 48 ... + 79 (atoms outside [0, lk) count as masked), with one bias [32][128] per window:
+  // bias_mod = lk / 32 windows per sample, bias_div = samples that share the biases.  A CTA takes 128 queries =
+  // four windows and walks the 256 atoms that start 48 before them; a window's band inside that range is enforced
+  // through the mask operand (one column per window), its bias rows are fetched by window-local key.
+  int win;
   // key mask (0/1 bytes): element (b, k) at mask + b_hi*m_hi + b_lo*m_lo + k*m_k with b_hi = b / mask_lo_extent
   const unsigned char* mask; long long m_hi, m_lo, m_k; int mask_lo_extent;
   // optional gate logits, addressed like q

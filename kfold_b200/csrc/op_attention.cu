@@ -836,4 +836,118 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
   return KFB_OK;
 }
 
+KFB_API size_t kfb_apb_window_workspace_bytes(int batch, int l, int c, int heads) {
+  ApbCrossWs w;
+  return carve_apb_cross(w, nullptr, batch, l, l, c, heads);
+}
+
+KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
+                               const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
+                               const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
+                               void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_share,
+                               int mask_share, int bias_head_major, int out_dtype, void* stream_) {
+  KFB_CHECK_ARG(x_q && x_k && pair_bias && mask && w_q_packed && w_kv_packed && w_out && out && workspace,
+                "apb_window: null pointer");
+  KFB_CHECK_ARG(out_dtype == KFB_BF16 || out_dtype == KFB_FP32, "apb_window: dtype %d (bf16 or fp32 output, bf16 compute)", out_dtype);
+  KFB_CHECK_ARG(batch >= 1 && l >= 32 && l % 32 == 0, "apb_window: %d atoms must be a positive multiple of 32", l);
+  KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "apb_window: c=%d heads=%d", c, heads);
+  KFB_CHECK_ARG(bias_share >= 1 && batch % bias_share == 0 && mask_share >= 1 && batch % mask_share == 0 && bias_head_major >= 0,
+                "apb_window: batch %d bias_share %d mask_share %d", batch, bias_share, mask_share);
+  const int d = c / heads;
+  KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 32, "apb_window: head dim %d not in {16, 24, 32}", d);
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "apb_window: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  const long long rows = static_cast<long long>(batch) * l;
+  if (out_gate == nullptr || gate_rows <= 0) gate_rows = rows;
+  KFB_CHECK_ARG(rows % gate_rows == 0 && gate_rows < (1ll << 31), "apb_window: %lld rows are not a multiple of gate_rows %lld", rows,
+                gate_rows);
+  const int gate_reps = static_cast<int>(rows / gate_rows);
+  const int dp = dpad_of(d), hdp = heads * dp;
+  ApbCrossWs w;
+  const size_t need = carve_apb_cross(w, workspace, batch, l, l, c, heads);
+  KFB_CHECK_ARG(workspace_bytes >= need, "apb_window: workspace %zu < %zu bytes", workspace_bytes, need);
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(rows);
+    p.o_extent = 1;
+    p.batch = 1;
+    p.n_cols = 2 * hdp;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(w.qg, 2 * hdp, 2 * hdp, 0, 0, 0);
+    p.col_bias = q_bias;
+    GemmOperandA a = {x_q, c, 0, 0};
+    GemmOperandB b = {w_q_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "apb_window_q_proj"));
+  }
+  {
+    // keys of the un-windowed atoms: k position-major, v transposed per sample (atoms contiguous)
+    GemmParams p = {};
+    p.n_extent = l;
+    p.o_extent = batch;
+    p.batch = 1;
+    p.n_cols = 2 * hdp;
+    p.k_extent = c;
+    p.nseg = 2;
+    p.seg[0] = row_major_seg(w.kk, hdp, hdp, static_cast<long long>(l) * hdp, 0, 0, 0);
+    EpiSeg& sv = p.seg[1];
+    sv = {};
+    sv.col_begin = hdp;
+    sv.ncols = hdp;
+    sv.dst = w.vt;
+    sv.s_col = l;
+    sv.s_n = 1;
+    sv.s_o = static_cast<long long>(hdp) * l;
+    GemmOperandA a = {x_k, c, static_cast<long long>(l) * c, 0};
+    GemmOperandB b = {w_kv_packed, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 128, "apb_window_kv_proj"));
+  }
+  {
+    AttnParams p = {};
+    p.batch = batch;
+    p.heads = heads;
+    p.lq = l;
+    p.lk = l;
+    p.d = d;
+    p.dpad = dp;
+    p.win = 1;
+    p.q = w.qg; p.ldq = 2 * hdp; p.q_col0 = 0;
+    p.g = w.qg; p.ldg = 2 * hdp; p.g_col0 = hdp;
+    p.k = w.kk; p.ldk = hdp; p.k_col0 = 0;
+    p.vt = w.vt; p.ldv = l;
+    p.bias = pair_bias; p.ldb = 128; p.bias_div = bias_share; p.bias_mod = l / 32; p.bias_head_major = bias_head_major;
+    p.mask = mask;
+    p.mask_lo_extent = mask_share;   // batch entry b reads mask row b / mask_share
+    p.m_hi = l;
+    p.m_lo = 0;
+    p.m_k = 1;
+    p.out = w.og; p.ldo = c;
+    p.tag = "apb_window_attention";
+    KFB_TRY(launch_attention(stream, p));
+  }
+  {
+    GemmParams p = {};
+    p.n_extent = static_cast<int>(gate_rows);
+    p.o_extent = gate_reps;
+    p.batch = 1;
+    p.n_cols = c;
+    p.k_extent = c;
+    p.nseg = 1;
+    p.seg[0] = row_major_seg(out, c, c, gate_rows * c, 0, out_dtype == KFB_FP32);
+    p.col_bias = out_bias;
+    p.resid = resid;
+    if (out_gate != nullptr) {
+      p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // row r uses logits row r % gate_rows
+      p.g_col = 1;
+      p.g_n = c;
+      p.g_o = 0;
+      p.g_b = 0;
+    }
+    GemmOperandA a = {w.og, c, gate_rows * c, 0};
+    GemmOperandB b = {w_out, c, 0};
+    KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "apb_window_out_proj"));
+  }
+  return KFB_OK;
+}
+
 }  // extern "C"

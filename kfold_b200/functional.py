@@ -354,6 +354,49 @@ def attention_pair_bias_cross(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: t
     return out.to(want)
 
 
+def attention_pair_bias_window(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor, packed: dict,
+                               bias_share: int = 1, bias_head_major: bool = False, out_dtype=None,
+                               out_gate: torch.Tensor | None = None, resid: torch.Tensor | None = None) -> torch.Tensor:
+    """The windowed cross attention of the atom transformers on UN-windowed atoms (bf16 compute, head dim <= 32): query
+    atom q attends atoms 32 (q // 32) - 48 ... + 79 (model/layers/folding/utils.py:97-188); the kernel walks the windows.
+
+    x_q, x_k (batch, L, c), L a multiple of 32; mask (batch // mask_share, L) atom validity; pair_bias one (32, 128) bias
+    per window and head: (groups * L/32, H, 32, 128) or head-major (H, n, 32, 128); ``bias_share`` consecutive batch
+    entries (samples) use the same biases.  out_gate / resid as in attention_pair_bias_cross."""
+    _require_cuda(x_q, x_k, pair_bias, mask)
+    batch, l, c = x_q.shape
+    heads = packed["heads"]
+    if packed.get("precise"):
+        raise ValueError("attention_pair_bias_window: bfloat16 compute only (the float32 path gathers the windows)")
+    if tuple(x_k.shape) != (batch, l, c) or l % 32 or mask.shape[-1] != l or batch % mask.shape[0] or batch % bias_share:
+        raise ValueError(f"attention_pair_bias_window: x_q {tuple(x_q.shape)}, x_k {tuple(x_k.shape)}, mask {tuple(mask.shape)}")
+    windows = l // 32
+    nbb = pair_bias.shape[1] if bias_head_major else pair_bias.shape[0]
+    exp_shape = (heads, nbb, 32, 128) if bias_head_major else (nbb, heads, 32, 128)
+    if tuple(pair_bias.shape) != exp_shape or nbb < batch // bias_share * windows:
+        raise ValueError(f"attention_pair_bias_window: pair_bias {tuple(pair_bias.shape)}, expected {exp_shape} with at least "
+                         f"{batch // bias_share * windows} window biases")
+    bf = torch.bfloat16
+    xq, xk, pb = x_q.to(bf).contiguous(), x_k.to(bf).contiguous(), pair_bias.to(bf).contiguous()
+    mb = mask.to(torch.bool).contiguous().view(torch.uint8)
+    gate, gate_rows = None, 0
+    if out_gate is not None:
+        gate = out_gate.reshape(-1, c).to(bf).contiguous()
+        gate_rows = gate.shape[0]
+    want = out_dtype or (resid.dtype if resid is not None else x_q.dtype)
+    out = torch.empty(batch, l, c, dtype=want, device=x_q.device)
+    res = None if resid is None else resid.reshape(batch, l, c).to(want).contiguous()
+    lib = L.lib()
+    with torch.cuda.device(x_q.device):
+        ws = _workspace(x_q.device, lib.kfb_apb_window_workspace_bytes(batch, l, c, heads))
+        L.check(lib.kfb_apb_window_fwd(L.ptr(xq), L.ptr(xk), L.ptr(pb), L.ptr(mb), L.ptr(packed["w_q"]), L.ptr(packed["q_bias"]),
+                                       L.ptr(packed["w_kv"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
+                                       gate_rows, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, l, c, heads, bias_share,
+                                       batch // mask.shape[0], nbb if bias_head_major else 0, L.dtype_code(out.dtype),
+                                       L.stream_ptr()))
+    return out
+
+
 def attention_pair_bias_cross_bcast(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor,
                                     packed: dict, out_dtype=None, out_gate: torch.Tensor | None = None,
                                     resid: torch.Tensor | None = None) -> torch.Tensor:

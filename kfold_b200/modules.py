@@ -470,6 +470,12 @@ def _bias_sharing(lead: tuple, bias_lead: tuple):
     return (shared if windows == 1 else 1), 0
 
 
+def _index_share(lead: tuple, other_lead: tuple):
+    """n such that entry b of a batch with leading dims `lead` uses row b // n of a tensor whose leading dims `other_lead`
+    equal `lead` up to trailing 1s (those dims are shared); None for any other broadcast pattern."""
+    return F._index_sharing(lead, other_lead)
+
+
 class CrossAttentionPairBias(nn.Module, _PackedMixin):
     """Pair-bias cross attention of the atom windows (model/layers/folding/attention_pair_bias.py:161-260): AdaLN (or
     LayerNorm) prologues for the query and the key side, attention with `call_site="diffusion_local"`, and the
@@ -585,8 +591,9 @@ class LocalTransformerBlock(nn.Module):
 
 class LocalTransformerStack(nn.Module):
     """model/layers/folding/diffusion_transformer.py:419-512.  The whole stack works on the un-windowed atoms: the
-    prologues, the query-side projection, the output gate and the transition are row-wise, so only the key side is
-    gathered into windows; the pair biases of all blocks come from one pass over z."""
+    prologues, the projections, the output gate and the transition are row-wise, and under bfloat16 compute (head dim
+    <= 32) the attention kernel walks the windows itself; the float32 path gathers the key side into windows.  The pair
+    biases of all blocks come from one pass over z."""
 
     def __init__(self, channel_a: int, channel_s: int, channel_z: int, num_heads: int, num_blocks: int,
                  kernel_backend: str = "b200"):
@@ -616,37 +623,57 @@ class LocalTransformerStack(nn.Module):
         dt = torch.float32 if precise else torch.bfloat16
         length, c = a.shape[-2:]
         lead = tuple(a.shape[:-2])
-        to_qk = build_atom_to_qk_fn(length, a.device)
+        if length % WINDOW_Q != 0:
+            raise ValueError("Length must be divisible by 32")
         windows = length // WINDOW_Q
         h = self.num_heads
         with torch.autocast(a.device.type, enabled=False):
-            _, mask_k = to_qk(mask.to(torch.bool), -1)                                  # (*, W, 128)
-            mask_k = mask_k.expand(*lead, windows, WINDOW_K).reshape(-1, WINDOW_K)
             ln = self.layernorm_z
             bias_all = F.window_bias(z.to(dt), None if ln.weight is None else ln.weight.detach().float(),
                                      None if ln.bias is None else ln.bias.detach().float(),
                                      self._stacked_bias_weights(a.device, dt), ln.eps)      # (blocks*H, *z_lead, W, 32, 128)
             z_lead = tuple(z.shape[:-3])                                                 # includes the window dim
-            sharing = _bias_sharing(lead + (windows,), z_lead)
-            if sharing is None:
-                bias_all = bias_all.expand(bias_all.shape[0], *lead, windows, WINDOW_Q, WINDOW_K)
-                sharing = (1, 0)
-            bias_all = bias_all.reshape(len(self.blocks), h, -1, WINDOW_Q, WINDOW_K)
-            batch = mask_k.shape[0]
+            # bf16 compute with head dim <= 32: the kernel walks the windows over the un-gathered atoms
+            native = (not precise and c // h <= 32 and c % h == 0
+                      and _index_share(lead, tuple(z.shape[:-4])) is not None and _index_share(lead, tuple(mask.shape[:-1])) is not None)
+            if native:
+                batch = 1
+                for dd in lead:
+                    batch *= dd
+                bias_share = _index_share(lead, tuple(z.shape[:-4]))
+                mask2 = mask.to(torch.bool).reshape(-1, length)
+                bias_all = bias_all.reshape(len(self.blocks), h, -1, WINDOW_Q, WINDOW_K)
+            else:
+                to_qk = build_atom_to_qk_fn(length, a.device)
+                _, mask_k = to_qk(mask.to(torch.bool), -1)                              # (*, W, 128)
+                mask_k = mask_k.expand(*lead, windows, WINDOW_K).reshape(-1, WINDOW_K)
+                sharing = _bias_sharing(lead + (windows,), z_lead)
+                if sharing is None:
+                    bias_all = bias_all.expand(bias_all.shape[0], *lead, windows, WINDOW_Q, WINDOW_K)
+                    sharing = (1, 0)
+                bias_all = bias_all.reshape(len(self.blocks), h, -1, WINDOW_Q, WINDOW_K)
+                batch = mask_k.shape[0]
             for i, blk in enumerate(self.blocks):
                 att = blk.attention
                 xq, xk_flat, gate = att.normed_inputs(a, s, precise)
-                _, xk = to_qk(xk_flat, -2)                                              # (*, W, 128, c)
                 if gate is not None:
                     gl = tuple(gate.shape[:-2])
                     while gl and gl[0] == 1:
                         gl = gl[1:]
                     if gl != lead[len(lead) - len(gl):]:
                         gate = gate.expand(*lead, length, c)
-                a = F.attention_pair_bias_cross(
-                    xq.reshape(batch, WINDOW_Q, c), xk.reshape(batch, WINDOW_K, c), bias_all[i], mask_k,
-                    att._cross_packed(a.device, precise), bias_div=sharing[0], bias_mod=sharing[1], bias_head_major=True,
-                    out_dtype=a.dtype, out_gate=gate, resid=a).view(*lead, length, c)
+                pk = att._cross_packed(a.device, precise)
+                if native:
+                    a = F.attention_pair_bias_window(
+                        xq.reshape(batch, length, c), xk_flat.reshape(batch, length, c), bias_all[i], mask2, pk,
+                        bias_share=bias_share, bias_head_major=True, out_dtype=a.dtype, out_gate=gate,
+                        resid=a).view(*lead, length, c)
+                else:
+                    _, xk = to_qk(xk_flat, -2)                                          # (*, W, 128, c)
+                    a = F.attention_pair_bias_cross(
+                        xq.reshape(batch, WINDOW_Q, c), xk.reshape(batch, WINDOW_K, c), bias_all[i], mask_k, pk,
+                        bias_div=sharing[0], bias_mod=sharing[1], bias_head_major=True,
+                        out_dtype=a.dtype, out_gate=gate, resid=a).view(*lead, length, c)
                 a = blk.transition(a, s, residual=True, precise=precise)
         return a
 

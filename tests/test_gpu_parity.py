@@ -590,3 +590,25 @@ def test_token_atom_maps_against_reference_golden(dev):
     with pytest.raises(L.KfbError, match="900"):
         L.device_status()
     assert L.device_status() == 0
+
+
+@pytest.mark.parametrize("z_per_sample", [False, True])
+def test_local_transformer_stack_two_complexes(dev, z_per_sample):
+    """Two complexes x two samples, 7 windows (the last query block holds three of its four windows): the window pair
+    tensor shared by the samples of a complex, or one per sample; per-complex atom masks."""
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    rng = synth._Rng(64 + int(z_per_sample))
+    l, c, c_z, h, blocks = 224, 128, 16, 4, 2
+    w = synth.local_stack_weights(rng, c, c, c_z, h, blocks)
+    a, s = rng.normal(2, 2, l, c), rng.normal(2, 1, l, c)
+    z = rng.normal(2, 2 if z_per_sample else 1, l // 32, 32, 128, c_z)
+    mask = torch.stack([synth.token_mask(l, 200), synth.token_mask(l, 215)]).view(2, 1, l)
+    stack = M.LocalTransformerStack(c, c, c_z, h, blocks).to(dev)
+    stack.load_state_dict(w, strict=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = stack(a.to(dev), s.to(dev), z.to(dev), mask.to(dev)).cpu()
+    ref = _oracle_on(dev, O.local_transformer_stack, a, s, z, mask, w, h, blocks)
+    assert torch.isfinite(out).all()
+    keep = mask.expand(2, 2, l)
+    _check(*err_stats(out[keep], ref[keep]), "local stack, two complexes")
