@@ -192,8 +192,8 @@ KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads);
 KFB_API size_t kfb_apb_workspace_bytes_precise(int batch, int l, int c);
 KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
                         const float* proj_bias, const void* w_out, const float* out_bias, const void* out_gate,
-                        int gate_share, void* out, const void* resid, void* workspace, size_t workspace_bytes, int batch,
-                        int l, int c, int heads, int bias_div, int out_dtype, void* stream);
+                        int gate_share, long long gate_ld, void* out, const void* resid, void* workspace,
+                        size_t workspace_bytes, int batch, int l, int c, int heads, int bias_div, int out_dtype, void* stream);
 
 /*
  * Gated cross attention with pair bias on already-normalised inputs: queries from x_q, keys and values from x_k.
@@ -220,8 +220,8 @@ KFB_API size_t kfb_apb_cross_workspace_bytes(int batch, int lq, int lk, int c, i
 KFB_API size_t kfb_apb_cross_workspace_bytes_precise(int batch, int lq, int lk, int c);
 KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
                               const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
-                              const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
-                              void* workspace, size_t workspace_bytes, int batch, int lq, int lk, int c, int heads,
+                              const float* out_bias, const void* out_gate, long long gate_rows, long long gate_ld, void* out,
+                              const void* resid, void* workspace, size_t workspace_bytes, int batch, int lq, int lk, int c, int heads,
                               int bias_div, int bias_mod, int bias_head_major, int out_dtype, void* stream);
 
 /*
@@ -238,8 +238,8 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
 KFB_API size_t kfb_apb_window_workspace_bytes(int batch, int l, int c, int heads);
 KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
                                const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
-                               const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
-                               void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_share,
+                               const float* out_bias, const void* out_gate, long long gate_rows, long long gate_ld, void* out,
+                               const void* resid, void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_share,
                                int mask_share, int bias_head_major, int out_dtype, void* stream);
 
 /*
@@ -279,9 +279,12 @@ KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, con
  * the caller (kfb_layernorm + kfb_gemm_bf16) once per token and passed as `gate_shift`: bf16 [rows / samples, 2c]
  * (logits g, then v).  a : (rows, c) of `in_dtype`, rows ordered (group, sample, position) with `l` positions;
  * the `samples` diffusion samples of a group share one conditioning row per position.  out : bf16 (rows, c).
+ * gate_shift_ld (here) and gate_ld (kfb_apb_fwd, kfb_apb_cross_fwd, kfb_apb_window_fwd, kfb_cond_transition_fwd) are the
+ * element strides between consecutive rows of those tables, 0 for densely packed rows: the conditioning projections of
+ * all blocks of a stack can then be computed by one GEMM into one wide table of which every block reads its columns.
  */
-KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, void* out, long long rows, int c, int samples, int l,
-                          float eps, int in_dtype, void* stream);
+KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, long long gate_shift_ld, void* out, long long rows, int c,
+                          int samples, int l, float eps, int in_dtype, void* stream);
 
 /*
  * Conditioned transition: out = sigmoid(gate) * Linear_out(silu(u_a) * u_b) (+ resid), [u_a, u_b] = Linear(x).
@@ -300,7 +303,7 @@ KFB_API size_t kfb_linear_fp32_workspace_bytes(long long rows, int k);
 KFB_API int kfb_linear_fp32(const void* x, const void* w6, const float* bias, void* out, void* workspace,
                             size_t workspace_bytes, long long rows, int n, int k, void* stream);
 KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_packed, const void* w_out,
-                                    const void* out_gate, void* out, const void* resid, void* workspace,
+                                    const void* out_gate, long long gate_ld, void* out, const void* resid, void* workspace,
                                     size_t workspace_bytes, long long rows, int c, int hidden, int samples, int l, int dtype,
                                     void* stream);
 

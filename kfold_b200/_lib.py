@@ -38,11 +38,11 @@ _SIGNATURES = {
                        c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_triatt_fwd": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        ctypes.c_size_t, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+    "kfb_apb_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p,
                     c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_apb_cross_fwd": [c_void_p] * 10 + [c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
+    "kfb_apb_cross_fwd": [c_void_p] * 10 + [c_ll, c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_apb_window_fwd": [c_void_p] * 10 + [c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
+    "kfb_apb_window_fwd": [c_void_p] * 10 + [c_ll, c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void_p],
     "kfb_window_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "kfb_tokens_to_atoms": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -56,8 +56,8 @@ _SIGNATURES = {
     "kfb_pair_bias_rows_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int,
                                c_int, c_int, c_float, c_int, c_void_p],
     "kfb_linear_fp32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll, c_int, c_int, c_void_p],
-    "kfb_adaln_fwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "kfb_cond_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
+    "kfb_adaln_fwd": [c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_cond_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_transition_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t,
                            c_ll, c_int, c_int, c_float, c_int, c_void_p],

@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(128) layernorm_cm_split_kernel(const float* __
 // ------------------------------------------------------------------------------------------------
 template <typename TI, typename TO, typename TG, int G>
 __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ a, TO* __restrict__ y,
-                                                         const TG* __restrict__ gv, long long rows, int c,
+                                                         const TG* __restrict__ gv, long long gv_ld, long long rows, int c,
                                                          int samples, int l, float eps) {
   const int lane = threadIdx.x & 31;
   const long long warps_per_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
        row += warps_per_grid) {
     const TI* xr = a + row * c;
     const long long srow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
-    const TG* gr = gv + srow * 2 * c;
+    const TG* gr = gv + srow * gv_ld;
     float2 v[G];
     float s = 0.f;
 #pragma unroll
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
 }
 
 template <typename TI, typename TO, typename TG>
-static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const void* gv_, long long rows, int c,
+static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const void* gv_, long long gv_ld, long long rows, int c,
                           int samples, int l, float eps) {
   const TG* gv = static_cast<const TG*>(gv_);
   const int warps = 8;
@@ -280,7 +280,7 @@ static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const voi
   LaunchScope scope(stream, "adaln_rows");
 #define KFB_ADALN(GG)                                                                                          \
   adaln_rows_kernel<TI, TO, TG, GG><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(                  \
-      static_cast<const TI*>(a), static_cast<TO*>(y), gv, rows, c, samples, l, eps)
+      static_cast<const TI*>(a), static_cast<TO*>(y), gv, gv_ld, rows, c, samples, l, eps)
   if (g <= 2) KFB_ADALN(2);
   else if (g <= 6) KFB_ADALN(6);
   else if (g <= 12) KFB_ADALN(12);
@@ -295,17 +295,20 @@ static int adaln_dispatch(cudaStream_t stream, const void* a, void* y, const voi
 }
 
 int launch_adaln(cudaStream_t stream, const void* a, void* y, const void* gv, long long rows, int c, int samples,
-                 int l, float eps, int in_dtype, int out_dtype) {
+                 int l, float eps, int in_dtype, int out_dtype, long long gv_ld) {
+  if (gv_ld <= 0) gv_ld = 2ll * c;
+  KFB_CHECK_ARG(gv_ld >= 2ll * c && gv_ld % 2 == 0 && (reinterpret_cast<uintptr_t>(gv) & 7) == 0,
+                "adaln: gate/shift row stride %lld (at least 2c, even) or misaligned pointer", gv_ld);
   KFB_CHECK_ARG(rows >= 0 && c > 0 && c % 2 == 0 && samples >= 1 && l >= 1, "adaln: rows %lld c %d samples %d l %d", rows, c,
                 samples, l);
   KFB_CHECK_ARG(rows % (static_cast<long long>(samples) * l) == 0, "adaln: rows %lld is not a multiple of samples*l", rows);
   if (rows == 0) return KFB_OK;
   if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16)
-    return adaln_dispatch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+    return adaln_dispatch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, gv_ld, rows, c, samples, l, eps);
   if (in_dtype == KFB_FP32 && out_dtype == KFB_BF16)
-    return adaln_dispatch<float, __nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, rows, c, samples, l, eps);
+    return adaln_dispatch<float, __nv_bfloat16, __nv_bfloat16>(stream, a, y, gv, gv_ld, rows, c, samples, l, eps);
   if (in_dtype == KFB_FP32_PRECISE && out_dtype == KFB_FP32)  // everything fp32, gate / shift rows included
-    return adaln_dispatch<float, float, float>(stream, a, y, gv, rows, c, samples, l, eps);
+    return adaln_dispatch<float, float, float>(stream, a, y, gv, gv_ld, rows, c, samples, l, eps);
   set_error("adaln: unsupported dtype combination");
   return KFB_ERR_INVALID_ARGUMENT;
 }

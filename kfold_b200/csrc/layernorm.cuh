@@ -24,8 +24,9 @@ int launch_layernorm_cm(cudaStream_t stream, const void* t, __nv_bfloat16* y, co
 // Adaptive LayerNorm: y[r] = sigmoid(g[s(r)]) * LN(a[r]) + v[s(r)], LN without affine, fp32 statistics.
 // a, y: `rows` rows of c channels; gv: rows_s rows of [2c] (gate logits | shift), bf16.  Row r of a uses row
 // (r / (samples * l)) * l + r % l of gv: the conditioning is shared by the `samples` diffusion samples.
+// gv_ld: elements between consecutive gv rows (0 = 2c), for rows that are slices of a wider table.
 int launch_adaln(cudaStream_t stream, const void* a, void* y, const void* gv, long long rows, int c, int samples,
-                 int l, float eps, int in_dtype, int out_dtype);
+                 int l, float eps, int in_dtype, int out_dtype, long long gv_ld = 0);
 
 // LayerNorm folded into the following GEMM (see layernorm.cu): per-position (mean, rstd) of a channel-major tensor, and the
 // folded weights W' = gamma * W (bf16) with s1[n] = sum_k W'[n][k], s0[n] = sum_k beta[k] W[n][k].

@@ -492,8 +492,8 @@ KFB_API size_t kfb_apb_workspace_bytes(int batch, int l, int c, int heads) {
 
 KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned char* mask, const void* w_proj_packed,
                         const float* proj_bias, const void* w_out, const float* out_bias, const void* out_gate,
-                        int gate_share, void* out, const void* resid, void* workspace, size_t workspace_bytes, int batch,
-                        int l, int c, int heads, int bias_div, int out_dtype, void* stream_) {
+                        int gate_share, long long gate_ld, void* out, const void* resid, void* workspace,
+                        size_t workspace_bytes, int batch, int l, int c, int heads, int bias_div, int out_dtype, void* stream_) {
   KFB_CHECK_ARG(x && pair_bias && mask && w_proj_packed && w_out && out && workspace, "apb: null pointer");
   KFB_CHECK_ARG(is_dtype(out_dtype), "apb: bad dtype %d", out_dtype);
   KFB_CHECK_ARG(batch >= 1 && l >= 8 && l % 8 == 0, "apb: L=%d must be a positive multiple of 8 (pad in the caller)", l);
@@ -503,6 +503,8 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     KFB_CHECK_ARG(gate_share >= 1 && batch % gate_share == 0, "apb: batch %d not a multiple of gate_share %d", batch, gate_share);
   else
     gate_share = 1;
+  if (gate_ld <= 0) gate_ld = c;
+  KFB_CHECK_ARG(gate_ld >= c, "apb: gate row stride %lld below c=%d", gate_ld, c);
   const int d = c / heads;
   KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "apb: head dim %d not in {16, 24, ..., 64}", d);
   if (out_dtype == KFB_FP32_PRECISE) {
@@ -565,9 +567,9 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     if (out_gate != nullptr) {
       p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // fp32 logits in this mode
       p.g_col = 1;
-      p.g_n = c;
+      p.g_n = gate_ld;
       p.g_o = 0;
-      p.g_b = lc;
+      p.g_b = l * gate_ld;
     }
     GemmOperandA a = {wp.og6, c6, l * c6, l * c6 * gate_share};
     GemmOperandB b = {w_out, c6, 0};
@@ -639,9 +641,9 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     if (out_gate != nullptr) {
       p.gate = static_cast<const __nv_bfloat16*>(out_gate);
       p.g_col = 1;
-      p.g_n = c;
+      p.g_n = gate_ld;
       p.g_o = 0;
-      p.g_b = lc;
+      p.g_b = l * gate_ld;
     }
     GemmOperandA a = {w.og, c, lc, lc * gate_share};
     GemmOperandB b = {w_out, c, 0};
@@ -662,8 +664,8 @@ KFB_API size_t kfb_apb_cross_workspace_bytes_precise(int batch, int lq, int lk, 
 
 KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
                               const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
-                              const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
-                              void* workspace, size_t workspace_bytes, int batch, int lq, int lk, int c, int heads,
+                              const float* out_bias, const void* out_gate, long long gate_rows, long long gate_ld, void* out,
+                              const void* resid, void* workspace, size_t workspace_bytes, int batch, int lq, int lk, int c, int heads,
                               int bias_div, int bias_mod, int bias_head_major, int out_dtype, void* stream_) {
   KFB_CHECK_ARG(x_q && x_k && pair_bias && mask && w_q_packed && w_kv_packed && w_out && out && workspace,
                 "apb_cross: null pointer");
@@ -679,6 +681,8 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
   cudaStream_t stream = as_stream(stream_);
   const long long rows_q = static_cast<long long>(batch) * lq, rows_k = static_cast<long long>(batch) * lk;
   if (out_gate == nullptr || gate_rows <= 0) gate_rows = rows_q;
+  if (gate_ld <= 0) gate_ld = c;
+  KFB_CHECK_ARG(gate_ld >= c, "apb_cross: gate row stride %lld below c=%d", gate_ld, c);
   KFB_CHECK_ARG(rows_q % gate_rows == 0 && gate_rows < (1ll << 31), "apb_cross: %lld query rows are not a multiple of gate_rows %lld",
                 rows_q, gate_rows);
   const int gate_reps = static_cast<int>(rows_q / gate_rows);
@@ -740,7 +744,7 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
     if (out_gate != nullptr) {
       p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // fp32 logits in this mode; query row r uses row r % gate_rows
       p.g_col = 1;
-      p.g_n = c;
+      p.g_n = gate_ld;
       p.g_o = 0;
       p.g_b = 0;
     }
@@ -825,7 +829,7 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
     if (out_gate != nullptr) {
       p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // query row r uses logits row r % gate_rows
       p.g_col = 1;
-      p.g_n = c;
+      p.g_n = gate_ld;
       p.g_o = 0;
       p.g_b = 0;
     }
@@ -843,8 +847,8 @@ KFB_API size_t kfb_apb_window_workspace_bytes(int batch, int l, int c, int heads
 
 KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pair_bias, const unsigned char* mask,
                                const void* w_q_packed, const float* q_bias, const void* w_kv_packed, const void* w_out,
-                               const float* out_bias, const void* out_gate, long long gate_rows, void* out, const void* resid,
-                               void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_share,
+                               const float* out_bias, const void* out_gate, long long gate_rows, long long gate_ld, void* out,
+                               const void* resid, void* workspace, size_t workspace_bytes, int batch, int l, int c, int heads, int bias_share,
                                int mask_share, int bias_head_major, int out_dtype, void* stream_) {
   KFB_CHECK_ARG(x_q && x_k && pair_bias && mask && w_q_packed && w_kv_packed && w_out && out && workspace,
                 "apb_window: null pointer");
@@ -859,6 +863,8 @@ KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pai
   cudaStream_t stream = as_stream(stream_);
   const long long rows = static_cast<long long>(batch) * l;
   if (out_gate == nullptr || gate_rows <= 0) gate_rows = rows;
+  if (gate_ld <= 0) gate_ld = c;
+  KFB_CHECK_ARG(gate_ld >= c, "apb_window: gate row stride %lld below c=%d", gate_ld, c);
   KFB_CHECK_ARG(rows % gate_rows == 0 && gate_rows < (1ll << 31), "apb_window: %lld rows are not a multiple of gate_rows %lld", rows,
                 gate_rows);
   const int gate_reps = static_cast<int>(rows / gate_rows);
@@ -939,7 +945,7 @@ KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pai
     if (out_gate != nullptr) {
       p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // row r uses logits row r % gate_rows
       p.g_col = 1;
-      p.g_n = c;
+      p.g_n = gate_ld;
       p.g_o = 0;
       p.g_b = 0;
     }

@@ -10,13 +10,13 @@ using namespace kfb;
 extern "C" {
 
 // y = sigmoid(gv[:, :c]) * LayerNorm(a) + gv[:, c:]
-KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, void* out, long long rows, int c, int samples, int l,
-                          float eps, int in_dtype, void* stream) {
+KFB_API int kfb_adaln_fwd(const void* a, const void* gate_shift, long long gate_shift_ld, void* out, long long rows, int c,
+                          int samples, int l, float eps, int in_dtype, void* stream) {
   KFB_CHECK_ARG(a && gate_shift && out, "adaln: null pointer");
   KFB_CHECK_ARG(is_dtype(in_dtype), "adaln: bad dtype %d", in_dtype);
   // KFB_FP32_PRECISE: a, gate_shift and out are all fp32
   return launch_adaln(as_stream(stream), a, out, gate_shift, rows, c, samples, l, eps, in_dtype,
-                      in_dtype == KFB_FP32_PRECISE ? KFB_FP32 : KFB_BF16);
+                      in_dtype == KFB_FP32_PRECISE ? KFB_FP32 : KFB_BF16, gate_shift_ld);
 }
 
 // y = x W^T (+ bias) at fp32 accuracy: x fp32 [rows, k], w6 the bf16 triple split of W [n, 6k], out fp32 [rows, n]
@@ -58,10 +58,12 @@ KFB_API size_t kfb_cond_transition_workspace_bytes(long long rows, int hidden) {
 
 // out = sigmoid(gate[s(r)]) * (silu(u_a) * u_b) W_out^T  (+ resid),  [u_a, u_b] = x W_swiglu^T,  x already AdaLN-normalised
 KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_packed, const void* w_out,
-                                    const void* out_gate, void* out, const void* resid, void* workspace,
+                                    const void* out_gate, long long gate_ld, void* out, const void* resid, void* workspace,
                                     size_t workspace_bytes, long long rows, int c, int hidden, int samples, int l, int dtype,
                                     void* stream_) {
   KFB_CHECK_ARG(x_normed && w_swiglu_packed && w_out && out_gate && out && workspace, "cond_transition: null pointer");
+  if (gate_ld <= 0) gate_ld = c;
+  KFB_CHECK_ARG(gate_ld >= c, "cond_transition: gate row stride %lld below c=%d", gate_ld, c);
   KFB_CHECK_ARG(is_dtype(dtype), "cond_transition: bad dtype %d", dtype);
   KFB_CHECK_ARG(rows >= 1 && rows < (1ll << 31) && samples >= 1 && l >= 1 && rows % (static_cast<long long>(samples) * l) == 0,
                 "cond_transition: rows %lld samples %d l %d", rows, samples, l);
@@ -108,9 +110,9 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
     p.resid = resid;
     p.gate = static_cast<const __nv_bfloat16*>(out_gate);  // fp32 logits in this mode
     p.g_col = 1;
-    p.g_n = c;
+    p.g_n = gate_ld;
     p.g_o = 0;
-    p.g_b = lc;
+    p.g_b = l * gate_ld;
     GemmOperandA a = {h6, 6ll * hidden, lh6, lh6 * samples};
     GemmOperandB b = {w_out, 6ll * hidden, 0};
     return launch_gemm_bf16(stream, a, b, p, 0, "cond_transition_out_precise");
@@ -145,9 +147,9 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
     p.resid = resid;
     p.gate = static_cast<const __nv_bfloat16*>(out_gate);
     p.g_col = 1;
-    p.g_n = c;
+    p.g_n = gate_ld;
     p.g_o = 0;
-    p.g_b = lc;
+    p.g_b = l * gate_ld;
     GemmOperandA a = {h, hidden, lh, lh * samples};
     GemmOperandB b = {w_out, hidden, 0};
     KFB_TRY(launch_gemm_bf16(stream, a, b, p, 0, "cond_transition_out"));

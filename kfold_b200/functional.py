@@ -31,6 +31,25 @@ def release_workspaces() -> None:
     _workspaces.clear()
 
 
+def _rows(t: torch.Tensor, c: int, dtype=None):
+    """(tensor, rows, row stride) of `t` (..., c) seen as rows of c contiguous elements at a constant stride: a column
+    slice of a wider row-major table is passed as it lies, anything else is made contiguous first."""
+    if dtype is not None and t.dtype != dtype:
+        t = t.to(dtype)
+    rows = t.numel() // c
+    if t.stride(-1) == 1 and t.dim() >= 2:
+        ld = t.stride(-2) if t.shape[-2] > 1 else c
+        ok, span = ld >= c, ld * t.shape[-2]
+        for d in range(t.dim() - 3, -1, -1):
+            if t.shape[d] != 1 and t.stride(d) != span:
+                ok = False
+            span *= t.shape[d]
+        if ok and (t.data_ptr() % 16 == 0) and ld % 8 == 0:
+            return t, rows, ld
+    t = t.reshape(-1, c).contiguous()
+    return t, rows, c
+
+
 def _require_cuda(*ts: torch.Tensor) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -174,9 +193,9 @@ def adaln(a: torch.Tensor, gate_shift: torch.Tensor, samples: int, eps: float = 
     if precise:
         a2 = a2.float()
     out = torch.empty(a2.shape, dtype=torch.float32 if precise else torch.bfloat16, device=a.device)
-    gs = gate_shift.reshape(-1, 2 * c).contiguous()
+    gs, _, gs_ld = _rows(gate_shift, 2 * c)
     with torch.cuda.device(a.device):
-        L.check(L.lib().kfb_adaln_fwd(L.ptr(a2), L.ptr(gs), L.ptr(out), a2.shape[0], c, samples, l, eps,
+        L.check(L.lib().kfb_adaln_fwd(L.ptr(a2), L.ptr(gs), gs_ld, L.ptr(out), a2.shape[0], c, samples, l, eps,
                                       L.KFB_FP32_PRECISE if precise else L.dtype_code(a2.dtype), L.stream_ptr()))
     return out.view(a.shape)
 
@@ -193,16 +212,16 @@ def conditioned_transition(x_normed: torch.Tensor, packed: dict, out_gate: torch
     want = out_dtype or (resid.dtype if resid is not None else x_normed.dtype)
     out = torch.empty(rows, c, dtype=torch.float32 if precise else want, device=x2.device)
     r2 = None if resid is None else resid.reshape(-1, c).contiguous()
-    g2 = out_gate.reshape(-1, c).contiguous()
+    g2, _, g_ld = _rows(out_gate, c, torch.float32 if precise else None)
     if precise:
-        x2, g2 = x2.float(), g2.float()
+        x2 = x2.float()
         r2 = None if r2 is None else r2.float()
     lib = L.lib()
     with torch.cuda.device(x2.device):
         need = (lib.kfb_cond_transition_workspace_bytes_precise(rows, c, hidden) if precise
                 else lib.kfb_cond_transition_workspace_bytes(rows, hidden))
         ws = _workspace(x2.device, need)
-        L.check(lib.kfb_cond_transition_fwd(L.ptr(x2), L.ptr(packed["w_swiglu"]), L.ptr(packed["w_out"]), L.ptr(g2), L.ptr(out),
+        L.check(lib.kfb_cond_transition_fwd(L.ptr(x2), L.ptr(packed["w_swiglu"]), L.ptr(packed["w_out"]), L.ptr(g2), g_ld, L.ptr(out),
                                             L.ptr(r2), L.ptr(ws), ws.numel(), rows, c, hidden, samples, l,
                                             L.KFB_FP32_PRECISE if precise else L.dtype_code(out.dtype), L.stream_ptr()))
     return out.view(x_normed.shape).to(want)
@@ -251,12 +270,12 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
         xb = torch.nn.functional.pad(xb, (0, 0, 0, lp - l))
         pbb = torch.nn.functional.pad(pbb, (0, lp - l, 0, lp - l))
         mb = torch.nn.functional.pad(mb, (0, lp - l))
-    gate = None
+    gate, gate_ld = None, 0
     if out_gate is not None:
-        gate = out_gate.reshape(-1, l, c).to(act)
         if lp != l:
-            gate = torch.nn.functional.pad(gate, (0, 0, 0, lp - l))
-        gate = gate.contiguous()
+            gate = torch.nn.functional.pad(out_gate.reshape(-1, l, c).to(act), (0, 0, 0, lp - l)).contiguous()
+        else:
+            gate, _, gate_ld = _rows(out_gate, c, act)
     res = None
     if resid is not None:
         res = resid.reshape(batch, l, c)
@@ -274,7 +293,7 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
         ws = _workspace(x.device, need)
         L.check(lib.kfb_apb_fwd(L.ptr(xb), L.ptr(pbb), L.ptr(mb.view(torch.uint8)), L.ptr(packed["w_proj"]),
                                 L.ptr(packed["proj_bias"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
-                                gate_share, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div,
+                                gate_share, gate_ld, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lp, c, heads, bias_div,
                                 L.KFB_FP32_PRECISE if precise else L.dtype_code(out.dtype), L.stream_ptr()))
     return out[:, :l].reshape(*lead, l, c).to(want)
 
@@ -329,10 +348,9 @@ def attention_pair_bias_cross(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: t
     xq, xk = x_q.to(act).contiguous(), x_k.to(act).contiguous()
     pb = pair_bias.to(act).contiguous()
     mb = mask.to(torch.bool).contiguous().view(torch.uint8)
-    gate, gate_rows = None, 0
+    gate, gate_rows, gate_ld = None, 0, 0
     if out_gate is not None:
-        gate = out_gate.reshape(-1, c).to(act).contiguous()
-        gate_rows = gate.shape[0]
+        gate, gate_rows, gate_ld = _rows(out_gate, c, act)
     res = None
     if resid is not None:
         res = resid.reshape(batch, lq, c)
@@ -348,7 +366,7 @@ def attention_pair_bias_cross(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: t
         ws = _workspace(x_q.device, need)
         L.check(lib.kfb_apb_cross_fwd(L.ptr(xq), L.ptr(xk), L.ptr(pb), L.ptr(mb), L.ptr(packed["w_q"]), L.ptr(packed["q_bias"]),
                                       L.ptr(packed["w_kv"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
-                                      gate_rows, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lq, lk, c, heads,
+                                      gate_rows, gate_ld, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, lq, lk, c, heads,
                                       bias_div, bias_mod, nbb if bias_head_major else 0,
                                       L.KFB_FP32_PRECISE if precise else L.dtype_code(out.dtype), L.stream_ptr()))
     return out.to(want)
@@ -379,10 +397,9 @@ def attention_pair_bias_window(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: 
     bf = torch.bfloat16
     xq, xk, pb = x_q.to(bf).contiguous(), x_k.to(bf).contiguous(), pair_bias.to(bf).contiguous()
     mb = mask.to(torch.bool).contiguous().view(torch.uint8)
-    gate, gate_rows = None, 0
+    gate, gate_rows, gate_ld = None, 0, 0
     if out_gate is not None:
-        gate = out_gate.reshape(-1, c).to(bf).contiguous()
-        gate_rows = gate.shape[0]
+        gate, gate_rows, gate_ld = _rows(out_gate, c, bf)
     want = out_dtype or (resid.dtype if resid is not None else x_q.dtype)
     out = torch.empty(batch, l, c, dtype=want, device=x_q.device)
     res = None if resid is None else resid.reshape(batch, l, c).to(want).contiguous()
@@ -391,7 +408,7 @@ def attention_pair_bias_window(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: 
         ws = _workspace(x_q.device, lib.kfb_apb_window_workspace_bytes(batch, l, c, heads))
         L.check(lib.kfb_apb_window_fwd(L.ptr(xq), L.ptr(xk), L.ptr(pb), L.ptr(mb), L.ptr(packed["w_q"]), L.ptr(packed["q_bias"]),
                                        L.ptr(packed["w_kv"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
-                                       gate_rows, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, l, c, heads, bias_share,
+                                       gate_rows, gate_ld, L.ptr(out), L.ptr(res), L.ptr(ws), ws.numel(), batch, l, c, heads, bias_share,
                                        batch // mask.shape[0], nbb if bias_head_major else 0, L.dtype_code(out.dtype),
                                        L.stream_ptr()))
     return out

@@ -267,6 +267,55 @@ def _sample_share(a: torch.Tensor, s: torch.Tensor) -> int:
     return 1
 
 
+class _ConditioningBank:
+    """The conditioning projections of EVERY block of a stack from one LayerNorm and two GEMMs.
+
+    Each AdaLN computes sigmoid-gate and shift rows from LayerNorm_s(s) with its own scale, and each block adds output
+    gates Linear(s).  All of them depend on s alone, so the stack normalises s once (the per-AdaLN scale is folded into
+    that AdaLN's weight columns), multiplies once by all stacked AdaLN matrices and once by all stacked gate matrices,
+    and every block reads its columns of the two wide tables in place (the kernels take a row stride).
+    bfloat16 compute only: folding the scale moves a bf16 rounding, which the float32-accurate path must not do."""
+
+    def __init__(self):
+        self._key = None
+        self._packed = None
+
+    def _pack(self, adalns, gates, device):
+        params = [p for m in adalns for p in (m.layernorm_s.weight, m.linear_g.weight, m.linear_g.bias, m.linear_bias.weight)]
+        params += [p for g in gates for p in (g.weight, g.bias)]
+        key = (device,) + tuple(v for p in params for v in (p.data_ptr(), None if torch.is_inference(p) else p._version))
+        if self._key != key:
+            w1, b1 = [], []
+            for m in adalns:
+                gamma = m.layernorm_s.weight.detach().float()[None, :]
+                w1 += [m.linear_g.weight.detach().float() * gamma, m.linear_bias.weight.detach().float() * gamma]
+                b1 += [m.linear_g.bias.detach().float(), torch.zeros_like(m.linear_g.bias, dtype=torch.float32)]
+            w2 = [g.weight.detach().float() for g in gates]
+            b2 = [g.bias.detach().float() for g in gates]
+            bf = torch.bfloat16
+            self._packed = (torch.cat(w1).to(device, bf).contiguous(), torch.cat(b1).to(device).contiguous(),
+                            torch.cat(w2).to(device, bf).contiguous(), torch.cat(b2).to(device).contiguous())
+            self._key = key
+        return self._packed
+
+    def tables(self, s: torch.Tensor, adalns, gates):
+        """-> (gate_shift, out_gate): lists of views, one per AdaLN (..., L, 2 c_a) and one per gate (..., L, c_a)."""
+        eps = adalns[0].layernorm_s.eps
+        w1, b1, w2, b2 = self._pack(adalns, gates, s.device)
+        sn = F.layer_norm(s, None, None, eps, out_dtype=torch.bfloat16)
+        t1 = F.linear(sn, w1, b1)
+        t2 = F.linear(s, w2, b2)
+        gs, off = [], 0
+        for m in adalns:
+            gs.append(t1[..., off: off + 2 * m.channel_a])
+            off += 2 * m.channel_a
+        og, off = [], 0
+        for g in gates:
+            og.append(t2[..., off: off + g.weight.shape[0]])
+            off += g.weight.shape[0]
+        return gs, og
+
+
 class SelfAttentionPairBias(nn.Module, _PackedMixin):
     """Pair-bias self-attention: the single-track form (``channel_s=None``, LayerNorm prologue) and the diffusion
     form (AdaLN prologue and the sigmoid(Linear(s)) output gate), model/layers/folding/attention_pair_bias.py:70-158."""
@@ -312,13 +361,19 @@ class SelfAttentionPairBias(nn.Module, _PackedMixin):
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor | None, pair_bias: torch.Tensor, mask: torch.Tensor,
-                residual: bool = False) -> torch.Tensor:
+                residual: bool = False, cond=None) -> torch.Tensor:
         """a (...,L,c_a); s (...,L,c_s) or None; pair_bias (...,H,L,L); mask (...,L) -> (...,L,c_a).
-        With ``residual`` the result is a + update (fused into the last kernel)."""
+        With ``residual`` the result is a + update (fused into the last kernel).  ``cond``: the (gate/shift rows, output
+        gate logits) of this module taken from a stack's conditioning tables (bfloat16 compute)."""
         _check_inference(a)
         precise = _is_precise(compute_dtype(a), "SelfAttentionPairBias")
         pk = self._apb_packed(a.device, precise)
         with torch.autocast(a.device.type, enabled=False):
+            if cond is not None and not precise and self.use_single_conditioning:
+                share = _sample_share(a, s)
+                an = F.adaln(a, cond[0], share)
+                return F.attention_pair_bias(an, pair_bias, mask, pk, out_dtype=a.dtype, out_gate=cond[1], gate_share=share,
+                                             resid=a if residual else None)
             if precise and self.use_single_conditioning:
                 assert s is not None
                 share = _sample_share(a, s)
@@ -356,9 +411,10 @@ class ConditionedTransitionBlock(nn.Module, _PackedMixin):
         self.linear_out = LinearNoBias(model_dim, channel_a)
 
     @torch.compiler.disable
-    def forward(self, a: torch.Tensor, s: torch.Tensor, residual: bool = False, precise: bool | None = None) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, s: torch.Tensor, residual: bool = False, precise: bool | None = None,
+                cond=None) -> torch.Tensor:
         """``precise`` overrides the choice made from the compute dtype (for callers that already run with autocast
-        switched off)."""
+        switched off).  ``cond``: (gate/shift rows, output gate logits) from a stack's conditioning tables."""
         _check_inference(a)
         if precise is None:
             precise = _is_precise(compute_dtype(a), "ConditionedTransitionBlock")
@@ -369,6 +425,8 @@ class ConditionedTransitionBlock(nn.Module, _PackedMixin):
             if precise:
                 an = F.adaln(a.float(), self.adaln.gate_shift(s, True), share)
                 gate = F.linear_fp32(s.float(), pk["w_g"], pk["b_g"])
+            elif cond is not None:
+                an, gate = F.adaln(a, cond[0], share), cond[1]
             else:
                 an = F.adaln(a, self.adaln.gate_shift(s), share)
                 gate = F.linear(s, pk["w_g"], pk["b_g"])
@@ -384,9 +442,11 @@ class CachedGlobalTransformerBlock(nn.Module):
         self.attention = SelfAttentionPairBias(channel_a, num_heads, channel_s, call_site="diffusion_global")
         self.transition = ConditionedTransitionBlock(channel_a, channel_s)
 
-    def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
-        a = self.attention(a, s, pair_bias, mask, residual=True)
-        return self.transition(a, s, residual=True)
+    def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor, cond=None) -> torch.Tensor:
+        """``cond``: ((attention gate/shift, attention output gate), (transition gate/shift, transition output gate)) from
+        the stack's conditioning tables."""
+        a = self.attention(a, s, pair_bias, mask, residual=True, cond=None if cond is None else cond[0])
+        return self.transition(a, s, residual=True, cond=None if cond is None else cond[1])
 
 
 class CachedGlobalTransformerStack(nn.Module):
@@ -401,6 +461,7 @@ class CachedGlobalTransformerStack(nn.Module):
             [CachedGlobalTransformerBlock(channel_a, channel_s, num_heads) for _ in range(num_blocks)])
         self._bias_cache = None
         self._bias_key = None
+        self._bank = _ConditioningBank()
 
     def _prepared_bias(self, pair_bias: torch.Tensor, precise: bool = False):
         key = (pair_bias.data_ptr(), tuple(pair_bias.shape), pair_bias.dtype, pair_bias._version, precise)
@@ -414,9 +475,17 @@ class CachedGlobalTransformerStack(nn.Module):
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
         _check_inference(a)
-        pb = self._prepared_bias(pair_bias, _is_precise(compute_dtype(a), "CachedGlobalTransformerStack"))
+        precise = _is_precise(compute_dtype(a), "CachedGlobalTransformerStack")
+        pb = self._prepared_bias(pair_bias, precise)
+        conds = [None] * len(self.blocks)
+        if not precise:
+            # the conditioning projections of all blocks: one LayerNorm of s and two GEMMs
+            with torch.autocast(a.device.type, enabled=False):
+                gs, og = self._bank.tables(s, [m for b in self.blocks for m in (b.attention.adaln_a, b.transition.adaln)],
+                                           [g for b in self.blocks for g in (b.attention.linear_ada_out, b.transition.linear_g)])
+            conds = [((gs[2 * i], og[2 * i]), (gs[2 * i + 1], og[2 * i + 1])) for i in range(len(self.blocks))]
         for i, blk in enumerate(self.blocks):
-            a = blk(a, s, pb[i], mask)
+            a = blk(a, s, pb[i], mask, cond=conds[i])
         return a
 
 
@@ -511,12 +580,15 @@ class CrossAttentionPairBias(nn.Module, _PackedMixin):
         return self._packed(device, torch.float32 if precise else torch.bfloat16,
                             lambda sd, dev: packing.pack_apb_cross({k: sd[k] for k in keys}, self.num_heads, dev, precise=precise))
 
-    def normed_inputs(self, a: torch.Tensor, s: torch.Tensor | None, precise: bool):
+    def normed_inputs(self, a: torch.Tensor, s: torch.Tensor | None, precise: bool, cond=None):
         """Query-side and key-side prologues on the un-windowed rows a (..., L, c_a), s (..., L, c_s), and the logits of
-        the output gate (or None).  Both prologues are row-wise, so windows can be cut afterwards."""
+        the output gate (or None).  Both prologues are row-wise, so windows can be cut afterwards.  ``cond``: (query
+        gate/shift rows, key gate/shift rows, output gate logits) from a stack's conditioning tables."""
         if self.use_single_conditioning:
             assert s is not None
             share = _sample_share(a, s)
+            if cond is not None and not precise:
+                return F.adaln(a, cond[0], share), F.adaln(a, cond[1], share), cond[2]
             af = a.float() if precise else a
             xq = F.adaln(af, self.adaln_a_q.gate_shift(s, precise), share)
             xk = F.adaln(af, self.adaln_a_k.gate_shift(s, precise), share)
@@ -605,6 +677,7 @@ class LocalTransformerStack(nn.Module):
             [LocalTransformerBlock(channel_a, channel_s, channel_z, num_heads) for _ in range(num_blocks)])
         self._bias_w = None
         self._bias_w_key = None
+        self._bank = _ConditioningBank()
 
     def _stacked_bias_weights(self, device, dt):
         ws = [b.linear_z_to_bias.weight for b in self.blocks]
@@ -653,9 +726,16 @@ class LocalTransformerStack(nn.Module):
                     sharing = (1, 0)
                 bias_all = bias_all.reshape(len(self.blocks), h, -1, WINDOW_Q, WINDOW_K)
                 batch = mask_k.shape[0]
+            conds = [None] * len(self.blocks)
+            if not precise and all(b.attention.use_single_conditioning for b in self.blocks):
+                # the conditioning projections of all blocks: one LayerNorm of s and two GEMMs
+                gs, og = self._bank.tables(
+                    s, [m for b in self.blocks for m in (b.attention.adaln_a_q, b.attention.adaln_a_k, b.transition.adaln)],
+                    [g for b in self.blocks for g in (b.attention.linear_ada_out, b.transition.linear_g)])
+                conds = [((gs[3 * i], gs[3 * i + 1], og[2 * i]), (gs[3 * i + 2], og[2 * i + 1])) for i in range(len(self.blocks))]
             for i, blk in enumerate(self.blocks):
                 att = blk.attention
-                xq, xk_flat, gate = att.normed_inputs(a, s, precise)
+                xq, xk_flat, gate = att.normed_inputs(a, s, precise, cond=None if conds[i] is None else conds[i][0])
                 if gate is not None:
                     gl = tuple(gate.shape[:-2])
                     while gl and gl[0] == 1:
@@ -674,7 +754,7 @@ class LocalTransformerStack(nn.Module):
                         xq.reshape(batch, WINDOW_Q, c), xk.reshape(batch, WINDOW_K, c), bias_all[i], mask_k, pk,
                         bias_div=sharing[0], bias_mod=sharing[1], bias_head_major=True,
                         out_dtype=a.dtype, out_gate=gate, resid=a).view(*lead, length, c)
-                a = blk.transition(a, s, residual=True, precise=precise)
+                a = blk.transition(a, s, residual=True, precise=precise, cond=None if conds[i] is None else conds[i][1])
         return a
 
 
