@@ -257,20 +257,34 @@ KFB_API int kfb_window_bias_fwd(const void* z, const float* ln_w, const float* l
                                 long long positions, int c, int heads, float eps, int normalise, int dtype, void* stream);
 
 /*
- * Token <-> atom maps of the atom attention encoder / decoder.
- *   kfb_tokens_to_atoms replaces broadcast_tokens_to_atoms (src/kfold/model/layers/folding/utils.py:25-51):
- *     out[b, a, :] = x[b, token_index[b / index_div, a], :];  x (batch, n_token, d), out (batch, n_atom, d).
- *     An index outside [0, n_token) gives a zero row and sets the device status word (kfb_device_status) to 900.
- *   kfb_atoms_to_tokens replaces aggregate_atoms_to_tokens (:54-93): out[b, t, :] = mean of x[b, a, :] over the atoms
- *     with mask[a] != 0 and token_index[a] == t, accumulated in fp32 in atom order; a token without atoms gives zeros.
- *     x (batch, n_atom, d), out (batch, n_token, d).
+ * Token <-> atom maps and the small projections of the atom attention encoder / decoder
+ * (src/kfold/model/layers/folding/atom_transformer.py:263-389 and :392-489).
+ *   kfb_tokens_to_atoms replaces broadcast_tokens_to_atoms (src/kfold/model/layers/folding/utils.py:25-51) and the skip
+ *     connection behind it (atom_transformer.py:468-470): out[b, a, :] = x[b, token_index[b / index_div, a], :]
+ *     (+ addend[b, a, :]);  x (batch, n_token, d) of x_dtype, addend (NULL or like out) and out (batch, n_atom, d) of
+ *     out_dtype (bf16 -> bf16, bf16 -> fp32, fp32 -> fp32).  An index outside [0, n_token) gives a zero row and sets
+ *     the device status word (kfb_device_status) to 900.
+ *   kfb_atoms_to_tokens replaces aggregate_atoms_to_tokens (utils.py:54-93): out[b, t, :] = mean of x[b, a, :] over the
+ *     atoms with mask[a] != 0 and token_index[a] == t, accumulated in fp32 in atom order; a token without atoms gives
+ *     zeros;  `relu` != 0 applies max(., 0) to x first (the ReLU of atom_transformer.py:384).
+ *     x (batch, n_atom, d), out (batch, n_token, d), both of `dtype`.
  *   token_index : int64 (batch / index_div, n_atom), mask : bytes of the same shape -- `index_div` consecutive batch
- *   entries (the diffusion samples) share one row.  dtype KFB_BF16 or KFB_FP32 is the element type of x and out.
+ *   entries (the diffusion samples) share one row.
+ *   kfb_coord_embed replaces `q + linear_r_to_q(r_noisy)` (atom_transformer.py:362-367, a float32 Linear):
+ *     out[row, :] = q[qrow, :] + w r[row, :];  q (rows / samples, c) of q_dtype shared by the `samples` samples
+ *     (rows ordered (group, sample, l atoms)), r fp32 (rows, kc <= 4), w fp32 [c, kc], out fp32 (rows, c).
+ *   kfb_ln_project replaces `linear_q_to_r(layernorm_q(q.float()))` (atom_transformer.py:487-488):
+ *     out[row, j] = sum_i LayerNorm(x[row])[i] w[j, i];  x (rows, c) of dtype, ln_w / ln_b fp32 [c] or NULL,
+ *     w fp32 [n_out <= 8, c], out fp32 (rows, n_out).
  */
-KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, void* out, int batch, int n_token, int n_atom,
-                                int d, int index_div, int dtype, void* stream);
+KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, const void* addend, void* out, int batch,
+                                int n_token, int n_atom, int d, int index_div, int x_dtype, int out_dtype, void* stream);
 KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, int batch,
-                                int n_atom, int n_token, int d, int index_div, int dtype, void* stream);
+                                int n_atom, int n_token, int d, int index_div, int relu, int dtype, void* stream);
+KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, float* out, long long rows, int c, int kc, int samples,
+                            int l, int q_dtype, void* stream);
+KFB_API int kfb_ln_project(const void* x, const float* ln_w, const float* ln_b, const float* w, float* out, long long rows, int c,
+                           int n_out, float eps, int dtype, void* stream);
 
 /*
  * Adaptive LayerNorm: out = sigmoid(g) * LayerNorm(a) + v, LayerNorm without affine (fp32 statistics).

@@ -45,8 +45,10 @@ _SIGNATURES = {
     "kfb_apb_window_fwd": [c_void_p] * 10 + [c_ll, c_ll, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void_p],
     "kfb_window_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p],
-    "kfb_tokens_to_atoms": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_atoms_to_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_tokens_to_atoms": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_atoms_to_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_coord_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_ln_project": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_finish": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -13,14 +13,20 @@ __device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat1
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }
 __device__ __forceinline__ void st_f(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 __device__ __forceinline__ void st_f(float* p, float v) { *p = v; }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
-// out[b][a][:] = x[b][index[b / index_div][a]][:]; one warp per atom row, 16-byte pieces.  An index outside
-// [0, n_token) yields a zero row and records code 900 in the device status word instead of reading out of bounds.
+// out[b][a][:] = x[b][index[b / index_div][a]][:] (+ addend[b][a][:]); one warp per atom row, 16-byte pieces when the
+// types agree and nothing is added.  An index outside [0, n_token) yields a zero row (plus the addend) and records
+// code 900 in the device status word instead of reading out of bounds.
 static constexpr int kBadIndexCode = 900;
-template <typename T>
-__global__ void __launch_bounds__(256) tokens_to_atoms_kernel(const T* __restrict__ x, const long long* __restrict__ index,
-                                                              T* __restrict__ out, long long rows, int n_atom, int n_token, int d,
-                                                              int index_div) {
+template <typename TX, typename TO>
+__global__ void __launch_bounds__(256) tokens_to_atoms_kernel(const TX* __restrict__ x, const long long* __restrict__ index,
+                                                              const TO* __restrict__ addend, TO* __restrict__ out, long long rows,
+                                                              int n_atom, int n_token, int d, int index_div) {
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -29,24 +35,82 @@ __global__ void __launch_bounds__(256) tokens_to_atoms_kernel(const T* __restric
   const long long t = index[(b / index_div) * n_atom + a];
   const bool ok = t >= 0 && t < n_token;
   if (!ok && lane == 0) atomicCAS(&g_status, 0, kBadIndexCode);
-  constexpr int kVec = 16 / sizeof(T);
-  const T* src = x + (b * n_token + (ok ? t : 0)) * d;
-  T* dst = out + row * d;
-  if (d % kVec == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
-    for (int i = lane * kVec; i < d; i += 32 * kVec)
-      *reinterpret_cast<uint4*>(dst + i) = ok ? *reinterpret_cast<const uint4*>(src + i) : make_uint4(0, 0, 0, 0);
-  } else {
-    for (int i = lane; i < d; i += 32) st_f(dst + i, ok ? ld_f(src + i) : 0.f);
+  const TX* src = x + (b * n_token + (ok ? t : 0)) * d;
+  TO* dst = out + row * d;
+  if constexpr (sizeof(TX) == sizeof(TO)) {
+    constexpr int kVec = 16 / sizeof(TX);
+    if (addend == nullptr && d % kVec == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+      for (int i = lane * kVec; i < d; i += 32 * kVec)
+        *reinterpret_cast<uint4*>(dst + i) = ok ? *reinterpret_cast<const uint4*>(src + i) : make_uint4(0, 0, 0, 0);
+      return;
+    }
+  }
+  const TO* add = addend == nullptr ? nullptr : addend + row * d;
+  for (int i = lane; i < d; i += 32) st_f(dst + i, (ok ? ld_f(src + i) : 0.f) + (add != nullptr ? ld_f(add + i) : 0.f));
+}
+
+// out[row][:] = q[qrow][:] + sum_k w[:, k] r[row][k], fp32 out: the coordinate embedding added to the atom features
+// (row r of out uses row (r / (samples * l)) * l + r % l of q: the samples share q).  One warp per row.
+template <typename TQ>
+__global__ void __launch_bounds__(256) coord_embed_kernel(const TQ* __restrict__ q, const float* __restrict__ r,
+                                                          const float* __restrict__ w, float* __restrict__ out, long long rows, int c,
+                                                          int kc, int samples, int l) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long qrow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
+  float rv[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < kc; ++k) rv[k] = r[row * kc + k];
+  for (int i = lane; i < c; i += 32) {
+    float acc = 0.f;
+    for (int k = 0; k < kc; ++k) acc = fmaf(rv[k], w[i * kc + k], acc);   // same order as a dot product over k
+    out[row * c + i] = ld_f(q + qrow * c + i) + acc;
+  }
+}
+
+// out[row][j] = sum_i LayerNorm(x[row])[i] w[j][i], j < n_out <= 8, everything fp32 after the load: the projection of the
+// atom features to coordinate updates.  One warp per row; the row is re-read from L1 for the three passes.
+template <typename T>
+__global__ void __launch_bounds__(256) ln_project_kernel(const T* __restrict__ x, const float* __restrict__ ln_w,
+                                                         const float* __restrict__ ln_b, const float* __restrict__ w,
+                                                         float* __restrict__ out, long long rows, int c, int n_out, float eps) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* xr = x + row * c;
+  float s = 0.f;
+  for (int i = lane; i < c; i += 32) s += ld_f(xr + i);
+  const float mean = warp_sum(s) / static_cast<float>(c);
+  float q = 0.f;
+  for (int i = lane; i < c; i += 32) {
+    const float dlt = ld_f(xr + i) - mean;
+    q += dlt * dlt;
+  }
+  const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int i = lane; i < c; i += 32) {
+    const float xn = (ld_f(xr + i) - mean) * rstd * (ln_w != nullptr ? ln_w[i] : 1.f) + (ln_b != nullptr ? ln_b[i] : 0.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < n_out) acc[j] = fmaf(xn, w[j * c + i], acc[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j < n_out) {
+      const float v = warp_sum(acc[j]);
+      if (lane == 0) out[row * n_out + j] = v;
+    }
   }
 }
 
 // out[b][t][:] = mean over the atoms a of batch entry b with mask[a] and index[a] == t of x[b][a][:] (0 for a token
-// without atoms).  One warp per (b, t): the warp scans the atom indices 32 at a time and adds the matching rows in
+// without atoms); with `relu` the features pass through max(., 0) first.  One warp per (b, t): the warp scans the atom indices 32 at a time and adds the matching rows in
 // atom order with fp32 accumulators, so the result does not depend on scheduling.  kChunks * 32 channels per pass.
 template <typename T, int kChunks>
 __global__ void __launch_bounds__(256) atoms_to_tokens_kernel(const T* __restrict__ x, const long long* __restrict__ index,
                                                               const unsigned char* __restrict__ mask, T* __restrict__ out,
-                                                              long long rows, int n_atom, int n_token, int d, int index_div) {
+                                                              long long rows, int n_atom, int n_token, int d, int index_div,
+                                                              int relu) {
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -72,7 +136,10 @@ __global__ void __launch_bounds__(256) atoms_to_tokens_kernel(const T* __restric
 #pragma unroll
         for (int k = 0; k < kChunks; ++k) {
           const int col = k * 32 + lane;
-          if (d0 + col < d) acc[k] += ld_f(src + col);
+          if (d0 + col < d) {
+            const float v = ld_f(src + col);
+            acc[k] += relu ? fmaxf(v, 0.f) : v;
+          }
         }
       }
     }
@@ -92,29 +159,36 @@ using namespace kfb;
 
 extern "C" {
 
-KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, void* out, int batch, int n_token, int n_atom,
-                                int d, int index_div, int dtype, void* stream_) {
+KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, const void* addend, void* out, int batch,
+                                int n_token, int n_atom, int d, int index_div, int x_dtype, int out_dtype, void* stream_) {
   KFB_CHECK_ARG(x && token_index && out, "tokens_to_atoms: null pointer");
-  KFB_CHECK_ARG(dtype == KFB_BF16 || dtype == KFB_FP32, "tokens_to_atoms: dtype %d (bf16 or fp32)", dtype);
+  KFB_CHECK_ARG((x_dtype == KFB_BF16 || x_dtype == KFB_FP32) && (out_dtype == KFB_BF16 || out_dtype == KFB_FP32) &&
+                    !(x_dtype == KFB_FP32 && out_dtype == KFB_BF16),
+                "tokens_to_atoms: dtypes %d -> %d (bf16 -> bf16, bf16 -> fp32 or fp32 -> fp32)", x_dtype, out_dtype);
   KFB_CHECK_ARG(batch >= 1 && n_token >= 1 && n_atom >= 1 && d >= 1 && index_div >= 1 && batch % index_div == 0,
                 "tokens_to_atoms: batch %d tokens %d atoms %d d %d index_div %d", batch, n_token, n_atom, d, index_div);
   cudaStream_t stream = as_stream(stream_);
   const long long rows = static_cast<long long>(batch) * n_atom;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   LaunchScope scope(stream, "tokens_to_atoms");
-  if (dtype == KFB_BF16)
-    tokens_to_atoms_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), token_index,
-                                                                       static_cast<__nv_bfloat16*>(out), rows, n_atom, n_token, d,
-                                                                       index_div);
+  using bf = __nv_bfloat16;
+  if (x_dtype == KFB_BF16 && out_dtype == KFB_BF16)
+    tokens_to_atoms_kernel<bf, bf><<<blocks, 256, 0, stream>>>(static_cast<const bf*>(x), token_index, static_cast<const bf*>(addend),
+                                                               static_cast<bf*>(out), rows, n_atom, n_token, d, index_div);
+  else if (x_dtype == KFB_BF16)
+    tokens_to_atoms_kernel<bf, float><<<blocks, 256, 0, stream>>>(static_cast<const bf*>(x), token_index,
+                                                                  static_cast<const float*>(addend), static_cast<float*>(out), rows,
+                                                                  n_atom, n_token, d, index_div);
   else
-    tokens_to_atoms_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), token_index, static_cast<float*>(out),
-                                                               rows, n_atom, n_token, d, index_div);
+    tokens_to_atoms_kernel<float, float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), token_index,
+                                                                     static_cast<const float*>(addend), static_cast<float*>(out),
+                                                                     rows, n_atom, n_token, d, index_div);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }
 
 KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, int batch,
-                                int n_atom, int n_token, int d, int index_div, int dtype, void* stream_) {
+                                int n_atom, int n_token, int d, int index_div, int relu, int dtype, void* stream_) {
   KFB_CHECK_ARG(x && token_index && mask && out, "atoms_to_tokens: null pointer");
   KFB_CHECK_ARG(dtype == KFB_BF16 || dtype == KFB_FP32, "atoms_to_tokens: dtype %d (bf16 or fp32)", dtype);
   KFB_CHECK_ARG(batch >= 1 && n_token >= 1 && n_atom >= 1 && d >= 1 && index_div >= 1 && batch % index_div == 0,
@@ -126,10 +200,46 @@ KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, con
   if (dtype == KFB_BF16)
     atoms_to_tokens_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), token_index, mask,
                                                                           static_cast<__nv_bfloat16*>(out), rows, n_atom, n_token, d,
-                                                                          index_div);
+                                                                          index_div, relu);
   else
     atoms_to_tokens_kernel<float, 8><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), token_index, mask,
-                                                                  static_cast<float*>(out), rows, n_atom, n_token, d, index_div);
+                                                                  static_cast<float*>(out), rows, n_atom, n_token, d, index_div, relu);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, float* out, long long rows, int c, int kc, int samples,
+                            int l, int q_dtype, void* stream_) {
+  KFB_CHECK_ARG(q && r && w && out, "coord_embed: null pointer");
+  KFB_CHECK_ARG(q_dtype == KFB_BF16 || q_dtype == KFB_FP32, "coord_embed: dtype %d (bf16 or fp32)", q_dtype);
+  KFB_CHECK_ARG(rows >= 1 && c >= 1 && kc >= 1 && kc <= 4 && samples >= 1 && l >= 1 &&
+                    rows % (static_cast<long long>(samples) * l) == 0,
+                "coord_embed: rows %lld c %d coordinates %d samples %d l %d", rows, c, kc, samples, l);
+  cudaStream_t stream = as_stream(stream_);
+  const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  LaunchScope scope(stream, "coord_embed");
+  if (q_dtype == KFB_BF16)
+    coord_embed_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(q), r, w, out, rows, c, kc,
+                                                                   samples, l);
+  else
+    coord_embed_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(q), r, w, out, rows, c, kc, samples, l);
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+KFB_API int kfb_ln_project(const void* x, const float* ln_w, const float* ln_b, const float* w, float* out, long long rows, int c,
+                           int n_out, float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(x && w && out, "ln_project: null pointer");
+  KFB_CHECK_ARG(dtype == KFB_BF16 || dtype == KFB_FP32, "ln_project: dtype %d (bf16 or fp32)", dtype);
+  KFB_CHECK_ARG(rows >= 1 && c >= 1 && n_out >= 1 && n_out <= 8, "ln_project: rows %lld c %d outputs %d (at most 8)", rows, c, n_out);
+  cudaStream_t stream = as_stream(stream_);
+  const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  LaunchScope scope(stream, "ln_project");
+  if (dtype == KFB_BF16)
+    ln_project_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ln_w, ln_b, w, out, rows, c,
+                                                                  n_out, eps);
+  else
+    ln_project_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), ln_w, ln_b, w, out, rows, c, n_out, eps);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }

@@ -545,10 +545,14 @@ def _index_sharing(lead: tuple, index_lead: tuple):
     return div if tuple(il[:k]) == tuple(lead[:k]) else None
 
 
-def broadcast_tokens_to_atoms(x: torch.Tensor, token_index: torch.Tensor) -> torch.Tensor:
+def broadcast_tokens_to_atoms(x: torch.Tensor, token_index: torch.Tensor, add: torch.Tensor | None = None) -> torch.Tensor:
     """Token features gathered to their atoms (model/layers/folding/utils.py:25-51): x (*, Ntoken[, D]) bf16 or
-    float32, token_index (*, Natom) int64 (leading dims may be 1 where x's are not) -> (*, Natom[, D])."""
+    float32, token_index (*, Natom) int64 (leading dims may be 1 where x's are not) -> (*, Natom[, D]).
+    ``add``: a tensor like the result that is added in the same pass (the decoder's skip connection,
+    model/layers/folding/atom_transformer.py:468-470); the result then has the promoted dtype."""
     if x.ndim == token_index.ndim:
+        if add is not None:
+            raise ValueError("broadcast_tokens_to_atoms: `add` needs feature vectors")
         return broadcast_tokens_to_atoms(x.unsqueeze(-1), token_index).squeeze(-1)
     _require_cuda(x, token_index)
     if x.dtype not in (torch.bfloat16, torch.float32):
@@ -561,16 +565,22 @@ def broadcast_tokens_to_atoms(x: torch.Tensor, token_index: torch.Tensor) -> tor
         idx, div = idx.expand(*lead, n_atom), 1
     idx = idx.reshape(-1, n_atom).contiguous()
     x2 = x.reshape(-1, n_token, d).contiguous()
-    out = torch.empty(x2.shape[0], n_atom, d, dtype=x.dtype, device=x.device)
+    out_dtype = x.dtype if add is None else torch.promote_types(x.dtype, add.dtype)
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("broadcast_tokens_to_atoms: bfloat16 or float32 addend")
+    add2 = None if add is None else add.expand(*lead, n_atom, d).reshape(-1, n_atom, d).to(out_dtype).contiguous()
+    out = torch.empty(x2.shape[0], n_atom, d, dtype=out_dtype, device=x.device)
     with torch.cuda.device(x.device):
-        L.check(L.lib().kfb_tokens_to_atoms(L.ptr(x2), L.ptr(idx), L.ptr(out), x2.shape[0], n_token, n_atom, d, div,
-                                            L.dtype_code(x.dtype), L.stream_ptr()))
+        L.check(L.lib().kfb_tokens_to_atoms(L.ptr(x2), L.ptr(idx), L.ptr(add2), L.ptr(out), x2.shape[0], n_token, n_atom, d, div,
+                                            L.dtype_code(x.dtype), L.dtype_code(out_dtype), L.stream_ptr()))
     return out.view(*lead, n_atom, d)
 
 
-def aggregate_atoms_to_tokens(x: torch.Tensor, token_index: torch.Tensor, mask: torch.Tensor, num_tokens: int) -> torch.Tensor:
+def aggregate_atoms_to_tokens(x: torch.Tensor, token_index: torch.Tensor, mask: torch.Tensor, num_tokens: int,
+                              relu: bool = False) -> torch.Tensor:
     """Masked mean of the atom features of every token (model/layers/folding/utils.py:54-93): x (*, Natom, D) bf16 or
-    float32, token_index and mask (*, Natom) -> (*, num_tokens, D); fp32 accumulation in atom order."""
+    float32, token_index and mask (*, Natom) -> (*, num_tokens, D); fp32 accumulation in atom order.  ``relu`` applies
+    max(., 0) to the features as they are read (model/layers/folding/atom_transformer.py:384)."""
     _require_cuda(x, token_index, mask)
     if x.dtype not in (torch.bfloat16, torch.float32):
         raise TypeError("aggregate_atoms_to_tokens: bfloat16 or float32 features")
@@ -585,5 +595,45 @@ def aggregate_atoms_to_tokens(x: torch.Tensor, token_index: torch.Tensor, mask: 
     out = torch.empty(x2.shape[0], num_tokens, d, dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         L.check(L.lib().kfb_atoms_to_tokens(L.ptr(x2), L.ptr(idx), L.ptr(mk), L.ptr(out), x2.shape[0], n_atom, num_tokens, d, div,
-                                            L.dtype_code(x.dtype), L.stream_ptr()))
+                                            1 if relu else 0, L.dtype_code(x.dtype), L.stream_ptr()))
     return out.view(*lead, num_tokens, d)
+
+
+def coord_embed(q: torch.Tensor, r: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """q + Linear_fp32(r) (model/layers/folding/atom_transformer.py:362-367): q (*, [1 or N,] La, c) bf16 or float32,
+    r (*, N, La, k) coordinates, w (c, k) -> float32 (*, N, La, c).  q's sample dimension may be 1 (shared)."""
+    _require_cuda(q, r, w)
+    c, kc = w.shape
+    lead, l = tuple(r.shape[:-2]), r.shape[-2]
+    if q.dtype not in (torch.bfloat16, torch.float32):
+        q = q.float()
+    if q.dim() == r.dim() - 1:
+        q = q.unsqueeze(-3)
+    share = _index_sharing(lead, tuple(q.shape[:-2]))
+    if share is None:
+        q, share = q.expand(*lead, l, c), 1
+    q2 = q.reshape(-1, c).contiguous()
+    r2 = r.reshape(-1, kc).float().contiguous()
+    out = torch.empty(r2.shape[0], c, dtype=torch.float32, device=r.device)
+    with torch.cuda.device(r.device):
+        L.check(L.lib().kfb_coord_embed(L.ptr(q2), L.ptr(r2), L.ptr(w.detach().float().contiguous()), L.ptr(out), r2.shape[0], c, kc,
+                                        share, l, L.dtype_code(q2.dtype), L.stream_ptr()))
+    return out.view(*lead, l, c)
+
+
+def ln_project(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | None, w: torch.Tensor,
+               eps: float = 1e-5) -> torch.Tensor:
+    """Linear_fp32(LayerNorm(x.float())) to a handful of outputs (model/layers/folding/atom_transformer.py:487-488):
+    x (*, c) bf16 or float32, w (n_out <= 8, c) -> float32 (*, n_out)."""
+    _require_cuda(x, w)
+    c, n_out = x.shape[-1], w.shape[0]
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        x = x.float()
+    x2 = x.reshape(-1, c).contiguous()
+    out = torch.empty(x2.shape[0], n_out, dtype=torch.float32, device=x.device)
+    f32 = lambda t: None if t is None else t.detach().float().contiguous()
+    lw, lb, ww = f32(ln_w), f32(ln_b), f32(w)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().kfb_ln_project(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(ww), L.ptr(out), x2.shape[0], c, n_out, eps,
+                                       L.dtype_code(x2.dtype), L.stream_ptr()))
+    return out.view(*x.shape[:-1], n_out)

@@ -433,6 +433,42 @@ class ConditionedTransitionBlock(nn.Module, _PackedMixin):
             return F.conditioned_transition(an, pk, gate, share, resid=a if residual else None, out_dtype=a.dtype)
 
 
+class TokenPairBias(nn.Module):
+    """The pair bias of the token transformer, ``DiffusionStack.get_pair_bias`` (model/layers/folding/diffusion.py:290-294
+    and :397-416): LayerNorm(z) projected to blocks x heads values per pair, laid out (B, Nblock, H, L, L).  Parameter
+    names as in DiffusionStack (``layernorm_z``, ``linear_z_to_bias``).  The result is bf16 (float32 under float32
+    compute) and is what CachedGlobalTransformerStack consumes without another conversion or copy; it does not depend
+    on the noise level, so one call serves all sampler steps."""
+
+    def __init__(self, channel_z: int, token_transformer_blocks: int = 24, token_transformer_heads: int = 16):
+        super().__init__()
+        self.blocks, self.heads = token_transformer_blocks, token_transformer_heads
+        self.layernorm_z = LayerNorm(channel_z, create_offset=False)
+        self.linear_z_to_bias = LinearNoBias(channel_z, token_transformer_blocks * token_transformer_heads)
+        self._w = None
+        self._w_key = None
+
+    @torch.compiler.disable
+    def forward(self, z: torch.Tensor) -> torch.Tensor:
+        _check_inference(z)
+        precise = _is_precise(compute_dtype(z), "TokenPairBias")
+        w = self.linear_z_to_bias.weight
+        key = (z.device, precise, w.data_ptr(), None if torch.is_inference(w) else w._version)
+        if self._w_key != key:
+            self._w = packing.split3_weights(w).to(z.device) if precise else w.detach().to(z.device, torch.bfloat16).contiguous()
+            self._w_key = key
+        b, l = z.shape[0], z.shape[1]
+        lp = (l + 7) // 8 * 8
+        with torch.autocast(z.device.type, enabled=False):
+            zz = z.float() if precise else z.to(torch.bfloat16)
+            if lp != l:
+                zz = torch.nn.functional.pad(zz, (0, 0, 0, lp - l, 0, lp - l))
+            ln = self.layernorm_z
+            out = F.pair_bias(zz, ln.weight.detach().float(), None, self._w, ln.eps)      # (B, blocks*H, L, L)
+        out = out.view(b, self.blocks, self.heads, lp, lp)
+        return out if lp == l else out[..., :l, :l]
+
+
 class CachedGlobalTransformerBlock(nn.Module):
     """model/layers/folding/diffusion_transformer.py:342-413: a += attention(a, s, bias, mask); a += transition(a, s)."""
 
@@ -756,6 +792,93 @@ class LocalTransformerStack(nn.Module):
                         out_dtype=a.dtype, out_gate=gate, resid=a).view(*lead, length, c)
                 a = blk.transition(a, s, residual=True, precise=precise, cond=None if conds[i] is None else conds[i][1])
         return a
+
+
+class _ProjectionCache:
+    """Device copies of plain projection weights (bf16, or the bf16 triple split for the float32-accurate path),
+    re-made when the parameter changes."""
+
+    def __init__(self):
+        self._c = {}
+
+    def get(self, lin: nn.Module, device, precise: bool) -> torch.Tensor:
+        w = lin.weight
+        key = (device, precise, w.data_ptr(), None if torch.is_inference(w) else w._version)
+        hit = self._c.get(id(lin))
+        if hit is None or hit[0] != key:
+            wd = packing.split3_weights(w).to(device) if precise else w.detach().to(device, torch.bfloat16).contiguous()
+            hit = (key, wd)
+            self._c[id(lin)] = hit
+        return hit[1]
+
+
+def _project(x: torch.Tensor, w: torch.Tensor, precise: bool) -> torch.Tensor:
+    return F.linear_fp32(x.float(), w, None) if precise else F.linear(x, w, None)
+
+
+class AtomAttentionEncoder(nn.Module):
+    """model/layers/folding/atom_transformer.py:263-389 (AF3 Algorithm 5): optional coordinate embedding, the atom-level
+    local transformer, then ReLU(Linear(q)) averaged over the atoms of every token."""
+
+    def __init__(self, channel_atom: int, channel_atompair: int, channel_token: int, channel_coords: int = 3, num_blocks=3,
+                 num_heads=4, use_structure: bool = False, ckpt_atom_stack: bool = False, kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend, self.use_structure, self.ckpt_atom_stack = kernel_backend, use_structure, ckpt_atom_stack
+        if use_structure:
+            self.linear_r_to_q = LinearNoBias(channel_coords, channel_atom)
+        self.transformer = LocalTransformerStack(channel_atom, channel_atom, channel_atompair, num_heads, num_blocks)
+        self.linear_q_to_a = LinearNoBias(channel_atom, channel_token)
+        self._proj = _ProjectionCache()
+
+    @torch.compiler.disable
+    def forward(self, q: torch.Tensor, c: torch.Tensor, p: torch.Tensor, token_index: torch.Tensor, mask: torch.Tensor,
+                num_tokens: int, r_noisy: torch.Tensor | None = None):
+        """q (*, La, c_atom); c (*, La, c_atom); p (*, W, 32, 128, c_atompair); token_index, mask (*, La);
+        r_noisy (*, N, La, 3) -> (a (*, Lt, c_token), q_skip, c_skip, p_skip)."""
+        _check_inference(q)
+        precise = _is_precise(compute_dtype(q), "AtomAttentionEncoder")
+        if self.use_structure:
+            assert r_noisy is not None, "r_noisy must be provided if use_structure is True"
+            with torch.autocast(q.device.type, enabled=False):
+                q = F.coord_embed(q, r_noisy, self.linear_r_to_q.weight)
+        else:
+            assert r_noisy is None, "r_noisy must be None if use_structure is False"
+        q = self.transformer(q, c, p, mask)
+        with torch.autocast(q.device.type, enabled=False):
+            x = _project(q, self._proj.get(self.linear_q_to_a, q.device, precise), precise)
+            a = F.aggregate_atoms_to_tokens(x, token_index, mask, num_tokens, relu=True)
+        return a, q, c, p
+
+
+class AtomAttentionDecoder(nn.Module):
+    """model/layers/folding/atom_transformer.py:392-489 (AF3 Algorithm 6): token features projected and broadcast to their
+    atoms plus the skip connection, the atom-level local transformer, LayerNorm and the float32 projection to
+    coordinate updates."""
+
+    def __init__(self, channel_a: int, channel_atom: int, channel_atompair: int, num_blocks: int = 3, num_heads: int = 4,
+                 ckpt_atom_stack: bool = False, kernel_backend: str = "b200"):
+        super().__init__()
+        self.kernel_backend, self.ckpt_atom_stack = kernel_backend, ckpt_atom_stack
+        self.linear_a_to_q = LinearNoBias(channel_a, channel_atom)
+        self.transformer = LocalTransformerStack(channel_atom, channel_atom, channel_atompair, num_heads, num_blocks)
+        self.layernorm_q = LayerNorm(channel_atom, create_offset=False)
+        self.linear_q_to_r = LinearNoBias(channel_atom, 3)
+        self._proj = _ProjectionCache()
+
+    @torch.compiler.disable
+    def forward(self, a: torch.Tensor, q_skip: torch.Tensor, c_skip: torch.Tensor, p_skip: torch.Tensor,
+                token_index: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """a (*, Lt, c_token); q_skip, c_skip (*, La, c_atom); p_skip (*, W, 32, 128, c_atompair); token_index, mask
+        (*, La) -> float32 position updates (*, La, 3)."""
+        _check_inference(a)
+        precise = _is_precise(compute_dtype(a), "AtomAttentionDecoder")
+        with torch.autocast(a.device.type, enabled=False):
+            a_to_q = _project(a, self._proj.get(self.linear_a_to_q, a.device, precise), precise)
+            q = F.broadcast_tokens_to_atoms(a_to_q, token_index, add=q_skip)
+        q = self.transformer(q, c_skip, p_skip, mask)
+        ln = self.layernorm_q
+        with torch.autocast(a.device.type, enabled=False):
+            return F.ln_project(q, ln.weight, ln.bias, self.linear_q_to_r.weight, ln.eps)
 
 
 # --------------------------------------------------------------------------------------------

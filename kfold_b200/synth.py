@@ -125,6 +125,25 @@ def local_stack_weights(rng: _Rng, c_a: int, c_s: int, c_z: int, heads: int, blo
     return w
 
 
+def atom_encoder_weights(rng: _Rng, c_atom: int, c_pair: int, c_token: int, heads: int, blocks: int, use_structure: bool) -> dict:
+    """AtomAttentionEncoder (model/layers/folding/atom_transformer.py:263-309)."""
+    w = {}
+    if use_structure:
+        w["linear_r_to_q.weight"] = rng.linear(c_atom, 3)
+    w.update(_prefixed("transformer", local_stack_weights(rng, c_atom, c_atom, c_pair, heads, blocks)))
+    w["linear_q_to_a.weight"] = rng.linear(c_token, c_atom)
+    return w
+
+
+def atom_decoder_weights(rng: _Rng, c_token: int, c_atom: int, c_pair: int, heads: int, blocks: int) -> dict:
+    """AtomAttentionDecoder (model/layers/folding/atom_transformer.py:392-431)."""
+    w = {"linear_a_to_q.weight": rng.linear(c_atom, c_token)}
+    w.update(_prefixed("transformer", local_stack_weights(rng, c_atom, c_atom, c_pair, heads, blocks)))
+    w["layernorm_q.weight"] = rng.ln_w(c_atom)
+    w["linear_q_to_r.weight"] = rng.linear(3, c_atom)
+    return w
+
+
 def conditioned_transition_weights(rng: _Rng, c_a: int, c_s: int, factor: int = 2) -> dict:
     """ConditionedTransitionBlock (model/layers/folding/diffusion_transformer.py:50-71)."""
     w = _prefixed("adaln", adaln_weights(rng, c_a, c_s))

@@ -321,6 +321,32 @@ def local_transformer_stack(a, s, z, mask, w: dict, num_heads: int, num_blocks: 
     return a
 
 
+def atom_attention_encoder(q, c, p, token_index, mask, num_tokens: int, r_noisy, w: dict, num_heads: int, num_blocks: int,
+                           mode: str = "fp32"):
+    """``AtomAttentionEncoder.forward`` -- model/layers/folding/atom_transformer.py:311-389 with use_structure: the
+    float32 coordinate embedding (:362-367), the local transformer, ReLU(Linear(q)) averaged per token (:383-385).
+    Returns (a, q_skip)."""
+    m = _Mode(mode)
+    if r_noisy is not None:
+        q = q.float() + F.linear(r_noisy.float(), w["linear_r_to_q.weight"].float())
+    q = local_transformer_stack(q, c, p, mask, sub(w, "transformer"), num_heads, num_blocks, mode)
+    x = torch.relu(m.linear(m.r(q), w["linear_q_to_a.weight"]))
+    idx = torch.broadcast_to(token_index, x.shape[:-1])
+    return m.r(aggregate_atoms_to_tokens(x, idx, torch.broadcast_to(mask, x.shape[:-1]), num_tokens)), q
+
+
+def atom_attention_decoder(a, q_skip, c_skip, p_skip, token_index, mask, w: dict, num_heads: int, num_blocks: int,
+                           mode: str = "fp32"):
+    """``AtomAttentionDecoder.forward`` -- model/layers/folding/atom_transformer.py:433-489: Linear(a) broadcast to the
+    atoms plus the skip connection, the local transformer, LayerNorm and the float32 projection to 3 coordinates."""
+    m = _Mode(mode)
+    a_to_q = m.linear(m.r(a.float()), w["linear_a_to_q.weight"])
+    q = broadcast_tokens_to_atoms(a_to_q, torch.broadcast_to(token_index, a_to_q.shape[:-2] + token_index.shape[-1:])) + q_skip
+    q = local_transformer_stack(q, c_skip, p_skip, mask, sub(w, "transformer"), num_heads, num_blocks, mode)
+    qn = F.layer_norm(q.float(), (q.shape[-1],), w["layernorm_q.weight"].float(), None, 1e-5)
+    return F.linear(qn, w["linear_q_to_r.weight"].float())
+
+
 def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
     """``TriangularBlock.forward`` (eval) -- model/modules/tri_stack.py:130-151."""
     m = _Mode(mode)

@@ -45,6 +45,11 @@ CASES = {
     "local_stack": dict(kind="local_stack", seed=45, l=160, c=128, c_s=128, c_z=16, heads=4, blocks=3, samples=2, valid=150),
     # token <-> atom maps: 40 tokens, 160 atoms (1 to 8 atoms per token, one token without atoms), 2 samples
     "atom_token_maps": dict(kind="atom_token_maps", seed=46, tokens=40, atoms=160, d=96, samples=2, valid=150),
+    # atom attention encoder (with coordinate embedding) and decoder around a 2-block local transformer: 96 atoms, 24 tokens
+    "atom_encoder": dict(kind="atom_encoder", seed=47, tokens=24, atoms=96, c=128, c_z=16, c_token=256, heads=4, blocks=2,
+                         samples=2, valid=90),
+    "atom_decoder": dict(kind="atom_decoder", seed=48, tokens=24, atoms=96, c=128, c_z=16, c_token=256, heads=4, blocks=2,
+                         samples=2, valid=90),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -107,6 +112,21 @@ def build_inputs(name: str) -> dict:
         out["mask"] = synth.token_mask(na, cs["valid"]).view(1, 1, na)
         out["x_token"] = rng.normal(1, cs["samples"], nt, cs["d"])
         out["x_atom"] = rng.normal(1, cs["samples"], na, cs["d"])
+    elif kind in ("atom_encoder", "atom_decoder"):
+        nt, na, c = cs["tokens"], cs["atoms"], cs["c"]
+        index = np.sort(rng.rs.randint(0, nt, size=na)).astype(np.int64)
+        out["token_index"] = torch.from_numpy(index).view(1, 1, na)
+        out["mask"] = synth.token_mask(na, cs["valid"]).view(1, 1, na)
+        out["c"] = rng.normal(1, 1, na, c)
+        out["p"] = rng.normal(1, 1, na // 32, 32, 128, cs["c_z"])
+        if kind == "atom_encoder":
+            out["w"] = synth.atom_encoder_weights(rng, c, cs["c_z"], cs["c_token"], cs["heads"], cs["blocks"], True)
+            out["q"] = rng.normal(1, 1, na, c)
+            out["r_noisy"] = rng.normal(1, cs["samples"], na, 3) * 4.0
+        else:
+            out["w"] = synth.atom_decoder_weights(rng, cs["c_token"], c, cs["c_z"], cs["heads"], cs["blocks"])
+            out["a"] = rng.normal(1, cs["samples"], nt, cs["c_token"])
+            out["q_skip"] = rng.normal(1, cs["samples"], na, c)
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

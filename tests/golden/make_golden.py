@@ -78,6 +78,21 @@ def run_reference(ns, name: str) -> dict:
         idx = inp["token_index"].expand(1, cs["samples"], cs["atoms"])
         return {"atoms": ut.broadcast_tokens_to_atoms(inp["x_token"], idx),
                 "tokens": ut.aggregate_atoms_to_tokens(inp["x_atom"], idx, inp["mask"].expand_as(idx), cs["tokens"])}
+    if kind in ("atom_encoder", "atom_decoder"):
+        import importlib
+        at = importlib.import_module("kfold.model.layers.folding.atom_transformer")
+        if kind == "atom_encoder":
+            mod = at.AtomAttentionEncoder(cs["c"], cs["c_z"], cs["c_token"], num_blocks=cs["blocks"], num_heads=cs["heads"],
+                                          use_structure=True)
+        else:
+            mod = at.AtomAttentionDecoder(cs["c_token"], cs["c"], cs["c_z"], num_blocks=cs["blocks"], num_heads=cs["heads"])
+        for blk in mod.transformer.blocks:
+            blk.attention.kernel_backend = "torch"      # the oracle path; the constructor hard-codes "sdpa"
+        _load(mod, inp["w"])
+        if kind == "atom_encoder":
+            a, q_skip, _, _ = mod(inp["q"], inp["c"], inp["p"], inp["token_index"], inp["mask"], cs["tokens"], inp["r_noisy"])
+            return {"a": a, "q_skip": q_skip}
+        return {"out": mod(inp["a"], inp["q_skip"].clone(), inp["c"], inp["p"], inp["token_index"], inp["mask"])}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "block":

@@ -612,3 +612,92 @@ def test_local_transformer_stack_two_complexes(dev, z_per_sample):
     assert torch.isfinite(out).all()
     keep = mask.expand(2, 2, l)
     _check(*err_stats(out[keep], ref[keep]), "local stack, two complexes")
+
+
+def test_token_pair_bias_feeds_the_token_transformer(dev):
+    """get_pair_bias: LayerNorm(z) -> blocks x heads values per pair in the (B, Nblock, H, L, L) layout, against torch; its
+    result goes into the token transformer as it is (no second conversion)."""
+    from kfold_b200 import modules as M
+    g = torch.Generator().manual_seed(71)
+    l, c_z, blocks, heads = 40, 128, 3, 16
+    z = torch.randn(1, l, l, c_z, generator=g)
+    mod = M.TokenPairBias(c_z, blocks, heads).to(dev)
+    with torch.no_grad():
+        mod.layernorm_z.weight.copy_(1.0 + 0.1 * torch.randn(c_z, generator=g))
+        mod.linear_z_to_bias.weight.copy_(torch.randn(blocks * heads, c_z, generator=g) * c_z ** -0.5)
+    wz, wl = mod.layernorm_z.weight.detach().cpu(), mod.linear_z_to_bias.weight.detach().cpu()
+    ref = torch.nn.functional.linear(torch.nn.functional.layer_norm(z, (c_z,), wz, None, 1e-5), wl)
+    ref = ref.view(1, l, l, blocks, heads).permute(0, 3, 4, 1, 2)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = mod(z.to(dev))
+    assert out.shape == (1, blocks, heads, l, l) and out.dtype == torch.bfloat16
+    _check(*err_stats(out.float().cpu(), ref), "token pair bias bf16")
+    out32 = mod(z.to(dev))
+    mx, r = err_stats(out32.cpu(), ref)
+    assert out32.dtype == torch.float32 and mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"token pair bias fp32: {mx:.3e} {r:.3e}"
+    stack = M.CachedGlobalTransformerStack(768, 384, heads, blocks).to(dev)
+    assert stack._prepared_bias(out).data_ptr() == out.data_ptr()       # consumed in place: no conversion, no copy
+
+
+def test_graphed_call_replays_the_atom_transformer(dev):
+    """A CUDA-graph replay of the atom-level local transformer (window attention, conditioning tables) equals the eager call."""
+    from kfold_b200 import modules as M
+    from kfold_b200.graphs import GraphedCall
+    inp = cases.build_inputs("local_stack")
+    cs = inp["case"]
+    stack = M.LocalTransformerStack(cs["c"], cs["c_s"], cs["c_z"], cs["heads"], cs["blocks"]).to(dev)
+    stack.load_state_dict(inp["w"], strict=True)
+    a, s, z, mask = (inp[k].to(dev) for k in ("a", "s", "z", "mask"))
+
+    def step(a_, s_):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            return stack(a_, s_, z, mask)
+
+    with torch.no_grad():
+        graphed = GraphedCall(step, a, s)
+        for scale in (1.0, 0.5):
+            a2, s2 = a * scale, s * scale
+            eager = step(a2, s2).clone()
+            replay = graphed(a2, s2)
+            torch.cuda.synchronize()
+            assert torch.equal(eager, replay)
+
+
+def test_atom_attention_encoder_and_decoder_against_reference_golden(dev):
+    """AtomAttentionEncoder (coordinate embedding, local transformer, ReLU projection averaged per token) and
+    AtomAttentionDecoder (token broadcast + skip, local transformer, LayerNorm + float32 projection to coordinates)
+    against the reference outputs, under bfloat16 and under float32 compute.  Padding atoms are not compared."""
+    from kfold_b200 import modules as M
+    to = lambda t: t.to(dev)
+    inp = cases.build_inputs("atom_encoder")
+    cs = inp["case"]
+    gold = load_golden("atom_encoder")
+    enc = M.AtomAttentionEncoder(cs["c"], cs["c_z"], cs["c_token"], num_blocks=cs["blocks"], num_heads=cs["heads"],
+                                 use_structure=True).to(dev)
+    enc.load_state_dict(inp["w"], strict=True)
+    args = (to(inp["q"]), to(inp["c"]), to(inp["p"]), to(inp["token_index"]), to(inp["mask"]), cs["tokens"], to(inp["r_noisy"]))
+    keep = inp["mask"].reshape(-1)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        a, q_skip, _, _ = enc(*args)
+    assert a.dtype == torch.bfloat16 and q_skip.dtype == torch.float32
+    _check(*err_stats(a.float().cpu(), gold["a"]), "atom encoder a, bf16")
+    _check(*err_stats(q_skip.cpu()[..., keep, :], gold["q_skip"][..., keep, :]), "atom encoder q_skip, bf16")
+    a, q_skip, _, _ = enc(*args)
+    for got, ref, what in ((a.cpu(), gold["a"], "a"), (q_skip.cpu()[..., keep, :], gold["q_skip"][..., keep, :], "q_skip")):
+        mx, r = err_stats(got, ref)
+        assert got.dtype == torch.float32 and mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"atom encoder {what} fp32: {mx:.3e} {r:.3e}"
+
+    inp = cases.build_inputs("atom_decoder")
+    cs = inp["case"]
+    gold = load_golden("atom_decoder")["out"]
+    dec = M.AtomAttentionDecoder(cs["c_token"], cs["c"], cs["c_z"], num_blocks=cs["blocks"], num_heads=cs["heads"]).to(dev)
+    dec.load_state_dict(inp["w"], strict=True)
+    args = (to(inp["a"]), to(inp["q_skip"]), to(inp["c"]), to(inp["p"]), to(inp["token_index"]), to(inp["mask"]))
+    keep = inp["mask"].reshape(-1)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = dec(*args)
+    assert out.dtype == torch.float32 and out.shape == gold.shape
+    _check(*err_stats(out.cpu()[..., keep, :], gold[..., keep, :]), "atom decoder, bf16")
+    out = dec(*args)
+    mx, r = err_stats(out.cpu()[..., keep, :], gold[..., keep, :])
+    assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"atom decoder fp32: {mx:.3e} {r:.3e}"

@@ -32,6 +32,13 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
         idx = inp["token_index"].expand(1, cs["samples"], cs["atoms"])
         return {"atoms": O.broadcast_tokens_to_atoms(inp["x_token"], idx),
                 "tokens": O.aggregate_atoms_to_tokens(inp["x_atom"], idx, inp["mask"].expand_as(idx), cs["tokens"])}
+    if kind == "atom_encoder":
+        a, q_skip = O.atom_attention_encoder(inp["q"], inp["c"], inp["p"], inp["token_index"], inp["mask"], cs["tokens"],
+                                             inp["r_noisy"], w, cs["heads"], cs["blocks"], mode)
+        return {"a": a, "q_skip": q_skip}
+    if kind == "atom_decoder":
+        return {"out": O.atom_attention_decoder(inp["a"], inp["q_skip"], inp["c"], inp["p"], inp["token_index"], inp["mask"], w,
+                                                cs["heads"], cs["blocks"], mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "block":
@@ -49,6 +56,8 @@ def test_oracle_matches_reference_golden(name):
         assert compare_pair_output(got["z"], gold, "z")[0] < 5 * FP32_TOL
         zs = float(got["z"].double().sum())
         assert abs(zs - float(gold["z_sum"])) <= 1e-3 * float(gold["z_sumsq"]) ** 0.5
+    elif cases.CASES[name]["kind"] == "atom_encoder":
+        assert err_stats(got["a"], gold["a"])[0] < FP32_TOL and err_stats(got["q_skip"], gold["q_skip"])[0] < FP32_TOL
     elif cases.CASES[name]["kind"] == "atom_token_maps":
         assert torch.equal(got["atoms"], gold["atoms"])                 # a gather: exact
         assert err_stats(got["tokens"], gold["tokens"])[0] < FP32_TOL
