@@ -322,6 +322,16 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
                                     void* stream);
 
 /*
+ * Pieces of SingleConditioning.forward (src/kfold/model/layers/folding/diffusion.py:122-152), all fp32:
+ *   kfb_fourier_embed replaces FourierEmbedding.forward (src/kfold/model/layers/folding/embeddings.py:159-174):
+ *     out[row, j] = cos(2 pi t[row] w[j] + b[j]);  t [rows], w and b [dim], out (rows, dim).
+ *   kfb_broadcast_add replaces `s[:, None, :, :] + fourier_embed[:, :, None, :]` (diffusion.py:146):
+ *     out[g, n, l, :] = s[g, l, :] + f[g, n, :];  s (groups, l, c), f (groups, samples, c), out (groups, samples, l, c).
+ */
+KFB_API int kfb_fourier_embed(const float* t, const float* w, const float* b, float* out, int rows, int dim, void* stream);
+KFB_API int kfb_broadcast_add(const float* s, const float* f, float* out, int groups, int samples, int l, int c, void* stream);
+
+/*
  * Transition: out = Linear_out(silu(u_a) * u_b), [u_a, u_b] = Linear(LayerNorm(x))  (+ resid).
  * Replaces Transition.forward (src/kfold/model/layers/folding/transition.py:48-68) with SwiGLU.forward
  * (src/kfold/model/primitives/activation.py:27-29).

@@ -47,6 +47,8 @@ _SIGNATURES = {
     "kfb_window_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "kfb_tokens_to_atoms": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_atoms_to_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_fourier_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "kfb_broadcast_add": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_coord_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_ln_project": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

@@ -637,3 +637,26 @@ def ln_project(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | 
         L.check(L.lib().kfb_ln_project(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(ww), L.ptr(out), x2.shape[0], c, n_out, eps,
                                        L.dtype_code(x2.dtype), L.stream_ptr()))
     return out.view(*x.shape[:-1], n_out)
+
+
+def fourier_embed(t: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """cos(2 pi t w + b), float32 (model/layers/folding/embeddings.py:159-174): t (*,), w and b (dim,) -> (*, dim)."""
+    _require_cuda(t, w, b)
+    t2 = t.reshape(-1).float().contiguous()
+    w2, b2 = w.reshape(-1).float().contiguous(), b.reshape(-1).float().contiguous()
+    out = torch.empty(t2.shape[0], w2.shape[0], dtype=torch.float32, device=t.device)
+    with torch.cuda.device(t.device):
+        L.check(L.lib().kfb_fourier_embed(L.ptr(t2), L.ptr(w2), L.ptr(b2), L.ptr(out), t2.shape[0], w2.shape[0], L.stream_ptr()))
+    return out.view(*t.shape, w2.shape[0])
+
+
+def broadcast_add(s: torch.Tensor, f: torch.Tensor) -> torch.Tensor:
+    """s[:, None] + f[:, :, None], float32 (model/layers/folding/diffusion.py:146): s (B, L, c), f (B, N, c) -> (B, N, L, c)."""
+    _require_cuda(s, f)
+    b, l, c = s.shape
+    n = f.shape[1]
+    s2, f2 = s.float().contiguous(), f.float().contiguous()
+    out = torch.empty(b, n, l, c, dtype=torch.float32, device=s.device)
+    with torch.cuda.device(s.device):
+        L.check(L.lib().kfb_broadcast_add(L.ptr(s2), L.ptr(f2), L.ptr(out), b, n, l, c, L.stream_ptr()))
+    return out

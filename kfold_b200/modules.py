@@ -433,6 +433,42 @@ class ConditionedTransitionBlock(nn.Module, _PackedMixin):
             return F.conditioned_transition(an, pk, gate, share, resid=a if residual else None, out_dtype=a.dtype)
 
 
+class SingleConditioning(nn.Module):
+    """model/layers/folding/diffusion.py:97-152 (AF3 Algorithm 21, single part): float32 Linear(s_inputs) plus the
+    float32 projection of the normalised Fourier features of the noise level, broadcast over tokens and samples, then two
+    Transitions.  The two projections are float32 in the reference whatever the autocast state; they run on the
+    split-operand tensor-core GEMM.  The Fourier weights are the reference's (torch.randn with generator seed 42 on
+    the CPU, non-persistent buffers)."""
+
+    def __init__(self, channel_s: int = 384, dim_fourier: int = 256):
+        super().__init__()
+        gen = torch.Generator()
+        gen.manual_seed(42)
+        self.register_buffer("fourier_w", torch.randn(size=(1, dim_fourier), generator=gen, device="cpu"), persistent=False)
+        self.register_buffer("fourier_b", torch.randn(size=(1, dim_fourier), generator=gen, device="cpu"), persistent=False)
+        self.layernorm_fourier = LayerNorm(dim_fourier, create_offset=False)
+        self.linear_fourier = LinearNoBias(dim_fourier, channel_s)
+        self.linear = LinearNoBias(channel_s, channel_s)
+        self.transitions = nn.ModuleList([Transition(channel_s, expansion_factor=2) for _ in range(2)])
+        self._proj = _ProjectionCache()
+
+    @torch.compiler.disable
+    def forward(self, s_inputs: torch.Tensor, c_noise: torch.Tensor) -> torch.Tensor:
+        """s_inputs (B, Lt, c_s); c_noise (B, N) -> (B, N, Lt, c_s)."""
+        _check_inference(s_inputs)
+        with torch.autocast(s_inputs.device.type, enabled=False):
+            dev = s_inputs.device
+            s = F.linear_fp32(s_inputs.float(), self._proj.get(self.linear, dev, True), None)
+            emb = F.fourier_embed(c_noise, self.fourier_w, self.fourier_b)
+            ln = self.layernorm_fourier
+            emb = F.layer_norm(emb, ln.weight, ln.bias, ln.eps, out_dtype=torch.float32)
+            emb = F.linear_fp32(emb, self._proj.get(self.linear_fourier, dev, True), None)
+            s = F.broadcast_add(s, emb).to(s_inputs.dtype)
+        for transition in self.transitions:
+            s = transition(s, residual=True)
+        return s
+
+
 class TokenPairBias(nn.Module):
     """The pair bias of the token transformer, ``DiffusionStack.get_pair_bias`` (model/layers/folding/diffusion.py:290-294
     and :397-416): LayerNorm(z) projected to blocks x heads values per pair, laid out (B, Nblock, H, L, L).  Parameter

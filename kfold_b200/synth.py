@@ -144,6 +144,15 @@ def atom_decoder_weights(rng: _Rng, c_token: int, c_atom: int, c_pair: int, head
     return w
 
 
+def single_conditioning_weights(rng: _Rng, c_s: int, dim_fourier: int) -> dict:
+    """SingleConditioning (model/layers/folding/diffusion.py:102-120)."""
+    w = {"layernorm_fourier.weight": rng.ln_w(dim_fourier), "linear_fourier.weight": rng.linear(c_s, dim_fourier),
+         "linear.weight": rng.linear(c_s, c_s)}
+    for i in range(2):
+        w.update(_prefixed(f"transitions.{i}", transition_weights(rng, c_s, 2)))
+    return w
+
+
 def conditioned_transition_weights(rng: _Rng, c_a: int, c_s: int, factor: int = 2) -> dict:
     """ConditionedTransitionBlock (model/layers/folding/diffusion_transformer.py:50-71)."""
     w = _prefixed("adaln", adaln_weights(rng, c_a, c_s))

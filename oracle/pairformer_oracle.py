@@ -347,6 +347,32 @@ def atom_attention_decoder(a, q_skip, c_skip, p_skip, token_index, mask, w: dict
     return F.linear(qn, w["linear_q_to_r.weight"].float())
 
 
+def fourier_weights(dim: int):
+    """The fixed random Fourier weights -- model/layers/folding/embeddings.py:149-157: two draws of torch.randn from a
+    CPU generator seeded with 42."""
+    gen = torch.Generator()
+    gen.manual_seed(42)
+    w = torch.randn(size=(1, dim), generator=gen, device="cpu")
+    b = torch.randn(size=(1, dim), generator=gen, device="cpu")
+    return w, b
+
+
+def single_conditioning(s_inputs, c_noise, w: dict, mode: str = "fp32"):
+    """``SingleConditioning.forward`` -- model/layers/folding/diffusion.py:122-152: float32 Linear(s_inputs), Fourier
+    features of the noise level (embeddings.py:174) normalised and projected in float32, broadcast sum, two
+    Transitions.  s_inputs (B, Lt, c_s); c_noise (B, N) -> (B, N, Lt, c_s)."""
+    fw, fb = fourier_weights(w["linear_fourier.weight"].shape[1])
+    fw, fb = fw.to(s_inputs.device), fb.to(s_inputs.device)
+    s = F.linear(s_inputs.float(), w["linear.weight"].float())
+    emb = torch.cos((2 * math.pi) * c_noise.float()[..., None] * fw + fb)
+    emb = F.layer_norm(emb, (emb.shape[-1],), w["layernorm_fourier.weight"].float(), None, 1e-5)
+    emb = F.linear(emb, w["linear_fourier.weight"].float())
+    s = (s[:, None, :, :] + emb[:, :, None, :]).to(s_inputs.dtype)
+    for i in range(2):
+        s = s + transition(s, sub(w, f"transitions.{i}"), mode)
+    return s
+
+
 def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
     """``TriangularBlock.forward`` (eval) -- model/modules/tri_stack.py:130-151."""
     m = _Mode(mode)

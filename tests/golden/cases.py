@@ -50,6 +50,8 @@ CASES = {
                          samples=2, valid=90),
     "atom_decoder": dict(kind="atom_decoder", seed=48, tokens=24, atoms=96, c=128, c_z=16, c_token=256, heads=4, blocks=2,
                          samples=2, valid=90),
+    # single conditioning of the sampler: 40 tokens, 3 noise levels
+    "single_conditioning": dict(kind="single_conditioning", seed=49, l=40, c_s=384, dim_fourier=256, samples=3),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -127,6 +129,10 @@ def build_inputs(name: str) -> dict:
             out["w"] = synth.atom_decoder_weights(rng, cs["c_token"], c, cs["c_z"], cs["heads"], cs["blocks"])
             out["a"] = rng.normal(1, cs["samples"], nt, cs["c_token"])
             out["q_skip"] = rng.normal(1, cs["samples"], na, c)
+    elif kind == "single_conditioning":
+        out["w"] = synth.single_conditioning_weights(rng, cs["c_s"], cs["dim_fourier"])
+        out["s_inputs"] = rng.normal(1, cs["l"], cs["c_s"])
+        out["c_noise"] = rng.normal(1, cs["samples"]) * 1.5       # 1/4 log(t_hat / sigma_data) spans about +-2
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

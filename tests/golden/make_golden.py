@@ -93,6 +93,11 @@ def run_reference(ns, name: str) -> dict:
             a, q_skip, _, _ = mod(inp["q"], inp["c"], inp["p"], inp["token_index"], inp["mask"], cs["tokens"], inp["r_noisy"])
             return {"a": a, "q_skip": q_skip}
         return {"out": mod(inp["a"], inp["q_skip"].clone(), inp["c"], inp["p"], inp["token_index"], inp["mask"])}
+    if kind == "single_conditioning":
+        import importlib
+        df = importlib.import_module("kfold.model.layers.folding.diffusion")
+        mod = _load(df.SingleConditioning(cs["c_s"], cs["dim_fourier"]), inp["w"])
+        return {"out": mod(inp["s_inputs"], inp["c_noise"]), "fourier_w": mod.fourier_embed.w, "fourier_b": mod.fourier_embed.b}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "block":

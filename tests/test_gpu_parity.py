@@ -701,3 +701,45 @@ def test_atom_attention_encoder_and_decoder_against_reference_golden(dev):
     out = dec(*args)
     mx, r = err_stats(out.cpu()[..., keep, :], gold[..., keep, :])
     assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"atom decoder fp32: {mx:.3e} {r:.3e}"
+
+
+@pytest.mark.parametrize("l,valid", [(32, 32), (64, 40), (160, 64), (288, 288)])
+def test_local_transformer_stack_window_edges(dev, l, valid):
+    """Window edge cases of the kernel that walks the windows: a single window (every key block reaches outside the
+    molecule on both sides), two windows, a window whose keys are all padding atoms (160 atoms, 64 valid), and a length that
+    fills two query blocks and a quarter.  One sample, window pair tensor of its own, against the oracle."""
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    rng = synth._Rng(80 + l)
+    c, c_z, h, blocks = 128, 16, 4, 1
+    w = synth.local_stack_weights(rng, c, c, c_z, h, blocks)
+    a, s = rng.normal(1, 1, l, c), rng.normal(1, 1, l, c)
+    z = rng.normal(1, 1, l // 32, 32, 128, c_z)
+    mask = synth.token_mask(l, valid).view(1, 1, l)
+    stack = M.LocalTransformerStack(c, c, c_z, h, blocks).to(dev)
+    stack.load_state_dict(w, strict=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = stack(a.to(dev), s.to(dev), z.to(dev), mask.to(dev)).cpu()
+    ref = _oracle_on(dev, O.local_transformer_stack, a, s, z, mask, w, h, blocks)
+    _check(*err_stats(*_valid_rows(out, ref, mask)), f"local stack L={l}")
+
+
+def test_single_conditioning_against_reference_golden(dev):
+    """SingleConditioning: float32 projections and Fourier features of the noise level, two Transitions; float32 compute
+    against the reference at float32 accuracy, bfloat16 compute (Transitions on the bf16 path) within bf16 noise.
+    The Fourier weights are regenerated from the reference's seed and compared with the stored ones."""
+    from kfold_b200 import modules as M
+    inp = cases.build_inputs("single_conditioning")
+    cs = inp["case"]
+    gold = load_golden("single_conditioning")
+    mod = M.SingleConditioning(cs["c_s"], cs["dim_fourier"]).to(dev)
+    mod.load_state_dict(inp["w"], strict=True)
+    assert torch.equal(mod.fourier_w.cpu(), gold["fourier_w"]) and torch.equal(mod.fourier_b.cpu(), gold["fourier_b"])
+    s_in, c_noise = inp["s_inputs"].to(dev), inp["c_noise"].to(dev)
+    out = mod(s_in, c_noise)
+    mx, r = err_stats(out.cpu(), gold["out"])
+    assert out.dtype == torch.float32 and out.shape == gold["out"].shape
+    assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"single conditioning fp32: {mx:.3e} {r:.3e}"
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = mod(s_in, c_noise)
+    _check(*err_stats(out.float().cpu(), gold["out"]), "single conditioning, bf16 transitions")

@@ -39,6 +39,8 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
     if kind == "atom_decoder":
         return {"out": O.atom_attention_decoder(inp["a"], inp["q_skip"], inp["c"], inp["p"], inp["token_index"], inp["mask"], w,
                                                 cs["heads"], cs["blocks"], mode)}
+    if kind == "single_conditioning":
+        return {"out": O.single_conditioning(inp["s_inputs"], inp["c_noise"], w, mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "block":
