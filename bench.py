@@ -347,6 +347,83 @@ def run_atom_step(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
+# optional fourth workload (--sampler-step): one call of DiffusionStack.step at BASELINE config 4's shape (atom attention
+# encoder, 24-block token transformer, atom attention decoder; 768 tokens, 6 016 atoms, 5 samples), bf16 compute.
+# ------------------------------------------------------------------------------------------------
+def run_sampler_step(args) -> None:
+    from kfold_b200 import _lib as L
+    from kfold_b200 import modules as M
+    from kfold_b200 import synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nt, na, ns = N_TOKENS, 6016, 5
+    c_a, c_s, c_atom, c_pair, tb, th = 768, 384, 128, 16, 24, 16
+    rng = synth._Rng(SEED)
+    w = synth.diffusion_step_weights(rng, c_a, c_s, c_atom, c_pair, 3, 4, tb, th)
+    mod = M.DiffusionStack(channel_a=c_a, channel_s=c_s, channel_z=128, channel_atom=c_atom, channel_atompair=c_pair,
+                           token_transformer_blocks=tb, token_transformer_heads=th).to(dev)
+    mod.load_state_dict(w, strict=False)
+    r = (rng.normal(1, ns, na, 3) * 4.0).to(dev)
+    q, c = rng.normal(1, na, c_atom).to(dev), rng.normal(1, na, c_atom).to(dev)
+    p = rng.normal(1, na // 32, 32, 128, c_pair).to(dev)
+    import numpy as np
+    token_index = torch.from_numpy(np.sort(rng.rs.randint(0, nt, size=na)).astype(np.int64)).view(1, na).to(dev)
+    atom_mask = synth.token_mask(na, pad_frac=0.02).view(1, na).to(dev)
+    s = rng.normal(1, ns, nt, c_s).to(dev)
+    pair_bias = rng.normal(1, tb, th, nt, nt).to(dev, torch.bfloat16)
+    token_mask = synth.token_mask(nt, pad_frac=PAD_FRAC).view(1, nt).to(dev)
+
+    def step():
+        return mod.step(r, q, c, p, token_index, atom_mask, s, pair_bias, token_mask)
+
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        L.profile_enable(True)
+        launches0 = L.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        launches_per_step = (L.launch_count() - launches0) // max(args.steps, 1)
+        prof = L.profile_report()
+        L.profile_enable(False)
+        ms_eager = e0.elapsed_time(e1) / args.steps
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            out_g = step()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_graph = e0.elapsed_time(e1) / args.steps
+        graph_ok = bool(torch.isfinite(out_g.float()).all())
+    ms = min(ms_eager, ms_graph) if graph_ok else ms_eager
+    top = sorted(prof.items(), key=lambda kv: -kv[1][1])[:8]
+    emit({"metric": f"diffusion_stack_step_ms_l{nt}_a{na}_s{ns}_bf16", "value": ms, "unit": "ms", "n_gpus": 1,
+          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+          "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+          "config": {"workload": f"DiffusionStack.step (BASELINE config 4): atom encoder 3 blocks, token transformer {tb} blocks "
+                                 f"c={c_a}, atom decoder 3 blocks; {nt} tokens, {na} atoms, {ns} samples; one call = one sampler step"},
+          "gpu_launches": launches_per_step * args.steps, "ms_eager": round(ms_eager, 3), "ms_cuda_graph": round(ms_graph, 3),
+          "launches_per_step": launches_per_step,
+          "top_kernels": {tag: {"launches": cnt, "total_ms": round(t, 3)} for tag, (cnt, t) in top},
+          "device_status": L.device_status()})
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
@@ -519,6 +596,8 @@ def main() -> None:
                     help="with N > 1 ranks: row-shard ONE pair tensor over the GPUs (strong scaling) instead of one block per GPU")
     ap.add_argument("--tokens", type=int, default=N_TOKENS,
                     help="profiling aid: run the block at another N (the reported line is then NOT the benchmark workload)")
+    ap.add_argument("--sampler-step", action="store_true",
+                    help="fourth workload: one DiffusionStack.step at BASELINE config 4's shape (its own JSON line)")
     ap.add_argument("--atom-step", action="store_true",
                     help="third workload: one pass of an atom-level local transformer of BASELINE config 4 (its own JSON line)")
     ap.add_argument("--diffusion-step", action="store_true",
@@ -529,6 +608,9 @@ def main() -> None:
         return
     if args.atom_step:
         run_atom_step(args)
+        return
+    if args.sampler_step:
+        run_sampler_step(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and args.tokens == N_TOKENS else args.warmup
     if args.tokens != N_TOKENS:

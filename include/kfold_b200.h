@@ -267,24 +267,31 @@ KFB_API int kfb_window_bias_fwd(const void* z, const float* ln_w, const float* l
  *   kfb_atoms_to_tokens replaces aggregate_atoms_to_tokens (utils.py:54-93): out[b, t, :] = mean of x[b, a, :] over the
  *     atoms with mask[a] != 0 and token_index[a] == t, accumulated in fp32 in atom order; a token without atoms gives
  *     zeros;  `relu` != 0 applies max(., 0) to x first (the ReLU of atom_transformer.py:384).
- *     x (batch, n_atom, d), out (batch, n_token, d), both of `dtype`.
+ *     x (batch, n_atom, d), out (batch, n_token, d), both of `dtype`.  workspace: NULL (every token scans all atoms) or
+ *     kfb_atoms_to_tokens_workspace_bytes bytes, in which two small kernels first record each token's first and last
+ *     atom so that the mean scans only that range (same result, any atom order).
  *   token_index : int64 (batch / index_div, n_atom), mask : bytes of the same shape -- `index_div` consecutive batch
  *   entries (the diffusion samples) share one row.
  *   kfb_coord_embed replaces `q + linear_r_to_q(r_noisy)` (atom_transformer.py:362-367, a float32 Linear):
  *     out[row, :] = q[qrow, :] + w r[row, :];  q (rows / samples, c) of q_dtype shared by the `samples` samples
- *     (rows ordered (group, sample, l atoms)), r fp32 (rows, kc <= 4), w fp32 [c, kc], out fp32 (rows, c).
+ *     (rows ordered (group, sample, l atoms)), r fp32 (rows, kc <= 4), w fp32 [c, kc], out fp32 (rows, c);
+ *     mask : NULL or bytes (rows / samples), atom validity shared like q: the coordinates of padding atoms count as zero
+ *     (`r_noisy * atom_mask`, src/kfold/model/layers/folding/diffusion.py:521).
  *   kfb_ln_project replaces `linear_q_to_r(layernorm_q(q.float()))` (atom_transformer.py:487-488):
  *     out[row, j] = sum_i LayerNorm(x[row])[i] w[j, i];  x (rows, c) of dtype, ln_w / ln_b fp32 [c] or NULL,
- *     w fp32 [n_out <= 8, c], out fp32 (rows, n_out).
+ *     w fp32 [n_out <= 8, c], out fp32 (rows, n_out);  mask : NULL or bytes (rows / samples) with rows ordered
+ *     (group, sample, l atoms): rows of padding atoms give zeros (`r_update * atom_mask`, diffusion.py:596).
  */
 KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, const void* addend, void* out, int batch,
                                 int n_token, int n_atom, int d, int index_div, int x_dtype, int out_dtype, void* stream);
-KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, int batch,
-                                int n_atom, int n_token, int d, int index_div, int relu, int dtype, void* stream);
-KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, float* out, long long rows, int c, int kc, int samples,
-                            int l, int q_dtype, void* stream);
-KFB_API int kfb_ln_project(const void* x, const float* ln_w, const float* ln_b, const float* w, float* out, long long rows, int c,
-                           int n_out, float eps, int dtype, void* stream);
+KFB_API size_t kfb_atoms_to_tokens_workspace_bytes(int batch, int n_token, int index_div);
+KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, void* workspace,
+                                size_t workspace_bytes, int batch, int n_atom, int n_token, int d, int index_div, int relu,
+                                int dtype, void* stream);
+KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, const unsigned char* mask, float* out, long long rows,
+                            int c, int kc, int samples, int l, int q_dtype, void* stream);
+KFB_API int kfb_ln_project(const void* x, const float* ln_w, const float* ln_b, const float* w, const unsigned char* mask,
+                           float* out, long long rows, int c, int n_out, float eps, int samples, int l, int dtype, void* stream);
 
 /*
  * Adaptive LayerNorm: out = sigmoid(g) * LayerNorm(a) + v, LayerNorm without affine (fp32 statistics).
@@ -316,6 +323,12 @@ KFB_API size_t kfb_cond_transition_workspace_bytes_precise(long long rows, int c
 KFB_API size_t kfb_linear_fp32_workspace_bytes(long long rows, int k);
 KFB_API int kfb_linear_fp32(const void* x, const void* w6, const float* bias, void* out, void* workspace,
                             size_t workspace_bytes, long long rows, int n, int k, void* stream);
+/* out = LayerNorm(x) W^T (+ bias) (+ resid) at fp32 accuracy (kfb_linear_fp32 with the LayerNorm and the residual fused):
+ * `a + linear_s_to_a(layernorm_s(s))` of DiffusionStack.step (src/kfold/model/layers/folding/diffusion.py:568).
+ * x, resid, out fp32; ln_w / ln_b fp32 [k] or NULL; normalise == 0 skips the LayerNorm; workspace as kfb_linear_fp32. */
+KFB_API int kfb_ln_linear_fp32(const void* x, const float* ln_w, const float* ln_b, const void* w6, const float* bias,
+                               const void* resid, void* out, void* workspace, size_t workspace_bytes, long long rows, int n, int k,
+                               float eps, int normalise, void* stream);
 KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_packed, const void* w_out,
                                     const void* out_gate, long long gate_ld, void* out, const void* resid, void* workspace,
                                     size_t workspace_bytes, long long rows, int c, int hidden, int samples, int l, int dtype,

@@ -46,11 +46,15 @@ _SIGNATURES = {
                            c_int, c_int, c_int, c_void_p],
     "kfb_window_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "kfb_tokens_to_atoms": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_atoms_to_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_atoms_to_tokens": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_int, c_void_p],
     "kfb_fourier_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "kfb_broadcast_add": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_coord_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_ln_project": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_coord_embed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_ln_project": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_int,
+                       c_void_p],
+    "kfb_ln_linear_fp32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
+                           c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_finish": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -84,6 +88,7 @@ _SIZE_FUNCS = {
     "kfb_transition_workspace_bytes": [c_ll, c_int, c_int],
     "kfb_triatt_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_workspace_bytes": [c_int, c_int, c_int, c_int],
+    "kfb_atoms_to_tokens_workspace_bytes": [c_int, c_int, c_int],
     "kfb_apb_cross_workspace_bytes": [c_int, c_int, c_int, c_int, c_int],
     "kfb_apb_window_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_cross_workspace_bytes_precise": [c_int, c_int, c_int, c_int],

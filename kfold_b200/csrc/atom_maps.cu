@@ -50,17 +50,19 @@ __global__ void __launch_bounds__(256) tokens_to_atoms_kernel(const TX* __restri
 }
 
 // out[row][:] = q[qrow][:] + sum_k w[:, k] r[row][k], fp32 out: the coordinate embedding added to the atom features
-// (row r of out uses row (r / (samples * l)) * l + r % l of q: the samples share q).  One warp per row.
+// (row r of out uses row (r / (samples * l)) * l + r % l of q and of the optional atom mask: the samples share them).
+// One warp per row.
 template <typename TQ>
 __global__ void __launch_bounds__(256) coord_embed_kernel(const TQ* __restrict__ q, const float* __restrict__ r,
-                                                          const float* __restrict__ w, float* __restrict__ out, long long rows, int c,
-                                                          int kc, int samples, int l) {
+                                                          const float* __restrict__ w, const unsigned char* __restrict__ mask,
+                                                          float* __restrict__ out, long long rows, int c, int kc, int samples, int l) {
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
   const long long qrow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
   float rv[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int k = 0; k < kc; ++k) rv[k] = r[row * kc + k];
+  const bool keep = mask == nullptr || mask[qrow] != 0;   // coordinates of padding atoms count as zero
+  for (int k = 0; k < kc; ++k) rv[k] = keep ? r[row * kc + k] : 0.f;
   for (int i = lane; i < c; i += 32) {
     float acc = 0.f;
     for (int k = 0; k < kc; ++k) acc = fmaf(rv[k], w[i * kc + k], acc);   // same order as a dot product over k
@@ -73,10 +75,15 @@ __global__ void __launch_bounds__(256) coord_embed_kernel(const TQ* __restrict__
 template <typename T>
 __global__ void __launch_bounds__(256) ln_project_kernel(const T* __restrict__ x, const float* __restrict__ ln_w,
                                                          const float* __restrict__ ln_b, const float* __restrict__ w,
-                                                         float* __restrict__ out, long long rows, int c, int n_out, float eps) {
+                                                         const unsigned char* __restrict__ mask, float* __restrict__ out,
+                                                         long long rows, int c, int n_out, float eps, int samples, int l) {
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
+  if (mask != nullptr && mask[(row / (static_cast<long long>(samples) * l)) * l + row % l] == 0) {
+    if (lane < n_out) out[row * n_out + lane] = 0.f;   // padding atoms get a zero update
+    return;
+  }
   const T* xr = x + row * c;
   float s = 0.f;
   for (int i = lane; i < c; i += 32) s += ld_f(xr + i);
@@ -103,6 +110,26 @@ __global__ void __launch_bounds__(256) ln_project_kernel(const T* __restrict__ x
   }
 }
 
+// Per (index row, token): the first and last valid atom that maps to the token (first > last: none).  The mean below
+// then scans only that range; it still tests every atom in it, so unsorted indices stay correct, and for the usual
+// sorted atom order the range is just the token's own atoms.
+__global__ void __launch_bounds__(256) token_range_init_kernel(int2* __restrict__ range, long long n) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) range[i] = make_int2(0x7fffffff, -1);
+}
+__global__ void __launch_bounds__(256) token_range_kernel(const long long* __restrict__ index, const unsigned char* __restrict__ mask,
+                                                          int2* __restrict__ range, long long total, int n_atom, int n_token) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = index[i];
+  if (mask[i] == 0 || t < 0 || t >= n_token) return;
+  const long long row = i / n_atom;
+  const int a = static_cast<int>(i - row * n_atom);
+  int* r = reinterpret_cast<int*>(range + row * n_token + t);
+  atomicMin(r, a);
+  atomicMax(r + 1, a);
+}
+
 // out[b][t][:] = mean over the atoms a of batch entry b with mask[a] and index[a] == t of x[b][a][:] (0 for a token
 // without atoms); with `relu` the features pass through max(., 0) first.  One warp per (b, t): the warp scans the atom indices 32 at a time and adds the matching rows in
 // atom order with fp32 accumulators, so the result does not depend on scheduling.  kChunks * 32 channels per pass.
@@ -110,7 +137,7 @@ template <typename T, int kChunks>
 __global__ void __launch_bounds__(256) atoms_to_tokens_kernel(const T* __restrict__ x, const long long* __restrict__ index,
                                                               const unsigned char* __restrict__ mask, T* __restrict__ out,
                                                               long long rows, int n_atom, int n_token, int d, int index_div,
-                                                              int relu) {
+                                                              int relu, const int2* __restrict__ range) {
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -119,14 +146,20 @@ __global__ void __launch_bounds__(256) atoms_to_tokens_kernel(const T* __restric
   const long long* idx = index + (b / index_div) * n_atom;
   const unsigned char* mk = mask + (b / index_div) * n_atom;
   const T* xb = x + b * n_atom * d;
+  int a_begin = 0, a_end = n_atom;
+  if (range != nullptr) {
+    const int2 rg = range[(b / index_div) * n_token + t];
+    a_begin = rg.x <= rg.y ? (rg.x & ~31) : 0;      // aligned to the 32-atom steps of the scan
+    a_end = rg.x <= rg.y ? rg.y + 1 : 0;
+  }
   for (int d0 = 0; d0 < d; d0 += kChunks * 32) {
     float acc[kChunks];
 #pragma unroll
     for (int k = 0; k < kChunks; ++k) acc[k] = 0.f;
     int count = 0;
-    for (int a0 = 0; a0 < n_atom; a0 += 32) {
+    for (int a0 = a_begin; a0 < a_end; a0 += 32) {
       const int a = a0 + lane;
-      const bool hit = a < n_atom && mk[a] != 0 && idx[a] == t;
+      const bool hit = a < a_end && mk[a] != 0 && idx[a] == t;
       unsigned m = __ballot_sync(0xffffffffu, hit);
       count += __popc(m);
       while (m) {
@@ -187,8 +220,13 @@ KFB_API int kfb_tokens_to_atoms(const void* x, const long long* token_index, con
   return KFB_OK;
 }
 
-KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, int batch,
-                                int n_atom, int n_token, int d, int index_div, int relu, int dtype, void* stream_) {
+KFB_API size_t kfb_atoms_to_tokens_workspace_bytes(int batch, int n_token, int index_div) {
+  return align_up(static_cast<size_t>(batch / (index_div > 0 ? index_div : 1)) * n_token * sizeof(int2), 256);
+}
+
+KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, const unsigned char* mask, void* out, void* workspace,
+                                size_t workspace_bytes, int batch, int n_atom, int n_token, int d, int index_div, int relu,
+                                int dtype, void* stream_) {
   KFB_CHECK_ARG(x && token_index && mask && out, "atoms_to_tokens: null pointer");
   KFB_CHECK_ARG(dtype == KFB_BF16 || dtype == KFB_FP32, "atoms_to_tokens: dtype %d (bf16 or fp32)", dtype);
   KFB_CHECK_ARG(batch >= 1 && n_token >= 1 && n_atom >= 1 && d >= 1 && index_div >= 1 && batch % index_div == 0,
@@ -196,20 +234,33 @@ KFB_API int kfb_atoms_to_tokens(const void* x, const long long* token_index, con
   cudaStream_t stream = as_stream(stream_);
   const long long rows = static_cast<long long>(batch) * n_token;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  int2* range = nullptr;
+  if (workspace != nullptr) {
+    KFB_CHECK_ARG(workspace_bytes >= kfb_atoms_to_tokens_workspace_bytes(batch, n_token, index_div) &&
+                      (reinterpret_cast<uintptr_t>(workspace) & 7) == 0,
+                  "atoms_to_tokens: workspace too small or misaligned");
+    range = static_cast<int2*>(workspace);
+    const long long nr = static_cast<long long>(batch / index_div) * n_token, na = static_cast<long long>(batch / index_div) * n_atom;
+    LaunchScope scope_r(stream, "atoms_to_tokens_ranges");
+    token_range_init_kernel<<<static_cast<unsigned>((nr + 255) / 256), 256, 0, stream>>>(range, nr);
+    token_range_kernel<<<static_cast<unsigned>((na + 255) / 256), 256, 0, stream>>>(token_index, mask, range, na, n_atom, n_token);
+    KFB_CUDA(cudaGetLastError());
+  }
   LaunchScope scope(stream, "atoms_to_tokens");
   if (dtype == KFB_BF16)
     atoms_to_tokens_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), token_index, mask,
                                                                           static_cast<__nv_bfloat16*>(out), rows, n_atom, n_token, d,
-                                                                          index_div, relu);
+                                                                          index_div, relu, range);
   else
     atoms_to_tokens_kernel<float, 8><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), token_index, mask,
-                                                                  static_cast<float*>(out), rows, n_atom, n_token, d, index_div, relu);
+                                                                  static_cast<float*>(out), rows, n_atom, n_token, d, index_div, relu,
+                                                                  range);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }
 
-KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, float* out, long long rows, int c, int kc, int samples,
-                            int l, int q_dtype, void* stream_) {
+KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, const unsigned char* mask, float* out, long long rows,
+                            int c, int kc, int samples, int l, int q_dtype, void* stream_) {
   KFB_CHECK_ARG(q && r && w && out, "coord_embed: null pointer");
   KFB_CHECK_ARG(q_dtype == KFB_BF16 || q_dtype == KFB_FP32, "coord_embed: dtype %d (bf16 or fp32)", q_dtype);
   KFB_CHECK_ARG(rows >= 1 && c >= 1 && kc >= 1 && kc <= 4 && samples >= 1 && l >= 1 &&
@@ -219,27 +270,31 @@ KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, float
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   LaunchScope scope(stream, "coord_embed");
   if (q_dtype == KFB_BF16)
-    coord_embed_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(q), r, w, out, rows, c, kc,
+    coord_embed_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(q), r, w, mask, out, rows, c, kc,
                                                                    samples, l);
   else
-    coord_embed_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(q), r, w, out, rows, c, kc, samples, l);
+    coord_embed_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(q), r, w, mask, out, rows, c, kc, samples, l);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }
 
-KFB_API int kfb_ln_project(const void* x, const float* ln_w, const float* ln_b, const float* w, float* out, long long rows, int c,
-                           int n_out, float eps, int dtype, void* stream_) {
+KFB_API int kfb_ln_project(const void* x, const float* ln_w, const float* ln_b, const float* w, const unsigned char* mask,
+                           float* out, long long rows, int c, int n_out, float eps, int samples, int l, int dtype, void* stream_) {
   KFB_CHECK_ARG(x && w && out, "ln_project: null pointer");
   KFB_CHECK_ARG(dtype == KFB_BF16 || dtype == KFB_FP32, "ln_project: dtype %d (bf16 or fp32)", dtype);
   KFB_CHECK_ARG(rows >= 1 && c >= 1 && n_out >= 1 && n_out <= 8, "ln_project: rows %lld c %d outputs %d (at most 8)", rows, c, n_out);
+  if (mask == nullptr) samples = l = 1;
+  KFB_CHECK_ARG(samples >= 1 && l >= 1 && rows % (static_cast<long long>(samples) * l) == 0,
+                "ln_project: rows %lld are not a multiple of samples %d x l %d", rows, samples, l);
   cudaStream_t stream = as_stream(stream_);
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   LaunchScope scope(stream, "ln_project");
   if (dtype == KFB_BF16)
-    ln_project_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ln_w, ln_b, w, out, rows, c,
-                                                                  n_out, eps);
+    ln_project_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ln_w, ln_b, w, mask, out, rows,
+                                                                  c, n_out, eps, samples, l);
   else
-    ln_project_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), ln_w, ln_b, w, out, rows, c, n_out, eps);
+    ln_project_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), ln_w, ln_b, w, mask, out, rows, c, n_out, eps,
+                                                         samples, l);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }

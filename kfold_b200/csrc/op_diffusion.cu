@@ -48,6 +48,34 @@ KFB_API int kfb_linear_fp32(const void* x, const void* w6, const float* bias, vo
   return launch_gemm_bf16(stream, a, b, p, 0, "linear_fp32");
 }
 
+// out = LayerNorm(x) W^T (+ bias) (+ resid) at fp32 accuracy; `normalise` == 0 skips the LayerNorm
+KFB_API int kfb_ln_linear_fp32(const void* x, const float* ln_w, const float* ln_b, const void* w6, const float* bias,
+                               const void* resid, void* out, void* workspace, size_t workspace_bytes, long long rows, int n, int k,
+                               float eps, int normalise, void* stream_) {
+  KFB_CHECK_ARG(x && w6 && out && workspace, "ln_linear_fp32: null pointer");
+  KFB_CHECK_ARG(rows >= 1 && rows < (1ll << 31) && n >= 1 && k >= 8 && k % 8 == 0, "ln_linear_fp32: rows %lld n %d k %d", rows, n, k);
+  KFB_CHECK_ARG(workspace_bytes >= kfb_linear_fp32_workspace_bytes(rows, k), "ln_linear_fp32: workspace too small");
+  KFB_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ln_linear_fp32: workspace must be 256-byte aligned");
+  cudaStream_t stream = as_stream(stream_);
+  __nv_bfloat16* x6 = static_cast<__nv_bfloat16*>(workspace);
+  KFB_TRY(launch_layernorm_split(stream, static_cast<const float*>(x), x6, normalise ? ln_w : nullptr, normalise ? ln_b : nullptr, rows,
+                                 k, k, eps, normalise ? 1 : 0));
+  GemmParams p = {};
+  p.n_extent = static_cast<int>(rows);
+  p.o_extent = 1;
+  p.batch = 1;
+  p.n_cols = n;
+  p.k_extent = 6 * k;
+  p.precise = 1;
+  p.nseg = 1;
+  p.seg[0] = row_major_seg(out, n, n, 0, 0, 1);
+  p.col_bias = bias;
+  p.resid = resid;
+  GemmOperandA a = {x6, 6ll * k, 0, 0};
+  GemmOperandB b = {w6, 6ll * k, 0};
+  return launch_gemm_bf16(stream, a, b, p, 0, "ln_linear_fp32");
+}
+
 KFB_API size_t kfb_cond_transition_workspace_bytes_precise(long long rows, int c, int hidden) {
   return align_up(static_cast<size_t>(rows) * 6 * c * 2, 256) + align_up(static_cast<size_t>(rows) * 6 * hidden * 2, 256);
 }

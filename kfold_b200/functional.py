@@ -183,6 +183,28 @@ def linear_fp32(x: torch.Tensor, w6: torch.Tensor, bias: torch.Tensor | None = N
     return out.view(*x.shape[:-1], n)
 
 
+def ln_linear_fp32(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | None, w6: torch.Tensor,
+                   bias: torch.Tensor | None = None, resid: torch.Tensor | None = None, eps: float = 1e-5) -> torch.Tensor:
+    """resid + LayerNorm(x) w^T (+ bias) at float32 accuracy (model/layers/folding/diffusion.py:568): x (..., k) float32,
+    w6 (n, 6k) the bf16 triple split of w; float32 result."""
+    _require_cuda(x, w6)
+    k = x.shape[-1]
+    if w6.shape[1] != 6 * k:
+        raise ValueError(f"ln_linear_fp32: weight {tuple(w6.shape)} is not the triple split of a (n, {k}) matrix")
+    x2 = x.reshape(-1, k).float().contiguous()
+    n = w6.shape[0]
+    out = torch.empty(x2.shape[0], n, dtype=torch.float32, device=x.device)
+    res = None if resid is None else resid.expand(*x.shape[:-1], n).reshape(-1, n).float().contiguous()
+    f32 = lambda t: None if t is None else t.detach().float().contiguous()
+    lw, lb = f32(ln_w), f32(ln_b)
+    lib = L.lib()
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, lib.kfb_linear_fp32_workspace_bytes(x2.shape[0], k))
+        L.check(lib.kfb_ln_linear_fp32(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(w6), L.ptr(bias), L.ptr(res), L.ptr(out), L.ptr(ws),
+                                       ws.numel(), x2.shape[0], n, k, eps, 1, L.stream_ptr()))
+    return out.view(*x.shape[:-1], n)
+
+
 def adaln(a: torch.Tensor, gate_shift: torch.Tensor, samples: int, eps: float = 1e-5) -> torch.Tensor:
     """sigmoid(g) * LayerNorm(a) + v  (model/primitives/normalization.py:117-125).
     a (groups * samples, L, c) flattened as rows; gate_shift (groups, L, 2c) bf16 = [g | v]."""
@@ -593,15 +615,31 @@ def aggregate_atoms_to_tokens(x: torch.Tensor, token_index: torch.Tensor, mask: 
     mk = mk.reshape(-1, n_atom).contiguous().view(torch.uint8)
     x2 = x.reshape(-1, n_atom, d).contiguous()
     out = torch.empty(x2.shape[0], num_tokens, d, dtype=x.dtype, device=x.device)
+    lib = L.lib()
     with torch.cuda.device(x.device):
-        L.check(L.lib().kfb_atoms_to_tokens(L.ptr(x2), L.ptr(idx), L.ptr(mk), L.ptr(out), x2.shape[0], n_atom, num_tokens, d, div,
+        ws = _workspace(x.device, lib.kfb_atoms_to_tokens_workspace_bytes(x2.shape[0], num_tokens, div))
+        L.check(lib.kfb_atoms_to_tokens(L.ptr(x2), L.ptr(idx), L.ptr(mk), L.ptr(out), L.ptr(ws), ws.numel(), x2.shape[0], n_atom,
+                                        num_tokens, d, div,
                                             1 if relu else 0, L.dtype_code(x.dtype), L.stream_ptr()))
     return out.view(*lead, num_tokens, d)
 
 
-def coord_embed(q: torch.Tensor, r: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def _shared_mask(mask: torch.Tensor | None, lead: tuple, l: int, share: int):
+    """The atom mask as bytes with one row per `share` consecutive batch entries, or None."""
+    if mask is None:
+        return None
+    m = mask.to(torch.bool)
+    if _index_sharing(lead, tuple(m.shape[:-1])) != share:
+        m = m.expand(*lead, l)
+        if share != 1:
+            raise ValueError("the atom mask must be shared like the atom features")
+    return m.reshape(-1, l).contiguous().view(torch.uint8)
+
+
+def coord_embed(q: torch.Tensor, r: torch.Tensor, w: torch.Tensor, mask: torch.Tensor | None = None) -> torch.Tensor:
     """q + Linear_fp32(r) (model/layers/folding/atom_transformer.py:362-367): q (*, [1 or N,] La, c) bf16 or float32,
-    r (*, N, La, k) coordinates, w (c, k) -> float32 (*, N, La, c).  q's sample dimension may be 1 (shared)."""
+    r (*, N, La, k) coordinates, w (c, k) -> float32 (*, N, La, c).  q's sample dimension may be 1 (shared).
+    ``mask`` (atom validity, shared like q): the coordinates of padding atoms count as zero."""
     _require_cuda(q, r, w)
     c, kc = w.shape
     lead, l = tuple(r.shape[:-2]), r.shape[-2]
@@ -615,16 +653,18 @@ def coord_embed(q: torch.Tensor, r: torch.Tensor, w: torch.Tensor) -> torch.Tens
     q2 = q.reshape(-1, c).contiguous()
     r2 = r.reshape(-1, kc).float().contiguous()
     out = torch.empty(r2.shape[0], c, dtype=torch.float32, device=r.device)
+    mk = _shared_mask(mask, lead, l, share)
     with torch.cuda.device(r.device):
-        L.check(L.lib().kfb_coord_embed(L.ptr(q2), L.ptr(r2), L.ptr(w.detach().float().contiguous()), L.ptr(out), r2.shape[0], c, kc,
+        L.check(L.lib().kfb_coord_embed(L.ptr(q2), L.ptr(r2), L.ptr(w.detach().float().contiguous()), L.ptr(mk), L.ptr(out), r2.shape[0], c, kc,
                                         share, l, L.dtype_code(q2.dtype), L.stream_ptr()))
     return out.view(*lead, l, c)
 
 
 def ln_project(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | None, w: torch.Tensor,
-               eps: float = 1e-5) -> torch.Tensor:
+               eps: float = 1e-5, mask: torch.Tensor | None = None) -> torch.Tensor:
     """Linear_fp32(LayerNorm(x.float())) to a handful of outputs (model/layers/folding/atom_transformer.py:487-488):
-    x (*, c) bf16 or float32, w (n_out <= 8, c) -> float32 (*, n_out)."""
+    x (*, L, c) bf16 or float32, w (n_out <= 8, c) -> float32 (*, L, n_out).  ``mask`` (*, L), leading dims 1 where
+    shared: rows of padding atoms give zeros."""
     _require_cuda(x, w)
     c, n_out = x.shape[-1], w.shape[0]
     if x.dtype not in (torch.bfloat16, torch.float32):
@@ -633,9 +673,14 @@ def ln_project(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | 
     out = torch.empty(x2.shape[0], n_out, dtype=torch.float32, device=x.device)
     f32 = lambda t: None if t is None else t.detach().float().contiguous()
     lw, lb, ww = f32(ln_w), f32(ln_b), f32(w)
+    mk, share, l = None, 1, 1
+    if mask is not None:
+        lead, l = tuple(x.shape[:-2]), x.shape[-2]
+        share = _index_sharing(lead, tuple(mask.shape[:-1])) or 1
+        mk = _shared_mask(mask, lead, l, share)
     with torch.cuda.device(x.device):
-        L.check(L.lib().kfb_ln_project(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(ww), L.ptr(out), x2.shape[0], c, n_out, eps,
-                                       L.dtype_code(x2.dtype), L.stream_ptr()))
+        L.check(L.lib().kfb_ln_project(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(ww), L.ptr(mk), L.ptr(out), x2.shape[0], c, n_out, eps,
+                                       share, l, L.dtype_code(x2.dtype), L.stream_ptr()))
     return out.view(*x.shape[:-1], n_out)
 
 

@@ -481,28 +481,32 @@ class TokenPairBias(nn.Module):
         self.blocks, self.heads = token_transformer_blocks, token_transformer_heads
         self.layernorm_z = LayerNorm(channel_z, create_offset=False)
         self.linear_z_to_bias = LinearNoBias(channel_z, token_transformer_blocks * token_transformer_heads)
-        self._w = None
-        self._w_key = None
+        self._cache = {}
 
     @torch.compiler.disable
     def forward(self, z: torch.Tensor) -> torch.Tensor:
-        _check_inference(z)
-        precise = _is_precise(compute_dtype(z), "TokenPairBias")
-        w = self.linear_z_to_bias.weight
-        key = (z.device, precise, w.data_ptr(), None if torch.is_inference(w) else w._version)
-        if self._w_key != key:
-            self._w = packing.split3_weights(w).to(z.device) if precise else w.detach().to(z.device, torch.bfloat16).contiguous()
-            self._w_key = key
-        b, l = z.shape[0], z.shape[1]
-        lp = (l + 7) // 8 * 8
-        with torch.autocast(z.device.type, enabled=False):
-            zz = z.float() if precise else z.to(torch.bfloat16)
-            if lp != l:
-                zz = torch.nn.functional.pad(zz, (0, 0, 0, lp - l, 0, lp - l))
-            ln = self.layernorm_z
-            out = F.pair_bias(zz, ln.weight.detach().float(), None, self._w, ln.eps)      # (B, blocks*H, L, L)
-        out = out.view(b, self.blocks, self.heads, lp, lp)
-        return out if lp == l else out[..., :l, :l]
+        return _token_pair_bias(z, self.layernorm_z, self.linear_z_to_bias, self.blocks, self.heads, self._cache)
+
+
+def _token_pair_bias(z: torch.Tensor, layernorm_z, linear_z_to_bias, blocks: int, heads: int, cache: dict) -> torch.Tensor:
+    """LayerNorm(z) projected to blocks x heads values per pair, laid out (B, Nblock, H, L, L)
+    (model/layers/folding/diffusion.py:411-416); `cache` keeps the device copy of the projection weight."""
+    _check_inference(z)
+    precise = _is_precise(compute_dtype(z), "TokenPairBias")
+    w = linear_z_to_bias.weight
+    key = (z.device, precise, w.data_ptr(), None if torch.is_inference(w) else w._version)
+    if cache.get("key") != key:
+        cache["w"] = packing.split3_weights(w).to(z.device) if precise else w.detach().to(z.device, torch.bfloat16).contiguous()
+        cache["key"] = key
+    b, l = z.shape[0], z.shape[1]
+    lp = (l + 7) // 8 * 8
+    with torch.autocast(z.device.type, enabled=False):
+        zz = z.float() if precise else z.to(torch.bfloat16)
+        if lp != l:
+            zz = torch.nn.functional.pad(zz, (0, 0, 0, lp - l, 0, lp - l))
+        out = F.pair_bias(zz, layernorm_z.weight.detach().float(), None, cache["w"], layernorm_z.eps)      # (B, blocks*H, L, L)
+    out = out.view(b, blocks, heads, lp, lp)
+    return out if lp == l else out[..., :l, :l]
 
 
 class CachedGlobalTransformerBlock(nn.Module):
@@ -868,15 +872,16 @@ class AtomAttentionEncoder(nn.Module):
 
     @torch.compiler.disable
     def forward(self, q: torch.Tensor, c: torch.Tensor, p: torch.Tensor, token_index: torch.Tensor, mask: torch.Tensor,
-                num_tokens: int, r_noisy: torch.Tensor | None = None):
+                num_tokens: int, r_noisy: torch.Tensor | None = None, mask_coords: bool = False):
         """q (*, La, c_atom); c (*, La, c_atom); p (*, W, 32, 128, c_atompair); token_index, mask (*, La);
-        r_noisy (*, N, La, 3) -> (a (*, Lt, c_token), q_skip, c_skip, p_skip)."""
+        r_noisy (*, N, La, 3) -> (a (*, Lt, c_token), q_skip, c_skip, p_skip).  ``mask_coords``: the coordinates of
+        padding atoms count as zero (the `r_noisy * atom_mask` of DiffusionStack.step, fused into the embedding)."""
         _check_inference(q)
         precise = _is_precise(compute_dtype(q), "AtomAttentionEncoder")
         if self.use_structure:
             assert r_noisy is not None, "r_noisy must be provided if use_structure is True"
             with torch.autocast(q.device.type, enabled=False):
-                q = F.coord_embed(q, r_noisy, self.linear_r_to_q.weight)
+                q = F.coord_embed(q, r_noisy, self.linear_r_to_q.weight, mask=mask if mask_coords else None)
         else:
             assert r_noisy is None, "r_noisy must be None if use_structure is False"
         q = self.transformer(q, c, p, mask)
@@ -903,9 +908,10 @@ class AtomAttentionDecoder(nn.Module):
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, q_skip: torch.Tensor, c_skip: torch.Tensor, p_skip: torch.Tensor,
-                token_index: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+                token_index: torch.Tensor, mask: torch.Tensor, mask_out: bool = False) -> torch.Tensor:
         """a (*, Lt, c_token); q_skip, c_skip (*, La, c_atom); p_skip (*, W, 32, 128, c_atompair); token_index, mask
-        (*, La) -> float32 position updates (*, La, 3)."""
+        (*, La) -> float32 position updates (*, La, 3).  ``mask_out``: padding atoms get a zero update (the
+        `r_update * atom_mask` of DiffusionStack.step, fused into the projection)."""
         _check_inference(a)
         precise = _is_precise(compute_dtype(a), "AtomAttentionDecoder")
         with torch.autocast(a.device.type, enabled=False):
@@ -914,7 +920,67 @@ class AtomAttentionDecoder(nn.Module):
         q = self.transformer(q, c_skip, p_skip, mask)
         ln = self.layernorm_q
         with torch.autocast(a.device.type, enabled=False):
-            return F.ln_project(q, ln.weight, ln.bias, self.linear_q_to_r.weight, ln.eps)
+            return F.ln_project(q, ln.weight, ln.bias, self.linear_q_to_r.weight, ln.eps, mask=mask if mask_out else None)
+
+
+class DiffusionStack(nn.Module):
+    """The time-dependent part of the AF3 diffusion module, ``DiffusionStack.step`` with ``get_single_conditioning`` and
+    ``get_pair_bias`` (model/layers/folding/diffusion.py:155-600, AF3 Algorithm 20): atom attention encoder ->
+    token transformer -> atom attention decoder.  Sub-module and parameter names are the reference's, so the matching
+    part of a reference state dict loads by name.  Not included: ``pair_conditioning`` and ``atom_embedder`` (they run once
+    per complex, before the sampler loop) and the separate-endpoint encoder variant."""
+
+    def __init__(self, channel_a: int = 768, channel_s: int = 384, channel_z: int = 256, channel_atom: int = 128,
+                 channel_atompair: int = 16, channel_coords: int = 3, separate_endpoint_atom_encoder: bool = False,
+                 atom_encoder_blocks: int = 3, atom_encoder_heads: int = 4, token_transformer_blocks: int = 24,
+                 token_transformer_heads: int = 16, atom_decoder_blocks: int = 3, atom_decoder_heads: int = 4,
+                 blocks_per_ckpt: int | None = None, ckpt_atom_stack: bool = False, kernel_backend: str = "b200"):
+        super().__init__()
+        if separate_endpoint_atom_encoder:
+            raise NotImplementedError("DiffusionStack: the separate-endpoint atom encoder variant is not available")
+        self.kernel_backend = kernel_backend
+        self.token_transformer_blocks, self.token_transformer_heads = token_transformer_blocks, token_transformer_heads
+        self.single_conditioning = SingleConditioning(channel_s, dim_fourier=256)
+        self.atom_attention_encoder = AtomAttentionEncoder(channel_atom, channel_atompair, channel_a, channel_coords,
+                                                           atom_encoder_blocks, atom_encoder_heads, use_structure=True)
+        self.layernorm_s = LayerNorm(channel_s, create_offset=False)
+        self.linear_s_to_a = LinearNoBias(channel_s, channel_a)
+        self.layernorm_z = LayerNorm(channel_z, create_offset=False)
+        self.linear_z_to_bias = LinearNoBias(channel_z, token_transformer_blocks * token_transformer_heads)
+        self.token_transformer = CachedGlobalTransformerStack(channel_a, channel_s, token_transformer_heads,
+                                                              token_transformer_blocks)
+        self.layernorm_a = LayerNorm(channel_a, create_offset=False)
+        self.atom_attention_decoder = AtomAttentionDecoder(channel_a, channel_atom, channel_atompair, atom_decoder_blocks,
+                                                           atom_decoder_heads)
+        self._proj = _ProjectionCache()
+        self._bias_w = {}
+
+    def get_single_conditioning(self, s_inputs: torch.Tensor, c_noise: torch.Tensor) -> torch.Tensor:
+        return self.single_conditioning(s_inputs, c_noise)
+
+    def get_pair_bias(self, z: torch.Tensor) -> torch.Tensor:
+        """(B, Nblock, H, Lt, Lt): bf16 under bfloat16 compute, float32 under float32 compute; time-independent."""
+        return _token_pair_bias(z, self.layernorm_z, self.linear_z_to_bias, self.token_transformer_blocks,
+                                self.token_transformer_heads, self._bias_w)
+
+    @torch.compiler.disable
+    def step(self, r_noisy: torch.Tensor, q: torch.Tensor, c: torch.Tensor, p: torch.Tensor, token_index: torch.Tensor,
+             atom_mask: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, token_mask: torch.Tensor) -> torch.Tensor:
+        """r_noisy (B, N, La, 3); q, c (B, La, c_atom); p (B, W, 32, 128, c_atompair); token_index, atom_mask (B, La);
+        s (B, N, Lt, c_s); pair_bias (B, Nblock, H, Lt, Lt); token_mask (B, Lt) -> float32 position updates (B, N, La, 3)."""
+        _check_inference(r_noisy)
+        q, c, p = q.unsqueeze(-3), c.unsqueeze(-3), p.unsqueeze(-5)
+        atom_mask, token_mask, token_index = atom_mask.unsqueeze(-2), token_mask.unsqueeze(-2), token_index.unsqueeze(-2)
+        a, q_skip, c_skip, p_skip = self.atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1],
+                                                                r_noisy=r_noisy, mask_coords=True)
+        ln = self.layernorm_s
+        with torch.autocast(a.device.type, enabled=False):
+            # a.float() + linear_s_to_a(layernorm_s(s)): a float32 Linear in the reference whatever the autocast state
+            a = F.ln_linear_fp32(s.float(), ln.weight, ln.bias, self._proj.get(self.linear_s_to_a, a.device, True), None,
+                                 resid=a.float(), eps=ln.eps)
+        a = self.token_transformer(a, s, pair_bias.unsqueeze(-5), token_mask)
+        a = self.layernorm_a(a)
+        return self.atom_attention_decoder(a, q_skip, c_skip, p_skip, token_index, atom_mask, mask_out=True)
 
 
 # --------------------------------------------------------------------------------------------

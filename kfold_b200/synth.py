@@ -153,6 +153,21 @@ def single_conditioning_weights(rng: _Rng, c_s: int, dim_fourier: int) -> dict:
     return w
 
 
+def diffusion_step_weights(rng: _Rng, c_a: int, c_s: int, c_atom: int, c_pair: int, atom_blocks: int, atom_heads: int,
+                           token_blocks: int, token_heads: int) -> dict:
+    """The parameters DiffusionStack.step touches (model/layers/folding/diffusion.py:250-325): atom attention encoder and
+    decoder, layernorm_s / linear_s_to_a, the token transformer, layernorm_a."""
+    w = _prefixed("atom_attention_encoder", atom_encoder_weights(rng, c_atom, c_pair, c_a, atom_heads, atom_blocks, True))
+    w["layernorm_s.weight"] = rng.ln_w(c_s)
+    w["linear_s_to_a.weight"] = rng.linear(c_a, c_s)
+    for i in range(token_blocks):
+        w.update(_prefixed(f"token_transformer.blocks.{i}.attention", apb_weights(rng, c_a, c_s)))
+        w.update(_prefixed(f"token_transformer.blocks.{i}.transition", conditioned_transition_weights(rng, c_a, c_s)))
+    w["layernorm_a.weight"] = rng.ln_w(c_a)
+    w.update(_prefixed("atom_attention_decoder", atom_decoder_weights(rng, c_a, c_atom, c_pair, atom_heads, atom_blocks)))
+    return w
+
+
 def conditioned_transition_weights(rng: _Rng, c_a: int, c_s: int, factor: int = 2) -> dict:
     """ConditionedTransitionBlock (model/layers/folding/diffusion_transformer.py:50-71)."""
     w = _prefixed("adaln", adaln_weights(rng, c_a, c_s))

@@ -373,6 +373,24 @@ def single_conditioning(s_inputs, c_noise, w: dict, mode: str = "fp32"):
     return s
 
 
+def diffusion_step(r_noisy, q, c, p, token_index, atom_mask, s, pair_bias, token_mask, w: dict, atom_heads: int,
+                   atom_blocks: int, token_heads: int, token_blocks: int, mode: str = "fp32"):
+    """``DiffusionStack.step`` -- model/layers/folding/diffusion.py:465-600 (the plain, single-encoder variant)."""
+    q, c, p = q.unsqueeze(-3), c.unsqueeze(-3), p.unsqueeze(-5)
+    atom_mask, token_mask, token_index = atom_mask.unsqueeze(-2), token_mask.unsqueeze(-2), token_index.unsqueeze(-2)
+    r_noisy = r_noisy * atom_mask[..., None]
+    a, q_skip = atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1], r_noisy,
+                                       sub(w, "atom_attention_encoder"), atom_heads, atom_blocks, mode)
+    sn = F.layer_norm(s.float(), (s.shape[-1],), w["layernorm_s.weight"].float(), None, 1e-5)
+    a = a.float() + F.linear(sn, w["linear_s_to_a.weight"].float())
+    a = global_transformer_stack(a, s, pair_bias.unsqueeze(-5), token_mask, sub(w, "token_transformer"), token_heads, token_blocks,
+                                 mode)
+    a = layer_norm(a, w["layernorm_a.weight"], None, 1e-5, mode)
+    r_update = atom_attention_decoder(a, q_skip, c, p, token_index, atom_mask, sub(w, "atom_attention_decoder"), atom_heads,
+                                      atom_blocks, mode)
+    return r_update * atom_mask[..., None]
+
+
 def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
     """``TriangularBlock.forward`` (eval) -- model/modules/tri_stack.py:130-151."""
     m = _Mode(mode)

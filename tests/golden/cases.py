@@ -52,6 +52,9 @@ CASES = {
                          samples=2, valid=90),
     # single conditioning of the sampler: 40 tokens, 3 noise levels
     "single_conditioning": dict(kind="single_conditioning", seed=49, l=40, c_s=384, dim_fourier=256, samples=3),
+    # DiffusionStack.step: encoder (2 blocks) -> token transformer (2 blocks) -> decoder (2 blocks); 24 tokens, 96 atoms, 2 samples
+    "diffusion_step": dict(kind="diffusion_step", seed=50, tokens=24, atoms=96, c_a=256, c_s=384, c_z=128, c_atom=128, c_pair=16,
+                           atom_blocks=2, atom_heads=4, token_blocks=2, token_heads=8, samples=2, valid_atoms=90, valid_tokens=23),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -133,6 +136,18 @@ def build_inputs(name: str) -> dict:
         out["w"] = synth.single_conditioning_weights(rng, cs["c_s"], cs["dim_fourier"])
         out["s_inputs"] = rng.normal(1, cs["l"], cs["c_s"])
         out["c_noise"] = rng.normal(1, cs["samples"]) * 1.5       # 1/4 log(t_hat / sigma_data) spans about +-2
+    elif kind == "diffusion_step":
+        nt, na, ns = cs["tokens"], cs["atoms"], cs["samples"]
+        out["w"] = synth.diffusion_step_weights(rng, cs["c_a"], cs["c_s"], cs["c_atom"], cs["c_pair"], cs["atom_blocks"],
+                                                cs["atom_heads"], cs["token_blocks"], cs["token_heads"])
+        out["r_noisy"] = rng.normal(1, ns, na, 3) * 4.0
+        out["q"], out["c"] = rng.normal(1, na, cs["c_atom"]), rng.normal(1, na, cs["c_atom"])
+        out["p"] = rng.normal(1, na // 32, 32, 128, cs["c_pair"])
+        out["token_index"] = torch.from_numpy(np.sort(rng.rs.randint(0, cs["valid_tokens"], size=na)).astype(np.int64)).view(1, na)
+        out["atom_mask"] = synth.token_mask(na, cs["valid_atoms"]).view(1, na)
+        out["s"] = rng.normal(1, ns, nt, cs["c_s"])
+        out["pair_bias"] = rng.normal(1, cs["token_blocks"], cs["token_heads"], nt, nt)
+        out["token_mask"] = synth.token_mask(nt, cs["valid_tokens"]).view(1, nt)
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

@@ -98,6 +98,22 @@ def run_reference(ns, name: str) -> dict:
         df = importlib.import_module("kfold.model.layers.folding.diffusion")
         mod = _load(df.SingleConditioning(cs["c_s"], cs["dim_fourier"]), inp["w"])
         return {"out": mod(inp["s_inputs"], inp["c_noise"]), "fourier_w": mod.fourier_embed.w, "fourier_b": mod.fourier_embed.b}
+    if kind == "diffusion_step":
+        import importlib
+        df = importlib.import_module("kfold.model.layers.folding.diffusion")
+        mod = df.DiffusionStack(channel_a=cs["c_a"], channel_s=cs["c_s"], channel_z=cs["c_z"], channel_atom=cs["c_atom"],
+                                channel_atompair=cs["c_pair"], atom_encoder_blocks=cs["atom_blocks"],
+                                atom_encoder_heads=cs["atom_heads"], token_transformer_blocks=cs["token_blocks"],
+                                token_transformer_heads=cs["token_heads"], atom_decoder_blocks=cs["atom_blocks"],
+                                atom_decoder_heads=cs["atom_heads"], kernel_backend="torch")
+        missing, unexpected = mod.load_state_dict(inp["w"], strict=False)   # the time-independent parts are not used by step()
+        assert not unexpected, unexpected
+        mod.eval()
+        for m in mod.modules():
+            if getattr(m, "kernel_backend", None) == "sdpa":
+                m.kernel_backend = "torch"      # the oracle path; the constructors hard-code "sdpa"
+        return {"out": mod.step(inp["r_noisy"], inp["q"], inp["c"], inp["p"], inp["token_index"], inp["atom_mask"], inp["s"],
+                                inp["pair_bias"], inp["token_mask"])}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "block":

@@ -572,6 +572,15 @@ def test_token_atom_maps_against_reference_golden(dev):
         tokens = F.aggregate_atoms_to_tokens(xa, index, m, cs["tokens"])
         assert (tokens.cpu() - gold["tokens"]).abs().max() < 1e-6
         assert (tokens[..., cs["tokens"] - 2, :] == 0).all()
+    # atoms in a shuffled order: every token's range then spans most of the molecule; same means up to the summation order
+    perm = torch.randperm(cs["atoms"], generator=torch.Generator().manual_seed(5)).to(dev)
+    shuffled = F.aggregate_atoms_to_tokens(xa[..., perm, :].contiguous(), idx[..., perm].contiguous(), mask[..., perm].contiguous(),
+                                           cs["tokens"])
+    assert (shuffled.cpu() - gold["tokens"]).abs().max() < 1e-5
+    relu_mean = F.aggregate_atoms_to_tokens(xa, idx, mask, cs["tokens"], relu=True)
+    ref_relu = O.aggregate_atoms_to_tokens(torch.relu(inp["x_atom"]), inp["token_index"].expand(1, cs["samples"], -1),
+                                           inp["mask"].expand(1, cs["samples"], -1), cs["tokens"])
+    assert (relu_mean.cpu() - ref_relu).abs().max() < 1e-6
     atoms16 = F.broadcast_tokens_to_atoms(xt.bfloat16(), idx)
     assert torch.equal(atoms16.float().cpu(), gold["atoms"].bfloat16().float())
     tokens16 = F.aggregate_atoms_to_tokens(xa.bfloat16(), idx, mask, cs["tokens"])
@@ -743,3 +752,28 @@ def test_single_conditioning_against_reference_golden(dev):
     with torch.autocast("cuda", dtype=torch.bfloat16):
         out = mod(s_in, c_noise)
     _check(*err_stats(out.float().cpu(), gold["out"]), "single conditioning, bf16 transitions")
+
+
+def test_diffusion_stack_step_against_reference_golden(dev):
+    """DiffusionStack.step (atom encoder -> token transformer -> atom decoder) against the reference's output: float32
+    compute at float32 accuracy, bfloat16 compute within bf16 noise.  Weights load by the reference's parameter names."""
+    from kfold_b200 import modules as M
+    inp = cases.build_inputs("diffusion_step")
+    cs = inp["case"]
+    gold = load_golden("diffusion_step")["out"]
+    mod = M.DiffusionStack(channel_a=cs["c_a"], channel_s=cs["c_s"], channel_z=cs["c_z"], channel_atom=cs["c_atom"],
+                           channel_atompair=cs["c_pair"], atom_encoder_blocks=cs["atom_blocks"], atom_encoder_heads=cs["atom_heads"],
+                           token_transformer_blocks=cs["token_blocks"], token_transformer_heads=cs["token_heads"],
+                           atom_decoder_blocks=cs["atom_blocks"], atom_decoder_heads=cs["atom_heads"]).to(dev)
+    missing, unexpected = mod.load_state_dict(inp["w"], strict=False)
+    assert not unexpected and all(k.startswith(("single_conditioning.", "layernorm_z.", "linear_z_to_bias.")) for k in missing)
+    args = [inp[k].to(dev) for k in ("r_noisy", "q", "c", "p", "token_index", "atom_mask", "s", "pair_bias", "token_mask")]
+    out = mod.step(*args)
+    assert out.dtype == torch.float32 and out.shape == gold.shape
+    keep = inp["atom_mask"].reshape(-1)
+    assert (out.cpu()[..., ~keep, :] == 0).all()                       # padding atoms get a zero update
+    mx, r = err_stats(out.cpu(), gold)
+    assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"diffusion step fp32: {mx:.3e} {r:.3e}"
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = mod.step(*args)
+    _check(*err_stats(out.cpu(), gold), "diffusion step, bf16")

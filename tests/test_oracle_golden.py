@@ -41,6 +41,10 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
                                                 cs["heads"], cs["blocks"], mode)}
     if kind == "single_conditioning":
         return {"out": O.single_conditioning(inp["s_inputs"], inp["c_noise"], w, mode)}
+    if kind == "diffusion_step":
+        return {"out": O.diffusion_step(inp["r_noisy"], inp["q"], inp["c"], inp["p"], inp["token_index"], inp["atom_mask"], inp["s"],
+                                        inp["pair_bias"], inp["token_mask"], w, cs["atom_heads"], cs["atom_blocks"],
+                                        cs["token_heads"], cs["token_blocks"], mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "block":
