@@ -234,12 +234,15 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
     const TI* xr = a + row * c;
     const long long srow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
     const TG* gr = gv + srow * gv_ld;
-    float2 v[G];
+    float2 v[G], gate[G], shift[G];
     float s = 0.f;
+    // the gate / shift rows do not depend on the statistics: their loads are issued together with the row's own
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int ch = (lane + 32 * g) * 2;
       v[g] = ch < c ? load2<TI>(xr + ch) : make_float2(0.f, 0.f);
+      gate[g] = ch < c ? load2<TG>(gr + ch) : make_float2(0.f, 0.f);
+      shift[g] = ch < c ? load2<TG>(gr + c + ch) : make_float2(0.f, 0.f);
       s += v[g].x + v[g].y;
     }
     const float mean = warp_sum(s) / static_cast<float>(c);
@@ -259,10 +262,8 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const TI* __restrict__ 
     for (int g = 0; g < G; ++g) {
       const int ch = (lane + 32 * g) * 2;
       if (ch < c) {
-        const float2 gate = load2<TG>(gr + ch);
-        const float2 shift = load2<TG>(gr + c + ch);
-        const float s0 = 1.f / (1.f + __expf(-gate.x)), s1 = 1.f / (1.f + __expf(-gate.y));
-        store2<TO>(yr + ch, s0 * (v[g].x * rstd) + shift.x, s1 * (v[g].y * rstd) + shift.y);
+        const float s0 = 1.f / (1.f + __expf(-gate[g].x)), s1 = 1.f / (1.f + __expf(-gate[g].y));
+        store2<TO>(yr + ch, s0 * (v[g].x * rstd) + shift[g].x, s1 * (v[g].y * rstd) + shift[g].y);
       }
     }
   }
