@@ -15,7 +15,8 @@ import os
 import sys
 import types
 
-_DEFAULT_ROOT = "/root/reference"
+# default: a checkout named "reference" beside this repository; KFOLD_REFERENCE_ROOT overrides it
+_DEFAULT_ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 
 
 def reference_root() -> str | None:
