@@ -159,3 +159,48 @@ def test_pack_apb_cross_layout():
     assert torch.equal(pk["w_kv"][128:].float(), w["linear_v.weight"].bfloat16().float())
     pkp = packing.pack_apb_cross({k: w[k] for k in keys}, 4, "cpu", precise=True)
     assert pkp["w_q"].shape == (256, 6 * 128) and pkp["w_kv"].shape == (256, 6 * 128) and pkp["precise"]
+
+
+def test_rows_helper_passes_column_slices_as_they_lie():
+    """A column slice of a wide row-major table reaches the kernels as (pointer, rows, row stride) without a copy; layouts
+    that are not rows at a constant stride are made contiguous."""
+    from kfold_b200.functional import _rows
+    table = torch.zeros(2, 1, 40, 96, dtype=torch.bfloat16)
+    sl = table[..., 32:64]
+    t, rows, ld = _rows(sl, 32)
+    assert t.data_ptr() == sl.data_ptr() and rows == 80 and ld == 96
+    t, rows, ld = _rows(table, 96)
+    assert rows == 80 and ld == 96
+    t, rows, ld = _rows(sl.expand(2, 3, 40, 32), 32)             # a broadcast dimension: copied
+    assert t.is_contiguous() and rows == 240 and ld == 32
+    t, rows, ld = _rows(table[..., 4:36], 32)                     # misaligned start: copied
+    assert t.is_contiguous() and ld == 32
+    t, rows, ld = _rows(sl, 32, torch.float32)                    # dtype change: converted, then dense
+    assert t.dtype == torch.float32 and rows == 80
+
+
+def test_conditioning_tables_fold_the_layernorm_scale():
+    """The stacked, scale-folded AdaLN matrices of a stack reproduce every AdaLN's gate / shift rows:
+    LN(s) (W * gamma)^T + b == (LN(s) * gamma) W^T + b, and the gate table is the plain stack of the gate Linears."""
+    from kfold_b200 import modules as M
+    torch.manual_seed(3)
+    c_a, c_s = 64, 48
+    adalns = [M.AdaLN(c_a, c_s) for _ in range(3)]
+    gates = [M.Linear(c_s, c_a) for _ in range(2)]
+    for m in adalns:
+        m.layernorm_s.weight.data = 1.0 + 0.2 * torch.randn(c_s)
+        m.linear_g.bias.data = torch.randn(c_a)
+    for g in gates:
+        g.bias.data = torch.randn(c_a)
+    w1, b1, w2, b2 = M._ConditioningBank()._pack(adalns, gates, torch.device("cpu"))
+    assert w1.shape == (3 * 2 * c_a, c_s) and w2.shape == (2 * c_a, c_s) and w1.dtype == torch.bfloat16
+    s = torch.randn(10, c_s)
+    sn = torch.nn.functional.layer_norm(s, (c_s,))
+    t1 = sn @ w1.float().t() + b1
+    t2 = s @ w2.float().t() + b2
+    for i, m in enumerate(adalns):
+        sm = sn * m.layernorm_s.weight
+        ref = torch.cat([sm @ m.linear_g.weight.t() + m.linear_g.bias, sm @ m.linear_bias.weight.t()], dim=-1)
+        assert (t1[:, i * 2 * c_a:(i + 1) * 2 * c_a] - ref).abs().max() < 0.05            # bf16 weights
+    for i, g in enumerate(gates):
+        assert (t2[:, i * c_a:(i + 1) * c_a] - (s @ g.weight.t() + g.bias)).abs().max() < 0.05
