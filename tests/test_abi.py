@@ -62,3 +62,29 @@ def test_invalid_arguments_are_rejected_without_a_gpu(library):
     assert st == 1  # KFB_ERR_INVALID_ARGUMENT
     library.kfb_last_error.restype = ctypes.c_char_p
     assert b"null" in library.kfb_last_error()
+
+
+def test_ctypes_signatures_match_the_header():
+    """Every prototype bound in kfold_b200/_lib.py has as many parameters as its declaration in the header, pointers where
+    the header has pointers and 64-bit integers where it has `long long` / `size_t` (a mismatch would corrupt the call)."""
+    from kfold_b200 import _lib
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    protos = {m.group(1): m.group(2) for m in re.finditer(r"KFB_API[^;(]*?\b(kfb_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S)}
+    bound = dict(_lib._SIGNATURES)
+    bound.update(_lib._SIZE_FUNCS)
+    assert bound, "no bound prototypes found"
+    for name, args in bound.items():
+        assert name in protos, f"{name} is bound but not declared"
+        params = [p.strip() for p in protos[name].split(",")] if protos[name].strip() not in ("", "void") else []
+        assert len(params) == len(args), f"{name}: header has {len(params)} parameters, the binding {len(args)}"
+        for i, (par, ct) in enumerate(zip(params, args)):
+            if "*" in par:
+                assert ct in (ctypes.c_void_p, ctypes.c_char_p) or issubclass(ct, ctypes._Pointer), f"{name} parameter {i} ({par}) is a pointer"
+            elif "long long" in par:
+                assert ct is ctypes.c_longlong, f"{name} parameter {i} ({par}) is 64-bit"
+            elif "size_t" in par:
+                assert ct is ctypes.c_size_t, f"{name} parameter {i} ({par}) is size_t"
+            elif "float" in par:
+                assert ct is ctypes.c_float, f"{name} parameter {i} ({par}) is float"
+            else:
+                assert ct is ctypes.c_int, f"{name} parameter {i} ({par}) is int"
