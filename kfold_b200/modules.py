@@ -753,6 +753,9 @@ class LocalTransformerStack(nn.Module):
             [LocalTransformerBlock(channel_a, channel_s, channel_z, num_heads) for _ in range(num_blocks)])
         self._bias_w = None
         self._bias_w_key = None
+        self._bias_all = None
+        self._bias_all_key = None
+        self._bias_all_src = None
         self._bank = _ConditioningBank()
 
     def _stacked_bias_weights(self, device, dt):
@@ -762,6 +765,21 @@ class LocalTransformerStack(nn.Module):
             self._bias_w = torch.cat([w.detach() for w in ws], dim=0).to(device, dt).contiguous()
             self._bias_w_key = key
         return self._bias_w
+
+    def _window_biases(self, z: torch.Tensor, dt) -> torch.Tensor:
+        """LayerNorm(z) projected to the heads of every block, head-major.  The window pair tensor does not change between
+        the steps of a sampler run, so the result is kept for as long as z (same storage, same version) and the weights stay."""
+        ln = self.layernorm_z
+        w = self._stacked_bias_weights(z.device, dt)
+        lw = ln.weight
+        key = (z.data_ptr(), tuple(z.shape), z.dtype, z._version, dt, w.data_ptr(),
+               None if lw is None else (lw.data_ptr(), None if torch.is_inference(lw) else lw._version))
+        if self._bias_all_key != key:
+            self._bias_all = F.window_bias(z.to(dt), None if lw is None else lw.detach().float(),
+                                           None if ln.bias is None else ln.bias.detach().float(), w, ln.eps)
+            self._bias_all_key = key
+            self._bias_all_src = z          # keeps z's storage alive so that its address cannot be reused
+        return self._bias_all
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
@@ -777,10 +795,7 @@ class LocalTransformerStack(nn.Module):
         windows = length // WINDOW_Q
         h = self.num_heads
         with torch.autocast(a.device.type, enabled=False):
-            ln = self.layernorm_z
-            bias_all = F.window_bias(z.to(dt), None if ln.weight is None else ln.weight.detach().float(),
-                                     None if ln.bias is None else ln.bias.detach().float(),
-                                     self._stacked_bias_weights(a.device, dt), ln.eps)      # (blocks*H, *z_lead, W, 32, 128)
+            bias_all = self._window_biases(z, dt)                                        # (blocks*H, *z_lead, W, 32, 128)
             z_lead = tuple(z.shape[:-3])                                                 # includes the window dim
             # bf16 compute with head dim <= 32: the kernel walks the windows over the un-gathered atoms
             native = (not precise and c // h <= 32 and c % h == 0
