@@ -505,6 +505,8 @@ KFB_API int kfb_apb_fwd(const void* x, const void* pair_bias, const unsigned cha
     gate_share = 1;
   if (gate_ld <= 0) gate_ld = c;
   KFB_CHECK_ARG(gate_ld >= c, "apb: gate row stride %lld below c=%d", gate_ld, c);
+  KFB_CHECK_ARG(out_gate == nullptr || out_dtype == KFB_FP32_PRECISE || (gate_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(out_gate) & 15) == 0),
+                "apb: bf16 gate rows must start on 16-byte boundaries (pointer and row stride %lld)", gate_ld);
   const int d = c / heads;
   KFB_CHECK_ARG(d % 8 == 0 && d >= 16 && d <= 64, "apb: head dim %d not in {16, 24, ..., 64}", d);
   if (out_dtype == KFB_FP32_PRECISE) {
@@ -683,6 +685,8 @@ KFB_API int kfb_apb_cross_fwd(const void* x_q, const void* x_k, const void* pair
   if (out_gate == nullptr || gate_rows <= 0) gate_rows = rows_q;
   if (gate_ld <= 0) gate_ld = c;
   KFB_CHECK_ARG(gate_ld >= c, "apb_cross: gate row stride %lld below c=%d", gate_ld, c);
+  KFB_CHECK_ARG(out_gate == nullptr || out_dtype == KFB_FP32_PRECISE || (gate_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(out_gate) & 15) == 0),
+                "apb_cross: bf16 gate rows must start on 16-byte boundaries (pointer and row stride %lld)", gate_ld);
   KFB_CHECK_ARG(rows_q % gate_rows == 0 && gate_rows < (1ll << 31), "apb_cross: %lld query rows are not a multiple of gate_rows %lld",
                 rows_q, gate_rows);
   const int gate_reps = static_cast<int>(rows_q / gate_rows);
@@ -865,6 +869,8 @@ KFB_API int kfb_apb_window_fwd(const void* x_q, const void* x_k, const void* pai
   if (out_gate == nullptr || gate_rows <= 0) gate_rows = rows;
   if (gate_ld <= 0) gate_ld = c;
   KFB_CHECK_ARG(gate_ld >= c, "apb_window: gate row stride %lld below c=%d", gate_ld, c);
+  KFB_CHECK_ARG(out_gate == nullptr || (gate_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(out_gate) & 15) == 0),
+                "apb_window: bf16 gate rows must start on 16-byte boundaries (pointer and row stride %lld)", gate_ld);
   KFB_CHECK_ARG(rows % gate_rows == 0 && gate_rows < (1ll << 31), "apb_window: %lld rows are not a multiple of gate_rows %lld", rows,
                 gate_rows);
   const int gate_reps = static_cast<int>(rows / gate_rows);

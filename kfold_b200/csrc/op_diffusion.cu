@@ -92,6 +92,8 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
   KFB_CHECK_ARG(x_normed && w_swiglu_packed && w_out && out_gate && out && workspace, "cond_transition: null pointer");
   if (gate_ld <= 0) gate_ld = c;
   KFB_CHECK_ARG(gate_ld >= c, "cond_transition: gate row stride %lld below c=%d", gate_ld, c);
+  KFB_CHECK_ARG(dtype == KFB_FP32_PRECISE || (gate_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(out_gate) & 15) == 0),
+                "cond_transition: bf16 gate rows must start on 16-byte boundaries (pointer and row stride %lld)", gate_ld);
   KFB_CHECK_ARG(is_dtype(dtype), "cond_transition: bad dtype %d", dtype);
   KFB_CHECK_ARG(rows >= 1 && rows < (1ll << 31) && samples >= 1 && l >= 1 && rows % (static_cast<long long>(samples) * l) == 0,
                 "cond_transition: rows %lld samples %d l %d", rows, samples, l);
