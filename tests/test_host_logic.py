@@ -204,3 +204,43 @@ def test_conditioning_tables_fold_the_layernorm_scale():
         assert (t1[:, i * 2 * c_a:(i + 1) * 2 * c_a] - ref).abs().max() < 0.05            # bf16 weights
     for i, g in enumerate(gates):
         assert (t2[:, i * c_a:(i + 1) * c_a] - (s @ g.weight.t() + g.bias)).abs().max() < 0.05
+
+
+def test_index_sharing_patterns():
+    """Which batch entries share an index / mask row: trailing size-1 leading dims are shared, anything else is not."""
+    from kfold_b200.functional import _index_sharing, _shared_mask
+    assert _index_sharing((1, 5), (1, 1)) == 5
+    assert _index_sharing((2, 5), (2, 1)) == 5
+    assert _index_sharing((2, 5), (2, 5)) == 1
+    assert _index_sharing((1, 5), (1,)) == 5              # fewer leading dims: padded with 1 on the left
+    assert _index_sharing((2, 5), (2,)) is None           # (1, 2) against (2, 5): not a trailing-share pattern
+    assert _index_sharing((2, 5), (1, 5)) is None
+    assert _index_sharing((), ()) == 1
+    m = torch.tensor([[[True, False, True, True]]])       # (1, 1, 4) shared by 3 samples
+    mk = _shared_mask(m, (1, 3), 4, 3)
+    assert mk.dtype == torch.uint8 and mk.shape == (1, 4) and mk.tolist() == [[1, 0, 1, 1]]
+    full = _shared_mask(m.expand(1, 3, 4), (1, 3), 4, 1)
+    assert full.shape == (3, 4)
+    with pytest.raises(ValueError):
+        _shared_mask(m.expand(1, 3, 4), (1, 3), 4, 3)     # per-sample mask with shared features
+
+
+def test_modules_refuse_what_they_do_not_cover():
+    from kfold_b200 import modules as M
+    with pytest.raises(NotImplementedError):
+        M.DiffusionStack(separate_endpoint_atom_encoder=True, token_transformer_blocks=1)
+    with pytest.raises(ValueError):
+        M.CrossAttentionPairBias(128, 4, 128, inf=1e6)
+    with pytest.raises(ValueError):
+        M.build_atom_to_qk_fn(100, "cpu")
+    ds = M.DiffusionStack(channel_a=64, channel_s=32, channel_z=32, channel_atom=32, channel_atompair=16, atom_encoder_blocks=1,
+                          atom_encoder_heads=2, token_transformer_blocks=1, token_transformer_heads=2, atom_decoder_blocks=1,
+                          atom_decoder_heads=2)
+    keys = set(ds.state_dict())
+    for k in ("layernorm_s.weight", "linear_s_to_a.weight", "layernorm_z.weight", "linear_z_to_bias.weight", "layernorm_a.weight",
+              "atom_attention_encoder.linear_r_to_q.weight", "atom_attention_encoder.transformer.blocks.0.attention.adaln_a_q.linear_g.bias",
+              "token_transformer.blocks.0.attention.linear_ada_out.bias", "atom_attention_decoder.linear_q_to_r.weight",
+              "single_conditioning.transitions.1.linear_out.weight"):
+        assert k in keys, k
+    with torch.no_grad(), pytest.raises(RuntimeError, match="CUDA"):
+        ds.get_pair_bias(torch.zeros(1, 8, 8, 32))
