@@ -5,7 +5,7 @@
 One step = one forward of the AF3-shaped Pairformer block (triangle multiplication out/in,
 triangle attention start/end, pair transition, single-track pair-bias attention, single
 transition) on synthetic z ~ N(0,1) (1,768,768,128), s ~ N(0,1) (1,768,384), 10 % padding tail,
-random-init weights -- the unit BASELINE's headline "Pairformer-block fwd ms @N=768 bf16" names.
+random-init weights -- the unit the headline metric "Pairformer-block fwd ms @N=768 bf16" names.
 
 With N > 1 ranks (launched by torch.distributed.run) every rank runs its own block on its own
 GPU -- independent complexes, the way the reference distributes work across GPUs
@@ -211,7 +211,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-# optional second workload (--diffusion-step): one pass of the sampler's token transformer of BASELINE config 4
+# optional second workload (--diffusion-step): one pass of the sampler's token transformer of benchmark config 4
 # (24 conditioned blocks, c=768, 16 heads x 48, L=768 tokens, 5 samples sharing the pair bias), bf16 compute.
 # Not the headline metric; printed as its own JSON line when asked for.
 # ------------------------------------------------------------------------------------------------
@@ -282,7 +282,7 @@ def run_diffusion_step(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-# optional third workload (--atom-step): one pass of an atom-level local transformer of BASELINE config 4
+# optional third workload (--atom-step): one pass of an atom-level local transformer of benchmark config 4
 # (3 blocks, 6 016 atoms = 188 windows of 32 queries x 128 keys, c=128, 4 heads x 32, pair channels 16, 5 samples
 # sharing the window pair tensor and the conditioning), bf16 compute.  Its own JSON line.
 # ------------------------------------------------------------------------------------------------
@@ -347,7 +347,7 @@ def run_atom_step(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-# optional fourth workload (--sampler-step): one call of DiffusionStack.step at BASELINE config 4's shape (atom attention
+# optional fourth workload (--sampler-step): one call of DiffusionStack.step at benchmark config 4's shape (atom attention
 # encoder, 24-block token transformer, atom attention decoder; 768 tokens, 6 016 atoms, 5 samples), bf16 compute.
 # ------------------------------------------------------------------------------------------------
 def run_sampler_step(args) -> None:
@@ -446,7 +446,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     blk.load_state_dict(w, strict=True)
     sharded_mode = args.sharded and world > 1
     if sharded_mode:
-        # strong scaling: all ranks share ONE pair tensor, row-sharded (BASELINE config 5's layout)
+        # strong scaling: all ranks share ONE pair tensor, row-sharded (benchmark config 5's layout)
         from kfold_b200 import sharded as SH
         r0, r1 = SH.shard_rows(N_TOKENS, world, rank)
         z, pm = z[:, r0:r1].contiguous(), pm[:, r0:r1].contiguous()
@@ -597,11 +597,11 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=N_TOKENS,
                     help="profiling aid: run the block at another N (the reported line is then NOT the benchmark workload)")
     ap.add_argument("--sampler-step", action="store_true",
-                    help="fourth workload: one DiffusionStack.step at BASELINE config 4's shape (its own JSON line)")
+                    help="fourth workload: one DiffusionStack.step at benchmark config 4's shape (its own JSON line)")
     ap.add_argument("--atom-step", action="store_true",
-                    help="third workload: one pass of an atom-level local transformer of BASELINE config 4 (its own JSON line)")
+                    help="third workload: one pass of an atom-level local transformer of benchmark config 4 (its own JSON line)")
     ap.add_argument("--diffusion-step", action="store_true",
-                    help="second workload: one pass of the sampler's token transformer of BASELINE config 4 (its own JSON line)")
+                    help="second workload: one pass of the sampler's token transformer of benchmark config 4 (its own JSON line)")
     args = ap.parse_args()
     if args.diffusion_step:
         run_diffusion_step(args)

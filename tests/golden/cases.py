@@ -57,7 +57,7 @@ CASES = {
                            atom_blocks=2, atom_heads=4, token_blocks=2, token_heads=8, samples=2, valid_atoms=90, valid_tokens=23),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
-    # composite block: BASELINE config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
+    # composite block: benchmark config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
     "block_cfg1_n64": dict(kind="block", seed=0, n=64, c_z=128, c_s=384, valid=64),
     "block_n32": dict(kind="block", seed=5, n=32, c_z=128, c_s=384, valid=28),
 }

@@ -177,7 +177,7 @@ def test_fp32_accurate_block_against_reference_golden(dev):
         assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"{name} z: {mx:.3e} {r:.3e}"
 
 
-# ----------------------------------------------------------------------------- oracle at BASELINE sizes (oracle run on the GPU in fp32)
+# ----------------------------------------------------------------------------- oracle at the benchmark sizes (oracle run on the GPU in fp32)
 def _oracle_on(dev, fn, *args, **kw):
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -192,7 +192,7 @@ def _oracle_on(dev, fn, *args, **kw):
 @pytest.mark.parametrize("n", [256, 512, 768])
 @pytest.mark.parametrize("direction", ["outgoing", "incoming"])
 def test_trimul_config2_sizes(dev, n, direction):
-    """BASELINE config 2: N in {256, 512, 768}, C=128, last 10% of tokens padded, seed 1."""
+    """benchmark config 2: N in {256, 512, 768}, C=128, last 10% of tokens padded, seed 1."""
     from kfold_b200 import functional as F
     from kfold_b200 import packing, synth
     z, pm, _ = synth.pair_inputs(1, n, 128, 1, pad_frac=0.1)
@@ -206,7 +206,7 @@ def test_trimul_config2_sizes(dev, n, direction):
 
 @pytest.mark.parametrize("starting", [True, False])
 def test_triatt_config3_size(dev, starting):
-    """BASELINE config 3: N=384, 4 heads x 32, first 352 tokens valid, seed 2."""
+    """benchmark config 3: N=384, 4 heads x 32, first 352 tokens valid, seed 2."""
     from kfold_b200 import functional as F
     from kfold_b200 import packing, synth
     z, pm, _ = synth.pair_inputs(2, 384, 128, 1, valid=352)
@@ -393,7 +393,7 @@ def test_graphed_call_replays_the_token_transformer(dev):
 
 
 def test_diffusion_stack_config4_shape(dev):
-    """BASELINE config 4's token transformer shape: c=768, 16 heads x 48, L=768, 5 samples sharing the pair bias
+    """benchmark config 4's token transformer shape: c=768, 16 heads x 48, L=768, 5 samples sharing the pair bias
     (2 of the 24 blocks), against the oracle run on the GPU in fp32."""
     from kfold_b200 import modules as M
     from kfold_b200 import synth
@@ -538,7 +538,7 @@ def test_local_transformer_block_windowed_signature(dev):
 
 
 def test_local_transformer_config4_shape(dev):
-    """BASELINE config 4's atom transformer shape: 6 016 atoms = 188 windows, c=128, 4 heads x 32, c_z=16, 5 samples
+    """benchmark config 4's atom transformer shape: 6 016 atoms = 188 windows, c=128, 4 heads x 32, c_z=16, 5 samples
     sharing z and s, 3 blocks, against the oracle run on the GPU in fp32."""
     from kfold_b200 import modules as M
     from kfold_b200 import synth
