@@ -136,6 +136,31 @@ def stream_ptr():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class on_device:
+    """``with on_device(t.device):`` -- makes the tensor's GPU current for the calls inside, like ``torch.cuda.device``,
+    but does nothing at all when that GPU already is current (the usual case: one process per GPU), which keeps the
+    per-call host cost of the wrappers down."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index
+        self.prev = -1
+
+    def __enter__(self):
+        if self.idx is not None:
+            cur = torch.cuda.current_device()
+            if cur != self.idx:
+                self.prev = cur
+                torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def dtype_code(dt: torch.dtype) -> int:
     if dt == torch.bfloat16:
         return KFB_BF16

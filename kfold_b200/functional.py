@@ -78,7 +78,7 @@ def layer_norm(x: torch.Tensor, weight, bias, eps: float = 1e-5, out_dtype=None)
     out = torch.empty(x2.shape, dtype=out_dtype or x.dtype, device=x.device)
     w = None if weight is None else weight.detach().float().contiguous()
     b = None if bias is None else bias.detach().float().contiguous()
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         L.check(L.lib().kfb_layernorm(L.ptr(x2), L.ptr(out), L.ptr(w), L.ptr(b), x2.shape[0], c, x2.stride(0), c, eps,
                                       L.dtype_code(x2.dtype), L.dtype_code(out.dtype), L.stream_ptr()))
     return out.view(*x.shape[:-1], c)
@@ -107,7 +107,7 @@ def triangle_multiplication(x: torch.Tensor, mask: torch.Tensor, packed: dict, d
     precise = bool(packed.get("precise"))
     if precise and xp.dtype != torch.float32:
         raise ValueError("the fp32-accurate mode takes float32 tensors")
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         need = (lib.kfb_trimul_workspace_bytes_precise if precise else lib.kfb_trimul_workspace_bytes)(b, npad, c)
         ws = _workspace(x.device, need)
         L.check(lib.kfb_trimul_fwd(1 if direction == "incoming" else 0, L.ptr(xp), L.ptr(mp8), L.ptr(packed["ln_in_w"]),
@@ -139,7 +139,7 @@ def triangle_attention(x: torch.Tensor, mask: torch.Tensor | None, packed: dict,
     precise = bool(packed.get("precise"))
     if precise and xp.dtype != torch.float32:
         raise ValueError("the fp32-accurate mode takes float32 tensors")
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         need = (lib.kfb_triatt_workspace_bytes_precise if precise else lib.kfb_triatt_workspace_bytes)(b, npad, c, heads)
         ws = _workspace(x.device, need)
         L.check(lib.kfb_triatt_fwd(0 if starting else 1, L.ptr(xp), L.ptr(mp.view(torch.uint8)), L.ptr(packed["ln_w"]),
@@ -159,7 +159,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, o
     x2 = x2.contiguous()
     n = w.shape[0]
     out = torch.empty(x2.shape[0], n, dtype=out_dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         L.check(L.lib().kfb_gemm_bf16(L.ptr(x2), L.ptr(w), L.ptr(out), L.ptr(bias), 1, x2.shape[0], n, k, k, k, n, 0, 0, 0,
                                       L.dtype_code(out_dtype), L.stream_ptr()))
     return out.view(*x.shape[:-1], n)
@@ -176,7 +176,7 @@ def linear_fp32(x: torch.Tensor, w6: torch.Tensor, bias: torch.Tensor | None = N
     n = w6.shape[0]
     out = torch.empty(x2.shape[0], n, dtype=torch.float32, device=x.device)
     lib = L.lib()
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         ws = _workspace(x.device, lib.kfb_linear_fp32_workspace_bytes(x2.shape[0], k))
         L.check(lib.kfb_linear_fp32(L.ptr(x2), L.ptr(w6), L.ptr(bias), L.ptr(out), L.ptr(ws), ws.numel(), x2.shape[0], n, k,
                                     L.stream_ptr()))
@@ -198,7 +198,7 @@ def ln_linear_fp32(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tenso
     f32 = lambda t: None if t is None else t.detach().float().contiguous()
     lw, lb = f32(ln_w), f32(ln_b)
     lib = L.lib()
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         ws = _workspace(x.device, lib.kfb_linear_fp32_workspace_bytes(x2.shape[0], k))
         L.check(lib.kfb_ln_linear_fp32(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(w6), L.ptr(bias), L.ptr(res), L.ptr(out), L.ptr(ws),
                                        ws.numel(), x2.shape[0], n, k, eps, 1, L.stream_ptr()))
@@ -216,7 +216,7 @@ def adaln(a: torch.Tensor, gate_shift: torch.Tensor, samples: int, eps: float = 
         a2 = a2.float()
     out = torch.empty(a2.shape, dtype=torch.float32 if precise else torch.bfloat16, device=a.device)
     gs, _, gs_ld = _rows(gate_shift, 2 * c)
-    with torch.cuda.device(a.device):
+    with L.on_device(a.device):
         L.check(L.lib().kfb_adaln_fwd(L.ptr(a2), L.ptr(gs), gs_ld, L.ptr(out), a2.shape[0], c, samples, l, eps,
                                       L.KFB_FP32_PRECISE if precise else L.dtype_code(a2.dtype), L.stream_ptr()))
     return out.view(a.shape)
@@ -239,7 +239,7 @@ def conditioned_transition(x_normed: torch.Tensor, packed: dict, out_gate: torch
         x2 = x2.float()
         r2 = None if r2 is None else r2.float()
     lib = L.lib()
-    with torch.cuda.device(x2.device):
+    with L.on_device(x2.device):
         need = (lib.kfb_cond_transition_workspace_bytes_precise(rows, c, hidden) if precise
                 else lib.kfb_cond_transition_workspace_bytes(rows, hidden))
         ws = _workspace(x2.device, need)
@@ -310,7 +310,7 @@ def attention_pair_bias(x: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Te
     want = out_dtype or (resid.dtype if resid is not None else x.dtype)
     out = torch.empty(batch, lp, c, dtype=torch.float32 if precise else want, device=x.device)
     lib = L.lib()
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         need = lib.kfb_apb_workspace_bytes_precise(batch, lp, c) if precise else lib.kfb_apb_workspace_bytes(batch, lp, c, heads)
         ws = _workspace(x.device, need)
         L.check(lib.kfb_apb_fwd(L.ptr(xb), L.ptr(pbb), L.ptr(mb.view(torch.uint8)), L.ptr(packed["w_proj"]),
@@ -333,7 +333,7 @@ def window_bias(z: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor |
     z2 = z.reshape(-1, c).contiguous()
     nh = w.shape[0]
     out = torch.empty((nh,) + tuple(z.shape[:-1]), dtype=z.dtype, device=z.device)
-    with torch.cuda.device(z.device):
+    with L.on_device(z.device):
         L.check(L.lib().kfb_window_bias_fwd(L.ptr(z2), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w.contiguous()), L.ptr(out), z2.shape[0], c,
                                             nh, eps, 1 if normalise else 0, L.dtype_code(z.dtype), L.stream_ptr()))
     return out
@@ -382,7 +382,7 @@ def attention_pair_bias_cross(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: t
     if res is not None and res.dtype != out.dtype:
         res = res.to(out.dtype)
     lib = L.lib()
-    with torch.cuda.device(x_q.device):
+    with L.on_device(x_q.device):
         need = (lib.kfb_apb_cross_workspace_bytes_precise(batch, lq, lk, c) if precise
                 else lib.kfb_apb_cross_workspace_bytes(batch, lq, lk, c, heads))
         ws = _workspace(x_q.device, need)
@@ -426,7 +426,7 @@ def attention_pair_bias_window(x_q: torch.Tensor, x_k: torch.Tensor, pair_bias: 
     out = torch.empty(batch, l, c, dtype=want, device=x_q.device)
     res = None if resid is None else resid.reshape(batch, l, c).to(want).contiguous()
     lib = L.lib()
-    with torch.cuda.device(x_q.device):
+    with L.on_device(x_q.device):
         ws = _workspace(x_q.device, lib.kfb_apb_window_workspace_bytes(batch, l, c, heads))
         L.check(lib.kfb_apb_window_fwd(L.ptr(xq), L.ptr(xk), L.ptr(pb), L.ptr(mb), L.ptr(packed["w_q"]), L.ptr(packed["q_bias"]),
                                        L.ptr(packed["w_kv"]), L.ptr(packed["w_out"]), L.ptr(packed["out_bias"]), L.ptr(gate),
@@ -504,7 +504,7 @@ def transition(x: torch.Tensor, packed: dict, eps: float = 1e-5, residual: bool 
     precise = bool(packed.get("precise"))
     if precise and x2.dtype != torch.float32:
         raise ValueError("the fp32-accurate mode takes float32 tensors")
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         need = (lib.kfb_transition_workspace_bytes_precise if precise else lib.kfb_transition_workspace_bytes)(rows, c, hidden)
         ws = _workspace(x.device, need)
         L.check(lib.kfb_transition_fwd(L.ptr(x2), L.ptr(packed["ln_w"]), L.ptr(packed["ln_b"]), L.ptr(packed["w_swiglu"]),
@@ -531,7 +531,7 @@ def pair_bias(z: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor, w: torch.
     out = torch.empty(b, heads, n, n, dtype=torch.float32 if precise else torch.bfloat16, device=z.device)
     zc = z.contiguous()
     lib = L.lib()
-    with torch.cuda.device(z.device):
+    with L.on_device(z.device):
         need = (lib.kfb_pair_bias_workspace_bytes_precise if precise else lib.kfb_pair_bias_workspace_bytes)(b, n, c)
         ws = _workspace(z.device, need)
         L.check(lib.kfb_pair_bias_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), b, n,
@@ -548,7 +548,7 @@ def pair_bias_rows(z_rows: torch.Tensor, ln_w: torch.Tensor, ln_b: torch.Tensor,
     out = torch.empty(heads, rows, n, dtype=torch.bfloat16, device=z_rows.device)
     zc = z_rows.contiguous()
     lib = L.lib()
-    with torch.cuda.device(zc.device):
+    with L.on_device(zc.device):
         ws = _workspace(zc.device, rows * n * c * 2 + 256)
         L.check(lib.kfb_pair_bias_rows_fwd(L.ptr(zc), L.ptr(ln_w), L.ptr(ln_b), L.ptr(w), L.ptr(out), L.ptr(ws), ws.numel(), rows,
                                            n, c, heads, eps, L.dtype_code(zc.dtype), L.stream_ptr()))
@@ -592,7 +592,7 @@ def broadcast_tokens_to_atoms(x: torch.Tensor, token_index: torch.Tensor, add: t
         raise TypeError("broadcast_tokens_to_atoms: bfloat16 or float32 addend")
     add2 = None if add is None else add.expand(*lead, n_atom, d).reshape(-1, n_atom, d).to(out_dtype).contiguous()
     out = torch.empty(x2.shape[0], n_atom, d, dtype=out_dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         L.check(L.lib().kfb_tokens_to_atoms(L.ptr(x2), L.ptr(idx), L.ptr(add2), L.ptr(out), x2.shape[0], n_token, n_atom, d, div,
                                             L.dtype_code(x.dtype), L.dtype_code(out_dtype), L.stream_ptr()))
     return out.view(*lead, n_atom, d)
@@ -616,7 +616,7 @@ def aggregate_atoms_to_tokens(x: torch.Tensor, token_index: torch.Tensor, mask: 
     x2 = x.reshape(-1, n_atom, d).contiguous()
     out = torch.empty(x2.shape[0], num_tokens, d, dtype=x.dtype, device=x.device)
     lib = L.lib()
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         ws = _workspace(x.device, lib.kfb_atoms_to_tokens_workspace_bytes(x2.shape[0], num_tokens, div))
         L.check(lib.kfb_atoms_to_tokens(L.ptr(x2), L.ptr(idx), L.ptr(mk), L.ptr(out), L.ptr(ws), ws.numel(), x2.shape[0], n_atom,
                                         num_tokens, d, div,
@@ -654,7 +654,7 @@ def coord_embed(q: torch.Tensor, r: torch.Tensor, w: torch.Tensor, mask: torch.T
     r2 = r.reshape(-1, kc).float().contiguous()
     out = torch.empty(r2.shape[0], c, dtype=torch.float32, device=r.device)
     mk = _shared_mask(mask, lead, l, share)
-    with torch.cuda.device(r.device):
+    with L.on_device(r.device):
         L.check(L.lib().kfb_coord_embed(L.ptr(q2), L.ptr(r2), L.ptr(w.detach().float().contiguous()), L.ptr(mk), L.ptr(out), r2.shape[0], c, kc,
                                         share, l, L.dtype_code(q2.dtype), L.stream_ptr()))
     return out.view(*lead, l, c)
@@ -678,7 +678,7 @@ def ln_project(x: torch.Tensor, ln_w: torch.Tensor | None, ln_b: torch.Tensor | 
         lead, l = tuple(x.shape[:-2]), x.shape[-2]
         share = _index_sharing(lead, tuple(mask.shape[:-1])) or 1
         mk = _shared_mask(mask, lead, l, share)
-    with torch.cuda.device(x.device):
+    with L.on_device(x.device):
         L.check(L.lib().kfb_ln_project(L.ptr(x2), L.ptr(lw), L.ptr(lb), L.ptr(ww), L.ptr(mk), L.ptr(out), x2.shape[0], c, n_out, eps,
                                        share, l, L.dtype_code(x2.dtype), L.stream_ptr()))
     return out.view(*x.shape[:-1], n_out)
@@ -690,7 +690,7 @@ def fourier_embed(t: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Te
     t2 = t.reshape(-1).float().contiguous()
     w2, b2 = w.reshape(-1).float().contiguous(), b.reshape(-1).float().contiguous()
     out = torch.empty(t2.shape[0], w2.shape[0], dtype=torch.float32, device=t.device)
-    with torch.cuda.device(t.device):
+    with L.on_device(t.device):
         L.check(L.lib().kfb_fourier_embed(L.ptr(t2), L.ptr(w2), L.ptr(b2), L.ptr(out), t2.shape[0], w2.shape[0], L.stream_ptr()))
     return out.view(*t.shape, w2.shape[0])
 
@@ -702,6 +702,6 @@ def broadcast_add(s: torch.Tensor, f: torch.Tensor) -> torch.Tensor:
     n = f.shape[1]
     s2, f2 = s.float().contiguous(), f.float().contiguous()
     out = torch.empty(b, n, l, c, dtype=torch.float32, device=s.device)
-    with torch.cuda.device(s.device):
+    with L.on_device(s.device):
         L.check(L.lib().kfb_broadcast_add(L.ptr(s2), L.ptr(f2), L.ptr(out), b, n, l, c, L.stream_ptr()))
     return out

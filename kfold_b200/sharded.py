@@ -119,7 +119,7 @@ class ShardedPairOps:
         m8 = mask_ab.to(torch.bool).contiguous().view(torch.uint8)
         x_ab = x_ab.contiguous()
         x_row = x_row.contiguous()
-        with torch.cuda.device(dev):
+        with L.on_device(dev):
             st = L.stream_ptr()
             same = x_ab.data_ptr() == x_row.data_ptr()
             L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
@@ -155,7 +155,7 @@ class ShardedPairOps:
         m8 = mask_ab.to(torch.bool).contiguous().view(torch.uint8)
         x_ab = x_ab.contiguous()
         x_row = x_row.contiguous()
-        with torch.cuda.device(dev):
+        with L.on_device(dev):
             st = L.stream_ptr()
             same = x_ab.data_ptr() == x_row.data_ptr()
             L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
@@ -196,7 +196,7 @@ class ShardedPairOps:
         vt = _bf16((rows, hdp, n), dev)
         bias_loc = _bf16((heads, rows, n), dev)
         m8 = mask_loc.to(torch.bool).contiguous().view(torch.uint8)
-        with torch.cuda.device(dev):
+        with L.on_device(dev):
             L.check(lib.kfb_triatt_project(L.ptr(x_loc), L.ptr(pk["ln_w"]), L.ptr(pk["ln_b"]), L.ptr(pk["w_proj"]), L.ptr(xn),
                                            L.ptr(qkg), L.ptr(vt), L.ptr(bias_loc), rows, n, c, heads, eps, dt, L.stream_ptr()))
             bias_full = gather_head_rows(bias_loc, self.group)
