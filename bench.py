@@ -28,8 +28,9 @@ import time
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-if ROOT not in sys.path:
-    sys.path.insert(0, ROOT)
+for _p in (ROOT, os.path.join(ROOT, "tests")):   # tests/ holds the seeded synthetic inputs (synth.py)
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
 
 N_TOKENS = 768
 C_Z, C_S = 128, 384
@@ -133,7 +134,7 @@ class ClockSampler:
 
 
 def make_inputs():
-    from kfold_b200 import synth
+    import synth
     z, pm, m = synth.pair_inputs(SEED, N_TOKENS, C_Z, 1, pad_frac=PAD_FRAC)
     s = synth.single_inputs(SEED, N_TOKENS, C_S, 1)
     w = synth.pairformer_block_weights(SEED, C_Z, C_S)
@@ -158,7 +159,7 @@ def config_dict(n_gpus: int, sharded_mode: bool = False) -> dict:
 # ------------------------------------------------------------------------------------------------
 def cpu_block_time(n: int, repeats: int, warmup: int):
     """Times the CPU oracle's composite block at `n` tokens in fp32; returns (best_ms, cores)."""
-    from kfold_b200 import synth
+    import synth
     from oracle import pairformer_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -218,7 +219,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
 def run_diffusion_step(args) -> None:
     from kfold_b200 import _lib as L
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     blocks, l, ns, c, cs, heads = 24, N_TOKENS, 5, 768, 384, 16
@@ -289,7 +290,7 @@ def run_diffusion_step(args) -> None:
 def run_atom_step(args) -> None:
     from kfold_b200 import _lib as L
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     blocks, l, ns, c, c_z, heads = 3, 6016, 5, 128, 16, 4
@@ -353,7 +354,7 @@ def run_atom_step(args) -> None:
 def run_sampler_step(args) -> None:
     from kfold_b200 import _lib as L
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     nt, na, ns = N_TOKENS, 6016, 5

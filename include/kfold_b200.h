@@ -59,9 +59,15 @@ KFB_API int kfb_version(void);
 /* Text of the last error raised on the calling host thread ("" if none). */
 KFB_API const char* kfb_last_error(void);
 
-/* Synchronises the current device and returns the device-side status word:
- * 0, or the code of the first bounded wait that gave up inside a kernel
- * (then also resets it).  For tests and post-mortems; not on the hot path. */
+/* Synchronises the current device and returns the device-side status:
+ * 0, or the code of the first bounded wait that gave up inside a kernel, or
+ * 900 when a kernel met a token index out of range (both are then reset).
+ * Kernels never stop the process on such an error: a wait that gave up leaves
+ * the tiles it was waiting for unwritten, and every later kernel on that device
+ * abandons its waits early until the status is read.  Callers poll this at a
+ * point where a device synchronisation is acceptable -- once per complex, or
+ * once per sampler run -- and discard the results of that span when it is
+ * non-zero.  A data error (900) does not affect other kernels. */
 KFB_API int kfb_device_status(int* code_out);
 
 /* Number of kernels this library has launched in the calling process so far. */
@@ -72,12 +78,6 @@ KFB_API long long kfb_launch_count(void);
  * launch tag: "<tag> <launches> <total_ms>\n".  Creates events while enabled; off by default. */
 KFB_API int kfb_profile_enable(int on);
 KFB_API int kfb_profile_report(char* buf, size_t cap);
-
-/* Debugging aid (off by default): a device buffer of at least 512 int64 that receives clock stamps of the
- * attention kernel's pipeline events for its first CTA; pass NULL to switch it off again. */
-KFB_API int kfb_debug_attention_trace(void* device_buffer_512_i64);
-/* Same for the GEMM launches whose profile tag equals `tag` (per-tile stamps of the first CTA). */
-KFB_API int kfb_debug_gemm_trace(void* device_buffer_512_i64, const char* tag);
 
 /*
  * Triangle multiplicative update, outgoing (incoming = 0) or incoming (incoming = 1).
@@ -367,8 +367,9 @@ KFB_API int kfb_transition_fwd(const void* x, const float* ln_w, const float* ln
  * start-up, or a plugin callback that must not call cudaMalloc because it synchronises the device.
  * The function itself allocates nothing on the device or through any library.
  *   - Sizes whose temporaries exceed the array (rows * (c + hidden) * 2 bytes, each part rounded up
- *     to 256) are refused with KFB_ERR_UNSUPPORTED and a message naming the limit; e.g. c=384,
- *     hidden=1536 fits up to 2184 rows.
+ *     to 256; six times that with dtype = KFB_FP32_PRECISE) are refused with KFB_ERR_UNSUPPORTED and
+ *     a message naming the limit; e.g. c=384, hidden=1536 fits up to 2184 rows (364 in the
+ *     fp32-accurate mode).
  *   - The first call on each device looks up the array's device address (with that device
  *     current); make that first call outside any stream capture.
  *   - All calls on a device share the one array: calls that may overlap on the GPU (different

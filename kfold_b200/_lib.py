@@ -28,8 +28,6 @@ _SIGNATURES = {
     "kfb_version": [],
     "kfb_device_status": [ctypes.POINTER(c_int)],
     "kfb_profile_enable": [c_int],
-    "kfb_debug_attention_trace": [c_void_p],
-    "kfb_debug_gemm_trace": [c_void_p, ctypes.c_char_p],
     "kfb_profile_report": [ctypes.c_char_p, ctypes.c_size_t],
     "kfb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_float, c_int, c_int, c_void_p],
     "kfb_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll,

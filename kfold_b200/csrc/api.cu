@@ -12,12 +12,13 @@ KFB_API const char* kfb_last_error(void) { return get_error(); }
 
 KFB_API int kfb_device_status(int* code_out) {
   KFB_CUDA(cudaDeviceSynchronize());
-  int code = 0;
+  int code = 0, data_code = 0;
+  const int zero = 0;
   KFB_CUDA(cudaMemcpyFromSymbol(&code, g_status, sizeof(int)));
-  if (code != 0) {
-    const int zero = 0;
-    KFB_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
-  }
+  KFB_CUDA(cudaMemcpyFromSymbol(&data_code, g_data_status, sizeof(int)));
+  if (code != 0) KFB_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+  if (data_code != 0) KFB_CUDA(cudaMemcpyToSymbol(g_data_status, &zero, sizeof(int)));
+  if (code == 0) code = data_code;  // a wait that gave up outranks a data error
   if (code_out) *code_out = code;
   if (code != 0) {
     set_error("device-side error status %d (900: a token index out of range; otherwise a bounded wait that gave up)", code);
@@ -26,8 +27,11 @@ KFB_API int kfb_device_status(int* code_out) {
   return KFB_OK;
 }
 
-KFB_API KFB_API long long kfb_launch_count(void) { return launch_count(); }
+KFB_API long long kfb_launch_count(void) { return launch_count(); }
 
+#ifdef KFB_DEBUG_TRACE
+// Development builds only (-DKFB_DEBUG_TRACE): a device buffer of at least 512 int64 receives clock stamps of the
+// pipeline events of the first CTA of the attention kernel / of the GEMM launches whose profile tag equals `tag`.
 KFB_API int kfb_debug_attention_trace(void* device_buffer_512_i64) {
   set_attention_trace(static_cast<long long*>(device_buffer_512_i64));
   return KFB_OK;
@@ -37,6 +41,7 @@ KFB_API int kfb_debug_gemm_trace(void* device_buffer_512_i64, const char* tag) {
   set_gemm_trace(static_cast<long long*>(device_buffer_512_i64), tag);
   return KFB_OK;
 }
+#endif
 
 KFB_API int kfb_profile_enable(int on) {
   profile_enable(on != 0);

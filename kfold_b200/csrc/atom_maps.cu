@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256) tokens_to_atoms_kernel(const TX* __restri
   const int a = static_cast<int>(row - b * n_atom);
   const long long t = index[(b / index_div) * n_atom + a];
   const bool ok = t >= 0 && t < n_token;
-  if (!ok && lane == 0) atomicCAS(&g_status, 0, kBadIndexCode);
+  if (!ok && lane == 0) atomicCAS(&g_data_status, 0, kBadIndexCode);
   const TX* src = x + (b * n_token + (ok ? t : 0)) * d;
   TO* dst = out + row * d;
   if constexpr (sizeof(TX) == sizeof(TO)) {

@@ -105,7 +105,11 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int nkv = WIN ? 2 : (p.lk + kBKV - 1) / kBKV;
   const int nhalf = 2 * nkv;
   long long* trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+#ifdef KFB_DEBUG_TRACE
 #define KFB_STAMP(slot) do { if (trace != nullptr) trace[slot] = clock64(); } while (0)
+#else
+#define KFB_STAMP(slot) do { (void)trace; } while (0)
+#endif
 
   if (threadIdx.x == 0) {
     KFB_STAMP(0);

@@ -13,6 +13,7 @@
 namespace kfb {
 
 __device__ int g_status = 0;
+__device__ int g_data_status = 0;
 
 static thread_local char t_error[512] = "";
 

@@ -248,7 +248,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const int num_k = (p.k_extent + kBK - 1) / kBK;
   const int total_tiles = p.num_m_tiles * p.num_n_tiles;
   long long* trace = (p.trace != nullptr && blockIdx.x == 0) ? p.trace : nullptr;
+#ifdef KFB_DEBUG_TRACE
 #define KFB_GSTAMP(slot) do { if (trace != nullptr && (slot) < 512) trace[slot] = clock64(); } while (0)
+#else
+#define KFB_GSTAMP(slot) do { (void)trace; } while (0)
+#endif
 
   if (threadIdx.x == 0) {
     KFB_GSTAMP(0);

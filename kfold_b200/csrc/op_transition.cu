@@ -170,12 +170,15 @@ KFB_API size_t kfb_transition_static_max_bytes(void) { return kStaticScratchByte
 KFB_API int kfb_transition_fwd_static(const void* x, const float* ln_w, const float* ln_b, const void* w_swiglu_packed,
                                       const void* w_out, void* out, const void* resid, long long rows, int c, int hidden,
                                       float eps, int dtype, void* stream) {
+  KFB_CHECK_ARG(is_dtype(dtype), "transition_static: bad dtype %d", dtype);
   KFB_CHECK_ARG(rows >= 1 && c >= 8 && hidden >= 128, "transition_static: rows %lld c %d hidden %d", rows, c, hidden);
-  const size_t need = kfb_transition_workspace_bytes(rows, c, hidden);
+  // the fp32-accurate mode keeps six bf16 parts of every temporary: six times the bytes
+  const size_t need = dtype == KFB_FP32_PRECISE ? kfb_transition_workspace_bytes_precise(rows, c, hidden)
+                                                : kfb_transition_workspace_bytes(rows, c, hidden);
   if (need > kStaticScratchBytes) {
-    set_error("transition_static: %lld rows x (c=%d + hidden=%d) need %zu bytes of scratch, the built-in array holds %zu; "
+    set_error("transition_static: %lld rows x (c=%d + hidden=%d)%s need %zu bytes of scratch, the built-in array holds %zu; "
               "use kfb_transition_fwd with a caller-provided workspace for this size",
-              rows, c, hidden, need, kStaticScratchBytes);
+              rows, c, hidden, dtype == KFB_FP32_PRECISE ? " in the fp32-accurate mode" : "", need, kStaticScratchBytes);
     return KFB_ERR_UNSUPPORTED;
   }
   void* scratch = nullptr;

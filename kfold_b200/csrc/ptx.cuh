@@ -13,8 +13,12 @@
 
 namespace kfb {
 
-// Device-global status word: 0 = ok, otherwise the code of the first wait that gave up.
+// Device-global status word: 0 = ok, otherwise the code of the first wait that gave up.  Once it is set, every later
+// bounded wait on the device gives up early, so it records pipeline failures only.
 extern __device__ int g_status;
+// Data errors (a token index out of range) are recorded apart, in a word no wait consults: bad input to one kernel
+// must not make the kernels after it abandon their tiles.
+extern __device__ int g_data_status;
 
 namespace ptx {
 

@@ -18,6 +18,12 @@ class GraphedCall:
     ``fn`` must be free of host synchronisation and of data-dependent control flow, and every call must use the shapes,
     dtypes and devices of the example.  Tensors that never change between calls (weights, a cached pair bias, masks) can
     be closed over by ``fn`` instead of being passed as inputs, which saves their copy.
+
+    The stacks keep what they derive from per-complex tensors (the converted token pair bias, the window biases of the atom
+    transformers) in caches that already hold their result when the capture runs, so those kernels are NOT part of the
+    graph: the pair tensor ``z``, the window pair tensor ``p`` and ``pair_bias`` must be closed over by ``fn``, never passed
+    as inputs that later calls replace -- a replay would keep using the bias of the captured tensors.  For a new complex
+    build a new GraphedCall.
     """
 
     def __init__(self, fn, *example_inputs: torch.Tensor, warmup: int = 2):

@@ -104,6 +104,13 @@ def _is_precise(dt: torch.dtype, what: str) -> bool:
     raise NotImplementedError(f"{what}: compute dtype {dt} is not available (bfloat16 and float32 are)")
 
 
+def _tensor_key(t: torch.Tensor) -> tuple:
+    """Identity of an activation tensor for a cache: storage address, shape, dtype and in-place version.  Tensors created
+    under ``torch.inference_mode()`` (how the reference runs, model/model.py:294 and :361) carry no version counter; for
+    them the key has no version, and a caller that overwrites such a tensor in place must call ``reset_caches()``."""
+    return (t.data_ptr(), tuple(t.shape), t.dtype, None if torch.is_inference(t) else t._version)
+
+
 class _PackedMixin:
     """Packs the module's weights once and re-packs when any parameter changes
     (same cache key as model/primitives/triangle_multiplication.py:73-91)."""
@@ -537,16 +544,25 @@ class CachedGlobalTransformerStack(nn.Module):
             [CachedGlobalTransformerBlock(channel_a, channel_s, num_heads) for _ in range(num_blocks)])
         self._bias_cache = None
         self._bias_key = None
+        self._bias_src = None
         self._bank = _ConditioningBank()
 
     def _prepared_bias(self, pair_bias: torch.Tensor, precise: bool = False):
-        key = (pair_bias.data_ptr(), tuple(pair_bias.shape), pair_bias.dtype, pair_bias._version, precise)
+        key = _tensor_key(pair_bias) + (precise,)
         if self._bias_key != key:
             # (*, N, H, L, L) -> N tensors (*, H, L, L), contiguous: bf16 for the tensor-core kernel, float32 for the
             # fp32-accurate one
             pb = pair_bias.movedim(-4, 0).to(torch.float32 if precise else torch.bfloat16).contiguous()
             self._bias_cache, self._bias_key = pb, key
+            # the conversion may have copied: keep the source alive, so that its address cannot be handed to the bias of
+            # the next complex (same shape, version 0) while this entry is still in the cache
+            self._bias_src = pair_bias
         return self._bias_cache
+
+    def reset_caches(self) -> None:
+        """Forget the converted pair bias (call once per complex when the bias tensor is overwritten in place under
+        ``torch.inference_mode()``, where tensors carry no version counter)."""
+        self._bias_cache = self._bias_key = self._bias_src = None
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
@@ -772,14 +788,18 @@ class LocalTransformerStack(nn.Module):
         ln = self.layernorm_z
         w = self._stacked_bias_weights(z.device, dt)
         lw = ln.weight
-        key = (z.data_ptr(), tuple(z.shape), z.dtype, z._version, dt, w.data_ptr(),
-               None if lw is None else (lw.data_ptr(), None if torch.is_inference(lw) else lw._version))
+        key = _tensor_key(z) + (dt, w.data_ptr(),
+                                None if lw is None else (lw.data_ptr(), None if torch.is_inference(lw) else lw._version))
         if self._bias_all_key != key:
             self._bias_all = F.window_bias(z.to(dt), None if lw is None else lw.detach().float(),
                                            None if ln.bias is None else ln.bias.detach().float(), w, ln.eps)
             self._bias_all_key = key
             self._bias_all_src = z          # keeps z's storage alive so that its address cannot be reused
         return self._bias_all
+
+    def reset_caches(self) -> None:
+        """Forget the window biases (see CachedGlobalTransformerStack.reset_caches)."""
+        self._bias_all = self._bias_all_key = self._bias_all_src = None
 
     @torch.compiler.disable
     def forward(self, a: torch.Tensor, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
@@ -972,6 +992,21 @@ class DiffusionStack(nn.Module):
 
     def get_single_conditioning(self, s_inputs: torch.Tensor, c_noise: torch.Tensor) -> torch.Tensor:
         return self.single_conditioning(s_inputs, c_noise)
+
+    def reset_caches(self) -> None:
+        """Forget everything derived from the tensors of one complex (the converted token pair bias, the window biases of
+        both atom transformers).  The caches are keyed on the source tensor's storage, shape and version; call this between
+        complexes when those tensors are overwritten in place under ``torch.inference_mode()``."""
+        self.token_transformer.reset_caches()
+        self.atom_attention_encoder.transformer.reset_caches()
+        self.atom_attention_decoder.transformer.reset_caches()
+
+    @staticmethod
+    def check() -> None:
+        """Synchronise and raise if a kernel recorded an error since the last check (a bounded wait that gave up, or a token
+        index out of range): results computed since then must be discarded.  Cheap enough for once per sampler run."""
+        from . import _lib
+        _lib.device_status()
 
     def get_pair_bias(self, z: torch.Tensor) -> torch.Tensor:
         """(B, Nblock, H, Lt, Lt): bf16 under bfloat16 compute, float32 under float32 compute; time-independent."""

@@ -98,7 +98,8 @@ class ShardedPairOps:
 
     def _transposed_mask(self, mask_loc: torch.Tensor) -> torch.Tensor:
         """Row shard of the transposed pair mask, exchanged once per mask tensor and reused by every later call."""
-        key = (mask_loc.data_ptr(), mask_loc._version, tuple(mask_loc.shape), mask_loc.dtype)
+        key = (mask_loc.data_ptr(), None if torch.is_inference(mask_loc) else mask_loc._version, tuple(mask_loc.shape),
+               mask_loc.dtype)
         if self._mask_t is None or self._mask_t[0] != key:
             # the cache keeps `mask_loc` alive so that its address cannot be reused by another tensor
             self._mask_t = (key, transpose_shard(mask_loc.to(torch.uint8), self.group), mask_loc)

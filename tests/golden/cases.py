@@ -10,7 +10,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from kfold_b200 import synth
+import synth
 
 # pair outputs with N >= 48 are stored as out[:, ::SUB_STRIDE, ::SUB_STRIDE] plus checksums
 SUB_STRIDE = 3
@@ -24,6 +24,11 @@ CASES = {
     "trimul_in_b2": dict(kind="trimul", direction="incoming", seed=14, n=16, c=128, batch=2, blockmask=True),
     "trimul_out_n64": dict(kind="trimul", direction="outgoing", seed=15, n=64, c=128, batch=1, valid=58),
     "trimul_in_n64": dict(kind="trimul", direction="incoming", seed=16, n=64, c=128, batch=1, valid=58),
+    # production trunk width (configs/kfold.yaml:2-3, channel_z 256) and the apo stack's width (configs/kfold.yaml:15-20)
+    "trimul_out_c256": dict(kind="trimul", direction="outgoing", seed=17, n=24, c=256, batch=1, valid=21),
+    "trimul_in_c256": dict(kind="trimul", direction="incoming", seed=18, n=24, c=256, batch=1, valid=21),
+    "trimul_out_c64": dict(kind="trimul", direction="outgoing", seed=19, n=32, c=64, batch=2, blockmask=True),
+    "trimul_in_c64": dict(kind="trimul", direction="incoming", seed=20, n=32, c=64, batch=2, blockmask=True),
     # triangle attention
     "triatt_start_n24": dict(kind="triatt", starting=True, seed=21, n=24, c=128, heads=4, batch=1, valid=20),
     "triatt_end_n24": dict(kind="triatt", starting=False, seed=22, n=24, c=128, heads=4, batch=1, valid=20),
@@ -60,6 +65,9 @@ CASES = {
     # composite block: benchmark config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
     "block_cfg1_n64": dict(kind="block", seed=0, n=64, c_z=128, c_s=384, valid=64),
     "block_n32": dict(kind="block", seed=5, n=32, c_z=128, c_s=384, valid=28),
+    # K-Fold's own trunk block (tri-mult out + in + transition x4), at the production width and at the benchmark's
+    "tri_block_c256": dict(kind="tri_block", seed=6, n=24, c_z=256, valid=21),
+    "tri_block_c128": dict(kind="tri_block", seed=7, n=40, c_z=128, valid=36),
 }
 
 
@@ -156,6 +164,10 @@ def build_inputs(name: str) -> dict:
         out["z"], out["pair_mask"], out["mask"] = z, pm, m
         out["s"] = synth.single_inputs(seed, cs["n"], cs["c_s"], 1)
         out["w"] = synth.pairformer_block_weights(seed, cs["c_z"], cs["c_s"])
+    elif kind == "tri_block":
+        z, pm, _ = synth.pair_inputs(seed, cs["n"], cs["c_z"], 1, valid=cs["valid"])
+        out["z"], out["pair_mask"] = z, pm
+        out["w"] = synth.triangular_block_weights(seed, cs["c_z"])
     else:
         raise ValueError(kind)
     return out

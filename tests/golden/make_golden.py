@@ -24,6 +24,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+sys.path.insert(0, os.path.dirname(HERE))          # tests/: synth.py
 
 import cases  # noqa: E402
 import ref_shim  # noqa: E402
@@ -116,6 +117,10 @@ def run_reference(ns, name: str) -> dict:
                                 inp["pair_bias"], inp["token_mask"])}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
+    if kind == "tri_block":
+        import importlib
+        ts = importlib.import_module("kfold.model.modules.tri_stack")
+        return {"out": _load(ts.TriangularBlock(cs["c_z"], kernel_backend="torch"), inp["w"])(inp["z"].clone(), inp["pair_mask"])}
     if kind == "block":
         w, c_z, c_s = inp["w"], cs["c_z"], cs["c_s"]
         z, s, pm, m = inp["z"].clone(), inp["s"].clone(), inp["pair_mask"], inp["mask"]

@@ -196,6 +196,16 @@ def pairformer_block_weights(seed: int, c_z: int = 128, c_s: int = 384, tri_head
     return w
 
 
+def triangular_block_weights(seed: int, c_z: int = 256) -> dict:
+    """TriangularBlock, the block of K-Fold's own trunk (model/modules/tri_stack.py:119-128)."""
+    rng = _Rng(seed)
+    w = {}
+    w.update(_prefixed("tri_mul_out", trimul_weights(rng, c_z)))
+    w.update(_prefixed("tri_mul_in", trimul_weights(rng, c_z)))
+    w.update(_prefixed("transition_z", transition_weights(rng, c_z, 4)))
+    return w
+
+
 def token_mask(n: int, valid: int | None = None, pad_frac: float | None = None) -> torch.Tensor:
     """Boolean token mask with a trailing padding tail (how K-Fold pads, inference/data_pipeline.py:129-134)."""
     if valid is None:

@@ -1,7 +1,8 @@
 """GPU parity: the CUDA path (through the C ABI) against the golden vectors and the oracle.
 
 Tolerances (bf16 arithmetic, fp32 accumulation), stated relative to RMS(reference):
-  RMS error  <= 2e-2  -- the parity criterion for bf16 mode;
+  RMS error  <= 1e-2  -- the parity criterion for bf16 mode (the bound asked of bf16 mode is 2e-2; measured errors sit
+                        at 5e-3 .. 7e-3, so the tests hold the kernels to half the bound to catch regressions);
   max-abs    <= 0.15  -- a sanity bound; the reference's own bf16 path sits at 4e-2 .. 9e-2 max-abs
                         from its fp32 path on these inputs, so max-abs cannot be tighter than that.
 """
@@ -14,7 +15,7 @@ from oracle import pairformer_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-RMS_TOL = 2e-2
+RMS_TOL = 1e-2
 MAX_TOL = 0.15
 
 
@@ -194,7 +195,8 @@ def _oracle_on(dev, fn, *args, **kw):
 def test_trimul_config2_sizes(dev, n, direction):
     """benchmark config 2: N in {256, 512, 768}, C=128, last 10% of tokens padded, seed 1."""
     from kfold_b200 import functional as F
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     z, pm, _ = synth.pair_inputs(1, n, 128, 1, pad_frac=0.1)
     w = synth.trimul_weights(synth._Rng(1), 128)
     zb = z.bfloat16()
@@ -208,7 +210,8 @@ def test_trimul_config2_sizes(dev, n, direction):
 def test_triatt_config3_size(dev, starting):
     """benchmark config 3: N=384, 4 heads x 32, first 352 tokens valid, seed 2."""
     from kfold_b200 import functional as F
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     z, pm, _ = synth.pair_inputs(2, 384, 128, 1, valid=352)
     w = synth.triatt_weights(synth._Rng(2), 128, 4)
     zb = z.bfloat16()
@@ -224,7 +227,8 @@ def test_triatt_config3_size(dev, starting):
 def test_ending_node_is_starting_node_on_the_transpose(dev):
     """Size-independent property at full size: ending(x, m) == starting(x^T, m^T)^T, bit for bit."""
     from kfold_b200 import functional as F
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     z, pm, _ = synth.pair_inputs(9, 768, 128, 1, pad_frac=0.05)
     pk = packing.pack_triatt(synth.triatt_weights(synth._Rng(9), 128, 4), 4, dev)
     zb, pm = z.to(dev, torch.bfloat16), pm.to(dev)
@@ -237,7 +241,8 @@ def test_trimul_full_size_linearity_in_the_mask(dev):
     """Masking property at N=768: zeroing the mask of token t removes exactly row/column t's contribution,
     i.e. the result equals running on inputs whose masked entries are anything at all."""
     from kfold_b200 import functional as F
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     z, pm, _ = synth.pair_inputs(10, 768, 128, 1, pad_frac=0.1)
     pk = packing.pack_trimul(synth.trimul_weights(synth._Rng(10), 128), dev)
     zb, pmd = z.to(dev, torch.bfloat16), pm.to(dev)
@@ -252,7 +257,8 @@ def test_trimul_full_size_linearity_in_the_mask(dev):
 
 def test_residual_fusion_matches_separate_add(dev):
     from kfold_b200 import functional as F
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     z, pm, _ = synth.pair_inputs(12, 128, 128, 1, pad_frac=0.1)
     zb, pmd = z.to(dev, torch.bfloat16), pm.to(dev)
     pk = packing.pack_trimul(synth.trimul_weights(synth._Rng(12), 128), dev)
@@ -264,7 +270,8 @@ def test_residual_fusion_matches_separate_add(dev):
 
 def test_transition_sizes(dev):
     from kfold_b200 import functional as F
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     for c, f, rows in ((128, 4, 384 * 384), (384, 4, 768)):
         w = synth.transition_weights(synth._Rng(c), c, f)
         x = synth._Rng(c + 1).normal(rows, c).bfloat16()
@@ -277,7 +284,7 @@ def test_transition_sizes(dev):
 def test_apb_single_track_size(dev):
     """Single-track pair-bias attention of the composite block: L=768, c=384, 16 heads x 24."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(77)
     w = synth.apb_weights(rng, 384, None)
     s = rng.normal(1, 768, 384).bfloat16()
@@ -296,7 +303,7 @@ def test_attention_stabiliser_moves_when_later_keys_dominate(dev):
     only when a later half tile would overflow.  A pair bias that grows by 100 per 64 keys (144 in log2 units, beyond
     the 2^100 row-sum limit) forces that path on every half tile; rows whose first keys are masked start from -1e9."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(78)
     L = 320
     w = synth.apb_weights(rng, 384, None)
@@ -396,7 +403,7 @@ def test_diffusion_stack_config4_shape(dev):
     """benchmark config 4's token transformer shape: c=768, 16 heads x 48, L=768, 5 samples sharing the pair bias
     (2 of the 24 blocks), against the oracle run on the GPU in fp32."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(404)
     blocks, l, ns = 2, 768, 5
     w = {}
@@ -418,7 +425,7 @@ def test_diffusion_stack_config4_shape(dev):
 def test_ragged_and_general_mask_through_module_api(dev):
     """N not a multiple of 8 and a non-separable (B,N,N) mask with batch 3 through the module API."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     n, b = 37, 3
     rng = synth._Rng(5)
     x = rng.normal(b, n, n, 128).bfloat16()
@@ -509,7 +516,7 @@ def test_local_transformer_block_windowed_signature(dev):
     """LocalTransformerBlock.forward with the reference's windowed arguments (a_q, a_k, s_q, s_k, normalised z, mask_k):
     the generic cross-attention entry with a broadcast bias, against the oracle."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(62)
     l, c, c_z, h, ns = 96, 128, 16, 4, 2
     w = {"linear_z_to_bias.weight": rng.linear(h, c_z)}
@@ -541,7 +548,7 @@ def test_local_transformer_config4_shape(dev):
     """benchmark config 4's atom transformer shape: 6 016 atoms = 188 windows, c=128, 4 heads x 32, c_z=16, 5 samples
     sharing z and s, 3 blocks, against the oracle run on the GPU in fp32."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(63)
     l, c, c_z, h, blocks, ns = 6016, 128, 16, 4, 3, 5
     w = synth.local_stack_weights(rng, c, c, c_z, h, blocks)
@@ -606,7 +613,7 @@ def test_local_transformer_stack_two_complexes(dev, z_per_sample):
     """Two complexes x two samples, 7 windows (the last query block holds three of its four windows): the window pair
     tensor shared by the samples of a complex, or one per sample; per-complex atom masks."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(64 + int(z_per_sample))
     l, c, c_z, h, blocks = 224, 128, 16, 4, 2
     w = synth.local_stack_weights(rng, c, c, c_z, h, blocks)
@@ -718,7 +725,7 @@ def test_local_transformer_stack_window_edges(dev, l, valid):
     molecule on both sides), two windows, a window whose keys are all padding atoms (160 atoms, 64 valid), and a length that
     fills two query blocks and a quarter.  One sample, window pair tensor of its own, against the oracle."""
     from kfold_b200 import modules as M
-    from kfold_b200 import synth
+    import synth
     rng = synth._Rng(80 + l)
     c, c_z, h, blocks = 128, 16, 4, 1
     w = synth.local_stack_weights(rng, c, c, c_z, h, blocks)

@@ -26,7 +26,8 @@ def _worker(rank: int, world: int, port: int, n: int, exchange: str, q):
     try:
         from kfold_b200 import _lib as L
         from kfold_b200 import modules as M
-        from kfold_b200 import sharded, synth
+        from kfold_b200 import sharded
+        import synth
         w = synth.pairformer_block_weights(21)
         z, pm, m = synth.pair_inputs(21, n, 128, 1, pad_frac=0.1)
         s = synth.single_inputs(21, n, 384, 1)

@@ -4,7 +4,8 @@ import torch
 
 from kfold_b200 import functional as F
 from kfold_b200 import modules as M
-from kfold_b200 import packing, synth
+from kfold_b200 import packing
+import synth
 
 
 def test_interleave_glu_layout():
@@ -148,7 +149,8 @@ def test_bias_sharing_patterns():
 
 
 def test_pack_apb_cross_layout():
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
     w = synth.cross_apb_weights(synth._Rng(3), 128, 128)
     keys = ("linear_q.weight", "linear_q.bias", "linear_k.weight", "linear_v.weight", "linear_g.weight", "linear_out.weight")
     pk = packing.pack_apb_cross({k: w[k] for k in keys}, 4, "cpu")

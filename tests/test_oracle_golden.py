@@ -47,6 +47,8 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
                                         cs["token_heads"], cs["token_blocks"], mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
+    if kind == "tri_block":
+        return {"out": O.triangular_block(inp["z"], inp["pair_mask"], w, mode)}
     if kind == "block":
         z, s = O.pairformer_block(inp["z"], inp["s"], inp["pair_mask"], inp["mask"], w, mode=mode)
         return {"z": z, "s": s}

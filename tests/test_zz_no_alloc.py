@@ -31,7 +31,8 @@ def _call_both(L, x, pk, rows, c, hidden, dtype_code):
 
 def test_static_scratch_transition_matches_workspace_version_twice():
     from kfold_b200 import _lib as L
-    from kfold_b200 import packing, synth
+    from kfold_b200 import packing
+    import synth
 
     dev = torch.device("cuda:0")
     c, factor = 384, 4
