@@ -28,11 +28,12 @@ import time
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for _p in (ROOT, os.path.join(ROOT, "tests")):   # tests/ holds the seeded synthetic inputs (synth.py)
+for _p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")):   # synth.py, ref_shim.py
     if _p not in sys.path:
         sys.path.insert(0, _p)
 
 N_TOKENS = 768
+N_TOKENS_DEFAULT = 768
 C_Z, C_S = 128, 384
 PAD_FRAC = 0.1
 SEED = 3
@@ -71,7 +72,8 @@ def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C
 
 # DRAM traffic of the triangle-attention kernel from its ncu capture at N=384 (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch: 152.4 MB + 25.8 MB); it grows with the number of pair positions.
-NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 152.376576e6 + 26.054656e6}}
+NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 152.376576e6 + 26.054656e6,
+                                     "source": "ncu capture at N=384 scaled by pair positions (profiles/triatt_attention_n384_ncu.md)"}}
 
 
 def ncu_traffic(tag: str, n: int):
@@ -82,12 +84,25 @@ def ncu_traffic(tag: str, n: int):
 
 
 def load_peaks() -> dict:
+    """Roofline denominators: the copy bandwidth and the two cuBLAS bf16 figures measured on this pool's B200s (burst =
+    a kernel timed alone at the full SM clock, sustained = inside a seconds-long loop under the power cap)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return {"hbm_gbs": d["hbm_gbs"], "tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": d["hbm_gbs"], "tflops_burst": d["bf16_tflops"],
+                "tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def pick_tensor_peak(peaks: dict, region_s: float, clocks: dict) -> tuple[float, str]:
+    """Which bf16 peak a timed region is compared with: the burst figure when the region is short (under a second) and the
+    sampled SM clock sat at its maximum, the sustained one otherwise."""
+    sm, smax = clocks.get("sm_mhz"), clocks.get("sm_max_mhz")
+    at_max = sm is not None and smax is not None and sm >= 0.97 * smax
+    if region_s < 1.0 and at_max:
+        return peaks["tflops_burst"], "burst"
+    return peaks["tflops_sustained"], "sustained"
 
 
 class ClockSampler:
@@ -155,26 +170,46 @@ def config_dict(n_gpus: int, sharded_mode: bool = False) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU arm: the oracle port of the reference's torch path on the host cores
+# CPU arm: the reference's own torch modules on the host cores (the oracle port where the reference is absent)
 # ------------------------------------------------------------------------------------------------
-def cpu_block_time(n: int, repeats: int, warmup: int):
-    """Times the CPU oracle's composite block at `n` tokens in fp32; returns (best_ms, cores)."""
+def cpu_block_runner(n: int):
+    """-> (run, kind, what): `run()` executes one composite block at `n` tokens in float32 on the CPU and returns nothing.
+    kind "reference": the block assembled from the reference's own modules (kernel_backend="torch"), imported from the
+    installed copy under baseline/_ref; kind "port": the oracle's restatement, when no reference copy is on the machine."""
     import synth
-    from oracle import pairformer_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     z, pm, m = synth.pair_inputs(SEED, n, C_Z, 1, pad_frac=PAD_FRAC)
     s = synth.single_inputs(SEED, n, C_S, 1)
     w = synth.pairformer_block_weights(SEED, C_Z, C_S)
+    try:
+        import ref_shim
+        block = ref_shim.build_reference_block(ref_shim.load_reference(), w, C_Z, C_S)
+
+        def run():
+            block(z.clone(), s.clone(), pm, m)      # the reference adds in place
+
+        return run, "reference", f"the reference's torch modules (float32, kernel_backend=\"torch\", {cores} threads)", cores
+    except Exception as exc:      # no reference copy on this machine
+        from oracle import pairformer_oracle as O
+        why = f"{type(exc).__name__}: {exc}"
+
+        def run():
+            with torch.no_grad():
+                O.pairformer_block(z, s, pm, m, w, row_chunk=64)
+
+        return run, "port", f"CPU port of the reference torch path (float32, {cores} threads; reference not importable: {why})", cores
+
+
+def time_cpu_block(run, repeats: int, warmup: int) -> list:
     times = []
-    with torch.no_grad():
-        for i in range(warmup + repeats):
-            t0 = time.perf_counter()
-            O.pairformer_block(z, s, pm, m, w, row_chunk=64)
-            dt = (time.perf_counter() - t0) * 1e3
-            if i >= warmup:
-                times.append(dt)
-    return times, cores
+    for i in range(warmup + repeats):
+        t0 = time.perf_counter()
+        run()
+        dt = (time.perf_counter() - t0) * 1e3
+        if i >= warmup:
+            times.append(dt)
+    return times
 
 
 def block_flops(n: int, c: int = C_Z, h: int = 4, cs: int = C_S, hs: int = 16) -> float:
@@ -188,23 +223,35 @@ def block_flops(n: int, c: int = C_Z, h: int = 4, cs: int = C_S, hs: int = 16) -
     return 2 * trimul + 2 * triatt + transition_z + single
 
 
-CPU_SAMPLE_N = 256
+# The reference arm runs the block at the benchmark's own size.  One block takes several seconds on the host cores, so the
+# arm bounds its run time by the NUMBER of steps it measures, never by the work per step: at most this many seconds of
+# measured steps (at least two), after one warm-up step; the line reports the steps and warm-ups actually done.
+REFERENCE_BUDGET_S = 120.0
 
 
 def run_reference_arm(args, rank: int, world: int) -> None:
     if rank != 0:
         return
-    times, cores = cpu_block_time(CPU_SAMPLE_N, args.steps, args.warmup)
-    scale = block_flops(N_TOKENS) / block_flops(CPU_SAMPLE_N)
-    ms_sample = sum(times) / len(times)
-    value = ms_sample * scale
-    sample = (f"CPU port of the reference torch path (fp32, {cores} threads): one block at N={CPU_SAMPLE_N} per step "
-              f"({ms_sample:.1f} ms), scaled to N={N_TOKENS} by the algorithmic FLOP ratio {scale:.2f}")
+    run, kind, what, cores = cpu_block_runner(N_TOKENS)
+    # warm-up steps as asked, cut short once they have taken 30 s
+    warm, t0 = 0, time.perf_counter()
+    while warm < args.warmup and (warm == 0 or time.perf_counter() - t0 < 30.0):
+        run()
+        warm += 1
+    first = time.perf_counter() - t0
+    times = []
+    while len(times) < args.steps and (len(times) < 2 or sum(times) / 1e3 + (times[-1] / 1e3) < REFERENCE_BUDGET_S):
+        times += time_cpu_block(run, 1, 0)
+    value = sum(times) / len(times)
+    sample = (f"{what}: one block at N={N_TOKENS} per step, {len(times)} measured steps of {args.steps} asked "
+              f"(run time bounded at {REFERENCE_BUDGET_S:.0f} s of measured steps), {warm} warm-up steps of {args.warmup} asked"
+              + (f" ({first:.1f} s)" if warm else ""))
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": len(times),
+        "warmup": warm, "steps_requested": args.steps, "warmup_requested": args.warmup, "ms_per_step": value,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": config_dict(1),
-        "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -427,6 +474,132 @@ def run_sampler_step(args) -> None:
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+def _event_time(fn, steps: int, stream, barrier) -> float:
+    """ms per call of `fn`, CUDA events on `stream`, a barrier + device synchronisation on both sides."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def _rel_rms(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.double(), b.double()
+    return float((a - b).pow(2).mean().sqrt() / (b.pow(2).mean().sqrt() + 1e-30))
+
+
+def sharded_bytes_out(n: int, c: int, h: int, hs: int, p: int, channel: bool) -> int:
+    """Bytes one rank sends to its peers during one row-sharded block (bf16): the operand exchanges of the two triangle
+    multiplications, the shard transposes of the incoming / ending-node operators, the gathered triangle and single-track
+    biases.  An all-gathered piece leaves the GPU once per peer."""
+    shard = n * n * c * 2 // p                       # one rank's rows of a pair-sized tensor
+    out_frac = (p - 1) / p
+    if channel:
+        trimul = 2 * (2 * shard + shard) * out_frac      # a and b out, t back: all-to-all
+    else:
+        trimul = 2 * shard * (p - 1)                     # all-gather of b
+    transposes = 3 * shard * out_frac                    # z^T for the incoming operator, z^T and the update back for the ending node
+    biases = (2 * h + hs) * (n * n * 2 // p) * (p - 1)   # two triangle biases and the single-track bias, all-gathered
+    return int(trimul + transposes + biases)
+
+
+def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
+    """Benchmark config 5's unit on the ranks of this run: ONE Pairformer block at N=2048 (5 % padding tail, seed 4), its
+    pair tensor row-sharded over the GPUs; beside it the same block on one GPU, so that the speed-up is measured inside
+    one process group.  With one rank only the plain block runs."""
+    import torch.distributed as dist
+    from kfold_b200 import _lib as L
+    import synth
+    n = 2048
+    steps = 3
+    z, pm, m = synth.pair_inputs(4, n, C_Z, 1, pad_frac=0.05)
+    s = synth.single_inputs(4, n, C_S, 1)
+    stream = torch.cuda.current_stream()
+    zd, sd, pmd, md = z.to(dev, torch.bfloat16), s.to(dev, torch.bfloat16), pm.to(dev), m.to(dev)
+    del z
+    for _ in range(2):
+        blk(zd, sd, pmd, md)
+    ms_1gpu = _event_time(lambda: blk(zd, sd, pmd, md), steps, stream, barrier)
+    res = {"n_token": n, "ms_1gpu": round(ms_1gpu, 3)}
+    if world == 1:
+        res.update(ms=round(ms_1gpu, 3), speedup_vs_1gpu=1.0, exchange="none (one GPU: the plain block)")
+        return res
+    from kfold_b200 import sharded as SH
+    r0, r1 = SH.shard_rows(n, world, rank)
+    z_loc, pm_loc = zd[0, r0:r1].contiguous(), pmd[0, r0:r1].contiguous()
+    del zd
+    from kfold_b200 import functional as F
+    F.release_workspaces()
+    torch.cuda.empty_cache()
+    sblk = SH.ShardedPairformerBlock(blk)
+    channel = world >= 4 and C_Z % world == 0
+    for _ in range(2):
+        sblk(z_loc, sd, pm_loc, md)
+    L.profile_enable(True)
+    ms = _event_time(lambda: sblk(z_loc, sd, pm_loc, md), steps, stream, barrier)
+    prof = L.profile_report()
+    L.profile_enable(False)
+    kernel_ms = sum(t for _, t in prof.values()) / steps
+    # a plain NCCL all-to-all of the size of one shard transpose, for the bandwidth the exchanges could reach
+    probe = torch.empty(n * n * C_Z // world, dtype=torch.bfloat16, device=dev)
+    probe_out = torch.empty_like(probe)
+    for _ in range(2):
+        dist.all_to_all_single(probe_out, probe)
+    ms_probe = _event_time(lambda: dist.all_to_all_single(probe_out, probe), 5, stream, barrier)
+    sent = probe.numel() * 2 * (world - 1) / world
+    a2a_gbs = sent / (ms_probe * 1e-3) / 1e9
+    t = torch.tensor([ms, kernel_ms, ms_1gpu, ms_probe], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, kernel_ms, ms_1gpu, ms_probe = (float(v) for v in t)
+    out_bytes = sharded_bytes_out(n, C_Z, 4, 16, world, channel)
+    bound_ms = out_bytes / (a2a_gbs * 1e9) * 1e3
+    res.update(ms=round(ms, 3), ms_1gpu=round(ms_1gpu, 3), kernel_ms=round(kernel_ms, 3), comm_ms=round(ms - kernel_ms, 3),
+               exchange="channel all-to-all" if channel else "all-gather of b",
+               speedup_vs_1gpu=round(ms_1gpu / ms, 3), bytes_sent_per_rank=out_bytes,
+               nccl_all_to_all_gbs_per_rank=round(a2a_gbs, 1), comm_bound_ms=round(bound_ms, 3),
+               note="comm_ms = step time - kernel time: collectives, reorder copies and host gaps not hidden under kernels")
+    return res
+
+
+def measure_sharded_parity(rank: int, world: int, dev, blk, w) -> dict:
+    """The row-sharded block at N=512 on the ranks of this run, both exchange forms, against (i) the one-GPU block on
+    the same rank and (ii) the oracle run on this GPU in float32 (the checker; TF32 off).  Relative RMS errors, maximum
+    over the ranks; each rank compares its own rows of z and the replicated s."""
+    import torch.distributed as dist
+    from kfold_b200 import sharded as SH
+    from oracle import pairformer_oracle as O
+    import synth
+    n = 512
+    z, pm, m = synth.pair_inputs(4, n, C_Z, 1, pad_frac=0.05)
+    s = synth.single_inputs(4, n, C_S, 1)
+    zb, sb = z.bfloat16(), s.bfloat16()
+    zd, sd, pmd, md = zb.to(dev), sb.to(dev), pm.to(dev), m.to(dev)
+    z1, s1 = blk(zd, sd, pmd, md)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        wd = {k: v.to(dev) for k, v in w.items()}
+        zo, so = O.pairformer_block(zd.float(), sd.float(), pmd, md, wd, row_chunk=64)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    r0, r1 = SH.shard_rows(n, world, rank)
+    out = {"n_token": n, "rms_1gpu_vs_oracle": round(_rel_rms(z1[0, r0:r1].float(), zo[0, r0:r1]), 5)}
+    for exchange in ("gather", "channel"):
+        if exchange == "channel" and C_Z % world != 0:
+            continue
+        sblk = SH.ShardedPairformerBlock(blk, exchange=exchange)
+        zs, ss = sblk(zd[0, r0:r1].contiguous(), sd, pmd[0, r0:r1].contiguous(), md)
+        errs = torch.tensor([_rel_rms(zs.float(), z1[0, r0:r1].float()), _rel_rms(zs.float(), zo[0, r0:r1]),
+                             _rel_rms(ss.float(), s1.float()), _rel_rms(ss.float(), so)], device=dev, dtype=torch.float64)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        out[exchange] = {"z_rms_vs_1gpu": round(float(errs[0]), 5), "z_rms_vs_oracle": round(float(errs[1]), 5),
+                         "s_rms_vs_1gpu": round(float(errs[2]), 5), "s_rms_vs_oracle": round(float(errs[3]), 5)}
+    return out
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     import torch.distributed as dist
     from kfold_b200 import _lib as L
@@ -476,6 +649,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         z_out_host.copy_(zo, non_blocking=True)
         s_out_host.copy_(so, non_blocking=True)
 
+    trunk = None
+    sharded_n2048 = None
+    parity = None
     with torch.no_grad():
         # ---- device-resident timing (with per-launch events recorded by the library)
         for _ in range(args.warmup):
@@ -509,6 +685,39 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         ms_e2e = e0.elapsed_time(e1) / args.steps
         clocks = sampler.stop() if rank == 0 else {}
 
+        if not sharded_mode and args.tokens == N_TOKENS_DEFAULT and not args.headline_only:
+            # ---- a longer region: 48 blocks back to back on one pair tensor (each block's output feeds the next), the
+            # trunk depth of benchmark config 4; the same block weights serve all 48 (1.4 MB of weights: no cache effect)
+            def trunk_pass():
+                zt, st = z_dev, s_dev
+                for _ in range(48):
+                    zt, st = blk(zt, st, pm_dev, m_dev)
+                return zt, st
+
+            trunk_pass()
+            barrier()
+            tsampler = ClockSampler(local_rank)
+            if rank == 0:
+                tsampler.start()
+            passes = 3
+            ms_trunk = _event_time(trunk_pass, passes, stream, barrier)
+            zt, _ = trunk_pass()
+            finite = bool(torch.isfinite(zt.float()).all())
+            tclocks = tsampler.stop() if rank == 0 else {}
+            if world > 1:
+                t = torch.tensor([ms_trunk], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms_trunk = float(t[0])
+            trunk = {"ms": round(ms_trunk, 3), "blocks": 48, "passes_timed": passes, "ms_per_block": round(ms_trunk / 48, 4),
+                     "region_s": round(ms_trunk * passes / 1e3, 3), "clocks": tclocks, "finite": finite,
+                     "ms_x_sm_mhz": round(ms_trunk * tclocks["sm_mhz"], 1) if tclocks.get("sm_mhz") else None}
+            del zt
+            # ---- benchmark config 5's block: N=2048, row-sharded over the ranks of this run (plain block with one rank)
+            sharded_n2048 = measure_sharded(args, rank, world, dev, blk, barrier)
+            if world > 1:
+                parity = measure_sharded_parity(rank, world, dev, blk, w)
+        status = status or L.device_status()
+
     if world > 1:
         t = torch.tensor([ms_step, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -516,6 +725,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     if rank == 0:
         peaks = load_peaks()
+        region_s = ms_step * args.steps / 1e3
+        tensor_peak, peak_kind = pick_tensor_peak(peaks, region_s, clocks)
         work = algorithmic_work()
         total_ms = sum(v[1] for v in prof.values()) or 1.0
         kernels = {}
@@ -525,8 +736,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             if tag in work:
                 kind, amount = work[tag]
                 if kind == "tensor":
-                    ent.update(bound="tensor", achieved=round(amount / (avg_ms * 1e-3) / 1e12, 2), unit="TFLOP/s",
-                               frac=round(amount / (avg_ms * 1e-3) / 1e12 / peaks["tflops"], 4))
+                    ach = amount / (avg_ms * 1e-3) / 1e12
+                    ent.update(bound="tensor", achieved=round(ach, 2), unit="TFLOP/s", frac=round(ach / tensor_peak, 4),
+                               frac_burst=round(ach / peaks["tflops_burst"], 4),
+                               frac_sustained=round(ach / peaks["tflops_sustained"], 4))
                 else:
                     ent.update(bound="hbm", achieved=round(amount / (avg_ms * 1e-3) / 1e9, 1), unit="GB/s",
                                frac=round(amount / (avg_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4))
@@ -536,32 +749,41 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         if top and "bound" in kernels[top]:
             k = kernels[top]
             roofline = {"kernel": top, "bound": k["bound"], "achieved": k["achieved"],
-                        "peak": peaks["tflops"] if k["bound"] == "tensor" else peaks["hbm_gbs"], "unit": k["unit"],
+                        "peak": tensor_peak if k["bound"] == "tensor" else peaks["hbm_gbs"], "unit": k["unit"],
                         "frac": k["frac"], "traffic": ncu_traffic(top, N_TOKENS),
-                        "traffic_source": "ncu capture at N=384 scaled by pair positions (profiles/triatt_attention_n384_ncu.md)", "peak_source": peaks["source"],
+                        "traffic_source": NCU_TRAFFIC.get(top, {}).get("source"), "peak_source": peaks["source"],
                         "share_of_step": k["share"]}
-        # CPU baseline: the oracle port on this box's host cores, one bounded sample
+            if k["bound"] == "tensor":
+                roofline.update(peak_kind=f"{peak_kind} bf16 (timed region {region_s:.2f} s, median SM clock {clocks.get('sm_mhz')} MHz)",
+                                frac_burst=k["frac_burst"], frac_sustained=k["frac_sustained"])
+        # CPU baseline: the reference's own modules on this box's host cores, one bounded sample at the benchmark's size
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            times, cores = cpu_block_time(CPU_SAMPLE_N, 2, 1)
-            scale = block_flops(N_TOKENS) / block_flops(CPU_SAMPLE_N)
-            best = min(times)
-            cpu = {"value": best * scale, "unit": "ms", "cores": cores, "kind": "port",
-                   "sample": f"oracle (CPU port of the reference torch path, fp32) on one block at N={CPU_SAMPLE_N}: best of 2 = "
-                             f"{best:.1f} ms, scaled to N={N_TOKENS} by the algorithmic FLOP ratio {scale:.2f}"}
+            run, kind, what, cores = cpu_block_runner(N_TOKENS)
+            t_cpu = time_cpu_block(run, 1, 0)[0]
+            cpu = {"value": t_cpu, "unit": "ms", "cores": cores, "kind": kind,
+                   "sample": f"{what}: ONE block at N={N_TOKENS}, a single run without warm-up"}
         h2d = z_host.numel() * 2 + s_host.numel() * 2
         d2h = z_out_host.numel() * 2 + s_out_host.numel() * 2
+        bf = block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12
         line = {
             "metric": METRIC, "value": ms_step if sharded_mode else ms_step / world, "unit": "ms", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
             "scaling": "strong" if sharded_mode else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world, sharded_mode),
-            "block_tflops": round(block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12, 2),
-            "block_frac_of_tensor_peak": round(block_flops(N_TOKENS) / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
+            "block_tflops": round(bf, 2),
+            "block_frac_of_tensor_peak": round(bf / tensor_peak, 4),
+            "block_frac_burst": round(bf / peaks["tflops_burst"], 4), "block_frac_sustained": round(bf / peaks["tflops_sustained"], 4),
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": ms_e2e / world, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches, "clocks": clocks, "device_status": status, "kernels": kernels,
+            "gpu_launches": launches, "clocks": clocks, "device_status": status,
+            "trunk48_ms": None if trunk is None else trunk["ms"], "trunk48": trunk,
+            "sharded_n2048": sharded_n2048, "sharded_parity": parity, "kernels": kernels,
         }
+        if trunk is not None and trunk["clocks"].get("sm_mhz"):
+            tp, tk = pick_tensor_peak(peaks, trunk["region_s"], trunk["clocks"])
+            tf = 48 * block_flops(N_TOKENS) / (trunk["ms"] * 1e-3) / 1e12
+            trunk.update(tflops=round(tf, 1), frac_of_tensor_peak=round(tf / tp, 4), peak_kind=tk)
         emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -593,6 +815,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the side measurements (48-block trunk, N=2048 sharded block and its parity check)")
     ap.add_argument("--sharded", action="store_true",
                     help="with N > 1 ranks: row-shard ONE pair tensor over the GPUs (strong scaling) instead of one block per GPU")
     ap.add_argument("--tokens", type=int, default=N_TOKENS,

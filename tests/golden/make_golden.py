@@ -122,19 +122,8 @@ def run_reference(ns, name: str) -> dict:
         ts = importlib.import_module("kfold.model.modules.tri_stack")
         return {"out": _load(ts.TriangularBlock(cs["c_z"], kernel_backend="torch"), inp["w"])(inp["z"].clone(), inp["pair_mask"])}
     if kind == "block":
-        w, c_z, c_s = inp["w"], cs["c_z"], cs["c_s"]
-        z, s, pm, m = inp["z"].clone(), inp["s"].clone(), inp["pair_mask"], inp["mask"]
-        z.add_(_load(ns.TriangleMultiplicationOutgoing(c_z), sub(w, "tri_mul_out"))(z, pm))
-        z.add_(_load(ns.TriangleMultiplicationIncoming(c_z), sub(w, "tri_mul_in"))(z, pm))
-        z.add_(_load(ns.TriangleAttentionStartingNode(c_z, 4), sub(w, "tri_att_start"))(z, pm))
-        z.add_(_load(ns.TriangleAttentionEndingNode(c_z, 4), sub(w, "tri_att_end"))(z, pm))
-        z.add_(_load(ns.Transition(c_z, 4), sub(w, "transition_z"))(z))
-        zn = _load(ns.LayerNorm(c_z), sub(w, "layernorm_z"))(z)
-        lin = _load(ns.LinearNoBias(c_z, 16), sub(w, "linear_pair_bias"))
-        pair_bias = lin(zn).movedim(-1, -3)
-        att = _load(ns.SelfAttentionPairBias(c_s, 16, None, "confidence", kernel_backend="torch"), sub(w, "attention"))
-        s.add_(att(s, None, pair_bias, m))
-        s.add_(_load(ns.Transition(c_s, 4), sub(w, "transition"))(s))
+        z, s = ref_shim.build_reference_block(ns, inp["w"], cs["c_z"], cs["c_s"])(
+            inp["z"].clone(), inp["s"].clone(), inp["pair_mask"], inp["mask"])
         res = {"s": s, "z_sum": z.double().sum().reshape(1), "z_sumsq": (z.double() ** 2).sum().reshape(1)}
         if cs["n"] > 32:
             res["z_sub"] = z[:, ::cases.SUB_STRIDE, ::cases.SUB_STRIDE].contiguous()

@@ -5,8 +5,13 @@ atlaslm, none of which the hot path needs.  This shim registers empty namespace
 modules for those packages (with ``__path__`` pointing at the real directories)
 so that the individual primitive/layer files can be imported unmodified.
 
-Only the fixture generator (``make_golden.py``) and the optional
-reference-vs-oracle tests use this file; nothing shipped depends on it.
+The reference is looked for, in this order, at ``$KFOLD_REFERENCE_ROOT``, in
+``baseline/_ref`` of this repository (where ``pip install --no-deps --target
+baseline/_ref <kfold checkout>`` puts the package; that directory is not under
+version control) and in a checkout named ``reference`` beside the repository.
+
+Only the fixture generator (``make_golden.py``), the reference-vs-oracle tests and
+the CPU reference arm of ``bench.py`` use this file; nothing shipped depends on it.
 """
 from __future__ import annotations
 
@@ -15,13 +20,27 @@ import os
 import sys
 import types
 
-# default: a checkout named "reference" beside this repository; KFOLD_REFERENCE_ROOT overrides it
-_DEFAULT_ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
+_REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _package_parent(root: str) -> str | None:
+    """The directory that holds the ``kfold`` package under `root`: ``root/src`` (a checkout) or ``root`` (an install)."""
+    for parent in (os.path.join(root, "src"), root):
+        if os.path.isfile(os.path.join(parent, "kfold", "model", "primitives", "__init__.py")):
+            return parent
+    return None
 
 
 def reference_root() -> str | None:
-    root = os.environ.get("KFOLD_REFERENCE_ROOT", _DEFAULT_ROOT)
-    return root if os.path.isdir(os.path.join(root, "src", "kfold")) else None
+    """Directory to put on sys.path so that ``import kfold`` finds the reference, or None."""
+    cands = [os.environ.get("KFOLD_REFERENCE_ROOT"), os.path.join(_REPO, "baseline", "_ref"),
+             os.path.join(os.path.dirname(_REPO), "reference")]
+    for root in cands:
+        if root and os.path.isdir(root):
+            parent = _package_parent(root)
+            if parent is not None:
+                return parent
+    return None
 
 
 def _namespace(name: str, path: str) -> None:
@@ -37,10 +56,9 @@ def _namespace(name: str, path: str) -> None:
 
 def load_reference():
     """Return a namespace of the reference classes on the hot path."""
-    root = reference_root()
-    if root is None:
+    src = reference_root()
+    if src is None:
         raise RuntimeError("K-Fold reference tree not found")
-    src = os.path.join(root, "src")
     if src not in sys.path:
         sys.path.insert(0, src)
     import kfold  # noqa: F401  (top-level package has a light __init__)
@@ -82,3 +100,44 @@ def load_reference():
     ns.SelfAttentionPairBias = apb.SelfAttentionPairBias
     ns.CrossAttentionPairBias = apb.CrossAttentionPairBias
     return ns
+
+
+def _sub(weights: dict, prefix: str) -> dict:
+    p = prefix + "."
+    return {k[len(p):]: v for k, v in weights.items() if k.startswith(p)}
+
+
+def build_reference_block(ns, w: dict, c_z: int = 128, c_s: int = 384, tri_heads: int = 4, single_heads: int = 16):
+    """The composite Pairformer block of the benchmark, assembled from REFERENCE modules only (torch backend): the pair
+    track in the order of ``PairformerBlock.forward`` (model/modules/apo_module.py:145-172) with ``Transition(c_z, 4)``,
+    then the single track of ``ConfidencePairSingleBlock.forward`` (model/modules/confidence_head.py:152-175).
+    Returns ``fn(z, s, pair_mask, mask) -> (z, s)``; the inputs are updated in place, as the reference does in eval."""
+    import torch
+
+    def load(mod, sd):
+        mod.load_state_dict(sd, strict=True)
+        return mod.eval()
+
+    tmo = load(ns.TriangleMultiplicationOutgoing(c_z), _sub(w, "tri_mul_out"))
+    tmi = load(ns.TriangleMultiplicationIncoming(c_z), _sub(w, "tri_mul_in"))
+    tas = load(ns.TriangleAttentionStartingNode(c_z, tri_heads), _sub(w, "tri_att_start"))
+    tae = load(ns.TriangleAttentionEndingNode(c_z, tri_heads), _sub(w, "tri_att_end"))
+    trz = load(ns.Transition(c_z, 4), _sub(w, "transition_z"))
+    lnz = load(ns.LayerNorm(c_z), _sub(w, "layernorm_z"))
+    lin = load(ns.LinearNoBias(c_z, single_heads), _sub(w, "linear_pair_bias"))
+    att = load(ns.SelfAttentionPairBias(c_s, single_heads, None, "confidence", kernel_backend="torch"), _sub(w, "attention"))
+    trs = load(ns.Transition(c_s, 4), _sub(w, "transition"))
+
+    @torch.no_grad()
+    def block(z, s, pair_mask, mask):
+        z.add_(tmo(z, pair_mask))
+        z.add_(tmi(z, pair_mask))
+        z.add_(tas(z, pair_mask))
+        z.add_(tae(z, pair_mask))
+        z.add_(trz(z))
+        pair_bias = lin(lnz(z)).movedim(-1, -3)
+        s.add_(att(s, None, pair_bias, mask))
+        s.add_(trs(s))
+        return z, s
+
+    return block
