@@ -274,7 +274,8 @@ KFB_API int kfb_window_bias_fwd(const void* z, const float* ln_w, const float* l
  *   entries (the diffusion samples) share one row.
  *   kfb_coord_embed replaces `q + linear_r_to_q(r_noisy)` (atom_transformer.py:362-367, a float32 Linear):
  *     out[row, :] = q[qrow, :] + w r[row, :];  q (rows / samples, c) of q_dtype shared by the `samples` samples
- *     (rows ordered (group, sample, l atoms)), r fp32 (rows, kc <= 4), w fp32 [c, kc], out fp32 (rows, c);
+ *     (rows ordered (group, sample, l atoms)), r fp32 (rows, kc <= 8: the sampler passes the scaled noisy
+ *     coordinates and the scaled prior coordinates side by side, kc = 6), w fp32 [c, kc], out fp32 (rows, c);
  *     mask : NULL or bytes (rows / samples), atom validity shared like q: the coordinates of padding atoms count as zero
  *     (`r_noisy * atom_mask`, src/kfold/model/layers/folding/diffusion.py:521).
  *   kfb_ln_project replaces `linear_q_to_r(layernorm_q(q.float()))` (atom_transformer.py:487-488):
@@ -343,6 +344,41 @@ KFB_API int kfb_cond_transition_fwd(const void* x_normed, const void* w_swiglu_p
  */
 KFB_API int kfb_fourier_embed(const float* t, const float* w, const float* b, float* out, int rows, int dim, void* stream);
 KFB_API int kfb_broadcast_add(const float* s, const float* f, float* out, int groups, int samples, int l, int c, void* stream);
+
+/*
+ * The coordinate-space steps of the sampler loop around the score network, KFoldECSI.sample_structure
+ * (src/kfold/model/modules/ecsi.py:498-560).  A coordinate set is one diffusion sample of one complex: l atoms x 3 fp32,
+ * contiguous; the n sets of a call are ordered (complex, sample) and `mask_div` consecutive sets share one row of the
+ * atom mask (bytes, (n / mask_div, l)).  The host keeps the scalar schedule (times, bridge coefficients, churn and update
+ * coefficients) and draws the normals -- in the reference's order, so that a run with the same generator state consumes
+ * the same numbers -- and passes them in.
+ *   kfb_coords_augment replaces CenterRandomAugmentation with centering=False (src/kfold/utils/geometry/random_augment.py:
+ *     463-513): x <- x R + trans on the valid atoms, 0 on padding, in place, for x_a and (if not NULL) x_b with the same
+ *     R and trans per set.  normals4 (n, 4): the standard normals the rotation quaternion is built from (:296-350);
+ *     trans (n, 3) or NULL.
+ *   kfb_sampler_prepare replaces _apply_forward_pinned_churn (ecsi.py:670-732) and the input preconditioning of
+ *     inference_step (:624-633): x_hat = a x_t + b x_T + c noise (noise counted as zero on padding atoms; with noise = NULL
+ *     the step does not churn and x_hat = x_t), r6 = [c_in x_hat | x_T * inv_sigma_T] (n, l, 6), the score network's input.
+ *   kfb_sampler_update replaces the output preconditioning (:666-667), custom_rigid_align(..., rotation_only=True) (:59-103,
+ *     :535), do_centering (:538) and _update_step (:734-807): x0 = c_skip x_noisy + c_out r_update, rotated onto x_noisy
+ *     over the valid atoms, centred on them, zero on padding; x_next = ca x_noisy + cb x0 + cc x_T + cd noise (noise = NULL:
+ *     the deterministic SI update).  x0_hat (n, l, 3) or NULL receives the aligned, centred estimate.
+ *   kfb_rigid_align replaces custom_rigid_align with output_mask = mask (ecsi.py:59-103; the weighted Kabsch fit of
+ *     src/kfold/utils/geometry/rigid_align.py:685-771, computed from the 3 x 3 covariance through the largest eigenvector
+ *     of Horn's 4 x 4 matrix instead of an SVD: the same proper rotation).
+ *   kfb_center_coords replaces do_centering (random_augment.py:90-130): subtract the mean of the valid atoms, zero padding.
+ */
+KFB_API int kfb_coords_augment(float* x_a, float* x_b, const float* normals4, const float* trans, const unsigned char* mask, int n,
+                               int l, int mask_div, void* stream);
+KFB_API int kfb_sampler_prepare(const float* x_t, const float* x_T, const float* noise, const unsigned char* mask, float a, float b,
+                                float c, float c_in, float inv_sigma_T, float* x_hat, float* r6, int n, int l, int mask_div,
+                                void* stream);
+KFB_API int kfb_sampler_update(const float* x_noisy, const float* r_update, const float* x_T, const float* noise,
+                               const unsigned char* mask, float c_skip, float c_out, float ca, float cb, float cc, float cd,
+                               float* x_next, float* x0_hat, int n, int l, int mask_div, void* stream);
+KFB_API int kfb_rigid_align(const float* coords, const float* target, const unsigned char* mask, int rotation_only, float* out, int n,
+                            int l, int mask_div, void* stream);
+KFB_API int kfb_center_coords(const float* coords, const unsigned char* mask, float* out, int n, int l, int mask_div, void* stream);
 
 /*
  * Transition: out = Linear_out(silu(u_a) * u_b), [u_a, u_b] = Linear(LayerNorm(x))  (+ resid).

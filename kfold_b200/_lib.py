@@ -69,6 +69,13 @@ _SIGNATURES = {
                            c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_pair_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_coords_augment": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kfb_sampler_prepare": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_float, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_void_p],
+    "kfb_sampler_update": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_float, c_float,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kfb_rigid_align": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kfb_center_coords": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "kfb_transition_fwd_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
                                   c_float, c_int, c_void_p],
 }

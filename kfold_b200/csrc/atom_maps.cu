@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(256) coord_embed_kernel(const TQ* __restrict__
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
   const long long qrow = (row / (static_cast<long long>(samples) * l)) * l + row % l;
-  float rv[4] = {0.f, 0.f, 0.f, 0.f};
+  float rv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const bool keep = mask == nullptr || mask[qrow] != 0;   // coordinates of padding atoms count as zero
   for (int k = 0; k < kc; ++k) rv[k] = keep ? r[row * kc + k] : 0.f;
   for (int i = lane; i < c; i += 32) {
@@ -263,7 +263,7 @@ KFB_API int kfb_coord_embed(const void* q, const float* r, const float* w, const
                             int c, int kc, int samples, int l, int q_dtype, void* stream_) {
   KFB_CHECK_ARG(q && r && w && out, "coord_embed: null pointer");
   KFB_CHECK_ARG(q_dtype == KFB_BF16 || q_dtype == KFB_FP32, "coord_embed: dtype %d (bf16 or fp32)", q_dtype);
-  KFB_CHECK_ARG(rows >= 1 && c >= 1 && kc >= 1 && kc <= 4 && samples >= 1 && l >= 1 &&
+  KFB_CHECK_ARG(rows >= 1 && c >= 1 && kc >= 1 && kc <= 8 && samples >= 1 && l >= 1 &&
                     rows % (static_cast<long long>(samples) * l) == 0,
                 "coord_embed: rows %lld c %d coordinates %d samples %d l %d", rows, c, kc, samples, l);
   cudaStream_t stream = as_stream(stream_);

@@ -1,7 +1,6 @@
 // Flash-style pair-bias attention kernel (see attention.cuh for the contract).
 #include <cuda_bf16.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "attention.cuh"
@@ -106,7 +105,11 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int nhalf = 2 * nkv;
   long long* trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
 #ifdef KFB_DEBUG_TRACE
+#ifdef KFB_DEBUG_TRACE
 #define KFB_STAMP(slot) do { if (trace != nullptr) trace[slot] = clock64(); } while (0)
+#else
+#define KFB_STAMP(slot) do { (void)trace; } while (0)
+#endif
 #else
 #define KFB_STAMP(slot) do { (void)trace; } while (0)
 #endif
@@ -616,15 +619,10 @@ int launch_attention(cudaStream_t stream, const AttnParams& p_in) {
                   "attention: window mode needs head dim <= 32, Lq == Lk a multiple of 32 and bias_mod == Lq / 32 windows");
     return launch_cfg<32, 1, true>(stream, p);
   }
-  if (p.dpad == 32) {
-    // One row group per CTA with two CTAs resident per SM is the default: the two CTAs interleave their
-    // softmax and tensor-core phases better than two row groups inside one CTA do (measured 6% faster at
-    // N=768), and the bias tile both read stays in L2.  KFB_ATT_R2 selects the variant with two batch rows
-    // per CTA sharing one bias tile in shared memory (needs consecutive rows to share their bias).
-    static const bool two_rows = getenv("KFB_ATT_R2") != nullptr;
-    if (two_rows && p.batch % 2 == 0 && p.bias_div % 2 == 0 && p.bias_mod == 0) return launch_cfg<32, 2>(stream, p);
-    return launch_cfg<32, 1>(stream, p);
-  }
+  // head dim <= 32: one row group per CTA, two CTAs resident per SM -- they interleave their softmax and tensor-core
+  // phases better than two row groups inside one CTA did (measured 6 % faster at N=768); the bias tile both read stays
+  // in L2
+  if (p.dpad == 32) return launch_cfg<32, 1>(stream, p);
   if (p.dpad == 64) return launch_cfg<64, 1>(stream, p);
   set_error("attention: padded head dim %d not supported (32 or 64)", p.dpad);
   return KFB_ERR_UNSUPPORTED;

@@ -705,3 +705,106 @@ def broadcast_add(s: torch.Tensor, f: torch.Tensor) -> torch.Tensor:
     with L.on_device(s.device):
         L.check(L.lib().kfb_broadcast_add(L.ptr(s2), L.ptr(f2), L.ptr(out), b, n, l, c, L.stream_ptr()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# coordinate-space steps of the sampler loop (model/modules/ecsi.py:498-560)
+# ------------------------------------------------------------------------------------------------
+def _coord_sets(x: torch.Tensor, mask: torch.Tensor):
+    """(n sets, l atoms, sets per mask row, mask bytes) of coordinates x (*, L, 3) with an atom mask (*, L) whose leading
+    dims equal x's up to trailing 1s (the samples of a complex share their mask)."""
+    if x.dtype != torch.float32 or x.shape[-1] != 3:
+        raise ValueError(f"coordinates must be float32 (*, L, 3), got {x.dtype} {tuple(x.shape)}")
+    lead, l = tuple(x.shape[:-2]), x.shape[-2]
+    div = _index_sharing(lead, tuple(mask.shape[:-1]))
+    m = mask.to(torch.bool)
+    if div is None:
+        m, div = m.expand(*lead, l), 1
+    n = 1
+    for d in lead:
+        n *= d
+    return n, l, div, m.reshape(-1, l).contiguous().view(torch.uint8)
+
+
+def coords_augment(coords: list, normals: torch.Tensor, trans: torch.Tensor | None, mask: torch.Tensor) -> list:
+    """x <- x R + trans on the valid atoms, 0 on padding (CenterRandomAugmentation with centering=False,
+    utils/geometry/random_augment.py:463-513) for one or two coordinate tensors (*, L, 3) that share R and trans.
+    normals (n, 4): the standard normals of the rotation quaternions; trans (*, 1, 3) or None.  Returns new tensors."""
+    _require_cuda(*coords, normals, mask)
+    if not 1 <= len(coords) <= 2:
+        raise ValueError("coords_augment takes one or two coordinate tensors")
+    n, l, div, mk = _coord_sets(coords[0], mask)
+    out = [x.contiguous().clone() for x in coords]
+    nr = normals.reshape(n, 4).float().contiguous()
+    tr = None if trans is None else trans.reshape(n, 3).float().contiguous()
+    with L.on_device(out[0].device):
+        L.check(L.lib().kfb_coords_augment(L.ptr(out[0]), L.ptr(out[1]) if len(out) > 1 else None, L.ptr(nr), L.ptr(tr), L.ptr(mk),
+                                           n, l, div, L.stream_ptr()))
+    return out
+
+
+def sampler_prepare(x_t: torch.Tensor, x_T: torch.Tensor, mask: torch.Tensor, c_in: float, sigma_T: float,
+                    churn: tuple | None = None, noise: torch.Tensor | None = None):
+    """Churn and input preconditioning (model/modules/ecsi.py:670-732, :624-633): with ``churn = (a, b, c)`` and ``noise``,
+    x_hat = a x_t + b x_T + c noise (noise zero on padding), else x_hat = x_t; returns (x_hat, r6) with
+    r6 = [c_in x_hat | x_T / sigma_T] (*, L, 6)."""
+    _require_cuda(x_t, x_T, mask)
+    n, l, div, mk = _coord_sets(x_t, mask)
+    xt, xT = x_t.contiguous(), x_T.contiguous()
+    x_hat = torch.empty_like(xt)
+    r6 = torch.empty(*xt.shape[:-1], 6, dtype=torch.float32, device=xt.device)
+    a, b, c = churn if churn is not None else (1.0, 0.0, 0.0)
+    nz = None
+    if churn is not None:
+        if noise is None or noise.shape != x_t.shape:
+            raise ValueError("Sigma-matched churn noise must match x_t shape.")
+        nz = noise.float().contiguous()
+    with L.on_device(xt.device):
+        L.check(L.lib().kfb_sampler_prepare(L.ptr(xt), L.ptr(xT), L.ptr(nz), L.ptr(mk), a, b, c, c_in, 1.0 / sigma_T, L.ptr(x_hat),
+                                            L.ptr(r6), n, l, div, L.stream_ptr()))
+    return x_hat, r6
+
+
+def sampler_update(x_noisy: torch.Tensor, r_update: torch.Tensor, x_T: torch.Tensor, mask: torch.Tensor, c_skip: float,
+                   c_out: float, coef: tuple, noise: torch.Tensor | None = None, return_x0: bool = False):
+    """Output preconditioning, rotation-only rigid alignment onto x_noisy, centring and the SI / ECSI update in one kernel
+    (model/modules/ecsi.py:666-667, :535-550): x0 = c_skip x_noisy + c_out r_update aligned and centred;
+    x_next = A x_noisy + B x0 + C x_T + D noise with ``coef = (A, B, C, D)``."""
+    _require_cuda(x_noisy, r_update, x_T, mask)
+    n, l, div, mk = _coord_sets(x_noisy, mask)
+    xn, ru, xT = x_noisy.contiguous(), r_update.float().contiguous(), x_T.contiguous()
+    A, B, C, D = coef
+    nz = None
+    if D != 0.0:
+        if noise is None or noise.shape != x_noisy.shape:
+            raise ValueError("the stochastic update needs noise of the coordinates' shape")
+        nz = noise.float().contiguous()
+    x_next = torch.empty_like(xn)
+    x0 = torch.empty_like(xn) if return_x0 else None
+    with L.on_device(xn.device):
+        L.check(L.lib().kfb_sampler_update(L.ptr(xn), L.ptr(ru), L.ptr(xT), L.ptr(nz), L.ptr(mk), c_skip, c_out, A, B, C, D,
+                                           L.ptr(x_next), L.ptr(x0), n, l, div, L.stream_ptr()))
+    return (x_next, x0) if return_x0 else x_next
+
+
+def rigid_align(coords: torch.Tensor, target: torch.Tensor, mask: torch.Tensor, rotation_only: bool = False) -> torch.Tensor:
+    """custom_rigid_align with output_mask = mask (model/modules/ecsi.py:59-103): the weighted Kabsch fit of `coords`
+    onto `target` over the masked atoms, applied to them; padding atoms give zeros."""
+    _require_cuda(coords, target, mask)
+    n, l, div, mk = _coord_sets(coords, mask)
+    c, t = coords.float().contiguous(), target.float().contiguous()
+    out = torch.empty_like(c)
+    with L.on_device(c.device):
+        L.check(L.lib().kfb_rigid_align(L.ptr(c), L.ptr(t), L.ptr(mk), 1 if rotation_only else 0, L.ptr(out), n, l, div, L.stream_ptr()))
+    return out.to(coords.dtype)
+
+
+def center_coords(coords: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """do_centering (utils/geometry/random_augment.py:90-130): subtract the mean position of the valid atoms, zero padding."""
+    _require_cuda(coords, mask)
+    n, l, div, mk = _coord_sets(coords, mask)
+    c = coords.contiguous()
+    out = torch.empty_like(c)
+    with L.on_device(c.device):
+        L.check(L.lib().kfb_center_coords(L.ptr(c), L.ptr(mk), L.ptr(out), n, l, div, L.stream_ptr()))
+    return out

@@ -962,8 +962,9 @@ class DiffusionStack(nn.Module):
     """The time-dependent part of the AF3 diffusion module, ``DiffusionStack.step`` with ``get_single_conditioning`` and
     ``get_pair_bias`` (model/layers/folding/diffusion.py:155-600, AF3 Algorithm 20): atom attention encoder ->
     token transformer -> atom attention decoder.  Sub-module and parameter names are the reference's, so the matching
-    part of a reference state dict loads by name.  Not included: ``pair_conditioning`` and ``atom_embedder`` (they run once
-    per complex, before the sampler loop) and the separate-endpoint encoder variant."""
+    part of a reference state dict loads by name (both the plain form and the production form with
+    ``separate_endpoint_atom_encoder``).  Not included: ``pair_conditioning`` and ``atom_embedder`` (they run once per
+    complex, before the sampler loop)."""
 
     def __init__(self, channel_a: int = 768, channel_s: int = 384, channel_z: int = 256, channel_atom: int = 128,
                  channel_atompair: int = 16, channel_coords: int = 3, separate_endpoint_atom_encoder: bool = False,
@@ -971,13 +972,23 @@ class DiffusionStack(nn.Module):
                  token_transformer_heads: int = 16, atom_decoder_blocks: int = 3, atom_decoder_heads: int = 4,
                  blocks_per_ckpt: int | None = None, ckpt_atom_stack: bool = False, kernel_backend: str = "b200"):
         super().__init__()
-        if separate_endpoint_atom_encoder:
-            raise NotImplementedError("DiffusionStack: the separate-endpoint atom encoder variant is not available")
+        if separate_endpoint_atom_encoder and channel_coords != 6:
+            raise ValueError("separate_endpoint_atom_encoder expects channel_coords=6 for [r_t, r_T] ECSI inputs.")
         self.kernel_backend = kernel_backend
+        self.separate_endpoint_atom_encoder = separate_endpoint_atom_encoder
         self.token_transformer_blocks, self.token_transformer_heads = token_transformer_blocks, token_transformer_heads
         self.single_conditioning = SingleConditioning(channel_s, dim_fourier=256)
-        self.atom_attention_encoder = AtomAttentionEncoder(channel_atom, channel_atompair, channel_a, channel_coords,
+        enc_coords = 3 if separate_endpoint_atom_encoder else channel_coords
+        self.atom_attention_encoder = AtomAttentionEncoder(channel_atom, channel_atompair, channel_a, enc_coords,
                                                            atom_encoder_blocks, atom_encoder_heads, use_structure=True)
+        if separate_endpoint_atom_encoder:
+            # the production form (model/layers/folding/diffusion.py:254-279): a second encoder reads the prior coordinates,
+            # the two token streams are normalised, concatenated and fused by a float32 Linear
+            self.endpoint_atom_attention_encoder = AtomAttentionEncoder(channel_atom, channel_atompair, channel_a, enc_coords,
+                                                                        atom_encoder_blocks, atom_encoder_heads, use_structure=True)
+            self.layernorm_a_t = LayerNorm(channel_a, create_offset=False)
+            self.layernorm_a_endpoint = LayerNorm(channel_a, create_offset=False)
+            self.endpoint_fusion = LinearNoBias(channel_a * 2, channel_a)
         self.layernorm_s = LayerNorm(channel_s, create_offset=False)
         self.linear_s_to_a = LinearNoBias(channel_s, channel_a)
         self.layernorm_z = LayerNorm(channel_z, create_offset=False)
@@ -1000,6 +1011,8 @@ class DiffusionStack(nn.Module):
         self.token_transformer.reset_caches()
         self.atom_attention_encoder.transformer.reset_caches()
         self.atom_attention_decoder.transformer.reset_caches()
+        if self.separate_endpoint_atom_encoder:
+            self.endpoint_atom_attention_encoder.transformer.reset_caches()
 
     @staticmethod
     def check() -> None:
@@ -1016,18 +1029,32 @@ class DiffusionStack(nn.Module):
     @torch.compiler.disable
     def step(self, r_noisy: torch.Tensor, q: torch.Tensor, c: torch.Tensor, p: torch.Tensor, token_index: torch.Tensor,
              atom_mask: torch.Tensor, s: torch.Tensor, pair_bias: torch.Tensor, token_mask: torch.Tensor) -> torch.Tensor:
-        """r_noisy (B, N, La, 3); q, c (B, La, c_atom); p (B, W, 32, 128, c_atompair); token_index, atom_mask (B, La);
+        """r_noisy (B, N, La, channel_coords); q, c (B, La, c_atom); p (B, W, 32, 128, c_atompair); token_index, atom_mask (B, La);
         s (B, N, Lt, c_s); pair_bias (B, Nblock, H, Lt, Lt); token_mask (B, Lt) -> float32 position updates (B, N, La, 3)."""
         _check_inference(r_noisy)
         q, c, p = q.unsqueeze(-3), c.unsqueeze(-3), p.unsqueeze(-5)
         atom_mask, token_mask, token_index = atom_mask.unsqueeze(-2), token_mask.unsqueeze(-2), token_index.unsqueeze(-2)
-        a, q_skip, c_skip, p_skip = self.atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1],
-                                                                r_noisy=r_noisy, mask_coords=True)
+        if self.separate_endpoint_atom_encoder:
+            r_t, r_T = r_noisy[..., :3].contiguous(), r_noisy[..., 3:].contiguous()
+            a, q_skip, c_skip, p_skip = self.atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1],
+                                                                    r_noisy=r_t, mask_coords=True)
+            a_e, _, _, _ = self.endpoint_atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1],
+                                                                r_noisy=r_T, mask_coords=True)
+            with torch.autocast(a.device.type, enabled=False):
+                lt, le = self.layernorm_a_t, self.layernorm_a_endpoint
+                cat = torch.cat((F.layer_norm(a, lt.weight, lt.bias, lt.eps), F.layer_norm(a_e, le.weight, le.bias, le.eps)), dim=-1)
+                a = F.linear_fp32(cat.float(), self._proj.get(self.endpoint_fusion, a.device, True), None)
+        else:
+            a, q_skip, c_skip, p_skip = self.atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1],
+                                                                    r_noisy=r_noisy, mask_coords=True)
         ln = self.layernorm_s
         with torch.autocast(a.device.type, enabled=False):
             # a.float() + linear_s_to_a(layernorm_s(s)): a float32 Linear in the reference whatever the autocast state
-            a = F.ln_linear_fp32(s.float(), ln.weight, ln.bias, self._proj.get(self.linear_s_to_a, a.device, True), None,
-                                 resid=a.float(), eps=ln.eps)
+            w_sa = self._proj.get(self.linear_s_to_a, a.device, True)
+            if s.shape[-3] == a.shape[-3]:
+                a = F.ln_linear_fp32(s.float(), ln.weight, ln.bias, w_sa, None, resid=a.float(), eps=ln.eps)
+            else:       # one conditioning row shared by the samples (the sampler's form): project once, add to every sample
+                a = a.float() + F.ln_linear_fp32(s.float(), ln.weight, ln.bias, w_sa, None, eps=ln.eps)
         a = self.token_transformer(a, s, pair_bias.unsqueeze(-5), token_mask)
         a = self.layernorm_a(a)
         return self.atom_attention_decoder(a, q_skip, c_skip, p_skip, token_index, atom_mask, mask_out=True)

@@ -375,12 +375,24 @@ def single_conditioning(s_inputs, c_noise, w: dict, mode: str = "fp32"):
 
 def diffusion_step(r_noisy, q, c, p, token_index, atom_mask, s, pair_bias, token_mask, w: dict, atom_heads: int,
                    atom_blocks: int, token_heads: int, token_blocks: int, mode: str = "fp32"):
-    """``DiffusionStack.step`` -- model/layers/folding/diffusion.py:465-600 (the plain, single-encoder variant)."""
+    """``DiffusionStack.step`` -- model/layers/folding/diffusion.py:465-600.  With ``endpoint_atom_attention_encoder.*``
+    among the weights this is the separate-endpoint variant (:521-550): the six coordinate channels split between two atom
+    encoders, whose token streams are normalised, concatenated and fused by a float32 Linear."""
+    m = _Mode(mode)
     q, c, p = q.unsqueeze(-3), c.unsqueeze(-3), p.unsqueeze(-5)
     atom_mask, token_mask, token_index = atom_mask.unsqueeze(-2), token_mask.unsqueeze(-2), token_index.unsqueeze(-2)
     r_noisy = r_noisy * atom_mask[..., None]
-    a, q_skip = atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1], r_noisy,
-                                       sub(w, "atom_attention_encoder"), atom_heads, atom_blocks, mode)
+    if "endpoint_fusion.weight" in w:
+        a, q_skip = atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1], r_noisy[..., :3],
+                                           sub(w, "atom_attention_encoder"), atom_heads, atom_blocks, mode)
+        a_e, _ = atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1], r_noisy[..., 3:],
+                                        sub(w, "endpoint_atom_attention_encoder"), atom_heads, atom_blocks, mode)
+        cat = torch.cat((layer_norm(a, w["layernorm_a_t.weight"], None, 1e-5, mode),
+                         layer_norm(a_e, w["layernorm_a_endpoint.weight"], None, 1e-5, mode)), dim=-1)
+        a = F.linear(cat.float(), w["endpoint_fusion.weight"].float())      # a float32 Linear whatever the autocast state
+    else:
+        a, q_skip = atom_attention_encoder(q, c, p, token_index, atom_mask, token_mask.shape[-1], r_noisy,
+                                           sub(w, "atom_attention_encoder"), atom_heads, atom_blocks, mode)
     sn = F.layer_norm(s.float(), (s.shape[-1],), w["layernorm_s.weight"].float(), None, 1e-5)
     a = a.float() + F.linear(sn, w["linear_s_to_a.weight"].float())
     a = global_transformer_stack(a, s, pair_bias.unsqueeze(-5), token_mask, sub(w, "token_transformer"), token_heads, token_blocks,

@@ -60,6 +60,16 @@ CASES = {
     # DiffusionStack.step: encoder (2 blocks) -> token transformer (2 blocks) -> decoder (2 blocks); 24 tokens, 96 atoms, 2 samples
     "diffusion_step": dict(kind="diffusion_step", seed=50, tokens=24, atoms=96, c_a=256, c_s=384, c_z=128, c_atom=128, c_pair=16,
                            atom_blocks=2, atom_heads=4, token_blocks=2, token_heads=8, samples=2, valid_atoms=90, valid_tokens=23),
+    # the production form of the step (configs/kfold.yaml:61-76): six coordinate channels [c_in x_t | x_T / sigma_T], split
+    # between two atom encoders whose token streams are normalised, concatenated and fused by a float32 Linear
+    "diffusion_step_sep": dict(kind="diffusion_step", seed=52, tokens=24, atoms=96, c_a=256, c_s=384, c_z=128, c_atom=128, c_pair=16,
+                               atom_blocks=2, atom_heads=4, token_blocks=2, token_heads=8, samples=2, valid_atoms=90, valid_tokens=23,
+                               coords=6, separate_endpoint=True),
+    # the sampler loop around the step (model/modules/ecsi.py:498-560): 6 steps, 2 samples, 16 tokens, 64 atoms, every normal
+    # draw taken from a tape (seed in `tape`): steps 0-2 churn + ECSI SDE, step 3 SDE, steps 4-5 SI ODE
+    "sampler_small": dict(kind="sampler", seed=53, tape=5301, tokens=16, atoms=64, priors=2, c_a=256, c_s=384, c_z=128, c_atom=128,
+                          c_pair=16, atom_blocks=1, atom_heads=4, token_blocks=2, token_heads=8, samples=2, steps=6, valid_atoms=60,
+                          valid_tokens=15, coords=6),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: benchmark config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -147,8 +157,9 @@ def build_inputs(name: str) -> dict:
     elif kind == "diffusion_step":
         nt, na, ns = cs["tokens"], cs["atoms"], cs["samples"]
         out["w"] = synth.diffusion_step_weights(rng, cs["c_a"], cs["c_s"], cs["c_atom"], cs["c_pair"], cs["atom_blocks"],
-                                                cs["atom_heads"], cs["token_blocks"], cs["token_heads"])
-        out["r_noisy"] = rng.normal(1, ns, na, 3) * 4.0
+                                                cs["atom_heads"], cs["token_blocks"], cs["token_heads"], cs.get("coords", 3),
+                                                cs.get("separate_endpoint", False))
+        out["r_noisy"] = rng.normal(1, ns, na, cs.get("coords", 3)) * 4.0
         out["q"], out["c"] = rng.normal(1, na, cs["c_atom"]), rng.normal(1, na, cs["c_atom"])
         out["p"] = rng.normal(1, na // 32, 32, 128, cs["c_pair"])
         out["token_index"] = torch.from_numpy(np.sort(rng.rs.randint(0, cs["valid_tokens"], size=na)).astype(np.int64)).view(1, na)
@@ -156,6 +167,23 @@ def build_inputs(name: str) -> dict:
         out["s"] = rng.normal(1, ns, nt, cs["c_s"])
         out["pair_bias"] = rng.normal(1, cs["token_blocks"], cs["token_heads"], nt, nt)
         out["token_mask"] = synth.token_mask(nt, cs["valid_tokens"]).view(1, nt)
+    elif kind == "sampler":
+        nt, na = cs["tokens"], cs["atoms"]
+        out["w"] = synth.diffusion_step_weights(rng, cs["c_a"], cs["c_s"], cs["c_atom"], cs["c_pair"], cs["atom_blocks"],
+                                                cs["atom_heads"], cs["token_blocks"], cs["token_heads"], cs["coords"], False)
+        out["w"].update(synth._prefixed("single_conditioning", synth.single_conditioning_weights(rng, cs["c_s"], 256)))
+        out["x_apo"] = rng.normal(1, cs["priors"], na, 3) * 8.0                       # (B, Nprior, La, 3)
+        out["s_inputs"] = rng.normal(1, nt, cs["c_s"])
+        out["z"] = rng.normal(1, nt, nt, cs["c_z"])
+        out["token_index"] = torch.from_numpy(np.sort(rng.rs.randint(0, cs["valid_tokens"], size=na)).astype(np.int64)).view(1, na)
+        out["atom_mask"] = synth.token_mask(na, cs["valid_atoms"]).view(1, na)
+        out["token_mask"] = synth.token_mask(nt, cs["valid_tokens"]).view(1, nt)
+        # the remaining fields of the duck-typed FoldingInput the reference's embedders read (reference-side only)
+        out["ref_pos"] = rng.normal(1, na, 3) * 2.0
+        out["ref_charge"] = torch.from_numpy(rng.rs.randint(-1, 2, size=(1, na)).astype(np.float32))
+        out["ref_element"] = torch.nn.functional.one_hot(torch.from_numpy(rng.rs.randint(0, 20, size=(1, na))), 128).float()
+        out["ref_atom_name_chars"] = torch.nn.functional.one_hot(torch.from_numpy(rng.rs.randint(0, 64, size=(1, na, 4))), 64).float()
+        out["ref_space_uid"] = out["token_index"].clone()
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

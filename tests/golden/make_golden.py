@@ -103,7 +103,9 @@ def run_reference(ns, name: str) -> dict:
         import importlib
         df = importlib.import_module("kfold.model.layers.folding.diffusion")
         mod = df.DiffusionStack(channel_a=cs["c_a"], channel_s=cs["c_s"], channel_z=cs["c_z"], channel_atom=cs["c_atom"],
-                                channel_atompair=cs["c_pair"], atom_encoder_blocks=cs["atom_blocks"],
+                                channel_atompair=cs["c_pair"], channel_coords=cs.get("coords", 3),
+                                separate_endpoint_atom_encoder=cs.get("separate_endpoint", False),
+                                atom_encoder_blocks=cs["atom_blocks"],
                                 atom_encoder_heads=cs["atom_heads"], token_transformer_blocks=cs["token_blocks"],
                                 token_transformer_heads=cs["token_heads"], atom_decoder_blocks=cs["atom_blocks"],
                                 atom_decoder_heads=cs["atom_heads"], kernel_backend="torch")
@@ -115,6 +117,8 @@ def run_reference(ns, name: str) -> dict:
                 m.kernel_backend = "torch"      # the oracle path; the constructors hard-code "sdpa"
         return {"out": mod.step(inp["r_noisy"], inp["q"], inp["c"], inp["p"], inp["token_index"], inp["atom_mask"], inp["s"],
                                 inp["pair_bias"], inp["token_mask"])}
+    if kind == "sampler":
+        return run_reference_sampler(inp)
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "tri_block":
@@ -131,6 +135,76 @@ def run_reference(ns, name: str) -> dict:
             res["z"] = z
         return res
     raise ValueError(kind)
+
+
+class _TapeRandn:
+    """Stands in for torch.randn / torch.randn_like while the reference sampler runs: every draw comes from the tape."""
+
+    def __init__(self, tape):
+        self.tape = tape
+
+    def randn(self, *size, dtype=None, device=None, generator=None, **kw):
+        if len(size) == 1 and isinstance(size[0], (tuple, list, torch.Size)):
+            size = tuple(size[0])
+        return self.tape.randn(size).to(dtype or torch.float32)
+
+    def randn_like(self, t, **kw):
+        return self.tape.randn(tuple(t.shape)).to(t.dtype)
+
+
+@torch.no_grad()
+def run_reference_sampler(inp: dict) -> dict:
+    """``KFoldECSI.sample_structure`` (model/modules/ecsi.py:468-560) of the real reference on a duck-typed FoldingInput,
+    its normal draws taken from a NoiseTape.  Stored besides the final coordinates: what the time-independent precompute
+    of the reference (pair conditioning, atom embedder -- not part of the accelerated path) hands to the loop."""
+    import importlib
+    import types
+
+    from oracle.sampler_oracle import NoiseTape
+    cs = inp["case"]
+    sm = importlib.import_module("kfold.model.modules.score_model")
+    ecsi = importlib.import_module("kfold.model.modules.ecsi")
+    cfg = sm.DiffusionModule.Config(channel_a=cs["c_a"], channel_s=cs["c_s"], channel_z=cs["c_z"], channel_atom=cs["c_atom"],
+                                    channel_atompair=cs["c_pair"], channel_coords=cs["coords"],
+                                    atom_encoder_blocks=cs["atom_blocks"], atom_encoder_heads=cs["atom_heads"],
+                                    token_transformer_blocks=cs["token_blocks"], token_transformer_heads=cs["token_heads"],
+                                    atom_decoder_blocks=cs["atom_blocks"], atom_decoder_heads=cs["atom_heads"])
+    model = sm.DiffusionModule(cfg, kernel_backend="torch")
+    # the reference-only parts (pair conditioning, atom embedder) get seeded random weights: zero-initialised ones would
+    # make their outputs trivial
+    rs = np.random.RandomState(cs["seed"] + 1000)
+    for name, prm in sorted(model.named_parameters()):
+        if prm.dim() >= 2:
+            prm.copy_(torch.from_numpy((rs.standard_normal(tuple(prm.shape)) * prm.shape[-1] ** -0.5).astype(np.float32)))
+    missing, unexpected = model.diffusion_stack.load_state_dict(inp["w"], strict=False)
+    assert not unexpected, unexpected
+    model.eval()
+    for m in model.modules():
+        if getattr(m, "kernel_backend", None) == "sdpa":
+            m.kernel_backend = "torch"
+    atom = types.SimpleNamespace(pad_mask=inp["atom_mask"], token_index=inp["token_index"],
+                                 prior_coords=inp["x_apo"].permute(0, 2, 1, 3).contiguous(), ref_pos=inp["ref_pos"],
+                                 ref_charge=inp["ref_charge"], ref_element=inp["ref_element"],
+                                 ref_atom_name_chars=inp["ref_atom_name_chars"], ref_space_uid=inp["ref_space_uid"])
+    nt = cs["tokens"]
+    ar = torch.arange(nt).view(1, nt)
+    token = types.SimpleNamespace(pad_mask=inp["token_mask"], asym_id=torch.zeros(1, nt, dtype=torch.long),
+                                  entity_id=torch.zeros(1, nt, dtype=torch.long), sym_id=torch.zeros(1, nt, dtype=torch.long),
+                                  residue_index=ar.clone(), token_index=ar.clone())
+    f_input = types.SimpleNamespace(atom=atom, token=token, num_atoms=cs["atoms"], device=torch.device("cpu"))
+    z_cond = model.get_pair_conditioning(f_input, inp["z"])
+    q, c, p = model.get_atom_embeddings(f_input, z_cond)
+    pair_bias = model.get_pair_bias(z_cond)
+    sampler = ecsi.KFoldECSI(ecsi.KFoldECSI.Config(), model)
+    stand_in = _TapeRandn(NoiseTape(cs["tape"]))
+    real_randn, real_randn_like = torch.randn, torch.randn_like
+    torch.randn, torch.randn_like = stand_in.randn, stand_in.randn_like
+    try:
+        out = sampler.sample_structure(f_input, inp["s_inputs"], inp["z"], num_steps=cs["steps"], num_samples=cs["samples"])
+    finally:
+        torch.randn, torch.randn_like = real_randn, real_randn_like
+    return {"q": q, "c": c, "p": p, "pair_bias": pair_bias, "x_T": out["init_coordinates"], "coordinates": out["coordinates"],
+            "draws": torch.tensor([stand_in.tape.calls])}
 
 
 def _thin(res: dict) -> dict:

@@ -125,11 +125,12 @@ def local_stack_weights(rng: _Rng, c_a: int, c_s: int, c_z: int, heads: int, blo
     return w
 
 
-def atom_encoder_weights(rng: _Rng, c_atom: int, c_pair: int, c_token: int, heads: int, blocks: int, use_structure: bool) -> dict:
+def atom_encoder_weights(rng: _Rng, c_atom: int, c_pair: int, c_token: int, heads: int, blocks: int, use_structure: bool,
+                         c_coords: int = 3) -> dict:
     """AtomAttentionEncoder (model/layers/folding/atom_transformer.py:263-309)."""
     w = {}
     if use_structure:
-        w["linear_r_to_q.weight"] = rng.linear(c_atom, 3)
+        w["linear_r_to_q.weight"] = rng.linear(c_atom, c_coords)
     w.update(_prefixed("transformer", local_stack_weights(rng, c_atom, c_atom, c_pair, heads, blocks)))
     w["linear_q_to_a.weight"] = rng.linear(c_token, c_atom)
     return w
@@ -154,10 +155,12 @@ def single_conditioning_weights(rng: _Rng, c_s: int, dim_fourier: int) -> dict:
 
 
 def diffusion_step_weights(rng: _Rng, c_a: int, c_s: int, c_atom: int, c_pair: int, atom_blocks: int, atom_heads: int,
-                           token_blocks: int, token_heads: int) -> dict:
+                           token_blocks: int, token_heads: int, c_coords: int = 3, separate_endpoint: bool = False) -> dict:
     """The parameters DiffusionStack.step touches (model/layers/folding/diffusion.py:250-325): atom attention encoder and
-    decoder, layernorm_s / linear_s_to_a, the token transformer, layernorm_a."""
-    w = _prefixed("atom_attention_encoder", atom_encoder_weights(rng, c_atom, c_pair, c_a, atom_heads, atom_blocks, True))
+    decoder, layernorm_s / linear_s_to_a, the token transformer, layernorm_a; with ``separate_endpoint`` also the second
+    encoder for the prior coordinates and the fusion of the two token streams (:254-279)."""
+    enc_coords = 3 if separate_endpoint else c_coords
+    w = _prefixed("atom_attention_encoder", atom_encoder_weights(rng, c_atom, c_pair, c_a, atom_heads, atom_blocks, True, enc_coords))
     w["layernorm_s.weight"] = rng.ln_w(c_s)
     w["linear_s_to_a.weight"] = rng.linear(c_a, c_s)
     for i in range(token_blocks):
@@ -165,6 +168,12 @@ def diffusion_step_weights(rng: _Rng, c_a: int, c_s: int, c_atom: int, c_pair: i
         w.update(_prefixed(f"token_transformer.blocks.{i}.transition", conditioned_transition_weights(rng, c_a, c_s)))
     w["layernorm_a.weight"] = rng.ln_w(c_a)
     w.update(_prefixed("atom_attention_decoder", atom_decoder_weights(rng, c_a, c_atom, c_pair, atom_heads, atom_blocks)))
+    if separate_endpoint:
+        w.update(_prefixed("endpoint_atom_attention_encoder",
+                           atom_encoder_weights(rng, c_atom, c_pair, c_a, atom_heads, atom_blocks, True, 3)))
+        w["layernorm_a_t.weight"] = rng.ln_w(c_a)
+        w["layernorm_a_endpoint.weight"] = rng.ln_w(c_a)
+        w["endpoint_fusion.weight"] = rng.linear(c_a, 2 * c_a)
     return w
 
 

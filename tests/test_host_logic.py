@@ -229,8 +229,14 @@ def test_index_sharing_patterns():
 
 def test_modules_refuse_what_they_do_not_cover():
     from kfold_b200 import modules as M
-    with pytest.raises(NotImplementedError):
-        M.DiffusionStack(separate_endpoint_atom_encoder=True, token_transformer_blocks=1)
+    with pytest.raises(ValueError):
+        M.DiffusionStack(separate_endpoint_atom_encoder=True, token_transformer_blocks=1)      # needs channel_coords=6
+    sep = M.DiffusionStack(channel_a=64, channel_s=32, channel_z=32, channel_atom=32, channel_atompair=16, channel_coords=6,
+                           separate_endpoint_atom_encoder=True, atom_encoder_blocks=1, atom_encoder_heads=2,
+                           token_transformer_blocks=1, token_transformer_heads=2, atom_decoder_blocks=1, atom_decoder_heads=2)
+    assert {"endpoint_fusion.weight", "layernorm_a_t.weight", "layernorm_a_endpoint.weight",
+            "endpoint_atom_attention_encoder.linear_r_to_q.weight"} <= set(sep.state_dict())
+    assert sep.atom_attention_encoder.linear_r_to_q.weight.shape == (32, 3)
     with pytest.raises(ValueError):
         M.CrossAttentionPairBias(128, 4, 128, inf=1e6)
     with pytest.raises(ValueError):

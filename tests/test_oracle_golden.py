@@ -45,6 +45,16 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
         return {"out": O.diffusion_step(inp["r_noisy"], inp["q"], inp["c"], inp["p"], inp["token_index"], inp["atom_mask"], inp["s"],
                                         inp["pair_bias"], inp["token_mask"], w, cs["atom_heads"], cs["atom_blocks"],
                                         cs["token_heads"], cs["token_blocks"], mode)}
+    if kind == "sampler":
+        from oracle import sampler_oracle as SO
+        gold = load_golden(name)
+        step = SO.diffusion_step_fn(gold["q"], gold["c"], gold["p"], inp["token_index"], inp["atom_mask"], gold["pair_bias"],
+                                    inp["token_mask"], w, cs["atom_heads"], cs["atom_blocks"], cs["token_heads"],
+                                    cs["token_blocks"], mode)
+        tape = SO.NoiseTape(cs["tape"])
+        x_T, x = SO.sample_loop(inp["x_apo"], inp["atom_mask"], step, inp["s_inputs"], cs["steps"], cs["samples"], tape,
+                                single_conditioning=lambda s_in, cn: O.single_conditioning(s_in, cn, O.sub(w, "single_conditioning"), mode))
+        return {"x_T": x_T, "coordinates": x, "draws": torch.tensor([tape.calls])}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "tri_block":
@@ -64,6 +74,13 @@ def test_oracle_matches_reference_golden(name):
         assert compare_pair_output(got["z"], gold, "z")[0] < 5 * FP32_TOL
         zs = float(got["z"].double().sum())
         assert abs(zs - float(gold["z_sum"])) <= 1e-3 * float(gold["z_sumsq"]) ** 0.5
+    elif cases.CASES[name]["kind"] == "sampler":
+        # same tape, same number of draws, same coordinates: the restated loop consumes the normals in the reference's order
+        assert int(got["draws"]) == int(gold["draws"])
+        assert err_stats(got["x_T"], gold["x_T"])[0] < FP32_TOL
+        d = (got["coordinates"] - gold["coordinates"]).pow(2).sum(-1)
+        rmsd = float(d.mean().sqrt())
+        assert rmsd < 1e-3, f"sampler: coordinate RMSD {rmsd:.3e} A between the oracle and the reference"
     elif cases.CASES[name]["kind"] == "atom_encoder":
         assert err_stats(got["a"], gold["a"])[0] < FP32_TOL and err_stats(got["q_skip"], gold["q_skip"])[0] < FP32_TOL
     elif cases.CASES[name]["kind"] == "atom_token_maps":
