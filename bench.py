@@ -564,6 +564,64 @@ def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
     return res
 
 
+def measure_sampler(rank: int, world: int, dev, barrier, steps: int = 200, samples: int = 5) -> dict:
+    """Benchmark config 4's diffusion part: the 200-step ECSI sampler (kfold_b200.sampler.KFoldECSI.sample_structure) over
+    5 samples of a 768-token, 6 016-atom complex, score network = atom encoder (3 blocks), 24-block token transformer
+    (c=768, 16 heads), atom decoder (3 blocks), bf16 compute, the network replayed as a CUDA graph.  With several ranks
+    every rank samples its own seed (the data-parallel form of config 5); the time is the maximum over the ranks."""
+    import types
+
+    import numpy as np
+    import torch.distributed as dist
+    from kfold_b200 import _lib as L
+    from kfold_b200 import modules as M
+    from kfold_b200.sampler import KFoldECSI
+    import synth
+    nt, na = N_TOKENS_DEFAULT, 6016
+    c_a, c_s, c_atom, c_pair, tb, th = 768, 384, 128, 16, 24, 16
+    rng = synth._Rng(SEED)
+    w = synth.diffusion_step_weights(rng, c_a, c_s, c_atom, c_pair, 3, 4, tb, th, 6, False)
+    w.update(synth._prefixed("single_conditioning", synth.single_conditioning_weights(rng, c_s, 256)))
+    mod = M.DiffusionStack(channel_a=c_a, channel_s=c_s, channel_z=C_Z, channel_atom=c_atom, channel_atompair=c_pair, channel_coords=6,
+                           token_transformer_blocks=tb, token_transformer_heads=th).to(dev)
+    mod.load_state_dict(w, strict=False)
+    pre = {"q": rng.normal(1, na, c_atom).to(dev), "c": rng.normal(1, na, c_atom).to(dev),
+           "p": rng.normal(1, na // 32, 32, 128, c_pair).to(dev),
+           "pair_bias": rng.normal(1, tb, th, nt, nt).to(dev, torch.bfloat16)}
+    token_index = torch.from_numpy(np.sort(rng.rs.randint(0, nt, size=na)).astype(np.int64)).view(1, na).to(dev)
+    atom = types.SimpleNamespace(pad_mask=synth.token_mask(na, pad_frac=0.02).view(1, na).to(dev), token_index=token_index,
+                                 prior_coords=(rng.normal(1, na, 1, 3) * 10.0).to(dev))
+    f_input = types.SimpleNamespace(atom=atom, token=types.SimpleNamespace(pad_mask=synth.token_mask(nt, pad_frac=PAD_FRAC).view(1, nt).to(dev)))
+    s_inputs = rng.normal(1, nt, c_s).to(dev)
+    sampler = KFoldECSI(KFoldECSI.Config(), mod)
+    stream = torch.cuda.current_stream()
+    res = {}
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        torch.manual_seed(SEED + rank)
+        sampler.sample_structure(f_input, s_inputs, None, num_steps=4, num_samples=samples, precomputed=pre, cuda_graph=True)   # warm-up
+        barrier()
+        launches0 = L.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        out = sampler.sample_structure(f_input, s_inputs, None, num_steps=steps, num_samples=samples, precomputed=pre, cuda_graph=True)
+        e1.record(stream)
+        barrier()
+        wall = time.perf_counter() - t0
+        ms = e0.elapsed_time(e1)
+        finite = bool(torch.isfinite(out["coordinates"]).all())
+    if world > 1:
+        t = torch.tensor([ms, wall], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, wall = float(t[0]), float(t[1])
+    res.update(steps=steps, samples=samples, tokens=nt, atoms=na, seconds=round(ms / 1e3, 4), ms_per_step=round(ms / steps, 3),
+               wall_seconds=round(wall, 4), structures_per_s=round(world * samples / (ms / 1e3), 3), seeds=world, finite=finite,
+               device_status=L.device_status(),
+               note="eager launches counted by the library (the graph-replayed network launches are not): "
+                    f"{L.launch_count() - launches0}; includes the one-off graph capture of the network")
+    return res
+
+
 def measure_sharded_parity(rank: int, world: int, dev, blk, w) -> dict:
     """The row-sharded block at N=512 on the ranks of this run, both exchange forms, against (i) the one-GPU block on
     the same rank and (ii) the oracle run on this GPU in float32 (the checker; TF32 off).  Relative RMS errors, maximum
@@ -650,6 +708,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         s_out_host.copy_(so, non_blocking=True)
 
     trunk = None
+    sampler_run = None
     sharded_n2048 = None
     parity = None
     with torch.no_grad():
@@ -713,6 +772,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                      "ms_x_sm_mhz": round(ms_trunk * tclocks["sm_mhz"], 1) if tclocks.get("sm_mhz") else None}
             del zt
             # ---- benchmark config 5's block: N=2048, row-sharded over the ranks of this run (plain block with one rank)
+            sampler_run = measure_sampler(rank, world, dev, barrier)
             sharded_n2048 = measure_sharded(args, rank, world, dev, blk, barrier)
             if world > 1:
                 parity = measure_sharded_parity(rank, world, dev, blk, w)
@@ -778,6 +838,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "e2e": {"value": ms_e2e / world, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
             "trunk48_ms": None if trunk is None else trunk["ms"], "trunk48": trunk,
+            "sampler_200x5": sampler_run,
+            "config4_s": None if trunk is None or sampler_run is None else round(trunk["ms"] / 1e3 + sampler_run["seconds"], 4),
             "sharded_n2048": sharded_n2048, "sharded_parity": parity, "kernels": kernels,
         }
         if trunk is not None and trunk["clocks"].get("sm_mhz"):

@@ -346,6 +346,47 @@ KFB_API int kfb_fourier_embed(const float* t, const float* w, const float* b, fl
 KFB_API int kfb_broadcast_add(const float* s, const float* f, float* out, int groups, int samples, int l, int c, void* stream);
 
 /*
+ * Callers of the pair stacks in the trunk (src/kfold/model/model.py:477-534).
+ *   kfb_parcae_fwd replaces the recurrence between recycling iterations, `z = a * z + F.linear(self.layernorm_z(u_t), b)`
+ *     (model.py:528): out = a (per channel) * z + LayerNorm(u) b^T.  z, u, out : (rows, c) of `dtype` (KFB_BF16 or KFB_FP32;
+ *     bf16 arithmetic, fp32 accumulation -- the reference casts a and b to the autocast dtype, model.py:505);
+ *     a : fp32 [c];  b_w : bf16 [c, c];  ln_w / ln_b : fp32 [c] or NULL.  out may equal z.
+ *   kfb_lm_pair_features replaces `torch.cat([xi * xj, xi - xj], dim=-1)` of LMToPair.forward (model.py:128-131):
+ *     x (batch, n, 2 d) of `dtype` = [xi | xj] per token -> out bf16 (batch, n, n, 2 d).
+ *   kfb_gelu replaces torch.nn.GELU() (erf form) inside LMToPair's MLP (model.py:120-124), element-wise.
+ */
+KFB_API size_t kfb_parcae_workspace_bytes(long long rows, int c);
+KFB_API int kfb_parcae_fwd(const void* z, const void* u, const float* ln_w, const float* ln_b, const float* a, const void* b_w,
+                           void* out, void* workspace, size_t workspace_bytes, long long rows, int c, float eps, int dtype,
+                           void* stream);
+KFB_API int kfb_lm_pair_features(const void* x, void* out, int batch, int n, int d, int dtype, void* stream);
+KFB_API int kfb_gelu(const void* x, void* y, long long n, int in_dtype, int out_dtype, void* stream);
+
+/*
+ * Pair conditioning of the diffusion module (src/kfold/model/layers/folding/diffusion.py:84-90): replaces
+ * `self.layernorm(torch.cat([z, rel_pos_feats], dim=-1))` in one pass.  z (rows, c1) of z_dtype, rel (rows, c2) of rel_dtype
+ * (KFB_BF16 or KFB_FP32 each) -> out fp32 (rows, k_pad): LayerNorm over the c1 + c2 concatenated channels (ln_w / ln_b fp32
+ * [c1 + c2] or NULL), columns c1 + c2 .. k_pad - 1 zero so that the row feeds kfb_linear_fp32 (K a multiple of 8).
+ * k_pad <= 512.
+ */
+KFB_API int kfb_concat_layernorm(const void* z, int z_dtype, const void* rel, int rel_dtype, const float* ln_w, const float* ln_b,
+                                 float* out, long long rows, int c1, int c2, int k_pad, float eps, void* stream);
+
+/*
+ * Pair-tensor preparation of the confidence head (src/kfold/model/modules/confidence_head.py:306-470).
+ *   kfb_pair_outer_add replaces `z + self.linear_s1(s_inputs)[..., None, :, :] + self.linear_s2(s_inputs)[..., :, None, :]`
+ *     (:347-351): out[b, i, j, :] = z[b, i, j, :] + row_add[b, j, :] + col_add[b, i, :];  z, out (batch, n, n, c), row_add and
+ *     col_add (batch, n, c), all of `dtype`; c a multiple of 4.
+ *   kfb_distogram_embed_add replaces the distogram embedding of forward_single (:449-455): out = z + w_t[bin(|x_i - x_j|)],
+ *     bin = the number of `boundaries` (fp32, ascending) below the distance;  x fp32 (batch, n, 3), w_t (n_boundaries + 1, c)
+ *     = linear_distogram.weight transposed, of `dtype` like z and out.
+ */
+KFB_API int kfb_pair_outer_add(const void* z, const void* row_add, const void* col_add, void* out, int batch, int n, int c, int dtype,
+                               void* stream);
+KFB_API int kfb_distogram_embed_add(const void* z, const float* x, const float* boundaries, int n_boundaries, const void* w_t, void* out,
+                                    int batch, int n, int c, int dtype, void* stream);
+
+/*
  * The coordinate-space steps of the sampler loop around the score network, KFoldECSI.sample_structure
  * (src/kfold/model/modules/ecsi.py:498-560).  A coordinate set is one diffusion sample of one complex: l atoms x 3 fp32,
  * contiguous; the n sets of a call are ordered (complex, sample) and `mask_div` consecutive sets share one row of the

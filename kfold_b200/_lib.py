@@ -69,6 +69,13 @@ _SIGNATURES = {
                            c_ll, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_pair_bias_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int, c_int,
                           c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_parcae_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll, c_int,
+                       c_float, c_int, c_void_p],
+    "kfb_lm_pair_features": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
+    "kfb_concat_layernorm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_void_p],
+    "kfb_pair_outer_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_distogram_embed_add": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_coords_augment": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "kfb_sampler_prepare": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float, c_float, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_void_p],
@@ -98,6 +105,7 @@ _SIZE_FUNCS = {
     "kfb_apb_window_workspace_bytes": [c_int, c_int, c_int, c_int],
     "kfb_apb_cross_workspace_bytes_precise": [c_int, c_int, c_int, c_int],
     "kfb_trimul_workspace_bytes": [c_int, c_int, c_int],
+    "kfb_parcae_workspace_bytes": [c_ll, c_int],
 }
 
 

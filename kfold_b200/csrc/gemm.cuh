@@ -77,6 +77,8 @@ struct GemmParams {
   int aux_gate, aux_resid;        // which of the two the prefetch covers
   long long* trace;               // debugging aid: CTA 0 stores clock64() stamps per tile here when non-null
   const void* resid;              // optional: seg 0 value += resid[...] (same dtype and strides as seg 0 dst)
+  const float* resid_scale;       // optional, per output column: seg 0 value += resid_scale[col] * resid[...] instead
+                                  // (the state decay of the trunk's recurrence, z <- a * z + Linear(...))
 };
 
 static constexpr int kBM = 128;
@@ -652,10 +654,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int q = 0; q < 4; ++q) {
               const uint4 u = *reinterpret_cast<const uint4*>(rrow + (((cbase + q) ^ (r & 7)) << 4));
               const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+              if (p.resid_scale != nullptr) {
+                const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.resid_scale + out_col + q * 8));
+                const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.resid_scale + out_col + q * 8 + 4));
+                const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                v[q * 8 + j * 2] += __uint_as_float(w[j] << 16);
-                v[q * 8 + j * 2 + 1] += __uint_as_float(w[j] & 0xffff0000u);
+                for (int j = 0; j < 4; ++j) {
+                  v[q * 8 + j * 2] = fmaf(__uint_as_float(w[j] << 16), sc[j * 2], v[q * 8 + j * 2]);
+                  v[q * 8 + j * 2 + 1] = fmaf(__uint_as_float(w[j] & 0xffff0000u), sc[j * 2 + 1], v[q * 8 + j * 2 + 1]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[q * 8 + j * 2] += __uint_as_float(w[j] << 16);
+                  v[q * 8 + j * 2 + 1] += __uint_as_float(w[j] & 0xffff0000u);
+                }
               }
             }
           }
@@ -695,7 +708,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
                 const float4 f = rs[q];
-                v[q * 4] += f.x; v[q * 4 + 1] += f.y; v[q * 4 + 2] += f.z; v[q * 4 + 3] += f.w;
+                const float4 sc = p.resid_scale != nullptr ? __ldg(reinterpret_cast<const float4*>(p.resid_scale + out_col + q * 4))
+                                                           : make_float4(1.f, 1.f, 1.f, 1.f);
+                v[q * 4] = fmaf(f.x, sc.x, v[q * 4]); v[q * 4 + 1] = fmaf(f.y, sc.y, v[q * 4 + 1]);
+                v[q * 4 + 2] = fmaf(f.z, sc.z, v[q * 4 + 2]); v[q * 4 + 3] = fmaf(f.w, sc.w, v[q * 4 + 3]);
               }
             } else {
               const uint4* rs = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.resid) + row_off + col_local);
@@ -706,8 +722,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
-                  v[q * 8 + j * 2] += f.x;
-                  v[q * 8 + j * 2 + 1] += f.y;
+                  const float sx = p.resid_scale != nullptr ? __ldg(p.resid_scale + out_col + q * 8 + j * 2) : 1.0f;
+                  const float sy = p.resid_scale != nullptr ? __ldg(p.resid_scale + out_col + q * 8 + j * 2 + 1) : 1.0f;
+                  v[q * 8 + j * 2] = fmaf(f.x, sx, v[q * 8 + j * 2]);
+                  v[q * 8 + j * 2 + 1] = fmaf(f.y, sy, v[q * 8 + j * 2 + 1]);
                 }
               }
             }
@@ -716,13 +734,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               const float* rs = reinterpret_cast<const float*>(p.resid) + row_off + static_cast<long long>(col_local) * sg.s_col;
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (col_local + i < sg.ncols) v[i] += rs[static_cast<long long>(i) * sg.s_col];
+                if (col_local + i < sg.ncols)
+                  v[i] = fmaf(rs[static_cast<long long>(i) * sg.s_col], p.resid_scale != nullptr ? p.resid_scale[out_col + i] : 1.0f, v[i]);
             } else {
               const __nv_bfloat16* rs =
                   reinterpret_cast<const __nv_bfloat16*>(p.resid) + row_off + static_cast<long long>(col_local) * sg.s_col;
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (col_local + i < sg.ncols) v[i] += __bfloat162float(rs[static_cast<long long>(i) * sg.s_col]);
+                if (col_local + i < sg.ncols)
+                  v[i] = fmaf(__bfloat162float(rs[static_cast<long long>(i) * sg.s_col]),
+                              p.resid_scale != nullptr ? p.resid_scale[out_col + i] : 1.0f, v[i]);
             }
           }
         }

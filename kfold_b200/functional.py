@@ -808,3 +808,88 @@ def center_coords(coords: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
     with L.on_device(c.device):
         L.check(L.lib().kfb_center_coords(L.ptr(c), L.ptr(mk), L.ptr(out), n, l, div, L.stream_ptr()))
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# callers of the pair stacks in the trunk (model/model.py:477-534)
+# ------------------------------------------------------------------------------------------------
+def parcae_update(z: torch.Tensor, u: torch.Tensor, ln_w, ln_b, a: torch.Tensor, b_w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """a * z + Linear_b(LayerNorm(u)) (model/model.py:528): z, u (..., C) bf16 or float32; a float32 (C,); b_w bf16 (C, C)."""
+    _require_cuda(z, u, a, b_w)
+    c = z.shape[-1]
+    z2, u2 = z.reshape(-1, c).contiguous(), u.reshape(-1, c).to(z.dtype).contiguous()
+    out = torch.empty_like(z2)
+    f32 = lambda t: None if t is None else t.detach().float().contiguous()
+    lw, lb, af = f32(ln_w), f32(ln_b), f32(a)
+    lib = L.lib()
+    with L.on_device(z.device):
+        ws = _workspace(z.device, lib.kfb_parcae_workspace_bytes(z2.shape[0], c))
+        L.check(lib.kfb_parcae_fwd(L.ptr(z2), L.ptr(u2), L.ptr(lw), L.ptr(lb), L.ptr(af), L.ptr(b_w), L.ptr(out), L.ptr(ws), ws.numel(),
+                                   z2.shape[0], c, eps, L.dtype_code(z2.dtype), L.stream_ptr()))
+    return out.view(z.shape)
+
+
+def lm_pair_features(x: torch.Tensor) -> torch.Tensor:
+    """[xi * xj | xi - xj] for every token pair (model/model.py:128-131): x (B, L, 2 D) = [xi | xj] -> bf16 (B, L, L, 2 D)."""
+    _require_cuda(x)
+    b, n, d2 = x.shape
+    xc = x.contiguous()
+    out = torch.empty(b, n, n, d2, dtype=torch.bfloat16, device=x.device)
+    with L.on_device(x.device):
+        L.check(L.lib().kfb_lm_pair_features(L.ptr(xc), L.ptr(out), b, n, d2 // 2, L.dtype_code(xc.dtype), L.stream_ptr()))
+    return out
+
+
+def gelu(x: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """erf GELU, element-wise (torch.nn.GELU() of model/model.py:122)."""
+    _require_cuda(x)
+    xc = x.contiguous()
+    out = torch.empty(xc.shape, dtype=out_dtype or x.dtype, device=x.device)
+    with L.on_device(x.device):
+        L.check(L.lib().kfb_gelu(L.ptr(xc), L.ptr(out), xc.numel(), L.dtype_code(xc.dtype), L.dtype_code(out.dtype), L.stream_ptr()))
+    return out
+
+
+def concat_layer_norm(z: torch.Tensor, rel: torch.Tensor, ln_w, ln_b, k_pad: int, eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm(cat([z, rel], -1)) in one pass (model/layers/folding/diffusion.py:84-90): float32 (..., k_pad), the columns past
+    c_z + c_rel zero.  z and rel bf16 or float32, same leading shape."""
+    _require_cuda(z, rel)
+    if z.shape[:-1] != rel.shape[:-1]:
+        raise ValueError(f"concat_layer_norm: leading shapes {tuple(z.shape[:-1])} and {tuple(rel.shape[:-1])} differ")
+    c1, c2 = z.shape[-1], rel.shape[-1]
+    fix = lambda t: (t if t.dtype in (torch.bfloat16, torch.float32) else t.float()).contiguous()
+    zc, rc = fix(z), fix(rel)
+    f32 = lambda t: None if t is None else t.detach().float().contiguous()
+    lw, lb = f32(ln_w), f32(ln_b)
+    rows = zc.numel() // c1
+    out = torch.empty(*z.shape[:-1], k_pad, dtype=torch.float32, device=z.device)
+    with L.on_device(z.device):
+        L.check(L.lib().kfb_concat_layernorm(L.ptr(zc), L.dtype_code(zc.dtype), L.ptr(rc), L.dtype_code(rc.dtype), L.ptr(lw), L.ptr(lb),
+                                             L.ptr(out), rows, c1, c2, k_pad, eps, L.stream_ptr()))
+    return out
+
+
+def pair_outer_add(z: torch.Tensor, row_add: torch.Tensor, col_add: torch.Tensor) -> torch.Tensor:
+    """z[b, i, j] + row_add[b, j] + col_add[b, i] (model/modules/confidence_head.py:347-351): z (B, L, L, C), the addends (B, L, C)."""
+    _require_cuda(z, row_add, col_add)
+    b, n, _, c = z.shape
+    zc = z.contiguous()
+    ra, ca = row_add.to(z.dtype).contiguous(), col_add.to(z.dtype).contiguous()
+    out = torch.empty_like(zc)
+    with L.on_device(z.device):
+        L.check(L.lib().kfb_pair_outer_add(L.ptr(zc), L.ptr(ra), L.ptr(ca), L.ptr(out), b, n, c, L.dtype_code(zc.dtype), L.stream_ptr()))
+    return out
+
+
+def distogram_embed_add(z: torch.Tensor, x: torch.Tensor, boundaries: torch.Tensor, w_t: torch.Tensor) -> torch.Tensor:
+    """z + Linear(one_hot(distance bin of |x_i - x_j|)) (model/modules/confidence_head.py:449-455): z (B, L, L, C), x (B, L, 3),
+    boundaries (bins - 1,), w_t (bins, C) = the embedding weight transposed, in z's dtype."""
+    _require_cuda(z, x, boundaries, w_t)
+    b, n, _, c = z.shape
+    zc = z.contiguous()
+    xc, bd, wt = x.float().contiguous(), boundaries.float().contiguous(), w_t.to(z.dtype).contiguous()
+    out = torch.empty_like(zc)
+    with L.on_device(z.device):
+        L.check(L.lib().kfb_distogram_embed_add(L.ptr(zc), L.ptr(xc), L.ptr(bd), bd.numel(), L.ptr(wt), L.ptr(out), b, n, c,
+                                                L.dtype_code(zc.dtype), L.stream_ptr()))
+    return out

@@ -403,6 +403,81 @@ def diffusion_step(r_noisy, q, c, p, token_index, atom_mask, s, pair_bias, token
     return r_update * atom_mask[..., None]
 
 
+def parcae_dynamics(w: dict):
+    """``KFold._parcae_discretized_dynamics`` -- model/model.py:272-277."""
+    delta = F.softplus(w["parcae_log_delta"].float())
+    a = torch.exp(-delta * torch.exp(w["parcae_log_a"].float()))
+    return a, delta[:, None] * w["parcae_b_cont"].float()
+
+
+def parcae_update(z, u, w: dict, mode: str = "fp32"):
+    """The trunk's recurrence between recycling iterations, ``z = a * z + F.linear(self.layernorm_z(u_t), b)`` --
+    model/model.py:528 (a and b cast to the autocast dtype first, :505)."""
+    m = _Mode(mode)
+    a, b = parcae_dynamics(w)
+    un = layer_norm(u, w["layernorm_z.weight"], w["layernorm_z.bias"], 1e-5, mode)
+    return m.r(m.r(m.r(a) * m.r(z.float())) + m.linear(un, b))
+
+
+def lm_to_pair(s_lm, w: dict, mode: str = "fp32"):
+    """``LMToPair.forward`` -- model/model.py:127-134."""
+    m = _Mode(mode)
+    x = m.linear(layer_norm(s_lm, w["proj.0.weight"], w["proj.0.bias"], 1e-5, mode), w["proj.1.weight"], w["proj.1.bias"])
+    xi, xj = torch.chunk(x, 2, dim=-1)
+    xi, xj = xi.unsqueeze(-2), xj.unsqueeze(-3)
+    feats = torch.cat([m.r(xi * xj), m.r(xi - xj)], dim=-1)
+    h = m.r(F.gelu(m.linear(feats, w["mlp.0.weight"], w["mlp.0.bias"])))
+    y = m.linear(h, w["mlp.2.weight"], w["mlp.2.bias"])
+    return layer_norm(y, w["layernorm_pair.weight"], w["layernorm_pair.bias"], 1e-5, mode)
+
+
+def pair_conditioning(rel_pos_feats, z, w: dict, mode: str = "fp32"):
+    """``PairConditioning.forward`` -- model/layers/folding/diffusion.py:70-94, the relative-position features given:
+    a float32 LayerNorm + Linear over [z | rel_pos], then two Transitions added in place."""
+    zc = torch.cat((z.float(), rel_pos_feats.float()), dim=-1)
+    zn = F.layer_norm(zc, (zc.shape[-1],), w["layernorm.weight"].float(), None, 1e-5)
+    out = F.linear(zn, w["linear.weight"].float())
+    for i in range(2):
+        out = out + transition(out, sub(w, f"transitions.{i}"), mode)
+    return out
+
+
+def confidence_head(s_inputs, s_lm, z, x_repr, mask, w: dict, num_heads: int, num_blocks: int, mode: str = "fp32",
+                    min_dist: float = 3.25, max_dist: float = 50.75, num_bins: int = 39):
+    """``ConfidenceHead.forward`` between the representative-atom gather and the atom-layout scatter, with
+    ``forward_single`` for every sample -- model/modules/confidence_head.py:343-378, :413-470; blocks :152-175."""
+    m = _Mode(mode)
+    s0 = m.linear(layer_norm(s_lm, w["s_lm_to_s.0.weight"], w["s_lm_to_s.0.bias"], 1e-5, mode), w["s_lm_to_s.1.weight"])
+    z0 = m.r(m.r(z.float()) + m.linear(s_inputs, w["linear_s1.weight"])[..., None, :, :]
+             + m.linear(s_inputs, w["linear_s2.weight"])[..., :, None, :])
+    boundaries = torch.linspace(min_dist, max_dist, num_bins - 1, device=z.device)
+    pair_mask = mask[..., :, None] & mask[..., None, :]
+    outs = []
+    for i in range(x_repr.shape[1]):
+        x = x_repr[:, i].float()
+        d = (x[..., :, None, :] - x[..., None, :, :]).norm(dim=-1)
+        dgram = F.one_hot((d[..., None] > boundaries).sum(dim=-1), num_bins).float()
+        zi, si = m.r(z0 + m.linear(dgram, w["linear_distogram.weight"])), s0
+        for b in range(num_blocks):
+            wb = sub(w, f"stack.blocks.{b}")
+            zi = triangular_block(zi, pair_mask, sub(wb, "pair_block"), mode)
+            zn = layer_norm(zi, wb["layernorm_z.weight"], wb["layernorm_z.bias"], 1e-5, mode)
+            bias = m.linear(zn, wb["linear_pair_bias.weight"]).movedim(-1, -3)
+            si = m.r(si + self_attention_pair_bias(si, None, bias, mask, sub(wb, "attention"), num_heads, mode))
+            si = m.r(si + transition(si, sub(wb, "transition"), mode))
+        zf, sf = zi.float(), si.float()
+
+        def head(x_, name):
+            xn = F.layer_norm(x_, (x_.shape[-1],), w[name + ".0.weight"].float(), w[name + ".0.bias"].float(), 1e-5)
+            return F.linear(xn, w[name + ".1.weight"].float())
+
+        pde = head(zf, "pde_head")
+        outs.append((head(zf, "pae_head"), pde + pde.transpose(-2, -3), head(sf, "plddt_head").unflatten(-1, (24, -1)),
+                     head(sf, "resolved_head").unflatten(-1, (24, 2))))
+    names = ("pae_logits", "pde_logits", "plddt_logits", "resolved_logits")
+    return {n: torch.stack([o[k] for o in outs], dim=1) for k, n in enumerate(names)}
+
+
 def triangular_block(z, pair_mask, w: dict, mode: str = "fp32"):
     """``TriangularBlock.forward`` (eval) -- model/modules/tri_stack.py:130-151."""
     m = _Mode(mode)

@@ -70,6 +70,12 @@ CASES = {
     "sampler_small": dict(kind="sampler", seed=53, tape=5301, tokens=16, atoms=64, priors=2, c_a=256, c_s=384, c_z=128, c_atom=128,
                           c_pair=16, atom_blocks=1, atom_heads=4, token_blocks=2, token_heads=8, samples=2, steps=6, valid_atoms=60,
                           valid_tokens=15, coords=6),
+    # callers of the pair stacks in the trunk (model/model.py:114-134, :523-529) and the diffusion module's pair conditioning
+    "parcae_c128": dict(kind="parcae", seed=54, n=24, c=128),
+    "lm_to_pair": dict(kind="lm_to_pair", seed=55, l=24, c_s=256, c_z=128),
+    "pair_conditioning": dict(kind="pair_conditioning", seed=56, l=24, c_z=128),
+    # confidence head: z / s preparation, then forward_single for each of 2 samples (2 blocks, 24 tokens, 21 valid)
+    "confidence_head": dict(kind="confidence_head", seed=57, l=24, c_s=384, c_z=128, heads=16, blocks=2, samples=2, valid=21),
     # layer norm
     "layernorm_c128": dict(kind="layernorm", seed=51, rows=50, c=128),
     # composite block: benchmark config 1 (N=64, fp32, all-ones mask, seed 0) and a padded N=32 one
@@ -184,6 +190,31 @@ def build_inputs(name: str) -> dict:
         out["ref_element"] = torch.nn.functional.one_hot(torch.from_numpy(rng.rs.randint(0, 20, size=(1, na))), 128).float()
         out["ref_atom_name_chars"] = torch.nn.functional.one_hot(torch.from_numpy(rng.rs.randint(0, 64, size=(1, na, 4))), 64).float()
         out["ref_space_uid"] = out["token_index"].clone()
+    elif kind == "parcae":
+        out["w"] = synth.parcae_weights(rng, cs["c"])
+        out["z"] = rng.normal(1, cs["n"], cs["n"], cs["c"])
+        out["u"] = rng.normal(1, cs["n"], cs["n"], cs["c"]) * 2.0 + 0.5
+    elif kind == "lm_to_pair":
+        out["w"] = synth.lm_to_pair_weights(rng, cs["c_s"], cs["c_z"])
+        out["s_lm"] = rng.normal(1, cs["l"], cs["c_s"])
+    elif kind == "pair_conditioning":
+        l = cs["l"]
+        out["w"] = synth.pair_conditioning_weights(rng, cs["c_z"])
+        out["z"] = rng.normal(1, l, l, cs["c_z"])
+        # two chains (12 + 12 tokens) of one entity, the second a symmetric copy: every relative-position feature is exercised
+        half = l // 2
+        out["asym_id"] = torch.cat([torch.zeros(half), torch.ones(l - half)]).long().view(1, l)
+        out["entity_id"] = torch.zeros(1, l, dtype=torch.long)
+        out["sym_id"] = out["asym_id"].clone()
+        out["residue_index"] = torch.cat([torch.arange(half), torch.arange(l - half)]).view(1, l)
+        out["token_index"] = torch.arange(l).view(1, l)
+    elif kind == "confidence_head":
+        l = cs["l"]
+        out["w"] = synth.confidence_head_weights(rng, cs["c_s"], cs["c_z"], cs["heads"], cs["blocks"])
+        out["s_inputs"], out["s_lm"] = rng.normal(1, l, cs["c_s"]), rng.normal(1, l, cs["c_s"])
+        out["z"] = rng.normal(1, l, l, cs["c_z"])
+        out["x_repr"] = rng.normal(1, cs["samples"], l, 3) * 9.0          # pairwise distances span the 3.25 .. 50.75 A bins
+        out["mask"] = synth.token_mask(l, cs["valid"]).view(1, l)
     elif kind == "layernorm":
         out["x"] = rng.normal(cs["rows"], cs["c"]) * 3.0 + 1.5
         out["w"] = {"weight": rng.ln_w(cs["c"]), "bias": rng.ln_b(cs["c"])}

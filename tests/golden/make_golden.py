@@ -119,6 +119,43 @@ def run_reference(ns, name: str) -> dict:
                                 inp["pair_bias"], inp["token_mask"])}
     if kind == "sampler":
         return run_reference_sampler(inp)
+    if kind == "confidence_head":
+        import importlib
+        ch = importlib.import_module("kfold.model.modules.confidence_head")
+        head = ch.ConfidenceHead(ch.ConfidenceHead.Config(channel_s=cs["c_s"], channel_z=cs["c_z"], num_heads_attn=cs["heads"],
+                                                          num_blocks=cs["blocks"]), kernel_backend="torch")
+        _load(head, inp["w"])
+        for m in head.modules():
+            if getattr(m, "kernel_backend", None) == "sdpa":
+                m.kernel_backend = "torch"      # the oracle path; the constructor hard-codes "sdpa"
+        # the part of ConfidenceHead.forward between the representative-atom gather and the atom-layout scatter
+        # (model/modules/confidence_head.py:343-378), float32
+        s = head.s_lm_to_s(inp["s_lm"])
+        z = inp["z"] + head.linear_s1(inp["s_inputs"])[..., None, :, :] + head.linear_s2(inp["s_inputs"])[..., :, None, :]
+        outs = [head.forward_single(z, s, inp["x_repr"][:, i], mask=inp["mask"]) for i in range(cs["samples"])]
+        names = ("pae_logits", "pde_logits", "plddt_logits", "resolved_logits")
+        return {n: torch.stack([o[k] for o in outs], dim=1) for k, n in enumerate(names)}
+    if kind == "parcae":
+        import types
+        model = ref_shim.load_reference_model()
+        w = inp["w"]
+        holder = types.SimpleNamespace(parcae_log_a=w["parcae_log_a"], parcae_log_delta=w["parcae_log_delta"],
+                                       parcae_b_cont=w["parcae_b_cont"])
+        a, b = model.KFold._parcae_discretized_dynamics(holder)          # model/model.py:272-277
+        ln = _load(ns.LayerNorm(cs["c"]), sub(w, "layernorm_z"))
+        return {"out": a * inp["z"] + torch.nn.functional.linear(ln(inp["u"]), b)}   # model/model.py:528
+    if kind == "lm_to_pair":
+        model = ref_shim.load_reference_model()
+        return {"out": _load(model.LMToPair(cs["c_s"], cs["c_z"]), inp["w"])(inp["s_lm"])}
+    if kind == "pair_conditioning":
+        import importlib
+        import types
+        df = importlib.import_module("kfold.model.layers.folding.diffusion")
+        mod = _load(df.PairConditioning(cs["c_z"]), inp["w"])
+        token = types.SimpleNamespace(**{k: inp[k] for k in ("asym_id", "entity_id", "sym_id", "residue_index", "token_index")})
+        f_input = types.SimpleNamespace(token=token)
+        rel = mod.rel_pos_encoding(f_input, torch.float32)
+        return {"out": mod(f_input, inp["z"].clone()), "rel_pos_feats": rel}
     if kind == "layernorm":
         return {"out": _load(ns.LayerNorm(cs["c"]), inp["w"])(inp["x"])}
     if kind == "tri_block":

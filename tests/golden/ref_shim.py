@@ -102,6 +102,39 @@ def load_reference():
     return ns
 
 
+class _AnyMeta(type):
+    def __getattr__(cls, name):
+        return cls
+
+
+class _Any(metaclass=_AnyMeta):
+    """Stands for any class of a module that cannot be imported here; attribute access on it yields itself."""
+
+
+class _StubModule(types.ModuleType):
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return _Any
+
+
+def load_reference_model():
+    """Import the reference's ``kfold.model.model`` (LMToPair, the Parcae dynamics of KFold) after ``load_reference()``.
+    The modules it pulls in for the parts of K-Fold outside the hot path (input embedder, sequence / structure encoders,
+    heads) need rdkit and friends; they are replaced by stub modules whose every attribute is a placeholder class, which
+    is all the import needs (class-level annotations such as ``input_embedder.InputEmbedder.Config``)."""
+    load_reference()
+    mods = sys.modules["kfold.model.modules"]
+    for n in ("input_embedder", "prot_seq_encoder", "prot_struct_encoder", "rna_seq_encoder", "patch_geometry", "distogram_head",
+              "confidence_head", "apo_module"):
+        full = "kfold.model.modules." + n
+        if full not in sys.modules:
+            stub = _StubModule(full)
+            sys.modules[full] = stub
+            setattr(mods, n, stub)
+    return importlib.import_module("kfold.model.model")
+
+
 def _sub(weights: dict, prefix: str) -> dict:
     p = prefix + "."
     return {k[len(p):]: v for k, v in weights.items() if k.startswith(p)}

@@ -215,6 +215,54 @@ def triangular_block_weights(seed: int, c_z: int = 256) -> dict:
     return w
 
 
+def lm_to_pair_weights(rng: _Rng, c_s: int, c_z: int) -> dict:
+    """LMToPair (model/model.py:114-126)."""
+    return {"proj.0.weight": rng.ln_w(c_s), "proj.0.bias": rng.ln_b(c_s),
+            "proj.1.weight": rng.linear(2 * c_z, c_s), "proj.1.bias": rng.normal(2 * c_z, std=0.1),
+            "mlp.0.weight": rng.linear(c_z, 2 * c_z), "mlp.0.bias": rng.normal(c_z, std=0.1),
+            "mlp.2.weight": rng.linear(c_z, c_z), "mlp.2.bias": rng.normal(c_z, std=0.1),
+            "layernorm_pair.weight": rng.ln_w(c_z), "layernorm_pair.bias": rng.ln_b(c_z)}
+
+
+def pair_conditioning_weights(rng: _Rng, c_z: int, rel_pos_dim: int = 139) -> dict:
+    """PairConditioning (model/layers/folding/diffusion.py:50-68)."""
+    w = {"layernorm.weight": rng.ln_w(c_z + rel_pos_dim), "linear.weight": rng.linear(c_z, c_z + rel_pos_dim)}
+    for i in range(2):
+        w.update(_prefixed(f"transitions.{i}", transition_weights(rng, c_z, 2)))
+    return w
+
+
+def parcae_weights(rng: _Rng, c_z: int) -> dict:
+    """The recurrence parameters of KFold (model/model.py:203-217) and its layernorm_z; perturbed around their initial
+    values so that every term matters."""
+    import math
+    delta_init = -math.log(0.4472135954999579)
+    return {"parcae_log_a": rng.normal(c_z, std=0.3), "parcae_log_delta": rng.normal(c_z, std=0.2) + math.log(math.expm1(delta_init)),
+            "parcae_b_cont": torch.eye(c_z) + rng.normal(c_z, c_z, std=0.05),
+            "layernorm_z.weight": rng.ln_w(c_z), "layernorm_z.bias": rng.ln_b(c_z)}
+
+
+def confidence_head_weights(rng: _Rng, c_s: int, c_z: int, heads: int, blocks: int, num_bins: int = 39, pae: int = 64,
+                            pde: int = 64, plddt: int = 50) -> dict:
+    """ConfidenceHead (model/modules/confidence_head.py:216-296)."""
+    w = {"linear_s1.weight": rng.linear(c_z, c_s), "linear_s2.weight": rng.linear(c_z, c_s),
+         "s_lm_to_s.0.weight": rng.ln_w(c_s), "s_lm_to_s.0.bias": rng.ln_b(c_s), "s_lm_to_s.1.weight": rng.linear(c_s, c_s),
+         "linear_distogram.weight": rng.linear(c_z, num_bins)}
+    for i in range(blocks):
+        p = f"stack.blocks.{i}"
+        w.update(_prefixed(p + ".pair_block.tri_mul_out", trimul_weights(rng, c_z)))
+        w.update(_prefixed(p + ".pair_block.tri_mul_in", trimul_weights(rng, c_z)))
+        w.update(_prefixed(p + ".pair_block.transition_z", transition_weights(rng, c_z, 4)))
+        w[p + ".layernorm_z.weight"], w[p + ".layernorm_z.bias"] = rng.ln_w(c_z), rng.ln_b(c_z)
+        w[p + ".linear_pair_bias.weight"] = rng.linear(heads, c_z)
+        w.update(_prefixed(p + ".attention", apb_weights(rng, c_s, None)))
+        w.update(_prefixed(p + ".transition", transition_weights(rng, c_s, 4)))
+    for name, c_in, c_out in (("pae_head", c_z, pae), ("pde_head", c_z, pde), ("plddt_head", c_s, 24 * plddt), ("resolved_head", c_s, 48)):
+        w[name + ".0.weight"], w[name + ".0.bias"] = rng.ln_w(c_in), rng.ln_b(c_in)
+        w[name + ".1.weight"] = rng.linear(c_out, c_in)
+    return w
+
+
 def token_mask(n: int, valid: int | None = None, pad_frac: float | None = None) -> torch.Tensor:
     """Boolean token mask with a trailing padding tail (how K-Fold pads, inference/data_pipeline.py:129-134)."""
     if valid is None:

@@ -55,6 +55,14 @@ def run_oracle(name: str, mode: str = "fp32") -> dict:
         x_T, x = SO.sample_loop(inp["x_apo"], inp["atom_mask"], step, inp["s_inputs"], cs["steps"], cs["samples"], tape,
                                 single_conditioning=lambda s_in, cn: O.single_conditioning(s_in, cn, O.sub(w, "single_conditioning"), mode))
         return {"x_T": x_T, "coordinates": x, "draws": torch.tensor([tape.calls])}
+    if kind == "confidence_head":
+        return O.confidence_head(inp["s_inputs"], inp["s_lm"], inp["z"], inp["x_repr"], inp["mask"], w, cs["heads"], cs["blocks"], mode)
+    if kind == "parcae":
+        return {"out": O.parcae_update(inp["z"], inp["u"], w, mode)}
+    if kind == "lm_to_pair":
+        return {"out": O.lm_to_pair(inp["s_lm"], w, mode)}
+    if kind == "pair_conditioning":
+        return {"out": O.pair_conditioning(load_golden(name)["rel_pos_feats"], inp["z"], w, mode)}
     if kind == "layernorm":
         return {"out": O.layer_norm(inp["x"], w["weight"], w["bias"], 1e-5, mode)}
     if kind == "tri_block":
@@ -81,6 +89,9 @@ def test_oracle_matches_reference_golden(name):
         d = (got["coordinates"] - gold["coordinates"]).pow(2).sum(-1)
         rmsd = float(d.mean().sqrt())
         assert rmsd < 1e-3, f"sampler: coordinate RMSD {rmsd:.3e} A between the oracle and the reference"
+    elif cases.CASES[name]["kind"] == "confidence_head":
+        for k in ("pae_logits", "pde_logits", "plddt_logits", "resolved_logits"):
+            assert err_stats(got[k], gold[k])[0] < 5 * FP32_TOL, k
     elif cases.CASES[name]["kind"] == "atom_encoder":
         assert err_stats(got["a"], gold["a"])[0] < FP32_TOL and err_stats(got["q_skip"], gold["q_skip"])[0] < FP32_TOL
     elif cases.CASES[name]["kind"] == "atom_token_maps":
