@@ -1,6 +1,6 @@
 """Benchmark of the hot path: one composite Pairformer block forward at N=768, bf16.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference_triton]
 
 One step = one forward of the AF3-shaped Pairformer block (triangle multiplication out/in,
 triangle attention start/end, pair transition, single-track pair-bias attention, single
@@ -256,6 +256,46 @@ def run_reference_arm(args, rank: int, world: int) -> None:
         "gpu_launches": 0,
     }
     emit(line)
+
+
+def run_reference_triton_arm(args, rank: int) -> None:
+    """Report only (not the headline): the reference's GPU incumbent, its Triton backend, on this GPU.  The four pair
+    operators of the block at N=768 through the reference's own modules with kernel_backend="triton" (stock code path,
+    bf16 under autocast, as its inference runs them), each timed with CUDA events.  Any failure to import, JIT or run
+    prints the `unavailable` line with the message."""
+    if rank != 0:
+        return
+    try:
+        import ref_shim
+        import synth
+        ns = ref_shim.load_reference()
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        z, pm, _ = synth.pair_inputs(SEED, N_TOKENS, C_Z, 1, pad_frac=PAD_FRAC)
+        w = synth.pairformer_block_weights(SEED, C_Z, C_S)
+        zd, pmd = z.to(dev, torch.bfloat16), pm.to(dev)
+        mods = {}
+        for name, cls, extra in (("tri_mul_out", ns.TriangleMultiplicationOutgoing, ()), ("tri_mul_in", ns.TriangleMultiplicationIncoming, ()),
+                                 ("tri_att_start", ns.TriangleAttentionStartingNode, (4,)), ("tri_att_end", ns.TriangleAttentionEndingNode, (4,))):
+            mod = cls(C_Z, *extra, kernel_backend="triton")
+            mod.load_state_dict(ref_shim._sub(w, name), strict=True)
+            mods[name] = mod.to(dev).eval()
+        stream = torch.cuda.current_stream()
+        per_op = {}
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            for name, mod in mods.items():
+                for _ in range(max(args.warmup, 3)):      # the first call JIT-compiles (and autotunes) the kernels
+                    mod(zd, pmd)
+                per_op[name] = round(_event_time(lambda: mod(zd, pmd), args.steps, stream, lambda: None), 4)
+        total = sum(per_op.values())
+        emit({"impl": "reference_triton", "metric": "pair_operators_fwd_ms_n768_bf16", "value": total, "unit": "ms", "n_gpus": 1,
+              "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total, "higher_is_better": False, "dtype": "bf16",
+              "data": "synthetic", "per_op_ms": per_op,
+              "config": {"workload": "the reference's Triton backend: tri-mult out + in, tri-att start + end, N_token=768, c_z=128, "
+                                     "4 heads x 32; updates only (no residual add, no transition, no single track)"},
+              "note": "report only: a GPU anchor for the per-operator numbers, not the block metric"})
+    except Exception as exc:      # Triton refused to JIT, or the reference copy did not travel
+        emit({"impl": "reference_triton", "unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"})
 
 
 # ------------------------------------------------------------------------------------------------
@@ -666,6 +706,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        from kfold_b200 import sharded as _sh
+        _sh.apply_nccl_env_defaults()
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -875,7 +917,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the side measurements (48-block trunk, N=2048 sharded block and its parity check)")
@@ -908,6 +950,9 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
+        return
+    if args.impl == "reference_triton":
+        run_reference_triton_arm(args, rank)
         return
     if world == 1 and args.gpus > 1:
         raise SystemExit("launch multi-GPU runs with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")

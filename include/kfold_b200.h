@@ -124,40 +124,55 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
  * rows as x (rows, n, c).
  *   kfb_trimul_project : LayerNorm + gated input projection (if w_in_packed) -> ab_out bf16 [2c][rows][n]
  *                        (operand a = first c channels, b = last c), + output-gate logits (if w_gout)
- *                        -> gl_out bf16 [rows*n][c].  xn_scratch: bf16 [rows*n][c].
+ *                        -> gl_out bf16 [rows*n][c].  xn_scratch: bf16 [rows*n][c].  x == NULL: xn_scratch already holds
+ *                        the normalised rows (a second call on the same tensor, e.g. the gate logits issued after the
+ *                        operands so that they run under the operands' exchange).  transposed != 0: the operands are
+ *                        written transposed, ab_out [2c][n][rows] (the incoming direction's a[k][i] at [i][k]).
  *   (the caller all-gathers operand b: every rank's [c][rows][n] piece, rank after rank)
  *   kfb_trimul_finish  : contraction of the local a rows against all rows of b, LayerNorm_out, gated output
  *                        projection (+ resid).  b_gathered: pieces of b_piece_rows rows, b_piece_stride elements
  *                        apart.  t_scratch / tn_scratch: bf16 [c*rows*n] each.  out/resid: (rows, n, c).
  * The incoming direction is the same pair of calls with ab taken from the TRANSPOSED shard (the caller
- * transposes z across ranks with an all-to-all) and gl / resid from the row shard.
+ * transposes z across ranks with an all-to-all) and gl / resid from the row shard -- or, with the channel-sharded
+ * exchange below, the transposed projection of the row shard itself and no transpose of z.
  *   kfb_triatt_project : LayerNorm + projection -> qkg_out bf16 [rows*n][3*heads*dp], vt_out bf16
  *                        [rows][heads*dp][n], bias_out bf16 [heads][rows][n] (the caller all-gathers it per head
  *                        into [heads][n][n]).
  *   kfb_triatt_finish  : attention of the local rows against the full bias, output projection (+ resid).
  *                        mask: (rows, n) bytes; og_scratch: bf16 [rows*n][c].
+ * Ending node without reorder copies (exchange_layout != 0; rows must divide n):
+ *   kfb_layernorm_exchange : LayerNorm of the row shard x (rows, n, c), written bf16 as the send buffer of the shard
+ *                        transpose, [q][i][j][c] = LN(x[i][q*rows + j]) -- block q goes to rank q.
+ *   kfb_triatt_project with exchange_layout: x = the received buffer [q][i_q][j][c] (already normalised, bf16; ln_w, ln_b,
+ *                        xn_scratch unused); outputs as above for the transposed shard (row j, position q*rows + i_q).
+ *   kfb_triatt_finish with exchange_layout: out = the update as the send buffer of the transpose back,
+ *                        bf16 [q][j][k_q][c] for position (j, q*rows + k_q); no residual.
  *   kfb_pair_bias_rows_fwd : kfb_pair_bias_fwd on a shard: z (rows, n, c) -> bf16 [heads][rows][n].
  */
 KFB_API int kfb_trimul_project(const void* x, const unsigned char* mask, const float* ln_in_w, const float* ln_in_b,
                                const void* w_in_packed, const void* w_gout, void* xn_scratch, void* ab_out, void* gl_out,
-                               int batch, int rows, int n, int c, float eps, int dtype, void* stream);
+                               int batch, int rows, int n, int c, int transposed, float eps, int dtype, void* stream);
 KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride,
                               const void* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout,
                               void* t_scratch, void* tn_scratch, void* out, const void* resid, int rows, int n, int c,
                               float eps, int dtype, void* stream);
 /* Channel-sharded contraction for the row-sharded pair track (the cheaper exchange: an all-to-all of a and b to a
  * channel-sharded layout, this call, an all-to-all of t back; kfb_trimul_finish is then called with a = b = NULL and
- * t_scratch = the received t).  ab_recv: bf16 [world][2][cl][rows][n] as received; t_send: bf16 [world][cl][rows][n]. */
-KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world, int rows, int n, int cl, void* stream);
+ * t_scratch = the received t).  ab_recv: bf16 [world][2][cl][rows][n] as received; t_send: bf16 [world][cl][rows][n].
+ * incoming != 0: the ranks projected with transposed != 0, ab_recv is [world][2][cl][n][rows], and the product is
+ * t[i][j] = sum_k a[k][i] b[k][j] with K in `world` pieces (rows a multiple of 64). */
+KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world, int rows, int n, int cl, int incoming, void* stream);
 KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln_b, const void* w_proj_packed,
                                void* xn_scratch, void* qkg_out, void* vt_out, void* bias_out, int rows, int n, int c,
-                               int heads, float eps, int dtype, void* stream);
+                               int heads, int exchange_layout, float eps, int dtype, void* stream);
+KFB_API int kfb_layernorm_exchange(const void* x, void* y, const float* weight, const float* bias, int rows, int n, int c, float eps,
+                                   int in_dtype, void* stream);
 KFB_API int kfb_pair_bias_rows_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w, void* bias_out,
                                    void* workspace, size_t workspace_bytes, int rows, int n, int c, int heads, float eps,
                                    int dtype, void* stream);
 KFB_API int kfb_triatt_finish(const void* qkg, const void* vt, const void* bias_full, const unsigned char* mask,
                               const void* w_out, void* og_scratch, void* out, const void* resid, int rows, int n, int c,
-                              int heads, int dtype, void* stream);
+                              int heads, int exchange_layout, int dtype, void* stream);
 
 /*
  * bias[b, h, i, j] = sum_c LayerNorm(z)[b, i, j, c] * w[h, c], written bf16 as (batch, heads, n, n).

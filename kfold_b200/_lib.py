@@ -53,12 +53,13 @@ _SIGNATURES = {
                        c_void_p],
     "kfb_ln_linear_fp32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
                            c_int, c_int, c_float, c_int, c_void_p],
-    "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_layernorm_exchange": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_finish": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "kfb_triatt_project": [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "kfb_triatt_finish": [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "kfb_triatt_project": [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_triatt_finish": [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_pair_bias_rows_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_int, c_int,
                                c_int, c_int, c_float, c_int, c_void_p],
     "kfb_linear_fp32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll, c_int, c_int, c_void_p],

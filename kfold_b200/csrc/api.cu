@@ -60,6 +60,17 @@ int kfb_layernorm(const void* x, void* y, const float* weight, const float* bias
                           out_dtype);
 }
 
+KFB_API int kfb_layernorm_exchange(const void* x, void* y, const float* weight, const float* bias, int rows, int n, int c, float eps,
+                                   int in_dtype, void* stream) {
+  KFB_CHECK_ARG(x != nullptr && y != nullptr, "layernorm_exchange: null tensor");
+  KFB_CHECK_ARG(rows >= 1 && n % rows == 0, "layernorm_exchange: N=%d must be a multiple of rows=%d", n, rows);
+  RowPerm perm;
+  perm.rows = rows;
+  perm.n = n;
+  return launch_layernorm(as_stream(stream), x, y, weight, bias, static_cast<long long>(rows) * n, c, c, c, eps, in_dtype, KFB_BF16,
+                          perm);
+}
+
 KFB_API int kfb_gemm_bf16(const void* a, const void* b, void* d, const float* bias, int batch, int m, int n, int k, long long lda,
                   long long ldb, long long ldd, long long batch_stride_a, long long batch_stride_b,
                   long long batch_stride_d, int out_dtype, void* stream) {

@@ -82,7 +82,17 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
 
   CUtensorMap ta, tb;
   p.a_mn_major = a.s_k != 0 ? 1 : 0;
-  if (p.a_mn_major) {
+  p.k_inner = a.k_inner;
+  KFB_CHECK_ARG(a.k_inner == b.k_inner, "split K: both operands must be split alike (%d, %d)", a.k_inner, b.k_inner);
+  if (p.k_inner) {
+    KFB_CHECK_ARG(!p.a_mn_major && !p.precise && p.k_inner % kBK == 0 && p.k_extent % p.k_inner == 0,
+                  "split K: pieces of %d elements (multiple of %d) in K=%d, plain bf16 GEMM", p.k_inner, kBK, p.k_extent);
+    const uint64_t dims[5] = {(uint64_t)p.k_inner, (uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)(p.k_extent / p.k_inner),
+                              (uint64_t)p.batch};
+    const uint64_t str[4] = {(uint64_t)a.s_n * 2, (uint64_t)a.s_o * 2, (uint64_t)a.s_k_hi * 2, (uint64_t)a.s_b * 2};
+    const uint32_t box[5] = {kBK, kBM, 1, 1, 1};
+    KFB_TRY(make_tmap(&ta, a.ptr, 2, 5, dims, str, box, 128));
+  } else if (p.a_mn_major) {
     KFB_CHECK_ARG(a.s_n == 1 && p.k_extent % kBK == 0 && !p.precise && !p.glu, "K-outer A operand: rows must be contiguous, K a "
                   "multiple of %d, plain bf16 GEMM", kBK);
     const uint64_t dims[4] = {(uint64_t)p.n_extent, (uint64_t)p.k_extent, (uint64_t)p.o_extent, (uint64_t)p.batch};
@@ -101,11 +111,19 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
       KFB_CHECK_ARG(p.n_cols % inner == 0 && inner % bn == 0, "split B operand: %d columns in pieces of %d, tile %d", p.n_cols,
                     inner, bn);
     p.b_col_inner = inner;
+    if (p.k_inner) {
+      const uint64_t dims[5] = {(uint64_t)p.k_inner, (uint64_t)inner, (uint64_t)(p.n_cols / inner),
+                                (uint64_t)(p.k_extent / p.k_inner), (uint64_t)(p.b_batched ? p.batch : 1)};
+      const uint64_t str[4] = {(uint64_t)b.s_col * 2, (uint64_t)b.s_col_hi * 2, (uint64_t)b.s_k_hi * 2, (uint64_t)b.s_b * 2};
+      const uint32_t box[5] = {kBK, (uint32_t)bn, 1, 1, 1};
+      KFB_TRY(make_tmap(&tb, b.ptr, 2, 5, dims, str, box, 128));
+    } else {
     const uint64_t dims[4] = {(uint64_t)p.k_extent, (uint64_t)inner, (uint64_t)(p.n_cols / inner),
                               (uint64_t)(p.b_batched ? p.batch : 1)};
     const uint64_t str[3] = {(uint64_t)b.s_col * 2, (uint64_t)b.s_col_hi * 2, (uint64_t)b.s_b * 2};
     const uint32_t box[4] = {kBK, (uint32_t)bn, 1, 1};
     KFB_TRY(make_tmap(&tb, b.ptr, 2, 4, dims, str, box, 128));
+    }
   }
   // channel-major bf16 segments that satisfy the TMA alignment rules are stored through shared memory
   CUtensorMap tout[2];

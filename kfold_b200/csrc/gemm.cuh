@@ -53,6 +53,8 @@ struct GemmParams {
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
   int swap;                       // launcher: channel-major GLU output computed in the swapped orientation (see SWAP)
   int a_mn_major;                 // launcher: the A operand is stored K-outer ([k][row], rows contiguous) and read MN-major
+  int k_inner;                    // launcher: != 0: both operands store K in pieces of k_inner elements (a multiple of the K
+                                  // tile) that lie `s_k_hi` apart: K index = (k / k_inner, k % k_inner), five-dimensional maps
   const float2* row_stats;        // optional LayerNorm fold: out = rstd[row] * (acc - mean[row] * col_s1[col]) + col_s0[col]
   const float* col_s1;            //   (mean, rstd) per flat row; col_s1 = sum_k W'[col][k], col_s0 = sum_k beta[k] W[col][k]
   const float* col_s0;            //   with W' = gamma * W the matrix actually multiplied (applied before gate / residual)
@@ -321,6 +323,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // two boxes of [64 k][64 rows]: 128-byte rows of consecutive rows (positions), one per k index
             ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], nb * kBM, kb * kBK, o, b);
             ptx::tma_load_4d(s_a + stage * Cfg::kAStage + Cfg::kAStage / 2, &tm_a, &full_bar[stage], nb * kBM + 64, kb * kBK, o, b);
+          } else if (p.k_inner) {
+            const int k_hi = (kb * kBK) / p.k_inner;
+            const int k_lo = kb * kBK - k_hi * p.k_inner;
+            ptx::tma_load_5d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], k_lo, nb * kBM, o, k_hi, b);
+            ptx::tma_load_5d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], k_lo, b_col_lo, b_col_hi, k_hi, bb);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+            continue;
           } else
           ptx::tma_load_4d(s_a + stage * Cfg::kAStage, &tm_a, &full_bar[stage], kb * kBK, nb * kBM, o, b);
           ptx::tma_load_4d(s_b + stage * Cfg::kBStage, &tm_b, &full_bar[stage], kb * kBK, b_col_lo, b_col_hi, bb);
@@ -782,12 +791,16 @@ struct GemmOperandA {  // A[(b,o,n), k], strides in elements
   long long s_n, s_o, s_b;
   long long s_k = 0;       // != 0: K-outer storage, element (row, k) at ptr + k * s_k + row (rows contiguous, s_n = 1):
                            // the operand is then read MN-major (n_extent must cover whole 64-row boxes in memory)
+  int k_inner = 0;         // != 0 (set on both operands alike): K lies in pieces of k_inner contiguous elements, piece h of a
+  long long s_k_hi = 0;    // row starting s_k_hi * h elements after piece 0
 };
 struct GemmOperandB {  // B[(b), col, k]; optionally col = hi * col_inner + lo with its own stride for hi
   const void* ptr;
   long long s_col, s_b;
   int col_inner = 0;       // 0: plain rows
   long long s_col_hi = 0;
+  int k_inner = 0;         // as for GemmOperandA
+  long long s_k_hi = 0;
 };
 
 // Fills the tile bookkeeping of `p`, builds the tensor maps and launches on `stream`.

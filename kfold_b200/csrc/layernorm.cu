@@ -36,7 +36,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <typename TI, typename TO, int G>
 __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restrict__ x, TO* __restrict__ y,
                                                              const float* __restrict__ w, const float* __restrict__ b,
-                                                             long long rows, int c, long long xs, long long ys, float eps) {
+                                                             long long rows, int c, long long xs, long long ys, float eps,
+                                                             RowPerm perm) {
   const int lane = threadIdx.x & 31;
   const long long warps_per_grid = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
@@ -62,7 +63,14 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restric
       }
     }
     const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
-    TO* yr = y + row * ys;
+    long long orow = row;
+    if (perm.rows) {   // (i, q, j) -> (q, i, j): the send buffer of a shard transpose, one block per destination rank
+      const long long i = row / perm.n;
+      const int rest = static_cast<int>(row - i * perm.n);
+      const int q = rest / perm.rows;
+      orow = (static_cast<long long>(q) * perm.rows + i) * perm.rows + (rest - q * perm.rows);
+    }
+    TO* yr = y + orow * ys;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int ch = (lane + 32 * g) * 2;
@@ -86,45 +94,47 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restric
 
 template <typename TI, typename TO, int G>
 static int launch_rows(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
-                       long long xs, long long ys, float eps) {
+                       long long xs, long long ys, float eps, RowPerm perm) {
   const int warps = 8;
   long long blocks = (rows + warps - 1) / warps;
   const long long cap = static_cast<long long>(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   LaunchScope scope(stream, "layernorm_rows");
   layernorm_rows_kernel<TI, TO, G><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(
-      static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps);
+      static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps, perm);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }
 
 template <typename TI, typename TO>
 static int dispatch_g(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
-                      long long xs, long long ys, float eps) {
+                      long long xs, long long ys, float eps, RowPerm perm) {
   const int g = cdiv(c, 64);
-  if (g <= 1) return launch_rows<TI, TO, 1>(stream, x, y, w, b, rows, c, xs, ys, eps);
-  if (g <= 2) return launch_rows<TI, TO, 2>(stream, x, y, w, b, rows, c, xs, ys, eps);
-  if (g <= 4) return launch_rows<TI, TO, 4>(stream, x, y, w, b, rows, c, xs, ys, eps);
-  if (g <= 6) return launch_rows<TI, TO, 6>(stream, x, y, w, b, rows, c, xs, ys, eps);
-  if (g <= 12) return launch_rows<TI, TO, 12>(stream, x, y, w, b, rows, c, xs, ys, eps);
-  if (g <= 16) return launch_rows<TI, TO, 16>(stream, x, y, w, b, rows, c, xs, ys, eps);
+  if (g <= 1) return launch_rows<TI, TO, 1>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
+  if (g <= 2) return launch_rows<TI, TO, 2>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
+  if (g <= 4) return launch_rows<TI, TO, 4>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
+  if (g <= 6) return launch_rows<TI, TO, 6>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
+  if (g <= 12) return launch_rows<TI, TO, 12>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
+  if (g <= 16) return launch_rows<TI, TO, 16>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
   set_error("layernorm: channel count %d above 1024 is not supported", c);
   return KFB_ERR_UNSUPPORTED;
 }
 
 int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
-                     long long xs, long long ys, float eps, int in_dtype, int out_dtype) {
+                     long long xs, long long ys, float eps, int in_dtype, int out_dtype, RowPerm perm) {
   KFB_CHECK_ARG(rows >= 0 && c > 0 && c % 2 == 0, "layernorm: rows %lld, channels %d (must be even)", rows, c);
+  KFB_CHECK_ARG(perm.rows == 0 || (perm.n % perm.rows == 0 && rows == static_cast<long long>(perm.rows) * perm.n),
+                "layernorm: exchange order needs a (%d, %d) shard, got %lld rows", perm.rows, perm.n, rows);
   KFB_CHECK_ARG(xs % 2 == 0 && ys % 2 == 0, "layernorm: row strides must be even");
   if (rows == 0) return KFB_OK;
   if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16)
-    return dispatch_g<__nv_bfloat16, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps);
+    return dispatch_g<__nv_bfloat16, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
   if (in_dtype == KFB_FP32 && out_dtype == KFB_BF16)
-    return dispatch_g<float, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps);
+    return dispatch_g<float, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
   if (in_dtype == KFB_FP32 && out_dtype == KFB_FP32)
-    return dispatch_g<float, float>(stream, x, y, w, b, rows, c, xs, ys, eps);
+    return dispatch_g<float, float>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
   if (in_dtype == KFB_BF16 && out_dtype == KFB_FP32)
-    return dispatch_g<__nv_bfloat16, float>(stream, x, y, w, b, rows, c, xs, ys, eps);
+    return dispatch_g<__nv_bfloat16, float>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
   set_error("layernorm: bad dtype");
   return KFB_ERR_INVALID_ARGUMENT;
 }

@@ -4,9 +4,16 @@
 
 namespace kfb {
 
+// Output row order of a (rows, n) shard written as the send buffer of a shard transpose: row (i, q * rows + j) goes to
+// block q, [q][i][j].  rows == 0: rows keep their order.
+struct RowPerm {
+  int rows = 0;
+  int n = 0;
+};
+
 // Row-wise LayerNorm, one warp per row, fp32 statistics.  in/out dtype KFB_BF16 or KFB_FP32.
 int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
-                     long long xs, long long ys, float eps, int in_dtype, int out_dtype);
+                     long long xs, long long ys, float eps, int in_dtype, int out_dtype, RowPerm perm = RowPerm());
 
 // Row-wise LayerNorm of fp32 rows written as the bf16 triple split [x0 x0 x1 x1 x0 x2] (six blocks of c columns,
 // row stride 6c): the A operand of the fp32-accurate GEMMs.  With w == b == nullptr and `normalise` == 0 it only

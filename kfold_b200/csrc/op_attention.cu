@@ -312,8 +312,9 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
 // ------------------------------------------------------------------------------------------------
 KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln_b, const void* w_proj_packed,
                                void* xn_scratch, void* qkg_out, void* vt_out, void* bias_out, int rows, int n, int c,
-                               int heads, float eps, int dtype, void* stream_) {
-  KFB_CHECK_ARG(x && w_proj_packed && xn_scratch && qkg_out && vt_out && bias_out, "triatt_project: null pointer");
+                               int heads, int exchange_layout, float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(x && w_proj_packed && (xn_scratch || exchange_layout) && qkg_out && vt_out && bias_out, "triatt_project: null pointer");
+  KFB_CHECK_ARG(!exchange_layout || n % rows == 0, "triatt_project: the exchange layout needs N=%d to be a multiple of rows=%d", n, rows);
   KFB_CHECK_ARG(is_dtype(dtype), "triatt_project: bad dtype %d", dtype);
   KFB_CHECK_ARG(rows >= 1 && rows <= n && n >= 8 && n % 8 == 0, "triatt_project: rows=%d N=%d", rows, n);
   KFB_CHECK_ARG(heads >= 1 && c % heads == 0 && c % 8 == 0, "triatt_project: C=%d heads=%d", c, heads);
@@ -323,6 +324,39 @@ KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln
   cudaStream_t stream = as_stream(stream_);
   const long long rn = static_cast<long long>(rows) * n;
   __nv_bfloat16* xn = static_cast<__nv_bfloat16*>(xn_scratch);
+  if (exchange_layout) {
+    // x: the normalised rows as an all-to-all of kfb_layernorm_exchange's output leaves them, [q][i_q][j][c] holding row j of
+    // this (transposed) shard at position q * rows + i_q.  GEMM row = (batch j, o q, n i_q); outputs in the usual order.
+    GemmParams p = {};
+    p.n_extent = rows;
+    p.o_extent = n / rows;
+    p.batch = rows;
+    p.n_cols = 4 * hdp + 32;
+    p.k_extent = c;
+    p.nseg = 3;
+    p.seg[0] = row_major_seg(qkg_out, 3 * hdp, 3 * hdp, static_cast<long long>(rows) * 3 * hdp, static_cast<long long>(n) * 3 * hdp, 0, 0);
+    EpiSeg& sv = p.seg[1];
+    sv = {};
+    sv.col_begin = 3 * hdp;
+    sv.ncols = hdp;
+    sv.dst = vt_out;
+    sv.s_col = n;
+    sv.s_n = 1;
+    sv.s_o = rows;
+    sv.s_b = static_cast<long long>(hdp) * n;
+    EpiSeg& sb = p.seg[2];
+    sb = {};
+    sb.col_begin = 4 * hdp;
+    sb.ncols = heads;
+    sb.dst = bias_out;
+    sb.s_col = rn;
+    sb.s_n = 1;
+    sb.s_o = rows;
+    sb.s_b = n;
+    GemmOperandA a = {x, static_cast<long long>(rows) * c, static_cast<long long>(rows) * rows * c, c};
+    GemmOperandB b = {w_proj_packed, c, 0};
+    return launch_gemm_bf16(stream, a, b, p, 128, "triatt_proj");
+  }
   KFB_TRY(launch_layernorm(stream, x, xn, ln_w, ln_b, rn, c, c, c, eps, dtype, KFB_BF16));
   GemmParams p = {};
   p.n_extent = n;
@@ -355,7 +389,9 @@ KFB_API int kfb_triatt_project(const void* x, const float* ln_w, const float* ln
 
 KFB_API int kfb_triatt_finish(const void* qkg, const void* vt, const void* bias_full, const unsigned char* mask,
                               const void* w_out, void* og_scratch, void* out, const void* resid, int rows, int n, int c,
-                              int heads, int dtype, void* stream_) {
+                              int heads, int exchange_layout, int dtype, void* stream_) {
+  KFB_CHECK_ARG(!exchange_layout || (n % rows == 0 && resid == nullptr && dtype == KFB_BF16),
+                "triatt_finish: the exchange layout takes N=%d a multiple of rows=%d, bf16, no residual", n, rows);
   KFB_CHECK_ARG(qkg && vt && bias_full && mask && w_out && og_scratch && out, "triatt_finish: null pointer");
   KFB_CHECK_ARG(is_dtype(dtype), "triatt_finish: bad dtype %d", dtype);
   KFB_CHECK_ARG(rows >= 1 && rows <= n && rows <= 65535 && n >= 8 && n % 8 == 0, "triatt_finish: rows=%d N=%d", rows, n);
@@ -395,6 +431,14 @@ KFB_API int kfb_triatt_finish(const void* qkg, const void* vt, const void* bias_
   p.resid = resid;
   GemmOperandA a = {og_scratch, c, 0, 0};
   GemmOperandB b = {w_out, c, 0};
+  if (exchange_layout) {
+    // out[q][j][k_q][c] = update of position (j, q * rows + k_q): the send buffer of the transpose back, block q for rank q
+    p.n_extent = rows;
+    p.o_extent = n / rows;
+    p.batch = rows;
+    p.seg[0] = row_major_seg(out, c, c, static_cast<long long>(rows) * rows * c, static_cast<long long>(rows) * c, 0);
+    a = {og_scratch, c, static_cast<long long>(rows) * c, static_cast<long long>(n) * c};
+  }
   return launch_gemm_bf16(stream, a, b, p, 0, "triatt_out_proj");
 }
 

@@ -44,13 +44,14 @@ int check_shape(const char* what, int batch, int rows, int n, int c) {
   return KFB_OK;
 }
 
-// steps 1-3 on a (batch, rows, n, c) tensor.  transposed_walk (square tensors only) writes a^T, b^T.
+// steps 1-3 on a (batch, rows, n, c) tensor.  transposed_walk writes a^T, b^T: ab[ch][b][column][row of the shard].
+// x == nullptr: xn already holds the normalised input (a second call on the same tensor).
 int project(cudaStream_t stream, int transposed_walk, const void* x, const unsigned char* mask, const float* ln_w,
             const float* ln_b, const void* w_in_packed, const void* w_gout, __nv_bfloat16* xn, __nv_bfloat16* ab,
             __nv_bfloat16* gl, int batch, int rows, int n, int c, float eps, int dtype) {
   const long long rn = static_cast<long long>(rows) * n;
   const long long pos = rn * batch;
-  KFB_TRY(launch_layernorm(stream, x, xn, ln_w, ln_b, pos, c, c, c, eps, dtype, KFB_BF16));
+  if (x != nullptr) KFB_TRY(launch_layernorm(stream, x, xn, ln_w, ln_b, pos, c, c, c, eps, dtype, KFB_BF16));
   if (w_in_packed != nullptr) {
     // ab[ch][b][o][n_]: o = row of the shard, n_ = position inside the row (swapped for the transposed walk)
     GemmParams p = {};
@@ -332,14 +333,14 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
 
 KFB_API int kfb_trimul_project(const void* x, const unsigned char* mask, const float* ln_in_w, const float* ln_in_b,
                                const void* w_in_packed, const void* w_gout, void* xn_scratch, void* ab_out, void* gl_out,
-                               int batch, int rows, int n, int c, float eps, int dtype, void* stream_) {
-  KFB_CHECK_ARG(x && xn_scratch, "trimul_project: null pointer");
+                               int batch, int rows, int n, int c, int transposed, float eps, int dtype, void* stream_) {
+  KFB_CHECK_ARG(xn_scratch, "trimul_project: null pointer");
   KFB_CHECK_ARG((w_in_packed == nullptr) == (ab_out == nullptr) && (w_gout == nullptr) == (gl_out == nullptr),
                 "trimul_project: each weight needs its output buffer and vice versa");
   KFB_CHECK_ARG(w_in_packed == nullptr || mask != nullptr, "trimul_project: the input projection needs the mask");
   KFB_CHECK_ARG(is_dtype(dtype), "trimul_project: bad dtype %d", dtype);
   KFB_TRY(check_shape("trimul_project", batch, rows, n, c));
-  return project(as_stream(stream_), 0, x, mask, ln_in_w, ln_in_b, w_in_packed, w_gout, static_cast<__nv_bfloat16*>(xn_scratch),
+  return project(as_stream(stream_), transposed ? 1 : 0, x, mask, ln_in_w, ln_in_b, w_in_packed, w_gout, static_cast<__nv_bfloat16*>(xn_scratch),
                  static_cast<__nv_bfloat16*>(ab_out), static_cast<__nv_bfloat16*>(gl_out), batch, rows, n, c, eps, dtype);
 }
 
@@ -364,7 +365,10 @@ KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece
 // for `cl` of the channels: ab_recv [world (source rank q)][2 (a, b)][cl][rows][n], rows q*rows .. q*rows+rows-1 of the pair
 // tensor coming from rank q.  Result t_send [world (q)][cl][rows][n]: the rows of t that belong to rank q, laid out for
 // the all-to-all back (after which every rank holds t [c][rows][n] for its own rows, channel-major).
-KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world, int rows, int n, int cl, void* stream_) {
+// incoming != 0: the ranks projected with the transposed walk, ab_recv is [world (q)][2][cl][n][rows] holding
+// a[k = q*rows + k_q][i] at [i][k_q]; t[i][j] = sum_k a[k][i] b[k][j] is then a K-major product whose K lies in `world` pieces.
+KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world, int rows, int n, int cl, int incoming,
+                                   void* stream_) {
   KFB_CHECK_ARG(ab_recv && t_send, "trimul_contract_cs: null pointer");
   KFB_CHECK_ARG(world >= 1 && rows >= 64 && rows % 64 == 0 && static_cast<long long>(world) * rows == n && cl >= 1,
                 "trimul_contract_cs: world %d x rows %d (multiple of 64) must equal N=%d; channels %d", world, rows, n, cl);
@@ -379,6 +383,16 @@ KFB_API int kfb_trimul_contract_cs(const void* ab_recv, void* t_send, int world,
   p.b_batched = 1;
   p.nseg = 1;
   p.seg[0] = row_major_seg(t_send, n, n, static_cast<long long>(cl) * rn, rn, 0);
+  if (incoming) {
+    GemmOperandA oa = {a, rows, static_cast<long long>(rows) * rows, rn};
+    oa.k_inner = rows;
+    oa.s_k_hi = 2ll * cl * rn;
+    GemmOperandB ob = {a + static_cast<long long>(cl) * rn, rows, rn};
+    ob.k_inner = rows;
+    ob.s_k_hi = 2ll * cl * rn;
+    const int bn = n % 256 == 0 ? 256 : (n % 128 == 0 ? 128 : 64);
+    return launch_gemm_bf16(as_stream(stream_), oa, ob, p, bn, "trimul_contraction");
+  }
   GemmOperandA oa = {a, n, 2ll * cl * rn, rn};
   GemmOperandB ob = {a + static_cast<long long>(cl) * rn, n, rn};
   ob.col_inner = rows;

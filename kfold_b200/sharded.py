@@ -10,11 +10,15 @@ pair representation z (N, N, C) by rows: rank r owns rows [r*N/P, (r+1)*N/P).  P
                                       C/P channels), local contraction, ALL-TO-ALL of t back to row shards.  That moves
                                       3 N^2 C / P values per rank instead of the (P-1) N^2 C / P of an all-gather of b
                                       (the all-gather form is kept below four ranks and for C not divisible by P)
-  triangle multiplication, incoming   t[i,j] = sum_k a[k,i] b[k,j]    a, b are taken from the TRANSPOSED shard
-                                      (all-to-all transpose of z), where it is the outgoing form; the
-                                      output gate and the residual use the row shard
+  triangle multiplication, incoming   t[i,j] = sum_k a[k,i] b[k,j]    channel-sharded form: the projection writes a, b
+                                      transposed ([i][k], k = the rank's own rows), the all-to-all leaves K in one piece
+                                      per source rank and the contraction walks the pieces: z itself is never transposed.
+                                      All-gather form: a, b are taken from the TRANSPOSED shard (all-to-all transpose of
+                                      z), where it is the outgoing form; the output gate and the residual use the row shard
   triangle attention, starting node   rows local; ALL-GATHER of the projected triangle bias only (N*N*H)
-  triangle attention, ending node     starting node on the transposed shard, result transposed back
+  triangle attention, ending node     starting node on the transposed shard, result transposed back; the three reorders
+                                      around the two all-to-alls ride in the LayerNorm, the projection's operand strides and
+                                      the output projection's store strides
   single track / pair bias            bias rows all-gathered (one collective for all heads), single track replicated
 
 Everything here is host-side orchestration: the kernels are the same ones the single-GPU path uses, called
@@ -30,6 +34,18 @@ import torch.distributed as dist
 from . import _lib as L
 from . import functional as F
 from . import packing
+
+
+# NCCL's point-to-point transport (what an all-to-all is made of) uses few channels by default: on two B200s a 268 MB
+# all-to-all ran at 323 GB/s per rank with the defaults and at 550 GB/s with these (the all-gather is unaffected).
+NCCL_ENV_DEFAULTS = {"NCCL_MIN_P2P_NCHANNELS": "64", "NCCL_MAX_P2P_NCHANNELS": "64", "NCCL_MIN_NCHANNELS": "32"}
+
+
+def apply_nccl_env_defaults() -> None:
+    """Set the NCCL variables above unless the user already chose values.  Call before the process group is created."""
+    import os
+    for k, v in NCCL_ENV_DEFAULTS.items():
+        os.environ.setdefault(k, v)
 
 
 def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
@@ -106,46 +122,44 @@ class ShardedPairOps:
         return self._mask_t[1]
 
     # ------------------------------------------------------------------ triangle multiplication
-    def _trimul_cs(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
-        """Channel-sharded exchange.  `pk` must come from pack_trimul(..., shard_world=world): the projection then writes
-        the operand channels rank by rank, [q][a, b][C/P], which is the send buffer of the all-to-all as it lies."""
-        rows, n, c = x_row.shape
+    def _trimul_cs(self, x_loc: torch.Tensor, mask_loc: torch.Tensor, pk: dict, eps: float, incoming: bool):
+        """Channel-sharded exchange, either direction, from the row shard alone.  `pk` must come from
+        pack_trimul(..., shard_world=world): the projection then writes the operand channels rank by rank, [q][a, b][C/P],
+        which is the send buffer of the all-to-all as it lies.  The incoming direction projects with the transposed walk
+        (a[k][i] stored at [i][k]) and contracts over a K that lies in one piece per source rank: no transpose of z."""
+        rows, n, c = x_loc.shape
         world, cl = self.world, c // self.world
-        dev = x_row.device
+        dev = x_loc.device
         lib = L.lib()
-        dt = L.dtype_code(x_row.dtype)
+        dt = L.dtype_code(x_loc.dtype)
         xn = _bf16((rows * n, c), dev)
-        ab = _bf16((world, 2, cl, rows, n), dev)
+        ab = _bf16((world, 2, cl, n, rows) if incoming else (world, 2, cl, rows, n), dev)
         gl = _bf16((rows * n, c), dev)
-        m8 = mask_ab.to(torch.bool).contiguous().view(torch.uint8)
-        x_ab = x_ab.contiguous()
-        x_row = x_row.contiguous()
+        m8 = mask_loc.to(torch.bool).contiguous().view(torch.uint8)
+        x_loc = x_loc.contiguous()
+        tr = 1 if incoming else 0
         with L.on_device(dev):
             st = L.stream_ptr()
-            same = x_ab.data_ptr() == x_row.data_ptr()
-            L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
-                                           L.ptr(pk["w_gout"]) if same else None, L.ptr(xn), L.ptr(ab),
-                                           L.ptr(gl) if same else None, 1, rows, n, c, eps, dt, st))
+            L.check(lib.kfb_trimul_project(L.ptr(x_loc), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
+                                           None, L.ptr(xn), L.ptr(ab), None, 1, rows, n, c, tr, eps, dt, st))
             ab_recv = torch.empty_like(ab)
-            work = dist.all_to_all_single(ab_recv, ab, group=self.group, async_op=True)   # [source rank][a, b][cl][rows][n]
-            if not same:   # gate logits of the row shard while the exchange is in flight
-                L.check(lib.kfb_trimul_project(L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
-                                               L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, eps, dt, st))
+            work = dist.all_to_all_single(ab_recv, ab, group=self.group, async_op=True)   # [source rank][a, b][cl][..][..]
+            # the output-gate logits, from the rows normalised above, while the exchange is in flight
+            L.check(lib.kfb_trimul_project(None, None, None, None, None, L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows,
+                                           n, c, 0, eps, dt, st))
             work.wait()
             t_send = _bf16((world, cl, rows, n), dev)
-            L.check(lib.kfb_trimul_contract_cs(L.ptr(ab_recv), L.ptr(t_send), world, rows, n, cl, L.stream_ptr()))
+            L.check(lib.kfb_trimul_contract_cs(L.ptr(ab_recv), L.ptr(t_send), world, rows, n, cl, tr, L.stream_ptr()))
             t = torch.empty_like(t_send)
             dist.all_to_all_single(t, t_send, group=self.group)         # [channel group][cl][rows][n] = t [c][rows][n]
-            out = torch.empty_like(x_row)
+            out = torch.empty_like(x_loc)
             L.check(lib.kfb_trimul_finish(None, None, rows, 0, L.ptr(gl), L.ptr(pk["ln_out_w"]), L.ptr(pk["ln_out_b"]),
-                                          L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out), L.ptr(x_row), rows, n, c, eps,
+                                          L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out), L.ptr(x_loc), rows, n, c, eps,
                                           dt, L.stream_ptr()))
         return out
 
     def _trimul(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
-        """a, b from (x_ab, mask_ab); gate logits and residual from x_row.  All (rows, N, ...) shards."""
-        if pk.get("shard_world", 0) == self.world and self.world > 1:
-            return self._trimul_cs(x_ab, mask_ab, x_row, pk, eps)
+        """All-gather form: a, b from (x_ab, mask_ab); gate logits and residual from x_row.  All (rows, N, ...) shards."""
         rows, n, c = x_row.shape
         dev = x_row.device
         lib = L.lib()
@@ -160,12 +174,13 @@ class ShardedPairOps:
             st = L.stream_ptr()
             same = x_ab.data_ptr() == x_row.data_ptr()
             L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
-                                           L.ptr(pk["w_gout"]) if same else None, L.ptr(xn), L.ptr(ab),
-                                           L.ptr(gl) if same else None, 1, rows, n, c, eps, dt, st))
-            if not same:
-                L.check(lib.kfb_trimul_project(L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
-                                               L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, eps, dt, st))
-            b_full = gather_rows(ab[c:], self.group)          # [world][c][rows][n]: rank after rank
+                                           None, L.ptr(xn), L.ptr(ab), None, 1, rows, n, c, 0, eps, dt, st))
+            # [world][c][rows][n], rank after rank; the gate logits are projected while the gather is in flight
+            b_full = torch.empty((self.world * c, rows, n), dtype=torch.bfloat16, device=dev)
+            work = dist.all_gather_into_tensor(b_full, ab[c:], group=self.group, async_op=True)
+            L.check(lib.kfb_trimul_project(None if same else L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
+                                           L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, 0, eps, dt, st))
+            work.wait()
             t = _bf16((c, rows, n), dev)
             out = torch.empty_like(x_row)
             L.check(lib.kfb_trimul_finish(L.ptr(ab), L.ptr(b_full), rows, c * rows * n, L.ptr(gl), L.ptr(pk["ln_out_w"]),
@@ -173,12 +188,22 @@ class ShardedPairOps:
                                           L.ptr(x_row), rows, n, c, eps, dt, L.stream_ptr()))
         return out
 
+    def _channel_form(self, pk: dict, rows: int) -> bool:
+        return pk.get("shard_world", 0) == self.world and self.world > 1 and rows % 64 == 0
+
     def trimul_outgoing(self, x_loc, mask_loc, pk, eps: float = 1e-5):
         """x + TriangleMultiplicationOutgoing(x) on the row shard (rows, N, C); mask_loc (rows, N)."""
+        if self._channel_form(pk, x_loc.shape[0]):
+            return self._trimul_cs(x_loc, mask_loc, pk, eps, incoming=False)
         return self._trimul(x_loc, mask_loc, x_loc, pk, eps)
 
     def trimul_incoming(self, x_loc, mask_loc, pk, eps: float = 1e-5):
-        """x + TriangleMultiplicationIncoming(x): operands from the transposed shard."""
+        """x + TriangleMultiplicationIncoming(x): with the channel-sharded exchange straight from the row shard, otherwise
+        with the operands taken from the transposed shard."""
+        if self._channel_form(pk, x_loc.shape[0]):
+            return self._trimul_cs(x_loc, mask_loc, pk, eps, incoming=True)
+        if pk.get("shard_world", 0):
+            raise ValueError("trimul_incoming: weights packed for the channel exchange need shards of a multiple of 64 rows")
         xt = transpose_shard(x_loc, self.group)
         return self._trimul(xt, self._transposed_mask(mask_loc), x_loc, pk, eps)
 
@@ -199,20 +224,48 @@ class ShardedPairOps:
         m8 = mask_loc.to(torch.bool).contiguous().view(torch.uint8)
         with L.on_device(dev):
             L.check(lib.kfb_triatt_project(L.ptr(x_loc), L.ptr(pk["ln_w"]), L.ptr(pk["ln_b"]), L.ptr(pk["w_proj"]), L.ptr(xn),
-                                           L.ptr(qkg), L.ptr(vt), L.ptr(bias_loc), rows, n, c, heads, eps, dt, L.stream_ptr()))
+                                           L.ptr(qkg), L.ptr(vt), L.ptr(bias_loc), rows, n, c, heads, 0, eps, dt, L.stream_ptr()))
             bias_full = gather_head_rows(bias_loc, self.group)
             out = torch.empty_like(x_loc)
             L.check(lib.kfb_triatt_finish(L.ptr(qkg), L.ptr(vt), L.ptr(bias_full), L.ptr(m8), L.ptr(pk["w_out"]), L.ptr(xn),
-                                          L.ptr(out), L.ptr(x_loc) if resid else None, rows, n, c, heads, dt, L.stream_ptr()))
+                                          L.ptr(out), L.ptr(x_loc) if resid else None, rows, n, c, heads, 0, dt, L.stream_ptr()))
         return out
 
     def triatt_starting(self, x_loc, mask_loc, pk, eps: float = 1e-5):
         return self._triatt_start(x_loc, mask_loc, pk, eps, resid=True)
 
     def triatt_ending(self, x_loc, mask_loc, pk, eps: float = 1e-5):
-        xt = transpose_shard(x_loc, self.group)
-        upd_t = self._triatt_start(xt, self._transposed_mask(mask_loc), pk, eps, resid=False)
-        return transpose_shard(upd_t, self.group, add_to=x_loc)
+        """x + TriangleAttentionEndingNode(x): the starting-node operator on the transposed shard.  LayerNorm runs before
+        the transpose and writes the all-to-all's send buffer; the projection reads the received buffer as it lies, the
+        output projection writes the update as the send buffer of the transpose back: three kernels carry the reorders
+        that would otherwise be three copies of the shard."""
+        rows, n, c = x_loc.shape
+        world = self.world
+        heads = pk["heads"]
+        hdp = heads * packing.head_dim_pad(c // heads)
+        dev = x_loc.device
+        lib = L.lib()
+        bf = L.dtype_code(torch.bfloat16)
+        x_loc = x_loc.contiguous()
+        m8 = self._transposed_mask(mask_loc).to(torch.bool).contiguous().view(torch.uint8)
+        send = _bf16((world, rows, rows, c), dev)
+        recv = torch.empty_like(send)
+        qkg = _bf16((rows * n, 3 * hdp), dev)
+        vt = _bf16((rows, hdp, n), dev)
+        bias_loc = _bf16((heads, rows, n), dev)
+        with L.on_device(dev):
+            L.check(lib.kfb_layernorm_exchange(L.ptr(x_loc), L.ptr(send), L.ptr(pk["ln_w"]), L.ptr(pk["ln_b"]), rows, n, c, eps,
+                                               L.dtype_code(x_loc.dtype), L.stream_ptr()))
+            dist.all_to_all_single(recv, send, group=self.group)      # recv[q][i_q][j] = LN(z)[q*rows + i_q][r*rows + j]
+            L.check(lib.kfb_triatt_project(L.ptr(recv), None, None, L.ptr(pk["w_proj"]), None, L.ptr(qkg), L.ptr(vt),
+                                           L.ptr(bias_loc), rows, n, c, heads, 1, eps, bf, L.stream_ptr()))
+            bias_full = gather_head_rows(bias_loc, self.group)
+            # `send` is free again (the exchange has read it): attention output; `recv` (read by the projection): the update
+            L.check(lib.kfb_triatt_finish(L.ptr(qkg), L.ptr(vt), L.ptr(bias_full), L.ptr(m8), L.ptr(pk["w_out"]), L.ptr(send),
+                                          L.ptr(recv), None, rows, n, c, heads, 1, bf, L.stream_ptr()))
+            upd = torch.empty_like(recv)
+            dist.all_to_all_single(upd, recv, group=self.group)       # upd[q][j][i] = update of z[r*rows + i][q*rows + j]
+        return x_loc + upd.permute(2, 0, 1, 3).reshape(rows, n, c)
 
     # ------------------------------------------------------------------ pair bias for the single track
     def pair_bias(self, x_loc, ln_w, ln_b, w, eps: float = 1e-5):
@@ -237,14 +290,14 @@ class ShardedPairformerBlock:
         self.exchange = exchange
         self._trimul_packs = {}
 
-    def _pack_trimul(self, mod, dev):
+    def _pack_trimul(self, mod, dev, rows: int, incoming: bool):
         """Weights for the channel-sharded exchange when C divides by the number of ranks (packed once per module)."""
         world = self.ops.world
         c = mod.layernorm_in.normalized_shape
-        # the channel-sharded exchange moves 3 N^2 C / P values per rank, the all-gather of b (P - 1) N^2 C / P: it pays from
-        # four ranks on
-        channel = self.exchange == "channel" or (self.exchange == "auto" and world >= 4)
-        if world == 1 or not channel or c % world != 0:
+        # outgoing: the channel-sharded exchange moves 3 N^2 C / P values per rank, the all-gather of b (P - 1) N^2 C / P: it
+        # pays from four ranks on.  Incoming: the all-gather form also transposes z, the channel form does not: it pays always.
+        channel = self.exchange == "channel" or (self.exchange == "auto" and (world >= 4 or incoming))
+        if world == 1 or not channel or c % world != 0 or rows % 64 != 0:
             return mod._packed(dev, torch.bfloat16, packing.pack_trimul)
         key = (id(mod), dev)
         if key not in self._trimul_packs:
@@ -259,8 +312,9 @@ class ShardedPairformerBlock:
         b, ops = self.block, self.ops
         dev = z_loc.device
         bf = torch.bfloat16
-        z = ops.trimul_outgoing(z_loc, pair_mask_loc, self._pack_trimul(b.tri_mul_out, dev))
-        z = ops.trimul_incoming(z, pair_mask_loc, self._pack_trimul(b.tri_mul_in, dev))
+        rows = z_loc.shape[0]
+        z = ops.trimul_outgoing(z_loc, pair_mask_loc, self._pack_trimul(b.tri_mul_out, dev, rows, False))
+        z = ops.trimul_incoming(z, pair_mask_loc, self._pack_trimul(b.tri_mul_in, dev, rows, True))
         pk_s = b.tri_att_start._packed(dev, bf, lambda sd, d: packing.pack_triatt(sd, b.tri_att_start.no_heads, d))
         pk_e = b.tri_att_end._packed(dev, bf, lambda sd, d: packing.pack_triatt(sd, b.tri_att_end.no_heads, d))
         z = ops.triatt_starting(z, pair_mask_loc, pk_s)

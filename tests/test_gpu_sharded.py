@@ -22,11 +22,12 @@ def _worker(rank: int, world: int, port: int, n: int, exchange: str, q):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
+    from kfold_b200 import sharded
+    sharded.apply_nccl_env_defaults()
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         from kfold_b200 import _lib as L
         from kfold_b200 import modules as M
-        from kfold_b200 import sharded
         import synth
         w = synth.pairformer_block_weights(21)
         z, pm, m = synth.pair_inputs(21, n, 128, 1, pad_frac=0.1)
