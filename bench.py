@@ -741,13 +741,13 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     def step_resident():
         return run_block(z_dev, s_dev)
 
-    def step_e2e():
-        zd = z_host.to(dev, non_blocking=True)
-        sd = s_host.to(dev, non_blocking=True)
-        zo, so = run_block(zd, sd)
-        zo = zo.reshape(z_out_host.shape)
-        z_out_host.copy_(zo, non_blocking=True)
-        s_out_host.copy_(so, non_blocking=True)
+    from kfold_b200.host_pipeline import HostPipeline
+    pipe = HostPipeline(run_block, dev, depth=2)
+
+    def run_e2e(k: int):
+        """k steps through the public host-side call: every step copies its own inputs in from pinned host memory and its
+        own result out; the copies of neighbouring steps run under the compute on separate streams."""
+        pipe.run([(z_host, s_host)] * k, [(z_out_host, s_out_host)] * k)
 
     trunk = None
     sampler_run = None
@@ -775,12 +775,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         L.profile_enable(False)
         status = L.device_status()
         # ---- end to end: host buffers in, host buffers out, copies inside the timed region
-        for _ in range(max(1, min(args.warmup, 2))):
-            step_e2e()
+        run_e2e(max(2, min(args.warmup, 3)))
         barrier()
         e0.record(stream)
-        for _ in range(args.steps):
-            step_e2e()
+        run_e2e(args.steps)
         e1.record(stream)
         barrier()
         ms_e2e = e0.elapsed_time(e1) / args.steps
@@ -877,7 +875,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "block_frac_of_tensor_peak": round(bf / tensor_peak, 4),
             "block_frac_burst": round(bf / peaks["tflops_burst"], 4), "block_frac_sustained": round(bf / peaks["tflops_sustained"], 4),
             "roofline": roofline, "cpu_baseline": cpu,
-            "e2e": {"value": ms_e2e / world, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": ms_e2e / world, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "kfold_b200.host_pipeline.HostPipeline: every step copies its inputs in from pinned host memory and "
+                           "its result out; copies of neighbouring steps overlap the compute on three streams, two steps in flight"},
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
             "trunk48_ms": None if trunk is None else trunk["ms"], "trunk48": trunk,
             "sampler_200x5": sampler_run,

@@ -128,6 +128,11 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
  *                        the normalised rows (a second call on the same tensor, e.g. the gate logits issued after the
  *                        operands so that they run under the operands' exchange).  transposed != 0: the operands are
  *                        written transposed, ab_out [2c][n][rows] (the incoming direction's a[k][i] at [i][k]).
+ *                        parts > 1 (4c a multiple of 256 * parts): only part `part` of the 2c operand channels, in the
+ *                        packed order, into ab_out = that part's buffer [2c / parts][..][..] -- the caller starts the
+ *                        exchange of one part while the next is projected.
+ *   kfb_trimul_contract : the contraction alone on `cpart` channels (a, t: [cpart][rows][n]; b in gathered pieces), so that
+ *                        one half of the channels is contracted while the other half's operand is still in flight.
  *   (the caller all-gathers operand b: every rank's [c][rows][n] piece, rank after rank)
  *   kfb_trimul_finish  : contraction of the local a rows against all rows of b, LayerNorm_out, gated output
  *                        projection (+ resid).  b_gathered: pieces of b_piece_rows rows, b_piece_stride elements
@@ -151,7 +156,10 @@ KFB_API int kfb_triatt_fwd(int ending, const void* x, const unsigned char* mask,
  */
 KFB_API int kfb_trimul_project(const void* x, const unsigned char* mask, const float* ln_in_w, const float* ln_in_b,
                                const void* w_in_packed, const void* w_gout, void* xn_scratch, void* ab_out, void* gl_out,
-                               int batch, int rows, int n, int c, int transposed, float eps, int dtype, void* stream);
+                               int batch, int rows, int n, int c, int transposed, int part, int parts, float eps, int dtype,
+                               void* stream);
+KFB_API int kfb_trimul_contract(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride, void* t, int rows,
+                                int n, int cpart, void* stream);
 KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride,
                               const void* gl, const float* ln_out_w, const float* ln_out_b, const void* w_pout,
                               void* t_scratch, void* tn_scratch, void* out, const void* resid, int rows, int n, int c,

@@ -54,7 +54,8 @@ _SIGNATURES = {
     "kfb_ln_linear_fp32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_ll,
                            c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_contract_cs": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_trimul_project": [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "kfb_trimul_contract": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p],
     "kfb_layernorm_exchange": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "kfb_trimul_finish": [c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],

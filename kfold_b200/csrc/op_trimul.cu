@@ -46,9 +46,10 @@ int check_shape(const char* what, int batch, int rows, int n, int c) {
 
 // steps 1-3 on a (batch, rows, n, c) tensor.  transposed_walk writes a^T, b^T: ab[ch][b][column][row of the shard].
 // x == nullptr: xn already holds the normalised input (a second call on the same tensor).
+// parts > 1: only part `part` of the 2c operand channels (in packed order) is projected, into `ab` = that part's buffer.
 int project(cudaStream_t stream, int transposed_walk, const void* x, const unsigned char* mask, const float* ln_w,
             const float* ln_b, const void* w_in_packed, const void* w_gout, __nv_bfloat16* xn, __nv_bfloat16* ab,
-            __nv_bfloat16* gl, int batch, int rows, int n, int c, float eps, int dtype) {
+            __nv_bfloat16* gl, int batch, int rows, int n, int c, float eps, int dtype, int part = 0, int parts = 1) {
   const long long rn = static_cast<long long>(rows) * n;
   const long long pos = rn * batch;
   if (x != nullptr) KFB_TRY(launch_layernorm(stream, x, xn, ln_w, ln_b, pos, c, c, c, eps, dtype, KFB_BF16));
@@ -58,13 +59,13 @@ int project(cudaStream_t stream, int transposed_walk, const void* x, const unsig
     p.n_extent = transposed_walk ? rows : n;
     p.o_extent = transposed_walk ? n : rows;
     p.batch = batch;
-    p.n_cols = 4 * c;
+    p.n_cols = 4 * c / parts;
     p.k_extent = c;
     p.glu = GLU_SIGMOID;
     p.nseg = 1;
     EpiSeg& s = p.seg[0];
     s.col_begin = 0;
-    s.ncols = 2 * c;
+    s.ncols = 2 * c / parts;
     s.out_fp32 = 0;
     s.vec = 0;
     s.dst = ab;
@@ -79,7 +80,7 @@ int project(cudaStream_t stream, int transposed_walk, const void* x, const unsig
     p.m_n = transposed_walk ? n : 1;
     GemmOperandA a = {xn, transposed_walk ? static_cast<long long>(n) * c : c,
                       transposed_walk ? c : static_cast<long long>(n) * c, rn * c};
-    GemmOperandB b = {w_in_packed, c, 0};
+    GemmOperandB b = {static_cast<const __nv_bfloat16*>(w_in_packed) + static_cast<long long>(part) * (4 * c / parts) * c, c, 0};
     KFB_TRY(launch_gemm_bf16(stream, a, b, p, 256, "trimul_in_proj"));
   }
   if (w_gout != nullptr) {
@@ -333,15 +334,49 @@ KFB_API int kfb_trimul_fwd(int incoming, const void* x, const unsigned char* mas
 
 KFB_API int kfb_trimul_project(const void* x, const unsigned char* mask, const float* ln_in_w, const float* ln_in_b,
                                const void* w_in_packed, const void* w_gout, void* xn_scratch, void* ab_out, void* gl_out,
-                               int batch, int rows, int n, int c, int transposed, float eps, int dtype, void* stream_) {
+                               int batch, int rows, int n, int c, int transposed, int part, int parts, float eps, int dtype,
+                               void* stream_) {
   KFB_CHECK_ARG(xn_scratch, "trimul_project: null pointer");
+  KFB_CHECK_ARG(parts >= 1 && part >= 0 && part < parts && (4 * c) % (256 * parts) == 0,
+                "trimul_project: part %d of %d needs 4C=%d to split into whole 256-column tiles", part, parts, 4 * c);
   KFB_CHECK_ARG((w_in_packed == nullptr) == (ab_out == nullptr) && (w_gout == nullptr) == (gl_out == nullptr),
                 "trimul_project: each weight needs its output buffer and vice versa");
   KFB_CHECK_ARG(w_in_packed == nullptr || mask != nullptr, "trimul_project: the input projection needs the mask");
   KFB_CHECK_ARG(is_dtype(dtype), "trimul_project: bad dtype %d", dtype);
   KFB_TRY(check_shape("trimul_project", batch, rows, n, c));
   return project(as_stream(stream_), transposed ? 1 : 0, x, mask, ln_in_w, ln_in_b, w_in_packed, w_gout, static_cast<__nv_bfloat16*>(xn_scratch),
-                 static_cast<__nv_bfloat16*>(ab_out), static_cast<__nv_bfloat16*>(gl_out), batch, rows, n, c, eps, dtype);
+                 static_cast<__nv_bfloat16*>(ab_out), static_cast<__nv_bfloat16*>(gl_out), batch, rows, n, c, eps, dtype, part,
+                 parts);
+}
+
+// The contraction alone, on `cpart` channels: t[ch][i][j] = sum_k a[ch][i][k] b[ch][j][k] with b in gathered pieces (as in
+// kfb_trimul_finish).  Lets the caller contract one half of the channels while the other half's operand is still in flight;
+// kfb_trimul_finish is then called with a = b = NULL.
+KFB_API int kfb_trimul_contract(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride, void* t, int rows,
+                                int n, int cpart, void* stream_) {
+  KFB_CHECK_ARG(a && b_gathered && t && cpart >= 1, "trimul_contract: null pointer");
+  KFB_CHECK_ARG(rows >= 1 && rows <= n && n % 8 == 0, "trimul_contract: rows=%d N=%d", rows, n);
+  KFB_CHECK_ARG(b_piece_rows >= 64 && n % b_piece_rows == 0 && b_piece_rows % 64 == 0 && b_piece_stride % 8 == 0,
+                "trimul_contract: pieces of %d rows (multiple of 64 dividing N=%d), stride %lld", b_piece_rows, n, b_piece_stride);
+  const long long rn = static_cast<long long>(rows) * n;
+  GemmParams p = {};
+  p.n_extent = rows;
+  p.o_extent = 1;
+  p.batch = cpart;
+  p.n_cols = n;
+  p.k_extent = n;
+  p.b_batched = 1;
+  p.nseg = 1;
+  p.seg[0] = row_major_seg(t, n, n, 0, rn, 0);
+  GemmOperandA oa = {a, n, 0, rn};
+  GemmOperandB ob = {b_gathered, n, static_cast<long long>(b_piece_rows) * n};
+  int force_bn = 0;
+  if (b_piece_rows != n) {
+    ob.col_inner = b_piece_rows;
+    ob.s_col_hi = b_piece_stride;
+    force_bn = b_piece_rows % 256 == 0 ? 256 : (b_piece_rows % 128 == 0 ? 128 : 64);
+  }
+  return launch_gemm_bf16(as_stream(stream_), oa, ob, p, force_bn, "trimul_contraction");
 }
 
 KFB_API int kfb_trimul_finish(const void* a, const void* b_gathered, int b_piece_rows, long long b_piece_stride,

@@ -48,21 +48,23 @@ def _dev(t: torch.Tensor, device, dtype) -> torch.Tensor:
     return t.detach().to(device=device, dtype=dtype).contiguous()
 
 
-def channel_shard_order(c: int, world: int) -> torch.Tensor:
-    """Order of the 2c operand channels [a | b] in which rank q's share comes first for q = 0, 1, ...:
-    [q][a, b][c / world].  Position (q, s, i) holds source channel s*c + q*(c/world) + i."""
-    cl = c // world
-    q, s_, i = torch.meshgrid(torch.arange(world), torch.arange(2), torch.arange(cl), indexing="ij")
-    return (s_ * c + q * cl + i).reshape(-1)
+def channel_shard_order(c: int, world: int, parts: int = 1) -> torch.Tensor:
+    """Order of the 2c operand channels [a | b] for the channel-sharded exchange: `parts` groups of c / parts channels
+    that are exchanged one after the other, inside each group rank q's share first for q = 0, 1, ...:
+    [h][q][a, b][c / (parts * world)].  Position (h, q, s, i) holds source channel s*c + h*(c/parts) + q*cl + i, so that
+    the contraction result, returned group by group and rank by rank, lies in the original channel order."""
+    cl = c // (world * parts)
+    h, q, s_, i = torch.meshgrid(torch.arange(parts), torch.arange(world), torch.arange(2), torch.arange(cl), indexing="ij")
+    return (s_ * c + h * (c // parts) + q * cl + i).reshape(-1)
 
 
-def pack_trimul(w: dict, device, dtype=torch.bfloat16, precise: bool = False, shard_world: int = 0) -> dict:
+def pack_trimul(w: dict, device, dtype=torch.bfloat16, precise: bool = False, shard_world: int = 0, shard_parts: int = 1) -> dict:
     """Weights of TriangleMultiplication{Outgoing,Incoming}: keys as in the reference state_dict
     (model/primitives/triangle_multiplication.py:171-177).  LayerNorm affine stays fp32.
     ``shard_world`` > 1 orders the operand channels for the channel-sharded exchange (channel_shard_order)."""
     wp, wg = w["linear_p_in.weight"].detach().float(), w["linear_g_in.weight"].detach().float()
     if shard_world > 1:
-        order = channel_shard_order(wp.shape[0] // 2, shard_world).to(wp.device)
+        order = channel_shard_order(wp.shape[0] // 2, shard_world, shard_parts).to(wp.device)
         wp, wg = wp[order], wg[order]
     return {
         "ln_in_w": _dev(w["layernorm_in.weight"], device, torch.float32),

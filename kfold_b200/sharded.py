@@ -124,42 +124,57 @@ class ShardedPairOps:
     # ------------------------------------------------------------------ triangle multiplication
     def _trimul_cs(self, x_loc: torch.Tensor, mask_loc: torch.Tensor, pk: dict, eps: float, incoming: bool):
         """Channel-sharded exchange, either direction, from the row shard alone.  `pk` must come from
-        pack_trimul(..., shard_world=world): the projection then writes the operand channels rank by rank, [q][a, b][C/P],
-        which is the send buffer of the all-to-all as it lies.  The incoming direction projects with the transposed walk
-        (a[k][i] stored at [i][k]) and contracts over a K that lies in one piece per source rank: no transpose of z."""
+        pack_trimul(..., shard_world=world, shard_parts=parts): the projection then writes the operand channels group by
+        group and rank by rank, [h][q][a, b][C/(parts P)], each group the send buffer of an all-to-all as it lies.  The
+        incoming direction projects with the transposed walk (a[k][i] stored at [i][k]) and contracts over a K that lies
+        in one piece per source rank: no transpose of z.  With two groups the exchanges of one run under the projection
+        and the contraction of the other."""
         rows, n, c = x_loc.shape
-        world, cl = self.world, c // self.world
+        world, parts = self.world, pk.get("shard_parts", 1)
+        cl = c // (world * parts)
         dev = x_loc.device
         lib = L.lib()
         dt = L.dtype_code(x_loc.dtype)
         xn = _bf16((rows * n, c), dev)
-        ab = _bf16((world, 2, cl, n, rows) if incoming else (world, 2, cl, rows, n), dev)
         gl = _bf16((rows * n, c), dev)
         m8 = mask_loc.to(torch.bool).contiguous().view(torch.uint8)
         x_loc = x_loc.contiguous()
         tr = 1 if incoming else 0
+        shape = (world, 2, cl, n, rows) if incoming else (world, 2, cl, rows, n)
+        t = _bf16((parts, world, cl, rows, n), dev)          # = t [c][rows][n] in the original channel order
         with L.on_device(dev):
             st = L.stream_ptr()
-            L.check(lib.kfb_trimul_project(L.ptr(x_loc), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
-                                           None, L.ptr(xn), L.ptr(ab), None, 1, rows, n, c, tr, eps, dt, st))
-            ab_recv = torch.empty_like(ab)
-            work = dist.all_to_all_single(ab_recv, ab, group=self.group, async_op=True)   # [source rank][a, b][cl][..][..]
-            # the output-gate logits, from the rows normalised above, while the exchange is in flight
+            sends, recvs, works = [], [], []
+            for h in range(parts):
+                ab = _bf16(shape, dev)
+                L.check(lib.kfb_trimul_project(L.ptr(x_loc) if h == 0 else None, L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]),
+                                               L.ptr(pk["w_in"]), None, L.ptr(xn), L.ptr(ab), None, 1, rows, n, c, tr, h, parts, eps,
+                                               dt, st))
+                ab_recv = torch.empty_like(ab)
+                works.append(dist.all_to_all_single(ab_recv, ab, group=self.group, async_op=True))   # [source rank][a, b][cl]..
+                sends.append(ab)
+                recvs.append(ab_recv)
+            # the output-gate logits, from the rows normalised above, while the exchanges are in flight
             L.check(lib.kfb_trimul_project(None, None, None, None, None, L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows,
-                                           n, c, 0, eps, dt, st))
-            work.wait()
-            t_send = _bf16((world, cl, rows, n), dev)
-            L.check(lib.kfb_trimul_contract_cs(L.ptr(ab_recv), L.ptr(t_send), world, rows, n, cl, tr, L.stream_ptr()))
-            t = torch.empty_like(t_send)
-            dist.all_to_all_single(t, t_send, group=self.group)         # [channel group][cl][rows][n] = t [c][rows][n]
+                                           n, c, 0, 0, 1, eps, dt, st))
+            back = []
+            for h in range(parts):
+                works[h].wait()
+                t_send = _bf16((world, cl, rows, n), dev)
+                L.check(lib.kfb_trimul_contract_cs(L.ptr(recvs[h]), L.ptr(t_send), world, rows, n, cl, tr, st))
+                back.append((dist.all_to_all_single(t[h], t_send, group=self.group, async_op=True), t_send))
+            for work, _ in back:
+                work.wait()
             out = torch.empty_like(x_loc)
             L.check(lib.kfb_trimul_finish(None, None, rows, 0, L.ptr(gl), L.ptr(pk["ln_out_w"]), L.ptr(pk["ln_out_b"]),
                                           L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out), L.ptr(x_loc), rows, n, c, eps,
-                                          dt, L.stream_ptr()))
+                                          dt, st))
         return out
 
     def _trimul(self, x_ab: torch.Tensor, mask_ab: torch.Tensor, x_row: torch.Tensor, pk: dict, eps: float):
-        """All-gather form: a, b from (x_ab, mask_ab); gate logits and residual from x_row.  All (rows, N, ...) shards."""
+        """All-gather form: a, b from (x_ab, mask_ab); gate logits and residual from x_row.  All (rows, N, ...) shards.
+        Operand b is projected first and gathered in two channel halves; a and the gate logits are projected, and the
+        first half contracted, while the gathers are in flight."""
         rows, n, c = x_row.shape
         dev = x_row.device
         lib = L.lib()
@@ -170,22 +185,37 @@ class ShardedPairOps:
         m8 = mask_ab.to(torch.bool).contiguous().view(torch.uint8)
         x_ab = x_ab.contiguous()
         x_row = x_row.contiguous()
+        split = c % 128 == 0              # the projection then divides into whole tiles per operand, the channels into halves
+        rn = rows * n
         with L.on_device(dev):
             st = L.stream_ptr()
             same = x_ab.data_ptr() == x_row.data_ptr()
-            L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
-                                           None, L.ptr(xn), L.ptr(ab), None, 1, rows, n, c, 0, eps, dt, st))
-            # [world][c][rows][n], rank after rank; the gate logits are projected while the gather is in flight
-            b_full = torch.empty((self.world * c, rows, n), dtype=torch.bfloat16, device=dev)
-            work = dist.all_gather_into_tensor(b_full, ab[c:], group=self.group, async_op=True)
+            if not split:
+                L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
+                                               None, L.ptr(xn), L.ptr(ab), None, 1, rows, n, c, 0, 0, 1, eps, dt, st))
+                halves = [(0, c)]
+            else:
+                L.check(lib.kfb_trimul_project(L.ptr(x_ab), L.ptr(m8), L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), L.ptr(pk["w_in"]),
+                                               None, L.ptr(xn), L.ptr(ab[c:]), None, 1, rows, n, c, 0, 1, 2, eps, dt, st))
+                halves = [(0, c // 2), (c // 2, c)]
+            gathers = []
+            for lo, hi in halves:      # [world][channels of the half][rows][n], rank after rank
+                b_full = torch.empty((self.world * (hi - lo), rows, n), dtype=torch.bfloat16, device=dev)
+                gathers.append((dist.all_gather_into_tensor(b_full, ab[c + lo:c + hi], group=self.group, async_op=True), b_full))
+            if split:
+                L.check(lib.kfb_trimul_project(None, L.ptr(m8), None, None, L.ptr(pk["w_in"]), None, L.ptr(xn), L.ptr(ab), None, 1,
+                                               rows, n, c, 0, 0, 2, eps, dt, st))
             L.check(lib.kfb_trimul_project(None if same else L.ptr(x_row), None, L.ptr(pk["ln_in_w"]), L.ptr(pk["ln_in_b"]), None,
-                                           L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, 0, eps, dt, st))
-            work.wait()
+                                           L.ptr(pk["w_gout"]), L.ptr(xn), None, L.ptr(gl), 1, rows, n, c, 0, 0, 1, eps, dt, st))
             t = _bf16((c, rows, n), dev)
+            for (lo, hi), (work, b_full) in zip(halves, gathers):
+                work.wait()
+                L.check(lib.kfb_trimul_contract(L.ptr(ab[lo:hi]), L.ptr(b_full), rows, (hi - lo) * rn, L.ptr(t[lo:hi]), rows, n,
+                                                hi - lo, st))
             out = torch.empty_like(x_row)
-            L.check(lib.kfb_trimul_finish(L.ptr(ab), L.ptr(b_full), rows, c * rows * n, L.ptr(gl), L.ptr(pk["ln_out_w"]),
-                                          L.ptr(pk["ln_out_b"]), L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out),
-                                          L.ptr(x_row), rows, n, c, eps, dt, L.stream_ptr()))
+            L.check(lib.kfb_trimul_finish(None, None, rows, 0, L.ptr(gl), L.ptr(pk["ln_out_w"]), L.ptr(pk["ln_out_b"]),
+                                          L.ptr(pk["w_pout"]), L.ptr(t), L.ptr(xn), L.ptr(out), L.ptr(x_row), rows, n, c, eps, dt,
+                                          st))
         return out
 
     def _channel_form(self, pk: dict, rows: int) -> bool:
@@ -301,8 +331,9 @@ class ShardedPairformerBlock:
             return mod._packed(dev, torch.bfloat16, packing.pack_trimul)
         key = (id(mod), dev)
         if key not in self._trimul_packs:
-            pk = packing.pack_trimul(mod.state_dict(), dev, shard_world=world)
-            pk["shard_world"] = world
+            parts = 2 if (c % 128 == 0 and (c // world) % 2 == 0) else 1     # two exchange groups when the tiles divide
+            pk = packing.pack_trimul(mod.state_dict(), dev, shard_world=world, shard_parts=parts)
+            pk["shard_world"], pk["shard_parts"] = world, parts
             self._trimul_packs[key] = pk
         return self._trimul_packs[key]
 

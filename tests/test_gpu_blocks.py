@@ -238,3 +238,24 @@ def test_token_transformer_production_width(dev):
 
 def test_tolerances_are_the_stated_ones():
     assert RMS_TOL == 1e-2 and MAX_TOL == 0.15
+
+
+def test_host_pipeline_matches_direct_calls(dev):
+    """host_pipeline.HostPipeline: five different host-resident inputs through a Transition with the copies overlapped;
+    every result equals the one of the plain call on that input, and unpinned buffers are refused."""
+    from kfold_b200 import modules as M
+    from kfold_b200.host_pipeline import HostPipeline
+    import synth
+    c = 128
+    mod = M.Transition(c, 4).to(dev)
+    mod.load_state_dict(synth.transition_weights(synth._Rng(5), c, 4), strict=True)
+    g = torch.Generator().manual_seed(9)
+    xs = [torch.randn(1, 96, 96, c, generator=g).bfloat16().pin_memory() for _ in range(5)]
+    outs = [(torch.empty_like(x).pin_memory(),) for x in xs]
+    pipe = HostPipeline(lambda x: mod(x, residual=True), dev, depth=2)
+    pipe.run([(x,) for x in xs], outs)
+    torch.cuda.synchronize()
+    for x, (o,) in zip(xs, outs):
+        assert torch.equal(o, mod(x.to(dev), residual=True).cpu())
+    with pytest.raises(ValueError):
+        pipe.run([(torch.zeros(1, 8, 8, c),)], [(torch.zeros(1, 8, 8, c),)])

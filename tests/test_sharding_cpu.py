@@ -113,3 +113,20 @@ def test_channel_shard_order_is_a_permutation():
     o = packing.channel_shard_order(128, 8)
     assert sorted(o.tolist()) == list(range(256))
     assert o[:3].tolist() == [0, 1, 2] and o[16] == 128 and o[32] == 16     # rank 0: a[0:16], b[0:16]; rank 1: a[16:32]
+
+
+@pytest.mark.parametrize("c,world,parts", [(128, 8, 2), (128, 2, 2), (256, 4, 2), (64, 4, 1)])
+def test_channel_shard_order_groups(c, world, parts):
+    """The operand channel order of the grouped channel exchange: group h, rank q holds a- and b-channels
+    h*(c/parts) + q*cl .. + cl, so that the results returned group by group and rank by rank are in channel order."""
+    from kfold_b200 import packing
+    cl = c // (world * parts)
+    order = packing.channel_shard_order(c, world, parts).view(parts, world, 2, cl)
+    assert sorted(order.reshape(-1).tolist()) == list(range(2 * c))
+    for h in range(parts):
+        for q in range(world):
+            want = h * (c // parts) + q * cl + torch.arange(cl)
+            assert torch.equal(order[h, q, 0], want) and torch.equal(order[h, q, 1], c + want)
+    # the contraction results come back as [h][q][cl]: flat position = channel index
+    back = order[:, :, 0].reshape(-1)
+    assert torch.equal(back, torch.arange(c))
