@@ -286,7 +286,7 @@ def run_reference_triton_arm(args, rank: int) -> None:
             for name, mod in mods.items():
                 for _ in range(max(args.warmup, 3)):      # the first call JIT-compiles (and autotunes) the kernels
                     mod(zd, pmd)
-                per_op[name] = round(_event_time(lambda: mod(zd, pmd), args.steps, stream, lambda: None), 4)
+                per_op[name] = round(_event_time(lambda: mod(zd, pmd), args.steps, stream, torch.cuda.synchronize), 4)
         total = sum(per_op.values())
         emit({"impl": "reference_triton", "metric": "pair_operators_fwd_ms_n768_bf16", "value": total, "unit": "ms", "n_gpus": 1,
               "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total, "higher_is_better": False, "dtype": "bf16",
@@ -563,9 +563,18 @@ def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
     for _ in range(2):
         blk(zd, sd, pmd, md)
     ms_1gpu = _event_time(lambda: blk(zd, sd, pmd, md), steps, stream, barrier)
-    res = {"n_token": n, "ms_1gpu": round(ms_1gpu, 3)}
+
+    def trunk_1gpu():
+        zt, st = zd, sd
+        for _ in range(48):
+            zt, st = blk(zt, st, pmd, md)
+
+    # the 48-block trunk of benchmark config 5 on one GPU: one pass (about three seconds)
+    ms_trunk_1gpu = _event_time(trunk_1gpu, 1, stream, barrier)
+    res = {"n_token": n, "ms_1gpu": round(ms_1gpu, 3), "trunk48_ms_1gpu": round(ms_trunk_1gpu, 2)}
     if world == 1:
-        res.update(ms=round(ms_1gpu, 3), speedup_vs_1gpu=1.0, exchange="none (one GPU: the plain block)")
+        res.update(ms=round(ms_1gpu, 3), speedup_vs_1gpu=1.0, trunk48_ms=round(ms_trunk_1gpu, 2),
+                   exchange="none (one GPU: the plain block)")
         return res
     from kfold_b200 import sharded as SH
     r0, r1 = SH.shard_rows(n, world, rank)
@@ -583,6 +592,13 @@ def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
     prof = L.profile_report()
     L.profile_enable(False)
     kernel_ms = sum(t for _, t in prof.values()) / steps
+
+    def trunk_sharded():      # 48 sharded blocks back to back: the transposed mask is exchanged once and reused
+        zt, st = z_loc, sd
+        for _ in range(48):
+            zt, st = sblk(zt, st, pm_loc, md)
+
+    ms_trunk = _event_time(trunk_sharded, 1, stream, barrier)
     # a plain NCCL all-to-all of the size of one shard transpose, for the bandwidth the exchanges could reach
     probe = torch.empty(n * n * C_Z // world, dtype=torch.bfloat16, device=dev)
     probe_out = torch.empty_like(probe)
@@ -591,20 +607,22 @@ def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
     ms_probe = _event_time(lambda: dist.all_to_all_single(probe_out, probe), 5, stream, barrier)
     sent = probe.numel() * 2 * (world - 1) / world
     a2a_gbs = sent / (ms_probe * 1e-3) / 1e9
-    t = torch.tensor([ms, kernel_ms, ms_1gpu, ms_probe], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, kernel_ms, ms_1gpu, ms_probe, ms_trunk, ms_trunk_1gpu], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, kernel_ms, ms_1gpu, ms_probe = (float(v) for v in t)
+    ms, kernel_ms, ms_1gpu, ms_probe, ms_trunk, ms_trunk_1gpu = (float(v) for v in t)
     out_bytes = sharded_bytes_out(n, C_Z, 4, 16, world, channel)
     bound_ms = out_bytes / (a2a_gbs * 1e9) * 1e3
     res.update(ms=round(ms, 3), ms_1gpu=round(ms_1gpu, 3), kernel_ms=round(kernel_ms, 3), comm_ms=round(ms - kernel_ms, 3),
                exchange="channel all-to-all" if channel else "all-gather of b",
-               speedup_vs_1gpu=round(ms_1gpu / ms, 3), bytes_sent_per_rank=out_bytes,
+               speedup_vs_1gpu=round(ms_1gpu / ms, 3), trunk48_ms=round(ms_trunk, 2), trunk48_ms_1gpu=round(ms_trunk_1gpu, 2),
+               trunk48_speedup=round(ms_trunk_1gpu / ms_trunk, 3), bytes_sent_per_rank=out_bytes,
                nccl_all_to_all_gbs_per_rank=round(a2a_gbs, 1), comm_bound_ms=round(bound_ms, 3),
                note="comm_ms = step time - kernel time: collectives, reorder copies and host gaps not hidden under kernels")
     return res
 
 
-def measure_sampler(rank: int, world: int, dev, barrier, steps: int = 200, samples: int = 5) -> dict:
+def measure_sampler(rank: int, world: int, dev, barrier, steps: int = 200, samples: int = 5, nt: int = N_TOKENS_DEFAULT,
+                    na: int = 6016, seed_offset: int | None = None) -> dict:
     """Benchmark config 4's diffusion part: the 200-step ECSI sampler (kfold_b200.sampler.KFoldECSI.sample_structure) over
     5 samples of a 768-token, 6 016-atom complex, score network = atom encoder (3 blocks), 24-block token transformer
     (c=768, 16 heads), atom decoder (3 blocks), bf16 compute, the network replayed as a CUDA graph.  With several ranks
@@ -617,7 +635,6 @@ def measure_sampler(rank: int, world: int, dev, barrier, steps: int = 200, sampl
     from kfold_b200 import modules as M
     from kfold_b200.sampler import KFoldECSI
     import synth
-    nt, na = N_TOKENS_DEFAULT, 6016
     c_a, c_s, c_atom, c_pair, tb, th = 768, 384, 128, 16, 24, 16
     rng = synth._Rng(SEED)
     w = synth.diffusion_step_weights(rng, c_a, c_s, c_atom, c_pair, 3, 4, tb, th, 6, False)
@@ -637,28 +654,61 @@ def measure_sampler(rank: int, world: int, dev, barrier, steps: int = 200, sampl
     stream = torch.cuda.current_stream()
     res = {}
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-        torch.manual_seed(SEED + rank)
-        sampler.sample_structure(f_input, s_inputs, None, num_steps=4, num_samples=samples, precomputed=pre, cuda_graph=True)   # warm-up
-        barrier()
+        torch.manual_seed(SEED + (rank if seed_offset is None else seed_offset))
         launches0 = L.launch_count()
+        if samples > 0:
+            sampler.sample_structure(f_input, s_inputs, None, num_steps=4, num_samples=samples, precomputed=pre, cuda_graph=True)   # warm-up
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record(stream)
-        out = sampler.sample_structure(f_input, s_inputs, None, num_steps=steps, num_samples=samples, precomputed=pre, cuda_graph=True)
+        finite = True
+        if samples > 0:      # a rank that was dealt no sample only joins the barriers
+            out = sampler.sample_structure(f_input, s_inputs, None, num_steps=steps, num_samples=samples, precomputed=pre,
+                                           cuda_graph=True)
         e1.record(stream)
         barrier()
         wall = time.perf_counter() - t0
         ms = e0.elapsed_time(e1)
-        finite = bool(torch.isfinite(out["coordinates"]).all())
+        if samples > 0:
+            finite = bool(torch.isfinite(out["coordinates"]).all())
     if world > 1:
         t = torch.tensor([ms, wall], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, wall = float(t[0]), float(t[1])
     res.update(steps=steps, samples=samples, tokens=nt, atoms=na, seconds=round(ms / 1e3, 4), ms_per_step=round(ms / steps, 3),
                wall_seconds=round(wall, 4), structures_per_s=round(world * samples / (ms / 1e3), 3), seeds=world, finite=finite,
+               ms=ms,
                device_status=L.device_status(),
                note="eager launches counted by the library (the graph-replayed network launches are not): "
                     f"{L.launch_count() - launches0}; includes the one-off graph capture of the network")
+    return res
+
+
+def measure_config5(rank: int, world: int, dev, barrier, sharded_res: dict) -> dict:
+    """Benchmark config 5 assembled: N=2048 tokens (16 064 atoms), the 48-block trunk plus the 200-step sampler for 5 samples.
+    One GPU: the plain trunk, then the five samples as one batch.  N ranks: the row-sharded trunk (measure_sharded), then
+    the five samples dealt out to the ranks (sample i on rank i mod N), every rank with the full pair bias.  The one-GPU
+    figures are measured in this same run (every rank runs them; maximum over the ranks)."""
+    import torch.distributed as dist
+    nt, na = 2048, 16064
+    one = measure_sampler(rank, 1, dev, barrier, samples=5, nt=nt, na=na, seed_offset=0)
+    res = {"n_token": nt, "n_atom": na, "samples": 5, "steps": 200, "trunk48_s_1gpu": round(sharded_res["trunk48_ms_1gpu"] / 1e3, 3),
+           "sampler_s_1gpu": round(one["ms"] / 1e3, 3), "finite": one["finite"]}
+    res["total_s_1gpu"] = round(res["trunk48_s_1gpu"] + res["sampler_s_1gpu"], 3)
+    if world == 1:
+        res.update(trunk48_s=res["trunk48_s_1gpu"], sampler_s=res["sampler_s_1gpu"], total_s=res["total_s_1gpu"], speedup=1.0)
+        return res
+    mine = len(range(rank, 5, world))
+    part = measure_sampler(rank, world, dev, barrier, samples=mine, nt=nt, na=na, seed_offset=0)
+    t = torch.tensor([one["ms"], part["ms"], 0.0 if (one["finite"] and part["finite"]) else 1.0], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res.update(sampler_s_1gpu=round(float(t[0]) / 1e3, 3), trunk48_s=round(sharded_res["trunk48_ms"] / 1e3, 3),
+               sampler_s=round(float(t[1]) / 1e3, 3), samples_per_rank=[len(range(r, 5, world)) for r in range(world)],
+               finite=bool(t[2] == 0))
+    res["total_s_1gpu"] = round(res["trunk48_s_1gpu"] + res["sampler_s_1gpu"], 3)
+    res["total_s"] = round(res["trunk48_s"] + res["sampler_s"], 3)
+    res["speedup"] = round(res["total_s_1gpu"] / res["total_s"], 3)
     return res
 
 
@@ -753,6 +803,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     sampler_run = None
     sharded_n2048 = None
     parity = None
+    config5 = None
     with torch.no_grad():
         # ---- device-resident timing (with per-launch events recorded by the library)
         for _ in range(args.warmup):
@@ -816,6 +867,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             sharded_n2048 = measure_sharded(args, rank, world, dev, blk, barrier)
             if world > 1:
                 parity = measure_sharded_parity(rank, world, dev, blk, w)
+            from kfold_b200 import functional as _F
+            _F.release_workspaces()
+            torch.cuda.empty_cache()
+            config5 = measure_config5(rank, world, dev, barrier, sharded_n2048)
         status = status or L.device_status()
 
     if world > 1:
@@ -882,7 +937,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "trunk48_ms": None if trunk is None else trunk["ms"], "trunk48": trunk,
             "sampler_200x5": sampler_run,
             "config4_s": None if trunk is None or sampler_run is None else round(trunk["ms"] / 1e3 + sampler_run["seconds"], 4),
-            "sharded_n2048": sharded_n2048, "sharded_parity": parity, "kernels": kernels,
+            "sharded_n2048": sharded_n2048, "sharded_parity": parity, "config5_n2048": config5, "kernels": kernels,
         }
         if trunk is not None and trunk["clocks"].get("sm_mhz"):
             tp, tk = pick_tensor_peak(peaks, trunk["region_s"], trunk["clocks"])

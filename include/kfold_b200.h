@@ -394,6 +394,16 @@ KFB_API int kfb_gelu(const void* x, void* y, long long n, int in_dtype, int out_
  */
 KFB_API int kfb_concat_layernorm(const void* z, int z_dtype, const void* rel, int rel_dtype, const float* ln_w, const float* ln_b,
                                  float* out, long long rows, int c1, int c2, int k_pad, float eps, void* stream);
+/*
+ * The same with the relative-position encoding computed inside the kernel instead of read: replaces
+ * `self.rel_pos_encoding(f_input, z.dtype)` (src/kfold/model/layers/folding/embeddings.py:58-130, AF3 Algorithm 3) together with
+ * the concatenation and the LayerNorm; the (batch, n, n, 4 (r_max + 1) + 2 (s_max + 1) + 1) one-hot tensor never exists.
+ * asym_id, residue_index, entity_id, token_index, sym_id: int64 [batch][n] (the fields of FoldingInput.token).  z (batch, n, n, c1).
+ */
+KFB_API int kfb_relpos_concat_layernorm(const void* z, int z_dtype, const long long* asym_id, const long long* residue_index,
+                                        const long long* entity_id, const long long* token_index, const long long* sym_id,
+                                        int r_max, int s_max, const float* ln_w, const float* ln_b, float* out, int batch, int n, int c1,
+                                        int k_pad, float eps, void* stream);
 
 /*
  * Pair-tensor preparation of the confidence head (src/kfold/model/modules/confidence_head.py:306-470).

@@ -75,6 +75,8 @@ _SIGNATURES = {
                        c_float, c_int, c_void_p],
     "kfb_lm_pair_features": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
+    "kfb_relpos_concat_layernorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "kfb_concat_layernorm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_void_p],
     "kfb_pair_outer_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kfb_distogram_embed_add": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

@@ -25,9 +25,19 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUte
   KFB_CUDA(attr_err);
   const int total = p.num_m_tiles * p.num_n_tiles;
   const int grid = total < sm_count() ? total : sm_count();
+  GemmParams q = p;
+  {
+    // the persistent loops step by the grid size: its digits in the (n tile, row block, outer, batch) index
+    const int m_step = grid / q.num_n_tiles;
+    q.step_n_tile = grid - m_step * q.num_n_tiles;
+    q.step_nb = m_step % q.n_blocks;
+    const int rest = m_step / q.n_blocks;
+    q.step_o = rest % q.o_extent;
+    q.step_b = rest / q.o_extent;
+  }
   {
     LaunchScope scope(stream, tag);
-    gemm_bf16_kernel<BN, GLU, AUX, PRECISE, SWAP><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], p);
+    gemm_bf16_kernel<BN, GLU, AUX, PRECISE, SWAP><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, tout[0], tout[1], q);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
@@ -48,9 +58,15 @@ static int launch_bn(cudaStream_t stream, const CUtensorMap& ta, const CUtensorM
     }
   }
   if constexpr (BN == 256) {
-    if (p.glu && p.swap) return launch_variant<BN, true, false, false, true>(stream, ta, tb, tout, p, tag);
+    if (p.glu && p.swap) {
+      p.stages = Cfg::stages_for(Cfg::kSwapStagingBytes);
+      return launch_variant<BN, true, false, false, true>(stream, ta, tb, tout, p, tag);
+    }
   }
-  if (p.glu) return launch_variant<BN, true, false, false>(stream, ta, tb, tout, p, tag);
+  if (p.glu) {
+    p.stages = Cfg::stages_for(Cfg::kGluStagingBytes);
+    return launch_variant<BN, true, false, false>(stream, ta, tb, tout, p, tag);
+  }
   if constexpr (BN <= 128) {
     if (p.aux) return launch_variant<BN, false, true, false>(stream, ta, tb, tout, p, tag);
   }
@@ -135,6 +151,21 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
             !p.seg[0].out_fp32 && p.seg[0].col_begin == 0 && p.n_cols % 256 == 0 && p.col_bias == nullptr &&
             p.gate == nullptr && p.resid == nullptr && (p.rowmask == nullptr || (p.mask_segs & 1)))
                ? 1 : 0;
+  // ... and, when the destination satisfies the copy engine's alignment rules, stored as whole tiles by TMA
+  p.swap_staged = 0;
+  if (p.swap) {
+    const EpiSeg& sg = p.seg[0];
+    const bool aligned = (reinterpret_cast<uintptr_t>(sg.dst) & 15) == 0 && sg.s_col % 8 == 0 &&
+                         (sg.s_o % 8 == 0 && (sg.s_o != 0 || p.o_extent == 1)) && (sg.s_b % 8 == 0 && (sg.s_b != 0 || p.batch == 1));
+    if (aligned) {
+      const uint64_t dims[4] = {(uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)sg.ncols, (uint64_t)p.batch};
+      const uint64_t str[3] = {(uint64_t)sg.s_o * 2, (uint64_t)sg.s_col * 2, (uint64_t)sg.s_b * 2};
+      const uint32_t box[4] = {64, 1, kBM, 1};
+      KFB_TRY(make_tmap(&tout[0], sg.dst, 2, 4, dims, str, box, 128));
+      p.swap_staged = 1;
+      next_slot = 1;
+    }
+  }
   // trailing channel-major bf16 segments that start on a tile boundary are computed in the swapped orientation as well
   // (plain BN = 128 kernel): the threads then store runs of consecutive positions directly
   p.swap_col_begin = INT_MAX;
@@ -189,6 +220,28 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
         p.aux_resid = 1;
       }
       p.aux = 1;
+    }
+  }
+  // full tiles of one row-major bf16 segment of the plain BN = 128 kernel leave through shared memory and a TMA store
+  p.rm_seg = -1;
+  p.rm_slot = 0;
+  const bool rm_plain = bn == 128 && !p.glu;
+  const bool rm_glu = bn == 256 && p.glu && !p.swap;      // the GLU kernel: 128 output columns per tile
+  if ((rm_plain || rm_glu) && !p.precise && !p.aux && !p.a_mn_major && next_slot == 0) {
+    for (int i = 0; i < p.nseg; ++i) {
+      const EpiSeg& sg = p.seg[i];
+      if (rm_glu && (i != 0 || sg.ncols % 128 != 0)) break;   // the GLU route handles segment 0 made of whole tiles only
+      const bool ok_seg = sg.s_col == 1 && sg.vec && !sg.out_fp32 && sg.col_begin % 128 == 0 && sg.ncols >= 128 &&
+                          sg.col_begin < p.swap_col_begin && (reinterpret_cast<uintptr_t>(sg.dst) & 15) == 0 && sg.s_n % 8 == 0 &&
+                          (sg.s_o % 8 == 0 && (sg.s_o != 0 || p.o_extent == 1)) && (sg.s_b % 8 == 0 && (sg.s_b != 0 || p.batch == 1)) &&
+                          !((p.mask_segs >> i) & 1) && (i != 0 || (p.gate == nullptr && p.resid == nullptr));
+      if (!ok_seg) continue;
+      const uint64_t dims[4] = {(uint64_t)sg.ncols, (uint64_t)p.n_extent, (uint64_t)p.o_extent, (uint64_t)p.batch};
+      const uint64_t str[3] = {(uint64_t)sg.s_n * 2, (uint64_t)sg.s_o * 2, (uint64_t)sg.s_b * 2};
+      const uint32_t box[4] = {64, kBM, 1, 1};
+      KFB_TRY(make_tmap(&tout[0], sg.dst, 2, 4, dims, str, box, 128));
+      p.rm_seg = i;
+      break;
     }
   }
   switch (bn) {

@@ -50,6 +50,10 @@ struct GemmParams {
   int b_col_inner;                // rows of B are addressed as (col / b_col_inner, col % b_col_inner): an all-gathered
                                   // operand whose pieces lie rank after rank (launcher; = n_cols when not split)
   int n_blocks, num_m_tiles, num_n_tiles;
+  int step_n_tile, step_nb, step_o, step_b;  // launcher: the grid size as digits of (n tile, row block, outer, batch)
+  int swap_staged;                // launcher: the swapped GLU tile leaves through shared memory and TMA stores (map tm_out0)
+  int rm_seg, rm_slot;            // launcher: segment whose full tiles leave through shared memory and a TMA store (row-major
+                                  // bf16; BN = 128 plain kernel), and the output map it uses; rm_seg < 0: none
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
   int swap;                       // launcher: channel-major GLU output computed in the swapped orientation (see SWAP)
   int a_mn_major;                 // launcher: the A operand is stored K-outer ([k][row], rows contiguous) and read MN-major
@@ -94,7 +98,16 @@ struct GemmCfg {
   static constexpr int kBStage = BN * kBK * 2;
   static constexpr int kStageBytes = kAStage + kBStage;
   static constexpr int kMaxStages = 8;
-  static constexpr int kStagingBytes = (kEpiWarps / 4) * 2 * 32 * kBM * 2;  // per group of 4 epilogue warps: 2 slabs of [32 channels][128 rows] bf16
+  // per group of 4 epilogue warps: 2 slabs of [32 channels][128 rows] bf16 -- or, in the BN = 128 kernel, two whole row-major
+  // output tiles (two 64-column boxes of [128 rows][128 bytes] each) on their way to a TMA store
+  static constexpr int kSlabBytes = (kEpiWarps / 4) * 2 * 32 * kBM * 2;
+  static constexpr int kRowTileBytes = kBM * 128 * 2;
+  static constexpr int kStagingBytes = (BN == 128) ? 2 * kRowTileBytes : kSlabBytes;
+  // the GLU kernel at BN = 256 writes 128 output columns per tile: the same two row-major tile buffers
+  static constexpr int kGluStagingBytes = (BN == 256) ? 2 * kRowTileBytes : kStagingBytes;
+  // swapped-orientation GLU kernel (BN = 256): the tile's position mask (1 KB, two accumulators) and two whole
+  // channel-major output tiles ([2 boxes of 64 positions][128 channels][128 bytes])
+  static constexpr int kSwapStagingBytes = 1024 + 2 * kRowTileBytes;
   static constexpr int kBarrierBytes = 512;
   static constexpr int kSmemBytes = 232448 - 1024;        // everything an SM offers one CTA
   // after the operand ring comes EITHER the channel-major staging slabs OR two buffers of prefetched
@@ -208,6 +221,36 @@ __device__ __forceinline__ void epi_store_chunk(const EpiSeg& sg, long long row_
   }
 }
 
+// A tile index as (n tile, row block, outer, batch).  The persistent loops step by the grid size; stepping the mixed-radix
+// digits with carries replaces five integer divisions per tile and role (which cost the epilogue warps about 800 cycles
+// of every 4500-cycle tile).
+struct TileIdx {
+  int n_tile, nb, o, b;
+};
+__device__ __forceinline__ TileIdx tile_decompose(int tile, const GemmParams& p) {
+  TileIdx t;
+  const int m_tile = tile / p.num_n_tiles;
+  t.n_tile = tile - m_tile * p.num_n_tiles;
+  t.nb = m_tile % p.n_blocks;
+  const int rest = m_tile / p.n_blocks;
+  t.o = rest % p.o_extent;
+  t.b = rest / p.o_extent;
+  return t;
+}
+// t += grid size, whose digits the launcher put into the parameters (each below its radix)
+__device__ __forceinline__ void tile_advance(TileIdx& t, const GemmParams& p) {
+  t.n_tile += p.step_n_tile;
+  int carry = t.n_tile >= p.num_n_tiles ? 1 : 0;
+  t.n_tile -= carry ? p.num_n_tiles : 0;
+  t.nb += p.step_nb + carry;
+  carry = t.nb >= p.n_blocks ? 1 : 0;
+  t.nb -= carry ? p.n_blocks : 0;
+  t.o += p.step_o + carry;
+  carry = t.o >= p.o_extent ? 1 : 0;
+  t.o -= carry ? p.o_extent : 0;
+  t.b += p.step_b + carry;
+}
+
 // GLU and AUX are compile-time so that each variant carries only its own epilogue code (and registers):
 //   GLU  the tile holds values and gates (p.glu says which activation);
 //   AUX  gate logits / residual come from shared-memory tiles prefetched by the producer.
@@ -237,7 +280,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint8_t* s_b = smem + kStages * Cfg::kAStage;
   uint8_t* s_stage_out = smem + kStages * Cfg::kStageBytes;  // [group of 4 epilogue warps][2][32 channels][128 rows] bf16 ...
   uint8_t* s_aux = s_stage_out;                               // ... or [2 buffers][gate, resid][2 halves? BN/64][128 x 64] bf16
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stage_out + (AUX ? Cfg::kAuxBytes : Cfg::kStagingBytes));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(
+      s_stage_out + (AUX ? Cfg::kAuxBytes : (SWAP ? Cfg::kSwapStagingBytes : (GLU ? Cfg::kGluStagingBytes : Cfg::kStagingBytes))));
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kMaxStages;
   uint64_t* tmem_full = bars + 2 * Cfg::kMaxStages;
@@ -245,7 +289,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint64_t* aux_full = tmem_empty + 2;   // [2]
   uint64_t* aux_empty = aux_full + 2;    // [2], one arrival per epilogue warp
   uint64_t* cm_bar = aux_empty + 2;      // [2 groups][slab free, slab written], 128 arrivals each
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cm_bar + 4);
+  uint64_t* rm_bar = cm_bar + 4;         // [2 staging buffers]: row-major tile written, one arrival per epilogue thread
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rm_bar + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -273,6 +318,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       ptx::mbar_init(&aux_empty[a], kEpiWarps);
     }
     for (int a = 0; a < 4; ++a) ptx::mbar_init(&cm_bar[a], 128);
+    for (int a = 0; a < 2; ++a) ptx::mbar_init(&rm_bar[a], 32 * kEpiWarps);
     ptx::fence_barrier_init();
   }
   if (warp == 1) {
@@ -400,34 +446,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int chunk_phase = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
     uint32_t staging_use = 0;
+    uint32_t rm_use = 0;  // row-major tiles sent through the staging buffers so far (the same count in every epilogue thread)
     const int r = quad * 32 + lane;
     uint32_t tile_iter = 0;
     bool ok = true;
-    // the row-mask byte of a tile is fetched one tile ahead, so that its latency never shows in the epilogue
-    auto load_mask = [&](int tile) -> float {
-      if (p.rowmask == nullptr || tile >= total_tiles) return 1.0f;
-      const int m_tile = tile / p.num_n_tiles;
-      const int nb = m_tile % p.n_blocks;
-      const int rest = m_tile / p.n_blocks;
-      const int o = rest % p.o_extent;
-      const int b = rest / p.o_extent;
-      const int n = nb * kBM + r;
-      if (n >= p.n_extent) return 1.0f;
-      return p.rowmask[static_cast<long long>(b) * p.m_b + static_cast<long long>(o) * p.m_o +
-                       static_cast<long long>(n) * p.m_n] ? 1.0f : 0.0f;
+    // the row-mask byte of a tile is fetched one tile ahead, so that its latency never shows in the epilogue: the load is
+    // issued here as it stands (volatile asm: the compiler may not sink it to its use) and only its raw byte is kept; the
+    // comparison that consumes it happens one tile later
+    auto load_mask = [&](int tile, const TileIdx& t) -> uint32_t {
+      if (p.rowmask == nullptr || tile >= total_tiles) return 1u;
+      const int n = t.nb * kBM + r;
+      if (n >= p.n_extent) return 1u;
+      uint32_t raw;
+      asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(raw)
+                   : "l"(p.rowmask + static_cast<long long>(t.b) * p.m_b + static_cast<long long>(t.o) * p.m_o +
+                         static_cast<long long>(n) * p.m_n));
+      return raw;
     };
-    float mask_next = load_mask(blockIdx.x);
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
-      const int m_tile = tile / p.num_n_tiles;
-      const int n_tile = tile - m_tile * p.num_n_tiles;
-      const int nb = m_tile % p.n_blocks;
-      const int rest = m_tile / p.n_blocks;
-      const int o = rest % p.o_extent;
-      const int b = rest / p.o_extent;
+    TileIdx tile_cur = tile_decompose(static_cast<int>(blockIdx.x), p);
+    uint32_t mask_next = load_mask(blockIdx.x, tile_cur);
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter, tile_advance(tile_cur, p)) {
+      const int n_tile = tile_cur.n_tile, nb = tile_cur.nb, o = tile_cur.o, b = tile_cur.b;
       const int n = nb * kBM + r;
       const bool row_ok = n < p.n_extent;
-      const float mask_v = mask_next;
-      mask_next = load_mask(tile + gridDim.x);
+      const float mask_v = mask_next ? 1.0f : 0.0f;
+      if (p.rowmask != nullptr) {   // the next tile's index only lives until its mask load is issued
+        TileIdx peek = tile_cur;
+        tile_advance(peek, p);
+        mask_next = load_mask(tile + gridDim.x, peek);
+      }
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_phase = (tile_iter >> 1) & 1;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_phase, 104)) { ok = false; break; }
@@ -472,6 +519,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             w[i >> 1] = pack_bf16x2(v0, v1);
           }
           const int n0 = nb * kBM + c;
+          if (p.swap_staged) {
+            // this channel's 32 positions into the staged tile: box c / 64, row = channel, 128-byte rows with the copy
+            // engine's 16-byte swizzle (conflict-free 16-byte stores)
+            uint8_t* rowp = s_stage_out + 1024 + (rm_use & 1) * Cfg::kRowTileBytes + (c >> 6) * (Cfg::kRowTileBytes / 2) + r * 128;
+            const int piece = (c & 63) >> 3;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              *reinterpret_cast<uint4*>(rowp + (((piece + q4) ^ (r & 7)) << 4)) =
+                  make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+            continue;
+          }
           if (ch < sg.ncols) {
             __nv_bfloat16* d = drow + n0;
             if (n0 + 32 <= p.n_extent && (reinterpret_cast<uintptr_t>(d) & 31) == 0) {
@@ -484,6 +542,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                   d[i] = __ushort_as_bfloat16(static_cast<unsigned short>((i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xffffu)));
             }
           }
+        }
+        if (p.swap_staged) {
+          // whole rows of the channel-major tile leave through the copy engine (a thread's own 32-byte stores cost one
+          // memory request per sector); two buffers alternate as in the row-major path below
+          ptx::fence_proxy_async_smem();
+          const bool issuer = (quad == 0 && chunk_phase == 0 && lane == 0);
+          if (issuer) ptx::tma_store_wait_read();
+          ptx::mbar_arrive(&rm_bar[rm_use & 1]);
+          if (!ptx::mbar_wait(&rm_bar[rm_use & 1], (rm_use >> 1) & 1, 111)) { ok = false; break; }
+          if (issuer) {
+            const uint8_t* buf = s_stage_out + 1024 + (rm_use & 1) * Cfg::kRowTileBytes;
+            ptx::tma_store_4d(&tm_out0, buf, nb * kBM, o, out_col_tile, b);
+            if (nb * kBM + 64 < p.n_extent)
+              ptx::tma_store_4d(&tm_out0, buf + Cfg::kRowTileBytes / 2, nb * kBM + 64, o, out_col_tile, b);
+            ptx::tma_store_commit();
+          }
+          ++rm_use;
         }
       } else if (kPlain128 && out_col_tile >= p.swap_col_begin) {
         // a tile of channel-major segments, computed swapped: this lane is output column (channel) out_col_tile + r, the
@@ -520,7 +595,97 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
           }
         }
-      } else
+      } else {
+      // Fast path of the plain kernel: a tile that lies inside one row-major bf16 segment and needs nothing but the
+      // conversion (the q / k / g columns of the attention projections, plain projections).  The warp's two 32-column
+      // chunks are fetched from tensor memory together and stored with 32-byte stores: one tensor-memory round trip and
+      // none of the per-chunk bookkeeping of the general loop below.
+      bool tile_done = false;
+      if constexpr (!GLU && !AUX && !PRECISE && BN >= 128) {
+        int si = 0;
+        if (p.nseg > 1 && out_col_tile >= p.seg[1].col_begin) si = 1;
+        if (p.nseg > 2 && out_col_tile >= p.seg[2].col_begin) si = 2;
+        const EpiSeg& sg = p.seg[si];
+        const bool plain = sg.vec && !sg.out_fp32 && sg.tma_slot < 0 && out_col_tile + BN <= sg.col_begin + sg.ncols &&
+                           p.col_bias == nullptr && p.row_stats == nullptr && !((p.mask_segs >> si) & 1) &&
+                           (si != 0 || (p.gate == nullptr && p.resid == nullptr));
+        if (plain) {
+          __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(sg.dst) + static_cast<long long>(b) * sg.s_b +
+                                static_cast<long long>(o) * sg.s_o + static_cast<long long>(n) * sg.s_n +
+                                (out_col_tile - sg.col_begin);
+#pragma unroll 1
+          for (int c = chunk_phase * 32; c < BN; c += 128) {
+            uint32_t r0[32], r1[32];
+            ptx::tmem_ld_32x32b_x32(t_row + c, r0);
+            ptx::tmem_ld_32x32b_x32(t_row + c + 64, r1);
+            ptx::tmem_ld_wait();
+            uint32_t w0[16], w1[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              w0[i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+              w1[i] = pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+            }
+            if constexpr (BN == 128) {
+              if (si == p.rm_seg) {
+                // Through shared memory: a thread's 32-byte stores to 32 different rows cost one memory request per
+                // sector; the copy engine writes whole rows of the tile instead.  Two buffers alternate; a buffer is
+                // reused two staged tiles later, after the issuing thread has seen its store read it (checked before
+                // the barrier of the tile in between).
+                uint8_t* buf = s_stage_out + (rm_use & 1) * Cfg::kRowTileBytes;
+                uint8_t* row0 = buf + r * 128;                              // columns 0..63 of this row
+                uint8_t* row1 = buf + Cfg::kRowTileBytes / 2 + r * 128;     // columns 64..127
+                const int piece = (c >> 3);                                 // first 16-byte piece: 0 or 4
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                  const int phys = ((piece + q4) ^ (r & 7)) << 4;
+                  *reinterpret_cast<uint4*>(row0 + phys) = make_uint4(w0[4 * q4], w0[4 * q4 + 1], w0[4 * q4 + 2], w0[4 * q4 + 3]);
+                  *reinterpret_cast<uint4*>(row1 + phys) = make_uint4(w1[4 * q4], w1[4 * q4 + 1], w1[4 * q4 + 2], w1[4 * q4 + 3]);
+                }
+                ptx::fence_proxy_async_smem();
+                const bool issuer = (quad == 0 && chunk_phase == 0 && lane == 0);
+                if (issuer) ptx::tma_store_wait_read();   // the previous staged tile's store has read the other buffer
+                ptx::mbar_arrive(&rm_bar[rm_use & 1]);
+                if (!ptx::mbar_wait(&rm_bar[rm_use & 1], (rm_use >> 1) & 1, 110)) { ok = false; break; }
+                if (issuer) {
+                  const CUtensorMap* tm = p.rm_slot == 0 ? &tm_out0 : &tm_out1;
+                  const int col0 = out_col_tile - sg.col_begin;
+                  ptx::tma_store_4d(tm, buf, col0, nb * kBM, o, b);
+                  if (col0 + 64 < sg.ncols) ptx::tma_store_4d(tm, buf + Cfg::kRowTileBytes / 2, col0 + 64, nb * kBM, o, b);
+                  ptx::tma_store_commit();
+                }
+                ++rm_use;
+                continue;
+              }
+            }
+            if (row_ok) {
+              __nv_bfloat16* d = drow + c;
+              if ((reinterpret_cast<uintptr_t>(d) & 31) == 0) {
+                st_global_v8(d, w0[0], w0[1], w0[2], w0[3], w0[4], w0[5], w0[6], w0[7]);
+                st_global_v8(d + 16, w0[8], w0[9], w0[10], w0[11], w0[12], w0[13], w0[14], w0[15]);
+                st_global_v8(d + 64, w1[0], w1[1], w1[2], w1[3], w1[4], w1[5], w1[6], w1[7]);
+                st_global_v8(d + 80, w1[8], w1[9], w1[10], w1[11], w1[12], w1[13], w1[14], w1[15]);
+              } else {
+                uint4* d4 = reinterpret_cast<uint4*>(d);
+                uint4* e4 = reinterpret_cast<uint4*>(d + 64);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  d4[i] = make_uint4(w0[4 * i], w0[4 * i + 1], w0[4 * i + 2], w0[4 * i + 3]);
+                  e4[i] = make_uint4(w1[4 * i], w1[4 * i + 1], w1[4 * i + 2], w1[4 * i + 3]);
+                }
+              }
+            }
+          }
+          tile_done = true;
+        }
+      }
+      // the GLU kernel's 128 output columns per tile take the same staged route when they lie in the staged segment
+      bool glu_staged = false;
+      if constexpr (GLU && !AUX && !PRECISE && BN == 256) {
+        const EpiSeg& s0 = p.seg[0];
+        glu_staged = p.rm_seg == 0 && out_col_tile >= s0.col_begin && out_col_tile + out_bn <= s0.col_begin + s0.ncols &&
+                     (p.nseg == 1 || out_col_tile + out_bn <= p.seg[1].col_begin);
+      }
+      if (!tile_done)
 #pragma unroll 1
       for (int c = chunk_phase * 32; c < out_bn; c += 32 * (kEpiWarps / 4)) {
         const int out_col = out_col_tile + c;
@@ -756,10 +921,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
           }
         }
+        if constexpr (GLU && !AUX && !PRECISE && BN == 256) {
+          if (glu_staged) {
+            uint8_t* rowp = s_stage_out + (rm_use & 1) * Cfg::kRowTileBytes + (c >> 6) * (Cfg::kRowTileBytes / 2) + r * 128;
+            const int piece = (c & 63) >> 3;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              *reinterpret_cast<uint4*>(rowp + (((piece + q4) ^ (r & 7)) << 4)) =
+                  make_uint4(pack_bf16x2(v[8 * q4], v[8 * q4 + 1]), pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]),
+                             pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]), pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]));
+            continue;
+          }
+        }
         if (PRECISE && sg.split)
           epi_store_split(sg, row_off, col_local, v, row_ok);
         else
           epi_store_chunk(sg, row_off, col_local, v, row_ok);
+      }
+      if constexpr (GLU && !AUX && !PRECISE && BN == 256) {
+        if (glu_staged && ok) {
+          ptx::fence_proxy_async_smem();
+          const bool issuer = (quad == 0 && chunk_phase == 0 && lane == 0);
+          if (issuer) ptx::tma_store_wait_read();
+          ptx::mbar_arrive(&rm_bar[rm_use & 1]);
+          if (!ptx::mbar_wait(&rm_bar[rm_use & 1], (rm_use >> 1) & 1, 112)) {
+            ok = false;
+          } else if (issuer) {
+            const uint8_t* buf = s_stage_out + (rm_use & 1) * Cfg::kRowTileBytes;
+            const int col0 = out_col_tile - p.seg[0].col_begin;
+            ptx::tma_store_4d(&tm_out0, buf, col0, nb * kBM, o, b);
+            ptx::tma_store_4d(&tm_out0, buf + Cfg::kRowTileBytes / 2, col0 + 64, nb * kBM, o, b);
+            ptx::tma_store_commit();
+          }
+          ++rm_use;
+        }
+      }
       }
       if (!ok) break;
       if (AUX) {

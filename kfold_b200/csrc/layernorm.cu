@@ -3,6 +3,8 @@
 // variance of the centred values, which is what torch's layer_norm computes).
 #include "layernorm.cuh"
 
+#include <type_traits>
+
 namespace kfb {
 
 template <typename T>
@@ -33,7 +35,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // One warp per row; lane l holds channel pairs (l + 32 g) * 2, g < G.
-template <typename TI, typename TO, int G>
+template <typename TI, typename TO, int G, bool PERM>
 __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restrict__ x, TO* __restrict__ y,
                                                              const float* __restrict__ w, const float* __restrict__ b,
                                                              long long rows, int c, long long xs, long long ys, float eps,
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restric
     }
     const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(c) + eps);
     long long orow = row;
-    if (perm.rows) {   // (i, q, j) -> (q, i, j): the send buffer of a shard transpose, one block per destination rank
+    if (PERM) {   // (i, q, j) -> (q, i, j): the send buffer of a shard transpose, one block per destination rank
       const long long i = row / perm.n;
       const int rest = static_cast<int>(row - i * perm.n);
       const int q = rest / perm.rows;
@@ -92,6 +94,69 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restric
   }
 }
 
+// The pair track's shape: 128 bf16 channels, contiguous rows.  A row is 256 bytes = 16 lanes x 16 bytes, so a warp takes two
+// rows per step and two steps per iteration: four rows (1 KB) in flight per warp, 16-byte loads and stores, the statistics
+// reduced over the 16 lanes of a row.  Same arithmetic as layernorm_rows_kernel (two passes, fp32).
+__global__ void __launch_bounds__(256) layernorm_c128_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                                  const float* __restrict__ w, const float* __restrict__ b,
+                                                                  long long rows, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 15;                 // 16-byte chunk of the row
+  const int half = lane >> 4;                // which of the warp's two rows
+  float g[8], o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    g[i] = w != nullptr ? w[sub * 8 + i] : 1.0f;
+    o[i] = b != nullptr ? b[sub * 8 + i] : 0.0f;
+  }
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const long long warp_id = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (long long base = warp_id * 4; base < rows; base += warps * 4) {
+    uint4 raw[2];
+    bool live[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const long long row = base + s * 2 + half;
+      live[s] = row < rows;
+      raw[s] = live[s] ? *reinterpret_cast<const uint4*>(x + row * 128 + sub * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const uint32_t wv[4] = {raw[s].x, raw[s].y, raw[s].z, raw[s].w};
+      float v[8];
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(wv[i] << 16);
+        v[2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
+        sum += v[2 * i] + v[2 * i + 1];
+      }
+#pragma unroll
+      for (int m = 8; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+      const float mean = sum * (1.0f / 128.0f);
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] -= mean;
+        sq = fmaf(v[i], v[i], sq);
+      }
+#pragma unroll
+      for (int m = 8; m > 0; m >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, m);
+      const float rstd = rsqrtf(sq * (1.0f / 128.0f) + eps);
+      uint4 out;
+      uint32_t* ov = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(fmaf(v[2 * i] * rstd, g[2 * i], o[2 * i]),
+                                                        fmaf(v[2 * i + 1] * rstd, g[2 * i + 1], o[2 * i + 1]));
+        ov[i] = *reinterpret_cast<const uint32_t*>(&pr);
+      }
+      const long long row = base + s * 2 + half;
+      if (live[s]) *reinterpret_cast<uint4*>(y + row * 128 + sub * 8) = out;
+    }
+  }
+}
+
 template <typename TI, typename TO, int G>
 static int launch_rows(cudaStream_t stream, const void* x, void* y, const float* w, const float* b, long long rows, int c,
                        long long xs, long long ys, float eps, RowPerm perm) {
@@ -100,8 +165,18 @@ static int launch_rows(cudaStream_t stream, const void* x, void* y, const float*
   const long long cap = static_cast<long long>(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   LaunchScope scope(stream, "layernorm_rows");
-  layernorm_rows_kernel<TI, TO, G><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(
-      static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps, perm);
+  if (perm.rows) {
+    if constexpr (std::is_same<TO, __nv_bfloat16>::value) {   // the exchange order is only ever written in bf16
+      layernorm_rows_kernel<TI, TO, G, true><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(
+          static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps, perm);
+    } else {
+      set_error("layernorm: the exchange order is written in bf16 only");
+      return KFB_ERR_UNSUPPORTED;
+    }
+  } else {
+    layernorm_rows_kernel<TI, TO, G, false><<<static_cast<unsigned>(blocks), warps * 32, 0, stream>>>(
+        static_cast<const TI*>(x), static_cast<TO*>(y), w, b, rows, c, xs, ys, eps, perm);
+  }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
 }
@@ -127,6 +202,17 @@ int launch_layernorm(cudaStream_t stream, const void* x, void* y, const float* w
                 "layernorm: exchange order needs a (%d, %d) shard, got %lld rows", perm.rows, perm.n, rows);
   KFB_CHECK_ARG(xs % 2 == 0 && ys % 2 == 0, "layernorm: row strides must be even");
   if (rows == 0) return KFB_OK;
+  if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16 && c == 128 && xs == 128 && ys == 128 && perm.rows == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    long long blocks = (rows + 31) / 32;      // 8 warps x 4 rows per iteration
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    LaunchScope scope(stream, "layernorm_rows");
+    layernorm_c128_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), w, b, rows, eps);
+    KFB_CUDA(cudaGetLastError());
+    return KFB_OK;
+  }
   if (in_dtype == KFB_BF16 && out_dtype == KFB_BF16)
     return dispatch_g<__nv_bfloat16, __nv_bfloat16>(stream, x, y, w, b, rows, c, xs, ys, eps, perm);
   if (in_dtype == KFB_FP32 && out_dtype == KFB_BF16)

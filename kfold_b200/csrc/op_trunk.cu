@@ -4,6 +4,7 @@
 //   kfb_gelu              erf GELU, element-wise                      the activation inside LMToPair's MLP
 // of the diffusion module's pair conditioning (model/layers/folding/diffusion.py:45-94):
 //   kfb_concat_layernorm  LayerNorm([z | relative-position features])  one pass, written K-padded for the float32 Linear
+//   kfb_relpos_concat_layernorm  the same with the features computed from the token attributes (never stored)
 // and of the confidence head (model/modules/confidence_head.py:306-470):
 //   kfb_pair_outer_add       z + Linear_1(s)[j] + Linear_2(s)[i]       the single representation added along both token axes
 //   kfb_distogram_embed_add  z + Linear(one_hot(distance bin))         the predicted structure's distogram, embedded
@@ -43,8 +44,49 @@ __global__ void __launch_bounds__(256) lm_pair_features_kernel(const T* __restri
 // y[row, 0:c1+c2] = LayerNorm([z[row, 0:c1] | rel[row, 0:c2]]) * w (+ b), y[row, c1+c2 : k_pad] = 0, float32 out.  One warp per
 // row, the row held in registers (up to 32 * kMaxPerLane channels), mean and variance in two register passes.
 constexpr int kCatPerLane = 16;
-template <typename TZ, typename TR>
-__global__ void __launch_bounds__(256) concat_layernorm_kernel(const TZ* __restrict__ z, const TR* __restrict__ rel,
+
+// The second part of the concatenated row, stored ...
+template <typename TR>
+struct StoredFeatures {
+  const TR* rel;
+  int c2;
+  struct Row {
+    const TR* p;
+    __device__ __forceinline__ float at(int k) const { return ldf(p + k); }
+  };
+  __device__ __forceinline__ Row row(long long r) const { return Row{rel + r * c2}; }
+};
+// ... or the relative-position encoding computed from the token attributes (model/layers/folding/embeddings.py:58-130):
+// [one_hot(residue offset, 2 r_max + 2) | one_hot(token offset, 2 r_max + 2) | same entity | one_hot(chain offset, 2 s_max + 2)],
+// offsets clipped to [0, 2 max] and moved to the last bin when the tokens are not comparable (other chain; other chain or
+// residue; other entity).
+struct RelPosFeatures {
+  const long long *asym, *residue, *entity, *token, *sym;   // [batch][n] each
+  int n, r_max, s_max;
+  struct Row {
+    int d_res, d_tok, ent, d_chain, nb;   // nb = 2 r_max + 2
+    __device__ __forceinline__ float at(int k) const {
+      const bool one = (k == d_res) || (k == nb + d_tok) || (k == 2 * nb && ent) || (k == 2 * nb + 1 + d_chain);
+      return one ? 1.0f : 0.0f;
+    }
+  };
+  __device__ __forceinline__ Row row(long long r) const {
+    const long long bi = r / n;                       // batch * n + i
+    const long long bj = (bi / n) * n + (r - bi * n); // batch * n + j
+    const bool chain = asym[bi] == asym[bj], res = residue[bi] == residue[bj], ent = entity[bi] == entity[bj];
+    auto clip = [](long long d, int mx) { return static_cast<int>(d < 0 ? 0 : (d > 2 * mx ? 2 * mx : d)); };
+    Row o;
+    o.nb = 2 * r_max + 2;
+    o.d_res = chain ? clip(residue[bi] - residue[bj] + r_max, r_max) : 2 * r_max + 1;
+    o.d_tok = (chain && res) ? clip(token[bi] - token[bj] + r_max, r_max) : 2 * r_max + 1;
+    o.ent = ent ? 1 : 0;
+    o.d_chain = ent ? clip(sym[bi] - sym[bj] + s_max, s_max) : 2 * s_max + 1;
+    return o;
+  }
+};
+
+template <typename TZ, typename FEAT>
+__global__ void __launch_bounds__(256) concat_layernorm_kernel(const TZ* __restrict__ z, const FEAT feat,
                                                                const float* __restrict__ w, const float* __restrict__ b,
                                                                float* __restrict__ y, long long rows, int c1, int c2, int k_pad,
                                                                float eps) {
@@ -53,13 +95,13 @@ __global__ void __launch_bounds__(256) concat_layernorm_kernel(const TZ* __restr
   const long long stride = static_cast<long long>(gridDim.x) * 8;
   for (long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += stride) {
     const TZ* zr = z + row * c1;
-    const TR* rr = rel + row * c2;
+    const auto fr = feat.row(row);
     float v[kCatPerLane];
     float sum = 0.f;
 #pragma unroll
     for (int g = 0; g < kCatPerLane; ++g) {
       const int ch = g * 32 + lane;
-      v[g] = ch < c1 ? ldf(zr + ch) : (ch < c ? ldf(rr + (ch - c1)) : 0.f);
+      v[g] = ch < c1 ? ldf(zr + ch) : (ch < c ? fr.at(ch - c1) : 0.f);
       sum += v[g];
     }
 #pragma unroll
@@ -241,18 +283,45 @@ KFB_API int kfb_concat_layernorm(const void* z, int z_dtype, const void* rel, in
   const unsigned g = static_cast<unsigned>(blocks);
   {
     LaunchScope scope(stream, "concat_layernorm");
+    const StoredFeatures<__nv_bfloat16> fb = {static_cast<const __nv_bfloat16*>(rel), c2};
+    const StoredFeatures<float> ff = {static_cast<const float*>(rel), c2};
     if (z_dtype == KFB_BF16 && rel_dtype == KFB_BF16)
-      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(rel),
-                                                     ln_w, ln_b, out, rows, c1, c2, k_pad, eps);
+      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(z), fb, ln_w, ln_b, out, rows, c1, c2, k_pad, eps);
     else if (z_dtype == KFB_BF16)
-      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(z), static_cast<const float*>(rel), ln_w, ln_b,
-                                                     out, rows, c1, c2, k_pad, eps);
+      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(z), ff, ln_w, ln_b, out, rows, c1, c2, k_pad, eps);
     else if (rel_dtype == KFB_BF16)
-      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const float*>(z), static_cast<const __nv_bfloat16*>(rel), ln_w, ln_b,
-                                                     out, rows, c1, c2, k_pad, eps);
+      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const float*>(z), fb, ln_w, ln_b, out, rows, c1, c2, k_pad, eps);
     else
-      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const float*>(z), static_cast<const float*>(rel), ln_w, ln_b, out,
-                                                     rows, c1, c2, k_pad, eps);
+      concat_layernorm_kernel<<<g, 256, 0, stream>>>(static_cast<const float*>(z), ff, ln_w, ln_b, out, rows, c1, c2, k_pad, eps);
+  }
+  KFB_CUDA(cudaGetLastError());
+  return KFB_OK;
+}
+
+KFB_API int kfb_relpos_concat_layernorm(const void* z, int z_dtype, const long long* asym_id, const long long* residue_index,
+                                        const long long* entity_id, const long long* token_index, const long long* sym_id,
+                                        int r_max, int s_max, const float* ln_w, const float* ln_b, float* out, int batch, int n, int c1,
+                                        int k_pad, float eps, void* stream_) {
+  KFB_CHECK_ARG(z && asym_id && residue_index && entity_id && token_index && sym_id && out, "relpos_concat_layernorm: null pointer");
+  KFB_CHECK_ARG(batch >= 1 && n >= 1 && c1 >= 1 && r_max >= 0 && s_max >= 0, "relpos_concat_layernorm: bad sizes");
+  const int c2 = 4 * (r_max + 1) + 2 * (s_max + 1) + 1;
+  KFB_CHECK_ARG(k_pad >= c1 + c2 && k_pad <= 32 * kCatPerLane, "relpos_concat_layernorm: %d + %d channels padded to %d (at most %d)", c1,
+                c2, k_pad, 32 * kCatPerLane);
+  KFB_CHECK_ARG(z_dtype == KFB_BF16 || z_dtype == KFB_FP32, "relpos_concat_layernorm: dtype %d", z_dtype);
+  cudaStream_t stream = as_stream(stream_);
+  const long long rows = static_cast<long long>(batch) * n * n;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  const RelPosFeatures feat = {asym_id, residue_index, entity_id, token_index, sym_id, n, r_max, s_max};
+  {
+    LaunchScope scope(stream, "relpos_concat_layernorm");
+    if (z_dtype == KFB_BF16)
+      concat_layernorm_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(z), feat, ln_w, ln_b,
+                                                                                  out, rows, c1, c2, k_pad, eps);
+    else
+      concat_layernorm_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const float*>(z), feat, ln_w, ln_b, out,
+                                                                                  rows, c1, c2, k_pad, eps);
   }
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;

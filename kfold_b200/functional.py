@@ -869,6 +869,25 @@ def concat_layer_norm(z: torch.Tensor, rel: torch.Tensor, ln_w, ln_b, k_pad: int
     return out
 
 
+def relpos_concat_layer_norm(z: torch.Tensor, token, ln_w, ln_b, k_pad: int, r_max: int = 32, s_max: int = 2,
+                             eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm(cat([z, RelativePositionEncoding(token)], -1)) without the one-hot tensor
+    (model/layers/folding/embeddings.py:58-130 + diffusion.py:84-90): `token` carries asym_id, residue_index, entity_id,
+    token_index and sym_id, (B, L) integer tensors; z (B, L, L, c_z).  float32 (B, L, L, k_pad)."""
+    _require_cuda(z)
+    b, n, _, c1 = z.shape
+    zc = (z if z.dtype in (torch.bfloat16, torch.float32) else z.float()).contiguous()
+    ids = [getattr(token, k).to(device=z.device, dtype=torch.int64).reshape(b, n).contiguous()
+           for k in ("asym_id", "residue_index", "entity_id", "token_index", "sym_id")]
+    f32 = lambda t: None if t is None else t.detach().float().contiguous()
+    lw, lb = f32(ln_w), f32(ln_b)
+    out = torch.empty(b, n, n, k_pad, dtype=torch.float32, device=z.device)
+    with L.on_device(z.device):
+        L.check(L.lib().kfb_relpos_concat_layernorm(L.ptr(zc), L.dtype_code(zc.dtype), *[L.ptr(t) for t in ids], r_max, s_max,
+                                                    L.ptr(lw), L.ptr(lb), L.ptr(out), b, n, c1, k_pad, eps, L.stream_ptr()))
+    return out
+
+
 def pair_outer_add(z: torch.Tensor, row_add: torch.Tensor, col_add: torch.Tensor) -> torch.Tensor:
     """z[b, i, j] + row_add[b, j] + col_add[b, i] (model/modules/confidence_head.py:347-351): z (B, L, L, C), the addends (B, L, C)."""
     _require_cuda(z, row_add, col_add)

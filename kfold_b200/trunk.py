@@ -111,9 +111,11 @@ class PairConditioning(nn.Module):
     then two Transitions with residual.  The relative-position features are an input here (the reference derives them from
     the FoldingInput with ``RelativePositionEncoding(32, 2)``, 139 channels, model/layers/folding/embeddings.py:25-140)."""
 
-    def __init__(self, channel_z: int = 256, rel_pos_dim: int = 139):
+    def __init__(self, channel_z: int = 256, rel_pos_dim: int = 139, r_max: int = 32, s_max: int = 2):
         super().__init__()
-        self.channel_z, self.rel_pos_dim = channel_z, rel_pos_dim
+        if rel_pos_dim != 4 * (r_max + 1) + 2 * (s_max + 1) + 1:
+            raise ValueError("rel_pos_dim does not match RelativePositionEncoding(r_max, s_max)")
+        self.channel_z, self.rel_pos_dim, self.r_max, self.s_max = channel_z, rel_pos_dim, r_max, s_max
         in_channel = channel_z + rel_pos_dim
         self.layernorm = LayerNorm(in_channel, create_offset=False)
         self.linear = LinearNoBias(in_channel, channel_z)
@@ -131,14 +133,19 @@ class PairConditioning(nn.Module):
         return self._w
 
     @torch.compiler.disable
-    def forward(self, rel_pos_feats: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
-        """rel_pos_feats (B, L, L, rel_pos_dim); z (B, L, L, c_z) -> float32 (B, L, L, c_z)."""
+    def forward(self, rel_pos, z: torch.Tensor) -> torch.Tensor:
+        """rel_pos: the relative-position features (B, L, L, rel_pos_dim), or -- the reference's own argument -- the
+        FoldingInput (anything whose `.token` carries asym_id, residue_index, entity_id, token_index, sym_id), in which case
+        the features are computed inside the LayerNorm kernel and never stored; z (B, L, L, c_z) -> float32 (B, L, L, c_z)."""
         _check_inference(z)
         ln = self.layernorm
         with torch.autocast(z.device.type, enabled=False):
-            k = z.shape[-1] + rel_pos_feats.shape[-1]
+            k = z.shape[-1] + self.rel_pos_dim
             k_pad = (k + 7) // 8 * 8          # the split-operand GEMM wants rows of a multiple of 8 elements
-            zn = F.concat_layer_norm(z, rel_pos_feats, ln.weight, ln.bias, k_pad, ln.eps)
+            if isinstance(rel_pos, torch.Tensor):
+                zn = F.concat_layer_norm(z, rel_pos, ln.weight, ln.bias, k_pad, ln.eps)
+            else:
+                zn = F.relpos_concat_layer_norm(z, rel_pos.token, ln.weight, ln.bias, k_pad, self.r_max, self.s_max, ln.eps)
             out = F.linear_fp32(zn, self._weight6(z.device, k_pad), None)
         for transition in self.transitions:
             out = transition(out, residual=True)

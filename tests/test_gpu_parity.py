@@ -67,6 +67,24 @@ def test_layernorm(dev, c, dt):
     assert mx < (5e-2 if dt == torch.bfloat16 else 1e-5)  # bf16: one output rounding of values up to ~10 RMS
 
 
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 5, 127, 4099])
+def test_layernorm_pair_track_shape(dev, rows):
+    """C = 128 bf16 contiguous rows take the 16-byte kernel (four rows per warp step): every tail length, against torch's
+    layer_norm on the same bf16 input -- equal up to one bf16 rounding step of the output."""
+    from kfold_b200 import functional as F
+    g = torch.Generator().manual_seed(rows)
+    x = (torch.randn(rows, 128, generator=g) * 2 + 0.7).bfloat16()
+    w, b = torch.randn(128, generator=g), torch.randn(128, generator=g)
+    y = F.layer_norm(x.to(dev), w.to(dev), b.to(dev)).float().cpu()
+    ref = torch.nn.functional.layer_norm(x.float(), (128,), w, b, 1e-5)
+    assert (y - ref).abs().max() <= 2 ** -7 * ref.abs().max()
+    assert (y - ref.bfloat16().float()).abs().max() <= 2 ** -6 * ref.abs().max()
+    # no affine (AdaLN's inner norm)
+    y0 = F.layer_norm(x.to(dev), None, None).float().cpu()
+    ref0 = torch.nn.functional.layer_norm(x.float(), (128,), None, None, 1e-5)
+    assert (y0 - ref0).abs().max() <= 2 ** -7 * ref0.abs().max()
+
+
 # ----------------------------------------------------------------------------- golden vectors (reference outputs)
 def _run_case(name, dev, dtype=torch.bfloat16):
     from kfold_b200 import functional as F

@@ -86,6 +86,14 @@ def test_pair_conditioning(dev):
     _check(*err_stats(out.float().cpu(), gold), "pair_conditioning autocast")
     out = mod(rel.bfloat16(), inp["z"].to(dev).bfloat16())
     _check(*err_stats(out.float().cpu(), gold), "pair_conditioning bf16")
+    # the reference's own call form: the FoldingInput instead of ready-made features (computed inside the kernel)
+    import types
+    f_input = types.SimpleNamespace(token=types.SimpleNamespace(**{k: inp[k].to(dev) for k in
+                                                                   ("asym_id", "entity_id", "sym_id", "residue_index", "token_index")}))
+    out2 = mod(f_input, inp["z"].to(dev))
+    assert torch.equal(out2, mod(rel, inp["z"].to(dev)))
+    mx, r = err_stats(out2.cpu(), gold)
+    assert mx < PRECISE_MAX_TOL and r < PRECISE_RMS_TOL, f"pair_conditioning from token attributes: {mx:.3e} {r:.3e}"
 
 
 def test_confidence_preparation_kernels(dev):
