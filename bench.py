@@ -58,7 +58,9 @@ def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C
         "apb_out_proj": ("tensor", 2.0 * n * cs * cs),
         # HBM-bound kernels: bytes per launch (every tensor read or written once, bf16).  The K = c projections do
         # 8 tensor-core instructions per 128-row tile: their time is the traffic of the tensors around them.
-        "layernorm_rows": ("hbm", 2.0 * p * c * 2),
+        # 8 launches per block share this tag: 6 over the pair tensor (tri-mult x2, tri-att x2, transition, pair bias) and 2
+        # over the single track; the figure is their average, so that bytes / average time is the achieved bandwidth
+        "layernorm_rows": ("hbm", (6 * 2.0 * p * c * 2 + 2 * 2.0 * n * cs * 2) / 8),
         "layernorm_cm": ("hbm", 2.0 * p * c * 2),
         "layernorm_cm_stats": ("hbm", 1.0 * p * c * 2 + p * 8),   # read t, write (mean, rstd) per position
         "trimul_in_proj": ("hbm", 3.0 * p * c * 2),            # read x~, write a and b
