@@ -87,7 +87,9 @@ KFB_API int kfb_profile_report(char* buf, size_t cap);
  *   x, out : (batch, n, n, c) contiguous, `dtype`; n a multiple of 8, c a multiple of 64.
  *   mask   : (batch, n, n) bytes, non-zero = valid.
  *   w_in_packed : bf16 [4c, c], linear_p_in / linear_g_in interleaved in blocks of 128 rows
- *                 (value rows of 128 channels, then their gate rows).
+ *                 (value rows of 128 channels, then their gate rows), BOTH multiplied by 0.5 (exact in bf16): the
+ *                 epilogue evaluates v sigmoid(g) as v' + v' tanh(g') with v' = v / 2, g' = g / 2.  With
+ *                 KFB_FP32_PRECISE the matrices are unscaled (bf16 triple splits, exact sigmoid).
  *   w_gout, w_pout : bf16 [c, c] (linear_g_out, linear_p_out);  ln_* : fp32 [c].
  *   resid  : NULL, or a (batch, n, n, c) tensor of `dtype` added to the update (may equal x and out).
  * Writes out = update (+ resid).  Arithmetic: bf16 operands, fp32 accumulation and statistics.
@@ -459,7 +461,8 @@ KFB_API int kfb_center_coords(const float* coords, const unsigned char* mask, fl
  * Replaces Transition.forward (src/kfold/model/layers/folding/transition.py:48-68) with SwiGLU.forward
  * (src/kfold/model/primitives/activation.py:27-29).
  *   x, out : (rows, c) of `dtype`;  w_swiglu_packed : bf16 [2*hidden, c], the silu half and the linear
- *   half interleaved in blocks of 128 rows;  w_out : bf16 [c, hidden];  hidden a multiple of 128.
+ *   half interleaved in blocks of 128 rows, the silu half multiplied by 0.5 (exact in bf16: silu(a) = a' + a' tanh(a'),
+ *   a' = a / 2; unscaled with KFB_FP32_PRECISE);  w_out : bf16 [c, hidden];  hidden a multiple of 128.
  */
 KFB_API size_t kfb_transition_workspace_bytes(long long rows, int c, int hidden);
 KFB_API size_t kfb_transition_workspace_bytes_precise(long long rows, int c, int hidden);

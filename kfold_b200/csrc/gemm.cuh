@@ -121,6 +121,17 @@ struct GemmCfg {
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
 };
 
+// The GLU epilogues of the bf16 kernels get their gate operands halved by the weight packing (exact in bf16):
+//   v sigmoid(g)   = v' + v' tanh(g')      with v' = v / 2, g' = g / 2
+//   a sigmoid(a) g = (a' + a' tanh(a')) g  with a' = a / 2
+// one MUFU op and one fused multiply-add per gate.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+__device__ __forceinline__ float glu_half(float v_half, float g_half) { return fmaf(v_half, tanh_fast(g_half), v_half); }
+
 // sigmoid(x) = 0.5 tanh(x / 2) + 0.5: one MUFU op instead of an exp2 and a reciprocal
 __device__ __forceinline__ float sigmoidf_fast(float x) {
   float t;
@@ -514,8 +525,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float v0 = __uint_as_float(raw[i]) * sigmoidf_fast(__uint_as_float(rawg[i])) * mk[i];
-            const float v1 = __uint_as_float(raw[i + 1]) * sigmoidf_fast(__uint_as_float(rawg[i + 1])) * mk[i + 1];
+            const float v0 = glu_half(__uint_as_float(raw[i]), __uint_as_float(rawg[i])) * mk[i];
+            const float v1 = glu_half(__uint_as_float(raw[i + 1]), __uint_as_float(rawg[i + 1])) * mk[i + 1];
             w[i >> 1] = pack_bf16x2(v0, v1);
           }
           const int n0 = nb * kBM + c;
@@ -698,12 +709,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ptx::tmem_ld_wait();
           if (p.glu == GLU_SIGMOID) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * sigmoidf_fast(__uint_as_float(rawg[i]));
+            for (int i = 0; i < 32; ++i) v[i] = glu_half(__uint_as_float(raw[i]), __uint_as_float(rawg[i]));
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const float a = __uint_as_float(raw[i]);
-              v[i] = a * sigmoidf_fast(a) * __uint_as_float(rawg[i]);
+              const float a = __uint_as_float(raw[i]);   // a / 2
+              v[i] = glu_half(a, a) * __uint_as_float(rawg[i]);
             }
           }
         } else {

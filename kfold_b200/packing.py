@@ -13,13 +13,27 @@ GLU_HALF = 128  # value (or gate) columns per 256-wide GEMM tile
 GLU_HALF_PRECISE = 64  # the fp32-accurate GEMM variant uses 128-wide tiles
 
 
-def interleave_glu(value_w: torch.Tensor, gate_w: torch.Tensor, half: int = GLU_HALF) -> torch.Tensor:
-    """[n, k] value and gate weights -> [2n, k] with alternating blocks of `half` rows."""
+def interleave_glu(value_w: torch.Tensor, gate_w: torch.Tensor, half: int = GLU_HALF, value_scale: float = 1.0,
+                   gate_scale: float = 1.0) -> torch.Tensor:
+    """[n, k] value and gate weights -> [2n, k] with alternating blocks of `half` rows.  The scales implement the bf16
+    kernels' gate arithmetic: sigmoid(g) = 0.5 + 0.5 tanh(g / 2), so the tensor core is handed the halved matrices
+    (exact in bf16) and the epilogue needs one tanh and one fused multiply-add per gate:
+      sigmoid GLU   v sigmoid(g)   = v' + v' tanh(g')     with v' = v / 2, g' = g / 2      -> glu_scales("sigmoid")
+      SwiGLU        a sigmoid(a) g = (a' + a' tanh(a')) g with a' = a / 2                  -> glu_scales("swiglu")
+    The fp32-accurate packing keeps the matrices as they are (exact sigmoid in the epilogue)."""
     n, k = value_w.shape
+    value_w, gate_w = value_w * value_scale, gate_w * gate_scale
     assert gate_w.shape == (n, k) and n % half == 0, (value_w.shape, gate_w.shape, half)
     v = value_w.reshape(n // half, half, k)
     g = gate_w.reshape(n // half, half, k)
     return torch.stack((v, g), dim=1).reshape(2 * n, k).contiguous()
+
+
+def glu_scales(kind: str, precise: bool) -> dict:
+    """Keyword arguments of interleave_glu for the bf16 kernels' halved gate operands (none for the fp32-accurate mode)."""
+    if precise:
+        return {}
+    return {"value_scale": 0.5, "gate_scale": 0.5} if kind == "sigmoid" else {"value_scale": 0.5}
 
 
 # The tensor-core attention kernel keeps its logits in log2 units: the query projection carries log2(e) / sqrt(D).
@@ -69,7 +83,7 @@ def pack_trimul(w: dict, device, dtype=torch.bfloat16, precise: bool = False, sh
     return {
         "ln_in_w": _dev(w["layernorm_in.weight"], device, torch.float32),
         "ln_in_b": _dev(w["layernorm_in.bias"], device, torch.float32),
-        "w_in": _w(interleave_glu(wp, wg, GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_in": _w(interleave_glu(wp, wg, GLU_HALF_PRECISE if precise else GLU_HALF, **glu_scales("sigmoid", precise)), device, precise),
         "w_gout": _w(w["linear_g_out.weight"], device, precise),
         "ln_out_w": _dev(w["layernorm_out.weight"], device, torch.float32),
         "ln_out_b": _dev(w["layernorm_out.bias"], device, torch.float32),
@@ -224,7 +238,8 @@ def pack_transition(w: dict, device, dtype=torch.bfloat16, precise: bool = False
     return {
         "ln_w": _dev(w["layernorm.weight"], device, torch.float32),
         "ln_b": _dev(w["layernorm.bias"], device, torch.float32),
-        "w_swiglu": _w(interleave_glu(sw[:hidden], sw[hidden:], GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_swiglu": _w(interleave_glu(sw[:hidden], sw[hidden:], GLU_HALF_PRECISE if precise else GLU_HALF, **glu_scales("swiglu", precise)), device,
+                       precise),
         "w_out": _w(w["linear_out.weight"], device, precise),
         "c": int(sw.shape[1]), "hidden": int(hidden), "precise": precise,
     }
@@ -251,7 +266,8 @@ def pack_cond_transition(w: dict, device, dtype=torch.bfloat16, precise: bool = 
     hidden = sw.shape[0] // 2
     return {
         "adaln": pack_adaln({k[len("adaln."):]: v for k, v in w.items() if k.startswith("adaln.")}, device, dtype, precise),
-        "w_swiglu": _w(interleave_glu(sw[:hidden], sw[hidden:], GLU_HALF_PRECISE if precise else GLU_HALF), device, precise),
+        "w_swiglu": _w(interleave_glu(sw[:hidden], sw[hidden:], GLU_HALF_PRECISE if precise else GLU_HALF, **glu_scales("swiglu", precise)), device,
+                       precise),
         "w_out": _w(w["linear_out.weight"], device, precise),
         "w_g": _w(w["linear_g.weight"], device, precise),
         "b_g": _dev(w["linear_g.bias"], device, torch.float32),

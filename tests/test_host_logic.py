@@ -15,6 +15,12 @@ def test_interleave_glu_layout():
     assert p.shape == (512, 4)
     assert torch.equal(p[:128], v[:128]) and torch.equal(p[128:256], g[:128])
     assert torch.equal(p[256:384], v[128:]) and torch.equal(p[384:], g[128:])
+    # the bf16 kernels' halved gate operands; none in the fp32-accurate packing
+    ps = packing.interleave_glu(v, g, **packing.glu_scales("sigmoid", False))
+    assert torch.equal(ps, 0.5 * p)
+    pw = packing.interleave_glu(v, g, **packing.glu_scales("swiglu", False))
+    assert torch.equal(pw[:128], 0.5 * v[:128]) and torch.equal(pw[128:256], g[:128])
+    assert torch.equal(packing.interleave_glu(v, g, **packing.glu_scales("swiglu", True)), p)
 
 
 def test_pad_heads_scales_and_zero_fills():
