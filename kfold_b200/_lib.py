@@ -203,12 +203,14 @@ def profile_enable(on: bool) -> None:
     check(lib().kfb_profile_enable(1 if on else 0))
 
 
-def profile_report() -> dict:
-    """{tag: (launches, total_ms)} for the launches recorded since profile_enable(True)."""
+def profile_report(detail: bool = False) -> dict:
+    """{tag: (launches, total_ms)} for the launches recorded since profile_enable(True); with `detail`
+    {tag: (launches, total_ms, large launches, their total_ms)}, "large" = at least half as long as the tag's longest launch
+    (tags shared by the pair tensor and the single track: the pair-sized launches)."""
     buf = ctypes.create_string_buffer(16384)
     check(lib().kfb_profile_report(buf, len(buf)))
     out = {}
     for line in buf.value.decode().splitlines():
-        tag, n, ms = line.split()
-        out[tag] = (int(n), float(ms))
+        tag, n, ms, nl, msl = line.split()
+        out[tag] = (int(n), float(ms), int(nl), float(msl)) if detail else (int(n), float(ms))
     return out

@@ -68,23 +68,35 @@ void profile_enable(bool on) {
   g_prof_on = on;
 }
 
-// Writes one line per tag: "<tag> <launches> <total_ms>\n".  Synchronises on the recorded events.
+// Writes one line per tag: "<tag> <launches> <total_ms> <large launches> <their total_ms>\n", "large" = the launches that
+// took at least half as long as the tag's longest one (a tag such as the transition's serves the pair tensor and the much
+// smaller single track: the large group is the pair-sized work).  Synchronises on the recorded events.
 int profile_report(char* buf, size_t cap) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
-  struct Agg { const char* tag; long long n; double ms; };
+  struct Agg { const char* tag; long long n; double ms; float mx; long long n_large; double ms_large; };
   std::vector<Agg> agg;
+  std::vector<std::pair<int, float>> each;   // (index into agg, ms) per launch
   for (auto& r : g_prof) {
     if (cudaEventSynchronize(r.e1) != cudaSuccess) continue;
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
-    bool found = false;
-    for (auto& a : agg)
-      if (strcmp(a.tag, r.tag) == 0) { a.n++; a.ms += ms; found = true; break; }
-    if (!found) agg.push_back({r.tag, 1, ms});
+    int idx = -1;
+    for (size_t i = 0; i < agg.size(); ++i)
+      if (strcmp(agg[i].tag, r.tag) == 0) { idx = static_cast<int>(i); break; }
+    if (idx < 0) {
+      agg.push_back({r.tag, 0, 0.0, 0.f, 0, 0.0});
+      idx = static_cast<int>(agg.size()) - 1;
+    }
+    agg[idx].n++;
+    agg[idx].ms += ms;
+    if (ms > agg[idx].mx) agg[idx].mx = ms;
+    each.emplace_back(idx, ms);
   }
+  for (auto& e : each)
+    if (e.second >= 0.5f * agg[e.first].mx) { agg[e.first].n_large++; agg[e.first].ms_large += e.second; }
   size_t off = 0;
   for (auto& a : agg) {
-    int w = snprintf(buf + off, off < cap ? cap - off : 0, "%s %lld %.6f\n", a.tag, a.n, a.ms);
+    int w = snprintf(buf + off, off < cap ? cap - off : 0, "%s %lld %.6f %lld %.6f\n", a.tag, a.n, a.ms, a.n_large, a.ms_large);
     if (w < 0 || off + w >= cap) break;
     off += w;
   }
