@@ -618,7 +618,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (p.nseg > 2 && out_col_tile >= p.seg[2].col_begin) si = 2;
         const EpiSeg& sg = p.seg[si];
         const bool plain = sg.vec && !sg.out_fp32 && sg.tma_slot < 0 && out_col_tile + BN <= sg.col_begin + sg.ncols &&
-                           p.col_bias == nullptr && p.row_stats == nullptr && !((p.mask_segs >> si) & 1) &&
+                           (reinterpret_cast<uintptr_t>(p.col_bias) & 15) == 0 && p.row_stats == nullptr &&
+                           !((p.mask_segs >> si) & 1) &&
                            (si != 0 || (p.gate == nullptr && p.resid == nullptr));
         if (plain) {
           __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(sg.dst) + static_cast<long long>(b) * sg.s_b +
@@ -630,6 +631,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             ptx::tmem_ld_32x32b_x32(t_row + c, r0);
             ptx::tmem_ld_32x32b_x32(t_row + c + 64, r1);
             ptx::tmem_ld_wait();
+            if (p.col_bias != nullptr) {   // per output column, the same for every row: uniform 16-byte loads
+              const float4* b0 = reinterpret_cast<const float4*>(p.col_bias + out_col_tile + c);
+              const float4* b1 = reinterpret_cast<const float4*>(p.col_bias + out_col_tile + c + 64);
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 u0 = __ldg(b0 + q4), u1 = __ldg(b1 + q4);
+                r0[4 * q4] = __float_as_uint(__uint_as_float(r0[4 * q4]) + u0.x);
+                r0[4 * q4 + 1] = __float_as_uint(__uint_as_float(r0[4 * q4 + 1]) + u0.y);
+                r0[4 * q4 + 2] = __float_as_uint(__uint_as_float(r0[4 * q4 + 2]) + u0.z);
+                r0[4 * q4 + 3] = __float_as_uint(__uint_as_float(r0[4 * q4 + 3]) + u0.w);
+                r1[4 * q4] = __float_as_uint(__uint_as_float(r1[4 * q4]) + u1.x);
+                r1[4 * q4 + 1] = __float_as_uint(__uint_as_float(r1[4 * q4 + 1]) + u1.y);
+                r1[4 * q4 + 2] = __float_as_uint(__uint_as_float(r1[4 * q4 + 2]) + u1.z);
+                r1[4 * q4 + 3] = __float_as_uint(__uint_as_float(r1[4 * q4 + 3]) + u1.w);
+              }
+            }
             uint32_t w0[16], w1[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
