@@ -534,19 +534,18 @@ def _rel_rms(a: torch.Tensor, b: torch.Tensor) -> float:
     return float((a - b).pow(2).mean().sqrt() / (b.pow(2).mean().sqrt() + 1e-30))
 
 
-def sharded_bytes_out(n: int, c: int, h: int, hs: int, p: int, channel: bool) -> int:
+def sharded_bytes_out(n: int, c: int, h: int, cs: int, p: int, channel: bool) -> int:
     """Bytes one rank sends to its peers during one row-sharded block (bf16): the operand exchanges of the two triangle
-    multiplications, the shard transposes of the incoming / ending-node operators, the gathered triangle and single-track
-    biases.  An all-gathered piece leaves the GPU once per peer."""
+    multiplications (incoming: always the channel form; outgoing: the channel form from four ranks on, else the all-gather
+    of b), the two shard transposes of the ending-node operator, the gathered triangle biases and the gathered rows of the
+    single track.  An all-gathered piece leaves the GPU once per peer."""
     shard = n * n * c * 2 // p                       # one rank's rows of a pair-sized tensor
     out_frac = (p - 1) / p
-    if channel:
-        trimul = 2 * (2 * shard + shard) * out_frac      # a and b out, t back: all-to-all
-    else:
-        trimul = 2 * shard * (p - 1)                     # all-gather of b
-    transposes = 3 * shard * out_frac                    # z^T for the incoming operator, z^T and the update back for the ending node
-    biases = (2 * h + hs) * (n * n * 2 // p) * (p - 1)   # two triangle biases and the single-track bias, all-gathered
-    return int(trimul + transposes + biases)
+    channel_form = (2 * shard + shard) * out_frac    # a and b out, t back: all-to-all
+    trimul = channel_form + (channel_form if channel else shard * (p - 1))
+    transposes = 2 * shard * out_frac                # the normalised rows and the update of the ending node
+    gathers = 2 * h * (n * n * 2 // p) * (p - 1) + (n * cs * 2 // p) * (p - 1)   # two triangle biases; the single track's rows
+    return int(trimul + transposes + gathers)
 
 
 def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
@@ -613,10 +612,10 @@ def measure_sharded(args, rank: int, world: int, dev, blk, barrier) -> dict:
     t = torch.tensor([ms, kernel_ms, ms_1gpu, ms_probe, ms_trunk, ms_trunk_1gpu], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, kernel_ms, ms_1gpu, ms_probe, ms_trunk, ms_trunk_1gpu = (float(v) for v in t)
-    out_bytes = sharded_bytes_out(n, C_Z, 4, 16, world, channel)
+    out_bytes = sharded_bytes_out(n, C_Z, 4, C_S, world, channel)
     bound_ms = out_bytes / (a2a_gbs * 1e9) * 1e3
     res.update(ms=round(ms, 3), ms_1gpu=round(ms_1gpu, 3), kernel_ms=round(kernel_ms, 3), comm_ms=round(ms - kernel_ms, 3),
-               exchange="channel all-to-all" if channel else "all-gather of b",
+               exchange="channel all-to-all" if channel else "outgoing: all-gather of b; incoming: channel all-to-all",
                speedup_vs_1gpu=round(ms_1gpu / ms, 3), trunk48_ms=round(ms_trunk, 2), trunk48_ms_1gpu=round(ms_trunk_1gpu, 2),
                trunk48_speedup=round(ms_trunk_1gpu / ms_trunk, 3), bytes_sent_per_rank=out_bytes,
                nccl_all_to_all_gbs_per_rank=round(a2a_gbs, 1), comm_bound_ms=round(bound_ms, 3),

@@ -319,6 +319,7 @@ class ShardedPairformerBlock:
         self.ops = ShardedPairOps(group)
         self.exchange = exchange
         self._trimul_packs = {}
+        self._apb_cross_pack = None
 
     def _pack_trimul(self, mod, dev, rows: int, incoming: bool):
         """Weights for the channel-sharded exchange when C divides by the number of ranks (packed once per module)."""
@@ -351,8 +352,32 @@ class ShardedPairformerBlock:
         z = ops.triatt_starting(z, pair_mask_loc, pk_s)
         z = ops.triatt_ending(z, pair_mask_loc, pk_e)
         z = b.transition_z(z, residual=True)
-        bias = ops.pair_bias(z, b.layernorm_z.weight.detach().float(), b.layernorm_z.bias.detach().float(),
-                             b.linear_pair_bias.weight.detach().to(dev, bf).contiguous(), b.layernorm_z.eps)
-        s = b.attention(s, None, bias.unsqueeze(0), mask, residual=True)
+        s = self._single_track(z, s, mask)
         s = b.transition(s, residual=True)
         return z, s
+
+    def _single_track(self, z_loc: torch.Tensor, s: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """s + SelfAttentionPairBias(s, bias from z): the single track is replicated, but its pair bias is not: every rank
+        projects the bias of its own rows, attends with its own rows as queries against all tokens as keys (the cross
+        form of the kernel) and the updated rows are all-gathered -- N x c_s values instead of the H x N x N bias."""
+        b, ops = self.block, self.ops
+        att = b.attention
+        dev = z_loc.device
+        bf = torch.bfloat16
+        rows, n, _ = z_loc.shape
+        if ops.world == 1 or rows % 8 != 0 or s.shape[0] != 1:
+            bias = ops.pair_bias(z_loc, b.layernorm_z.weight.detach().float(), b.layernorm_z.bias.detach().float(),
+                                 b.linear_pair_bias.weight.detach().to(dev, bf).contiguous(), b.layernorm_z.eps)
+            return att(s, None, bias.unsqueeze(0), mask, residual=True)
+        key = (id(att), dev)
+        if self._apb_cross_pack is None or self._apb_cross_pack[0] != key:
+            self._apb_cross_pack = (key, packing.pack_apb_cross(att.state_dict(), att.num_heads, dev))
+        pk = self._apb_cross_pack[1]
+        r0 = ops.rank * rows
+        bias_loc = F.pair_bias_rows(z_loc, b.layernorm_z.weight.detach().float(), b.layernorm_z.bias.detach().float(),
+                                    b.linear_pair_bias.weight.detach().to(dev, bf).contiguous(), b.layernorm_z.eps)   # (H, rows, N)
+        ln = att.layernorm_a
+        an = F.layer_norm(s, ln.weight, ln.bias, ln.eps, out_dtype=bf)                                              # (1, N, c_s)
+        upd = F.attention_pair_bias_cross(an[:, r0:r0 + rows].contiguous(), an, bias_loc.unsqueeze(0), mask.reshape(1, n), pk,
+                                          out_dtype=s.dtype, resid=s[:, r0:r0 + rows].contiguous())                # (1, rows, c_s)
+        return gather_rows(upd[0], ops.group).unsqueeze(0)
