@@ -101,8 +101,21 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int h = blockIdx.y;
   const int b0 = blockIdx.z * R;  // first batch entry of this CTA
   // window mode: a query block of 128 atoms = four windows sees the 256 atoms that start 48 before it (two key tiles)
-  const int nkv = WIN ? 2 : (p.lk + kBKV - 1) / kBKV;
-  const int nhalf = 2 * nkv;
+  // Half tiles of 64 keys to process.  Keys after the last valid key of this CTA's pair rows contribute exactly zero
+  // (the reference's finite -1e9 underflows in the exponential), so whole half tiles of them are skipped; a row without
+  // any valid key keeps the full range (its result is the uniform average over all keys, as in the reference).
+  int nhalf = WIN ? 4 : 2 * ((p.lk + kBKV - 1) / kBKV);
+  uint32_t* s_last = tmem_slot + 1;                   // [warps]: last valid key + 1 seen by each warp
+  constexpr bool kTrim = !WIN && R == 1;
+  if (kTrim) {
+    const int b_hi = b0 / p.mask_lo_extent, b_lo = b0 - b_hi * p.mask_lo_extent;
+    const unsigned char* mrow = p.mask + static_cast<long long>(b_hi) * p.m_hi + static_cast<long long>(b_lo) * p.m_lo;
+    int last = 0;
+    for (int k = threadIdx.x; k < p.lk; k += blockDim.x)
+      if (mrow[static_cast<long long>(k) * p.m_k]) last = k + 1;
+    last = __reduce_max_sync(0xffffffffu, last);
+    if (lane == 0) s_last[warp] = static_cast<uint32_t>(last);
+  }
   long long* trace = (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
 #ifdef KFB_DEBUG_TRACE
 #ifdef KFB_DEBUG_TRACE
@@ -161,6 +174,12 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (kTrim) {
+    uint32_t last = 0;
+    for (int wi = 0; wi < Cfg::kThreads / 32; ++wi) last = max(last, s_last[wi]);
+    if (last > 0) nhalf = max(2, (static_cast<int>(last) + 63) / 64);
+  }
+  const int nkv = (nhalf + 1) / 2;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -189,7 +208,7 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           ptx::tma_load_3d(s_v + slot * Cfg::kVBytes, &tm_v, &kv_full[slot], key_base + j * kBKV, h * DPAD, b0 + g);
           ptx::tma_load_3d(s_v + slot * Cfg::kVBytes + DPAD * 128, &tm_v, &kv_full[slot], key_base + j * kBKV + 64, h * DPAD, b0 + g);
         }
-        for (int hf = 0; ok && hf < 2; ++hf) {
+        for (int hf = 0; ok && hf < 2 && 2 * j + hf < nhalf; ++hf) {
           if (!ptx::mbar_wait(&bias_empty[bst], bpar ^ 1, 202)) { ok = false; break; }
           ptx::mbar_expect_tx(&bias_full[bst], Cfg::kTileBytes);
           if (WIN) {
@@ -242,7 +261,7 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&q_full[g], 0, 205) && ptx::mbar_wait(&init_ready[g], 0, 206)) &&
            issue_s(0, 0, 0, 0, 0) &&
            issue_s(1, 1, 0, 0, 0);
-      if (ok && nkv > 1) ok = issue_s(0, 2, 1 % kStages, (1 / kStages) & 1, 1);
+      if (ok && nhalf > 2) ok = issue_s(0, 2, 1 % kStages, (1 / kStages) & 1, 1);
       // half tile t lives in S buffer `buf` = t % 3 (use number `use` = t / 3) and in K/V stage `st` = (t / 2) % 3;
       // half tile t + 3 (issued below) belongs to tile j3 = (t + 3) / 2: stage st3 = j3 % 3, parity par3 = (j3 / 3) & 1
       int buf = 0, st = 0;
