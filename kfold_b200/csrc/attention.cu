@@ -170,6 +170,18 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       *reinterpret_cast<uint4*>(s_maskrow + u * Cfg::kSmallBytes + off + 128) = make_uint4(0, 0, 0, 0);
     ptx::fence_proxy_async_smem();
   }
+  // The mask bytes of the first two key tiles (the operands of S(0) .. S(3)) are fetched before the block-wide barrier by
+  // the threads that will store them: their latency runs under the tensor-memory allocation and the barrier.
+  int early_code0 = 2, early_code1 = 2;
+  if (!WIN && warp >= 4 && (((warp - 4) >> 2) & 1) == 0) {
+    const int g_ = (warp - 4) >> 3, r_ = (warp & 3) * 32 + lane, b_ = b0 + g_;
+    if (b_ < p.batch) {
+      const int b_hi = b_ / p.mask_lo_extent, b_lo = b_ - b_hi * p.mask_lo_extent;
+      const unsigned char* mrow_ = p.mask + static_cast<long long>(b_hi) * p.m_hi + static_cast<long long>(b_lo) * p.m_lo;
+      if (r_ < p.lk) early_code0 = mrow_[static_cast<long long>(r_) * p.m_k] ? 1 : 0;
+      if (kBKV + r_ < p.lk) early_code1 = mrow_[static_cast<long long>(kBKV + r_) * p.m_k] ? 1 : 0;
+    }
+  }
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
@@ -343,8 +355,8 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       *reinterpret_cast<uint4*>(my_maskrow + buf * Cfg::kSmallBytes) = v;
     };
     if (u == 0) {
-      store_mask_value(0, load_mask_byte(0));
-      if (nkv > 1) store_mask_value(1, load_mask_byte(1));
+      store_mask_value(0, WIN ? load_mask_byte(0) : early_code0);
+      if (nkv > 1) store_mask_value(1, WIN ? load_mask_byte(1) : early_code1);
       ptx::fence_proxy_async_smem();
       ptx::mbar_arrive(&init_ready[g]);
     }
@@ -479,6 +491,16 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // (with one row group per CTA the V stages follow the K stages directly and are just as free)
     static_assert(128 * (DPAD + 3) * 4 <= (R == 1 ? kStages * (Cfg::kKBytes + Cfg::kVBytes) : kStages * Cfg::kKBytes),
                   "exchange area does not fit in the K (and V) stages");
+    // the gate logits of this row are fetched now, under the wait for the last product and the exchange of the streams
+    const bool row_ok = q_idx < p.lq;  // rows past the end still take part in the warp-wide loads
+    const long long row = static_cast<long long>(b) * p.lq + (row_ok ? q_idx : 0);
+    const __nv_bfloat16* gp =
+        p.g != nullptr ? reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD : nullptr;
+    uint4 gate_raw[DPAD / 8];
+    if (u == 0 && gp != nullptr) {
+#pragma unroll
+      for (int i = 0; i < DPAD / 8; ++i) gate_raw[i] = *reinterpret_cast<const uint4*>(gp + i * 8);
+    }
     // the last P V product: then all of them are complete
     ok = ok && ptx::mbar_wait(&o_full[g * 3 + (nhalf - 1) % 3], ((nhalf - 1) / 3) & 1, 210);
     ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-wide: decide per warp
@@ -508,10 +530,6 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const float w_e = exp2f(s_cur - s_m), w_o = exp2f(s_o - s_m);
       const float inv_l = 1.0f / (l_run * w_e + l_o * w_o);
       const float c_e = w_e * inv_l, c_o = w_o * inv_l;
-      const bool row_ok = q_idx < p.lq;  // rows past the end still take part in the warp-wide loads
-      const long long row = static_cast<long long>(b) * p.lq + (row_ok ? q_idx : 0);
-      const __nv_bfloat16* gp =
-          p.g != nullptr ? reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD : nullptr;
       __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + h * p.d;
       {
 #pragma unroll
@@ -525,7 +543,7 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (gp != nullptr) {
 #pragma unroll
             for (int i = 0; i < 16; i += 8) {
-              const uint4 gu = *reinterpret_cast<const uint4*>(gp + cb * 16 + i);
+              const uint4 gu = gate_raw[cb * 2 + i / 8];
               const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
