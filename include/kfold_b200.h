@@ -76,7 +76,7 @@ KFB_API long long kfb_launch_count(void);
 /* Per-launch timing with CUDA events on the launch stream.  enable(1) clears old records and starts
  * recording, enable(0) stops.  report() waits for the recorded events and writes one text line per
  * launch tag: "<tag> <launches> <total_ms> <large launches> <their total_ms>\n", "large" = the launches that took at
- * least half as long as the tag's longest one (the pair-sized ones of a tag that also serves the single track).
+ * least half as long as the tag's upper-quartile launch (the pair-sized ones of a tag that also serves the single track).
  * Creates events while enabled; off by default. */
 KFB_API int kfb_profile_enable(int on);
 KFB_API int kfb_profile_report(char* buf, size_t cap);

@@ -205,7 +205,7 @@ def profile_enable(on: bool) -> None:
 
 def profile_report(detail: bool = False) -> dict:
     """{tag: (launches, total_ms)} for the launches recorded since profile_enable(True); with `detail`
-    {tag: (launches, total_ms, large launches, their total_ms)}, "large" = at least half as long as the tag's longest launch
+    {tag: (launches, total_ms, large launches, their total_ms)}, "large" = at least half as long as the tag's upper-quartile launch
     (tags shared by the pair tensor and the single track: the pair-sized launches)."""
     buf = ctypes.create_string_buffer(16384)
     check(lib().kfb_profile_report(buf, len(buf)))

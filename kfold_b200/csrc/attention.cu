@@ -186,12 +186,64 @@ attention_bias_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  bool uniform_row = false;   // no valid key in this pair row: every logit is the same finite -1e9, the result the mean of V
   if (kTrim) {
     uint32_t last = 0;
     for (int wi = 0; wi < Cfg::kThreads / 32; ++wi) last = max(last, s_last[wi]);
     if (last > 0) nhalf = max(2, (static_cast<int>(last) + 63) / 64);
+    uniform_row = (last == 0);
   }
   const int nkv = (nhalf + 1) / 2;
+
+  if (uniform_row) {
+    // ---------------------------------------------------------------- a pair row without valid keys (padding)
+    // The reference adds the same finite -1e9 to every logit of such a row; in float32 the logits then coincide (the
+    // spacing of floats at 1e9 is 64) and the softmax is uniform over all lk keys.  The pipeline below computes the same
+    // thing with P = 1 everywhere; here the mean of V is taken directly: DPAD rows of V^T, lk keys each.
+    float* s_mean = reinterpret_cast<float*>(s_q);                       // [DPAD]
+    const __nv_bfloat16* vrows = reinterpret_cast<const __nv_bfloat16*>(p.vt) +
+                                 (static_cast<long long>(b0) * p.heads * DPAD + static_cast<long long>(h) * DPAD) * p.ldv;
+    for (int dd = warp; dd < DPAD; dd += Cfg::kThreads / 32) {
+      const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(vrows + static_cast<long long>(dd) * p.ldv);
+      float acc = 0.f;
+      for (int k2 = lane; k2 < p.lk / 2; k2 += 32) {
+        const float2 f = __bfloat1622float2(vr[k2]);
+        acc += f.x + f.y;
+      }
+      if ((p.lk & 1) && lane == 0) acc += __bfloat162float(vrows[static_cast<long long>(dd) * p.ldv + p.lk - 1]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) s_mean[dd] = acc / static_cast<float>(p.lk);
+    }
+    __syncthreads();
+    if (threadIdx.x < kBQ) {
+      const int q_idx = qb * kBQ + threadIdx.x;
+      if (q_idx < p.lq) {
+        const long long row = static_cast<long long>(b0) * p.lq + q_idx;
+        const __nv_bfloat16* gp =
+            p.g != nullptr ? reinterpret_cast<const __nv_bfloat16*>(p.g) + row * p.ldg + p.g_col0 + h * DPAD : nullptr;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + h * p.d;
+        for (int dd = 0; dd < p.d; dd += 8) {   // d is a multiple of 8
+          float gs[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gs[i] = 1.0f;
+          if (gp != nullptr) {
+            const uint4 gu = *reinterpret_cast<const uint4*>(gp + dd);
+            const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              gs[2 * k] = sigmoidf_fast(__uint_as_float(gw[k] << 16));
+              gs[2 * k + 1] = sigmoidf_fast(__uint_as_float(gw[k] & 0xffff0000u));
+            }
+          }
+          uint32_t ow[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) ow[k] = pack_bf16x2(s_mean[dd + 2 * k] * gs[2 * k], s_mean[dd + 2 * k + 1] * gs[2 * k + 1]);
+          *reinterpret_cast<uint4*>(o + dd) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+      }
+    }
+  } else
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer

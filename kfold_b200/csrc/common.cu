@@ -5,6 +5,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <algorithm>
 #include <vector>
 
 #include "common.cuh"
@@ -69,7 +70,7 @@ void profile_enable(bool on) {
 }
 
 // Writes one line per tag: "<tag> <launches> <total_ms> <large launches> <their total_ms>\n", "large" = the launches that
-// took at least half as long as the tag's longest one (a tag such as the transition's serves the pair tensor and the much
+// took at least half as long as the tag's upper-quartile launch (a tag such as the transition's serves the pair tensor and the much
 // smaller single track: the large group is the pair-sized work).  Synchronises on the recorded events.
 int profile_report(char* buf, size_t cap) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
@@ -91,6 +92,15 @@ int profile_report(char* buf, size_t cap) {
     agg[idx].ms += ms;
     if (ms > agg[idx].mx) agg[idx].mx = ms;
     each.emplace_back(idx, ms);
+  }
+  // the reference duration of a tag is its upper quartile, not its maximum: one launch that was held up (a clock change, a
+  // neighbour on the GPU) must not make every other launch of the tag "small"
+  for (size_t i = 0; i < agg.size(); ++i) {
+    std::vector<float> v;
+    for (auto& e : each)
+      if (e.first == static_cast<int>(i)) v.push_back(e.second);
+    std::sort(v.begin(), v.end());
+    agg[i].mx = v.empty() ? 0.f : v[(v.size() * 3) / 4 < v.size() ? (v.size() * 3) / 4 : v.size() - 1];
   }
   for (auto& e : each)
     if (e.second >= 0.5f * agg[e.first].mx) { agg[e.first].n_large++; agg[e.first].ms_large += e.second; }
