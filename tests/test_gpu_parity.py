@@ -242,6 +242,29 @@ def test_triatt_config3_size(dev, starting):
     _check(mx, r, f"triatt starting={starting} everywhere")
 
 
+@pytest.mark.parametrize("starting", [True, False])
+@pytest.mark.parametrize("valid", [40, 70, 129, 200])
+def test_triatt_skipped_key_tiles_and_rows_without_keys(dev, starting, valid):
+    """Keys after a pair row's last valid key are skipped in half tiles of 64 (valid = 40: the minimum of two half tiles;
+    70, 129: an odd number of half tiles, the last key tile half used; 200: mid tile), rows without any valid key take
+    the mean of V: both against the oracle's plain softmax over all N keys.  A second, non-contiguous mask moves the last
+    valid key of some rows."""
+    from kfold_b200 import functional as F
+    from kfold_b200 import packing
+    import synth
+    n = 320
+    z, pm, _ = synth.pair_inputs(30 + valid, n, 128, 1, valid=valid)
+    w = synth.triatt_weights(synth._Rng(31), 128, 4)
+    pk = packing.pack_triatt(w, 4, dev)
+    zb = z.bfloat16()
+    for mask in (pm, pm & (torch.rand(pm.shape, generator=torch.Generator().manual_seed(valid)) > 0.3)):
+        out = F.triangle_attention(zb.to(dev), mask.to(dev), pk, starting).float().cpu()
+        ref = _oracle_on(dev, O.triangle_attention, zb.float(), mask, w, 4, starting)
+        assert torch.isfinite(out).all()
+        mx, r = err_stats(out, ref)
+        _check(mx, r, f"triatt starting={starting} valid={valid}")
+
+
 def test_ending_node_is_starting_node_on_the_transpose(dev):
     """Size-independent property at full size: ending(x, m) == starting(x^T, m^T)^T, bit for bit."""
     from kfold_b200 import functional as F
