@@ -19,7 +19,8 @@ pair representation z (N, N, C) by rows: rank r owns rows [r*N/P, (r+1)*N/P).  P
   triangle attention, ending node     starting node on the transposed shard, result transposed back; the three reorders
                                       around the two all-to-alls ride in the LayerNorm, the projection's operand strides and
                                       the output projection's store strides
-  single track / pair bias            bias rows all-gathered (one collective for all heads), single track replicated
+  single track / pair bias            bias rows stay local: every rank attends with its own rows as queries (cross form) and the
+                                      updated rows of the replicated single track are all-gathered
 
 Everything here is host-side orchestration: the kernels are the same ones the single-GPU path uses, called
 through the two-phase C entry points (kfb_trimul_project / _finish, kfb_triatt_project / _finish).
