@@ -74,8 +74,8 @@ def algorithmic_work(n: int | None = None, c: int = C_Z, h: int = 4, cs: int = C
 
 
 # DRAM traffic of the triangle-attention kernel from its ncu capture at N=384 (dram__bytes_read.sum +
-# dram__bytes_write.sum of one launch: 152.4 MB + 25.8 MB); it grows with the number of pair positions.
-NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 152.376576e6 + 26.054656e6,
+# dram__bytes_write.sum of one launch: 144.9 MB + 23.9 MB); it grows with the number of pair positions.
+NCU_TRAFFIC = {"triatt_attention": {"n": 384, "bytes": 144.919040e6 + 23.904512e6,
                                      "source": "ncu capture at N=384 scaled by pair positions (profiles/triatt_attention_n384_ncu.md)"}}
 
 
