@@ -14,7 +14,6 @@ import torch
 from torch import nn
 
 from . import functional as F
-from . import packing
 from .modules import (LayerNorm, LinearNoBias, SelfAttentionPairBias, Transition, TriangularBlock, _check_inference, _is_precise,
                       _ProjectionCache, compute_dtype)
 

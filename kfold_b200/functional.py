@@ -7,7 +7,6 @@ and the extension must be built.
 """
 from __future__ import annotations
 
-import ctypes
 
 import torch
 
