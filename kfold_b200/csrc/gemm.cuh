@@ -510,6 +510,51 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int ch = out_col_tile + r;  // output channel of this lane
         __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(sg.dst) + static_cast<long long>(ch) * sg.s_col +
                               static_cast<long long>(b) * sg.s_b + static_cast<long long>(o) * sg.s_o;
+        bool swap_done = false;
+        if (p.swap_staged) {
+          // staged tile: the lane's 64 positions go by as four pieces of 16, the tensor-memory load of the next piece issued
+          // before the arithmetic of the current one (one exposed round trip per tile instead of two)
+          constexpr int kPieces = 2 * (kBM / (32 * (kEpiWarps / 4)));
+          uint8_t* buf = s_stage_out + 1024 + (rm_use & 1) * Cfg::kRowTileBytes;
+          auto piece_col = [&](int i) { return chunk_phase * 32 + (i >> 1) * (32 * (kEpiWarps / 4)) + (i & 1) * 16; };
+          uint32_t va[16], ga[16], vb[16], gb[16];
+          ptx::tmem_ld_32x32b_x16(t_row + piece_col(0), va);
+          ptx::tmem_ld_32x32b_x16(t_row + 128 + piece_col(0), ga);
+          auto finish_piece = [&](int c, const uint32_t (&vv)[16], const uint32_t (&gg)[16]) {
+            uint32_t w[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 m4 = *reinterpret_cast<const float4*>(s_maskf + c + 4 * q);
+              const float mk4[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+              for (int i = 0; i < 4; i += 2)
+                w[q * 2 + (i >> 1)] =
+                    pack_bf16x2(glu_half(__uint_as_float(vv[4 * q + i]), __uint_as_float(gg[4 * q + i])) * mk4[i],
+                                glu_half(__uint_as_float(vv[4 * q + i + 1]), __uint_as_float(gg[4 * q + i + 1])) * mk4[i + 1]);
+            }
+            uint8_t* rowp = buf + (c >> 6) * (Cfg::kRowTileBytes / 2) + r * 128;
+            const int piece = (c & 63) >> 3;
+            *reinterpret_cast<uint4*>(rowp + (((piece) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(rowp + (((piece + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+          };
+#pragma unroll
+          for (int i = 0; i < kPieces; i += 2) {
+            ptx::tmem_ld_wait();
+            if (i + 1 < kPieces) {
+              ptx::tmem_ld_32x32b_x16(t_row + piece_col(i + 1), vb);
+              ptx::tmem_ld_32x32b_x16(t_row + 128 + piece_col(i + 1), gb);
+            }
+            finish_piece(piece_col(i), va, ga);
+            ptx::tmem_ld_wait();
+            if (i + 2 < kPieces) {
+              ptx::tmem_ld_32x32b_x16(t_row + piece_col(i + 2), va);
+              ptx::tmem_ld_32x32b_x16(t_row + 128 + piece_col(i + 2), ga);
+            }
+            if (i + 1 < kPieces) finish_piece(piece_col(i + 1), vb, gb);
+          }
+          swap_done = true;
+        }
+        if (!swap_done)
 #pragma unroll 1
         for (int c = chunk_phase * 32; c < kBM; c += 32 * (kEpiWarps / 4)) {
           uint32_t raw[32], rawg[32];
@@ -608,9 +653,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       } else {
       // Fast path of the plain kernel: a tile that lies inside one row-major bf16 segment and needs nothing but the
-      // conversion (the q / k / g columns of the attention projections, plain projections).  The warp's two 32-column
-      // chunks are fetched from tensor memory together and stored with 32-byte stores: one tensor-memory round trip and
-      // none of the per-chunk bookkeeping of the general loop below.
+      // conversion and a column bias (the q / k / g columns of the attention projections, plain projections): none of the
+      // per-chunk bookkeeping of the general loop below.
       bool tile_done = false;
       if constexpr (!GLU && !AUX && !PRECISE && BN >= 128) {
         int si = 0;
@@ -712,6 +756,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const EpiSeg& s0 = p.seg[0];
         glu_staged = p.rm_seg == 0 && out_col_tile >= s0.col_begin && out_col_tile + out_bn <= s0.col_begin + s0.ncols &&
                      (p.nseg == 1 || out_col_tile + out_bn <= p.seg[1].col_begin);
+      }
+      // Staged GLU tile without mask, bias, statistics, gate or residual (the transitions' SwiGLU): the warp's two 32-column
+      // chunks go by as four pieces of 16 columns, the tensor-memory load of the next piece issued before the arithmetic of
+      // the current one (a `tcgen05.wait::ld` then finds it done), so that one round trip per tile is exposed instead of two.
+      if constexpr (GLU && !AUX && !PRECISE && BN == 256) {
+        if (glu_staged && p.col_bias == nullptr && p.row_stats == nullptr && !(p.mask_segs & 1) && p.gate == nullptr &&
+            p.resid == nullptr) {
+          constexpr int kPieces = 2 * (OUT_BN_GLU / (32 * (kEpiWarps / 4)));   // 16-column pieces of this warp: 4
+          uint8_t* buf = s_stage_out + (rm_use & 1) * Cfg::kRowTileBytes;
+          auto piece_col = [&](int i) { return chunk_phase * 32 + (i >> 1) * (32 * (kEpiWarps / 4)) + (i & 1) * 16; };
+          uint32_t va[16], ga[16], vb[16], gb[16];
+          ptx::tmem_ld_32x32b_x16(t_row + piece_col(0), va);
+          ptx::tmem_ld_32x32b_x16(t_row + OUT_BN_GLU + piece_col(0), ga);
+          const bool swiglu = p.glu != GLU_SIGMOID;
+          auto finish_piece = [&](int c, const uint32_t (&vv)[16], const uint32_t (&gg)[16]) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float a0 = __uint_as_float(vv[i]), a1 = __uint_as_float(vv[i + 1]);
+              const float g0 = __uint_as_float(gg[i]), g1 = __uint_as_float(gg[i + 1]);
+              const float r0 = swiglu ? glu_half(a0, a0) * g0 : glu_half(a0, g0);
+              const float r1 = swiglu ? glu_half(a1, a1) * g1 : glu_half(a1, g1);
+              w[i >> 1] = pack_bf16x2(r0, r1);
+            }
+            uint8_t* rowp = buf + (c >> 6) * (Cfg::kRowTileBytes / 2) + r * 128;
+            const int piece = (c & 63) >> 3;
+            *reinterpret_cast<uint4*>(rowp + (((piece) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(rowp + (((piece + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+          };
+#pragma unroll
+          for (int i = 0; i < kPieces; i += 2) {
+            ptx::tmem_ld_wait();
+            if (i + 1 < kPieces) {
+              ptx::tmem_ld_32x32b_x16(t_row + piece_col(i + 1), vb);
+              ptx::tmem_ld_32x32b_x16(t_row + OUT_BN_GLU + piece_col(i + 1), gb);
+            }
+            finish_piece(piece_col(i), va, ga);
+            ptx::tmem_ld_wait();
+            if (i + 2 < kPieces) {
+              ptx::tmem_ld_32x32b_x16(t_row + piece_col(i + 2), va);
+              ptx::tmem_ld_32x32b_x16(t_row + OUT_BN_GLU + piece_col(i + 2), ga);
+            }
+            if (i + 1 < kPieces) finish_piece(piece_col(i + 1), vb, gb);
+          }
+          tile_done = true;
+        }
       }
       if (!tile_done)
 #pragma unroll 1
