@@ -53,7 +53,7 @@ def _worker(rank: int, world: int, port: int, n: int, exchange: str, q):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("exchange", ["gather", "channel"])
-@pytest.mark.parametrize("n", [256, 384])
+@pytest.mark.parametrize("n", [128, 256, 384])
 def test_sharded_block_matches_single_gpu(n, exchange):
     """Both exchanges of the triangle multiplication: the all-gather of b and the channel-sharded all-to-all."""
     world = 2
