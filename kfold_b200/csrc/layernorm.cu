@@ -657,12 +657,59 @@ __global__ void __launch_bounds__(256) cm_stats_kernel(const __nv_bfloat16* __re
   if (pair) stats[p2 + 1] = make_float2(x01 + m1, rsqrtf(fmaxf(q1 - s1 * m1, 0.f) * inv_c + eps));
 }
 
+// The same with four positions per thread (8-byte loads): half as many CTAs, all resident at once for a 768 x 768 pair
+// tensor, and twice the bytes in flight per thread.  npos and the channel stride multiples of 4, t 8-byte aligned.
+__global__ void __launch_bounds__(128) cm_stats4_kernel(const __nv_bfloat16* __restrict__ t, float2* __restrict__ stats,
+                                                        long long npos, int c, long long chan_stride, float eps) {
+  const long long p4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (p4 >= npos) return;
+  float s[4] = {0.f, 0.f, 0.f, 0.f}, q[4] = {0.f, 0.f, 0.f, 0.f}, x0[4];
+  {
+    const uint2 w = *reinterpret_cast<const uint2*>(t + p4);
+    x0[0] = __uint_as_float(w.x << 16);
+    x0[1] = __uint_as_float(w.x & 0xffff0000u);
+    x0[2] = __uint_as_float(w.y << 16);
+    x0[3] = __uint_as_float(w.y & 0xffff0000u);
+  }
+#pragma unroll 8
+  for (int ch = 0; ch < c; ++ch) {
+    const uint2 w = *reinterpret_cast<const uint2*>(t + ch * chan_stride + p4);
+    const float v[4] = {__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                        __uint_as_float(w.y & 0xffff0000u)};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float d = v[i] - x0[i];
+      s[i] += d;
+      q[i] = fmaf(d, d, q[i]);
+    }
+  }
+  const float inv_c = 1.0f / static_cast<float>(c);
+  float4 o[2];
+  float* of = reinterpret_cast<float*>(o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float m = s[i] * inv_c;
+    of[2 * i] = x0[i] + m;
+    of[2 * i + 1] = rsqrtf(fmaxf(q[i] - s[i] * m, 0.f) * inv_c + eps);
+  }
+  float4* dst = reinterpret_cast<float4*>(stats + p4);
+  dst[0] = o[0];
+  dst[1] = o[1];
+}
+
 int launch_cm_stats(cudaStream_t stream, const __nv_bfloat16* t, float2* stats, long long npos, int c, long long chan_stride,
                     float eps) {
   KFB_CHECK_ARG(npos > 0 && npos % 2 == 0 && c > 0 && chan_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(t) & 3) == 0,
                 "cm_stats: npos %lld (even), c %d, channel stride %lld (even)", npos, c, chan_stride);
-  const long long threads = npos / 2;
   LaunchScope scope(stream, "layernorm_cm_stats");
+  if (npos % 4 == 0 && chan_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(t) & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(stats) & 15) == 0) {
+    const long long threads4 = npos / 4;
+    cm_stats4_kernel<<<static_cast<unsigned>((threads4 + 127) / 128), 128, 0, stream>>>(t, stats, npos, c, chan_stride, eps);
+    KFB_CUDA(cudaGetLastError());
+    return KFB_OK;
+  }
+  const long long threads = npos / 2;
   cm_stats_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(t, stats, npos, c, chan_stride, eps);
   KFB_CUDA(cudaGetLastError());
   return KFB_OK;
