@@ -87,6 +87,23 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   int bn = force_bn;
   if (bn == 0) bn = p.n_cols >= 256 ? 256 : (p.n_cols > 64 ? 128 : 64);
   if (p.precise && bn > 128) bn = 128;  // the fp32-accurate variant keeps four accumulators in tensor memory
+  // One row-major float32 segment with a gate and / or a residual (the output projections of the sampler's float32 activation
+  // stream): 128-column tiles whose epilogue moves gate, residual and output through per-warp shared-memory tiles.
+  p.xpose = 0;
+  if (!p.precise && !p.glu && force_bn == 0 && bn >= 128 && p.nseg == 1 && a.s_k == 0 && a.k_inner == 0 && b.col_inner == 0 &&
+      (p.gate != nullptr || p.resid != nullptr) && p.resid_scale == nullptr) {
+    const EpiSeg& sg = p.seg[0];
+    const bool seg_ok = sg.out_fp32 && sg.vec && sg.s_col == 1 && sg.col_begin == 0 && !sg.split && sg.ncols % 32 == 0 &&
+                        sg.s_n % 4 == 0 && sg.s_o % 4 == 0 && sg.s_b % 4 == 0 &&
+                        (p.resid == nullptr || (reinterpret_cast<uintptr_t>(p.resid) & 15) == 0);
+    const bool gate_ok = p.gate == nullptr ||
+                         (p.g_col == 1 && (reinterpret_cast<uintptr_t>(p.gate) & 15) == 0 && p.g_n % 8 == 0 && p.g_o % 8 == 0 &&
+                          p.g_b % 8 == 0);
+    if (seg_ok && gate_ok) {
+      p.xpose = 1;
+      bn = 128;
+    }
+  }
   KFB_CHECK_ARG(bn == 64 || bn == 128 || bn == 256, "unsupported BN %d", bn);
   if (p.precise) KFB_CHECK_ARG(p.k_extent % 6 == 0, "precise GEMM: K=%d is not six equal parts", p.k_extent);
   if (p.glu) KFB_CHECK_ARG(p.n_cols % bn == 0, "GLU GEMM needs n_cols (%d) to be a multiple of the N tile (%d)", p.n_cols, bn);
@@ -196,8 +213,8 @@ int launch_gemm_bf16(cudaStream_t stream, const GemmOperandA& a, const GemmOpera
   p.aux = 0;
   p.aux_gate = 0;
   p.aux_resid = 0;
-  if (!p.precise && next_slot == 0 && p.nseg == 1 && p.seg[0].vec && (p.gate != nullptr || p.resid != nullptr) && bn >= 64 &&
-      p.n_cols % 32 == 0 && !p.glu) {
+  if (!p.precise && !p.xpose && next_slot == 0 && p.nseg == 1 && p.seg[0].vec && (p.gate != nullptr || p.resid != nullptr) &&
+      bn >= 64 && p.n_cols % 32 == 0 && !p.glu) {
     const EpiSeg& sg = p.seg[0];
     bool ok_g = true, ok_r = true;
     if (p.gate != nullptr)

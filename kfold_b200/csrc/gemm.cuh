@@ -54,6 +54,9 @@ struct GemmParams {
   int swap_staged;                // launcher: the swapped GLU tile leaves through shared memory and TMA stores (map tm_out0)
   int rm_seg, rm_slot;            // launcher: segment whose full tiles leave through shared memory and a TMA store (row-major
                                   // bf16; BN = 128 plain kernel), and the output map it uses; rm_seg < 0: none
+  int xpose;                      // launcher (BN = 128 plain kernel, one row-major float32 segment with gate / residual):
+                                  // every warp moves its 32 x 32 chunk of gate, residual and output through a private
+                                  // shared-memory tile, so that global memory sees whole 128-byte rows
   int glu;                        // GluMode; with GLU a BN tile holds BN/2 values then BN/2 gates
   int swap;                       // launcher: channel-major GLU output computed in the swapped orientation (see SWAP)
   int a_mn_major;                 // launcher: the A operand is stored K-outer ([k][row], rows contiguous) and read MN-major
@@ -807,6 +810,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll 1
       for (int c = chunk_phase * 32; c < out_bn; c += 32 * (kEpiWarps / 4)) {
         const int out_col = out_col_tile + c;
+        // Float32 row-major output with gate / residual (the sampler's output projections): a thread owns one row, so its
+        // 16-byte accesses to global memory would touch 32 different 128-byte lines per warp instruction.  Instead the warp
+        // copies the chunk's gate logits (32 rows x 64 bytes) and residual (32 rows x 128 bytes) into its own shared-memory
+        // tile with lane-contiguous asynchronous copies, issued here so that they fly under the tensor-memory load, and
+        // writes the result back the same way.  Only warp-level synchronisation is involved.
+        bool xp = false;
+        uint8_t* xp_res = nullptr;
+        uint8_t* xp_gate = nullptr;
+        if constexpr (BN == 128 && !GLU && !AUX && !PRECISE) {
+          xp = p.xpose != 0 && out_col + 32 <= p.seg[0].ncols;   // uniform across the warp
+          if (xp) {
+            const EpiSeg& s0 = p.seg[0];
+            xp_res = s_stage_out + (warp - 2) * 6144;
+            xp_gate = xp_res + 4096;
+            const int n_first = nb * kBM + quad * 32;
+            if (p.resid != nullptr) {
+              const float* rbase = reinterpret_cast<const float*>(p.resid) + static_cast<long long>(b) * s0.s_b +
+                                   static_cast<long long>(o) * s0.s_o + out_col;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + (lane >> 3), pc = lane & 7;
+                if (n_first + rr < p.n_extent)
+                  ptx::cp_async_16(xp_res + rr * 128 + ((pc ^ (rr & 7)) << 4),
+                                   rbase + static_cast<long long>(n_first + rr) * s0.s_n + pc * 4);
+              }
+            }
+            if (p.gate != nullptr) {
+              const __nv_bfloat16* gbase = p.gate + static_cast<long long>(b) * p.g_b + static_cast<long long>(o) * p.g_o + out_col;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = i * 8 + (lane >> 2), pc = lane & 3;
+                if (n_first + rr < p.n_extent)
+                  ptx::cp_async_16(xp_gate + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4),
+                                   gbase + static_cast<long long>(n_first + rr) * p.g_n + pc * 8);
+              }
+            }
+          }
+        }
         float v[32];
         if (GLU && !PRECISE) {
           // value and gate columns are fetched together: one round trip to tensor memory per chunk
@@ -924,6 +965,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         const long long row_off = static_cast<long long>(b) * sg.s_b + static_cast<long long>(o) * sg.s_o +
                                   static_cast<long long>(n) * sg.s_n;
+        if constexpr (BN == 128 && !GLU && !AUX && !PRECISE) {
+          if (xp) {
+            const int rl = lane;   // this thread's row within the warp's 32
+            ptx::cp_async_wait_all();
+            __syncwarp();
+            if (p.gate != nullptr) {
+              const uint8_t* grow = xp_gate + rl * 64;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 u = *reinterpret_cast<const uint4*>(grow + ((q ^ ((rl >> 1) & 3)) << 4));
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                  v[q * 8 + j * 2] *= sigmoidf_fast(f.x);
+                  v[q * 8 + j * 2 + 1] *= sigmoidf_fast(f.y);
+                }
+              }
+            }
+            uint8_t* rrow = xp_res + rl * 128;
+            if (p.resid != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 f = *reinterpret_cast<const float4*>(rrow + ((q ^ (rl & 7)) << 4));
+                v[q * 4] = fmaf(f.x, 1.0f, v[q * 4]); v[q * 4 + 1] = fmaf(f.y, 1.0f, v[q * 4 + 1]);
+                v[q * 4 + 2] = fmaf(f.z, 1.0f, v[q * 4 + 2]); v[q * 4 + 3] = fmaf(f.w, 1.0f, v[q * 4 + 3]);
+              }
+            }
+            // every thread writes its own row; below, eight lanes share a row
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(rrow + ((q ^ (rl & 7)) << 4)) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            __syncwarp();
+            {
+              const int n_first = nb * kBM + quad * 32;
+              float* obase = reinterpret_cast<float*>(sg.dst) + static_cast<long long>(b) * sg.s_b +
+                             static_cast<long long>(o) * sg.s_o + col_local;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + (lane >> 3), pc = lane & 7;
+                const float4 f = *reinterpret_cast<const float4*>(xp_res + rr * 128 + ((pc ^ (rr & 7)) << 4));
+                if (n_first + rr < p.n_extent)
+                  *reinterpret_cast<float4*>(obase + static_cast<long long>(n_first + rr) * sg.s_n + pc * 4) = f;
+              }
+            }
+            __syncwarp();   // the tile is free for the next chunk's copies
+            continue;
+          }
+        }
         if (AUX && si == 0) {
           // gate logits and residual come from the tiles the producer prefetched (128-byte swizzled rows)
           const uint8_t* rowp = aux_tile + (c >> 6) * (kBM * 128) + r * 128;
